@@ -1,0 +1,178 @@
+"""Generate the golden fixtures in this folder by EXECUTING reference code.
+
+Run once, in a container that has the reference checkout (it cannot travel to
+the GPU box, so the resulting ``.npz`` files are committed)::
+
+    python tests/golden/make_golden.py --reference /path/to/VeloxQuant-MLX
+
+What is executed from the reference, unmodified:
+
+* ``veloxquant_mlx/dsa/bit_pack.py`` and ``veloxquant_mlx/math/rotation.py``
+  are MLX-free and are loaded whole with ``importlib``.
+* The reference's test files hold the authors' own NumPy statements of the
+  kernels' math, but import ``mlx`` at module top. Their pure-NumPy functions
+  (``_quant_keys``, ``_quant_values``, ``_reference_attend``, ``_make_inputs``,
+  ``_wht_butterfly``, ``_reference_encode``, ``_pack_np`` ...) are pulled out
+  of the parsed source by name and executed as they stand, with only ``np``
+  and ``math`` in scope.
+* ``walsh_hadamard_matrix`` and ``_pack_signs`` are pulled the same way from
+  ``allocators/vecinfer.py`` / ``quantizers/rabitq.py`` (both NumPy-only
+  bodies inside MLX-importing modules).
+
+Nothing here imports the oracle: the fixtures are the reference's outputs and
+the oracle is checked against them by ``tests/test_oracle_golden.py``.
+"""
+
+from __future__ import annotations
+
+import argparse
+import ast
+import importlib.util
+import math
+import os
+
+import numpy as np
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def load_module(path: str, name: str):
+    spec = importlib.util.spec_from_file_location(name, path)
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod
+
+
+def extract_functions(path: str, names, extra_ns=None):
+    """Exec the named top-level ``def``s of ``path`` with np/math in scope."""
+    with open(path, "r", encoding="utf-8") as fh:
+        tree = ast.parse(fh.read(), filename=path)
+    wanted = [n for n in tree.body if isinstance(n, ast.FunctionDef) and n.name in names]
+    missing = set(names) - {n.name for n in wanted}
+    if missing:
+        raise RuntimeError(f"{path}: functions not found: {sorted(missing)}")
+    mod = ast.Module(body=wanted, type_ignores=[])
+    ns = {"np": np, "math": math, "__name__": "ref_extract"}
+    if extra_ns:
+        ns.update(extra_ns)
+    exec(compile(mod, path, "exec"), ns)
+    return ns
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--reference", default="/root/reference")
+    args = ap.parse_args()
+    R = args.reference
+    pkg = os.path.join(R, "veloxquant_mlx")
+
+    # ---------------- bit packing (whole module) ----------------
+    bp = load_module(os.path.join(pkg, "dsa", "bit_pack.py"), "ref_bit_pack")
+    rng = np.random.default_rng(1234)
+    out = {}
+    for b in (1, 2, 3, 4):
+        for n in (8, 13, 64, 257):
+            vals = rng.integers(0, 1 << b, n, dtype=np.uint8)
+            packed = bp.BitPackBuffer(b).pack(vals)
+            out[f"b{b}_n{n}_vals"] = vals
+            out[f"b{b}_n{n}_packed"] = packed
+    ka = bp.BitPackBuffer(2).pack(np.array([0, 1, 2, 3, 0, 1, 2, 3], dtype=np.uint8))
+    assert ka.tolist() == [228, 228]
+    out["known_answer_2bit"] = ka
+    np.savez_compressed(os.path.join(HERE, "bitpack.npz"), **out)
+
+    # ---------------- KIVI quant + attend (test-file NumPy functions) ----------------
+    tsa = os.path.join(pkg, "tests", "metal", "test_scalar_attend.py")
+    ns = extract_functions(tsa, ["_quant_keys", "_quant_values", "_reference_attend", "_make_inputs"])
+    out = {}
+    cases = [
+        # name, B, H, S_kv, D, b, g, seed, H_kv
+        ("mha_b2", 1, 4, 64, 128, 2, 32, 0, None),
+        ("mha_b3", 1, 4, 96, 128, 3, 32, 3, None),
+        ("mha_b4", 1, 2, 64, 64, 4, 32, 4, None),
+        ("gqa_b2", 2, 8, 160, 128, 2, 32, 0, 2),
+        ("ragged_b4", 1, 2, 50, 96, 4, 32, 7, None),
+        ("g4_b1", 1, 2, 33, 32, 1, 4, 9, None),
+        ("g128_b8", 1, 1, 200, 128, 8, 128, 11, None),
+    ]
+    names = []
+    for name, B, H, S_kv, D, b, g, seed, H_kv in cases:
+        q, kc, ks, kz, vc, vs, vz = ns["_make_inputs"](B, H, S_kv, D, b, g, seed=seed, H_kv=H_kv)
+        ref = ns["_reference_attend"](q, kc, ks, kz, vc, vs, vz, g, 1.0 / math.sqrt(D))
+        for k, v in dict(q=q, kc=kc, ks=ks, kz=kz, vc=vc, vs=vs, vz=vz, out=ref).items():
+            out[f"{name}_{k}"] = v
+        out[f"{name}_meta"] = np.array([B, H, S_kv, D, b, g, seed, -1 if H_kv is None else H_kv])
+        names.append(name)
+    out["names"] = np.array(names)
+    # special values the reference's own tests pin (tests/metal/test_kivi_quant.py:121-159)
+    const = np.full((1, 1, 32, 8), 3.5, dtype=np.float32)
+    c, s, z = ns["_quant_keys"](const, 32, 3)
+    out["const_kc"], out["const_ks"], out["const_kz"] = c, s, z
+    integer_tile = np.tile(np.array([0, 1, 2, 3], dtype=np.float32), 8).reshape(1, 1, 1, 32)
+    c, s, z = ns["_quant_values"](integer_tile, 32, 2)  # half-even case: levels=2
+    out["halfeven_vc"], out["halfeven_vs"], out["halfeven_vz"] = c, s, z
+    out["halfeven_in"] = integer_tile
+    np.savez_compressed(os.path.join(HERE, "kivi.npz"), **out)
+
+    # ---------------- RaBitQ ----------------
+    tre = os.path.join(pkg, "tests", "metal", "test_rabitq_encode.py")
+    ns_e = extract_functions(tre, ["_wht_butterfly", "_reference_encode", "_make_inputs"])
+    tra = os.path.join(pkg, "tests", "metal", "test_rabitq_attend.py")
+    ns_a = extract_functions(tra, ["_reference_attend", "_make_inputs"])
+    trv = os.path.join(pkg, "tests", "metal", "test_rabitq_values.py")
+    ns_v = extract_functions(trv, ["_pack_np"])
+    ns_s = extract_functions(os.path.join(pkg, "quantizers", "rabitq.py"), ["_pack_signs"])
+    rot = load_module(os.path.join(pkg, "math", "rotation.py"), "ref_rotation")
+    out = {}
+    for N, D, seed in [(1, 8, 0), (33, 64, 1), (64, 128, 2), (17, 256, 3)]:
+        keys, diag = ns_e["_make_inputs"](N, D, seed=seed)
+        bits, mag = ns_e["_reference_encode"](keys, diag)
+        tag = f"enc_N{N}_D{D}"
+        out[f"{tag}_keys"], out[f"{tag}_diag"] = keys, diag
+        out[f"{tag}_bits"], out[f"{tag}_mag"] = bits, mag
+    for B, H, S_q, S_kv, D, seed in [(1, 1, 1, 33, 64, 5), (2, 2, 1, 256, 128, 6), (1, 2, 4, 64, 256, 99)]:
+        q, q_scale, k_bits, k_mag, k_const, v_idx, v_cents = ns_a["_make_inputs"](B, H, S_q, S_kv, D, seed=seed)
+        ref = ns_a["_reference_attend"](q, q_scale, k_bits, k_mag, k_const, v_idx, v_cents)
+        tag = f"att_B{B}_H{H}_Sq{S_q}_S{S_kv}_D{D}"
+        for k, v in dict(q=q, q_scale=q_scale, k_bits=k_bits, k_mag=k_mag, k_const=k_const,
+                         v_idx=v_idx, v_cents=v_cents, out=ref, v_packed=ns_v["_pack_np"](v_idx)).items():
+            out[f"{tag}_{k}"] = v
+    resid = np.random.default_rng(8).standard_normal((5, 64)).astype(np.float32)
+    out["signs_in"], out["signs_out"] = resid, ns_s["_pack_signs"](resid)
+    for d, seed in [(64, 42), (128, 42), (128, 7)]:
+        out[f"diag_d{d}_s{seed}"] = rot.make_hadamard_diagonal(d, seed=seed)
+    out["rot_d24_s42"] = rot.make_rotation_matrix(24, seed=42)
+    out["rot_d128_s42"] = rot.make_rotation_matrix(128, seed=42).astype(np.float32)
+    np.savez_compressed(os.path.join(HERE, "rabitq.npz"), **out)
+
+    # ---------------- VecInfer pieces that are NumPy in the reference ----------------
+    ns_w = extract_functions(os.path.join(pkg, "allocators", "vecinfer.py"), ["walsh_hadamard_matrix"],
+                             extra_ns={"mx": _MxShim()})
+    out = {}
+    for d in (1, 2, 8, 128):
+        out[f"wht_{d}"] = np.asarray(ns_w["walsh_hadamard_matrix"](d))
+    np.savez_compressed(os.path.join(HERE, "vq.npz"), **out)
+    print("golden fixtures written to", HERE)
+
+
+class _NdView(np.ndarray):
+    """ndarray with MLX's ``astype`` spelling; used only so that
+    ``mx.array(H).astype(dtype)`` at the end of ``walsh_hadamard_matrix`` runs."""
+
+    def astype(self, dtype, *a, **k):  # noqa: D401
+        return np.asarray(self, dtype=np.float32)
+
+
+class _MxShim:
+    """Just enough of ``mx`` for ``walsh_hadamard_matrix``'s final cast: the
+    matrix itself is built with NumPy inside the reference function."""
+
+    float32 = np.float32
+
+    @staticmethod
+    def array(a):
+        return np.asarray(a).view(_NdView)
+
+
+if __name__ == "__main__":
+    main()

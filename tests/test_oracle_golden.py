@@ -1,0 +1,203 @@
+"""The oracle against fixtures produced by executing the reference's own code
+(``tests/golden/make_golden.py``) and against the reference's known answers."""
+
+from __future__ import annotations
+
+import math
+import os
+
+import numpy as np
+import pytest
+
+from oracle import bitpack, kivi, rabitq, vq
+
+GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+
+
+def _load(name):
+    return np.load(os.path.join(GOLDEN, name))
+
+
+# ----------------------------------------------------------------- bit packing
+def test_bitpack_known_answer():
+    # reference: tests/metal/test_worker_kernel_parity.py:18-30
+    got = bitpack.pack(np.array([0, 1, 2, 3, 0, 1, 2, 3], dtype=np.uint8), 2)
+    assert got.tolist() == [228, 228]
+    assert _load("bitpack.npz")["known_answer_2bit"].tolist() == [228, 228]
+
+
+@pytest.mark.parametrize("b", [1, 2, 3, 4])
+@pytest.mark.parametrize("n", [8, 13, 64, 257])
+def test_bitpack_matches_reference_module(b, n):
+    z = _load("bitpack.npz")
+    vals, packed = z[f"b{b}_n{n}_vals"], z[f"b{b}_n{n}_packed"]
+    np.testing.assert_array_equal(bitpack.pack(vals, b), packed)
+    np.testing.assert_array_equal(bitpack.unpack(packed, b, n), vals)
+
+
+@pytest.mark.parametrize("b", range(1, 9))
+def test_bitpack_roundtrip_any_width(b):
+    rng = np.random.default_rng(b)
+    vals = rng.integers(0, 1 << b, (3, 5, 77), dtype=np.uint8)
+    np.testing.assert_array_equal(bitpack.unpack(bitpack.pack(vals, b), b, 77), vals)
+
+
+# ------------------------------------------------------------------------ KIVI
+def _kivi_cases():
+    z = _load("kivi.npz")
+    return [str(n) for n in z["names"]]
+
+
+@pytest.mark.parametrize("name", _kivi_cases())
+def test_kivi_quant_bit_exact_with_reference_numpy(name):
+    z = _load("kivi.npz")
+    B, H, S_kv, D, b, g, seed, H_kv = [int(v) for v in z[f"{name}_meta"]]
+    H_kv = H if H_kv < 0 else H_kv
+    # regenerate the inputs exactly as the reference's _make_inputs does
+    rng = np.random.default_rng(seed)
+    levels = (1 << b) - 1
+    q = rng.standard_normal((B, H, 1, D)).astype(np.float16)
+    kf = rng.standard_normal((B, H_kv, S_kv, D)).astype(np.float32)
+    vf = rng.standard_normal((B, H_kv, S_kv, D)).astype(np.float32)
+    np.testing.assert_array_equal(q, z[f"{name}_q"])
+    kc, ks, kz = kivi.quant_keys(kf, g, levels)
+    vc, vs, vz = kivi.quant_values(vf, g, levels)
+    for got, key in [(kc, "kc"), (ks, "ks"), (kz, "kz"), (vc, "vc"), (vs, "vs"), (vz, "vz")]:
+        want = z[f"{name}_{key}"]
+        assert got.dtype == want.dtype and got.shape == want.shape
+        np.testing.assert_array_equal(got, want)
+    out = kivi.reference_attend(q, kc, ks, kz, vc, vs, vz, g, 1.0 / math.sqrt(D))
+    np.testing.assert_allclose(out, z[f"{name}_out"], rtol=0, atol=1e-6)
+
+
+def test_kivi_special_values():
+    z = _load("kivi.npz")
+    const = np.full((1, 1, 32, 8), 3.5, dtype=np.float32)
+    c, s, zz = kivi.quant_keys(const, 32, 3)
+    np.testing.assert_array_equal(c, z["const_kc"])
+    np.testing.assert_array_equal(s, z["const_ks"])
+    np.testing.assert_array_equal(zz, z["const_kz"])
+    assert np.all(s == np.float32(1e-8)) and np.all(c == 0)
+    c, s, zz = kivi.quant_values(z["halfeven_in"], 32, 2)
+    np.testing.assert_array_equal(c, z["halfeven_vc"])
+    # 1/1.5 -> 0.667 -> 1 ; 2/1.5 -> 1.33 -> 1 ; exact halves round to even
+    assert set(np.unique(c)) <= {0, 1, 2}
+
+
+def test_kivi_group_of_one_is_lossless():
+    # reference: tests/metal/test_kivi_quant.py:151-159
+    rng = np.random.default_rng(5)
+    x = rng.standard_normal((1, 2, 9, 16)).astype(np.float16)
+    np.testing.assert_array_equal(kivi.quant_dequant_along(x, -1, 1, 3), x)
+    np.testing.assert_array_equal(kivi.quant_dequant_along(x, -2, 1, 3), x)
+
+
+def test_kivi_pack_codes_layout():
+    codes = np.arange(16, dtype=np.uint8).reshape(1, 16) % 4
+    packed = kivi.pack_codes(codes, 2)
+    assert packed.shape == (1, 4)
+    assert packed[0, 0] == (0 | 1 << 2 | 2 << 4 | 3 << 6)
+    assert kivi.storage_bits(3) == 4 and kivi.storage_bits(5) == 8
+
+
+def test_kivi_boundary_rule():
+    # reference: cache/kivi_cache.py:206-225 ; tests/cache/test_kivi_cache.py:187-199
+    assert kivi.quantization_boundary(100, 128, 32) == 0
+    assert kivi.quantization_boundary(128 + 31, 128, 32) == 0
+    assert kivi.quantization_boundary(128 + 32, 128, 32) == 32
+    assert kivi.quantization_boundary(4096, 128, 32) == 3968
+
+
+# ---------------------------------------------------------------------- RaBitQ
+@pytest.mark.parametrize("N,D", [(1, 8), (33, 64), (64, 128), (17, 256)])
+def test_rabitq_encode_matches_reference_numpy(N, D):
+    z = _load("rabitq.npz")
+    tag = f"enc_N{N}_D{D}"
+    bits, mag, _ = rabitq.encode_hadamard(z[f"{tag}_keys"], z[f"{tag}_diag"])
+    np.testing.assert_array_equal(bits, z[f"{tag}_bits"])
+    np.testing.assert_allclose(mag, z[f"{tag}_mag"], rtol=1e-6)
+
+
+@pytest.mark.parametrize("tag", ["att_B1_H1_Sq1_S33_D64", "att_B2_H2_Sq1_S256_D128", "att_B1_H2_Sq4_S64_D256"])
+def test_rabitq_attend_matches_reference_numpy(tag):
+    z = _load("rabitq.npz")
+    g = lambda k: z[f"{tag}_{k}"]  # noqa: E731
+    out = rabitq.reference_attend(g("q"), g("q_scale"), g("k_bits"), g("k_mag"), g("k_const"),
+                                  g("v_idx"), g("v_cents"))
+    np.testing.assert_allclose(out, g("out"), rtol=1e-5, atol=1e-6)
+    np.testing.assert_array_equal(bitpack.pack_nibbles(g("v_idx")), g("v_packed"))
+
+
+def test_rabitq_signs_and_rotation_match_reference_modules():
+    z = _load("rabitq.npz")
+    np.testing.assert_array_equal(rabitq.pack_signs(z["signs_in"]), z["signs_out"])
+    for d, seed in [(64, 42), (128, 42), (128, 7)]:
+        np.testing.assert_array_equal(rabitq.make_hadamard_diagonal(d, seed), z[f"diag_d{d}_s{seed}"])
+    np.testing.assert_array_equal(rabitq.make_rotation_matrix(24, 42), z["rot_d24_s42"])
+    np.testing.assert_array_equal(rabitq.make_rotation_matrix(128, 42).astype(np.float32), z["rot_d128_s42"])
+
+
+def test_rabitq_hamming_score():
+    rng = np.random.default_rng(0)
+    bits = rng.integers(0, 256, (9, 16), dtype=np.uint8)
+    qb = rng.integers(0, 256, 16, dtype=np.uint8)
+    cx = rng.standard_normal(9).astype(np.float32)
+    s = rabitq.hamming_score(qb, bits, 0.25, cx)
+    want = np.array([bin(int.from_bytes(bytes(a ^ b for a, b in zip(row, qb)), "little")).count("1")
+                     for row in bits], dtype=np.float32) * np.float32(0.25) + cx
+    np.testing.assert_array_equal(s, want)
+
+
+# -------------------------------------------------------------------- VecInfer
+@pytest.mark.parametrize("d", [1, 2, 8, 128])
+def test_vq_wht_matches_reference_function(d):
+    np.testing.assert_array_equal(vq.walsh_hadamard_matrix(d), _load("vq.npz")[f"wht_{d}"])
+
+
+def test_vq_quantize_sequential_order_and_ties():
+    cb = np.array([[0, 0], [1, 1], [1, 1], [2, 2]], dtype=np.float32)
+    x = np.array([[1, 1, 0.5, 0.5, 9, 9]], dtype=np.float32)
+    idx = vq.quantize_vq(x, cb, 2)
+    assert idx.dtype == np.int32
+    # exact hit -> first of the duplicated centroids; midpoint tie -> lowest index
+    assert idx.tolist() == [[1, 0, 3]]
+    rng = np.random.default_rng(3)
+    x = rng.standard_normal((4, 50, 64)).astype(np.float16)
+    cb = rng.standard_normal((256, 8)).astype(np.float16)
+    idx = vq.quantize_vq(x, cb, 8)
+    # brute-force python loop on a few entries, same canonical order
+    xf, cf = x.astype(np.float32), cb.astype(np.float32)
+    for (a, b, j) in [(0, 0, 0), (3, 49, 7), (2, 17, 3)]:
+        best, bi = np.float32(np.inf), 0
+        for c in range(256):
+            dist = np.float32(0)
+            for i in range(8):
+                d = np.float32(xf[a, b, j * 8 + i] - cf[c, i])
+                dist = np.float32(dist + np.float32(d * d))
+            if dist < best:
+                best, bi = dist, c
+        assert idx[a, b, j] == bi
+
+
+def test_vq_lut_equals_explicit_dot_and_dual_transform_invariance():
+    # reference: tests/allocators/test_vecinfer.py:133-153 and :35-54
+    rng = np.random.default_rng(1)
+    D, sub = 64, 8
+    cb = rng.standard_normal((16, sub)).astype(np.float32)
+    q = rng.standard_normal((2, 3, D)).astype(np.float32)
+    idx = rng.integers(0, 16, (5, D // sub))
+    lut = vq.compute_query_lut(q, cb, sub)
+    k_hat = vq.dequantize_vq(idx, cb)
+    want = np.einsum("abd,sd->abs", q, k_hat)
+    got = lut[:, :, np.arange(D // sub), idx].sum(-1)  # [2,3,5]
+    np.testing.assert_allclose(got, want, rtol=1e-4, atol=1e-4)
+    H = vq.walsh_hadamard_matrix(D)
+    np.testing.assert_allclose(H @ H.T, np.eye(D), atol=1e-5)
+    lam = rng.uniform(0.5, 2.0, (4, D)).astype(np.float32)
+    K = rng.standard_normal((1, 4, 7, D)).astype(np.float32)
+    Q = rng.standard_normal((1, 8, 1, D)).astype(np.float32)  # GQA 2:1
+    Kt = vq.apply_dual_transform_keys(K, lam, H)
+    Qt = vq.apply_dual_transform_queries(Q, lam, H)
+    s0 = np.einsum("bhqd,bhsd->bhqs", Q, np.repeat(K, 2, axis=1))
+    s1 = np.einsum("bhqd,bhsd->bhqs", Qt, np.repeat(Kt, 2, axis=1))
+    np.testing.assert_allclose(s0, s1, rtol=1e-4, atol=1e-4)
