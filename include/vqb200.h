@@ -1,0 +1,161 @@
+/*
+ * vqb200.h -- C ABI of libvqb200.so: the compressed-KV hot path for NVIDIA B200 (sm_100a).
+ *
+ * Quantize-on-append (KIVI group-affine codes, VecInfer product-VQ indices, RaBitQ sign
+ * bits) and fused dequant + single-query attention over the packed codes.
+ *
+ * Conventions
+ *   - Every pointer is a DEVICE pointer owned by the caller unless stated otherwise; the
+ *     library never allocates. Scratch memory is passed in as `workspace`, sized by the
+ *     matching `*_workspace_bytes` query.
+ *   - Every call is asynchronous on `stream` (a cudaStream_t passed as void*; NULL = the
+ *     legacy default stream) and returns a vq_status (0 = ok, negative = error). After a
+ *     non-zero return `vq_last_error()` holds a thread-local, human-readable reason.
+ *   - Tensors are row-major and contiguous in their trailing axes; leading (batch*head)
+ *     slabs are addressed through explicit strides so a caller can hand in slices of
+ *     larger pre-allocated cache buffers.
+ *   - Packed codes: element i of a row occupies bits [i*sb, (i+1)*sb) of the row's
+ *     little-endian bit stream (sb = container width 1, 2, 4 or 8), i.e. consecutive
+ *     channels of head_dim are packed LSB first. This is the reference's convention:
+ *     veloxquant_mlx/dsa/bit_pack.py:120-139,198-220 and metal/src/bit_pack.metal:8-19.
+ *
+ * Each entry point names the reference interface it replaces (paths relative to the
+ * reference project root).
+ */
+#ifndef VQB200_H
+#define VQB200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum vq_status {
+    VQ_OK = 0,
+    VQ_ERR_SHAPE = -1,    /* bad dimension / unsupported size */
+    VQ_ERR_DTYPE = -2,    /* unknown dtype code */
+    VQ_ERR_ALIGN = -3,    /* pointer or stride not aligned as required */
+    VQ_ERR_CAPACITY = -4, /* workspace too small / static limit exceeded */
+    VQ_ERR_ARCH = -5,     /* device is not sm_100 */
+    VQ_ERR_TIMEOUT = -6,  /* a bounded device-side wait gave up */
+    VQ_ERR_CUDA = -7      /* CUDA runtime error (see vq_last_error) */
+} vq_status;
+
+typedef enum vq_dtype { VQ_F16 = 0, VQ_BF16 = 1, VQ_F32 = 2 } vq_dtype;
+
+/* Library version: major*10000 + minor*100 + patch. */
+int32_t vq_version(void);
+/* Thread-local message for the last non-zero status returned on this thread. */
+const char *vq_last_error(void);
+
+/* ------------------------------------------------------------------------------------
+ * KIVI asymmetric group quantization
+ * ---------------------------------------------------------------------------------- */
+
+/* One tensor [n_bh, n_tok, head_dim] -> codes + per-group (scale, zero), and/or the
+ * round-tripped reconstruction.
+ *
+ * axis = 0: per-CHANNEL (KIVI keys): groups of `group` consecutive tokens per channel;
+ *           scale/zero rows are [n_bh][ceil(n_tok/group)][head_dim].
+ * axis = 1: per-TOKEN (KIVI values): groups of `group` consecutive channels per token;
+ *           scale/zero rows are [n_bh][n_tok][ceil(head_dim/group)].
+ * Math (float32, in this order): min, max, scale = max((max-min)/levels, eps),
+ * q = clamp(rint((x-min)/scale), 0, levels) (round-half-even), zero = min. A ragged final
+ * group is padded with its last live element. recon = T(q*scale + min) with the product
+ * and the sum rounded separately.
+ *
+ * Replaces KIVIQuantizer._quantize_groups (veloxquant_mlx/quantizers/kivi.py:103-128),
+ * KIVIKVCache._quant_dequant_along (veloxquant_mlx/cache/kivi_cache.py:151-201) and
+ * kivi_group_quant_dequant (veloxquant_mlx/metal/_kivi_quant.py:138-207). */
+typedef struct vq_kivi_quant_args {
+    const void *x;            /* input, dtype `dtype` */
+    int32_t dtype;            /* vq_dtype */
+    int32_t axis;             /* 0 keys / per-channel, 1 values / per-token */
+    int64_t n_bh, n_tok, head_dim;
+    int64_t x_stride_bh;      /* elements between slabs of x; rows are head_dim apart */
+    int32_t levels;           /* 2^b - 1, 1..255 */
+    int32_t store_bits;       /* container width of one stored code: 1, 2, 4 or 8 */
+    int32_t group;            /* >= 1 */
+    float eps;                /* floor on scale (reference: 1e-8) */
+    uint8_t *codes;           /* may be NULL; rows of head_dim*store_bits/8 bytes */
+    int64_t codes_stride_bh;  /* bytes between slabs */
+    float *scale;             /* may be NULL (then zero must be NULL too) */
+    float *zero;
+    int64_t param_stride_bh;  /* floats between slabs of scale / zero */
+    void *recon;              /* may be NULL; same dtype and row layout as x */
+    int64_t recon_stride_bh;  /* elements between slabs */
+} vq_kivi_quant_args;
+int32_t vq_kivi_quantize(const vq_kivi_quant_args *args, void *stream);
+
+/* Flat dequantization code*scale+zero of one K (axis 0) or V (axis 1) tensor to
+ * f16/bf16/f32. Replaces scalar_decode_once (veloxquant_mlx/metal/_scalar_attend.py:650-699,
+ * metal/src/scalar_affine_decode_once.metal). */
+typedef struct vq_kivi_dequant_args {
+    const uint8_t *codes;
+    int64_t codes_stride_bh;
+    const float *scale;
+    const float *zero;
+    int64_t param_stride_bh;
+    int32_t axis, store_bits, group;
+    int64_t n_bh, n_tok, head_dim;
+    void *out;
+    int32_t out_dtype;
+    int64_t out_stride_bh;
+} vq_kivi_dequant_args;
+int32_t vq_kivi_dequant(const vq_kivi_dequant_args *args, void *stream);
+
+/* Fused dequant + softmax attention over packed KIVI codes, with an optional
+ * unquantized tail (the residual window) attended in the same call.
+ *   out[b,h,sq,:] = softmax_s( scale * q[b,h,sq,:] . K_hat[b,hk,s,:] ) . V_hat[b,hk,s,:]
+ * with hk = h / (H_q/H_kv) (contiguous GQA blocks), K_hat = code*k_scale+k_zero for
+ * s < n_quant and the tail rows after that. No mask: every query row sees every slot.
+ *
+ * Replaces scalar_fused_decode_attend (veloxquant_mlx/metal/_scalar_attend.py:370-493,
+ * metal/src/scalar_affine_attend.metal:8-175) and scalar_predecoded_attend
+ * (_scalar_attend.py:702-779) when n_quant == 0. */
+typedef struct vq_kivi_attend_args {
+    const void *q;            /* [B, H_q, S_q, D] contiguous */
+    void *out;                /* [B, H_q, S_q, D] contiguous */
+    int32_t q_dtype, out_dtype;
+    int32_t B, H_q, H_kv, S_q, D;
+    int32_t store_bits;       /* 1, 2, 4 or 8 */
+    int32_t group;
+    int32_t n_quant;          /* packed tokens attended */
+    int32_t n_res;            /* tail tokens attended */
+    float scale;
+    const uint8_t *k_codes;   /* [B*H_kv] slabs of rows D*store_bits/8 bytes */
+    int64_t k_codes_stride_bh;
+    const float *k_scale;     /* [B*H_kv] slabs of rows [token group][D] */
+    const float *k_zero;
+    int64_t k_param_stride_bh;
+    const uint8_t *v_codes;
+    int64_t v_codes_stride_bh;
+    const float *v_scale;     /* [B*H_kv] slabs of rows [token][ceil(D/group)] */
+    const float *v_zero;
+    int64_t v_param_stride_bh;
+    const void *k_res;        /* [B*H_kv] slabs of rows [token][D], dtype res_dtype */
+    const void *v_res;
+    int32_t res_dtype;
+    int64_t res_stride_bh;    /* elements */
+    void *workspace;          /* >= vq_kivi_attend_workspace_bytes(args) */
+    int64_t workspace_bytes;
+    int32_t n_splits;         /* context splits per (b, kv head); 0 = choose */
+    int32_t variant;          /* 0 = choose; 1 = force the general CUDA-core kernel;
+                                 2 = force the tensor-core kernel (error if unsupported) */
+} vq_kivi_attend_args;
+int64_t vq_kivi_attend_workspace_bytes(const vq_kivi_attend_args *args);
+int32_t vq_kivi_decode_attend(const vq_kivi_attend_args *args, void *stream);
+
+/* ------------------------------------------------------------------------------------
+ * Bit packing of flat uint8 code arrays, b in {1, 2, 4}
+ * Replaces bit_pack / bit_unpack (veloxquant_mlx/metal/_bit_packing.py:87-148,
+ * metal/src/bit_pack.metal, bit_unpack.metal).
+ * ---------------------------------------------------------------------------------- */
+int32_t vq_bit_pack(const uint8_t *codes, int64_t n, int32_t bits, uint8_t *packed, void *stream);
+int32_t vq_bit_unpack(const uint8_t *packed, int64_t n, int32_t bits, uint8_t *codes, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* VQB200_H */

@@ -1,0 +1,134 @@
+"""ctypes binding of ``libvqb200.so`` (the C ABI declared in ``include/vqb200.h``).
+
+There is no CPU fallback: if the shared library is missing, or a call returns a
+non-zero status, an exception is raised.
+"""
+
+from __future__ import annotations
+
+import ctypes as C
+import os
+import threading
+
+import torch
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "libvqb200.so")
+
+VQ_F16, VQ_BF16, VQ_F32 = 0, 1, 2
+
+_DTYPE_CODE = {torch.float16: VQ_F16, torch.bfloat16: VQ_BF16, torch.float32: VQ_F32}
+
+_STATUS_NAME = {
+    0: "VQ_OK", -1: "VQ_ERR_SHAPE", -2: "VQ_ERR_DTYPE", -3: "VQ_ERR_ALIGN",
+    -4: "VQ_ERR_CAPACITY", -5: "VQ_ERR_ARCH", -6: "VQ_ERR_TIMEOUT", -7: "VQ_ERR_CUDA",
+}
+
+
+class KiviQuantArgs(C.Structure):
+    _fields_ = [
+        ("x", C.c_void_p), ("dtype", C.c_int32), ("axis", C.c_int32),
+        ("n_bh", C.c_int64), ("n_tok", C.c_int64), ("head_dim", C.c_int64),
+        ("x_stride_bh", C.c_int64),
+        ("levels", C.c_int32), ("store_bits", C.c_int32), ("group", C.c_int32), ("eps", C.c_float),
+        ("codes", C.c_void_p), ("codes_stride_bh", C.c_int64),
+        ("scale", C.c_void_p), ("zero", C.c_void_p), ("param_stride_bh", C.c_int64),
+        ("recon", C.c_void_p), ("recon_stride_bh", C.c_int64),
+    ]
+
+
+class KiviDequantArgs(C.Structure):
+    _fields_ = [
+        ("codes", C.c_void_p), ("codes_stride_bh", C.c_int64),
+        ("scale", C.c_void_p), ("zero", C.c_void_p), ("param_stride_bh", C.c_int64),
+        ("axis", C.c_int32), ("store_bits", C.c_int32), ("group", C.c_int32),
+        ("n_bh", C.c_int64), ("n_tok", C.c_int64), ("head_dim", C.c_int64),
+        ("out", C.c_void_p), ("out_dtype", C.c_int32), ("out_stride_bh", C.c_int64),
+    ]
+
+
+class KiviAttendArgs(C.Structure):
+    _fields_ = [
+        ("q", C.c_void_p), ("out", C.c_void_p),
+        ("q_dtype", C.c_int32), ("out_dtype", C.c_int32),
+        ("B", C.c_int32), ("H_q", C.c_int32), ("H_kv", C.c_int32), ("S_q", C.c_int32), ("D", C.c_int32),
+        ("store_bits", C.c_int32), ("group", C.c_int32), ("n_quant", C.c_int32), ("n_res", C.c_int32),
+        ("scale", C.c_float),
+        ("k_codes", C.c_void_p), ("k_codes_stride_bh", C.c_int64),
+        ("k_scale", C.c_void_p), ("k_zero", C.c_void_p), ("k_param_stride_bh", C.c_int64),
+        ("v_codes", C.c_void_p), ("v_codes_stride_bh", C.c_int64),
+        ("v_scale", C.c_void_p), ("v_zero", C.c_void_p), ("v_param_stride_bh", C.c_int64),
+        ("k_res", C.c_void_p), ("v_res", C.c_void_p), ("res_dtype", C.c_int32), ("res_stride_bh", C.c_int64),
+        ("workspace", C.c_void_p), ("workspace_bytes", C.c_int64),
+        ("n_splits", C.c_int32), ("variant", C.c_int32),
+    ]
+
+
+# name -> (restype, argtypes); every symbol include/vqb200.h declares.
+SIGNATURES = {
+    "vq_version": (C.c_int32, []),
+    "vq_last_error": (C.c_char_p, []),
+    "vq_kivi_quantize": (C.c_int32, [C.POINTER(KiviQuantArgs), C.c_void_p]),
+    "vq_kivi_dequant": (C.c_int32, [C.POINTER(KiviDequantArgs), C.c_void_p]),
+    "vq_kivi_attend_workspace_bytes": (C.c_int64, [C.POINTER(KiviAttendArgs)]),
+    "vq_kivi_decode_attend": (C.c_int32, [C.POINTER(KiviAttendArgs), C.c_void_p]),
+    "vq_bit_pack": (C.c_int32, [C.c_void_p, C.c_int64, C.c_int32, C.c_void_p, C.c_void_p]),
+    "vq_bit_unpack": (C.c_int32, [C.c_void_p, C.c_int64, C.c_int32, C.c_void_p, C.c_void_p]),
+}
+
+_lib = None
+_lock = threading.Lock()
+
+
+class VQLibraryError(RuntimeError):
+    """The native library is missing or a native call failed."""
+
+
+def lib() -> C.CDLL:
+    """Load (once) and return the bound library; raises if it has not been built."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    with _lock:
+        if _lib is None:
+            if not os.path.exists(LIB_PATH):
+                raise VQLibraryError(
+                    f"{LIB_PATH} not found: build it with `python -m veloxquant_mlx_b200.build` "
+                    "(there is no CPU fallback)"
+                )
+            handle = C.CDLL(LIB_PATH)
+            for name, (res, args) in SIGNATURES.items():
+                fn = getattr(handle, name)
+                fn.restype = res
+                fn.argtypes = args
+            _lib = handle
+    return _lib
+
+
+def check(status: int, what: str) -> None:
+    """Raise on a non-zero vq_status: ValueError for argument problems, RuntimeError otherwise."""
+    if status == 0:
+        return
+    msg = lib().vq_last_error().decode("utf-8", "replace")
+    text = f"{what}: {_STATUS_NAME.get(status, status)}: {msg}"
+    if status in (-1, -2, -3):
+        raise ValueError(text)
+    raise VQLibraryError(text)
+
+
+def dtype_code(dt: torch.dtype) -> int:
+    try:
+        return _DTYPE_CODE[dt]
+    except KeyError:
+        raise ValueError(f"unsupported dtype {dt}; expected float16, bfloat16 or float32") from None
+
+
+def stream_ptr(device: torch.device) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+def require_cuda(t: torch.Tensor, name: str) -> None:
+    if not t.is_cuda:
+        raise VQLibraryError(
+            f"{name} must be a CUDA tensor: this package runs on sm_100a only and has no CPU path"
+        )

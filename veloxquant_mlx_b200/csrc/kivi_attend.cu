@@ -1,0 +1,250 @@
+// Fused dequant + softmax attention over packed KIVI codes: entry point, the general
+// CUDA-core kernel (any container width, group size, head_dim <= 256, any query length)
+// and the split merge. The tensor-core kernel for the serving shape lives in
+// kivi_attend_mma.cu and is selected here when its preconditions hold.
+#include <algorithm>
+
+#include "common.cuh"
+#include "kivi_attend.h"
+
+namespace vq {
+
+constexpr int kGenWarps = 4;
+constexpr int kGenHeads = 4;   // query heads of one KV head handled per CTA
+constexpr int kGenMaxDS = 8;   // ceil(256 / 32)
+
+// One CTA: one (batch, kv head, query row, chunk of <= 4 query heads, context split).
+// Warp w walks tokens start+w, start+w+4, ...; lanes split head_dim.
+__global__ void __launch_bounds__(kGenWarps * 32)
+kivi_attend_general_kernel(const vq_kivi_attend_args a, int n_splits, int n_head_chunks,
+                           float *__restrict__ part_o, float *__restrict__ part_ml) {
+    __shared__ float sh_q[kGenHeads][256];
+    __shared__ float sh_o[kGenWarps][kGenHeads][256];
+    __shared__ float sh_m[kGenWarps][kGenHeads];
+    __shared__ float sh_l[kGenWarps][kGenHeads];
+
+    const int split = blockIdx.x;
+    const int hpk = a.H_q / a.H_kv;
+    int y = blockIdx.y;
+    const int hc = y % n_head_chunks; y /= n_head_chunks;
+    const int sq = y % a.S_q;
+    const int hkv = y / a.S_q;
+    const int b = blockIdx.z;
+    const int D = a.D;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int h0 = hc * kGenHeads;                      // first head (within the kv group)
+    const int nh = min(kGenHeads, hpk - h0);
+    const int64_t bh = (int64_t)b * a.H_kv + hkv;
+
+    for (int i = threadIdx.x; i < nh * D; i += blockDim.x) {
+        const int hp = i / D, d = i % D;
+        const int hq = hkv * hpk + h0 + hp;
+        sh_q[hp][d] = load_as_f32(a.q, a.q_dtype, (((int64_t)b * a.H_q + hq) * a.S_q + sq) * D + d);
+    }
+    __syncthreads();
+
+    const int total = a.n_quant + a.n_res;
+    const int chunk = (total + n_splits - 1) / n_splits;
+    const int t_begin = split * chunk;
+    const int t_end = min(total, t_begin + chunk);
+    const int sb = a.store_bits;
+    const int64_t row_bytes = (int64_t)D * sb / 8;
+    const int gv = (D + a.group - 1) / a.group;
+    const int nd = (D + 31) / 32;
+
+    float run_m[kGenHeads], run_l[kGenHeads], acc[kGenHeads][kGenMaxDS];
+#pragma unroll
+    for (int hp = 0; hp < kGenHeads; ++hp) {
+        run_m[hp] = -INFINITY;
+        run_l[hp] = 0.f;
+#pragma unroll
+        for (int i = 0; i < kGenMaxDS; ++i) acc[hp][i] = 0.f;
+    }
+
+    for (int t = t_begin + warp; t < t_end; t += kGenWarps) {
+        float kd[kGenMaxDS], vd[kGenMaxDS];
+        if (t < a.n_quant) {
+            const uint8_t *krow = a.k_codes + bh * a.k_codes_stride_bh + (int64_t)t * row_bytes;
+            const uint8_t *vrow = a.v_codes + bh * a.v_codes_stride_bh + (int64_t)t * row_bytes;
+            const int64_t kp = bh * a.k_param_stride_bh + (int64_t)(t / a.group) * D;
+            const int64_t vp = bh * a.v_param_stride_bh + (int64_t)t * gv;
+#pragma unroll
+            for (int i = 0; i < kGenMaxDS; ++i) {
+                const int d = lane + 32 * i;
+                kd[i] = vd[i] = 0.f;
+                if (i < nd && d < D) {
+                    kd[i] = (float)load_code(krow, d, sb) * a.k_scale[kp + d] + a.k_zero[kp + d];
+                    vd[i] = (float)load_code(vrow, d, sb) * a.v_scale[vp + d / a.group] + a.v_zero[vp + d / a.group];
+                }
+            }
+        } else {
+            const int64_t r = bh * a.res_stride_bh + (int64_t)(t - a.n_quant) * D;
+#pragma unroll
+            for (int i = 0; i < kGenMaxDS; ++i) {
+                const int d = lane + 32 * i;
+                kd[i] = vd[i] = 0.f;
+                if (i < nd && d < D) {
+                    kd[i] = load_as_f32(a.k_res, a.res_dtype, r + d);
+                    vd[i] = load_as_f32(a.v_res, a.res_dtype, r + d);
+                }
+            }
+        }
+#pragma unroll
+        for (int hp = 0; hp < kGenHeads; ++hp) {
+            if (hp < nh) {
+                float dot = 0.f;
+#pragma unroll
+                for (int i = 0; i < kGenMaxDS; ++i)
+                    if (i < nd) dot += sh_q[hp][(lane + 32 * i) < D ? lane + 32 * i : 0] * kd[i];
+                const float s = warp_sum(dot) * a.scale;
+                const float m_new = fmaxf(run_m[hp], s);
+                const float factor = __expf(run_m[hp] - m_new);
+                const float w = __expf(s - m_new);
+                run_l[hp] = run_l[hp] * factor + w;
+                run_m[hp] = m_new;
+#pragma unroll
+                for (int i = 0; i < kGenMaxDS; ++i) acc[hp][i] = acc[hp][i] * factor + w * vd[i];
+            }
+        }
+    }
+
+    // merge the warps of this CTA
+    for (int hp = 0; hp < nh; ++hp) {
+        if (lane == 0) { sh_m[warp][hp] = run_m[hp]; sh_l[warp][hp] = run_l[hp]; }
+        for (int i = 0; i < nd; ++i) {
+            const int d = lane + 32 * i;
+            if (d < D) sh_o[warp][hp][d] = acc[hp][i];
+        }
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < nh * D; i += blockDim.x) {
+        const int hp = i / D, d = i % D;
+        float gm = -INFINITY;
+        for (int w = 0; w < kGenWarps; ++w) gm = fmaxf(gm, sh_m[w][hp]);
+        float gl = 0.f, o = 0.f;
+        for (int w = 0; w < kGenWarps; ++w) {
+            const float f = (sh_m[w][hp] == -INFINITY) ? 0.f : __expf(sh_m[w][hp] - gm);
+            gl += sh_l[w][hp] * f;
+            o += sh_o[w][hp][d] * f;
+        }
+        const int hq = hkv * hpk + h0 + hp;
+        const int64_t row = ((int64_t)b * a.H_q + hq) * a.S_q + sq;
+        if (n_splits == 1) {
+            store_from_f32(a.out, a.out_dtype, row * D + d, o / gl);
+        } else {
+            part_o[(row * n_splits + split) * D + d] = o;
+            if (d == 0) {
+                part_ml[(row * n_splits + split) * 2 + 0] = gm;
+                part_ml[(row * n_splits + split) * 2 + 1] = gl;
+            }
+        }
+    }
+}
+
+// Combine the per-split partial softmaxes: one CTA per output row.
+__global__ void kivi_attend_merge_kernel(const float *__restrict__ part_o, const float *__restrict__ part_ml,
+                                         int n_splits, int D, void *__restrict__ out, int out_dtype) {
+    const int64_t row = blockIdx.x;
+    float gm = -INFINITY;
+    for (int s = 0; s < n_splits; ++s) gm = fmaxf(gm, part_ml[(row * n_splits + s) * 2]);
+    float gl = 0.f;
+    for (int s = 0; s < n_splits; ++s) {
+        const float m = part_ml[(row * n_splits + s) * 2];
+        gl += (m == -INFINITY) ? 0.f : part_ml[(row * n_splits + s) * 2 + 1] * __expf(m - gm);
+    }
+    for (int d = threadIdx.x; d < D; d += blockDim.x) {
+        float o = 0.f;
+        for (int s = 0; s < n_splits; ++s) {
+            const float m = part_ml[(row * n_splits + s) * 2];
+            if (m != -INFINITY) o += part_o[(row * n_splits + s) * D + d] * __expf(m - gm);
+        }
+        store_from_f32(out, out_dtype, row * D + d, o / gl);
+    }
+}
+
+static int32_t validate(const vq_kivi_attend_args &a) {
+    VQ_REQUIRE(a.B >= 1 && a.H_q >= 1 && a.H_kv >= 1 && a.S_q >= 1, VQ_ERR_SHAPE, "vq_kivi_decode_attend: B, H_q, H_kv, S_q must be >= 1");
+    VQ_REQUIRE(a.D >= 1 && a.D <= 256, VQ_ERR_SHAPE, "vq_kivi_decode_attend: D=%d must be in 1..256", a.D);
+    VQ_REQUIRE(a.H_q % a.H_kv == 0, VQ_ERR_SHAPE, "vq_kivi_decode_attend: H_q=%d must be a multiple of H_kv=%d", a.H_q, a.H_kv);
+    VQ_REQUIRE(a.H_q / a.H_kv <= 16, VQ_ERR_SHAPE, "vq_kivi_decode_attend: heads_per_kv=%d exceeds the supported maximum of 16", a.H_q / a.H_kv);
+    VQ_REQUIRE(a.n_quant >= 0 && a.n_res >= 0 && a.n_quant + a.n_res >= 1, VQ_ERR_SHAPE, "vq_kivi_decode_attend: nothing to attend over");
+    VQ_REQUIRE(a.q && a.out, VQ_ERR_SHAPE, "vq_kivi_decode_attend: q/out is NULL");
+    VQ_REQUIRE(a.q_dtype >= 0 && a.q_dtype <= 2 && a.out_dtype >= 0 && a.out_dtype <= 2, VQ_ERR_DTYPE, "vq_kivi_decode_attend: bad q/out dtype");
+    if (a.n_quant > 0) {
+        const int sb = a.store_bits;
+        VQ_REQUIRE(sb == 1 || sb == 2 || sb == 4 || sb == 8, VQ_ERR_SHAPE, "vq_kivi_decode_attend: store_bits must be 1, 2, 4 or 8, got %d", sb);
+        VQ_REQUIRE(a.group >= 1, VQ_ERR_SHAPE, "vq_kivi_decode_attend: group must be >= 1");
+        VQ_REQUIRE(((int64_t)a.D * sb) % 8 == 0, VQ_ERR_SHAPE, "vq_kivi_decode_attend: D*store_bits must be a multiple of 8");
+        VQ_REQUIRE(a.k_codes && a.v_codes && a.k_scale && a.k_zero && a.v_scale && a.v_zero, VQ_ERR_SHAPE, "vq_kivi_decode_attend: a quantized tensor is NULL");
+    }
+    if (a.n_res > 0) {
+        VQ_REQUIRE(a.k_res && a.v_res, VQ_ERR_SHAPE, "vq_kivi_decode_attend: residual tensor is NULL");
+        VQ_REQUIRE(a.res_dtype >= 0 && a.res_dtype <= 2, VQ_ERR_DTYPE, "vq_kivi_decode_attend: bad residual dtype");
+    }
+    return VQ_OK;
+}
+
+static int general_splits(const vq_kivi_attend_args &a, int sm_count) {
+    if (a.n_splits > 0) return a.n_splits;
+    const int total = a.n_quant + a.n_res;
+    const int hpk = a.H_q / a.H_kv;
+    const int64_t ctas = (int64_t)a.B * a.H_kv * a.S_q * ceil_div(hpk, kGenHeads);
+    int64_t want = ceil_div((int64_t)sm_count * 4, ctas);
+    want = std::min<int64_t>(want, ceil_div(total, 64));
+    return (int)std::max<int64_t>(1, std::min<int64_t>(want, 256));
+}
+
+}  // namespace vq
+
+extern "C" int64_t vq_kivi_attend_workspace_bytes(const vq_kivi_attend_args *args) {
+    using namespace vq;
+    if (!args) return 0;
+    const vq_kivi_attend_args &a = *args;
+    if (a.B < 1 || a.H_q < 1 || a.S_q < 1 || a.D < 1) return 0;
+    // Room for the largest split count either kernel may choose.
+    const int64_t rows = (int64_t)a.B * a.H_q * a.S_q;
+    const int64_t splits = a.n_splits > 0 ? a.n_splits : 256;
+    return rows * splits * ((int64_t)a.D + 2) * (int64_t)sizeof(float) + 256;
+}
+
+extern "C" int32_t vq_kivi_decode_attend(const vq_kivi_attend_args *args, void *stream) {
+    using namespace vq;
+    VQ_REQUIRE(args != nullptr, VQ_ERR_SHAPE, "vq_kivi_decode_attend: args is NULL");
+    const vq_kivi_attend_args &a = *args;
+    int32_t rc = validate(a);
+    if (rc != VQ_OK) return rc;
+    DeviceInfo di;
+    rc = device_info(&di);
+    if (rc != VQ_OK) return rc;
+    cudaStream_t st = (cudaStream_t)stream;
+
+    if (a.variant != 1) {
+        const char *why = kivi_attend_mma_supported(a);
+        if (why == nullptr) return kivi_attend_mma_launch(a, di, st);
+        VQ_REQUIRE(a.variant != 2, VQ_ERR_SHAPE, "vq_kivi_decode_attend: tensor-core kernel unavailable: %s", why);
+    }
+
+    const int n_splits = general_splits(a, di.sm_count);
+    const int64_t rows = (int64_t)a.B * a.H_q * a.S_q;
+    float *part_o = nullptr, *part_ml = nullptr;
+    if (n_splits > 1) {
+        const int64_t need = rows * n_splits * ((int64_t)a.D + 2) * (int64_t)sizeof(float);
+        VQ_REQUIRE(a.workspace != nullptr && a.workspace_bytes >= need, VQ_ERR_CAPACITY,
+                   "vq_kivi_decode_attend: workspace of %lld bytes needed, %lld given", (long long)need, (long long)a.workspace_bytes);
+        VQ_REQUIRE(is_aligned(a.workspace, 16), VQ_ERR_ALIGN, "vq_kivi_decode_attend: workspace must be 16-byte aligned");
+        part_o = (float *)a.workspace;
+        part_ml = part_o + rows * n_splits * a.D;
+    }
+    const int hpk = a.H_q / a.H_kv;
+    const int n_head_chunks = (int)ceil_div(hpk, kGenHeads);
+    const int64_t gy = (int64_t)a.H_kv * a.S_q * n_head_chunks;
+    VQ_REQUIRE(gy <= 65535 && a.B <= 65535, VQ_ERR_SHAPE, "vq_kivi_decode_attend: grid too large (H_kv*S_q*chunks=%lld, B=%d)", (long long)gy, a.B);
+    dim3 grid(n_splits, (unsigned)gy, a.B);
+    kivi_attend_general_kernel<<<grid, kGenWarps * 32, 0, st>>>(a, n_splits, n_head_chunks, part_o, part_ml);
+    VQ_CHECK_LAUNCH("kivi_attend_general_kernel");
+    if (n_splits > 1) {
+        kivi_attend_merge_kernel<<<(unsigned)rows, 128, 0, st>>>(part_o, part_ml, n_splits, a.D, a.out, a.out_dtype);
+        VQ_CHECK_LAUNCH("kivi_attend_merge_kernel");
+    }
+    return VQ_OK;
+}

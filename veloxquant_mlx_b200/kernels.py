@@ -1,0 +1,435 @@
+"""Kernel wrappers with the reference's names and argument meaning, on ``torch.Tensor``.
+
+Mirrors the reference's ``veloxquant_mlx/metal/kernels.py`` facade for the compressed-KV
+hot path. Every function validates like its reference counterpart (same exception types,
+function name prefixed in the message) and then calls the C ABI in ``libvqb200.so``;
+nothing here computes on the CPU.
+"""
+
+from __future__ import annotations
+
+import ctypes as C
+import math
+
+import torch
+
+from . import _lib
+from ._lib import KiviAttendArgs, KiviDequantArgs, KiviQuantArgs, check, dtype_code, lib, require_cuda, stream_ptr
+
+_FLOAT_DTYPES = (torch.float16, torch.bfloat16, torch.float32)
+_MAX_HEADS_PER_KV = 16
+
+
+def kivi_available() -> bool:
+    """True when the native library is built and a CUDA device is visible."""
+    import os
+
+    return os.path.exists(_lib.LIB_PATH) and torch.cuda.is_available()
+
+
+def storage_bits(b: int) -> int:
+    """Container width (1, 2, 4 or 8) used to store ``b``-bit codes."""
+    if b < 1 or b > 8:
+        raise ValueError(f"storage_bits: b={b} must be in 1..8")
+    for sb in (1, 2, 4, 8):
+        if b <= sb:
+            return sb
+    raise AssertionError
+
+
+def _slab_view(x: torch.Tensor, name: str):
+    """Return (tensor with contiguous [S, D] rows, n_bh, stride_bh_in_elements).
+
+    Accepts ``[..., S, D]`` tensors whose leading axes collapse to one uniform stride (a
+    contiguous tensor, or a slice ``buf[:, :, lo:hi, :]`` of one); anything else is copied.
+    """
+    S, D = x.shape[-2], x.shape[-1]
+    n_bh = 1
+    for v in x.shape[:-2]:
+        n_bh *= v
+    ok = x.stride(-1) == 1 and x.stride(-2) == D
+    stride_bh = S * D
+    lead = [(x.shape[i], x.stride(i)) for i in range(x.ndim - 2) if x.shape[i] > 1]
+    if ok and lead:
+        stride_bh = lead[-1][1]
+        expect = stride_bh
+        for size, st in reversed(lead):
+            if st != expect:
+                ok = False
+                break
+            expect = st * size
+    if not ok:
+        x = x.contiguous()
+        stride_bh = S * D
+    return x, n_bh, stride_bh
+
+
+# ----------------------------------------------------------------------------------------
+# KIVI quantization
+# ----------------------------------------------------------------------------------------
+
+def kivi_group_quant_dequant(x: torch.Tensor, axis: int, group_size: int, levels: int,
+                             eps: float = 1e-8) -> torch.Tensor:
+    """Round-trip ``x [..., S, D]`` through KIVI asymmetric group quantization.
+
+    ``axis=-2``: per-channel (keys, groups along tokens); ``axis=-1``: per-token (values,
+    groups along channels). Output has ``x``'s shape and dtype and is bit-identical to the
+    reference's ``KIVIKVCache._quant_dequant_along`` (``cache/kivi_cache.py:151-201``,
+    ``metal/_kivi_quant.py:138-207``).
+    """
+    if axis not in (-1, -2):
+        raise ValueError(f"kivi_group_quant_dequant: axis must be -1 or -2, got {axis}")
+    if x.ndim < 2:
+        raise ValueError(f"kivi_group_quant_dequant: x must be at least 2D, got {tuple(x.shape)}")
+    if group_size < 1:
+        raise ValueError(f"kivi_group_quant_dequant: group_size must be >= 1, got {group_size}")
+    if levels < 1:
+        raise ValueError(f"kivi_group_quant_dequant: levels must be >= 1, got {levels}")
+    if x.dtype not in _FLOAT_DTYPES:
+        raise ValueError(
+            f"kivi_group_quant_dequant: unsupported dtype {x.dtype}; expected one of "
+            f"{sorted(str(d) for d in _FLOAT_DTYPES)}"
+        )
+    if x.numel() == 0:
+        return x
+    require_cuda(x, "kivi_group_quant_dequant: x")
+    xs, n_bh, stride = _slab_view(x, "x")
+    S, D = x.shape[-2], x.shape[-1]
+    out = torch.empty(x.shape, dtype=x.dtype, device=x.device)
+    a = KiviQuantArgs(
+        x=xs.data_ptr(), dtype=dtype_code(x.dtype), axis=0 if axis == -2 else 1,
+        n_bh=n_bh, n_tok=S, head_dim=D, x_stride_bh=stride,
+        levels=int(levels), store_bits=8, group=int(group_size), eps=float(eps),
+        codes=None, codes_stride_bh=0, scale=None, zero=None, param_stride_bh=0,
+        recon=out.data_ptr(), recon_stride_bh=S * D,
+    )
+    with torch.cuda.device(x.device):
+        check(lib().vq_kivi_quantize(C.byref(a), stream_ptr(x.device)), "kivi_group_quant_dequant")
+    return out
+
+
+def kivi_quantize_into(x: torch.Tensor, axis: int, group_size: int, bits: int, *,
+                       codes: torch.Tensor, scale: torch.Tensor, zero: torch.Tensor,
+                       tok_offset: int = 0, store_bits: int | None = None, eps: float = 1e-8) -> None:
+    """Quantize ``x [B,H,S,D]`` and write packed codes / params into cache buffers in place.
+
+    ``codes [B,H,cap,D*sb/8] u8``; keys (``axis=-2``): ``scale,zero [B,H,cap/g,D] f32`` and
+    ``tok_offset`` must be a multiple of ``group_size``; values (``axis=-1``):
+    ``scale,zero [B,H,cap,ceil(D/g)] f32``. Rows ``[tok_offset, tok_offset+S)`` are written.
+    Code-emitting twin of ``KIVIQuantizer._quantize_groups`` (``quantizers/kivi.py:103-128``)
+    fused with LSB-first packing (``dsa/bit_pack.py``).
+    """
+    if axis not in (-1, -2):
+        raise ValueError(f"kivi_quantize: axis must be -1 or -2, got {axis}")
+    if x.ndim != 4:
+        raise ValueError(f"kivi_quantize: x must be 4D [B,H,S,D], got {tuple(x.shape)}")
+    if bits < 1 or bits > 8:
+        raise ValueError(f"kivi_quantize: bits={bits} must be in [1, 8] (uint8 codes).")
+    if group_size < 1:
+        raise ValueError(f"kivi_quantize: group_size={group_size} must be >= 1.")
+    if x.dtype not in _FLOAT_DTYPES:
+        raise ValueError(f"kivi_quantize: unsupported dtype {x.dtype}")
+    sb = storage_bits(bits) if store_bits is None else int(store_bits)
+    B, H, S, D = x.shape
+    if S == 0:
+        return
+    require_cuda(x, "kivi_quantize: x")
+    row_bytes = D * sb // 8
+    if codes.dtype != torch.uint8 or codes.shape[-1] != row_bytes or not codes.is_contiguous():
+        raise ValueError(f"kivi_quantize: codes must be contiguous uint8 [B,H,cap,{row_bytes}]")
+    if scale.dtype != torch.float32 or zero.dtype != torch.float32 or scale.shape != zero.shape:
+        raise ValueError("kivi_quantize: scale/zero must be float32 tensors of equal shape")
+    if not (scale.is_contiguous() and zero.is_contiguous()):
+        raise ValueError("kivi_quantize: scale/zero must be contiguous")
+    cap = codes.shape[2]
+    if tok_offset < 0 or tok_offset + S > cap:
+        raise RuntimeError(f"kivi_quantize: rows [{tok_offset}, {tok_offset + S}) exceed capacity {cap}")
+    xs, n_bh, stride = _slab_view(x, "x")
+    if axis == -2:
+        if tok_offset % group_size:
+            raise ValueError("kivi_quantize: tok_offset must be a multiple of group_size for keys")
+        g_off = tok_offset // group_size
+        n_g = (S + group_size - 1) // group_size
+        if scale.shape[-1] != D or g_off + n_g > scale.shape[2]:
+            raise RuntimeError("kivi_quantize: key scale/zero buffer too small")
+        p_stride = scale.shape[2] * D
+        p_off = g_off * D
+    else:
+        gv = (D + group_size - 1) // group_size
+        if scale.shape[-1] != gv or tok_offset + S > scale.shape[2]:
+            raise RuntimeError("kivi_quantize: value scale/zero buffer too small")
+        p_stride = scale.shape[2] * gv
+        p_off = tok_offset * gv
+    a = KiviQuantArgs(
+        x=xs.data_ptr(), dtype=dtype_code(x.dtype), axis=0 if axis == -2 else 1,
+        n_bh=n_bh, n_tok=S, head_dim=D, x_stride_bh=stride,
+        levels=(1 << bits) - 1, store_bits=sb, group=int(group_size), eps=float(eps),
+        codes=codes.data_ptr() + tok_offset * row_bytes, codes_stride_bh=cap * row_bytes,
+        scale=scale.data_ptr() + 4 * p_off, zero=zero.data_ptr() + 4 * p_off, param_stride_bh=p_stride,
+        recon=None, recon_stride_bh=0,
+    )
+    with torch.cuda.device(x.device):
+        check(lib().vq_kivi_quantize(C.byref(a), stream_ptr(x.device)), "kivi_quantize")
+
+
+def kivi_quantize(x: torch.Tensor, axis: int, group_size: int, bits: int, *,
+                  store_bits: int | None = None, eps: float = 1e-8):
+    """Quantize ``x [B,H,S,D]``; returns ``(packed codes u8, scale f32, zero f32)``.
+
+    Freshly allocated outputs; see :func:`kivi_quantize_into` for layouts. With
+    ``store_bits=8`` the codes are one per byte, the reference's own layout.
+    """
+    if x.ndim != 4:
+        raise ValueError(f"kivi_quantize: x must be 4D [B,H,S,D], got {tuple(x.shape)}")
+    B, H, S, D = x.shape
+    sb = storage_bits(bits) if store_bits is None else int(store_bits)
+    codes = torch.empty((B, H, S, D * sb // 8), dtype=torch.uint8, device=x.device)
+    if axis == -2:
+        pshape = (B, H, (S + group_size - 1) // max(group_size, 1), D)
+    else:
+        pshape = (B, H, S, (D + group_size - 1) // max(group_size, 1))
+    scale = torch.empty(pshape, dtype=torch.float32, device=x.device)
+    zero = torch.empty(pshape, dtype=torch.float32, device=x.device)
+    kivi_quantize_into(x, axis, group_size, bits, codes=codes, scale=scale, zero=zero,
+                       store_bits=sb, eps=eps)
+    return codes, scale, zero
+
+
+def scalar_decode_once(codes: torch.Tensor, scale: torch.Tensor, zero: torch.Tensor,
+                       group_size: int, mode: str, *, store_bits: int = 8,
+                       out_dtype: torch.dtype = torch.float16) -> torch.Tensor:
+    """Decode a group-affine K (``mode="K"``) or V (``"V"``) tensor to ``out_dtype`` once.
+
+    ``codes [B,H_kv,S,D*store_bits/8] u8``. Mirrors ``scalar_decode_once``
+    (``metal/_scalar_attend.py:650-699``).
+    """
+    if mode not in ("K", "V"):
+        raise ValueError(f"scalar_decode_once: mode must be 'K' or 'V', got {mode!r}")
+    if codes.ndim != 4:
+        raise ValueError(f"scalar_decode_once: codes must be 4D, got {tuple(codes.shape)}")
+    require_cuda(codes, "scalar_decode_once: codes")
+    B, H, S, rb = codes.shape
+    D = rb * 8 // store_bits
+    codes = codes.contiguous()
+    scale = scale.to(torch.float32).contiguous()
+    zero = zero.to(torch.float32).contiguous()
+    out = torch.empty((B, H, S, D), dtype=out_dtype, device=codes.device)
+    if out.numel() == 0:
+        return out
+    a = KiviDequantArgs(
+        codes=codes.data_ptr(), codes_stride_bh=S * rb, scale=scale.data_ptr(), zero=zero.data_ptr(),
+        param_stride_bh=scale.shape[2] * scale.shape[3], axis=0 if mode == "K" else 1,
+        store_bits=store_bits, group=int(group_size), n_bh=B * H, n_tok=S, head_dim=D,
+        out=out.data_ptr(), out_dtype=dtype_code(out_dtype), out_stride_bh=S * D,
+    )
+    with torch.cuda.device(codes.device):
+        check(lib().vq_kivi_dequant(C.byref(a), stream_ptr(codes.device)), "scalar_decode_once")
+    return out
+
+
+# ----------------------------------------------------------------------------------------
+# KIVI decode attention
+# ----------------------------------------------------------------------------------------
+
+_workspaces: dict = {}
+
+
+def _workspace(device: torch.device, nbytes: int) -> torch.Tensor:
+    """Per-(device, stream) scratch buffer, grown geometrically and reused."""
+    key = (device.index, torch.cuda.current_stream(device).cuda_stream)
+    buf = _workspaces.get(key)
+    if buf is None or buf.numel() < nbytes:
+        buf = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
+        _workspaces[key] = buf
+    return buf
+
+
+def kivi_decode_attend(q, k_codes, k_scale, k_zero, v_codes, v_scale, v_zero, group_size, scale, *,
+                       store_bits=8, n_quant=None, k_res=None, v_res=None, n_res=None,
+                       out=None, out_dtype=None, n_splits=0, variant=0, _fn="kivi_decode_attend"):
+    """Fused dequant + attention over packed codes and an optional unquantized tail.
+
+    ``k_codes/v_codes [B,H_kv,cap,D*store_bits/8]`` (first ``n_quant`` rows used),
+    ``k_scale/k_zero [B,H_kv,capG,D]``, ``v_scale/v_zero [B,H_kv,cap,ceil(D/g)]``,
+    ``k_res/v_res [B,H_kv,capR,D]`` float (first ``n_res`` rows used), ``q [B,H_q,S_q,D]``.
+    Returns ``[B,H_q,S_q,D]`` in ``out_dtype`` (default: ``q.dtype``).
+    """
+    fn = _fn
+    if q.ndim != 4:
+        raise ValueError(f"{fn}: q must be 4D, got {tuple(q.shape)}")
+    require_cuda(q, f"{fn}: q")
+    B, H, S_q, D = q.shape
+    if D > 256:
+        raise ValueError(f"{fn}: D={D} must be <= 256")
+    has_q = k_codes is not None
+    if has_q:
+        if k_codes.ndim != 4 or v_codes.ndim != 4:
+            raise ValueError(
+                f"{fn}: k_codes and v_codes must be 4D, got k_codes={tuple(k_codes.shape)}, "
+                f"v_codes={tuple(v_codes.shape)}"
+            )
+        Bk, H_kv, cap, rb = k_codes.shape
+        Dk = rb * 8 // store_bits
+        if Bk != B:
+            raise ValueError(f"{fn}: batch mismatch: q B={B} vs k_codes B={Bk}")
+        if Dk != D:
+            raise ValueError(f"{fn}: head_dim mismatch: q D={D} vs k_codes D={Dk}")
+        if v_codes.shape[1] != H_kv:
+            raise ValueError(f"{fn}: k_codes H_kv={H_kv} vs v_codes H_kv={v_codes.shape[1]} mismatch")
+        if n_quant is None:
+            n_quant = cap
+        if n_quant > cap or n_quant > v_codes.shape[2]:
+            raise ValueError(f"{fn}: n_quant={n_quant} exceeds the code buffers")
+    else:
+        if k_res is None:
+            raise ValueError(f"{fn}: no keys given")
+        H_kv = k_res.shape[1]
+        n_quant = 0
+    if H % H_kv != 0:
+        raise ValueError(
+            f"{fn}: H_q={H} must be a multiple of H_kv={H_kv} (k_codes.shape[1]) for GQA head-packing"
+        )
+    if H // H_kv > _MAX_HEADS_PER_KV:
+        raise ValueError(
+            f"{fn}: heads_per_kv={H // H_kv} exceeds the supported maximum of {_MAX_HEADS_PER_KV}"
+        )
+    if k_res is not None:
+        if n_res is None:
+            n_res = k_res.shape[2]
+        if k_res.shape != v_res.shape or k_res.dtype != v_res.dtype:
+            raise ValueError(f"{fn}: k_res and v_res must match in shape and dtype")
+        if not (k_res.is_contiguous() and v_res.is_contiguous()):
+            raise ValueError(f"{fn}: k_res / v_res must be contiguous")
+        if n_res > k_res.shape[2]:
+            raise ValueError(f"{fn}: n_res={n_res} exceeds the residual buffers")
+    else:
+        n_res = 0
+    if q.dtype not in _FLOAT_DTYPES:
+        raise ValueError(f"{fn}: unsupported q dtype {q.dtype}")
+    q = q.contiguous()
+    out_dtype = out_dtype or q.dtype
+    if out is None:
+        out = torch.empty((B, H, S_q, D), dtype=out_dtype, device=q.device)
+    a = KiviAttendArgs(
+        q=q.data_ptr(), out=out.data_ptr(), q_dtype=dtype_code(q.dtype), out_dtype=dtype_code(out.dtype),
+        B=B, H_q=H, H_kv=H_kv, S_q=S_q, D=D, store_bits=int(store_bits), group=int(group_size),
+        n_quant=int(n_quant), n_res=int(n_res), scale=float(scale),
+        n_splits=int(n_splits), variant=int(variant),
+    )
+    if has_q:
+        for t, nm in ((k_codes, "k_codes"), (v_codes, "v_codes"), (k_scale, "k_scale"), (k_zero, "k_zero"),
+                      (v_scale, "v_scale"), (v_zero, "v_zero")):
+            if not t.is_contiguous():
+                raise ValueError(f"{fn}: {nm} must be contiguous")
+        a.k_codes, a.k_codes_stride_bh = k_codes.data_ptr(), k_codes.shape[2] * k_codes.shape[3]
+        a.v_codes, a.v_codes_stride_bh = v_codes.data_ptr(), v_codes.shape[2] * v_codes.shape[3]
+        a.k_scale, a.k_zero = k_scale.data_ptr(), k_zero.data_ptr()
+        a.k_param_stride_bh = k_scale.shape[2] * k_scale.shape[3]
+        a.v_scale, a.v_zero = v_scale.data_ptr(), v_zero.data_ptr()
+        a.v_param_stride_bh = v_scale.shape[2] * v_scale.shape[3]
+    if n_res:
+        a.k_res, a.v_res = k_res.data_ptr(), v_res.data_ptr()
+        a.res_dtype = dtype_code(k_res.dtype)
+        a.res_stride_bh = k_res.shape[2] * k_res.shape[3]
+    with torch.cuda.device(q.device):
+        need = lib().vq_kivi_attend_workspace_bytes(C.byref(a))
+        ws = _workspace(q.device, need)
+        a.workspace, a.workspace_bytes = ws.data_ptr(), ws.numel()
+        check(lib().vq_kivi_decode_attend(C.byref(a), stream_ptr(q.device)), fn)
+    return out
+
+
+def scalar_fused_decode_attend(q, k_codes, k_scale, k_zero, v_codes, v_scale, v_zero,
+                               group_size: int, scale: float, nsg: int | None = None, *,
+                               store_bits: int = 8) -> torch.Tensor:
+    """Reference-shaped entry: one code per byte by default, fp16 output.
+
+    Same arguments as ``scalar_fused_decode_attend`` (``metal/_scalar_attend.py:370-493``);
+    ``nsg`` (1..32) pins the number of context splits. Codes are ``uint8 [B,H_kv,S_kv,D]``
+    (or packed rows with ``store_bits`` < 8).
+    """
+    fn = "scalar_fused_decode_attend"
+    if nsg is not None and not (1 <= nsg <= 32):
+        raise ValueError(f"{fn}: nsg={nsg} must be in 1..32")
+    return kivi_decode_attend(
+        q, k_codes.to(torch.uint8), k_scale.to(torch.float32), k_zero.to(torch.float32),
+        v_codes.to(torch.uint8), v_scale.to(torch.float32), v_zero.to(torch.float32),
+        group_size, scale, store_bits=store_bits, out_dtype=torch.float16,
+        n_splits=0 if nsg is None else nsg, _fn=fn,
+    )
+
+
+def scalar_predecoded_attend(q, k_hat, v_hat, scale: float, nsg: int | None = None) -> torch.Tensor:
+    """Attention over already-decoded ``k_hat/v_hat [B,H_kv,S,D]``; fp16 output.
+
+    Mirrors ``scalar_predecoded_attend`` (``metal/_scalar_attend.py:702-779``).
+    """
+    fn = "scalar_predecoded_attend"
+    if q.ndim != 4:
+        raise ValueError(f"{fn}: q must be 4D, got {tuple(q.shape)}")
+    if k_hat.ndim != 4 or v_hat.ndim != 4:
+        raise ValueError(f"{fn}: k_hat and v_hat must be 4D, got k_hat={tuple(k_hat.shape)}, v_hat={tuple(v_hat.shape)}")
+    if nsg is not None and not (1 <= nsg <= 32):
+        raise ValueError(f"{fn}: nsg={nsg} must be in 1..32")
+    if k_hat.shape[0] != q.shape[0]:
+        raise ValueError(f"{fn}: batch mismatch: q B={q.shape[0]} vs k_hat B={k_hat.shape[0]}")
+    if k_hat.shape[3] != q.shape[3]:
+        raise ValueError(f"{fn}: head_dim mismatch: q D={q.shape[3]} vs k_hat D={k_hat.shape[3]}")
+    if v_hat.shape != k_hat.shape:
+        raise ValueError(f"{fn}: k_hat shape={tuple(k_hat.shape)} vs v_hat shape={tuple(v_hat.shape)} mismatch")
+    return kivi_decode_attend(
+        q, None, None, None, None, None, None, 1, scale,
+        k_res=k_hat.contiguous(), v_res=v_hat.contiguous().to(k_hat.dtype),
+        out_dtype=torch.float16, n_splits=0 if nsg is None else nsg, _fn=fn,
+    )
+
+
+# ----------------------------------------------------------------------------------------
+# Bit packing
+# ----------------------------------------------------------------------------------------
+
+def turboquant_bit_pack(indices: torch.Tensor, b: int) -> torch.Tensor:
+    """Pack uint8 indices (values < 2**b) LSB first; ``b`` in {1, 2, 4}.
+
+    Mirrors ``turboquant_bit_pack`` (``metal/_bit_packing.py:87-116``).
+    """
+    if b not in (1, 2, 4):
+        raise ValueError(f"turboquant_bit_pack: b must be 1, 2, or 4, got {b}")
+    N = indices.numel()
+    per = 8 // b
+    if N % per != 0:
+        raise ValueError(f"turboquant_bit_pack: N={N} not divisible by {per} (= 8/b)")
+    require_cuda(indices, "turboquant_bit_pack: indices")
+    flat = indices.reshape(-1).to(torch.uint8).contiguous()
+    out = torch.empty(N * b // 8, dtype=torch.uint8, device=indices.device)
+    with torch.cuda.device(indices.device):
+        check(lib().vq_bit_pack(flat.data_ptr(), N, b, out.data_ptr(), stream_ptr(indices.device)),
+              "turboquant_bit_pack")
+    return out
+
+
+def turboquant_bit_unpack(packed: torch.Tensor, N: int, b: int) -> torch.Tensor:
+    """Inverse of :func:`turboquant_bit_pack` (``metal/_bit_packing.py:119-148``)."""
+    if b not in (1, 2, 4):
+        raise ValueError(f"turboquant_bit_unpack: b must be 1, 2, or 4, got {b}")
+    if N < 0:
+        raise ValueError(f"turboquant_bit_unpack: N must be >= 0, got {N}")
+    need = -(-N * b // 8)
+    if packed.numel() < need:
+        raise ValueError(
+            f"turboquant_bit_unpack: packed has {packed.numel()} byte(s) but N={N} at b={b} needs {need}"
+        )
+    require_cuda(packed, "turboquant_bit_unpack: packed")
+    flat = packed.reshape(-1).to(torch.uint8).contiguous()
+    out = torch.empty(N, dtype=torch.uint8, device=packed.device)
+    with torch.cuda.device(packed.device):
+        check(lib().vq_bit_unpack(flat.data_ptr(), N, b, out.data_ptr(), stream_ptr(packed.device)),
+              "turboquant_bit_unpack")
+    return out
+
+
+__all__ = [
+    "kivi_available", "storage_bits", "kivi_group_quant_dequant", "kivi_quantize", "kivi_quantize_into",
+    "scalar_decode_once", "kivi_decode_attend", "scalar_fused_decode_attend", "scalar_predecoded_attend",
+    "turboquant_bit_pack", "turboquant_bit_unpack",
+]
