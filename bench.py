@@ -1,0 +1,390 @@
+#!/usr/bin/env python
+"""Benchmark of the compressed-KV decode hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Workload (default): the Llama-3.1-8B-shaped decode configuration -- 32 layers, 32 query
+heads, 8 KV heads, head_dim 128, KIVI 4-bit keys (per channel) and values (per token),
+group 32, a 128-token bf16 residual window, batch 16 per GPU, context 32768, bf16
+activations, K/V ~ N(0,1) with 4 outlier channels per head scaled x20. A "step" is one
+decode step of the attention path: for each layer, fused dequant + attention of one new
+query token over that layer's packed cache (no model weights are involved).
+
+Scaling across GPUs is weak: every rank holds its own batch shard of 16 sequences (the
+(batch, kv head) units are independent, so attention needs no collective); for N > 1 each
+layer's output is all-gathered over NCCL, overlapped with the next layer's attention.
+
+One JSON line is printed by rank 0. `value` is KV GB/s: algorithmic bytes of packed
+codes, scales, zero-points, residual window, queries and outputs that one step must move,
+divided by the step time, summed over ranks. `e2e` is the same metric through the cache
+interface with host buffers (query and new K/V token copied in, output copied out, every
+step). `--impl reference` times the CPU oracle (a NumPy restatement of the reference's
+path; the reference's own MLX code cannot be installed on this box) on a bounded sample.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+METRIC = "fused dequant-SDPA decode KV GB/s"
+UNIT = "GB/s"
+
+
+# ----------------------------------------------------------------------------- workload
+def workload(args):
+    w = dict(name="llama3.1-8b-decode-kivi4", layers=32, H_q=32, H_kv=8, D=128, bits=4, group=32,
+             residual=128, batch=16, ctx=32768, dtype="bf16")
+    if args.workload == "c1":
+        w.update(name="kivi2-single-layer", layers=1, bits=2, batch=1, ctx=4096, dtype="f16")
+    elif args.workload == "c5":
+        w.update(name="qwen2.5-32b-decode-kivi2", layers=64, H_q=40, bits=2, batch=4, ctx=16384 + 256)
+    for k in ("layers", "batch", "ctx", "bits"):
+        v = getattr(args, k)
+        if v is not None:
+            w[k] = v
+    w["n_quant"] = max(0, (w["ctx"] - w["residual"]) // w["group"]) * w["group"]
+    w["n_res"] = w["ctx"] - w["n_quant"]
+    return w
+
+
+def algorithmic_bytes_per_layer(w, batch=None):
+    """Bytes one layer's attend must move: packed codes + fp32 params + residual + q + out."""
+    B = w["batch"] if batch is None else batch
+    D, g, b, Sq, R = w["D"], w["group"], w["bits"], w["n_quant"], w["n_res"]
+    per_head = (Sq * D * b // 8 + (Sq // g) * D * 8) + (Sq * D * b // 8 + Sq * (D // g) * 8) + 2 * R * D * 2
+    return B * (w["H_kv"] * per_head + 2 * w["H_q"] * D * 2)
+
+
+# ----------------------------------------------------------------------------- clocks
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.gpu_index = gpu_index
+        self.proc = None
+        self.lines = []
+        self.nvml = None
+
+    def _start_nvml(self):
+        """Preferred: poll NVML in-process (no pipe buffering between us and the samples)."""
+        import pynvml
+
+        pynvml.nvmlInit()
+        vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+        phys = self.gpu_index
+        if vis:
+            ids = [v for v in vis.split(",") if v.strip()]
+            if self.gpu_index < len(ids) and ids[self.gpu_index].strip().isdigit():
+                phys = int(ids[self.gpu_index])
+        h = pynvml.nvmlDeviceGetHandleByIndex(phys)
+        self.nvml = {"sm": [], "power": [], "reasons": set(), "stop": False,
+                     "max": pynvml.nvmlDeviceGetMaxClockInfo(h, pynvml.NVML_CLOCK_SM)}
+        bits = {"hw_slowdown": pynvml.nvmlClocksEventReasonHwSlowdown,
+                "hw_thermal_slowdown": pynvml.nvmlClocksEventReasonHwThermalSlowdown,
+                "sw_thermal_slowdown": pynvml.nvmlClocksEventReasonSwThermalSlowdown,
+                "sw_power_cap": pynvml.nvmlClocksEventReasonSwPowerCap}
+
+        def poll():
+            while not self.nvml["stop"]:
+                try:
+                    self.nvml["sm"].append(pynvml.nvmlDeviceGetClockInfo(h, pynvml.NVML_CLOCK_SM))
+                    self.nvml["power"].append(pynvml.nvmlDeviceGetPowerUsage(h) / 1000.0)
+                    r = pynvml.nvmlDeviceGetCurrentClocksEventReasons(h)
+                    for nm, bit in bits.items():
+                        if r & bit:
+                            self.nvml["reasons"].add(nm)
+                except Exception:
+                    pass
+                time.sleep(0.02)
+
+        self.thread = threading.Thread(target=poll, daemon=True)
+        self.thread.start()
+
+    def start(self):
+        try:
+            self._start_nvml()
+            return
+        except Exception:
+            self.nvml = None
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.gpu_index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.nvml is not None:
+            self.nvml["stop"] = True
+            self.thread.join(timeout=2)
+            sm = self.nvml["sm"]
+            return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": float(self.nvml["max"]),
+                    "power_w_max": max(self.nvml["power"]) if self.nvml["power"] else None,
+                    "samples": len(sm), "reasons": sorted(self.nvml["reasons"]), "source": "nvml"}
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons, power = [], [], set(), []
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1])); mx.append(float(f[2])); power.append(float(f[3]))
+            except ValueError:
+                continue
+            for nm, val in zip(names, f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(nm)
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "power_w_max": max(power) if power else None, "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def measured_peak():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        try:
+            return float(json.load(open(p))["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return 6650.0, "fallback"
+
+
+# ----------------------------------------------------------------------------- CPU oracle arm
+def cpu_reference_sample(w, seconds_budget=20.0, seed=0):
+    """Time the oracle (NumPy restatement of the reference's KIVI quantize + attend) on a
+    bounded sample of the workload: one layer, as many sequences of the batch as fit the
+    budget. Returns (GB/s by the same algorithmic-bytes formula, sample description, cores)."""
+    from oracle import kivi as ok
+
+    rng = np.random.default_rng(seed)
+    H_kv, H_q, D, g, b = w["H_kv"], w["H_q"], w["D"], w["group"], w["bits"]
+    Sq, R = w["n_quant"], w["n_res"]
+    levels = (1 << b) - 1
+    k = rng.standard_normal((1, H_kv, Sq + R, D)).astype(np.float16)
+    v = rng.standard_normal((1, H_kv, Sq + R, D)).astype(np.float16)
+    q = rng.standard_normal((1, H_q, 1, D)).astype(np.float16)
+    kc, ks, kz = ok.quant_keys(k[:, :, :Sq], g, levels)
+    vc, vs, vz = ok.quant_values(v[:, :, :Sq], g, levels)
+    scale = 1.0 / math.sqrt(D)
+    ok.reference_attend(q, kc, ks, kz, vc, vs, vz, g, scale, k_res=k[:, :, Sq:], v_res=v[:, :, Sq:])  # warm-up
+    times = []
+    t_start = time.perf_counter()
+    while len(times) < 3 or (time.perf_counter() - t_start < seconds_budget and len(times) < 50):
+        t0 = time.perf_counter()
+        ok.reference_attend(q, kc, ks, kz, vc, vs, vz, g, scale, k_res=k[:, :, Sq:], v_res=v[:, :, Sq:])
+        times.append(time.perf_counter() - t0)
+    t = float(np.median(times))
+    nbytes = algorithmic_bytes_per_layer(w, batch=1)
+    sample = (f"1 layer x 1 sequence of the batch ({H_kv} kv heads, {Sq}+{R} tokens), median of "
+              f"{len(times)} runs of oracle.kivi.reference_attend (NumPy, BLAS threads); MLX unavailable on this box")
+    return nbytes / t / 1e9, sample, os.cpu_count(), t
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    w = workload(args)
+    per_step_budget = 8.0
+    vals = []
+    for _ in range(args.warmup):
+        cpu_reference_sample(w, seconds_budget=0.0)
+    t_all = 0.0
+    sample = ""
+    cores = os.cpu_count()
+    for _ in range(args.steps):
+        gbs, sample, cores, t = cpu_reference_sample(w, seconds_budget=per_step_budget / 4)
+        vals.append(gbs)
+        t_all += t
+    value = float(np.median(vals))
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": 1e3 * t_all / max(args.steps, 1), "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": w["dtype"], "data": "synthetic",
+        "config": {"workload": w["name"], **{k: w[k] for k in ("layers", "batch", "ctx", "bits", "group", "residual", "H_q", "H_kv", "D")}},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ----------------------------------------------------------------------------- our arm
+def build_layer(torch, kernels, w, device, seed, dtype):
+    """Seeded synthetic K/V for one layer, quantized on the device into packed buffers."""
+    B, H_kv, D, g, b = w["batch"], w["H_kv"], w["D"], w["group"], w["bits"]
+    Sq, R = w["n_quant"], w["n_res"]
+    gen = torch.Generator(device=device)
+    gen.manual_seed(seed)
+    out = {}
+    ch = torch.randperm(D, generator=gen, device=device)[:4]
+    for name, axis in (("k", -2), ("v", -1)):
+        x = torch.randn((B, H_kv, Sq + R, D), generator=gen, device=device, dtype=torch.float32)
+        x[..., ch] *= 20.0
+        x = x.to(dtype)
+        codes, scale, zero = kernels.kivi_quantize(x[:, :, :Sq], axis, g, b)
+        out[name] = (codes, scale, zero)
+        out[name + "_res"] = x[:, :, Sq:].contiguous()
+        del x
+    return out
+
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+
+    from veloxquant_mlx_b200 import kernels
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device; the product path has no CPU fallback")
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    w = workload(args)
+    dtype = torch.bfloat16 if w["dtype"] == "bf16" else torch.float16
+    L, B, H_q, D = w["layers"], w["batch"], w["H_q"], w["D"]
+    scale = 1.0 / math.sqrt(D)
+
+    layers = [build_layer(torch, kernels, w, device, 1000 * rank + l, dtype) for l in range(L)]
+    gen = torch.Generator(device=device)
+    gen.manual_seed(7 + rank)
+    qs = [torch.randn((B, H_q, 1, D), generator=gen, device=device, dtype=torch.float32).to(dtype) for _ in range(L)]
+    outs = [torch.empty((B, H_q, 1, D), device=device, dtype=dtype) for _ in range(L)]
+    gathered = [torch.empty((world * B, H_q, 1, D), device=device, dtype=dtype) for _ in range(L)] if world > 1 else None
+    comm_stream = torch.cuda.Stream(device) if world > 1 else None
+    torch.cuda.synchronize()
+
+    def step():
+        works = []
+        for l in range(L):
+            ly = layers[l]
+            kernels.kivi_decode_attend(qs[l], *ly["k"], *ly["v"], w["group"], scale, store_bits=w["bits"],
+                                       n_quant=w["n_quant"], k_res=ly["k_res"], v_res=ly["v_res"], out=outs[l],
+                                       n_splits=args.splits)
+            if world > 1:
+                ev = torch.cuda.Event()
+                ev.record()
+                with torch.cuda.stream(comm_stream):
+                    comm_stream.wait_event(ev)
+                    dist.all_gather_into_tensor(gathered[l], outs[l])
+        if world > 1:
+            torch.cuda.current_stream().wait_stream(comm_stream)
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    barrier()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    barrier()
+    ms = e0.elapsed_time(e1)
+    clocks = sampler.stop() if rank == 0 else None
+    t = torch.tensor([ms], device=device, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_total = float(t.item())
+    ms_step = ms_total / args.steps
+
+    from veloxquant_mlx_b200 import _lib
+    _lib.check(_lib.lib().vq_kivi_attend_status(), "bench")
+
+    if rank == 0:
+        bytes_layer = algorithmic_bytes_per_layer(w)
+        bytes_step = bytes_layer * L
+        value = world * bytes_step / (ms_step * 1e-3) / 1e9
+        peak, peak_kind = measured_peak()
+        per_launch_s = ms_step * 1e-3 / L
+        achieved = bytes_layer / per_launch_s / 1e9
+        cpu = None
+        if world == 1 and not args.no_cpu_baseline:
+            gbs, sample, cores, _ = cpu_reference_sample(w, seconds_budget=15.0)
+            cpu = {"value": gbs, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample}
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": w["dtype"], "data": "synthetic",
+            "config": {"workload": w["name"], **{k: w[k] for k in ("layers", "batch", "ctx", "bits", "group", "residual", "H_q", "H_kv", "D")},
+                       "global_batch": world * B, "parallelism": f"dp{world} over (batch, kv head) units",
+                       "l2": "inputs larger than L2: each layer's packed KV is read once per step and 32 distinct layers are cycled"},
+            "tokens_per_s": world * B / (ms_step * 1e-3),
+            "pct_of_hbm_peak": 100.0 * (value / world) / peak,
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                         "peak_kind": peak_kind + " (burst copy)", "traffic": None,
+                         "kernel": f"kivi_attend_mma_kernel<{w['bits']}> (+ merge; duration = step time / layers)",
+                         "algorithmic_bytes_per_launch": bytes_layer},
+            "cpu_baseline": cpu,
+            "e2e": None,
+            "gpu_launches": 2 * L * args.steps,
+            "clocks": clocks,
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="c3", choices=["c3", "c1", "c5"])
+    ap.add_argument("--layers", type=int, default=None)
+    ap.add_argument("--batch", type=int, default=None)
+    ap.add_argument("--ctx", type=int, default=None)
+    ap.add_argument("--bits", type=int, default=None)
+    ap.add_argument("--splits", type=int, default=0)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

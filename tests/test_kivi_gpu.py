@@ -292,3 +292,91 @@ def test_predecoded_attend_and_validation_errors():
     one = [t[:, :1].contiguous() for t in ins[1:]]
     with pytest.raises(ValueError, match="exceeds the supported maximum"):
         k.scalar_fused_decode_attend(bigq[:, :17 * 1], *[t for t in one], 32, 0.1)
+
+
+# ----------------------------------------------------------------- tensor-core kernel
+def _packed_case(rng, B, H, H_kv, n_quant, n_res, b, dt, outliers=False):
+    D, g = 128, 32
+    k = _k()
+    kf = rng.standard_normal((B, H_kv, n_quant + n_res, D)).astype(np.float32)
+    vf = rng.standard_normal((B, H_kv, n_quant + n_res, D)).astype(np.float32)
+    if outliers:  # 4 fixed outlier channels per head, x20 (reference: tests/allocators/test_vecinfer.py:67-77)
+        for h in range(H_kv):
+            ch = rng.choice(D, size=4, replace=False)
+            kf[:, h, :, ch] *= 20.0
+            vf[:, h, :, ch] *= 20.0
+    qt, q32 = _np_cast(rng.standard_normal((B, H, 1, D)).astype(np.float32), dt)
+    kt, k32 = _np_cast(kf, dt)
+    vt, v32 = _np_cast(vf, dt)
+    kc, ks, kz = k.kivi_quantize(kt[:, :, :n_quant], -2, g, b)
+    vc, vs, vz = k.kivi_quantize(vt[:, :, :n_quant], -1, g, b)
+    levels = (1 << b) - 1
+    okc, oks, okz = o_kivi.quant_keys(k32[:, :, :n_quant], g, levels)
+    ovc, ovs, ovz = o_kivi.quant_values(v32[:, :, :n_quant], g, levels)
+    np.testing.assert_array_equal(kc.cpu().numpy(), o_bitpack.pack(okc, b))
+    np.testing.assert_array_equal(vc.cpu().numpy(), o_bitpack.pack(ovc, b))
+    ref = o_kivi.reference_attend(q32, okc, oks, okz, ovc, ovs, ovz, g, 1.0 / math.sqrt(D),
+                                  k_res=k32[:, :, n_quant:], v_res=v32[:, :, n_quant:])
+    k_res = kt[:, :, n_quant:].contiguous() if n_res else None
+    v_res = vt[:, :, n_quant:].contiguous() if n_res else None
+    return (qt, kc, ks, kz, vc, vs, vz, k_res, v_res), ref
+
+
+@pytest.mark.parametrize("b", [2, 4])
+@pytest.mark.parametrize("H,H_kv", [(4, 4), (8, 4), (8, 2), (8, 1), (12, 2)])
+@pytest.mark.parametrize("n_quant,n_res", [(32, 0), (128, 5), (160, 128), (1024 + 96, 37), (4096 - 128, 128)])
+def test_mma_attend_parity(b, H, H_kv, n_quant, n_res):
+    rng = np.random.default_rng(b + H + n_quant)
+    (qt, kc, ks, kz, vc, vs, vz, k_res, v_res), ref = _packed_case(rng, 2, H, H_kv, n_quant, n_res, b, "float16")
+    k = _k()
+    out = k.kivi_decode_attend(qt, kc, ks, kz, vc, vs, vz, 32, 1.0 / math.sqrt(128), store_bits=b,
+                               k_res=k_res, v_res=v_res, variant=2)
+    _assert_attn_close(out.float().cpu().numpy(), ref)
+    from veloxquant_mlx_b200 import _lib
+    _lib.check(_lib.lib().vq_kivi_attend_status(), "status")
+    # the general kernel agrees too, and an explicit split count changes nothing material
+    out1 = k.kivi_decode_attend(qt, kc, ks, kz, vc, vs, vz, 32, 1.0 / math.sqrt(128), store_bits=b,
+                                k_res=k_res, v_res=v_res, variant=1)
+    _assert_attn_close(out1.float().cpu().numpy(), ref)
+    out3 = k.kivi_decode_attend(qt, kc, ks, kz, vc, vs, vz, 32, 1.0 / math.sqrt(128), store_bits=b,
+                                k_res=k_res, v_res=v_res, variant=2, n_splits=3)
+    _assert_attn_close(out3.float().cpu().numpy(), ref)
+
+
+@pytest.mark.parametrize("b", [2, 4])
+@pytest.mark.parametrize("dt", ["float16", "bfloat16"])
+def test_mma_attend_config1_with_outlier_channels(b, dt):
+    """BASELINE config 1 shape: B=1, 8 kv heads, 32 q heads, S=4096, residual 128, outliers x20."""
+    rng = np.random.default_rng(0)
+    args, ref = _packed_case(rng, 1, 32, 8, 4096 - 128, 128, b, dt, outliers=True)
+    qt, kc, ks, kz, vc, vs, vz, k_res, v_res = args
+    out = _k().kivi_decode_attend(qt, kc, ks, kz, vc, vs, vz, 32, 1.0 / math.sqrt(128), store_bits=b,
+                                  k_res=k_res, v_res=v_res, variant=2)
+    assert out.dtype == qt.dtype
+    _assert_attn_close(out.float().cpu().numpy(), ref, strict=False)
+
+
+def test_mma_attend_in_capacity_buffers():
+    """Codes live in larger pre-allocated buffers; only the first n_quant rows are attended."""
+    rng = np.random.default_rng(3)
+    k = _k()
+    B, H, H_kv, D, g, b, cap, n_quant, n_res = 2, 8, 2, 128, 32, 4, 512, 320, 40
+    (qt, kc, ks, kz, vc, vs, vz, k_res, v_res), ref = _packed_case(rng, B, H, H_kv, n_quant, n_res, b, "float16")
+    def grow(t, n):
+        out = torch.zeros(t.shape[0], t.shape[1], n, t.shape[3], dtype=t.dtype, device=t.device)
+        out[:, :, :t.shape[2]] = t
+        return out
+    KC, VC, VS, VZ = grow(kc, cap), grow(vc, cap), grow(vs, cap), grow(vz, cap)
+    KS, KZ = grow(ks, cap // g), grow(kz, cap // g)
+    KR, VR = grow(k_res, 160), grow(v_res, 160)
+    for variant in (1, 2):
+        out = k.kivi_decode_attend(qt, KC, KS, KZ, VC, VS, VZ, g, 1.0 / math.sqrt(D), store_bits=b,
+                                   n_quant=n_quant, k_res=KR, v_res=VR, n_res=n_res, variant=variant)
+        _assert_attn_close(out.float().cpu().numpy(), ref)
+
+
+def test_mma_variant_rejects_unsupported_shapes():
+    k = _k()
+    ins = _to_dev(*o_kivi.make_inputs(1, 4, 64, 64, 2, 32))
+    with pytest.raises(ValueError, match="tensor-core kernel unavailable"):
+        k.kivi_decode_attend(*ins, 32, 0.1, store_bits=8, variant=2)

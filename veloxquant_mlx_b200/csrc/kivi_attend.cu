@@ -201,10 +201,23 @@ extern "C" int64_t vq_kivi_attend_workspace_bytes(const vq_kivi_attend_args *arg
     if (!args) return 0;
     const vq_kivi_attend_args &a = *args;
     if (a.B < 1 || a.H_q < 1 || a.S_q < 1 || a.D < 1) return 0;
-    // Room for the largest split count either kernel may choose.
+    // Room for the split count of whichever kernel the call will pick (+1 part for the tail).
+    DeviceInfo di;
+    if (device_info(&di) != VQ_OK) { di.sm_count = 148; di.smem_optin = 227 * 1024; }
     const int64_t rows = (int64_t)a.B * a.H_q * a.S_q;
-    const int64_t splits = a.n_splits > 0 ? a.n_splits : 256;
+    int64_t splits = general_splits(a, di.sm_count);
+    if (a.variant != 1 && a.H_kv >= 1 && a.H_q % a.H_kv == 0 && kivi_attend_mma_supported(a) == nullptr)
+        splits = std::max<int64_t>(splits, kivi_attend_mma_splits(a, di) + 1);
     return rows * splits * ((int64_t)a.D + 2) * (int64_t)sizeof(float) + 256;
+}
+
+extern "C" int32_t vq_kivi_attend_status(void) {
+    using namespace vq;
+    int flag = 0;
+    int32_t rc = kivi_attend_mma_take_timeout(&flag);
+    if (rc != VQ_OK) return rc;
+    if (flag) return fail(VQ_ERR_TIMEOUT, "vq_kivi_decode_attend: a bounded wait on a bulk-copy barrier gave up");
+    return VQ_OK;
 }
 
 extern "C" int32_t vq_kivi_decode_attend(const vq_kivi_attend_args *args, void *stream) {

@@ -1,9 +1,716 @@
-// Placeholder until the tensor-core kernel lands.
+// Fused dequant + single-query attention over packed 2-/4-bit KIVI codes for the serving
+// shape (head_dim 128, group 32, one query row, <= 8 query heads per KV head).
+//
+// Why tensor cores: with the query heads of one KV head packed together, every KV token
+// costs 2*128*heads multiply-adds; at B200's HBM rate that is several times what the FP32
+// pipes sustain, so QK^T and PV run as m16n8k16 f16 MMAs with the KV tokens (QK^T) and the
+// head_dim rows (PV) on the M axis and the packed query heads on the 8-wide N axis.
+//
+// Exactness: the A operands are the RAW integer codes, produced in registers from the
+// packed words by a mask and a magic-number subtract (exact halves, no int->float cvt).
+// The group scales never touch the codes in half precision; they are folded, in float32,
+// into the small B operands instead:
+//     q.K_hat[t]  = sum_d code[t,d] * (q[d]*k_scale[G,d])  +  sum_d q[d]*k_zero[G,d]
+//     P.V_hat[:,d] = sum_t code[t,d] * (P[t]*v_scale[t,g(d)]) + sum_t P[t]*v_zero[t,g(d)]
+// and each float32 B value is split into a high and a low half (x = hi + lo) that occupy
+// the 4 + 4 columns of the N = 8 tile, so products are exact and sums are float32. The two
+// zero-point terms are plain float32 FMAs. Up to 4 query heads fit one CTA this way; a KV
+// head with 5..8 query heads is covered by two CTAs (the second read hits L2).
+// Warp-level MMAs are used (not tcgen05) because the A operand is born in registers.
+//
+// Data movement: one CTA owns a contiguous run of 128-token tiles of one (batch, kv head).
+// Per tile six contiguous pieces (K codes, V codes, K scale/zero for 4 groups, V scale/zero
+// for 128 tokens) are fetched by the bulk async-copy engine (cp.async.bulk, completion on
+// an mbarrier) into a 3-stage shared-memory ring, so HBM reads stay in flight while the
+// warps unpack. Warp w owns token group w of each tile (32 tokens = one K scale group).
+// The context is split across CTAs; each writes an unnormalised partial (m, l, o) and a
+// small second kernel merges them. The unquantized tail is one more partial from a
+// CUDA-core CTA in the same launch.
+#include <algorithm>
+
 #include "kivi_attend.h"
+
 namespace vq {
-const char *kivi_attend_mma_supported(const vq_kivi_attend_args &) { return "not built"; }
-int kivi_attend_mma_splits(const vq_kivi_attend_args &, const DeviceInfo &) { return 1; }
-int32_t kivi_attend_mma_launch(const vq_kivi_attend_args &, const DeviceInfo &, cudaStream_t) {
-    return fail(VQ_ERR_SHAPE, "tensor-core kernel not built");
+
+namespace {
+
+constexpr int kD = 128;
+constexpr int kTile = 128;     // tokens per pipeline stage
+constexpr int kWarps = 4;
+constexpr int kStages = 3;
+constexpr int kMaxHeads = 8;   // query heads per kv head
+constexpr int kChunkHeads = 4; // query heads per CTA (hi/lo halves fill the 8 MMA columns)
+constexpr uint32_t kSpinLimit = 1u << 18;
+
+__device__ int g_attend_timeout = 0;
+
+template <int BITS>
+struct Cfg {
+    static constexpr int RB = kD * BITS / 8;     // bytes per packed row: 64 / 32
+    static constexpr int CPW = 32 / BITS;        // codes per 32-bit word: 8 / 16
+    static constexpr int NH = CPW / 2;           // half2 registers per unpacked word: 4 / 8
+    static constexpr int KW = 32 / CPW;          // words of one thread's 32-channel K chunk: 4 / 2
+    static constexpr int CU = 16 / BITS;         // codes per 16-bit unit: 4 / 8
+    static constexpr int NSEG = RB / 16;         // 16-byte segments per row: 4 / 2
+    static constexpr int KC_OFF = 0;
+    static constexpr int VC_OFF = kTile * RB;
+    static constexpr int KS_OFF = 2 * kTile * RB;
+    static constexpr int KZ_OFF = KS_OFF + 2048;
+    static constexpr int VS_OFF = KZ_OFF + 2048;
+    static constexpr int VZ_OFF = VS_OFF + 2048;
+    static constexpr int STAGE_BYTES = VZ_OFF + 2048;  // 24576 / 16384
+    static constexpr int SMEM_BYTES = 128 + kStages * STAGE_BYTES;
+};
+
+// ---- PTX helpers ------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void *p) {
+    return (uint32_t)__cvta_generic_to_shared(p);
 }
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+// Bounded wait: returns false (and the caller records a timeout) instead of spinning forever.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+    for (uint32_t i = 0; i < kSpinLimit; ++i) {
+        uint32_t ok;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(ok)
+            : "r"(bar), "r"(parity)
+            : "memory");
+        if (ok) return true;
+    }
+    return false;
+}
+__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
+        "l"(src), "r"(bytes), "r"(bar)
+        : "memory");
+}
+__device__ __forceinline__ uint32_t lop3_and_or(uint32_t a, uint32_t b, uint32_t c) {
+    uint32_t r;
+    asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(r) : "r"(a), "r"(b), "r"(c));
+    return r;
+}
+__device__ __forceinline__ uint32_t h2sub(uint32_t a, uint32_t b) {
+    uint32_t r;
+    asm("sub.f16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+    return r;
+}
+__device__ __forceinline__ uint32_t pack_h2(float lo, float hi) {
+    __half2 h = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<uint32_t *>(&h);
+}
+__device__ __forceinline__ float2 unpack_h2(uint32_t v) {
+    return __half22float2(*reinterpret_cast<__half2 *>(&v));
+}
+// x = hi + lo with hi = half(x), lo = half(x - hi): ~22 significant bits in two halves.
+__device__ __forceinline__ void split_h2(float x0, float x1, uint32_t &hi, uint32_t &lo) {
+    hi = pack_h2(x0, x1);
+    const float2 h = unpack_h2(hi);
+    lo = pack_h2(x0 - h.x, x1 - h.y);
+}
+__device__ __forceinline__ void mma_f16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                        uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t movmatrix_trans(uint32_t a) {
+    uint32_t r;
+    asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(r) : "r"(a));
+    return r;
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(addr));
+}
+
+// Unpack one 32-bit word into half2 registers holding exact integer code values.
+// Register i pairs the i-th code of the low 16 bits with the i-th code of the high 16
+// bits. Codes are moved into a half's mantissa by a mask and an OR with a power-of-two
+// exponent ("magic number"), then the power of two is subtracted: exact, no int->float cvt.
+template <int BITS>
+__device__ __forceinline__ void unpack_word(uint32_t w, uint32_t (&h)[32 / BITS / 2]);
+
+template <>
+__device__ __forceinline__ void unpack_word<4>(uint32_t w, uint32_t (&h)[4]) {
+    const uint32_t w8 = w >> 8;
+    h[0] = h2sub(lop3_and_or(w, 0x000f000fu, 0x64006400u), 0x64006400u);   // 1024 + c
+    h[1] = h2sub(lop3_and_or(w, 0x00f000f0u, 0x54005400u), 0x54005400u);   //   64 + c
+    h[2] = h2sub(lop3_and_or(w8, 0x000f000fu, 0x64006400u), 0x64006400u);
+    h[3] = h2sub(lop3_and_or(w8, 0x00f000f0u, 0x54005400u), 0x54005400u);
+}
+template <>
+__device__ __forceinline__ void unpack_word<2>(uint32_t w, uint32_t (&h)[8]) {
+    const uint32_t w10 = w >> 10;
+    h[0] = h2sub(lop3_and_or(w, 0x00030003u, 0x64006400u), 0x64006400u);   // 1024 + c
+    h[1] = h2sub(lop3_and_or(w, 0x000c000cu, 0x5c005c00u), 0x5c005c00u);   //  256 + c
+    h[2] = h2sub(lop3_and_or(w, 0x00300030u, 0x54005400u), 0x54005400u);   //   64 + c
+    h[3] = h2sub(lop3_and_or(w, 0x00c000c0u, 0x4c004c00u), 0x4c004c00u);   //   16 + c
+    h[4] = h2sub(lop3_and_or(w, 0x03000300u, 0x44004400u), 0x44004400u);   //    4 + c
+    h[5] = h2sub(lop3_and_or(w10, 0x00030003u, 0x64006400u), 0x64006400u);
+    h[6] = h2sub(lop3_and_or(w10, 0x000c000cu, 0x5c005c00u), 0x5c005c00u);
+    h[7] = h2sub(lop3_and_or(w10, 0x00300030u, 0x54005400u), 0x54005400u);
+}
+
+struct Params {
+    vq_kivi_attend_args a;
+    int hpk;
+    int n_chunks;       // ceil(hpk / 4)
+    int n_splits;       // quantized-context splits
+    int n_parts;        // n_splits + (tail present)
+    int tiles_total;    // ceil(n_quant / 128)
+    int tiles_per_split;
+    float *part_o;      // [B*H_kv][n_parts][hpk][128]
+    float *part_ml;     // [B*H_kv][n_parts][hpk][2]
+};
+
+// ---- tail (unquantized tokens): CUDA cores, one CTA per (batch, kv head) ------------------
+__device__ void tail_partial(const Params &p, uint8_t *smem_raw, int b, int hkv) {
+    const vq_kivi_attend_args &a = p.a;
+    float *sh_q = reinterpret_cast<float *>(smem_raw);           // [8][128]
+    float *sh_o = sh_q + kMaxHeads * kD;                         // [4][8][128]
+    float *sh_m = sh_o + kWarps * kMaxHeads * kD;                // [4][8]
+    float *sh_l = sh_m + kWarps * kMaxHeads;                     // [4][8]
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int hpk = p.hpk;
+    const int64_t bh = (int64_t)b * a.H_kv + hkv;
+    const float sc = a.scale * 1.4426950408889634f;
+    for (int i = threadIdx.x; i < hpk * kD; i += blockDim.x) {
+        const int hp = i / kD, d = i % kD;
+        sh_q[i] = load_as_f32(a.q, a.q_dtype, ((int64_t)b * a.H_q + hkv * hpk + hp) * kD + d) * sc;
+    }
+    __syncthreads();
+    float m[kMaxHeads], l[kMaxHeads], o[kMaxHeads][4];
+#pragma unroll
+    for (int hp = 0; hp < kMaxHeads; ++hp) {
+        m[hp] = -INFINITY;
+        l[hp] = 0.f;
+        o[hp][0] = o[hp][1] = o[hp][2] = o[hp][3] = 0.f;
+    }
+    for (int t = warp; t < a.n_res; t += kWarps) {
+        const int64_t r = bh * a.res_stride_bh + (int64_t)t * kD + lane * 4;
+        float kd[4], vd[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            kd[i] = load_as_f32(a.k_res, a.res_dtype, r + i);
+            vd[i] = load_as_f32(a.v_res, a.res_dtype, r + i);
+        }
+#pragma unroll
+        for (int hp = 0; hp < kMaxHeads; ++hp) {
+            if (hp < hpk) {
+                const float4 qv = *reinterpret_cast<const float4 *>(sh_q + hp * kD + lane * 4);
+                float s = warp_sum(qv.x * kd[0] + qv.y * kd[1] + qv.z * kd[2] + qv.w * kd[3]);
+                const float mn = fmaxf(m[hp], s);
+                const float f = exp2f(m[hp] - mn), w = exp2f(s - mn);
+                l[hp] = l[hp] * f + w;
+                m[hp] = mn;
+#pragma unroll
+                for (int i = 0; i < 4; ++i) o[hp][i] = o[hp][i] * f + w * vd[i];
+            }
+        }
+    }
+#pragma unroll
+    for (int hp = 0; hp < kMaxHeads; ++hp) {
+        if (hp < hpk) {
+            if (lane == 0) { sh_m[warp * kMaxHeads + hp] = m[hp]; sh_l[warp * kMaxHeads + hp] = l[hp]; }
+#pragma unroll
+            for (int i = 0; i < 4; ++i) sh_o[(warp * kMaxHeads + hp) * kD + lane * 4 + i] = o[hp][i];
+        }
+    }
+    __syncthreads();
+    const int part = p.n_parts - 1;
+    for (int i = threadIdx.x; i < hpk * kD; i += blockDim.x) {
+        const int hp = i / kD, d = i % kD;
+        float gm = -INFINITY;
+        for (int w = 0; w < kWarps; ++w) gm = fmaxf(gm, sh_m[w * kMaxHeads + hp]);
+        float gl = 0.f, acc = 0.f;
+        for (int w = 0; w < kWarps; ++w) {
+            const float mw = sh_m[w * kMaxHeads + hp];
+            const float f = (mw == -INFINITY) ? 0.f : exp2f(mw - gm);
+            gl += sh_l[w * kMaxHeads + hp] * f;
+            acc += sh_o[(w * kMaxHeads + hp) * kD + d] * f;
+        }
+        const int64_t rec = (bh * p.n_parts + part) * hpk + hp;
+        p.part_o[rec * kD + d] = acc;
+        if (d == 0) { p.part_ml[rec * 2] = gm; p.part_ml[rec * 2 + 1] = gl; }
+    }
+}
+
+// ---- main kernel ----------------------------------------------------------------------------
+// Lane roles (g = lane / 4, c = lane % 4):
+//   as a B-operand column (n = g): query head g % 4, high half if g < 4, low half otherwise;
+//   as an accumulator column pair (cols 2c, 2c+1): heads 2(c%2), 2(c%2)+1, high halves if
+//   c < 2, low halves otherwise (lanes c and c^2 hold the two halves of the same heads).
+template <int BITS>
+__global__ void __launch_bounds__(kWarps * 32)
+kivi_attend_mma_kernel(const __grid_constant__ Params p) {
+    using C = Cfg<BITS>;
+    extern __shared__ __align__(128) uint8_t smem_raw[];
+    const vq_kivi_attend_args &a = p.a;
+    const int b = blockIdx.z, hkv = blockIdx.y;
+    if ((int)blockIdx.x >= p.n_splits * p.n_chunks) {  // the tail CTA
+        tail_partial(p, smem_raw, b, hkv);
+        return;
+    }
+    const int split = blockIdx.x / p.n_chunks;
+    const int h0 = (blockIdx.x % p.n_chunks) * kChunkHeads;  // first head of this CTA's chunk
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int g = lane >> 2, c = lane & 3;
+    const int hd = g & 3, half_id = g >> 2;
+    const int hpk = p.hpk;
+    const int64_t bh = (int64_t)b * a.H_kv + hkv;
+
+    uint64_t *bars = reinterpret_cast<uint64_t *>(smem_raw);
+    uint8_t *stages = smem_raw + 128;
+    const uint32_t bar0 = smem_u32(bars);
+
+    const int tile_begin = split * p.tiles_per_split;
+    const int tile_end = min(p.tiles_total, tile_begin + p.tiles_per_split);
+    const int n_local = max(0, tile_end - tile_begin);
+
+    const uint8_t *kc_g = a.k_codes + bh * a.k_codes_stride_bh;
+    const uint8_t *vc_g = a.v_codes + bh * a.v_codes_stride_bh;
+    const float *ks_g = a.k_scale + bh * a.k_param_stride_bh;
+    const float *kz_g = a.k_zero + bh * a.k_param_stride_bh;
+    const float *vs_g = a.v_scale + bh * a.v_param_stride_bh;
+    const float *vz_g = a.v_zero + bh * a.v_param_stride_bh;
+
+    auto issue_tile = [&](int local_idx) {
+        const int tile = tile_begin + local_idx;
+        const int tok0 = tile * kTile;
+        const int ntok = min(kTile, a.n_quant - tok0);  // multiple of 32
+        const int stage = local_idx % kStages;
+        const uint32_t bar = bar0 + 8u * stage;
+        const uint32_t dst = smem_u32(stages + (size_t)stage * C::STAGE_BYTES);
+        const uint32_t code_bytes = (uint32_t)ntok * C::RB;
+        const uint32_t kp_bytes = (uint32_t)(ntok / 32) * kD * 4;
+        const uint32_t vp_bytes = (uint32_t)ntok * 16;
+        mbar_expect_tx(bar, 2 * code_bytes + 2 * kp_bytes + 2 * vp_bytes);
+        bulk_g2s(dst + C::KC_OFF, kc_g + (int64_t)tok0 * C::RB, code_bytes, bar);
+        bulk_g2s(dst + C::VC_OFF, vc_g + (int64_t)tok0 * C::RB, code_bytes, bar);
+        bulk_g2s(dst + C::KS_OFF, ks_g + (int64_t)(tok0 / 32) * kD, kp_bytes, bar);
+        bulk_g2s(dst + C::KZ_OFF, kz_g + (int64_t)(tok0 / 32) * kD, kp_bytes, bar);
+        bulk_g2s(dst + C::VS_OFF, vs_g + (int64_t)tok0 * 4, vp_bytes, bar);
+        bulk_g2s(dst + C::VZ_OFF, vz_g + (int64_t)tok0 * 4, vp_bytes, bar);
+    };
+
+    if (tid == 0) {
+        for (int s = 0; s < kStages; ++s) mbar_init(bar0 + 8u * s, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    if (tid == 0) {
+        for (int i = 0; i < kStages - 1 && i < n_local; ++i) issue_tile(i);
+    }
+
+    // This lane's 16 query channels (head hd): channel 32c + 16*half_id + i, in float32.
+    float qd[16];
+    {
+        const bool live = h0 + hd < hpk;
+        const int64_t qbase = ((int64_t)b * a.H_q + hkv * hpk + h0 + hd) * kD + 32 * c + 16 * half_id;
+#pragma unroll
+        for (int i = 0; i < 16; ++i) qd[i] = live ? load_as_f32(a.q, a.q_dtype, qbase + i) : 0.f;
+    }
+    // 2-bit only: byte selector that regroups ldmatrix output so that one register holds
+    // 4 channels of each of two neighbouring channel groups (see the PV section).
+    const uint32_t v_sel = (g & 1) ? 0x7351u : 0x6240u;
+    const int v_src = ((g >> 1) << 2) | c;
+
+    float o[8][4];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+    float oz[2][4];  // sum_t P[t,h] * v_zero[t, group]
+#pragma unroll
+    for (int i = 0; i < 4; ++i) oz[0][i] = oz[1][i] = 0.f;
+    float m_run[2] = {-INFINITY, -INFINITY};
+    float l_run[2] = {0.f, 0.f};
+    const float sc = a.scale * 1.4426950408889634f;  // scores kept in the log2 domain
+    bool timed_out = false;
+
+    for (int it = 0; it < n_local; ++it) {
+        __syncthreads();  // every warp is done with the stage that is refilled next
+        if (tid == 0 && it + kStages - 1 < n_local) issue_tile(it + kStages - 1);
+        const int stage = it % kStages;
+        // After a timeout the CTA keeps its barrier cadence (no early exit: that could
+        // strand the other warps at __syncthreads) but stops waiting; its result is garbage
+        // and the host learns of it through vq_kivi_attend_status().
+        if (!timed_out && !mbar_wait(bar0 + 8u * stage, (uint32_t)((it / kStages) & 1))) timed_out = true;
+        const int tok0 = (tile_begin + it) * kTile;
+        if (tok0 + 32 * warp >= a.n_quant) continue;  // this warp's group is past the end
+        const uint8_t *st = stages + (size_t)stage * C::STAGE_BYTES;
+
+        // ---- B operand of QK^T for this group: q*k_scale split into hi/lo halves ----------
+        // Lanes g and g^4 share a head; each computes both halves for 16 of the 32 channels
+        // of chunk c and they swap what the other needs.
+        uint32_t qf[16];
+        float ck[2];
+        {
+            const float *ks = reinterpret_cast<const float *>(st + C::KS_OFF) + warp * kD + 32 * c + 16 * half_id;
+            const float *kz = reinterpret_cast<const float *>(st + C::KZ_OFF) + warp * kD + 32 * c + 16 * half_id;
+            float x[16];
+            float cpart = 0.f;
+#pragma unroll
+            for (int i4 = 0; i4 < 4; ++i4) {
+                const float4 s4 = *reinterpret_cast<const float4 *>(ks + 4 * i4);
+                const float4 z4 = *reinterpret_cast<const float4 *>(kz + 4 * i4);
+                x[4 * i4 + 0] = qd[4 * i4 + 0] * s4.x; x[4 * i4 + 1] = qd[4 * i4 + 1] * s4.y;
+                x[4 * i4 + 2] = qd[4 * i4 + 2] * s4.z; x[4 * i4 + 3] = qd[4 * i4 + 3] * s4.w;
+                cpart = fmaf(qd[4 * i4 + 0], z4.x, cpart); cpart = fmaf(qd[4 * i4 + 1], z4.y, cpart);
+                cpart = fmaf(qd[4 * i4 + 2], z4.z, cpart); cpart = fmaf(qd[4 * i4 + 3], z4.w, cpart);
+            }
+            uint32_t own_hi[8], own_lo[8], recv[8];
+#pragma unroll
+            for (int ii = 0; ii < 8; ++ii) {
+                // channels paired the way unpack_word pairs codes
+                const int lo_ch = (BITS == 4) ? 8 * (ii / 4) + (ii % 4) : ii;
+                split_h2(x[lo_ch], x[lo_ch + C::NH], own_hi[ii], own_lo[ii]);
+            }
+#pragma unroll
+            for (int ii = 0; ii < 8; ++ii) {
+                const uint32_t send = half_id ? own_hi[ii] : own_lo[ii];
+                recv[ii] = __shfl_xor_sync(0xffffffffu, send, 16);
+            }
+#pragma unroll
+            for (int ii = 0; ii < 8; ++ii) {
+                qf[ii] = half_id ? recv[ii] : own_hi[ii];
+                qf[8 + ii] = half_id ? own_lo[ii] : recv[ii];
+            }
+            // zero-point term sum_d q[d]*k_zero[d] of head hd: reduce over c and the half pair
+            cpart += __shfl_xor_sync(0xffffffffu, cpart, 1);
+            cpart += __shfl_xor_sync(0xffffffffu, cpart, 2);
+            cpart += __shfl_xor_sync(0xffffffffu, cpart, 16);
+            ck[0] = __shfl_sync(0xffffffffu, cpart, (2 * (c & 1)) << 2);
+            ck[1] = __shfl_sync(0xffffffffu, cpart, (2 * (c & 1) + 1) << 2);
+        }
+
+        // ---- S = codes . (q*k_scale)  for this warp's 32 tokens -----------------------------
+        float s_acc[2][4];
+#pragma unroll
+        for (int mt = 0; mt < 2; ++mt) {
+            s_acc[mt][0] = s_acc[mt][1] = s_acc[mt][2] = s_acc[mt][3] = 0.f;
+            uint32_t kw[2][C::KW];  // [row g / g+8][word]
+#pragma unroll
+            for (int r = 0; r < 2; ++r) {
+                const int tok = 32 * warp + 16 * mt + g + 8 * r;
+                const uint8_t *src = st + C::KC_OFF + tok * C::RB + c * (C::KW * 4);
+                if constexpr (C::KW == 4) {
+                    const uint4 v = *reinterpret_cast<const uint4 *>(src);
+                    kw[r][0] = v.x; kw[r][1] = v.y; kw[r][2] = v.z; kw[r][3] = v.w;
+                } else {
+                    const uint2 v = *reinterpret_cast<const uint2 *>(src);
+                    kw[r][0] = v.x; kw[r][1] = v.y;
+                }
+            }
+#pragma unroll
+            for (int w = 0; w < C::KW; ++w) {
+                uint32_t x0[C::NH], x1[C::NH];
+                unpack_word<BITS>(kw[0][w], x0);
+                unpack_word<BITS>(kw[1][w], x1);
+#pragma unroll
+                for (int jj = 0; jj < C::NH / 2; ++jj)
+                    mma_f16(s_acc[mt], x0[2 * jj], x1[2 * jj], x0[2 * jj + 1], x1[2 * jj + 1],
+                            qf[w * C::NH + 2 * jj], qf[w * C::NH + 2 * jj + 1]);
+            }
+        }
+
+        // ---- online softmax; this thread ends up with heads 2(c%2), 2(c%2)+1 --------------
+        float pr[2][4];
+        {
+#pragma unroll
+            for (int mt = 0; mt < 2; ++mt) {
+#pragma unroll
+                for (int r = 0; r < 4; ++r) {
+                    float s = s_acc[mt][r];
+                    s += __shfl_xor_sync(0xffffffffu, s, 2);  // high-half + low-half columns
+                    pr[mt][r] = (s + ck[r & 1]) * sc;
+                }
+            }
+            float corr[2];
+#pragma unroll
+            for (int hh = 0; hh < 2; ++hh) {
+                float v = fmaxf(fmaxf(pr[0][hh], pr[0][hh + 2]), fmaxf(pr[1][hh], pr[1][hh + 2]));
+                v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 4));
+                v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 8));
+                v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 16));
+                const float mn = fmaxf(m_run[hh], v);
+                corr[hh] = exp2f(m_run[hh] - mn);
+                m_run[hh] = mn;
+                float sum = 0.f;
+#pragma unroll
+                for (int mt = 0; mt < 2; ++mt) {
+                    pr[mt][hh] = exp2f(pr[mt][hh] - mn);
+                    pr[mt][hh + 2] = exp2f(pr[mt][hh + 2] - mn);
+                    sum += pr[mt][hh] + pr[mt][hh + 2];
+                }
+                l_run[hh] = l_run[hh] * corr[hh] + sum;
+            }
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                o[i][0] *= corr[0]; o[i][2] *= corr[0];
+                o[i][1] *= corr[1]; o[i][3] *= corr[1];
+            }
+#pragma unroll
+            for (int i = 0; i < 4; ++i) { oz[0][i] *= corr[0]; oz[1][i] *= corr[1]; }
+        }
+
+        // ---- O^T += codes^T . (P*v_scale), and the zero-point term in float32 ---------------
+#pragma unroll
+        for (int mt = 0; mt < 2; ++mt) {
+            const int t0 = 32 * warp + 16 * mt;
+            uint32_t pbw[4][2];  // [channel group][tokens 0-7 / 8-15 of the m-tile]
+            {
+                const float4 vsa = *reinterpret_cast<const float4 *>(st + C::VS_OFF + (t0 + g) * 16);
+                const float4 vsb = *reinterpret_cast<const float4 *>(st + C::VS_OFF + (t0 + g + 8) * 16);
+                const float4 vza = *reinterpret_cast<const float4 *>(st + C::VZ_OFF + (t0 + g) * 16);
+                const float4 vzb = *reinterpret_cast<const float4 *>(st + C::VZ_OFF + (t0 + g + 8) * 16);
+                const float sa[4] = {vsa.x, vsa.y, vsa.z, vsa.w}, sbv[4] = {vsb.x, vsb.y, vsb.z, vsb.w};
+                const float za[4] = {vza.x, vza.y, vza.z, vza.w}, zb[4] = {vzb.x, vzb.y, vzb.z, vzb.w};
+                const float pa0 = pr[mt][0], pa1 = pr[mt][1], pb0 = pr[mt][2], pb1 = pr[mt][3];
+#pragma unroll
+                for (int gd = 0; gd < 4; ++gd) {
+                    oz[0][gd] = fmaf(pa0, za[gd], fmaf(pb0, zb[gd], oz[0][gd]));
+                    oz[1][gd] = fmaf(pa1, za[gd], fmaf(pb1, zb[gd], oz[1][gd]));
+                    uint32_t ha, la, hb, lb;
+                    split_h2(pa0 * sa[gd], pa1 * sa[gd], ha, la);
+                    split_h2(pb0 * sbv[gd], pb1 * sbv[gd], hb, lb);
+                    // P tile (tokens x heads) -> B operand (tokens on K, heads on N): 8x8 transpose
+                    pbw[gd][0] = movmatrix_trans(c < 2 ? ha : la);
+                    pbw[gd][1] = movmatrix_trans(c < 2 ? hb : lb);
+                }
+            }
+#pragma unroll
+            for (int sb = 0; sb < C::NSEG; sb += 2) {
+                uint32_t R[4];  // [segment sb + i/2][token block i%2]
+                {
+                    const int mi = lane >> 3, r = lane & 7;
+                    const uint32_t addr = smem_u32(st + C::VC_OFF + (t0 + 8 * (mi & 1) + r) * C::RB + 16 * (sb + (mi >> 1)));
+                    ldmatrix_x4_trans(R, addr);
+                }
+                if constexpr (BITS == 2) {
+                    // A 16-bit unit holds 8 channels, so the 8 lanes of a column span two
+                    // channel groups. Regroup bytes so each lane holds channels 4g..4g+3 of
+                    // the first group in bits 0-7 and of the second group in bits 8-15.
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const uint32_t lo = __shfl_sync(0xffffffffu, R[i], v_src);
+                        const uint32_t hi = __shfl_sync(0xffffffffu, R[i], v_src + 16);
+                        R[i] = __byte_perm(lo, hi, v_sel);
+                    }
+                }
+#pragma unroll
+                for (int si = 0; si < 2; ++si) {
+                    const int seg = sb + si;
+                    uint32_t e0[C::CU], e1[C::CU];
+                    unpack_word<BITS>(R[2 * si + 0], e0);  // tokens (2c, 2c+1)
+                    unpack_word<BITS>(R[2 * si + 1], e1);  // tokens (2c+8, 2c+9)
+#pragma unroll
+                    for (int u = 0; u < C::CU / 2; ++u) {
+                        // channel group of the 16 rows of this MMA
+                        const int gd = (BITS == 4) ? seg : 2 * seg + (u >> 1);
+                        mma_f16(o[seg * (C::CU / 2) + u], e0[2 * u], e0[2 * u + 1], e1[2 * u], e1[2 * u + 1],
+                                pbw[gd][0], pbw[gd][1]);
+                    }
+                }
+            }
+        }
+    }
+
+    if (timed_out && lane == 0) atomicExch(&g_attend_timeout, 1);
+
+    // ---- merge the four warps, write this split's partial -----------------------------------
+#pragma unroll
+    for (int hh = 0; hh < 2; ++hh) {
+        float v = l_run[hh];
+        v += __shfl_xor_sync(0xffffffffu, v, 4);
+        v += __shfl_xor_sync(0xffffffffu, v, 8);
+        v += __shfl_xor_sync(0xffffffffu, v, 16);
+        l_run[hh] = v;
+#pragma unroll
+        for (int gd = 0; gd < 4; ++gd) {
+            float z = oz[hh][gd];
+            z += __shfl_xor_sync(0xffffffffu, z, 4);
+            z += __shfl_xor_sync(0xffffffffu, z, 8);
+            z += __shfl_xor_sync(0xffffffffu, z, 16);
+            oz[hh][gd] = z;
+        }
+    }
+    __syncthreads();  // all stages are drained: reuse them for the reduction
+    float *red_o = reinterpret_cast<float *>(stages);               // [4 warps][4 heads][128]
+    float *red_z = red_o + kWarps * kChunkHeads * kD;               // [4][4][4 groups]
+    float *red_m = red_z + kWarps * kChunkHeads * 4;                // [4][4]
+    float *red_l = red_m + kWarps * kChunkHeads;                    // [4][4]
+    const int hpair = 2 * (c & 1);
+    // channel of accumulator rows g / g+8 of MMA i
+    auto chan = [&](int i) {
+        const int seg = i / (C::CU / 2), u = i % (C::CU / 2);
+        if constexpr (BITS == 4) return 32 * seg + 4 * g + 2 * u;
+        else return 64 * seg + 32 * (u >> 1) + 4 * g + 2 * (u & 1);
+    };
+    if (c < 2) {  // high-half columns first
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const int d0 = chan(i);
+            float *base = red_o + (warp * kChunkHeads + hpair) * kD;
+            base[d0] = o[i][0]; base[kD + d0] = o[i][1];
+            base[d0 + 1] = o[i][2]; base[kD + d0 + 1] = o[i][3];
+        }
+        if (g == 0) {
+#pragma unroll
+            for (int hh = 0; hh < 2; ++hh) {
+                red_m[warp * kChunkHeads + hpair + hh] = m_run[hh];
+                red_l[warp * kChunkHeads + hpair + hh] = l_run[hh];
+#pragma unroll
+                for (int gd = 0; gd < 4; ++gd) red_z[(warp * kChunkHeads + hpair + hh) * 4 + gd] = oz[hh][gd];
+            }
+        }
+    }
+    __syncwarp();
+    if (c >= 2) {  // then add the low-half columns
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const int d0 = chan(i);
+            float *base = red_o + (warp * kChunkHeads + hpair) * kD;
+            base[d0] += o[i][0]; base[kD + d0] += o[i][1];
+            base[d0 + 1] += o[i][2]; base[kD + d0 + 1] += o[i][3];
+        }
+    }
+    __syncthreads();
+    const int n_heads = min(kChunkHeads, hpk - h0);
+    for (int i = tid; i < n_heads * kD; i += blockDim.x) {
+        const int hp = i / kD, d = i % kD;
+        float gm = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < kWarps; ++w) gm = fmaxf(gm, red_m[w * kChunkHeads + hp]);
+        float gl = 0.f, acc = 0.f;
+#pragma unroll
+        for (int w = 0; w < kWarps; ++w) {
+            const float mw = red_m[w * kChunkHeads + hp];
+            const float f = (mw == -INFINITY) ? 0.f : exp2f(mw - gm);
+            gl += red_l[w * kChunkHeads + hp] * f;
+            acc += (red_o[(w * kChunkHeads + hp) * kD + d] + red_z[(w * kChunkHeads + hp) * 4 + (d >> 5)]) * f;
+        }
+        const int64_t rec = (bh * p.n_parts + split) * hpk + h0 + hp;
+        p.part_o[rec * kD + d] = acc;
+        if (d == 0) { p.part_ml[rec * 2] = gm; p.part_ml[rec * 2 + 1] = gl; }
+    }
+}
+
+// One CTA per (batch, kv head): combine the partials (log2-domain maxima).
+__global__ void kivi_attend_mma_merge_kernel(const __grid_constant__ Params p) {
+    const vq_kivi_attend_args &a = p.a;
+    const int64_t bh = blockIdx.x;
+    const int b = (int)(bh / a.H_kv), hkv = (int)(bh % a.H_kv);
+    for (int i = threadIdx.x; i < p.hpk * kD; i += blockDim.x) {
+        const int hp = i / kD, d = i % kD;
+        float gm = -INFINITY;
+        for (int s = 0; s < p.n_parts; ++s) gm = fmaxf(gm, p.part_ml[((bh * p.n_parts + s) * p.hpk + hp) * 2]);
+        float gl = 0.f, acc = 0.f;
+        for (int s = 0; s < p.n_parts; ++s) {
+            const int64_t rec = (bh * p.n_parts + s) * p.hpk + hp;
+            const float ms = p.part_ml[rec * 2];
+            if (ms == -INFINITY) continue;
+            const float f = exp2f(ms - gm);
+            gl += p.part_ml[rec * 2 + 1] * f;
+            acc += p.part_o[rec * kD + d] * f;
+        }
+        const int64_t row = (int64_t)b * a.H_q + hkv * p.hpk + hp;
+        store_from_f32(a.out, a.out_dtype, row * kD + d, acc / gl);
+    }
+}
+
+int choose_splits(const vq_kivi_attend_args &a, const DeviceInfo &di) {
+    const int tiles = (int)ceil_div(a.n_quant, kTile);
+    if (tiles <= 1) return std::max(tiles, 0);
+    if (a.n_splits > 0) return std::min(a.n_splits, tiles);
+    const int stage_bytes = a.store_bits == 4 ? Cfg<4>::SMEM_BYTES : Cfg<2>::SMEM_BYTES;
+    const int occ = std::max(1, std::min(8, (int)(di.smem_optin / (stage_bytes + 1024))));
+    const int n_chunks = (int)ceil_div(a.H_q / a.H_kv, kChunkHeads);
+    const int64_t units = (int64_t)a.B * a.H_kv * n_chunks;
+    const int64_t slots = (int64_t)di.sm_count * occ;
+    // Aim for ~8 waves of CTAs so the last, partly filled wave costs little, but keep at
+    // least 4 tiles per CTA so pipeline fill and the partial write stay amortised.
+    int64_t want = std::max<int64_t>(1, (slots * 8) / units);
+    want = std::min<int64_t>(want, std::max(1, tiles / 4));
+    return (int)std::min<int64_t>(want, 512);
+}
+
+}  // namespace
+
+const char *kivi_attend_mma_supported(const vq_kivi_attend_args &a) {
+    if (a.D != kD) return "head_dim must be 128";
+    if (a.S_q != 1) return "one query row per call";
+    if (a.n_quant <= 0) return "no packed tokens";
+    if (a.group != 32) return "group size must be 32";
+    if (a.store_bits != 2 && a.store_bits != 4) return "codes must be stored in 2 or 4 bits";
+    if (a.H_q / a.H_kv > kMaxHeads) return "more than 8 query heads per kv head";
+    if (a.n_quant % 32) return "packed token count must be a multiple of the group size";
+    if (a.B > 65535 || a.H_kv > 65535) return "grid too large";
+    const int rb = kD * a.store_bits / 8;
+    if (!is_aligned(a.k_codes, 16) || !is_aligned(a.v_codes, 16) || a.k_codes_stride_bh % 16 ||
+        a.v_codes_stride_bh % 16 || rb % 16)
+        return "code buffers must be 16-byte aligned";
+    if (!is_aligned(a.k_scale, 16) || !is_aligned(a.k_zero, 16) || !is_aligned(a.v_scale, 16) ||
+        !is_aligned(a.v_zero, 16) || a.k_param_stride_bh % 4 || a.v_param_stride_bh % 4)
+        return "scale/zero buffers must be 16-byte aligned";
+    if (a.n_res > 0 && a.res_dtype != VQ_F16 && a.res_dtype != VQ_BF16 && a.res_dtype != VQ_F32)
+        return "bad residual dtype";
+    return nullptr;
+}
+
+int kivi_attend_mma_splits(const vq_kivi_attend_args &a, const DeviceInfo &di) { return choose_splits(a, di); }
+
+int32_t kivi_attend_mma_take_timeout(int *flag) {
+    int zero = 0;
+    VQ_CHECK_CUDA(cudaMemcpyFromSymbol(flag, g_attend_timeout, sizeof(int)));
+    if (*flag) VQ_CHECK_CUDA(cudaMemcpyToSymbol(g_attend_timeout, &zero, sizeof(int)));
+    return VQ_OK;
+}
+
+int32_t kivi_attend_mma_launch(const vq_kivi_attend_args &a, const DeviceInfo &di, cudaStream_t st) {
+    Params p;
+    p.a = a;
+    p.hpk = a.H_q / a.H_kv;
+    p.n_chunks = (int)ceil_div(p.hpk, kChunkHeads);
+    p.n_splits = choose_splits(a, di);
+    p.tiles_total = (int)ceil_div(a.n_quant, kTile);
+    p.tiles_per_split = (int)ceil_div(p.tiles_total, p.n_splits);
+    // a split count that leaves trailing splits empty is trimmed
+    p.n_splits = (int)ceil_div(p.tiles_total, p.tiles_per_split);
+    p.n_parts = p.n_splits + (a.n_res > 0 ? 1 : 0);
+    const int64_t recs = (int64_t)a.B * a.H_kv * p.n_parts * p.hpk;
+    const int64_t need = recs * (kD + 2) * (int64_t)sizeof(float);
+    VQ_REQUIRE(a.workspace != nullptr && a.workspace_bytes >= need, VQ_ERR_CAPACITY,
+               "vq_kivi_decode_attend: workspace of %lld bytes needed, %lld given", (long long)need,
+               (long long)a.workspace_bytes);
+    VQ_REQUIRE(is_aligned(a.workspace, 16), VQ_ERR_ALIGN, "vq_kivi_decode_attend: workspace must be 16-byte aligned");
+    p.part_o = (float *)a.workspace;
+    p.part_ml = p.part_o + recs * kD;
+
+    dim3 grid(p.n_splits * p.n_chunks + (a.n_res > 0 ? 1 : 0), a.H_kv, a.B);
+    const int tail_smem = (kMaxHeads * kD + kWarps * kMaxHeads * kD + 2 * kWarps * kMaxHeads) * 4;
+    if (a.store_bits == 4) {
+        const int smem = std::max(Cfg<4>::SMEM_BYTES, tail_smem);
+        VQ_CHECK_CUDA(cudaFuncSetAttribute(kivi_attend_mma_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        kivi_attend_mma_kernel<4><<<grid, kWarps * 32, smem, st>>>(p);
+    } else {
+        const int smem = std::max(Cfg<2>::SMEM_BYTES, tail_smem);
+        VQ_CHECK_CUDA(cudaFuncSetAttribute(kivi_attend_mma_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        kivi_attend_mma_kernel<2><<<grid, kWarps * 32, smem, st>>>(p);
+    }
+    VQ_CHECK_LAUNCH("kivi_attend_mma_kernel");
+    kivi_attend_mma_merge_kernel<<<(unsigned)((int64_t)a.B * a.H_kv), 128, 0, st>>>(p);
+    VQ_CHECK_LAUNCH("kivi_attend_mma_merge_kernel");
+    return VQ_OK;
+}
+
 }  // namespace vq
