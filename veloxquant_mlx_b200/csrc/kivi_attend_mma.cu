@@ -7,7 +7,7 @@
 // head_dim rows (PV) on the M axis and the packed query heads on the 8-wide N axis.
 //
 // Exactness: the A operands are the RAW integer codes, produced in registers from the
-// packed words by a mask and a magic-number subtract (exact halves, no int->float cvt).
+// packed words by one AND each (see unpack_word: exact halves, no int->float conversion).
 // The group scales never touch the codes in half precision; they are folded, in float32,
 // into the small B operands instead:
 //     q.K_hat[t]  = sum_d code[t,d] * (q[d]*k_scale[G,d])  +  sum_d q[d]*k_zero[G,d]
@@ -21,12 +21,13 @@
 // Data movement: one CTA owns a contiguous run of 128-token tiles of one (batch, kv head).
 // Per tile six contiguous pieces (K codes, V codes, K scale/zero for 4 groups, V scale/zero
 // for 128 tokens) are fetched by the bulk async-copy engine (cp.async.bulk, completion on
-// an mbarrier) into a 3-stage shared-memory ring, so HBM reads stay in flight while the
+// an mbarrier) into a 2- to 4-stage shared-memory ring, so HBM reads stay in flight while the
 // warps unpack. Warp w owns token group w of each tile (32 tokens = one K scale group).
 // The context is split across CTAs; each writes an unnormalised partial (m, l, o) and a
 // small second kernel merges them. The unquantized tail is one more partial from a
 // CUDA-core CTA in the same launch.
 #include <algorithm>
+#include <cstdlib>
 
 #include "kivi_attend.h"
 
@@ -37,7 +38,7 @@ namespace {
 constexpr int kD = 128;
 constexpr int kTile = 128;     // tokens per pipeline stage
 constexpr int kWarps = 4;
-constexpr int kStages = 3;
+constexpr int kMaxStages = 4;
 constexpr int kMaxHeads = 8;   // query heads per kv head
 constexpr int kChunkHeads = 4; // query heads per CTA (hi/lo halves fill the 8 MMA columns)
 constexpr uint32_t kSpinLimit = 1u << 18;
@@ -59,7 +60,7 @@ struct Cfg {
     static constexpr int VS_OFF = KZ_OFF + 2048;
     static constexpr int VZ_OFF = VS_OFF + 2048;
     static constexpr int STAGE_BYTES = VZ_OFF + 2048;  // 24576 / 16384
-    static constexpr int SMEM_BYTES = 128 + kStages * STAGE_BYTES;
+    static constexpr int smem_bytes(int stages) { return 128 + stages * STAGE_BYTES; }
 };
 
 // ---- PTX helpers ------------------------------------------------------------------------
@@ -93,16 +94,6 @@ __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void *src, uint32_t
         "l"(src), "r"(bytes), "r"(bar)
         : "memory");
 }
-__device__ __forceinline__ uint32_t lop3_and_or(uint32_t a, uint32_t b, uint32_t c) {
-    uint32_t r;
-    asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(r) : "r"(a), "r"(b), "r"(c));
-    return r;
-}
-__device__ __forceinline__ uint32_t h2sub(uint32_t a, uint32_t b) {
-    uint32_t r;
-    asm("sub.f16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
-    return r;
-}
 __device__ __forceinline__ uint32_t pack_h2(float lo, float hi) {
     __half2 h = __floats2half2_rn(lo, hi);
     return *reinterpret_cast<uint32_t *>(&h);
@@ -134,32 +125,47 @@ __device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t add
                  : "r"(addr));
 }
 
-// Unpack one 32-bit word into half2 registers holding exact integer code values.
-// Register i pairs the i-th code of the low 16 bits with the i-th code of the high 16
-// bits. Codes are moved into a half's mantissa by a mask and an OR with a power-of-two
-// exponent ("magic number"), then the power of two is subtracted: exact, no int->float cvt.
+// Unpack one 32-bit word into half2 registers by masking alone. A half whose bit pattern is
+// below 2048 (exponent field 0 or 1) has the value pattern * 2^-24: the subnormal range and
+// the first normal binade lie on one straight line. So a code left in place at bit offset s
+// of a 16-bit half IS the half-precision number code * 2^s * 2^-24, exactly, with no
+// conversion and no magic-number subtract; the tensor cores take subnormal inputs as they
+// are. Register i pairs the i-th code of the low 16 bits with the i-th code of the high 16
+// bits; code_weight<BITS>(i) = 2^s is folded into the other MMA operand or the final scale.
 template <int BITS>
 __device__ __forceinline__ void unpack_word(uint32_t w, uint32_t (&h)[32 / BITS / 2]);
 
 template <>
 __device__ __forceinline__ void unpack_word<4>(uint32_t w, uint32_t (&h)[4]) {
     const uint32_t w8 = w >> 8;
-    h[0] = h2sub(lop3_and_or(w, 0x000f000fu, 0x64006400u), 0x64006400u);   // 1024 + c
-    h[1] = h2sub(lop3_and_or(w, 0x00f000f0u, 0x54005400u), 0x54005400u);   //   64 + c
-    h[2] = h2sub(lop3_and_or(w8, 0x000f000fu, 0x64006400u), 0x64006400u);
-    h[3] = h2sub(lop3_and_or(w8, 0x00f000f0u, 0x54005400u), 0x54005400u);
+    h[0] = w & 0x000f000fu;
+    h[1] = w & 0x00f000f0u;
+    h[2] = w8 & 0x000f000fu;
+    h[3] = w8 & 0x00f000f0u;
 }
 template <>
 __device__ __forceinline__ void unpack_word<2>(uint32_t w, uint32_t (&h)[8]) {
-    const uint32_t w10 = w >> 10;
-    h[0] = h2sub(lop3_and_or(w, 0x00030003u, 0x64006400u), 0x64006400u);   // 1024 + c
-    h[1] = h2sub(lop3_and_or(w, 0x000c000cu, 0x5c005c00u), 0x5c005c00u);   //  256 + c
-    h[2] = h2sub(lop3_and_or(w, 0x00300030u, 0x54005400u), 0x54005400u);   //   64 + c
-    h[3] = h2sub(lop3_and_or(w, 0x00c000c0u, 0x4c004c00u), 0x4c004c00u);   //   16 + c
-    h[4] = h2sub(lop3_and_or(w, 0x03000300u, 0x44004400u), 0x44004400u);   //    4 + c
-    h[5] = h2sub(lop3_and_or(w10, 0x00030003u, 0x64006400u), 0x64006400u);
-    h[6] = h2sub(lop3_and_or(w10, 0x000c000cu, 0x5c005c00u), 0x5c005c00u);
-    h[7] = h2sub(lop3_and_or(w10, 0x00300030u, 0x54005400u), 0x54005400u);
+    const uint32_t w8 = w >> 8;
+    h[0] = w & 0x00030003u;
+    h[1] = w & 0x000c000cu;
+    h[2] = w & 0x00300030u;
+    h[3] = w & 0x00c000c0u;
+    h[4] = w8 & 0x00030003u;
+    h[5] = w8 & 0x000c000cu;
+    h[6] = w8 & 0x00300030u;
+    h[7] = w8 & 0x00c000c0u;
+}
+// 2^s of unpacked register i (depends only on i modulo 4 in both widths).
+template <int BITS>
+__host__ __device__ constexpr float code_weight(int i) {
+    return BITS == 4 ? ((i & 1) ? 16.f : 1.f) : (float)(1 << (2 * (i & 3)));
+}
+constexpr float kTwo24 = 16777216.f;
+
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
 }
 
 struct Params {
@@ -251,7 +257,7 @@ __device__ void tail_partial(const Params &p, uint8_t *smem_raw, int b, int hkv)
 //   as a B-operand column (n = g): query head g % 4, high half if g < 4, low half otherwise;
 //   as an accumulator column pair (cols 2c, 2c+1): heads 2(c%2), 2(c%2)+1, high halves if
 //   c < 2, low halves otherwise (lanes c and c^2 hold the two halves of the same heads).
-template <int BITS>
+template <int BITS, int STAGES>
 __global__ void __launch_bounds__(kWarps * 32)
 kivi_attend_mma_kernel(const __grid_constant__ Params p) {
     using C = Cfg<BITS>;
@@ -289,7 +295,7 @@ kivi_attend_mma_kernel(const __grid_constant__ Params p) {
         const int tile = tile_begin + local_idx;
         const int tok0 = tile * kTile;
         const int ntok = min(kTile, a.n_quant - tok0);  // multiple of 32
-        const int stage = local_idx % kStages;
+        const int stage = local_idx % STAGES;
         const uint32_t bar = bar0 + 8u * stage;
         const uint32_t dst = smem_u32(stages + (size_t)stage * C::STAGE_BYTES);
         const uint32_t code_bytes = (uint32_t)ntok * C::RB;
@@ -305,21 +311,37 @@ kivi_attend_mma_kernel(const __grid_constant__ Params p) {
     };
 
     if (tid == 0) {
-        for (int s = 0; s < kStages; ++s) mbar_init(bar0 + 8u * s, 1);
+        for (int s = 0; s < STAGES; ++s) mbar_init(bar0 + 8u * s, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
     if (tid == 0) {
-        for (int i = 0; i < kStages - 1 && i < n_local; ++i) issue_tile(i);
+        for (int i = 0; i < STAGES - 1 && i < n_local; ++i) issue_tile(i);
     }
 
-    // This lane's 16 query channels (head hd): channel 32c + 16*half_id + i, in float32.
+    // This lane's 16 query channels (head hd) are channels 32c + 16*half_id + [0, 16), handled
+    // as four blocks of 4. Unpacked K register (pair p, element e) couples the blocks
+    // blk(p, 0) and blk(p, 1). To keep the four lanes c of a quarter-warp on distinct
+    // shared-memory banks when they read their scales (their chunks are 128 B apart), slot
+    // (ps, ms) of lane c holds block blk(ps ^ (c >> 1), ms ^ (c & 1)); the permutation is
+    // undone with selects when the fragments are assembled. qd is pre-divided by the code
+    // weight of its element so that (code * weight) * (q * scale / weight) needs no fix-up.
+    const int c0 = c & 1, c1 = c >> 1;
+    int blk_off[4];  // float offset of the block held by slot s = 2*ps + ms
+#pragma unroll
+    for (int s = 0; s < 4; ++s) {
+        const int pt = (s >> 1) ^ c1, mt_ = (s & 1) ^ c0;
+        blk_off[s] = 4 * ((BITS == 4) ? 2 * pt + mt_ : pt + 2 * mt_);
+    }
     float qd[16];
     {
         const bool live = h0 + hd < hpk;
         const int64_t qbase = ((int64_t)b * a.H_q + hkv * hpk + h0 + hd) * kD + 32 * c + 16 * half_id;
 #pragma unroll
-        for (int i = 0; i < 16; ++i) qd[i] = live ? load_as_f32(a.q, a.q_dtype, qbase + i) : 0.f;
+        for (int s = 0; s < 4; ++s)
+#pragma unroll
+            for (int e = 0; e < 4; ++e)
+                qd[4 * s + e] = live ? load_as_f32(a.q, a.q_dtype, qbase + blk_off[s] + e) / code_weight<BITS>(e) : 0.f;
     }
     // 2-bit only: byte selector that regroups ldmatrix output so that one register holds
     // 4 channels of each of two neighbouring channel groups (see the PV section).
@@ -339,12 +361,12 @@ kivi_attend_mma_kernel(const __grid_constant__ Params p) {
 
     for (int it = 0; it < n_local; ++it) {
         __syncthreads();  // every warp is done with the stage that is refilled next
-        if (tid == 0 && it + kStages - 1 < n_local) issue_tile(it + kStages - 1);
-        const int stage = it % kStages;
+        if (tid == 0 && it + STAGES - 1 < n_local) issue_tile(it + STAGES - 1);
+        const int stage = it % STAGES;
         // After a timeout the CTA keeps its barrier cadence (no early exit: that could
         // strand the other warps at __syncthreads) but stops waiting; its result is garbage
         // and the host learns of it through vq_kivi_attend_status().
-        if (!timed_out && !mbar_wait(bar0 + 8u * stage, (uint32_t)((it / kStages) & 1))) timed_out = true;
+        if (!timed_out && !mbar_wait(bar0 + 8u * stage, (uint32_t)((it / STAGES) & 1))) timed_out = true;
         const int tok0 = (tile_begin + it) * kTile;
         if (tok0 + 32 * warp >= a.n_quant) continue;  // this warp's group is past the end
         const uint8_t *st = stages + (size_t)stage * C::STAGE_BYTES;
@@ -358,22 +380,34 @@ kivi_attend_mma_kernel(const __grid_constant__ Params p) {
             const float *ks = reinterpret_cast<const float *>(st + C::KS_OFF) + warp * kD + 32 * c + 16 * half_id;
             const float *kz = reinterpret_cast<const float *>(st + C::KZ_OFF) + warp * kD + 32 * c + 16 * half_id;
             float x[16];
-            float cpart = 0.f;
+            float cp[4] = {0.f, 0.f, 0.f, 0.f};  // per element index: sum q/weight * k_zero
 #pragma unroll
-            for (int i4 = 0; i4 < 4; ++i4) {
-                const float4 s4 = *reinterpret_cast<const float4 *>(ks + 4 * i4);
-                const float4 z4 = *reinterpret_cast<const float4 *>(kz + 4 * i4);
-                x[4 * i4 + 0] = qd[4 * i4 + 0] * s4.x; x[4 * i4 + 1] = qd[4 * i4 + 1] * s4.y;
-                x[4 * i4 + 2] = qd[4 * i4 + 2] * s4.z; x[4 * i4 + 3] = qd[4 * i4 + 3] * s4.w;
-                cpart = fmaf(qd[4 * i4 + 0], z4.x, cpart); cpart = fmaf(qd[4 * i4 + 1], z4.y, cpart);
-                cpart = fmaf(qd[4 * i4 + 2], z4.z, cpart); cpart = fmaf(qd[4 * i4 + 3], z4.w, cpart);
+            for (int s = 0; s < 4; ++s) {
+                const float4 s4 = *reinterpret_cast<const float4 *>(ks + blk_off[s]);
+                const float4 z4 = *reinterpret_cast<const float4 *>(kz + blk_off[s]);
+                x[4 * s + 0] = qd[4 * s + 0] * s4.x; x[4 * s + 1] = qd[4 * s + 1] * s4.y;
+                x[4 * s + 2] = qd[4 * s + 2] * s4.z; x[4 * s + 3] = qd[4 * s + 3] * s4.w;
+                cp[0] = fmaf(qd[4 * s + 0], z4.x, cp[0]); cp[1] = fmaf(qd[4 * s + 1], z4.y, cp[1]);
+                cp[2] = fmaf(qd[4 * s + 2], z4.z, cp[2]); cp[3] = fmaf(qd[4 * s + 3], z4.w, cp[3]);
+            }
+            float cpart = cp[0] * code_weight<BITS>(0) + cp[1] * code_weight<BITS>(1) +
+                          cp[2] * code_weight<BITS>(2) + cp[3] * code_weight<BITS>(3);
+            uint32_t t_hi[2][4], t_lo[2][4];  // [slot pair ps][element]
+#pragma unroll
+            for (int ps = 0; ps < 2; ++ps) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const float m0 = x[4 * (2 * ps) + e], m1 = x[4 * (2 * ps + 1) + e];
+                    split_h2(c0 ? m1 : m0, c0 ? m0 : m1, t_hi[ps][e], t_lo[ps][e]);
+                }
             }
             uint32_t own_hi[8], own_lo[8], recv[8];
 #pragma unroll
-            for (int ii = 0; ii < 8; ++ii) {
-                // channels paired the way unpack_word pairs codes
-                const int lo_ch = (BITS == 4) ? 8 * (ii / 4) + (ii % 4) : ii;
-                split_h2(x[lo_ch], x[lo_ch + C::NH], own_hi[ii], own_lo[ii]);
+            for (int e = 0; e < 4; ++e) {
+                own_hi[e] = c1 ? t_hi[1][e] : t_hi[0][e];
+                own_hi[4 + e] = c1 ? t_hi[0][e] : t_hi[1][e];
+                own_lo[e] = c1 ? t_lo[1][e] : t_lo[0][e];
+                own_lo[4 + e] = c1 ? t_lo[0][e] : t_lo[1][e];
             }
 #pragma unroll
             for (int ii = 0; ii < 8; ++ii) {
@@ -432,7 +466,8 @@ kivi_attend_mma_kernel(const __grid_constant__ Params p) {
                 for (int r = 0; r < 4; ++r) {
                     float s = s_acc[mt][r];
                     s += __shfl_xor_sync(0xffffffffu, s, 2);  // high-half + low-half columns
-                    pr[mt][r] = (s + ck[r & 1]) * sc;
+                    // the MMA saw codes * 2^-24; undo that and add the zero-point term
+                    pr[mt][r] = fmaf(s, sc * kTwo24, ck[r & 1] * sc);
                 }
             }
             float corr[2];
@@ -443,24 +478,28 @@ kivi_attend_mma_kernel(const __grid_constant__ Params p) {
                 v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 8));
                 v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 16));
                 const float mn = fmaxf(m_run[hh], v);
-                corr[hh] = exp2f(m_run[hh] - mn);
+                corr[hh] = fast_exp2(m_run[hh] - mn);
                 m_run[hh] = mn;
                 float sum = 0.f;
 #pragma unroll
                 for (int mt = 0; mt < 2; ++mt) {
-                    pr[mt][hh] = exp2f(pr[mt][hh] - mn);
-                    pr[mt][hh + 2] = exp2f(pr[mt][hh + 2] - mn);
+                    pr[mt][hh] = fast_exp2(pr[mt][hh] - mn);
+                    pr[mt][hh + 2] = fast_exp2(pr[mt][hh + 2] - mn);
                     sum += pr[mt][hh] + pr[mt][hh + 2];
                 }
                 l_run[hh] = l_run[hh] * corr[hh] + sum;
             }
+            // The running maxima settle after the first few groups; skip the rescale of the
+            // 40 accumulators whenever no lane's maximum moved (warp-uniform branch).
+            if (__any_sync(0xffffffffu, corr[0] != 1.f || corr[1] != 1.f)) {
 #pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                o[i][0] *= corr[0]; o[i][2] *= corr[0];
-                o[i][1] *= corr[1]; o[i][3] *= corr[1];
+                for (int i = 0; i < 8; ++i) {
+                    o[i][0] *= corr[0]; o[i][2] *= corr[0];
+                    o[i][1] *= corr[1]; o[i][3] *= corr[1];
+                }
+#pragma unroll
+                for (int i = 0; i < 4; ++i) { oz[0][i] *= corr[0]; oz[1][i] *= corr[1]; }
             }
-#pragma unroll
-            for (int i = 0; i < 4; ++i) { oz[0][i] *= corr[0]; oz[1][i] *= corr[1]; }
         }
 
         // ---- O^T += codes^T . (P*v_scale), and the zero-point term in float32 ---------------
@@ -556,6 +595,14 @@ kivi_attend_mma_kernel(const __grid_constant__ Params p) {
         if constexpr (BITS == 4) return 32 * seg + 4 * g + 2 * u;
         else return 64 * seg + 32 * (u >> 1) + 4 * g + 2 * (u & 1);
     };
+    // Accumulator rows saw codes * weight * 2^-24 (see unpack_word): undo per row.
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const int u = i % (C::CU / 2);
+        const float f0 = kTwo24 / code_weight<BITS>(2 * u), f1 = kTwo24 / code_weight<BITS>(2 * u + 1);
+        o[i][0] *= f0; o[i][1] *= f0;
+        o[i][2] *= f1; o[i][3] *= f1;
+    }
     if (c < 2) {  // high-half columns first
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
@@ -628,20 +675,64 @@ __global__ void kivi_attend_mma_merge_kernel(const __grid_constant__ Params p) {
     }
 }
 
+// Pipeline depth and waves-per-launch are tunables; the environment overrides exist for
+// measurement sweeps (VQ_ATTEND_STAGES = 2..4, VQ_ATTEND_WAVES = 1..32).
+int tuned_stages() {
+    static int v = [] {
+        const char *e = getenv("VQ_ATTEND_STAGES");
+        const int s = e ? atoi(e) : 3;
+        return (s >= 2 && s <= kMaxStages) ? s : 3;
+    }();
+    return v;
+}
+int tuned_waves() {
+    static int v = [] {
+        const char *e = getenv("VQ_ATTEND_WAVES");
+        const int s = e ? atoi(e) : 8;
+        return (s >= 1 && s <= 32) ? s : 8;
+    }();
+    return v;
+}
+
+int smem_for(int bits, int stages) {
+    const int tail_smem = (kMaxHeads * kD + kWarps * kMaxHeads * kD + 2 * kWarps * kMaxHeads) * 4;
+    return std::max(bits == 4 ? Cfg<4>::smem_bytes(stages) : Cfg<2>::smem_bytes(stages), tail_smem);
+}
+
 int choose_splits(const vq_kivi_attend_args &a, const DeviceInfo &di) {
     const int tiles = (int)ceil_div(a.n_quant, kTile);
     if (tiles <= 1) return std::max(tiles, 0);
     if (a.n_splits > 0) return std::min(a.n_splits, tiles);
-    const int stage_bytes = a.store_bits == 4 ? Cfg<4>::SMEM_BYTES : Cfg<2>::SMEM_BYTES;
-    const int occ = std::max(1, std::min(8, (int)(di.smem_optin / (stage_bytes + 1024))));
+    const int smem = smem_for(a.store_bits, tuned_stages());
+    // resident CTAs per SM: shared memory, and 4 by registers (128 threads x <= 128 regs)
+    const int occ = std::max(1, std::min(4, (int)(di.smem_optin / (smem + 1024))));
     const int n_chunks = (int)ceil_div(a.H_q / a.H_kv, kChunkHeads);
     const int64_t units = (int64_t)a.B * a.H_kv * n_chunks;
     const int64_t slots = (int64_t)di.sm_count * occ;
-    // Aim for ~8 waves of CTAs so the last, partly filled wave costs little, but keep at
-    // least 4 tiles per CTA so pipeline fill and the partial write stay amortised.
-    int64_t want = std::max<int64_t>(1, (slots * 8) / units);
+    // Aim for several waves of CTAs so the last, partly filled wave costs little, but keep
+    // at least 4 tiles per CTA so pipeline fill and the partial write stay amortised.
+    int64_t want = std::max<int64_t>(1, (slots * tuned_waves()) / units);
     want = std::min<int64_t>(want, std::max(1, tiles / 4));
     return (int)std::min<int64_t>(want, 512);
+}
+
+template <int BITS, int STAGES>
+int32_t launch_one(const Params &p, dim3 grid, cudaStream_t st) {
+    const int smem = smem_for(BITS, STAGES);
+    VQ_CHECK_CUDA(cudaFuncSetAttribute(kivi_attend_mma_kernel<BITS, STAGES>,
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    kivi_attend_mma_kernel<BITS, STAGES><<<grid, kWarps * 32, smem, st>>>(p);
+    VQ_CHECK_LAUNCH("kivi_attend_mma_kernel");
+    return VQ_OK;
+}
+
+template <int BITS>
+int32_t launch_bits(const Params &p, dim3 grid, cudaStream_t st) {
+    switch (tuned_stages()) {
+        case 2: return launch_one<BITS, 2>(p, grid, st);
+        case 4: return launch_one<BITS, 4>(p, grid, st);
+        default: return launch_one<BITS, 3>(p, grid, st);
+    }
 }
 
 }  // namespace
@@ -697,17 +788,8 @@ int32_t kivi_attend_mma_launch(const vq_kivi_attend_args &a, const DeviceInfo &d
     p.part_ml = p.part_o + recs * kD;
 
     dim3 grid(p.n_splits * p.n_chunks + (a.n_res > 0 ? 1 : 0), a.H_kv, a.B);
-    const int tail_smem = (kMaxHeads * kD + kWarps * kMaxHeads * kD + 2 * kWarps * kMaxHeads) * 4;
-    if (a.store_bits == 4) {
-        const int smem = std::max(Cfg<4>::SMEM_BYTES, tail_smem);
-        VQ_CHECK_CUDA(cudaFuncSetAttribute(kivi_attend_mma_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-        kivi_attend_mma_kernel<4><<<grid, kWarps * 32, smem, st>>>(p);
-    } else {
-        const int smem = std::max(Cfg<2>::SMEM_BYTES, tail_smem);
-        VQ_CHECK_CUDA(cudaFuncSetAttribute(kivi_attend_mma_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-        kivi_attend_mma_kernel<2><<<grid, kWarps * 32, smem, st>>>(p);
-    }
-    VQ_CHECK_LAUNCH("kivi_attend_mma_kernel");
+    const int32_t rc = a.store_bits == 4 ? launch_bits<4>(p, grid, st) : launch_bits<2>(p, grid, st);
+    if (rc != VQ_OK) return rc;
     kivi_attend_mma_merge_kernel<<<(unsigned)((int64_t)a.B * a.H_kv), 128, 0, st>>>(p);
     VQ_CHECK_LAUNCH("kivi_attend_mma_merge_kernel");
     return VQ_OK;
