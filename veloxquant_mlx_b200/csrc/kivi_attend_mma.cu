@@ -36,7 +36,7 @@ namespace vq {
 namespace {
 
 constexpr int kD = 128;
-constexpr int kTile = 128;     // tokens per pipeline stage
+constexpr int kGroup = 32;     // tokens per pipeline stage of one warp = one K scale group
 constexpr int kWarps = 4;
 constexpr int kMaxStages = 4;
 constexpr int kMaxHeads = 8;   // query heads per kv head
@@ -54,13 +54,13 @@ struct Cfg {
     static constexpr int CU = 16 / BITS;         // codes per 16-bit unit: 4 / 8
     static constexpr int NSEG = RB / 16;         // 16-byte segments per row: 4 / 2
     static constexpr int KC_OFF = 0;
-    static constexpr int VC_OFF = kTile * RB;
-    static constexpr int KS_OFF = 2 * kTile * RB;
-    static constexpr int KZ_OFF = KS_OFF + 2048;
-    static constexpr int VS_OFF = KZ_OFF + 2048;
-    static constexpr int VZ_OFF = VS_OFF + 2048;
-    static constexpr int STAGE_BYTES = VZ_OFF + 2048;  // 24576 / 16384
-    static constexpr int smem_bytes(int stages) { return 128 + stages * STAGE_BYTES; }
+    static constexpr int VC_OFF = kGroup * RB;
+    static constexpr int KS_OFF = 2 * kGroup * RB;
+    static constexpr int KZ_OFF = KS_OFF + 512;
+    static constexpr int VS_OFF = KZ_OFF + 512;
+    static constexpr int VZ_OFF = VS_OFF + 512;
+    static constexpr int STAGE_BYTES = VZ_OFF + 512;  // one warp, one stage: 6144 / 4096
+    static constexpr int smem_bytes(int stages) { return 128 + kWarps * stages * STAGE_BYTES; }
 };
 
 // ---- PTX helpers ------------------------------------------------------------------------
@@ -174,8 +174,8 @@ struct Params {
     int n_chunks;       // ceil(hpk / 4)
     int n_splits;       // quantized-context splits
     int n_parts;        // n_splits + (tail present)
-    int tiles_total;    // ceil(n_quant / 128)
-    int tiles_per_split;
+    int groups_total;     // n_quant / 32
+    int groups_per_warp;  // consecutive groups owned by one warp
     float *part_o;      // [B*H_kv][n_parts][hpk][128]
     float *part_ml;     // [B*H_kv][n_parts][hpk][2]
 };
@@ -258,7 +258,7 @@ __device__ void tail_partial(const Params &p, uint8_t *smem_raw, int b, int hkv)
 //   as an accumulator column pair (cols 2c, 2c+1): heads 2(c%2), 2(c%2)+1, high halves if
 //   c < 2, low halves otherwise (lanes c and c^2 hold the two halves of the same heads).
 template <int BITS, int STAGES>
-__global__ void __launch_bounds__(kWarps * 32)
+__global__ void __launch_bounds__(kWarps * 32, 4)
 kivi_attend_mma_kernel(const __grid_constant__ Params p) {
     using C = Cfg<BITS>;
     extern __shared__ __align__(128) uint8_t smem_raw[];
@@ -280,9 +280,13 @@ kivi_attend_mma_kernel(const __grid_constant__ Params p) {
     uint8_t *stages = smem_raw + 128;
     const uint32_t bar0 = smem_u32(bars);
 
-    const int tile_begin = split * p.tiles_per_split;
-    const int tile_end = min(p.tiles_total, tile_begin + p.tiles_per_split);
-    const int n_local = max(0, tile_end - tile_begin);
+    // Each warp owns a contiguous run of 32-token groups and runs its own copy pipeline:
+    // no CTA-wide synchronisation until the final merge.
+    const int grp_begin = min(p.groups_total, (split * kWarps + warp) * p.groups_per_warp);
+    const int grp_end = min(p.groups_total, grp_begin + p.groups_per_warp);
+    const int n_local = grp_end - grp_begin;
+    const uint32_t wbar0 = bar0 + 8u * (warp * STAGES);
+    uint8_t *wstages = stages + (size_t)warp * STAGES * C::STAGE_BYTES;
 
     const uint8_t *kc_g = a.k_codes + bh * a.k_codes_stride_bh;
     const uint8_t *vc_g = a.v_codes + bh * a.v_codes_stride_bh;
@@ -291,32 +295,29 @@ kivi_attend_mma_kernel(const __grid_constant__ Params p) {
     const float *vs_g = a.v_scale + bh * a.v_param_stride_bh;
     const float *vz_g = a.v_zero + bh * a.v_param_stride_bh;
 
-    auto issue_tile = [&](int local_idx) {
-        const int tile = tile_begin + local_idx;
-        const int tok0 = tile * kTile;
-        const int ntok = min(kTile, a.n_quant - tok0);  // multiple of 32
+    auto issue_group = [&](int local_idx) {  // called by lane 0 only
+        const int64_t grp = grp_begin + local_idx;
+        const int64_t tok0 = grp * kGroup;
         const int stage = local_idx % STAGES;
-        const uint32_t bar = bar0 + 8u * stage;
-        const uint32_t dst = smem_u32(stages + (size_t)stage * C::STAGE_BYTES);
-        const uint32_t code_bytes = (uint32_t)ntok * C::RB;
-        const uint32_t kp_bytes = (uint32_t)(ntok / 32) * kD * 4;
-        const uint32_t vp_bytes = (uint32_t)ntok * 16;
-        mbar_expect_tx(bar, 2 * code_bytes + 2 * kp_bytes + 2 * vp_bytes);
-        bulk_g2s(dst + C::KC_OFF, kc_g + (int64_t)tok0 * C::RB, code_bytes, bar);
-        bulk_g2s(dst + C::VC_OFF, vc_g + (int64_t)tok0 * C::RB, code_bytes, bar);
-        bulk_g2s(dst + C::KS_OFF, ks_g + (int64_t)(tok0 / 32) * kD, kp_bytes, bar);
-        bulk_g2s(dst + C::KZ_OFF, kz_g + (int64_t)(tok0 / 32) * kD, kp_bytes, bar);
-        bulk_g2s(dst + C::VS_OFF, vs_g + (int64_t)tok0 * 4, vp_bytes, bar);
-        bulk_g2s(dst + C::VZ_OFF, vz_g + (int64_t)tok0 * 4, vp_bytes, bar);
+        const uint32_t bar = wbar0 + 8u * stage;
+        const uint32_t dst = smem_u32(wstages + (size_t)stage * C::STAGE_BYTES);
+        constexpr uint32_t code_bytes = kGroup * C::RB;
+        mbar_expect_tx(bar, 2 * code_bytes + 4 * 512);
+        bulk_g2s(dst + C::KC_OFF, kc_g + tok0 * C::RB, code_bytes, bar);
+        bulk_g2s(dst + C::VC_OFF, vc_g + tok0 * C::RB, code_bytes, bar);
+        bulk_g2s(dst + C::KS_OFF, ks_g + grp * kD, 512, bar);
+        bulk_g2s(dst + C::KZ_OFF, kz_g + grp * kD, 512, bar);
+        bulk_g2s(dst + C::VS_OFF, vs_g + tok0 * 4, 512, bar);
+        bulk_g2s(dst + C::VZ_OFF, vz_g + tok0 * 4, 512, bar);
     };
 
     if (tid == 0) {
-        for (int s = 0; s < STAGES; ++s) mbar_init(bar0 + 8u * s, 1);
+        for (int s = 0; s < kWarps * STAGES; ++s) mbar_init(bar0 + 8u * s, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
-    if (tid == 0) {
-        for (int i = 0; i < STAGES - 1 && i < n_local; ++i) issue_tile(i);
+    if (lane == 0) {
+        for (int i = 0; i < STAGES - 1 && i < n_local; ++i) issue_group(i);
     }
 
     // This lane's 16 query channels (head hd) are channels 32c + 16*half_id + [0, 16), handled
@@ -360,16 +361,17 @@ kivi_attend_mma_kernel(const __grid_constant__ Params p) {
     bool timed_out = false;
 
     for (int it = 0; it < n_local; ++it) {
-        __syncthreads();  // every warp is done with the stage that is refilled next
-        if (tid == 0 && it + STAGES - 1 < n_local) issue_tile(it + STAGES - 1);
+        __syncwarp();  // every lane is done reading the stage that is refilled next
+        if (lane == 0 && it + STAGES - 1 < n_local) {
+            // order the lanes' generic-proxy reads before the async-proxy overwrite
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            issue_group(it + STAGES - 1);
+        }
         const int stage = it % STAGES;
-        // After a timeout the CTA keeps its barrier cadence (no early exit: that could
-        // strand the other warps at __syncthreads) but stops waiting; its result is garbage
-        // and the host learns of it through vq_kivi_attend_status().
-        if (!timed_out && !mbar_wait(bar0 + 8u * stage, (uint32_t)((it / STAGES) & 1))) timed_out = true;
-        const int tok0 = (tile_begin + it) * kTile;
-        if (tok0 + 32 * warp >= a.n_quant) continue;  // this warp's group is past the end
-        const uint8_t *st = stages + (size_t)stage * C::STAGE_BYTES;
+        // After a timeout the warp stops waiting (later waits would only repeat it); its
+        // result is garbage and the host learns of it through vq_kivi_attend_status().
+        if (!timed_out && !mbar_wait(wbar0 + 8u * stage, (uint32_t)((it / STAGES) & 1))) timed_out = true;
+        const uint8_t *st = wstages + (size_t)stage * C::STAGE_BYTES;
 
         // ---- B operand of QK^T for this group: q*k_scale split into hi/lo halves ----------
         // Lanes g and g^4 share a head; each computes both halves for 16 of the 32 channels
@@ -377,8 +379,8 @@ kivi_attend_mma_kernel(const __grid_constant__ Params p) {
         uint32_t qf[16];
         float ck[2];
         {
-            const float *ks = reinterpret_cast<const float *>(st + C::KS_OFF) + warp * kD + 32 * c + 16 * half_id;
-            const float *kz = reinterpret_cast<const float *>(st + C::KZ_OFF) + warp * kD + 32 * c + 16 * half_id;
+            const float *ks = reinterpret_cast<const float *>(st + C::KS_OFF) + 32 * c + 16 * half_id;
+            const float *kz = reinterpret_cast<const float *>(st + C::KZ_OFF) + 32 * c + 16 * half_id;
             float x[16];
             float cp[4] = {0.f, 0.f, 0.f, 0.f};  // per element index: sum q/weight * k_zero
 #pragma unroll
@@ -435,7 +437,7 @@ kivi_attend_mma_kernel(const __grid_constant__ Params p) {
             uint32_t kw[2][C::KW];  // [row g / g+8][word]
 #pragma unroll
             for (int r = 0; r < 2; ++r) {
-                const int tok = 32 * warp + 16 * mt + g + 8 * r;
+                const int tok = 16 * mt + g + 8 * r;
                 const uint8_t *src = st + C::KC_OFF + tok * C::RB + c * (C::KW * 4);
                 if constexpr (C::KW == 4) {
                     const uint4 v = *reinterpret_cast<const uint4 *>(src);
@@ -505,7 +507,7 @@ kivi_attend_mma_kernel(const __grid_constant__ Params p) {
         // ---- O^T += codes^T . (P*v_scale), and the zero-point term in float32 ---------------
 #pragma unroll
         for (int mt = 0; mt < 2; ++mt) {
-            const int t0 = 32 * warp + 16 * mt;
+            const int t0 = 16 * mt;
             uint32_t pbw[4][2];  // [channel group][tokens 0-7 / 8-15 of the m-tile]
             {
                 const float4 vsa = *reinterpret_cast<const float4 *>(st + C::VS_OFF + (t0 + g) * 16);
@@ -652,27 +654,51 @@ kivi_attend_mma_kernel(const __grid_constant__ Params p) {
     }
 }
 
-// One CTA per (batch, kv head): combine the partials (log2-domain maxima).
-__global__ void kivi_attend_mma_merge_kernel(const __grid_constant__ Params p) {
+// One CTA per (batch, query head): combine the partials (log2-domain maxima). The split
+// weights are computed once into shared memory; the accumulation over splits is unrolled so
+// that several independent loads are in flight per thread (the loop is latency-bound).
+constexpr int kMergeMaxParts = 520;
+__global__ void __launch_bounds__(kD) kivi_attend_mma_merge_kernel(const __grid_constant__ Params p) {
+    __shared__ float sh_w[kMergeMaxParts];
+    __shared__ float sh_red[kD / 32];
     const vq_kivi_attend_args &a = p.a;
-    const int64_t bh = blockIdx.x;
+    const int hp = blockIdx.x % p.hpk;
+    const int64_t bh = blockIdx.x / p.hpk;
     const int b = (int)(bh / a.H_kv), hkv = (int)(bh % a.H_kv);
-    for (int i = threadIdx.x; i < p.hpk * kD; i += blockDim.x) {
-        const int hp = i / kD, d = i % kD;
-        float gm = -INFINITY;
-        for (int s = 0; s < p.n_parts; ++s) gm = fmaxf(gm, p.part_ml[((bh * p.n_parts + s) * p.hpk + hp) * 2]);
-        float gl = 0.f, acc = 0.f;
-        for (int s = 0; s < p.n_parts; ++s) {
-            const int64_t rec = (bh * p.n_parts + s) * p.hpk + hp;
-            const float ms = p.part_ml[rec * 2];
-            if (ms == -INFINITY) continue;
-            const float f = exp2f(ms - gm);
-            gl += p.part_ml[rec * 2 + 1] * f;
-            acc += p.part_o[rec * kD + d] * f;
-        }
-        const int64_t row = (int64_t)b * a.H_q + hkv * p.hpk + hp;
-        store_from_f32(a.out, a.out_dtype, row * kD + d, acc / gl);
+    const int d = threadIdx.x, lane = d & 31, warp = d >> 5;
+    const int64_t rec0 = bh * p.n_parts * p.hpk + hp;  // record of part s: rec0 + s * hpk
+    // global maximum over parts
+    float m = -INFINITY;
+    for (int s = d; s < p.n_parts; s += kD) m = fmaxf(m, p.part_ml[(rec0 + (int64_t)s * p.hpk) * 2]);
+    m = warp_max(m);
+    if (lane == 0) sh_red[warp] = m;
+    __syncthreads();
+    const float gm = fmaxf(fmaxf(sh_red[0], sh_red[1]), fmaxf(sh_red[2], sh_red[3]));
+    __syncthreads();
+    // per-part weight, and the denominator
+    float l = 0.f;
+    for (int s = d; s < p.n_parts; s += kD) {
+        const float ms = p.part_ml[(rec0 + (int64_t)s * p.hpk) * 2];
+        const float w = (ms == -INFINITY) ? 0.f : exp2f(ms - gm);
+        sh_w[s] = w;
+        l += w * p.part_ml[(rec0 + (int64_t)s * p.hpk) * 2 + 1];
     }
+    l = warp_sum(l);
+    if (lane == 0) sh_red[warp] = l;
+    __syncthreads();
+    const float gl = sh_red[0] + sh_red[1] + sh_red[2] + sh_red[3];
+    float acc = 0.f;
+    int s = 0;
+    for (; s + 8 <= p.n_parts; s += 8) {
+        float v[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[j] = p.part_o[(rec0 + (int64_t)(s + j) * p.hpk) * kD + d];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc = fmaf(v[j], sh_w[s + j], acc);
+    }
+    for (; s < p.n_parts; ++s) acc = fmaf(p.part_o[(rec0 + (int64_t)s * p.hpk) * kD + d], sh_w[s], acc);
+    const int64_t row = (int64_t)b * a.H_q + hkv * p.hpk + hp;
+    store_from_f32(a.out, a.out_dtype, row * kD + d, acc / gl);
 }
 
 // Pipeline depth and waves-per-launch are tunables; the environment overrides exist for
@@ -680,16 +706,16 @@ __global__ void kivi_attend_mma_merge_kernel(const __grid_constant__ Params p) {
 int tuned_stages() {
     static int v = [] {
         const char *e = getenv("VQ_ATTEND_STAGES");
-        const int s = e ? atoi(e) : 3;
-        return (s >= 2 && s <= kMaxStages) ? s : 3;
+        const int s = e ? atoi(e) : 2;
+        return (s >= 2 && s <= kMaxStages) ? s : 2;
     }();
     return v;
 }
 int tuned_waves() {
     static int v = [] {
         const char *e = getenv("VQ_ATTEND_WAVES");
-        const int s = e ? atoi(e) : 8;
-        return (s >= 1 && s <= 32) ? s : 8;
+        const int s = e ? atoi(e) : 2;
+        return (s >= 1 && s <= 32) ? s : 2;
     }();
     return v;
 }
@@ -700,9 +726,9 @@ int smem_for(int bits, int stages) {
 }
 
 int choose_splits(const vq_kivi_attend_args &a, const DeviceInfo &di) {
-    const int tiles = (int)ceil_div(a.n_quant, kTile);
+    const int tiles = (int)ceil_div(a.n_quant, kGroup * kWarps);  // CTA-sized pieces of the context
     if (tiles <= 1) return std::max(tiles, 0);
-    if (a.n_splits > 0) return std::min(a.n_splits, tiles);
+    if (a.n_splits > 0) return std::min(std::min(a.n_splits, tiles), kMergeMaxParts - 8);
     const int smem = smem_for(a.store_bits, tuned_stages());
     // resident CTAs per SM: shared memory, and 4 by registers (128 threads x <= 128 regs)
     const int occ = std::max(1, std::min(4, (int)(di.smem_optin / (smem + 1024))));
@@ -713,7 +739,7 @@ int choose_splits(const vq_kivi_attend_args &a, const DeviceInfo &di) {
     // at least 4 tiles per CTA so pipeline fill and the partial write stay amortised.
     int64_t want = std::max<int64_t>(1, (slots * tuned_waves()) / units);
     want = std::min<int64_t>(want, std::max(1, tiles / 4));
-    return (int)std::min<int64_t>(want, 512);
+    return (int)std::min<int64_t>(want, kMergeMaxParts - 8);
 }
 
 template <int BITS, int STAGES>
@@ -729,9 +755,9 @@ int32_t launch_one(const Params &p, dim3 grid, cudaStream_t st) {
 template <int BITS>
 int32_t launch_bits(const Params &p, dim3 grid, cudaStream_t st) {
     switch (tuned_stages()) {
-        case 2: return launch_one<BITS, 2>(p, grid, st);
+        case 3: return launch_one<BITS, 3>(p, grid, st);
         case 4: return launch_one<BITS, 4>(p, grid, st);
-        default: return launch_one<BITS, 3>(p, grid, st);
+        default: return launch_one<BITS, 2>(p, grid, st);
     }
 }
 
@@ -773,10 +799,10 @@ int32_t kivi_attend_mma_launch(const vq_kivi_attend_args &a, const DeviceInfo &d
     p.hpk = a.H_q / a.H_kv;
     p.n_chunks = (int)ceil_div(p.hpk, kChunkHeads);
     p.n_splits = choose_splits(a, di);
-    p.tiles_total = (int)ceil_div(a.n_quant, kTile);
-    p.tiles_per_split = (int)ceil_div(p.tiles_total, p.n_splits);
+    p.groups_total = a.n_quant / kGroup;
+    p.groups_per_warp = (int)ceil_div(p.groups_total, (int64_t)p.n_splits * kWarps);
     // a split count that leaves trailing splits empty is trimmed
-    p.n_splits = (int)ceil_div(p.tiles_total, p.tiles_per_split);
+    p.n_splits = (int)ceil_div(p.groups_total, (int64_t)p.groups_per_warp * kWarps);
     p.n_parts = p.n_splits + (a.n_res > 0 ? 1 : 0);
     const int64_t recs = (int64_t)a.B * a.H_kv * p.n_parts * p.hpk;
     const int64_t need = recs * (kD + 2) * (int64_t)sizeof(float);
@@ -790,7 +816,7 @@ int32_t kivi_attend_mma_launch(const vq_kivi_attend_args &a, const DeviceInfo &d
     dim3 grid(p.n_splits * p.n_chunks + (a.n_res > 0 ? 1 : 0), a.H_kv, a.B);
     const int32_t rc = a.store_bits == 4 ? launch_bits<4>(p, grid, st) : launch_bits<2>(p, grid, st);
     if (rc != VQ_OK) return rc;
-    kivi_attend_mma_merge_kernel<<<(unsigned)((int64_t)a.B * a.H_kv), 128, 0, st>>>(p);
+    kivi_attend_mma_merge_kernel<<<(unsigned)((int64_t)a.B * a.H_q), kD, 0, st>>>(p);
     VQ_CHECK_LAUNCH("kivi_attend_mma_merge_kernel");
     return VQ_OK;
 }
