@@ -1,0 +1,74 @@
+"""Host-side configuration surface (no GPU): options read-through, explicit-field priority,
+factory validation. Mirrors the reference's tests/cache/test_kvcache_config_options.py:29-107
+and tests/cache/test_cache_factory.py:46-99."""
+
+from __future__ import annotations
+
+import warnings
+
+import pytest
+
+from veloxquant_mlx_b200.cache import (KIVIOptions, KVCacheBuilder, KVCacheConfig, KVCacheFactory,
+                                       QuantizerConfigError, VecInferOptions)
+
+
+def test_options_populate_flat_fields():
+    cfg = KVCacheConfig(method="kivi", options=KIVIOptions(kivi_group_size=64))
+    assert cfg.kivi_group_size == 64
+    cfg = KVCacheConfig(method="vecinfer", options=VecInferOptions(key_sub_dim=8, residual_length=32))
+    assert cfg.key_sub_dim == 8 and cfg.residual_length == 32 and cfg.value_sub_dim == 8
+
+
+def test_explicit_flat_kwarg_beats_options_even_when_equal_to_default():
+    cfg = KVCacheConfig(method="kivi", kivi_group_size=32, options=KIVIOptions(kivi_group_size=64))
+    assert cfg.kivi_group_size == 32
+    cfg = KVCacheConfig(method="kivi", residual_length=128, options=VecInferOptions(residual_length=16))
+    assert cfg.residual_length == 128
+
+
+def test_flat_setter_warns_after_construction():
+    cfg = KVCacheConfig(method="kivi")
+    with pytest.warns(DeprecationWarning, match="KIVIOptions"):
+        cfg.kivi_group_size = 16
+    with warnings.catch_warnings():
+        warnings.simplefilter("error")
+        cfg.head_dim = 64  # not an options-backed field: silent
+
+
+def test_factory_rejects_observers_outlier_bits_and_lists():
+    with pytest.raises(QuantizerConfigError, match="observers"):
+        KVCacheFactory.create(KVCacheConfig(method="kivi", observers=[object()]))
+    with pytest.raises(QuantizerConfigError, match="bit_width_outlier"):
+        KVCacheFactory.create(KVCacheConfig(method="kivi", bit_width_outlier=4))
+    with pytest.raises(QuantizerConfigError, match="single int"):
+        KVCacheFactory.create(KVCacheConfig(method="kivi", bit_width_inlier=[2, 4]))
+    with pytest.raises(QuantizerConfigError, match="sliding_window"):
+        KVCacheFactory.create(KVCacheConfig(method="kivi", sliding_window=64))
+
+
+def test_unknown_method_lists_every_choice():
+    with pytest.raises(QuantizerConfigError) as ei:
+        KVCacheFactory.create(KVCacheConfig(method="no_such_method"))
+    msg = str(ei.value)
+    assert "unknown method 'no_such_method'" in msg and "kivi" in msg
+
+
+def test_config_error_is_a_value_error_and_repr():
+    assert issubclass(QuantizerConfigError, ValueError)
+    assert "method='kivi'" in repr(KVCacheConfig(method="kivi", head_dim=64))
+
+
+def test_no_cpu_path():
+    # without a CUDA device (or with use_metal_kernels=False) construction fails loudly
+    import torch
+
+    with pytest.raises(RuntimeError, match="use_metal_kernels=False"):
+        KVCacheFactory.create(KVCacheConfig(method="kivi", use_metal_kernels=False))
+    if not torch.cuda.is_available():
+        with pytest.raises(RuntimeError, match="not available"):
+            KVCacheFactory.create(KVCacheConfig(method="kivi"))
+
+
+def test_builder_layer_lists_validate():
+    with pytest.raises(QuantizerConfigError, match="2 entries for 3 layers"):
+        KVCacheBuilder.for_layers(3, KVCacheConfig(method="kivi", bit_width_inlier=[2, 4]))

@@ -1,0 +1,576 @@
+"""Cache-level drop-in surface: ``KVCacheConfig`` / ``KVCacheFactory`` / ``KVCacheBuilder`` and
+the packed KIVI cache.
+
+Mirrors the reference's ``veloxquant_mlx/cache/base.py`` (config ``:473-864``, factory
+``:974-1048``, builder ``:1242-1433``), ``cache/options.py:35-50`` and
+``cache/kivi_cache.py`` for the methods on the compressed-KV hot path. Only the fields those
+methods read exist here. Tensors are ``torch`` CUDA tensors; all arithmetic runs in the
+native library (no CPU path).
+
+Difference from the reference that is the point of this package: the reference's KIVI cache
+quantizes and immediately dequantizes back into an fp16 buffer (``cache/kivi_cache.py:26-43``);
+this one KEEPS the packed codes + fp32 (scale, zero) and attends over them directly with
+:meth:`KIVIKVCache.fused_sdpa`. ``update_and_fetch`` still returns the reference's view of
+the history (round-tripped quantized region followed by the exact residual window) unless
+``fused_sdpa_memory_bound=True``, in which case it returns empty sentinels like the
+reference's VecInfer memory-bound mode (``cache/vecinfer_cache.py:491-532``).
+"""
+
+from __future__ import annotations
+
+import dataclasses
+import functools
+import math
+import warnings
+from dataclasses import dataclass, field
+from typing import Any
+
+import torch
+
+from . import kernels
+
+
+class QuantizerConfigError(ValueError):
+    """Invalid cache / quantizer configuration (reference: ``core/exceptions.py:12``)."""
+
+
+# ----------------------------------------------------------------------------------------
+# options (reference: cache/options.py)
+# ----------------------------------------------------------------------------------------
+@dataclass
+class VecInferOptions:
+    key_sub_dim: int = 4
+    value_sub_dim: int = 8
+    key_codebook_bits: int = 12
+    value_codebook_bits: int = 8
+    residual_length: int = 128
+
+
+@dataclass
+class KIVIOptions:
+    kivi_group_size: int = 32
+
+
+_FIELD_TO_OPTIONS_CLASS = {
+    "key_sub_dim": "VecInferOptions", "value_sub_dim": "VecInferOptions",
+    "key_codebook_bits": "VecInferOptions", "value_codebook_bits": "VecInferOptions",
+    "residual_length": "VecInferOptions", "kivi_group_size": "KIVIOptions",
+}
+
+_CACHE_CLASS_BY_METHOD: dict = {}  # filled at the bottom of the module
+
+
+@dataclass
+class KVCacheConfig:
+    """Configuration of one cache instance (hot-path subset of the reference's dataclass).
+
+    ``use_metal_kernels`` is kept for source compatibility: ``None``/``True`` select the
+    native kernels (the only implementation here); ``False`` asks for the reference's
+    pure-MLX twin, which does not exist in this package, and is rejected.
+    """
+
+    method: str = "kivi"
+    head_dim: int = 128
+    bit_width_inlier: Any = 2
+    bit_width_outlier: Any = None
+    seed: int = 42
+    dtype: Any = None
+    capacity: Any = None
+    sliding_window: Any = None
+    observers: list = field(default_factory=list)
+    options: Any = None
+    key_sub_dim: int = 4
+    value_sub_dim: int = 8
+    key_codebook_bits: int = 12
+    value_codebook_bits: int = 8
+    residual_length: int = 128
+    kivi_group_size: int = 32
+    smooth_factors: Any = None
+    key_codebook: Any = None
+    value_codebook: Any = None
+    use_metal_kernels: Any = None
+    fused_sdpa: Any = False
+    fused_sdpa_max_ctx: Any = None
+    fused_sdpa_memory_bound: bool = False
+
+    def __repr__(self) -> str:
+        return (f"KVCacheConfig(method={self.method!r}, d={self.head_dim}, "
+                f"b={self.bit_width_inlier}, seed={self.seed})")
+
+    def __post_init__(self) -> None:
+        # An `options` dataclass fills its flat fields unless the caller NAMED the flat
+        # field (even with its default value): reference cache/base.py:872-888, :957-971.
+        if self.options is not None and dataclasses.is_dataclass(self.options):
+            explicit = getattr(self, "_explicit_fields", frozenset())
+            for f in dataclasses.fields(self.options):
+                if f.name in _FIELD_TO_OPTIONS_CLASS and f.name not in explicit:
+                    object.__setattr__(self, f.name, getattr(self.options, f.name))
+        object.__setattr__(self, "_post_init_done", True)
+
+    def __setattr__(self, name: str, value: Any) -> None:
+        if getattr(self, "_post_init_done", False) and name in _FIELD_TO_OPTIONS_CLASS:
+            cls_name = _FIELD_TO_OPTIONS_CLASS[name]
+            warnings.warn(
+                f"KVCacheConfig.{name} is deprecated in favor of {cls_name} "
+                f"(pass it via KVCacheConfig(options={cls_name}({name}=...))).",
+                DeprecationWarning, stacklevel=2)
+        object.__setattr__(self, name, value)
+
+
+def _track_explicit_fields(cls):
+    init = cls.__init__
+    names = [f.name for f in dataclasses.fields(cls) if f.init]
+
+    @functools.wraps(init)
+    def __init__(self, *args, **kwargs):
+        object.__setattr__(self, "_explicit_fields", frozenset(names[: len(args)]) | kwargs.keys())
+        init(self, *args, **kwargs)
+
+    cls.__init__ = __init__
+    return cls
+
+
+_track_explicit_fields(KVCacheConfig)
+
+
+class KVCacheFactory:
+    """``KVCacheFactory.create(config)`` -> cache (reference: ``cache/base.py:974-1048``)."""
+
+    @staticmethod
+    def create(config: KVCacheConfig):
+        b = config.bit_width_inlier
+        if isinstance(b, list) and config.method != "vecinfer":
+            raise QuantizerConfigError(
+                "KVCacheFactory.create() requires bit_width_inlier to be a single int. "
+                "List-form bit_width_inlier (per-layer allocation) is consumed by "
+                "KVCacheBuilder.for_model(), which dispatches to create() once per layer.")
+        if config.observers:
+            raise QuantizerConfigError(
+                "KVCacheFactory.create() received a non-empty config.observers, but no cache "
+                "implementation emits QuantizationEvent -- remove `observers` from KVCacheConfig.")
+        if config.bit_width_outlier is not None:
+            raise QuantizerConfigError(
+                f"KVCacheFactory.create() received config.bit_width_outlier={config.bit_width_outlier!r}, "
+                "but no cache implementation reads this field. Remove `bit_width_outlier` from "
+                "KVCacheConfig; it has no effect.")
+        cls = _CACHE_CLASS_BY_METHOD.get(config.method)
+        if cls is None:
+            choices = ", ".join(_CACHE_CLASS_BY_METHOD)
+            raise QuantizerConfigError(f"KVCacheFactory: unknown method '{config.method}'. Choices: {choices}.")
+        if config.sliding_window is not None:
+            raise QuantizerConfigError(
+                f"KVCacheFactory: sliding_window is only compatible with standalone methods -- "
+                f"method {config.method!r} implements the update_and_fetch protocol.")
+        return cls(config)
+
+
+class KVCacheBuilder:
+    """Fluent builder (reference: ``cache/base.py:1195-1433``), hot-path subset."""
+
+    def __init__(self) -> None:
+        self._config = KVCacheConfig()
+
+    def with_method(self, method: str) -> "KVCacheBuilder":
+        object.__setattr__(self._config, "method", method)
+        return self
+
+    def with_head_dim(self, d: int) -> "KVCacheBuilder":
+        object.__setattr__(self._config, "head_dim", int(d))
+        return self
+
+    def with_bits(self, inlier: int) -> "KVCacheBuilder":
+        object.__setattr__(self._config, "bit_width_inlier", inlier)
+        return self
+
+    def with_seed(self, seed: int) -> "KVCacheBuilder":
+        object.__setattr__(self._config, "seed", int(seed))
+        return self
+
+    def build(self):
+        return KVCacheFactory.create(self._config)
+
+    @staticmethod
+    def for_layers(n_layers: int, config: KVCacheConfig, head_dims=None) -> list:
+        """One cache per attention layer with ``seed + i`` and the layer's own bit-width
+        (list-form ``bit_width_inlier``) and head_dim, as ``for_model`` does per layer."""
+        caches = []
+        bits = config.bit_width_inlier
+        if isinstance(bits, list) and len(bits) != n_layers:
+            raise QuantizerConfigError(
+                f"KVCacheBuilder.for_model: bit_width_inlier list has {len(bits)} entries for {n_layers} layers")
+        for i in range(n_layers):
+            changes = {"seed": config.seed + i}
+            if isinstance(bits, list):
+                changes["bit_width_inlier"] = int(bits[i])
+            if head_dims is not None:
+                changes["head_dim"] = int(head_dims[i])
+            caches.append(KVCacheFactory.create(dataclasses.replace(config, **changes)))
+        return caches
+
+    @staticmethod
+    def for_model(model: Any, config: KVCacheConfig) -> list:
+        """Build per-layer caches for ``model`` (anything with ``.layers`` or a HF-style
+        ``.config.num_hidden_layers``)."""
+        layers = getattr(model, "layers", None)
+        if layers is None and hasattr(model, "model"):
+            layers = getattr(model.model, "layers", None)
+        if layers is not None:
+            n = len(layers)
+        elif hasattr(model, "config") and hasattr(model.config, "num_hidden_layers"):
+            n = int(model.config.num_hidden_layers)
+        else:
+            raise QuantizerConfigError("KVCacheBuilder.for_model: cannot find the model's layers")
+        return KVCacheBuilder.for_layers(n, config)
+
+
+def _native_only(config, who: str) -> None:
+    if getattr(config, "use_metal_kernels", None) is False:
+        raise RuntimeError(
+            f"{who}: use_metal_kernels=False asks for the pure-framework twin, which this package "
+            "does not have (native sm_100a kernels only, no fallback)")
+    if not kernels.kivi_available():
+        raise RuntimeError(f"{who}: the native library or a CUDA device is not available")
+
+
+# ----------------------------------------------------------------------------------------
+# KIVI
+# ----------------------------------------------------------------------------------------
+class KIVIKVCache:
+    """Packed KIVI cache: per-channel keys, per-token values, fp residual window.
+
+    Storage (grown geometrically): packed codes ``u8 [B,H,cap,D*sb/8]``, key params
+    ``f32 [B,H,cap/g,D]``, value params ``f32 [B,H,cap,D/g]``, residual ``[B,H,R+g+.., D]``
+    in the activation dtype. Quantization policy = ``KIVIKVCache._quantization_boundary``
+    of the reference (``cache/kivi_cache.py:206-225``): after each append, tokens older than
+    ``residual_length`` are flushed in whole ``group_size`` blocks, so one-shot prefill and
+    token-by-token decode quantize identical groups. Never exposes ``.bits``.
+    """
+
+    def __init__(self, config: Any) -> None:
+        _native_only(config, "KIVIKVCache")
+        self._head_dim = int(config.head_dim)
+        b = config.bit_width_inlier
+        if isinstance(b, list):
+            raise QuantizerConfigError(
+                "KIVIKVCache: bit_width_inlier must be a single int; "
+                "per-layer lists are dispatched by KVCacheBuilder.for_model().")
+        self._b = int(b)
+        if not 1 <= self._b <= 8:
+            raise QuantizerConfigError(f"KIVIKVCache: bit_width_inlier={self._b} must be in [1, 8].")
+        self._group_size = int(getattr(config, "kivi_group_size", 32))
+        if self._group_size < 1:
+            raise QuantizerConfigError(f"KIVIKVCache: kivi_group_size={self._group_size} must be >= 1.")
+        self._residual_length = int(getattr(config, "residual_length", 128))
+        self._levels = (1 << self._b) - 1
+        self._sb = kernels.storage_bits(self._b)
+        if (self._head_dim * self._sb) % 8:
+            raise QuantizerConfigError("KIVIKVCache: head_dim * storage bits must be a multiple of 8")
+        self._eps = 1e-8
+        self._memory_bound = bool(getattr(config, "fused_sdpa_memory_bound", False))
+        self.offset = 0
+        self._n_quantized = 0
+        self._n_res = 0
+        self._cap = 0
+        self._k_codes = self._v_codes = None
+        self._k_scale = self._k_zero = self._v_scale = self._v_zero = None
+        self._k_res = self._v_res = None
+        self._shape_bhd = (1, 1, self._head_dim)
+        self._dtype = None
+        # byte accounting (same definitions as the reference's properties)
+        self._key_bytes_compressed = 0
+        self._value_bytes_compressed = 0
+        self._key_bytes_fp16 = 0
+        self._value_bytes_fp16 = 0
+        self._residual_fp16_bytes = 0
+        self._tokens_seen = 0
+
+    # -- policy ------------------------------------------------------------------------
+    def _quantization_boundary(self) -> int:
+        aged = max(0, self.offset - self._residual_length)
+        return (aged // self._group_size) * self._group_size
+
+    # -- storage -----------------------------------------------------------------------
+    def _ensure_capacity(self, B, H, D, n_tokens, device, dtype) -> None:
+        g = self._group_size
+        if self._k_codes is not None and n_tokens <= self._cap:
+            return
+        new_cap = max(256, self._cap)
+        while new_cap < n_tokens:
+            new_cap *= 2
+        new_cap = ((new_cap + g - 1) // g) * g
+        rb = D * self._sb // 8
+        gv = (D + g - 1) // g
+
+        def grow(old, shape, dt):
+            t = torch.empty(shape, dtype=dt, device=device)
+            if old is not None and old.shape[2] > 0:
+                t[:, :, : old.shape[2]] = old
+            return t
+
+        self._k_codes = grow(self._k_codes, (B, H, new_cap, rb), torch.uint8)
+        self._v_codes = grow(self._v_codes, (B, H, new_cap, rb), torch.uint8)
+        self._k_scale = grow(self._k_scale, (B, H, new_cap // g, D), torch.float32)
+        self._k_zero = grow(self._k_zero, (B, H, new_cap // g, D), torch.float32)
+        self._v_scale = grow(self._v_scale, (B, H, new_cap, gv), torch.float32)
+        self._v_zero = grow(self._v_zero, (B, H, new_cap, gv), torch.float32)
+        self._cap = new_cap
+
+    def _ensure_residual(self, B, H, D, n, device, dtype) -> None:
+        if self._k_res is not None and self._k_res.shape[2] >= n:
+            return
+        cap = max(self._residual_length + 2 * self._group_size, n)
+        k = torch.empty((B, H, cap, D), dtype=dtype, device=device)
+        v = torch.empty((B, H, cap, D), dtype=dtype, device=device)
+        if self._k_res is not None and self._n_res:
+            k[:, :, : self._n_res] = self._k_res[:, :, : self._n_res]
+            v[:, :, : self._n_res] = self._v_res[:, :, : self._n_res]
+        self._k_res, self._v_res = k, v
+
+    # -- protocol ----------------------------------------------------------------------
+    def update_and_fetch(self, keys: torch.Tensor, values: torch.Tensor):
+        """Append ``keys/values [B,H,S,D]``; flush aged whole groups into the packed store."""
+        if keys.ndim != 4 or keys.shape != values.shape:
+            raise ValueError(f"KIVIKVCache.update_and_fetch: keys/values must be equal 4D shapes, got "
+                             f"{tuple(keys.shape)} / {tuple(values.shape)}")
+        B, H, S, D = keys.shape
+        if D != self._head_dim:
+            raise QuantizerConfigError(f"KIVIKVCache: expected head_dim {self._head_dim}, got {D}.")
+        if self._dtype is None:
+            self._dtype = keys.dtype
+        self._shape_bhd = (B, H, D)
+        dev = keys.device
+        self._ensure_residual(B, H, D, self._n_res + S, dev, keys.dtype)
+        self._k_res[:, :, self._n_res : self._n_res + S] = keys
+        self._v_res[:, :, self._n_res : self._n_res + S] = values
+        self._n_res += S
+        self.offset += S
+
+        new_boundary = self._quantization_boundary()
+        n_flush = new_boundary - self._n_quantized
+        if n_flush > 0:
+            self._ensure_capacity(B, H, D, new_boundary, dev, keys.dtype)
+            g = self._group_size
+            kernels.kivi_quantize_into(self._k_res[:, :, :n_flush], -2, g, self._b, codes=self._k_codes,
+                                       scale=self._k_scale, zero=self._k_zero, tok_offset=self._n_quantized,
+                                       store_bits=self._sb, eps=self._eps)
+            kernels.kivi_quantize_into(self._v_res[:, :, :n_flush], -1, g, self._b, codes=self._v_codes,
+                                       scale=self._v_scale, zero=self._v_zero, tok_offset=self._n_quantized,
+                                       store_bits=self._sb, eps=self._eps)
+            keep = self._n_res - n_flush
+            if keep > 0:
+                self._k_res[:, :, :keep] = self._k_res[:, :, n_flush : self._n_res].clone()
+                self._v_res[:, :, :keep] = self._v_res[:, :, n_flush : self._n_res].clone()
+            self._n_res = keep
+            self._n_quantized = new_boundary
+        self._account_bytes(B, H, S, D, max(n_flush, 0))
+        if self._memory_bound:
+            z = keys.new_zeros((B, H, 0, D))
+            return z, z
+        return self._materialize()
+
+    def _materialize(self):
+        """The reference cache's view: round-tripped quantized rows, then the exact tail."""
+        B, H, D = self._shape_bhd
+        nq = self._n_quantized
+        parts_k, parts_v = [], []
+        if nq:
+            g = self._group_size
+            kq = kernels.scalar_decode_once(self._k_codes[:, :, :nq].contiguous(), self._k_scale[:, :, : nq // g].contiguous(),
+                                            self._k_zero[:, :, : nq // g].contiguous(), g, "K", store_bits=self._sb,
+                                            out_dtype=self._dtype)
+            vq = kernels.scalar_decode_once(self._v_codes[:, :, :nq].contiguous(), self._v_scale[:, :, :nq].contiguous(),
+                                            self._v_zero[:, :, :nq].contiguous(), g, "V", store_bits=self._sb,
+                                            out_dtype=self._dtype)
+            parts_k.append(kq)
+            parts_v.append(vq)
+        parts_k.append(self._k_res[:, :, : self._n_res])
+        parts_v.append(self._v_res[:, :, : self._n_res])
+        return torch.cat(parts_k, dim=2), torch.cat(parts_v, dim=2)
+
+    def fused_sdpa(self, q: torch.Tensor, scale: float, *, causal: bool = True, sliding_window: int = 0,
+                   out: torch.Tensor | None = None) -> torch.Tensor:
+        """Attention of ``q [B,H_q,S_q,D]`` over the packed store + residual, no dequantized
+        copy of the history. One query row per call (decode); for several rows pass
+        ``causal=False`` (every row then sees every slot, as the reference's
+        ``scalar_fused_decode_attend`` does)."""
+        if q.ndim != 4:
+            raise ValueError(f"KIVIKVCache.fused_sdpa: q must be 4D, got {tuple(q.shape)}")
+        if sliding_window:
+            raise ValueError("KIVIKVCache.fused_sdpa: sliding_window is not supported")
+        if q.shape[2] != 1 and causal:
+            raise ValueError("KIVIKVCache.fused_sdpa: causal masking needs S_q == 1 (decode); "
+                             "use dense attention over update_and_fetch's output for prefill")
+        if self.offset == 0:
+            raise RuntimeError("KIVIKVCache.fused_sdpa: the cache is empty")
+        has_q = self._n_quantized > 0
+        return kernels.kivi_decode_attend(
+            q, self._k_codes if has_q else None, self._k_scale, self._k_zero,
+            self._v_codes if has_q else None, self._v_scale, self._v_zero, self._group_size, scale,
+            store_bits=self._sb, n_quant=self._n_quantized,
+            k_res=self._k_res if self._n_res else None, v_res=self._v_res if self._n_res else None,
+            n_res=self._n_res, out=out, _fn="KIVIKVCache.fused_sdpa")
+
+    # -- trim / state ------------------------------------------------------------------
+    def trim(self, n: int) -> int:
+        """Drop the last ``n`` tokens. The quantized frontier snaps DOWN to a group multiple;
+        rows of a partly trimmed group return to the residual as their once-rounded values,
+        so the next flush re-quantizes exactly what the reference's fp16 buffer would hold
+        (``cache/kivi_cache.py:264-299``)."""
+        n = int(min(max(n, 0), self.offset))
+        if n == 0:
+            return 0
+        new_offset = self.offset - n
+        g = self._group_size
+        old_nq = self._n_quantized
+        if new_offset >= old_nq:
+            self._n_res -= n
+            n_rolled = 0
+        else:
+            new_nq = (new_offset // g) * g
+            n_rolled = old_nq - new_nq
+            keep = new_offset - new_nq
+            B, H, D = self._shape_bhd
+            if keep > 0:
+                lo_g, hi_g = new_nq // g, (new_offset + g - 1) // g
+                kq = kernels.scalar_decode_once(self._k_codes[:, :, new_nq : hi_g * g].contiguous(),
+                                                self._k_scale[:, :, lo_g:hi_g].contiguous(),
+                                                self._k_zero[:, :, lo_g:hi_g].contiguous(), g, "K",
+                                                store_bits=self._sb, out_dtype=self._dtype)
+                vq = kernels.scalar_decode_once(self._v_codes[:, :, new_nq : hi_g * g].contiguous(),
+                                                self._v_scale[:, :, new_nq : hi_g * g].contiguous(),
+                                                self._v_zero[:, :, new_nq : hi_g * g].contiguous(), g, "V",
+                                                store_bits=self._sb, out_dtype=self._dtype)
+                self._ensure_residual(B, H, D, keep, kq.device, self._dtype)
+                self._k_res[:, :, :keep] = kq[:, :, :keep]
+                self._v_res[:, :, :keep] = vq[:, :, :keep]
+            self._n_res = keep
+            self._n_quantized = new_nq
+        self.offset = new_offset
+        self._rollback_bytes(n, n_rolled)
+        return n
+
+    def is_trimmable(self) -> bool:
+        return True
+
+    def empty(self) -> bool:
+        return self.offset == 0
+
+    def size(self) -> int:
+        return self.offset
+
+    def __len__(self) -> int:
+        return self.offset
+
+    @property
+    def state(self):
+        """Live rows of every buffer plus the counters (checkpoint / prompt-cache reuse)."""
+        nq, g = self._n_quantized, self._group_size
+        if self._k_res is None:
+            return ()
+        pk = lambda t, n: None if t is None else t[:, :, :n].contiguous()  # noqa: E731
+        return (pk(self._k_codes, nq), pk(self._k_scale, nq // g), pk(self._k_zero, nq // g),
+                pk(self._v_codes, nq), pk(self._v_scale, nq), pk(self._v_zero, nq),
+                self._k_res[:, :, : self._n_res].contiguous(), self._v_res[:, :, : self._n_res].contiguous(),
+                torch.tensor([self.offset, nq, self._n_res]))
+
+    @state.setter
+    def state(self, st) -> None:
+        if not st:
+            return
+        kc, ks, kz, vc, vs, vz, kr, vr, counters = st
+        self.offset, nq, n_res = (int(x) for x in counters.tolist())
+        B, H, _, D = kr.shape
+        self._shape_bhd, self._dtype = (B, H, D), kr.dtype
+        self._k_codes = self._v_codes = None
+        self._cap = 0
+        if nq:
+            self._ensure_capacity(B, H, D, nq, kr.device, kr.dtype)
+            g = self._group_size
+            self._k_codes[:, :, :nq], self._v_codes[:, :, :nq] = kc, vc
+            self._k_scale[:, :, : nq // g], self._k_zero[:, :, : nq // g] = ks, kz
+            self._v_scale[:, :, :nq], self._v_zero[:, :, :nq] = vs, vz
+        self._n_quantized = nq
+        self._k_res = self._v_res = None
+        self._n_res = 0
+        self._ensure_residual(B, H, D, n_res, kr.device, kr.dtype)
+        self._k_res[:, :, :n_res], self._v_res[:, :, :n_res] = kr, vr
+        self._n_res = n_res
+
+    def merge(self, *a, **k):
+        raise NotImplementedError("KIVIKVCache.merge: batched-cache merging is not supported")
+
+    # -- accounting (reference: cache/kivi_cache.py:301-410) ---------------------------
+    def _quantized_bytes(self, n, B, H, D):
+        gs = self._group_size
+        k = math.ceil(n * D * self._b / 8) * H * B + math.ceil(n / gs) * D * 2 * 2 * H * B
+        v = math.ceil(n * D * self._b / 8) * H * B + n * math.ceil(D / gs) * 2 * 2 * H * B
+        return k, v
+
+    def _account_bytes(self, B, H, S, D, n_quant_now) -> None:
+        if n_quant_now > 0:
+            k, v = self._quantized_bytes(n_quant_now, B, H, D)
+            self._key_bytes_compressed += k
+            self._value_bytes_compressed += v
+        self._residual_fp16_bytes = (self.offset - self._n_quantized) * D * 2 * 2 * H * B
+        self._key_bytes_fp16 += H * B * S * D * 2
+        self._value_bytes_fp16 += H * B * S * D * 2
+        self._tokens_seen += S
+
+    def _rollback_bytes(self, n_tokens, n_rolled) -> None:
+        B, H, D = self._shape_bhd
+        if n_rolled > 0:
+            k, v = self._quantized_bytes(n_rolled, B, H, D)
+            self._key_bytes_compressed = max(0, self._key_bytes_compressed - k)
+            self._value_bytes_compressed = max(0, self._value_bytes_compressed - v)
+        self._key_bytes_fp16 = max(0, self._key_bytes_fp16 - H * B * n_tokens * D * 2)
+        self._value_bytes_fp16 = max(0, self._value_bytes_fp16 - H * B * n_tokens * D * 2)
+        self._tokens_seen = max(0, self._tokens_seen - n_tokens)
+        self._residual_fp16_bytes = (self.offset - self._n_quantized) * D * 2 * 2 * H * B
+
+    @property
+    def compressed_key_bytes(self) -> int:
+        return self._key_bytes_compressed
+
+    @property
+    def compressed_value_bytes(self) -> int:
+        return self._value_bytes_compressed
+
+    @property
+    def fp16_key_bytes(self) -> int:
+        return self._key_bytes_fp16
+
+    @property
+    def fp16_value_bytes(self) -> int:
+        return self._value_bytes_fp16
+
+    @property
+    def residual_fp16_bytes(self) -> int:
+        return self._residual_fp16_bytes
+
+    @property
+    def assigned_avg_bits(self) -> float:
+        return float(self._b)
+
+    @property
+    def effective_compression_ratio(self) -> float:
+        total_fp16 = self._key_bytes_fp16 + self._value_bytes_fp16
+        if total_fp16 == 0:
+            return 1.0
+        total = self._key_bytes_compressed + self._value_bytes_compressed + self._residual_fp16_bytes
+        return total_fp16 / total if total else 1.0
+
+    @property
+    def nbytes(self) -> int:
+        """True live footprint: packed codes + fp32 params of quantized rows + residual rows."""
+        B, H, D = self._shape_bhd
+        nq, g = self._n_quantized, self._group_size
+        rb = D * self._sb // 8
+        packed = 2 * nq * rb + (nq // g) * D * 8 + nq * ((D + g - 1) // g) * 8
+        esz = 2 if self._dtype in (None, torch.float16, torch.bfloat16) else 4
+        return B * H * (packed + 2 * self._n_res * D * esz)
+
+
+_CACHE_CLASS_BY_METHOD["kivi"] = KIVIKVCache
+
+__all__ = ["QuantizerConfigError", "VecInferOptions", "KIVIOptions", "KVCacheConfig", "KVCacheFactory",
+           "KVCacheBuilder", "KIVIKVCache"]
