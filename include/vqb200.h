@@ -152,6 +152,22 @@ int32_t vq_kivi_decode_attend(const vq_kivi_attend_args *args, void *stream);
  * kernels have no device-side waits). */
 int32_t vq_kivi_attend_status(void);
 
+/* The same operation as vq_kivi_decode_attend for callers that cannot allocate device
+ * memory (a frozen memory pool, a host runtime that owns all allocations, a path where a
+ * synchronising, fallible cudaMalloc is not acceptable). It has no counterpart in the
+ * reference. `workspace` / `workspace_bytes` in `args` are ignored: the split partials go
+ * into an array built into the library (VQ_KIVI_STATIC_SCRATCH_BYTES,
+ * 8 MiB, resident on every GPU that loads the library until the process exits). The call
+ * allocates nothing and returns VQ_ERR_CAPACITY, with the needed and available sizes in
+ * vq_last_error(), when vq_kivi_attend_workspace_bytes(args) exceeds that capacity.
+ *  - The first call on each device looks up the array's device address (one-time set-up,
+ *    done with that device current); make that first call before starting a stream capture.
+ *  - All calls on a device share the one array. Calls must not overlap on the GPU (issue
+ *    them on one stream, or order them with events): overlapping calls race on it. Nothing
+ *    in it needs clearing between calls; every record read is written by the same call. */
+#define VQ_KIVI_STATIC_SCRATCH_BYTES (8u << 20)
+int32_t vq_kivi_decode_attend_static(const vq_kivi_attend_args *args, void *stream);
+
 /* ------------------------------------------------------------------------------------
  * Bit packing of flat uint8 code arrays, b in {1, 2, 4}
  * Replaces bit_pack / bit_unpack (veloxquant_mlx/metal/_bit_packing.py:87-148,

@@ -73,6 +73,7 @@ SIGNATURES = {
     "vq_kivi_attend_workspace_bytes": (C.c_int64, [C.POINTER(KiviAttendArgs)]),
     "vq_kivi_decode_attend": (C.c_int32, [C.POINTER(KiviAttendArgs), C.c_void_p]),
     "vq_kivi_attend_status": (C.c_int32, []),
+    "vq_kivi_decode_attend_static": (C.c_int32, [C.POINTER(KiviAttendArgs), C.c_void_p]),
     "vq_bit_pack": (C.c_int32, [C.c_void_p, C.c_int64, C.c_int32, C.c_void_p, C.c_void_p]),
     "vq_bit_unpack": (C.c_int32, [C.c_void_p, C.c_int64, C.c_int32, C.c_void_p, C.c_void_p]),
 }

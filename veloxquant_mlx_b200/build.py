@@ -27,6 +27,7 @@ SOURCES = [
     ("kivi_quant.cu", ["-fmad=false"]),
     ("kivi_attend.cu", []),
     ("kivi_attend_mma.cu", []),
+    ("kivi_attend_static.cu", []),
 ]
 
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]

@@ -246,13 +246,19 @@ def _workspace(device: torch.device, nbytes: int) -> torch.Tensor:
 
 def kivi_decode_attend(q, k_codes, k_scale, k_zero, v_codes, v_scale, v_zero, group_size, scale, *,
                        store_bits=8, n_quant=None, k_res=None, v_res=None, n_res=None,
-                       out=None, out_dtype=None, n_splits=0, variant=0, _fn="kivi_decode_attend"):
+                       out=None, out_dtype=None, n_splits=0, variant=0, static_scratch=False,
+                       _fn="kivi_decode_attend"):
     """Fused dequant + attention over packed codes and an optional unquantized tail.
 
     ``k_codes/v_codes [B,H_kv,cap,D*store_bits/8]`` (first ``n_quant`` rows used),
     ``k_scale/k_zero [B,H_kv,capG,D]``, ``v_scale/v_zero [B,H_kv,cap,ceil(D/g)]``,
     ``k_res/v_res [B,H_kv,capR,D]`` float (first ``n_res`` rows used), ``q [B,H_q,S_q,D]``.
     Returns ``[B,H_q,S_q,D]`` in ``out_dtype`` (default: ``q.dtype``).
+
+    ``static_scratch=True`` routes to ``vq_kivi_decode_attend_static``: no workspace is
+    taken from torch's allocator, the split partials live in an 8 MiB array inside the
+    library. For callers that must not allocate (pass ``out=`` too, so that nothing is
+    allocated here either); such calls must not overlap on the GPU.
     """
     fn = _fn
     if q.ndim != 4:
@@ -332,6 +338,9 @@ def kivi_decode_attend(q, k_codes, k_scale, k_zero, v_codes, v_scale, v_zero, gr
         a.res_dtype = dtype_code(k_res.dtype)
         a.res_stride_bh = k_res.shape[2] * k_res.shape[3]
     with torch.cuda.device(q.device):
+        if static_scratch:
+            check(lib().vq_kivi_decode_attend_static(C.byref(a), stream_ptr(q.device)), fn)
+            return out
         need = lib().vq_kivi_attend_workspace_bytes(C.byref(a))
         ws = _workspace(q.device, need)
         a.workspace, a.workspace_bytes = ws.data_ptr(), ws.numel()
