@@ -238,30 +238,32 @@ def run_reference(args):
 
 
 # ----------------------------------------------------------------------------- our arm
-def build_layer(torch, kernels, w, device, seed, dtype):
-    """Seeded synthetic K/V for one layer, quantized on the device into packed buffers."""
-    B, H_kv, D, g, b = w["batch"], w["H_kv"], w["D"], w["group"], w["bits"]
-    Sq, R = w["n_quant"], w["n_res"]
+def build_cache(torch, w, device, seed, dtype):
+    """One layer's cache, filled by a prefill append of seeded synthetic K/V: quantize-on-write
+    through the public cache interface (packed codes + fp32 params + residual window)."""
+    from veloxquant_mlx_b200.cache import KVCacheConfig, KVCacheFactory
+
+    B, H_kv, D = w["batch"], w["H_kv"], w["D"]
     gen = torch.Generator(device=device)
     gen.manual_seed(seed)
-    out = {}
     ch = torch.randperm(D, generator=gen, device=device)[:4]
-    for name, axis in (("k", -2), ("v", -1)):
-        x = torch.randn((B, H_kv, Sq + R, D), generator=gen, device=device, dtype=torch.float32)
+    kv = []
+    for _ in range(2):
+        x = torch.randn((B, H_kv, w["ctx"], D), generator=gen, device=device, dtype=torch.float32)
         x[..., ch] *= 20.0
-        x = x.to(dtype)
-        codes, scale, zero = kernels.kivi_quantize(x[:, :, :Sq], axis, g, b)
-        out[name] = (codes, scale, zero)
-        out[name + "_res"] = x[:, :, Sq:].contiguous()
+        kv.append(x.to(dtype))
         del x
-    return out
+    cache = KVCacheFactory.create(KVCacheConfig(
+        method="kivi", head_dim=D, bit_width_inlier=w["bits"], kivi_group_size=w["group"],
+        residual_length=w["residual"], fused_sdpa_memory_bound=True))
+    cache.update_and_fetch(kv[0], kv[1])
+    assert cache._n_quantized == w["n_quant"] and cache.offset == w["ctx"]
+    return cache
 
 
 def run_ours(args):
     import torch
     import torch.distributed as dist
-
-    from veloxquant_mlx_b200 import kernels
 
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -274,10 +276,10 @@ def run_ours(args):
         dist.init_process_group("nccl", device_id=device)
     w = workload(args)
     dtype = torch.bfloat16 if w["dtype"] == "bf16" else torch.float16
-    L, B, H_q, D = w["layers"], w["batch"], w["H_q"], w["D"]
+    L, B, H_q, H_kv, D = w["layers"], w["batch"], w["H_q"], w["H_kv"], w["D"]
     scale = 1.0 / math.sqrt(D)
 
-    layers = [build_layer(torch, kernels, w, device, 1000 * rank + l, dtype) for l in range(L)]
+    caches = [build_cache(torch, w, device, 1000 * rank + l, dtype) for l in range(L)]
     gen = torch.Generator(device=device)
     gen.manual_seed(7 + rank)
     qs = [torch.randn((B, H_q, 1, D), generator=gen, device=device, dtype=torch.float32).to(dtype) for _ in range(L)]
@@ -286,21 +288,50 @@ def run_ours(args):
     comm_stream = torch.cuda.Stream(device) if world > 1 else None
     torch.cuda.synchronize()
 
+    def gather(l):
+        ev = torch.cuda.Event()
+        ev.record()
+        with torch.cuda.stream(comm_stream):
+            comm_stream.wait_event(ev)
+            dist.all_gather_into_tensor(gathered[l], outs[l])
+
     def step():
-        works = []
         for l in range(L):
-            ly = layers[l]
-            kernels.kivi_decode_attend(qs[l], *ly["k"], *ly["v"], w["group"], scale, store_bits=w["bits"],
-                                       n_quant=w["n_quant"], k_res=ly["k_res"], v_res=ly["v_res"], out=outs[l],
-                                       n_splits=args.splits)
+            caches[l].fused_sdpa(qs[l], scale, out=outs[l])
             if world > 1:
-                ev = torch.cuda.Event()
-                ev.record()
-                with torch.cuda.stream(comm_stream):
-                    comm_stream.wait_event(ev)
-                    dist.all_gather_into_tensor(gathered[l], outs[l])
+                gather(l)
         if world > 1:
             torch.cuda.current_stream().wait_stream(comm_stream)
+
+    # End-to-end step through the cache interface with HOST buffers: per layer the query and
+    # the new token's K/V come from pinned host memory, the token is appended (quantized when
+    # a group ages out of the residual window), attention runs over the packed cache, and the
+    # layer's output goes back to pinned host memory.
+    host = {
+        "q": [torch.randn((B, H_q, 1, D), dtype=torch.float32).to(dtype).pin_memory() for _ in range(L)],
+        "k": [torch.randn((B, H_kv, 1, D), dtype=torch.float32).to(dtype).pin_memory() for _ in range(L)],
+        "v": [torch.randn((B, H_kv, 1, D), dtype=torch.float32).to(dtype).pin_memory() for _ in range(L)],
+        "o": [torch.empty((B, H_q, 1, D), dtype=dtype).pin_memory() for _ in range(L)],
+    }
+    dq = torch.empty((B, H_q, 1, D), device=device, dtype=dtype)
+    dk = torch.empty((B, H_kv, 1, D), device=device, dtype=dtype)
+    dv = torch.empty((B, H_kv, 1, D), device=device, dtype=dtype)
+    h2d_bytes = L * (dq.numel() + dk.numel() + dv.numel()) * dq.element_size()
+    d2h_bytes = L * dq.numel() * dq.element_size()
+
+    def e2e_step():
+        for l in range(L):
+            dq.copy_(host["q"][l], non_blocking=True)
+            dk.copy_(host["k"][l], non_blocking=True)
+            dv.copy_(host["v"][l], non_blocking=True)
+            caches[l].update_and_fetch(dk, dv)
+            caches[l].fused_sdpa(dq, scale, out=outs[l])
+            host["o"][l].copy_(outs[l], non_blocking=True)
+            if world > 1:
+                gather(l)
+        if world > 1:
+            torch.cuda.current_stream().wait_stream(comm_stream)
+        torch.cuda.synchronize()  # the host reads this step's outputs
 
     def barrier():
         torch.cuda.synchronize()
@@ -328,6 +359,23 @@ def run_ours(args):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms_total = float(t.item())
     ms_step = ms_total / args.steps
+
+    # ---- end-to-end arm (after the kernel arm, so the cache contents above stay fixed)
+    e2e_ms = None
+    if not args.no_e2e:
+        for _ in range(3):
+            e2e_step()
+        barrier()
+        f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        f0.record()
+        for _ in range(args.steps):
+            e2e_step()
+        f1.record()
+        barrier()
+        te = torch.tensor([f0.elapsed_time(f1)], device=device, dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(te, op=dist.ReduceOp.MAX)
+        e2e_ms = float(te.item()) / args.steps
 
     from veloxquant_mlx_b200 import _lib
     _lib.check(_lib.lib().vq_kivi_attend_status(), "bench")
@@ -357,7 +405,11 @@ def run_ours(args):
                          "kernel": f"kivi_attend_mma_kernel<{w['bits']}> (+ merge; duration = step time / layers)",
                          "algorithmic_bytes_per_launch": bytes_layer},
             "cpu_baseline": cpu,
-            "e2e": None,
+            "e2e": None if e2e_ms is None else {
+                "value": world * bytes_step / (e2e_ms * 1e-3) / 1e9, "unit": UNIT, "ms_per_step": e2e_ms,
+                "tokens_per_s": world * B / (e2e_ms * 1e-3),
+                "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": d2h_bytes,
+                "path": "KIVIKVCache.update_and_fetch(new token) + KIVIKVCache.fused_sdpa per layer, pinned host buffers"},
             "gpu_launches": 2 * L * args.steps,
             "clocks": clocks,
         }
@@ -377,7 +429,7 @@ def main():
     ap.add_argument("--batch", type=int, default=None)
     ap.add_argument("--ctx", type=int, default=None)
     ap.add_argument("--bits", type=int, default=None)
-    ap.add_argument("--splits", type=int, default=0)
+    ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
     if args.impl == "reference":

@@ -339,27 +339,37 @@ class KIVIKVCache:
             self._dtype = keys.dtype
         self._shape_bhd = (B, H, D)
         dev = keys.device
-        self._ensure_residual(B, H, D, self._n_res + S, dev, keys.dtype)
-        self._k_res[:, :, self._n_res : self._n_res + S] = keys
-        self._v_res[:, :, self._n_res : self._n_res + S] = values
-        self._n_res += S
+        g = self._group_size
         self.offset += S
-
         new_boundary = self._quantization_boundary()
         n_flush = new_boundary - self._n_quantized
-        if n_flush > 0:
+        if n_flush <= 0:
+            self._ensure_residual(B, H, D, self._n_res + S, dev, keys.dtype)
+            self._k_res[:, :, self._n_res : self._n_res + S] = keys
+            self._v_res[:, :, self._n_res : self._n_res + S] = values
+            self._n_res += S
+        else:
+            # Rows to flush are the oldest unquantized ones: the residual first, then the
+            # head of this block. A large prefill block is quantized straight from the
+            # caller's tensor; only its tail is copied into the residual buffer.
+            if self._n_res == 0:
+                src_k, src_v = keys, values
+            else:
+                src_k = torch.cat([self._k_res[:, :, : self._n_res], keys], dim=2)
+                src_v = torch.cat([self._v_res[:, :, : self._n_res], values], dim=2)
             self._ensure_capacity(B, H, D, new_boundary, dev, keys.dtype)
-            g = self._group_size
-            kernels.kivi_quantize_into(self._k_res[:, :, :n_flush], -2, g, self._b, codes=self._k_codes,
+            kernels.kivi_quantize_into(src_k[:, :, :n_flush], -2, g, self._b, codes=self._k_codes,
                                        scale=self._k_scale, zero=self._k_zero, tok_offset=self._n_quantized,
                                        store_bits=self._sb, eps=self._eps)
-            kernels.kivi_quantize_into(self._v_res[:, :, :n_flush], -1, g, self._b, codes=self._v_codes,
+            kernels.kivi_quantize_into(src_v[:, :, :n_flush], -1, g, self._b, codes=self._v_codes,
                                        scale=self._v_scale, zero=self._v_zero, tok_offset=self._n_quantized,
                                        store_bits=self._sb, eps=self._eps)
-            keep = self._n_res - n_flush
+            keep = src_k.shape[2] - n_flush
+            self._n_res = 0
+            self._ensure_residual(B, H, D, keep, dev, keys.dtype)
             if keep > 0:
-                self._k_res[:, :, :keep] = self._k_res[:, :, n_flush : self._n_res].clone()
-                self._v_res[:, :, :keep] = self._v_res[:, :, n_flush : self._n_res].clone()
+                self._k_res[:, :, :keep] = src_k[:, :, n_flush:]
+                self._v_res[:, :, :keep] = src_v[:, :, n_flush:]
             self._n_res = keep
             self._n_quantized = new_boundary
         self._account_bytes(B, H, S, D, max(n_flush, 0))
