@@ -176,6 +176,107 @@ int32_t vq_kivi_decode_attend_static(const vq_kivi_attend_args *args, void *stre
 int32_t vq_bit_pack(const uint8_t *codes, int64_t n, int32_t bits, uint8_t *packed, void *stream);
 int32_t vq_bit_unpack(const uint8_t *packed, int64_t n, int32_t bits, uint8_t *codes, void *stream);
 
+/* ------------------------------------------------------------------------------------
+ * VecInfer product VQ
+ * ---------------------------------------------------------------------------------- */
+
+/* Nearest-centroid indices of n sub-vectors. Distances are float32 in the order of
+ * vecinfer_quantize.metal: dist = 0; for i in 0..sub_dim-1: d = x_i - c_i; dist = dist + d*d
+ * (product and sum rounded separately); strict '<' so the lowest index wins ties.
+ * x is [n, sub_dim] contiguous (dtype x_dtype). codebook is float32 [n_c, sub_dim], or with
+ * n_sub > 0 a stack [n_sub, n_c, sub_dim] where sub-vector i uses codebook i % n_sub.
+ * indices are written index_bytes (1, 2 or 4) wide, little endian unsigned.
+ * Replaces quantize_vq (veloxquant_mlx/allocators/vecinfer.py:281-318) and
+ * vecinfer_quantize_metal (metal/_vecinfer.py:181-222, metal/src/vecinfer_quantize.metal). */
+int32_t vq_vq_quantize(const void *x, int32_t x_dtype, int64_t n, int32_t sub_dim,
+                       const float *codebook, int32_t n_centroids, int32_t n_sub,
+                       void *indices, int32_t index_bytes, void *stream);
+
+/* Codebook gather: out[i, :] = codebook[min(indices[i], n_c-1), :] (stacked codebooks as
+ * above). Replaces dequantize_vq (allocators/vecinfer.py:321-335) and vecinfer_dequant_metal
+ * (metal/_vecinfer.py:144-178, metal/src/vecinfer_dequant.metal). */
+int32_t vq_vq_dequant(const void *indices, int32_t index_bytes, int64_t n, const float *codebook,
+                      int32_t n_centroids, int32_t sub_dim, int32_t n_sub, void *out,
+                      int32_t out_dtype, void *stream);
+
+/* Attention over VQ-coded keys scored through a per-query lookup table
+ * lut[s][c] = q_sub[s] . codebook[c], score = scale * sum_s lut[s][idx[s]]; values are either
+ * VQ-coded (indices + codebook: the reference form) or a dense tensor. Tail-aligned causal
+ * mask (query row r sits at position S_kv - S_q + r) and optional trailing window.
+ * h_kv = h_q * H_kv / H_q. Replaces metal_fused_sdpa (veloxquant_mlx/metal/fused_sdpa.py:200-299,
+ * metal/src/fused_sdpa.metal). */
+typedef struct vq_vq_attend_args {
+    const void *q;            /* [B, H_q, S_q, D], already dual-transformed */
+    void *out;                /* [B, H_q, S_q, D] */
+    int32_t q_dtype, out_dtype;
+    int32_t B, H_q, H_kv, S_q, S_kv, D;
+    int64_t kv_stride_tok;    /* token capacity between (b, kv head) slabs of k/v arrays */
+    float scale;
+    int32_t causal, sliding_window;
+    const void *k_indices;    /* [B*H_kv][cap][n_sub], k_index_bytes wide */
+    int32_t k_index_bytes;
+    const float *k_codebook;  /* [n_c, sub_dim] or [k_stacked = n_sub][n_c][sub_dim] */
+    int32_t k_n_centroids, k_sub_dim, k_stacked;
+    int32_t v_mode;           /* 0 = dense values (v_dtype), 1 = VQ indices + codebook */
+    const void *v;            /* dense [B*H_kv][cap][D] or indices [B*H_kv][cap][D/v_sub_dim] */
+    int32_t v_dtype, v_index_bytes;
+    const float *v_codebook;  /* [n_c_v, v_sub_dim] */
+    int32_t v_n_centroids, v_sub_dim;
+    void *workspace;
+    int64_t workspace_bytes;
+    int32_t n_splits;         /* 0 = choose */
+} vq_vq_attend_args;
+int64_t vq_vq_attend_workspace_bytes(const vq_vq_attend_args *args);
+int32_t vq_vq_decode_attend(const vq_vq_attend_args *args, void *stream);
+
+/* ------------------------------------------------------------------------------------
+ * RaBitQ 1-bit keys
+ * ---------------------------------------------------------------------------------- */
+
+/* keys [n, D] -> sign bits u8 [n, D/8] (element 8j+t at byte j bit t, >= 0 -> 1) and
+ * mag[n] = sum|y| / D.  rotate = 1: y = WHT(keys * diag) / sqrt(D) with the Sylvester
+ * butterfly (D a power of two <= 1024); rotate = 0: y = keys (already rotated, e.g. by a
+ * dense QR rotation). Replaces rabitq_encode (veloxquant_mlx/metal/_rabitq_encode.py:83-128,
+ * metal/src/rabitq_encode.metal) and _pack_signs (quantizers/rabitq.py:64-70). */
+int32_t vq_rabitq_encode(const void *keys, int32_t dtype, int64_t n, int32_t D, const float *diag,
+                         int32_t rotate, uint8_t *bits, float *mag, void *stream);
+
+/* Two 4-bit indices per byte, low nibble = even element; n_out = n_in / 2 bytes.
+ * Replaces rabitq_pack_values (metal/_rabitq_values.py:64-95). */
+int32_t vq_rabitq_pack_values(const uint8_t *v_idx, int64_t n_out, uint8_t *packed, void *stream);
+
+/* score[i] = popcount(q_bits ^ bits[i]) * scale + cx[i]. Replaces rabitq_hamming_score
+ * (metal/_rabitq.py:63-103). */
+int32_t vq_rabitq_hamming_score(const uint8_t *q_bits, const uint8_t *bits, int64_t n, int32_t n_bytes,
+                                float scale, const float *cx, float *score, void *stream);
+
+/* Attention over sign-bit keys: score = (D - 2*popcount(sign(q) ^ k_bits)) * q_scale * k_mag
+ * + k_const, softmax over all slots (no mask), values from a <= 16-entry scalar codebook
+ * (one index per byte or nibble-packed: the reference form) or a dense tensor. H_q may be a
+ * multiple of H_kv (contiguous blocks). Replaces rabitq_fused_attend
+ * (veloxquant_mlx/metal/_rabitq_attend.py:112-216, metal/src/rabitq_attend.metal). */
+typedef struct vq_rabitq_attend_args {
+    const void *q;            /* [B, H_q, S_q, D] */
+    void *out;
+    int32_t q_dtype, out_dtype;
+    int32_t B, H_q, H_kv, S_q, S_kv, D;
+    int64_t kv_stride_tok;
+    const float *q_scale;     /* [B, H_q, S_q] */
+    const uint8_t *k_bits;    /* [B*H_kv][cap][D/8] */
+    const float *k_mag;       /* [B*H_kv][cap] */
+    const float *k_const;     /* [B*H_kv][cap] or NULL (= 0) */
+    int32_t v_mode;           /* 0 dense (v_dtype), 2 codebook index per byte, 3 nibble-packed */
+    const void *v;
+    int32_t v_dtype;
+    const float *v_cents;     /* [<= 16] */
+    int32_t n_cents;
+    void *workspace;
+    int64_t workspace_bytes;
+    int32_t n_splits;
+} vq_rabitq_attend_args;
+int64_t vq_rabitq_attend_workspace_bytes(const vq_rabitq_attend_args *args);
+int32_t vq_rabitq_decode_attend(const vq_rabitq_attend_args *args, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1,0 +1,162 @@
+"""GPU parity for the VecInfer path through the C ABI against the CPU oracle.
+Mirrors tests/allocators/test_vecinfer.py, tests/metal/test_vecinfer_dequant.py and
+tests/cache/test_vecinfer_fused_sdpa.py:189-271 of the reference.
+
+Indices are compared bit for bit with the oracle's canonical order (sequential float32
+accumulation, lowest index on ties); attention within 1e-2 as in the reference's own tests,
+and within the tighter |got-ref| <= 2e-3 + 1e-2*|ref| bound used elsewhere here.
+"""
+
+from __future__ import annotations
+
+import math
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import vq as o_vq
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+_DT = {"float16": torch.float16, "bfloat16": torch.bfloat16, "float32": torch.float32}
+
+
+def _v():
+    from veloxquant_mlx_b200 import vecinfer
+
+    return vecinfer
+
+
+def _cast(x32, dt):
+    t = torch.from_numpy(x32).to(_DT[dt])
+    return t.to(DEV), t.float().numpy()
+
+
+@pytest.mark.parametrize("dt", ["float16", "bfloat16", "float32"])
+@pytest.mark.parametrize("sub_dim,n_c", [(8, 256), (4, 16), (2, 4), (16, 64), (1, 8)])
+def test_quantize_vq_bit_exact(dt, sub_dim, n_c):
+    rng = np.random.default_rng(sub_dim * 1000 + n_c)
+    x, x32 = _cast(rng.standard_normal((3, 5, 67, 64)).astype(np.float32), dt)
+    cb, cb32 = _cast(rng.standard_normal((n_c, sub_dim)).astype(np.float32), dt)
+    got = _v().quantize_vq(x, cb, sub_dim)
+    assert got.dtype == torch.int32 and got.shape == (3, 5, 67, 64 // sub_dim)
+    want = o_vq.quantize_vq(x32, cb32, sub_dim)
+    np.testing.assert_array_equal(got.cpu().numpy(), want)
+    if n_c <= 256:
+        got8 = _v().quantize_vq(x, cb, sub_dim, index_dtype=torch.uint8)
+        np.testing.assert_array_equal(got8.cpu().numpy().astype(np.int32), want)
+
+
+def test_quantize_vq_config2_shape_and_ties_and_large_magnitude():
+    v = _v()
+    rng = np.random.default_rng(0)
+    # BASELINE config 2: keys fp16 [8, 4096, 128], sub_dim 8, 256 centroids fp16
+    keys, k32 = _cast(rng.standard_normal((8, 4096, 128)).astype(np.float32), "float16")
+    cb, cb32 = _cast(np.random.default_rng(42).standard_normal((256, 8)).astype(np.float32), "float16")
+    got = v.quantize_vq(keys, cb, 8, index_dtype=torch.uint8)
+    np.testing.assert_array_equal(got.cpu().numpy().astype(np.int32), o_vq.quantize_vq(k32, cb32, 8))
+    # duplicated centroids and exact midpoints: the lowest index wins
+    cbt = torch.tensor([[0, 0], [1, 1], [1, 1], [2, 2]], dtype=torch.float32, device=DEV)
+    xt = torch.tensor([[1, 1, 0.5, 0.5, 9, 9]], dtype=torch.float32, device=DEV)
+    assert v.quantize_vq(xt, cbt, 2).cpu().tolist() == [[1, 0, 3]]
+    # entries ~100: squared sums overflow fp16, the float32 distances must not collapse to 0
+    big, b32 = _cast((rng.standard_normal((64, 32)) * 100).astype(np.float32), "float16")
+    cbb, cbb32 = _cast((rng.standard_normal((16, 4)) * 100).astype(np.float32), "float16")
+    np.testing.assert_array_equal(v.quantize_vq(big, cbb, 4).cpu().numpy(), o_vq.quantize_vq(b32, cbb32, 4))
+    # per-sub-space codebooks (BASELINE config 2 wording: each subspace has its own 256 centroids)
+    cbs, cbs32 = _cast(rng.standard_normal((16, 256, 8)).astype(np.float32), "float16")
+    got = v.quantize_vq(keys[:2, :300], cbs, 8)
+    np.testing.assert_array_equal(got.cpu().numpy(), o_vq.quantize_vq(k32[:2, :300], cbs32, 8))
+    flat = v.vecinfer_quantize(keys[0, :50].reshape(-1, 8), cb)
+    np.testing.assert_array_equal(flat.cpu().numpy(), o_vq.quantize_vq(k32[0, :50], cb32, 8).reshape(-1))
+    with pytest.raises(ValueError, match="not divisible"):
+        v.quantize_vq(keys, cb[:, :7], 7)
+
+
+def test_dequantize_gather_clamp_and_lut():
+    v = _v()
+    rng = np.random.default_rng(1)
+    cb = torch.from_numpy(rng.standard_normal((16, 8)).astype(np.float32)).to(DEV)
+    idx = torch.from_numpy(rng.integers(0, 16, (2, 3, 9, 8)).astype(np.int32)).to(DEV)
+    got = v.dequantize_vq(idx, cb)
+    np.testing.assert_array_equal(got.cpu().numpy(), o_vq.dequantize_vq(idx.cpu().numpy(), cb.cpu().numpy()))
+    bad = idx.clone()
+    bad[0, 0, 0, 0] = 999
+    assert torch.equal(v.dequantize_vq(bad, cb)[0, 0, 0, :8], cb[15])
+    got16 = v.dequantize_vq(idx.to(torch.uint8), cb.half())
+    assert got16.dtype == torch.float16
+    q = torch.from_numpy(rng.standard_normal((2, 3, 64)).astype(np.float32)).to(DEV)
+    lut = v.compute_query_lut(q, cb, 8)
+    np.testing.assert_allclose(lut.cpu().numpy(), o_vq.compute_query_lut(q.cpu().numpy(), cb.cpu().numpy(), 8),
+                               rtol=1e-5, atol=1e-5)
+
+
+def test_dual_transform_invariance_with_gqa():
+    v = _v()
+    rng = np.random.default_rng(2)
+    D = 64
+    H = v.walsh_hadamard_matrix(D, device=DEV)
+    np.testing.assert_array_equal(H.cpu().numpy(), o_vq.walsh_hadamard_matrix(D))
+    lam = torch.from_numpy(rng.uniform(0.5, 2.0, (4, D)).astype(np.float32)).to(DEV)
+    K = torch.from_numpy(rng.standard_normal((1, 4, 7, D)).astype(np.float32)).to(DEV)
+    Q = torch.from_numpy(rng.standard_normal((1, 8, 1, D)).astype(np.float32)).to(DEV)
+    Kt, Qt = v.apply_dual_transform_keys(K, lam, H), v.apply_dual_transform_queries(Q, lam, H)
+    s0 = torch.einsum("bhqd,bhsd->bhqs", Q, K.repeat_interleave(2, dim=1))
+    s1 = torch.einsum("bhqd,bhsd->bhqs", Qt, Kt.repeat_interleave(2, dim=1))
+    assert torch.allclose(s0, s1, rtol=1e-4, atol=1e-4)
+    with pytest.raises(ValueError, match="power of 2"):
+        v.walsh_hadamard_matrix(48)
+
+
+def _attend_case(rng, B, H_q, H_kv, S_q, S_kv, D=128, sub=8, n_c=256):
+    q = (rng.standard_normal((B, H_q, S_q, D)) * 0.3).astype(np.float32)
+    kcb = rng.standard_normal((n_c, sub)).astype(np.float32)
+    vcb = rng.standard_normal((n_c, sub)).astype(np.float32)
+    kidx = rng.integers(0, n_c, (B, H_kv, S_kv, D // sub)).astype(np.int32)
+    vidx = rng.integers(0, n_c, (B, H_kv, S_kv, D // sub)).astype(np.int32)
+    return q, kidx, kcb, vidx, vcb
+
+
+@pytest.mark.parametrize("causal,window", [(True, 0), (False, 0), (True, 64), (False, 16)])
+@pytest.mark.parametrize("H_q,H_kv,S_q,S_kv", [(4, 4, 1, 300), (32, 8, 1, 1000), (8, 2, 8, 129), (4, 4, 1, 1), (4, 2, 2, 2)])
+def test_fused_sdpa_vq_matches_oracle(causal, window, H_q, H_kv, S_q, S_kv):
+    rng = np.random.default_rng(H_q + S_kv + S_q)
+    q, kidx, kcb, vidx, vcb = _attend_case(rng, 2, H_q, H_kv, S_q, S_kv)
+    scale = 1.0 / math.sqrt(128)
+    ref = o_vq.reference_sdpa(q, kidx, kcb, vidx, scale, v_codebook=vcb, causal=causal, sliding_window=window)
+    t = lambda a: torch.from_numpy(a).to(DEV)  # noqa: E731
+    out = _v().metal_fused_sdpa(t(q), t(kidx), t(kcb), t(vidx), t(vcb), scale, causal=causal, sliding_window=window)
+    assert out.dtype == torch.float32 and out.shape == ref.shape
+    err = np.abs(out.cpu().numpy() - ref)
+    assert err.max() < 1e-2 and np.all(err <= 2e-3 + 1e-2 * np.abs(ref)), f"max err {err.max():.3e}"
+    # byte-wide indices and an explicit split count give the same answer
+    out8 = _v().fused_sdpa_vq(t(q), t(kidx).to(torch.uint8), t(kcb), t(vidx).to(torch.uint8), t(vcb), scale,
+                              causal=causal, sliding_window=window, n_splits=3)
+    assert np.abs(out8.cpu().numpy() - ref).max() < 1e-2
+
+
+def test_fused_sdpa_vq_long_context_dense_values_and_capacity():
+    """BASELINE config 2: VQ keys, fp16 values [8, 4096, 128], 32 query heads; buffers larger
+    than the live context."""
+    rng = np.random.default_rng(5)
+    v = _v()
+    S, cap = 4096, 4608
+    keys, k32 = _cast(rng.standard_normal((1, 8, S, 128)).astype(np.float32), "float16")
+    vals, v32 = _cast(rng.standard_normal((1, 8, S, 128)).astype(np.float32), "float16")
+    cb, cb32 = _cast(np.random.default_rng(42).standard_normal((256, 8)).astype(np.float32), "float16")
+    q, q32 = _cast(rng.standard_normal((1, 32, 1, 128)).astype(np.float32), "float16")
+    kidx = v.quantize_vq(keys, cb, 8, index_dtype=torch.uint8)
+    np.testing.assert_array_equal(kidx.cpu().numpy().astype(np.int32), o_vq.quantize_vq(k32, cb32, 8))
+    kbuf = torch.zeros((1, 8, cap, 16), dtype=torch.uint8, device=DEV)
+    vbuf = torch.zeros((1, 8, cap, 128), dtype=torch.float16, device=DEV)
+    kbuf[:, :, :S], vbuf[:, :, :S] = kidx, vals
+    scale = 1.0 / math.sqrt(128)
+    out = v.fused_sdpa_vq(q, kbuf, cb, vbuf, None, scale, s_kv=S, out_dtype=torch.float16)
+    ref = o_vq.reference_sdpa(q32, kidx.cpu().numpy(), cb32, v32, scale, causal=True)
+    err = np.abs(out.float().cpu().numpy() - ref)
+    assert np.all(err <= 2e-3 + 1e-2 * np.abs(ref)), f"max err {err.max():.3e}"
+    with pytest.raises(ValueError, match="multiple of H_kv"):
+        v.fused_sdpa_vq(q[:, :3], kbuf, cb, vbuf, None, scale, s_kv=S)
+    with pytest.raises(ValueError, match="must equal n_sub"):
+        v.fused_sdpa_vq(q, kbuf, cb[:, :4], vbuf, None, scale, s_kv=S)

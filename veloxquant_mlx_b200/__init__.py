@@ -6,7 +6,7 @@ the reference's ``KVCacheConfig(method=...)`` / cache / kernel-wrapper interface
 KIVI, VecInfer and RaBitQ paths. There is no CPU fallback.
 """
 
-from . import kernels  # noqa: F401
+from . import kernels, rabitq, vecinfer  # noqa: F401
 from ._lib import VQLibraryError, lib  # noqa: F401
 
 __version__ = "0.1.0"

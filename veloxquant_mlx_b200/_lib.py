@@ -64,6 +64,32 @@ class KiviAttendArgs(C.Structure):
     ]
 
 
+class VqAttendArgs(C.Structure):
+    _fields_ = [
+        ("q", C.c_void_p), ("out", C.c_void_p), ("q_dtype", C.c_int32), ("out_dtype", C.c_int32),
+        ("B", C.c_int32), ("H_q", C.c_int32), ("H_kv", C.c_int32), ("S_q", C.c_int32), ("S_kv", C.c_int32),
+        ("D", C.c_int32), ("kv_stride_tok", C.c_int64), ("scale", C.c_float),
+        ("causal", C.c_int32), ("sliding_window", C.c_int32),
+        ("k_indices", C.c_void_p), ("k_index_bytes", C.c_int32), ("k_codebook", C.c_void_p),
+        ("k_n_centroids", C.c_int32), ("k_sub_dim", C.c_int32), ("k_stacked", C.c_int32),
+        ("v_mode", C.c_int32), ("v", C.c_void_p), ("v_dtype", C.c_int32), ("v_index_bytes", C.c_int32),
+        ("v_codebook", C.c_void_p), ("v_n_centroids", C.c_int32), ("v_sub_dim", C.c_int32),
+        ("workspace", C.c_void_p), ("workspace_bytes", C.c_int64), ("n_splits", C.c_int32),
+    ]
+
+
+class RabitqAttendArgs(C.Structure):
+    _fields_ = [
+        ("q", C.c_void_p), ("out", C.c_void_p), ("q_dtype", C.c_int32), ("out_dtype", C.c_int32),
+        ("B", C.c_int32), ("H_q", C.c_int32), ("H_kv", C.c_int32), ("S_q", C.c_int32), ("S_kv", C.c_int32),
+        ("D", C.c_int32), ("kv_stride_tok", C.c_int64),
+        ("q_scale", C.c_void_p), ("k_bits", C.c_void_p), ("k_mag", C.c_void_p), ("k_const", C.c_void_p),
+        ("v_mode", C.c_int32), ("v", C.c_void_p), ("v_dtype", C.c_int32),
+        ("v_cents", C.c_void_p), ("n_cents", C.c_int32),
+        ("workspace", C.c_void_p), ("workspace_bytes", C.c_int64), ("n_splits", C.c_int32),
+    ]
+
+
 # name -> (restype, argtypes); every symbol include/vqb200.h declares.
 SIGNATURES = {
     "vq_version": (C.c_int32, []),
@@ -74,6 +100,19 @@ SIGNATURES = {
     "vq_kivi_decode_attend": (C.c_int32, [C.POINTER(KiviAttendArgs), C.c_void_p]),
     "vq_kivi_attend_status": (C.c_int32, []),
     "vq_kivi_decode_attend_static": (C.c_int32, [C.POINTER(KiviAttendArgs), C.c_void_p]),
+    "vq_vq_quantize": (C.c_int32, [C.c_void_p, C.c_int32, C.c_int64, C.c_int32, C.c_void_p, C.c_int32, C.c_int32,
+                                   C.c_void_p, C.c_int32, C.c_void_p]),
+    "vq_vq_dequant": (C.c_int32, [C.c_void_p, C.c_int32, C.c_int64, C.c_void_p, C.c_int32, C.c_int32, C.c_int32,
+                                  C.c_void_p, C.c_int32, C.c_void_p]),
+    "vq_vq_attend_workspace_bytes": (C.c_int64, [C.POINTER(VqAttendArgs)]),
+    "vq_vq_decode_attend": (C.c_int32, [C.POINTER(VqAttendArgs), C.c_void_p]),
+    "vq_rabitq_encode": (C.c_int32, [C.c_void_p, C.c_int32, C.c_int64, C.c_int32, C.c_void_p, C.c_int32,
+                                     C.c_void_p, C.c_void_p, C.c_void_p]),
+    "vq_rabitq_pack_values": (C.c_int32, [C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p]),
+    "vq_rabitq_hamming_score": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_int64, C.c_int32, C.c_float,
+                                            C.c_void_p, C.c_void_p, C.c_void_p]),
+    "vq_rabitq_attend_workspace_bytes": (C.c_int64, [C.POINTER(RabitqAttendArgs)]),
+    "vq_rabitq_decode_attend": (C.c_int32, [C.POINTER(RabitqAttendArgs), C.c_void_p]),
     "vq_bit_pack": (C.c_int32, [C.c_void_p, C.c_int64, C.c_int32, C.c_void_p, C.c_void_p]),
     "vq_bit_unpack": (C.c_int32, [C.c_void_p, C.c_int64, C.c_int32, C.c_void_p, C.c_void_p]),
 }

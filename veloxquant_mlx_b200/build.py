@@ -28,6 +28,9 @@ SOURCES = [
     ("kivi_attend.cu", []),
     ("kivi_attend_mma.cu", []),
     ("kivi_attend_static.cu", []),
+    ("vq_quant.cu", ["-fmad=false"]),
+    ("rabitq.cu", ["-fmad=false"]),
+    ("coded_attend.cu", []),
 ]
 
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]

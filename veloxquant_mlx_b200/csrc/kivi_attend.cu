@@ -162,6 +162,14 @@ __global__ void kivi_attend_merge_kernel(const float *__restrict__ part_o, const
     }
 }
 
+int32_t launch_split_merge(const float *part_o, const float *part_ml, int n_splits, int D, void *out,
+                           int out_dtype, int64_t rows, cudaStream_t st) {
+    VQ_REQUIRE(rows < (1ll << 31), VQ_ERR_SHAPE, "split merge: too many output rows");
+    kivi_attend_merge_kernel<<<(unsigned)rows, 128, 0, st>>>(part_o, part_ml, n_splits, D, out, out_dtype);
+    VQ_CHECK_LAUNCH("kivi_attend_merge_kernel");
+    return VQ_OK;
+}
+
 static int32_t validate(const vq_kivi_attend_args &a) {
     VQ_REQUIRE(a.B >= 1 && a.H_q >= 1 && a.H_kv >= 1 && a.S_q >= 1, VQ_ERR_SHAPE, "vq_kivi_decode_attend: B, H_q, H_kv, S_q must be >= 1");
     VQ_REQUIRE(a.D >= 1 && a.D <= 256, VQ_ERR_SHAPE, "vq_kivi_decode_attend: D=%d must be in 1..256", a.D);

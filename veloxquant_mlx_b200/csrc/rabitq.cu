@@ -1,0 +1,124 @@
+// RaBitQ 1-bit key encode (randomized Hadamard rotation + sign bits + L1 magnitude),
+// 4-bit value packing and the packed Hamming score.
+//
+// Encode: one warp per key row. The row (D <= 1024, a power of two) sits in shared memory;
+// the Sylvester butterfly pairs element i+j with i+j+stride exactly as the reference's
+// sequential loop does (lower = a+b, upper = a-b), so every stage is the same float32
+// operation on the same operands and the result is bit-identical however the pairs are
+// spread over lanes. Sign bits are packed with ballots (32 bits = 4 output bytes).
+#include <algorithm>
+
+#include "common.cuh"
+
+namespace vq {
+
+constexpr int kEncWarps = 4;
+
+template <typename T>
+__global__ void __launch_bounds__(kEncWarps * 32)
+rabitq_encode_kernel(const T *__restrict__ keys, int64_t n, int D, const float *__restrict__ diag,
+                     int rotate, uint8_t *__restrict__ bits, float *__restrict__ mag) {
+    extern __shared__ float sh[];  // [kEncWarps][D]
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    float *buf = sh + (size_t)warp * D;
+    const float inv_norm_den = sqrtf((float)D);
+    const int n_bytes = D / 8;
+    for (int64_t row = (int64_t)blockIdx.x * kEncWarps + warp; row < n; row += (int64_t)gridDim.x * kEncWarps) {
+        for (int i = lane; i < D; i += 32) {
+            float v = to_f32<T>(keys[row * D + i]);
+            if (rotate) v = __fmul_rn(v, diag[i]);
+            buf[i] = v;
+        }
+        __syncwarp();
+        if (rotate) {
+            for (int stride = 1; stride < D; stride <<= 1) {
+                // pair p (0..D/2-1): lower index = (p / stride) * 2 * stride + p % stride
+                for (int p = lane; p < D / 2; p += 32) {
+                    const int lo = (p / stride) * 2 * stride + (p % stride);
+                    const float a = buf[lo], b = buf[lo + stride];
+                    buf[lo] = __fadd_rn(a, b);
+                    buf[lo + stride] = __fsub_rn(a, b);
+                }
+                __syncwarp();
+            }
+        }
+        float l1 = 0.f;
+        for (int i0 = 0; i0 < D; i0 += 32) {
+            const int i = i0 + lane;
+            float y = 0.f;
+            bool live = i < D;
+            if (live) {
+                y = buf[i];
+                if (rotate) y = __fdiv_rn(y, inv_norm_den);
+                l1 += fabsf(y);
+            }
+            const uint32_t ballot = __ballot_sync(0xffffffffu, live && y >= 0.f);
+            if (lane < 4 && i0 / 8 + lane < n_bytes) bits[row * n_bytes + i0 / 8 + lane] = (uint8_t)(ballot >> (8 * lane));
+        }
+        l1 = warp_sum(l1);
+        if (lane == 0) mag[row] = l1 / (float)D;
+        __syncwarp();
+    }
+}
+
+__global__ void rabitq_pack_values_kernel(const uint8_t *__restrict__ v_idx, int64_t n_out,
+                                          uint8_t *__restrict__ packed) {
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n_out;
+         i += (int64_t)gridDim.x * blockDim.x)
+        packed[i] = (uint8_t)((v_idx[2 * i] & 0xF) | ((v_idx[2 * i + 1] & 0xF) << 4));
+}
+
+__global__ void rabitq_hamming_kernel(const uint8_t *__restrict__ q_bits, const uint8_t *__restrict__ bits,
+                                      int64_t n, int n_bytes, float scale, const float *__restrict__ cx,
+                                      float *__restrict__ score) {
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n;
+         i += (int64_t)gridDim.x * blockDim.x) {
+        int ham = 0;
+        for (int j = 0; j < n_bytes; ++j) ham += __popc((uint32_t)(q_bits[j] ^ bits[i * n_bytes + j]));
+        score[i] = __fadd_rn(__fmul_rn((float)ham, scale), cx ? cx[i] : 0.f);
+    }
+}
+
+}  // namespace vq
+
+extern "C" int32_t vq_rabitq_encode(const void *keys, int32_t dtype, int64_t n, int32_t D, const float *diag,
+                                    int32_t rotate, uint8_t *bits, float *mag, void *stream) {
+    using namespace vq;
+    VQ_REQUIRE(n >= 0, VQ_ERR_SHAPE, "rabitq_encode: n must be >= 0");
+    VQ_REQUIRE(D >= 8 && D <= 1024 && D % 8 == 0, VQ_ERR_SHAPE, "rabitq_encode: D=%d must be a multiple of 8 in 8..1024", D);
+    VQ_REQUIRE(!rotate || (D & (D - 1)) == 0, VQ_ERR_SHAPE, "rabitq_encode: D=%d must be a power of 2 for the Hadamard rotation", D);
+    VQ_REQUIRE(!rotate || diag != nullptr, VQ_ERR_SHAPE, "rabitq_encode: diag is NULL");
+    if (n == 0) return VQ_OK;
+    const unsigned blocks = (unsigned)std::min<int64_t>(ceil_div(n, kEncWarps), 148 * 16);
+    const size_t smem = (size_t)kEncWarps * D * sizeof(float);
+    cudaStream_t st = (cudaStream_t)stream;
+    switch (dtype) {
+        case VQ_F16: rabitq_encode_kernel<__half><<<blocks, kEncWarps * 32, smem, st>>>((const __half *)keys, n, D, diag, rotate, bits, mag); break;
+        case VQ_BF16: rabitq_encode_kernel<__nv_bfloat16><<<blocks, kEncWarps * 32, smem, st>>>((const __nv_bfloat16 *)keys, n, D, diag, rotate, bits, mag); break;
+        case VQ_F32: rabitq_encode_kernel<float><<<blocks, kEncWarps * 32, smem, st>>>((const float *)keys, n, D, diag, rotate, bits, mag); break;
+        default: return fail(VQ_ERR_DTYPE, "rabitq_encode: unknown dtype %d", dtype);
+    }
+    VQ_CHECK_LAUNCH("rabitq_encode_kernel");
+    return VQ_OK;
+}
+
+extern "C" int32_t vq_rabitq_pack_values(const uint8_t *v_idx, int64_t n_out, uint8_t *packed, void *stream) {
+    using namespace vq;
+    VQ_REQUIRE(n_out >= 0, VQ_ERR_SHAPE, "rabitq_pack_values: n_out must be >= 0");
+    if (n_out == 0) return VQ_OK;
+    const unsigned blocks = (unsigned)std::min<int64_t>(ceil_div(n_out, 256), 148 * 16);
+    rabitq_pack_values_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>(v_idx, n_out, packed);
+    VQ_CHECK_LAUNCH("rabitq_pack_values_kernel");
+    return VQ_OK;
+}
+
+extern "C" int32_t vq_rabitq_hamming_score(const uint8_t *q_bits, const uint8_t *bits, int64_t n, int32_t n_bytes,
+                                           float scale, const float *cx, float *score, void *stream) {
+    using namespace vq;
+    VQ_REQUIRE(n >= 0 && n_bytes >= 1, VQ_ERR_SHAPE, "rabitq_hamming_score: bad sizes");
+    if (n == 0) return VQ_OK;
+    const unsigned blocks = (unsigned)std::min<int64_t>(ceil_div(n, 256), 148 * 16);
+    rabitq_hamming_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>(q_bits, bits, n, n_bytes, scale, cx, score);
+    VQ_CHECK_LAUNCH("rabitq_hamming_kernel");
+    return VQ_OK;
+}
