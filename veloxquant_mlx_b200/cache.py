@@ -582,5 +582,7 @@ class KIVIKVCache:
 
 _CACHE_CLASS_BY_METHOD["kivi"] = KIVIKVCache
 
+from .cache_coded import RaBitQKVCache, VecInferKVCache  # noqa: E402  (registers "vecinfer", "rabitq")
+
 __all__ = ["QuantizerConfigError", "VecInferOptions", "KIVIOptions", "KVCacheConfig", "KVCacheFactory",
-           "KVCacheBuilder", "KIVIKVCache"]
+           "KVCacheBuilder", "KIVIKVCache", "VecInferKVCache", "RaBitQKVCache"]
