@@ -168,6 +168,15 @@ class ClockSampler:
                 "power_w_max": max(power) if power else None, "samples": len(sm), "reasons": sorted(reasons)}
 
 
+def ncu_traffic(w):
+    """dram__bytes_read.sum + dram__bytes_write.sum of one launch of the attend kernel, from
+    the ncu capture summarised in profiles/kivi_attend_mma_llama8b_decode.md (same per-layer
+    shape as the default workload); None for shapes that were not captured."""
+    if (w["batch"], w["ctx"], w["H_kv"], w["H_q"], w["D"], w["group"], w["residual"]) != (16, 32768, 8, 32, 128, 32, 128):
+        return None
+    return {4: 810_957_824 + 6_123_520, 2: 543_347_200 + 5_460_736}.get(w["bits"])
+
+
 def measured_peak():
     p = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(p):
@@ -401,7 +410,7 @@ def run_ours(args):
             "tokens_per_s": world * B / (ms_step * 1e-3),
             "pct_of_hbm_peak": 100.0 * (value / world) / peak,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                         "peak_kind": peak_kind + " (burst copy)", "traffic": None,
+                         "peak_kind": peak_kind + " (burst copy)", "traffic": ncu_traffic(w),
                          "kernel": f"kivi_attend_mma_kernel<{w['bits']}> (+ merge; duration = step time / layers)",
                          "algorithmic_bytes_per_launch": bytes_layer},
             "cpu_baseline": cpu,
