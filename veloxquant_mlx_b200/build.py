@@ -25,6 +25,7 @@ SOURCES = [
     ("api.cu", []),
     ("bitpack.cu", []),
     ("kivi_quant.cu", ["-fmad=false"]),
+    ("kivi_quant_tile.cu", ["-fmad=false"]),
     ("kivi_attend.cu", []),
     ("kivi_attend_mma.cu", []),
     ("kivi_attend_static.cu", []),

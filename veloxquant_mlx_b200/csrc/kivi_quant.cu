@@ -13,6 +13,7 @@
 #include <algorithm>
 
 #include "common.cuh"
+#include "kivi_quant_tile.h"
 
 namespace vq {
 
@@ -217,6 +218,7 @@ extern "C" int32_t vq_kivi_quantize(const vq_kivi_quant_args *args, void *stream
     if (a.n_bh == 0 || a.n_tok == 0) return VQ_OK;
     VQ_REQUIRE(a.x != nullptr, VQ_ERR_SHAPE, "vq_kivi_quantize: x is NULL");
     cudaStream_t st = (cudaStream_t)stream;
+    if (kivi_quant_tile_supported(a)) return kivi_quant_tile_launch(a, st);
     switch (a.dtype) {
         case VQ_F16: return launch_quant<__half>(a, st);
         case VQ_BF16: return launch_quant<__nv_bfloat16>(a, st);
