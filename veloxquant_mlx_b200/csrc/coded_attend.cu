@@ -3,11 +3,11 @@
 //   RaBitQ   : score = (D - 2*popcount(sign(q) ^ bits[t])) * q_scale * k_mag[t] + k_const[t]
 // Both read a few bytes per key (16 B at D=128) so the value stream dominates the traffic.
 //
-// One CTA per (context split, kv head x query row, batch); one warp per query head of the
-// kv head (GQA heads share the CTA so the value rows they all read hit L1). Within a warp a
-// lane owns one key of a 32-key tile for scoring, then owns D/32 output channels for the
-// value accumulation (the tile's weights are broadcast with shuffles). Online softmax per
-// warp; context splits are merged by the shared split-merge kernel.
+// One CTA per (context split, kv head x query row, batch) handles every query head of the kv
+// head (GQA): a key code is loaded once and scored against all heads, a value row is loaded
+// once and accumulated into all heads. A lane owns one key of a 32-key tile for scoring,
+// then D/32 output channels for the value accumulation (weights broadcast with shuffles).
+// Online softmax per warp and head; warps, then context splits, are merged afterwards.
 #include <algorithm>
 
 #include "common.cuh"
@@ -17,8 +17,6 @@ namespace vq {
 
 namespace {
 
-constexpr int kMaxWarps = 16;
-constexpr int kMaxDpl = 8;  // D <= 256
 
 enum { KEY_VQ = 0, KEY_RABITQ = 1 };
 enum { V_DENSE = 0, V_VQ = 1, V_CENT_BYTE = 2, V_CENT_NIBBLE = 3 };
@@ -42,9 +40,64 @@ __device__ __forceinline__ uint32_t load_index(const void *p, int bytes, int64_t
     return reinterpret_cast<const uint32_t *>(p)[i];
 }
 
-__global__ void __launch_bounds__(kMaxWarps * 32)
+constexpr int kWarpsC = 8;    // warps per CTA; each takes every 8th 32-key tile of the split
+constexpr int kHeadsC = 8;    // query heads of one kv head handled by one CTA
+
+// Fetch DPL consecutive value channels [lane*DPL, +DPL) of token `tok` as floats.
+template <int DPL>
+__device__ __forceinline__ void load_v_row(const CodedParams &p, int64_t tok, int lane, float (&v)[DPL]) {
+    const int D = p.D;
+    if (p.v_mode == V_DENSE) {
+        if (p.v_dtype == VQ_F32) {
+#pragma unroll
+            for (int i = 0; i < DPL; ++i) v[i] = reinterpret_cast<const float *>(p.v)[tok * D + lane * DPL + i];
+        } else if constexpr (DPL % 2 == 0) {
+            const uint32_t *src = reinterpret_cast<const uint32_t *>(reinterpret_cast<const uint16_t *>(p.v) + tok * D + lane * DPL);
+#pragma unroll
+            for (int i = 0; i < DPL / 2; ++i) {
+                const uint32_t w = src[i];
+                if (p.v_dtype == VQ_F16) {
+                    const float2 f = __half22float2(*reinterpret_cast<const __half2 *>(&w));
+                    v[2 * i] = f.x; v[2 * i + 1] = f.y;
+                } else {
+                    v[2 * i] = __uint_as_float(w << 16); v[2 * i + 1] = __uint_as_float(w & 0xffff0000u);
+                }
+            }
+        } else {
+#pragma unroll
+            for (int i = 0; i < DPL; ++i) v[i] = load_as_f32(p.v, p.v_dtype, tok * D + lane * DPL + i);
+        }
+    } else if (p.v_mode == V_VQ) {
+        const int nsv = D / p.v_sub;
+#pragma unroll
+        for (int i = 0; i < DPL; ++i) {
+            const int dim = lane * DPL + i;
+            uint32_t c = load_index(p.v, p.v_index_bytes, tok * nsv + dim / p.v_sub);
+            c = min(c, (uint32_t)(p.v_nc - 1));
+            v[i] = p.v_codebook[(int64_t)c * p.v_sub + dim % p.v_sub];
+        }
+    } else if (p.v_mode == V_CENT_BYTE) {
+#pragma unroll
+        for (int i = 0; i < DPL; ++i) v[i] = p.v_codebook[reinterpret_cast<const uint8_t *>(p.v)[tok * D + lane * DPL + i] & 0xF];
+    } else {
+#pragma unroll
+        for (int i = 0; i < DPL; ++i) {
+            const int dim = lane * DPL + i;
+            const uint32_t byte = reinterpret_cast<const uint8_t *>(p.v)[tok * (D / 2) + (dim >> 1)];
+            v[i] = p.v_codebook[(dim & 1) ? (byte >> 4) : (byte & 0xFu)];
+        }
+    }
+}
+
+// One CTA: (context split, kv head x query row x head chunk, batch). All (<= 8) query heads of
+// the kv head are handled together: a key's code is loaded once and scored against every
+// head, a value row is loaded once and accumulated into every head. Warps take alternate
+// 32-key tiles of the split; value rows are fetched eight at a time so that eight
+// independent loads are in flight per lane.
+template <int DPL>
+__global__ void __launch_bounds__(kWarpsC * 32)
 coded_attend_kernel(const CodedParams p) {
-    extern __shared__ float sh_lut[];  // VQ: [warps][n_sub * n_c]; RaBitQ: unused
+    extern __shared__ float smem[];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int split = blockIdx.x;
     int y = blockIdx.y;
@@ -53,129 +106,167 @@ coded_attend_kernel(const CodedParams p) {
     const int hkv = y / p.S_q;
     const int b = blockIdx.z;
     const int hpk = p.H_q / p.H_kv;
-    const int hp = hc * p.heads_per_cta + warp;  // head within the kv group
-    const bool head_live = hp < hpk;
-    const int hq = hkv * hpk + (head_live ? hp : 0);
-    const int D = p.D, dpl = D / 32;
+    const int h0 = hc * kHeadsC;
+    const int nh = min(kHeadsC, hpk - h0);
+    const int D = p.D;
     const int64_t bh = (int64_t)b * p.H_kv + hkv;
-    const int64_t qrow = ((int64_t)b * p.H_q + hq) * p.S_q + sq;
-
-    // ---- per-warp query state -----------------------------------------------------------
     const int n_sub = p.key_mode == KEY_VQ ? D / p.k_sub : 0;
-    float *lut = sh_lut + (size_t)warp * n_sub * p.k_nc;
-    uint32_t qbits[8];  // RaBitQ: sign bits of q, 32 per word
-    float qs = 0.f;
+    const int lut_stride = n_sub * p.k_nc;
+
+    // shared: VQ lookup tables [nh][n_sub*n_c] | RaBitQ: query sign words [nh][8] and scales [nh]
+    float *lut = smem;
+    uint32_t *sh_qbits = reinterpret_cast<uint32_t *>(smem);
+    float *sh_qs = smem + kHeadsC * 8;
     if (p.key_mode == KEY_VQ) {
-        if (head_live) {
-            for (int i = lane; i < n_sub * p.k_nc; i += 32) {
-                const int s = i / p.k_nc, c = i % p.k_nc;
-                const float *cb = p.k_codebook + ((int64_t)(p.k_stacked ? s : 0) * p.k_nc + c) * p.k_sub;
-                float dot = 0.f;
-                for (int e = 0; e < p.k_sub; ++e) dot += load_as_f32(p.q, p.q_dtype, qrow * D + s * p.k_sub + e) * cb[e];
-                lut[i] = dot;
-            }
+        for (int i = threadIdx.x; i < nh * lut_stride; i += blockDim.x) {
+            const int hp = i / lut_stride, r = i % lut_stride;
+            const int s = r / p.k_nc, c = r % p.k_nc;
+            const int64_t qrow = ((int64_t)b * p.H_q + hkv * hpk + h0 + hp) * p.S_q + sq;
+            const float *cb = p.k_codebook + ((int64_t)(p.k_stacked ? s : 0) * p.k_nc + c) * p.k_sub;
+            float dot = 0.f;
+            for (int e = 0; e < p.k_sub; ++e) dot += load_as_f32(p.q, p.q_dtype, qrow * D + s * p.k_sub + e) * cb[e];
+            lut[i] = dot;
         }
-        __syncwarp();
-    } else {
+    } else if (warp < nh) {
+        const int64_t qrow = ((int64_t)b * p.H_q + hkv * hpk + h0 + warp) * p.S_q + sq;
 #pragma unroll
         for (int w = 0; w < 8; ++w) {
-            float v = (32 * w + lane < D) ? load_as_f32(p.q, p.q_dtype, qrow * D + 32 * w + lane) : -1.f;
-            qbits[w] = __ballot_sync(0xffffffffu, v >= 0.f);
+            const float v = (32 * w + lane < D) ? load_as_f32(p.q, p.q_dtype, qrow * D + 32 * w + lane) : -1.f;
+            const uint32_t bits = __ballot_sync(0xffffffffu, v >= 0.f);
+            if (lane == 0) sh_qbits[warp * 8 + w] = bits;
         }
-        qs = p.q_scale[qrow];
+        if (lane == 0) sh_qs[warp] = p.q_scale[qrow];
     }
+    __syncthreads();
 
     const int chunk = (p.S_kv + p.n_splits - 1) / p.n_splits;
     const int t_begin = split * chunk;
     const int t_end = min(p.S_kv, t_begin + chunk);
     const int q_abs = p.S_kv - p.S_q + sq;
+    const int n_words = D / 32;
 
-    float m_run = -INFINITY, l_run = 0.f, acc[kMaxDpl];
+    float m_run[kHeadsC], l_run[kHeadsC], acc[kHeadsC][DPL];
 #pragma unroll
-    for (int i = 0; i < kMaxDpl; ++i) acc[i] = 0.f;
+    for (int h = 0; h < kHeadsC; ++h) {
+        m_run[h] = -INFINITY; l_run[h] = 0.f;
+#pragma unroll
+        for (int i = 0; i < DPL; ++i) acc[h][i] = 0.f;
+    }
 
-    if (head_live) {
-        for (int tile = t_begin; tile < t_end; tile += 32) {
-            const int t = tile + lane;
-            bool valid = t < t_end;
-            if (valid && p.causal && t > q_abs) valid = false;
-            if (valid && p.window > 0 && q_abs + 1 > p.window && t + p.window < q_abs + 1) valid = false;
-            float score = -INFINITY;
-            if (valid) {
-                const int64_t tok = bh * p.stride_tok + t;
-                if (p.key_mode == KEY_VQ) {
-                    float s = 0.f;
-                    for (int sub = 0; sub < n_sub; ++sub) {
-                        uint32_t c = load_index(p.k_codes, p.k_index_bytes, tok * n_sub + sub);
-                        c = min(c, (uint32_t)(p.k_nc - 1));
-                        s += lut[sub * p.k_nc + c];
-                    }
-                    score = s * p.scale;
-                } else {
-                    const uint32_t *kb = reinterpret_cast<const uint32_t *>(
-                        reinterpret_cast<const uint8_t *>(p.k_codes) + tok * (D / 8));
-                    int ham = 0;
-                    if ((D & 31) == 0) {
+    for (int tile = t_begin + 32 * warp; tile < t_end; tile += 32 * kWarpsC) {
+        const int t = tile + lane;
+        bool valid = t < t_end;
+        if (valid && p.causal && t > q_abs) valid = false;
+        if (valid && p.window > 0 && q_abs + 1 > p.window && t + p.window < q_abs + 1) valid = false;
+        const int64_t tok = bh * p.stride_tok + (valid ? t : t_begin);
+        float w[kHeadsC];
+        // ---- scores of this lane's key against every head ---------------------------------
+        if (p.key_mode == KEY_VQ) {
 #pragma unroll
-                        for (int w = 0; w < 8; ++w)
-                            if (32 * w < D) ham += __popc(qbits[w] ^ kb[w]);
-                    } else {
-                        const uint8_t *kbb = reinterpret_cast<const uint8_t *>(kb);
-                        for (int j = 0; j < D / 8; ++j)
-                            ham += __popc(((qbits[j >> 2] >> (8 * (j & 3))) & 0xffu) ^ (uint32_t)kbb[j]);
-                    }
-                    score = ((float)D - 2.0f * (float)ham) * qs * p.k_mag[tok] + (p.k_const ? p.k_const[tok] : 0.f);
-                }
+            for (int h = 0; h < kHeadsC; ++h) w[h] = 0.f;
+            for (int sub = 0; sub < n_sub; ++sub) {
+                uint32_t c = load_index(p.k_codes, p.k_index_bytes, tok * n_sub + sub);
+                c = min(c, (uint32_t)(p.k_nc - 1));
+                const float *row = lut + sub * p.k_nc + c;
+#pragma unroll
+                for (int h = 0; h < kHeadsC; ++h)
+                    if (h < nh) w[h] += row[h * lut_stride];
             }
-            const float tile_max = warp_max(score);
-            if (tile_max == -INFINITY) continue;  // whole tile masked
-            const float m_new = fmaxf(m_run, tile_max);
-            const float factor = (m_run == -INFINITY) ? 0.f : __expf(m_run - m_new);
-            m_run = m_new;
-            const float w = valid ? __expf(score - m_new) : 0.f;
-            l_run = l_run * factor + warp_sum(w);
 #pragma unroll
-            for (int i = 0; i < kMaxDpl; ++i) acc[i] *= factor;
-            const int n_in_tile = min(32, t_end - tile);
-            for (int l = 0; l < n_in_tile; ++l) {
-                const float wl = __shfl_sync(0xffffffffu, w, l);
-                if (wl == 0.f) continue;
-                const int64_t tok = bh * p.stride_tok + tile + l;
+            for (int h = 0; h < kHeadsC; ++h) w[h] = valid ? w[h] * p.scale : -INFINITY;
+        } else {
+            const uint32_t *kb = reinterpret_cast<const uint32_t *>(reinterpret_cast<const uint8_t *>(p.k_codes) + tok * (D / 8));
+            uint32_t kw[8];
 #pragma unroll
-                for (int i = 0; i < kMaxDpl; ++i) {
-                    if (i < dpl) {
-                        const int dim = lane * dpl + i;
-                        float vv;
-                        if (p.v_mode == V_DENSE) {
-                            vv = load_as_f32(p.v, p.v_dtype, tok * D + dim);
-                        } else if (p.v_mode == V_VQ) {
-                            const int nsv = D / p.v_sub;
-                            uint32_t c = load_index(p.v, p.v_index_bytes, tok * nsv + dim / p.v_sub);
-                            c = min(c, (uint32_t)(p.v_nc - 1));
-                            vv = p.v_codebook[(int64_t)c * p.v_sub + dim % p.v_sub];
-                        } else if (p.v_mode == V_CENT_BYTE) {
-                            vv = p.v_codebook[reinterpret_cast<const uint8_t *>(p.v)[tok * D + dim] & 0xF];
-                        } else {
-                            const uint32_t byte = reinterpret_cast<const uint8_t *>(p.v)[tok * (D / 2) + (dim >> 1)];
-                            vv = p.v_codebook[(dim & 1) ? (byte >> 4) : (byte & 0xFu)];
-                        }
-                        acc[i] = fmaf(wl, vv, acc[i]);
+            for (int i = 0; i < 8; ++i) kw[i] = i < n_words ? kb[i] : 0u;
+            const float km = p.k_mag[tok];
+            const float kc = p.k_const ? p.k_const[tok] : 0.f;
+#pragma unroll
+            for (int h = 0; h < kHeadsC; ++h) {
+                int ham = 0;
+#pragma unroll
+                for (int i = 0; i < 8; ++i)
+                    if (i < n_words) ham += __popc(sh_qbits[(h < nh ? h : 0) * 8 + i] ^ kw[i]);
+                const float s = ((float)D - 2.0f * (float)ham) * sh_qs[h < nh ? h : 0] * km + kc;
+                w[h] = valid ? s : -INFINITY;
+            }
+        }
+        // ---- online softmax per head ------------------------------------------------------
+        bool any_live = false;
+#pragma unroll
+        for (int h = 0; h < kHeadsC; ++h) {
+            if (h < nh) {
+                const float tile_max = warp_max(w[h]);
+                if (tile_max == -INFINITY) { w[h] = 0.f; continue; }
+                any_live = true;
+                const float m_new = fmaxf(m_run[h], tile_max);
+                const float factor = (m_run[h] == -INFINITY) ? 0.f : __expf(m_run[h] - m_new);
+                m_run[h] = m_new;
+                w[h] = valid ? __expf(w[h] - m_new) : 0.f;
+                l_run[h] = l_run[h] * factor + warp_sum(w[h]);
+#pragma unroll
+                for (int i = 0; i < DPL; ++i) acc[h][i] *= factor;
+            } else {
+                w[h] = 0.f;
+            }
+        }
+        if (!any_live) continue;
+        // ---- values: eight rows in flight, each accumulated into every head ----------------
+        const int n_in_tile = min(32, t_end - tile);
+        for (int l0 = 0; l0 < n_in_tile; l0 += 8) {
+            float vrow[8][DPL];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const int tl = min(l0 + j, n_in_tile - 1);  // rows past the end get weight 0
+                load_v_row<DPL>(p, bh * p.stride_tok + tile + tl, lane, vrow[j]);
+            }
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+#pragma unroll
+                for (int h = 0; h < kHeadsC; ++h) {
+                    if (h < nh) {
+                        const float wl = (l0 + j < n_in_tile) ? __shfl_sync(0xffffffffu, w[h], l0 + j) : 0.f;
+#pragma unroll
+                        for (int i = 0; i < DPL; ++i) acc[h][i] = fmaf(wl, vrow[j][i], acc[h][i]);
                     }
                 }
             }
         }
+    }
+
+    // ---- merge the warps of this CTA -------------------------------------------------------
+    __syncthreads();  // the lookup tables are dead: reuse shared memory
+    float *red_o = smem;                                   // [warps][heads][D]
+    float *red_m = red_o + kWarpsC * kHeadsC * D;          // [warps][heads]
+    float *red_l = red_m + kWarpsC * kHeadsC;
+#pragma unroll
+    for (int h = 0; h < kHeadsC; ++h) {
+        if (h < nh) {
+#pragma unroll
+            for (int i = 0; i < DPL; ++i) red_o[(warp * kHeadsC + h) * D + lane * DPL + i] = acc[h][i];
+            if (lane == 0) { red_m[warp * kHeadsC + h] = m_run[h]; red_l[warp * kHeadsC + h] = l_run[h]; }
+        }
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < nh * D; i += blockDim.x) {
+        const int h = i / D, d = i % D;
+        float gm = -INFINITY;
+        for (int wq = 0; wq < kWarpsC; ++wq) gm = fmaxf(gm, red_m[wq * kHeadsC + h]);
+        float gl = 0.f, o = 0.f;
+        for (int wq = 0; wq < kWarpsC; ++wq) {
+            const float mw = red_m[wq * kHeadsC + h];
+            const float f = (mw == -INFINITY) ? 0.f : __expf(mw - gm);
+            gl += red_l[wq * kHeadsC + h] * f;
+            o += red_o[(wq * kHeadsC + h) * D + d] * f;
+        }
+        const int64_t qrow = ((int64_t)b * p.H_q + hkv * hpk + h0 + h) * p.S_q + sq;
         if (p.n_splits == 1) {
-            const float inv = 1.0f / fmaxf(l_run, 1e-20f);
-#pragma unroll
-            for (int i = 0; i < kMaxDpl; ++i)
-                if (i < dpl) store_from_f32(p.out, p.out_dtype, qrow * D + lane * dpl + i, acc[i] * inv);
+            store_from_f32(p.out, p.out_dtype, qrow * D + d, o / fmaxf(gl, 1e-20f));
         } else {
-#pragma unroll
-            for (int i = 0; i < kMaxDpl; ++i)
-                if (i < dpl) p.part_o[(qrow * p.n_splits + split) * D + lane * dpl + i] = acc[i];
-            if (lane == 0) {
-                p.part_ml[(qrow * p.n_splits + split) * 2] = m_run;
-                p.part_ml[(qrow * p.n_splits + split) * 2 + 1] = l_run;
+            p.part_o[(qrow * p.n_splits + split) * D + d] = o;
+            if (d == 0) {
+                p.part_ml[(qrow * p.n_splits + split) * 2] = gm;
+                p.part_ml[(qrow * p.n_splits + split) * 2 + 1] = gl;
             }
         }
     }
@@ -199,11 +290,10 @@ int32_t launch_coded(CodedParams &p, void *workspace, int64_t workspace_bytes, i
     const int hpk = p.H_q / p.H_kv;
     size_t lut_bytes = 0;
     if (p.key_mode == KEY_VQ) lut_bytes = (size_t)(p.D / p.k_sub) * p.k_nc * sizeof(float);
-    int heads_per_cta = std::min(hpk, kMaxWarps);
-    if (lut_bytes) heads_per_cta = (int)std::max<size_t>(1, std::min<size_t>(heads_per_cta, (160 * 1024) / lut_bytes));
-    VQ_REQUIRE(lut_bytes <= 200 * 1024, VQ_ERR_CAPACITY, "%s: lookup table of %zu bytes does not fit shared memory", who, lut_bytes);
-    p.heads_per_cta = heads_per_cta;
-    p.n_head_chunks = (int)ceil_div(hpk, heads_per_cta);
+    VQ_REQUIRE(lut_bytes * std::min(hpk, kHeadsC) <= 200 * 1024, VQ_ERR_CAPACITY,
+               "%s: lookup tables of %zu bytes per head do not fit shared memory", who, lut_bytes);
+    p.heads_per_cta = kHeadsC;
+    p.n_head_chunks = (int)ceil_div(hpk, kHeadsC);
     const int64_t gy = (int64_t)p.H_kv * p.S_q * p.n_head_chunks;
     VQ_REQUIRE(gy <= 65535 && p.B <= 65535, VQ_ERR_SHAPE, "%s: grid too large", who);
     p.n_splits = pick_splits(requested_splits, p.S_kv, gy * p.B, di.sm_count);
@@ -215,11 +305,21 @@ int32_t launch_coded(CodedParams &p, void *workspace, int64_t workspace_bytes, i
         p.part_o = (float *)workspace;
         p.part_ml = p.part_o + rows * p.n_splits * p.D;
     }
-    const size_t smem = lut_bytes * heads_per_cta;
-    if (smem > 48 * 1024)
-        VQ_CHECK_CUDA(cudaFuncSetAttribute(coded_attend_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    const size_t red_bytes = ((size_t)kWarpsC * kHeadsC * p.D + 2 * kWarpsC * kHeadsC) * sizeof(float);
+    const size_t smem = std::max(red_bytes, std::max(lut_bytes * std::min(hpk, kHeadsC), (size_t)(kHeadsC * 9 * 4)));
     dim3 grid(p.n_splits, (unsigned)gy, p.B);
-    coded_attend_kernel<<<grid, heads_per_cta * 32, smem, st>>>(p);
+#define VQ_CODED(DPL)                                                                                     \
+    case DPL:                                                                                             \
+        if (smem > 48 * 1024)                                                                             \
+            VQ_CHECK_CUDA(cudaFuncSetAttribute(coded_attend_kernel<DPL>,                                   \
+                                               cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));  \
+        coded_attend_kernel<DPL><<<grid, kWarpsC * 32, smem, st>>>(p);                                    \
+        break;
+    switch (p.D / 32) {
+        VQ_CODED(1) VQ_CODED(2) VQ_CODED(3) VQ_CODED(4) VQ_CODED(5) VQ_CODED(6) VQ_CODED(7) VQ_CODED(8)
+        default: return fail(VQ_ERR_SHAPE, "%s: unsupported head_dim %d", who, p.D);
+    }
+#undef VQ_CODED
     VQ_CHECK_LAUNCH("coded_attend_kernel");
     if (p.n_splits > 1) return launch_split_merge(p.part_o, p.part_ml, p.n_splits, p.D, p.out, p.out_dtype, rows, st);
     return VQ_OK;

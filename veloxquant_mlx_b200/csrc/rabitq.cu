@@ -61,6 +61,70 @@ rabitq_encode_kernel(const T *__restrict__ keys, int64_t n, int D, const float *
     }
 }
 
+// Register-resident variant for D = 32 * EPL (32, 64, 128, 256): lane l holds elements
+// EPL*l .. EPL*l + EPL-1. Butterfly stages with stride < EPL pair registers of one lane;
+// larger strides pair lane l with lane l ^ (stride / EPL) through a shuffle. Every pair is
+// still (lower + upper, lower - upper), so the result is bit-identical to the shared-memory
+// kernel and to the reference's sequential loop.
+template <typename T, int EPL>
+__global__ void __launch_bounds__(128)
+rabitq_encode_reg_kernel(const T *__restrict__ keys, int64_t n, const float *__restrict__ diag, int rotate,
+                         uint8_t *__restrict__ bits, float *__restrict__ mag) {
+    constexpr int D = 32 * EPL;
+    const int lane = threadIdx.x & 31;
+    const int64_t warp_id = (int64_t)blockIdx.x * 4 + (threadIdx.x >> 5);
+    const int64_t n_warps = (int64_t)gridDim.x * 4;
+    float dg[EPL];
+#pragma unroll
+    for (int j = 0; j < EPL; ++j) dg[j] = rotate ? diag[EPL * lane + j] : 1.f;
+    const float den = sqrtf((float)D);
+    for (int64_t row = warp_id; row < n; row += n_warps) {
+        float v[EPL];
+#pragma unroll
+        for (int j = 0; j < EPL; ++j) v[j] = to_f32<T>(keys[row * D + EPL * lane + j]);
+        if (rotate) {
+#pragma unroll
+            for (int j = 0; j < EPL; ++j) v[j] = __fmul_rn(v[j], dg[j]);
+#pragma unroll
+            for (int s = 1; s < EPL; s <<= 1) {
+#pragma unroll
+                for (int j = 0; j < EPL; ++j) {
+                    if ((j & s) == 0) {
+                        const float a = v[j], b2 = v[j + s];
+                        v[j] = __fadd_rn(a, b2);
+                        v[j + s] = __fsub_rn(a, b2);
+                    }
+                }
+            }
+#pragma unroll
+            for (int m = 1; m < 32; m <<= 1) {
+                const bool upper = lane & m;
+#pragma unroll
+                for (int j = 0; j < EPL; ++j) {
+                    const float other = __shfl_xor_sync(0xffffffffu, v[j], m);
+                    v[j] = upper ? __fsub_rn(other, v[j]) : __fadd_rn(v[j], other);
+                }
+            }
+#pragma unroll
+            for (int j = 0; j < EPL; ++j) v[j] = __fdiv_rn(v[j], den);
+        }
+        float l1 = 0.f;
+        uint32_t mine = 0;
+#pragma unroll
+        for (int j = 0; j < EPL; ++j) {
+            l1 += fabsf(v[j]);
+            mine |= (v[j] >= 0.f ? 1u : 0u) << j;
+        }
+        constexpr int LPW = 32 / EPL;  // lanes per 32-bit output word
+        uint32_t word = mine << (EPL * (lane % LPW));
+#pragma unroll
+        for (int m = 1; m < LPW; m <<= 1) word |= __shfl_xor_sync(0xffffffffu, word, m);
+        if (lane % LPW == 0) reinterpret_cast<uint32_t *>(bits + row * (D / 8))[lane / LPW] = word;
+        l1 = warp_sum(l1);
+        if (lane == 0) mag[row] = l1 / (float)D;
+    }
+}
+
 __global__ void rabitq_pack_values_kernel(const uint8_t *__restrict__ v_idx, int64_t n_out,
                                           uint8_t *__restrict__ packed) {
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n_out;
@@ -89,9 +153,30 @@ extern "C" int32_t vq_rabitq_encode(const void *keys, int32_t dtype, int64_t n, 
     VQ_REQUIRE(!rotate || (D & (D - 1)) == 0, VQ_ERR_SHAPE, "rabitq_encode: D=%d must be a power of 2 for the Hadamard rotation", D);
     VQ_REQUIRE(!rotate || diag != nullptr, VQ_ERR_SHAPE, "rabitq_encode: diag is NULL");
     if (n == 0) return VQ_OK;
+    cudaStream_t st = (cudaStream_t)stream;
+    if ((D == 32 || D == 64 || D == 128 || D == 256) && is_aligned(bits, 4)) {
+        const unsigned rb = (unsigned)std::min<int64_t>(ceil_div(n, 4), 148 * 32);
+#define VQ_ENC(TT, EPL) rabitq_encode_reg_kernel<TT, EPL><<<rb, 128, 0, st>>>((const TT *)keys, n, diag, rotate, bits, mag)
+#define VQ_ENC_D(TT)                                                                   \
+    switch (D) {                                                                       \
+        case 32: VQ_ENC(TT, 1); break;                                                 \
+        case 64: VQ_ENC(TT, 2); break;                                                 \
+        case 128: VQ_ENC(TT, 4); break;                                                \
+        default: VQ_ENC(TT, 8); break;                                                 \
+    }
+        switch (dtype) {
+            case VQ_F16: VQ_ENC_D(__half); break;
+            case VQ_BF16: VQ_ENC_D(__nv_bfloat16); break;
+            case VQ_F32: VQ_ENC_D(float); break;
+            default: return fail(VQ_ERR_DTYPE, "rabitq_encode: unknown dtype %d", dtype);
+        }
+#undef VQ_ENC_D
+#undef VQ_ENC
+        VQ_CHECK_LAUNCH("rabitq_encode_reg_kernel");
+        return VQ_OK;
+    }
     const unsigned blocks = (unsigned)std::min<int64_t>(ceil_div(n, kEncWarps), 148 * 16);
     const size_t smem = (size_t)kEncWarps * D * sizeof(float);
-    cudaStream_t st = (cudaStream_t)stream;
     switch (dtype) {
         case VQ_F16: rabitq_encode_kernel<__half><<<blocks, kEncWarps * 32, smem, st>>>((const __half *)keys, n, D, diag, rotate, bits, mag); break;
         case VQ_BF16: rabitq_encode_kernel<__nv_bfloat16><<<blocks, kEncWarps * 32, smem, st>>>((const __nv_bfloat16 *)keys, n, D, diag, rotate, bits, mag); break;
