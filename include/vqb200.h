@@ -87,6 +87,15 @@ typedef struct vq_kivi_quant_args {
     int64_t recon_stride_bh;  /* elements between slabs */
 } vq_kivi_quant_args;
 int32_t vq_kivi_quantize(const vq_kivi_quant_args *args, void *stream);
+/* The two uses of vq_kivi_quantize under the names of the reference operations they stand
+ * for. vq_kivi_quantize_pack is quantize-on-append into the packed store: codes, scale and
+ * zero are required, recon is ignored (the reference has no packed KIVI store; its harness
+ * keeps one code per byte: benchmark_scripts/benchmark_real_model_scalar_attend.py:155-182).
+ * vq_kivi_quant_dequant is the round trip of kivi_group_quant_dequant
+ * (veloxquant_mlx/metal/_kivi_quant.py:138-207): recon is required, codes/scale/zero are
+ * written too when given. */
+int32_t vq_kivi_quantize_pack(const vq_kivi_quant_args *args, void *stream);
+int32_t vq_kivi_quant_dequant(const vq_kivi_quant_args *args, void *stream);
 
 /* Flat dequantization code*scale+zero of one K (axis 0) or V (axis 1) tensor to
  * f16/bf16/f32. Replaces scalar_decode_once (veloxquant_mlx/metal/_scalar_attend.py:650-699,
@@ -152,6 +161,23 @@ int32_t vq_kivi_decode_attend(const vq_kivi_attend_args *args, void *stream);
  * kernels have no device-side waits). */
 int32_t vq_kivi_attend_status(void);
 
+/* Attention over already-decoded K/V rows only: vq_kivi_decode_attend with n_quant taken as
+ * 0, so just k_res / v_res ([B*H_kv] slabs of n_res rows) are read. Replaces
+ * scalar_predecoded_attend (veloxquant_mlx/metal/_scalar_attend.py:702-779,
+ * metal/src/scalar_predecoded_attend.metal). */
+int32_t vq_predecoded_attend(const vq_kivi_attend_args *args, void *stream);
+
+/* Merge of split softmax partials, the last step of every split decode attend here:
+ *   part_o  float32 [rows][n_splits][D]   sum_s exp(score_s - m) * v_s over the split's slots
+ *   part_ml float32 [rows][n_splits][2]   (m = max score of the split or -inf if it saw no
+ *                                          slot, l = sum_s exp(score_s - m))
+ *   out[row, :] = sum_j part_o[row][j] * exp(m_j - M) / sum_j l_j * exp(m_j - M), M = max_j m_j
+ * Lets a caller that spreads one context over several calls (or devices) combine them. The
+ * reference merges its SIMD-group partials inside the kernel
+ * (metal/src/scalar_affine_attend.metal:120-175); it has no separate entry point. */
+int32_t vq_lse_merge(const float *part_o, const float *part_ml, int64_t rows, int32_t n_splits,
+                     int32_t D, void *out, int32_t out_dtype, void *stream);
+
 /* The same operation as vq_kivi_decode_attend for callers that cannot allocate device
  * memory (a frozen memory pool, a host runtime that owns all allocations, a path where a
  * synchronising, fallible cudaMalloc is not acceptable). It has no counterpart in the
@@ -198,6 +224,39 @@ int32_t vq_vq_quantize(const void *x, int32_t x_dtype, int64_t n, int32_t sub_di
 int32_t vq_vq_dequant(const void *indices, int32_t index_bytes, int64_t n, const float *codebook,
                       int32_t n_centroids, int32_t sub_dim, int32_t n_sub, void *out,
                       int32_t out_dtype, void *stream);
+
+/* Quantize-on-append in one launch.
+ * keys:   x [n_tok, D] -> (optional) smooth divide where smooth > 1e-8 -> y = H x as a
+ *         sequential float32 matvec (c = 0..D-1, product and sum rounded separately) ->
+ *         nearest centroid per sub-vector (as vq_vq_quantize) -> indices; and, when x_hat is
+ *         given, gather -> H^T c -> smooth multiply -> x_hat (the round-tripped keys).
+ *         Token t belongs to head (t / tok_per_head) % n_heads and uses smooth row
+ *         head % smooth_rows. H may be NULL (no rotation), smooth may be NULL.
+ * values: indices of x itself and x_hat = gathered centroids; H and smooth are ignored.
+ * Either output may be NULL. D <= 512; sub_dim in {1, 2, 4, 8, 16}.
+ * Replaces vecinfer_encode_decode_metal (veloxquant_mlx/metal/_vecinfer.py:225-293,
+ * metal/src/vecinfer_encode_decode_full.metal) and vecinfer_encode_decode_simple_metal
+ * (_vecinfer.py:296-345, metal/src/vecinfer_encode_decode_simple.metal). */
+typedef struct vq_vq_encode_args {
+    const void *x;            /* [n_tok, D] contiguous */
+    int32_t x_dtype;
+    int64_t n_tok;
+    int32_t D, sub_dim;
+    int64_t tok_per_head;     /* tokens per (batch, head) slab of x */
+    int32_t n_heads;
+    const float *codebook;    /* [n_c, sub_dim] or [D/sub_dim][n_c][sub_dim] */
+    int32_t n_centroids;
+    int32_t stacked_codebooks;/* 0 = one shared codebook, 1 = one per sub-space */
+    const float *H;           /* [D, D] row-major or NULL */
+    const float *smooth;      /* [smooth_rows, D] or NULL */
+    int32_t smooth_rows;
+    void *x_hat;              /* [n_tok, D], dtype hat_dtype, or NULL */
+    int32_t hat_dtype;
+    void *indices;            /* [n_tok, D/sub_dim], index_bytes wide, or NULL */
+    int32_t index_bytes;
+} vq_vq_encode_args;
+int32_t vq_vq_encode_decode_keys(const vq_vq_encode_args *args, void *stream);
+int32_t vq_vq_encode_decode_values(const vq_vq_encode_args *args, void *stream);
 
 /* Attention over VQ-coded keys scored through a per-query lookup table
  * lut[s][c] = q_sub[s] . codebook[c], score = scale * sum_s lut[s][idx[s]]; values are either

@@ -47,9 +47,13 @@ def quantize_vq(x: np.ndarray, codebook: np.ndarray, sub_dim: int,
         for s in range(0, N, chunk):
             sub = flat[s:s + chunk, j, :]
             dist = np.zeros((sub.shape[0], n_c), dtype=np.float32)
-            for i in range(sub_dim):
-                d = sub[:, i:i + 1] - cbj[None, :, i]
-                dist = dist + d * d
+            with np.errstate(invalid="ignore", over="ignore"):
+                for i in range(sub_dim):
+                    d = sub[:, i:i + 1] - cbj[None, :, i]
+                    dist = dist + d * d
+            # the kernel's scan is "if (dist < best)" from best = +inf: a NaN distance never
+            # wins, and if nothing is finite the index stays 0 (vecinfer_quantize.metal:16-27)
+            dist = np.where(np.isnan(dist), np.float32(np.inf), dist)
             out[s:s + chunk, j] = np.argmin(dist, axis=1).astype(np.int32)
     return out.reshape(*lead, n_sub)
 
@@ -159,3 +163,58 @@ def reference_sdpa(q_tilde, k_indices, k_codebook, v, scale, *, v_codebook=None,
     w = np.exp(scores)
     w = w / w.sum(axis=-1, keepdims=True)
     return (w @ v_hat).astype(np.float32)
+
+
+def _seq_matvec(mat_rows: np.ndarray, vec: np.ndarray) -> np.ndarray:
+    """``out[..., r] = sum_c mat_rows[r, c] * vec[..., c]`` accumulated for ``c = 0..D-1`` in
+    order from ``0.0``, product and sum rounded separately (float32)."""
+    D = vec.shape[-1]
+    acc = np.zeros(vec.shape[:-1] + (mat_rows.shape[0],), dtype=np.float32)
+    for c in range(D):
+        acc = acc + mat_rows[:, c].astype(np.float32) * vec[..., c : c + 1].astype(np.float32)
+    return acc
+
+
+def encode_decode_keys(keys: np.ndarray, k_codebook: np.ndarray, sub_dim: int, H_mat: np.ndarray,
+                       smooth: np.ndarray | None = None):
+    """Fused key encode + decode of the reference's one-dispatch kernel
+    (``veloxquant_mlx/metal/_vecinfer.py:225-293`` and
+    ``veloxquant_mlx/metal/src/vecinfer_encode_decode_full.metal:8-110``):
+    smooth divide (only where ``s > 1e-8``) -> ``H_mat @ x`` as a sequential matvec ->
+    nearest centroid (sequential distance, first minimum) -> gather -> ``H_mat.T @ c`` ->
+    smooth multiply -> float16. ``keys`` is ``[B, H, S, D]``; smooth rows are taken as
+    ``h % rows`` after the wrapper's reduction (rows not in {1, H} are averaged to one row).
+    Returns ``(k_hat float16 [B,H,S,D], indices int32 [B,H,S,n_sub])``. PARITY UNPINNED: whether
+    the Metal compiler contracts ``dot += a*b`` into a fused multiply-add is not visible; the
+    order fixed here rounds the product and the sum separately."""
+    x = np.asarray(keys).astype(np.float32)
+    if x.ndim != 4:
+        raise ValueError(f"encode_decode_keys: keys must be 4D, got {x.shape}")
+    B, Hn, S, D = x.shape
+    Hm = np.asarray(H_mat).astype(np.float32)
+    cb = np.asarray(k_codebook).astype(np.float32)
+    sm = None
+    if smooth is not None:
+        sm = np.asarray(smooth).astype(np.float32)
+        sm = sm.reshape(1, D) if sm.ndim == 1 else sm
+        if sm.shape[0] not in (1, Hn):
+            sm = sm.mean(axis=0, keepdims=True, dtype=np.float32)
+        rows = sm[np.arange(Hn) % sm.shape[0]][None, :, None, :]  # [1,H,1,D]
+        with np.errstate(divide="ignore", invalid="ignore"):
+            x = np.where(rows > np.float32(1e-8), x / rows, x).astype(np.float32)
+    y = _seq_matvec(Hm, x)
+    idx = quantize_vq(y, cb, sub_dim)
+    g = dequantize_vq(idx, cb).astype(np.float32)
+    back = _seq_matvec(Hm.T, g)
+    if sm is not None:
+        back = back * rows
+    return back.astype(np.float16), idx.astype(np.int32)
+
+
+def encode_decode_values(values: np.ndarray, v_codebook: np.ndarray, sub_dim: int):
+    """Fused value quantize + dequantize (``veloxquant_mlx/metal/_vecinfer.py:296-345``,
+    ``veloxquant_mlx/metal/src/vecinfer_encode_decode_simple.metal:15-41``).
+    Returns ``(v_hat float16, indices uint32)``."""
+    cb = np.asarray(v_codebook).astype(np.float32)
+    idx = quantize_vq(np.asarray(values).astype(np.float32), cb, sub_dim)
+    return dequantize_vq(idx, cb).astype(np.float16), idx.astype(np.uint32)

@@ -90,12 +90,29 @@ class RabitqAttendArgs(C.Structure):
     ]
 
 
+class VqEncodeArgs(C.Structure):
+    _fields_ = [
+        ("x", C.c_void_p), ("x_dtype", C.c_int32), ("n_tok", C.c_int64), ("D", C.c_int32), ("sub_dim", C.c_int32),
+        ("tok_per_head", C.c_int64), ("n_heads", C.c_int32), ("codebook", C.c_void_p),
+        ("n_centroids", C.c_int32), ("stacked_codebooks", C.c_int32), ("H", C.c_void_p),
+        ("smooth", C.c_void_p), ("smooth_rows", C.c_int32), ("x_hat", C.c_void_p), ("hat_dtype", C.c_int32),
+        ("indices", C.c_void_p), ("index_bytes", C.c_int32),
+    ]
+
+
 # name -> (restype, argtypes); every symbol include/vqb200.h declares.
 SIGNATURES = {
     "vq_version": (C.c_int32, []),
     "vq_last_error": (C.c_char_p, []),
     "vq_kivi_quantize": (C.c_int32, [C.POINTER(KiviQuantArgs), C.c_void_p]),
+    "vq_kivi_quantize_pack": (C.c_int32, [C.POINTER(KiviQuantArgs), C.c_void_p]),
+    "vq_kivi_quant_dequant": (C.c_int32, [C.POINTER(KiviQuantArgs), C.c_void_p]),
     "vq_kivi_dequant": (C.c_int32, [C.POINTER(KiviDequantArgs), C.c_void_p]),
+    "vq_predecoded_attend": (C.c_int32, [C.POINTER(KiviAttendArgs), C.c_void_p]),
+    "vq_lse_merge": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_int64, C.c_int32, C.c_int32, C.c_void_p, C.c_int32,
+                                 C.c_void_p]),
+    "vq_vq_encode_decode_keys": (C.c_int32, [C.POINTER(VqEncodeArgs), C.c_void_p]),
+    "vq_vq_encode_decode_values": (C.c_int32, [C.POINTER(VqEncodeArgs), C.c_void_p]),
     "vq_kivi_attend_workspace_bytes": (C.c_int64, [C.POINTER(KiviAttendArgs)]),
     "vq_kivi_decode_attend": (C.c_int32, [C.POINTER(KiviAttendArgs), C.c_void_p]),
     "vq_kivi_attend_status": (C.c_int32, []),

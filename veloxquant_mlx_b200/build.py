@@ -30,6 +30,8 @@ SOURCES = [
     ("kivi_attend_mma.cu", []),
     ("kivi_attend_static.cu", []),
     ("vq_quant.cu", ["-fmad=false"]),
+    ("vq_encode.cu", ["-fmad=false"]),
+    ("vq_quant_mma.cu", []),
     ("rabitq.cu", ["-fmad=false"]),
     ("coded_attend.cu", []),
 ]

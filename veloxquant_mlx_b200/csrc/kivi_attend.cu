@@ -269,3 +269,22 @@ extern "C" int32_t vq_kivi_decode_attend(const vq_kivi_attend_args *args, void *
     }
     return VQ_OK;
 }
+
+extern "C" int32_t vq_predecoded_attend(const vq_kivi_attend_args *args, void *stream) {
+    using namespace vq;
+    VQ_REQUIRE(args != nullptr, VQ_ERR_SHAPE, "vq_predecoded_attend: args is NULL");
+    VQ_REQUIRE(args->n_res >= 1 && args->k_res && args->v_res, VQ_ERR_SHAPE, "vq_predecoded_attend: k_res/v_res with n_res >= 1 rows are required");
+    vq_kivi_attend_args a = *args;
+    a.n_quant = 0;
+    return vq_kivi_decode_attend(&a, stream);
+}
+
+extern "C" int32_t vq_lse_merge(const float *part_o, const float *part_ml, int64_t rows, int32_t n_splits,
+                                int32_t D, void *out, int32_t out_dtype, void *stream) {
+    using namespace vq;
+    VQ_REQUIRE(rows >= 0 && n_splits >= 1 && D >= 1, VQ_ERR_SHAPE, "vq_lse_merge: bad sizes (rows=%lld, n_splits=%d, D=%d)", (long long)rows, n_splits, D);
+    VQ_REQUIRE(out_dtype >= 0 && out_dtype <= 2, VQ_ERR_DTYPE, "vq_lse_merge: unknown dtype %d", out_dtype);
+    if (rows == 0) return VQ_OK;
+    VQ_REQUIRE(part_o && part_ml && out, VQ_ERR_SHAPE, "vq_lse_merge: NULL argument");
+    return launch_split_merge(part_o, part_ml, n_splits, D, out, out_dtype, rows, (cudaStream_t)stream);
+}

@@ -255,3 +255,19 @@ extern "C" int32_t vq_kivi_dequant(const vq_kivi_dequant_args *args, void *strea
     VQ_CHECK_LAUNCH("kivi_dequant_kernel");
     return VQ_OK;
 }
+
+extern "C" int32_t vq_kivi_quantize_pack(const vq_kivi_quant_args *args, void *stream) {
+    using namespace vq;
+    VQ_REQUIRE(args != nullptr, VQ_ERR_SHAPE, "vq_kivi_quantize_pack: args is NULL");
+    VQ_REQUIRE(args->codes && args->scale && args->zero, VQ_ERR_SHAPE, "vq_kivi_quantize_pack: codes, scale and zero are required");
+    vq_kivi_quant_args a = *args;
+    a.recon = nullptr;
+    return vq_kivi_quantize(&a, stream);
+}
+
+extern "C" int32_t vq_kivi_quant_dequant(const vq_kivi_quant_args *args, void *stream) {
+    using namespace vq;
+    VQ_REQUIRE(args != nullptr, VQ_ERR_SHAPE, "vq_kivi_quant_dequant: args is NULL");
+    VQ_REQUIRE(args->recon != nullptr, VQ_ERR_SHAPE, "vq_kivi_quant_dequant: recon is required");
+    return vq_kivi_quantize(args, stream);
+}

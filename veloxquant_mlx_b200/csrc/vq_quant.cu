@@ -1,6 +1,7 @@
 // VecInfer product VQ: nearest-centroid search and codebook gather.
 //
-// vq_quantize_kernel is the exact search: float32 squared distances accumulated in the
+// vq_vq_quantize sends the serving shapes to the tensor-core search (vq_quant_mma.cu), which
+// returns the same indices; everything else runs vq_quantize_kernel, the exact search: float32 squared distances accumulated in the
 // canonical order (sequential over the sub-vector, product and sum rounded separately --
 // this file is compiled with -fmad=false), strict '<' so the lowest index wins ties. One
 // thread owns one sub-vector (its sub_dim values stay in registers); the codebook is staged
@@ -9,6 +10,7 @@
 #include <algorithm>
 
 #include "common.cuh"
+#include "vq_quant_mma.h"
 
 namespace vq {
 
@@ -104,6 +106,8 @@ extern "C" int32_t vq_vq_quantize(const void *x, int32_t x_dtype, int64_t n, int
     if (n == 0) return VQ_OK;
     VQ_REQUIRE(x && codebook && indices, VQ_ERR_SHAPE, "vq_vq_quantize: NULL argument");
     cudaStream_t st = (cudaStream_t)stream;
+    if (vq_quantize_mma_supported(x, x_dtype, n, sub_dim, n_centroids, n_sub))
+        return vq_quantize_mma_launch(x, x_dtype, n, sub_dim, codebook, n_centroids, n_sub, indices, index_bytes, st);
     switch (x_dtype) {
         case VQ_F16: return launch_quantize<__half>(x, n, sub_dim, codebook, n_centroids, n_sub, indices, index_bytes, st);
         case VQ_BF16: return launch_quantize<__nv_bfloat16>(x, n, sub_dim, codebook, n_centroids, n_sub, indices, index_bytes, st);

@@ -104,7 +104,7 @@ def kivi_group_quant_dequant(x: torch.Tensor, axis: int, group_size: int, levels
         recon=out.data_ptr(), recon_stride_bh=S * D,
     )
     with torch.cuda.device(x.device):
-        check(lib().vq_kivi_quantize(C.byref(a), stream_ptr(x.device)), "kivi_group_quant_dequant")
+        check(lib().vq_kivi_quant_dequant(C.byref(a), stream_ptr(x.device)), "kivi_group_quant_dequant")
     return out
 
 
@@ -169,7 +169,7 @@ def kivi_quantize_into(x: torch.Tensor, axis: int, group_size: int, bits: int, *
         recon=None, recon_stride_bh=0,
     )
     with torch.cuda.device(x.device):
-        check(lib().vq_kivi_quantize(C.byref(a), stream_ptr(x.device)), "kivi_quantize")
+        check(lib().vq_kivi_quantize_pack(C.byref(a), stream_ptr(x.device)), "kivi_quantize")
 
 
 def kivi_quantize(x: torch.Tensor, axis: int, group_size: int, bits: int, *,
@@ -344,7 +344,8 @@ def kivi_decode_attend(q, k_codes, k_scale, k_zero, v_codes, v_scale, v_zero, gr
         need = lib().vq_kivi_attend_workspace_bytes(C.byref(a))
         ws = _workspace(q.device, need)
         a.workspace, a.workspace_bytes = ws.data_ptr(), ws.numel()
-        check(lib().vq_kivi_decode_attend(C.byref(a), stream_ptr(q.device)), fn)
+        entry = lib().vq_kivi_decode_attend if has_q else lib().vq_predecoded_attend
+        check(entry(C.byref(a), stream_ptr(q.device)), fn)
     return out
 
 
@@ -366,6 +367,75 @@ def scalar_fused_decode_attend(q, k_codes, k_scale, k_zero, v_codes, v_scale, v_
         group_size, scale, store_bits=store_bits, out_dtype=torch.float16,
         n_splits=0 if nsg is None else nsg, _fn=fn,
     )
+
+
+def scalar_fused_decode_attend_batched(q, k_codes, k_scale, k_zero, v_codes, v_scale, v_zero,
+                                       group_size: int, scale: float, nsg: int | None = None, *,
+                                       store_bits: int = 8) -> torch.Tensor:
+    """Every layer of a decode step in one launch: all inputs carry a leading ``NL`` axis
+    (``q [NL,B,H_q,S_q,D]``, codes ``[NL,B,H_kv,S_kv,D*store_bits/8]``, ...); uniform ``S_kv``.
+
+    Mirrors ``scalar_fused_decode_attend_batched`` (``metal/_scalar_attend.py:496-647``). The
+    layer axis is folded into the batch axis of the same kernel (layers are just more
+    independent (batch, kv head) units), so stacked contiguous inputs cost no copy.
+    """
+    fn = "scalar_fused_decode_attend_batched"
+    if q.ndim != 5:
+        raise ValueError(f"{fn}: q must be 5D [NL,B,H,S_q,D], got {tuple(q.shape)}")
+    if k_codes.ndim != 5 or v_codes.ndim != 5:
+        raise ValueError(f"{fn}: k_codes and v_codes must be 5D, got k_codes={tuple(k_codes.shape)}, "
+                         f"v_codes={tuple(v_codes.shape)}")
+    NL, B, H, S_q, D = q.shape
+    if NL < 1:
+        raise ValueError(f"{fn}: NL={NL} must be >= 1")
+    if D > 256:
+        raise ValueError(f"{fn}: D={D} must be <= 256")
+    if nsg is not None and not (1 <= nsg <= 32):
+        raise ValueError(f"{fn}: nsg={nsg} must be in 1..32")
+    if k_codes.shape[0] != NL:
+        raise ValueError(f"{fn}: NL mismatch: q NL={NL} vs k_codes NL={k_codes.shape[0]}")
+    if k_codes.shape[1] != B:
+        raise ValueError(f"{fn}: batch mismatch: q B={B} vs k_codes B={k_codes.shape[1]}")
+    if v_codes.shape != k_codes.shape:
+        raise ValueError(f"{fn}: k_codes shape={tuple(k_codes.shape)} vs v_codes shape={tuple(v_codes.shape)} mismatch")
+    H_kv = k_codes.shape[2]
+    for name, arr in (("k_scale", k_scale), ("k_zero", k_zero), ("v_scale", v_scale), ("v_zero", v_zero)):
+        if arr.ndim != 5 or arr.shape[0] != NL or arr.shape[1] != B or arr.shape[2] != H_kv:
+            raise ValueError(f"{fn}: {name} shape={tuple(arr.shape)} must be 5D with leading "
+                             f"[NL={NL}, B={B}, H_kv={H_kv}, ...]")
+    if H % H_kv != 0:
+        raise ValueError(f"{fn}: H_q={H} must be a multiple of H_kv={H_kv} (k_codes.shape[2]) for GQA head-packing")
+
+    def fold(t):
+        return t.reshape(NL * B, *t.shape[2:])
+
+    out = kivi_decode_attend(
+        fold(q), fold(k_codes.to(torch.uint8)), fold(k_scale.to(torch.float32)), fold(k_zero.to(torch.float32)),
+        fold(v_codes.to(torch.uint8)), fold(v_scale.to(torch.float32)), fold(v_zero.to(torch.float32)),
+        group_size, scale, store_bits=store_bits, out_dtype=torch.float16,
+        n_splits=0 if nsg is None else nsg, _fn=fn,
+    )
+    return out.reshape(NL, B, H, S_q, D)
+
+
+def lse_merge(part_o: torch.Tensor, part_ml: torch.Tensor, out_dtype=torch.float16) -> torch.Tensor:
+    """Combine split softmax partials ``part_o f32 [rows, n_splits, D]`` (unnormalised,
+    relative to each split's own maximum) and ``part_ml f32 [rows, n_splits, 2]`` (max, sum)
+    into ``[rows, D]``. No counterpart in the reference (its kernels merge internally)."""
+    fn = "lse_merge"
+    if part_o.ndim != 3 or part_ml.ndim != 3 or part_ml.shape != (part_o.shape[0], part_o.shape[1], 2):
+        raise ValueError(f"{fn}: part_o [rows,n_splits,D] and part_ml [rows,n_splits,2] expected, got "
+                         f"{tuple(part_o.shape)} / {tuple(part_ml.shape)}")
+    require_cuda(part_o, f"{fn}: part_o")
+    if part_o.dtype != torch.float32 or part_ml.dtype != torch.float32:
+        raise ValueError(f"{fn}: partials must be float32")
+    rows, n_splits, D = part_o.shape
+    po, pm = part_o.contiguous(), part_ml.contiguous()
+    out = torch.empty((rows, D), dtype=out_dtype, device=part_o.device)
+    with torch.cuda.device(part_o.device):
+        check(lib().vq_lse_merge(po.data_ptr(), pm.data_ptr(), rows, n_splits, D, out.data_ptr(),
+                                 dtype_code(out_dtype), stream_ptr(part_o.device)), fn)
+    return out
 
 
 def scalar_predecoded_attend(q, k_hat, v_hat, scale: float, nsg: int | None = None) -> torch.Tensor:
@@ -440,5 +510,6 @@ def turboquant_bit_unpack(packed: torch.Tensor, N: int, b: int) -> torch.Tensor:
 __all__ = [
     "kivi_available", "storage_bits", "kivi_group_quant_dequant", "kivi_quantize", "kivi_quantize_into",
     "scalar_decode_once", "kivi_decode_attend", "scalar_fused_decode_attend", "scalar_predecoded_attend",
+    "scalar_fused_decode_attend_batched", "lse_merge",
     "turboquant_bit_pack", "turboquant_bit_unpack",
 ]

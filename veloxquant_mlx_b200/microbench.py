@@ -1,0 +1,129 @@
+"""Per-operation timings of the hot path on one GPU, at the sizes the headline configurations
+use. ``bench.py`` measures the decode step; this module times the other operations one at a
+time (quantize-on-append kernels, the coded-cache attends) so that each has a measured rate
+and a command a profiler can wrap:
+
+    python -m veloxquant_mlx_b200.microbench                 # every operation
+    python -m veloxquant_mlx_b200.microbench --op vq_quantize --dtype float16 --iters 20
+
+Each line is JSON: operation, shape, microseconds per call (CUDA events, after 3 warm-up calls,
+inputs larger than L2 or re-created so that nothing is served from cache where that matters),
+algorithmic bytes or useful FLOPs per call and the resulting rate.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+
+import torch
+
+from . import kernels as k
+from . import rabitq as rq
+from . import vecinfer as vi
+
+_DT = {"float16": torch.float16, "bfloat16": torch.bfloat16, "float32": torch.float32}
+
+
+def _time_us(fn, iters: int) -> float:
+    for _ in range(3):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / iters * 1e3
+
+
+def _line(op, shape, us, *, nbytes=None, flops=None, **extra):
+    rec = {"op": op, "shape": shape, "us": round(us, 2)}
+    if nbytes is not None:
+        rec.update(bytes=int(nbytes), GBps=round(nbytes / us / 1e3, 1))
+    if flops is not None:
+        rec.update(useful_flops=int(flops), TFLOPs=round(flops / us / 1e6, 2))
+    rec.update(extra)
+    print(json.dumps(rec), flush=True)
+
+
+def op_kivi_quantize(a):
+    """Quantize + pack of one layer's K and V at the decode workload's prefill shape."""
+    B, H, S, D = a.batch, 8, a.ctx, 128
+    x = torch.randn(B, H, S, D, device="cuda", dtype=_DT[a.dtype] if a.dtype != "float32" else torch.bfloat16)
+    for bits in (4, 2):
+        for axis, name in ((-2, "keys"), (-1, "values")):
+            us = _time_us(lambda: k.kivi_quantize(x, axis, 32, bits), a.iters)
+            n = x.numel()
+            nb = n * x.element_size() + n * bits // 8 + (n // 32) * 8
+            _line("kivi_quantize", f"{name} b={bits} [{B},{H},{S},{D}] {x.dtype}", us, nbytes=nb)
+
+
+def op_vq_quantize(a):
+    dt = _DT[a.dtype]
+    for S in (4096, 65536):
+        keys = torch.randn(8, S, 128, device="cuda").to(dt)
+        cb = torch.randn(256, 8, device="cuda")
+        us = _time_us(lambda: vi.quantize_vq(keys, cb, 8, index_dtype=torch.uint8), a.iters)
+        n = 8 * S * 16
+        _line("vq_quantize", f"[8,{S},128] {a.dtype} sub_dim=8 n_c=256", us, flops=2 * n * 256 * 8,
+              nbytes=keys.numel() * keys.element_size() + n)
+
+
+def op_vq_encode(a):
+    keys = torch.randn(1, 8, 4096, 128, device="cuda").to(_DT[a.dtype])
+    cb = torch.randn(256, 8, device="cuda")
+    H = vi.walsh_hadamard_matrix(128, device="cuda")
+    sm = torch.rand(8, 128, device="cuda") + 0.5
+    us = _time_us(lambda: vi.vecinfer_encode_decode_metal(keys, cb, 8, H, sm), a.iters)
+    _line("vq_encode_decode_keys", "[1,8,4096,128] sub_dim=8 n_c=256", us, flops=2 * 8 * 4096 * 16 * 256 * 8)
+    us = _time_us(lambda: vi.vecinfer_encode_decode_simple_metal(keys, cb, 8), a.iters)
+    _line("vq_encode_decode_values", "[1,8,4096,128] sub_dim=8 n_c=256", us, flops=2 * 8 * 4096 * 16 * 256 * 8)
+
+
+def op_vq_attend(a):
+    S = 4096
+    keys = torch.randn(1, 8, S, 128, device="cuda", dtype=torch.float16)
+    cb = torch.randn(256, 8, device="cuda")
+    kidx = vi.quantize_vq(keys, cb, 8, index_dtype=torch.uint8)
+    v = torch.randn(1, 8, S, 128, device="cuda", dtype=torch.float16)
+    q = torch.randn(1, 32, 1, 128, device="cuda", dtype=torch.float16)
+    us = _time_us(lambda: vi.fused_sdpa_vq(q, kidx, cb, v, None, 0.088), a.iters)
+    _line("vq_attend", f"H_q=32 H_kv=8 S={S} dense f16 values", us, nbytes=kidx.numel() + v.numel() * 2)
+
+
+def op_rabitq(a):
+    B, H, S, D = 8, 8, 16384, 128
+    keys = torch.randn(B * H * S, D, device="cuda", dtype=torch.float16)
+    diag = torch.from_numpy(rq.make_hadamard_diagonal(D)).to("cuda")
+    us = _time_us(lambda: rq.rabitq_encode(keys, diag), a.iters)
+    _line("rabitq_encode", f"[{B * H * S},{D}] f16", us, nbytes=keys.numel() * 2 + keys.shape[0] * (D // 8 + 4))
+    bits, mag = rq.rabitq_encode(keys, diag)
+    v = torch.randn(B, H, S, D, device="cuda", dtype=torch.float16)
+    q = torch.randn(B, 32, 1, D, device="cuda", dtype=torch.float16)
+    qs = torch.full((B, 32, 1), 0.01, device="cuda")
+    us = _time_us(lambda: rq.rabitq_fused_attend(q, qs, bits.view(B, H, S, D // 8), mag.view(B, H, S), None, v, None), a.iters)
+    _line("rabitq_attend", f"B={B} H_q=32 H_kv={H} S={S} dense f16 values", us, nbytes=B * H * S * (D // 8 + 4 + 2 * D))
+
+
+OPS = {"kivi_quantize": op_kivi_quantize, "vq_quantize": op_vq_quantize, "vq_encode": op_vq_encode,
+       "vq_attend": op_vq_attend, "rabitq": op_rabitq}
+
+
+def main(argv=None):
+    ap = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
+    ap.add_argument("--op", choices=sorted(OPS) + ["all"], default="all")
+    ap.add_argument("--dtype", choices=sorted(_DT), default="float16")
+    ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--batch", type=int, default=4, help="batch of the kivi_quantize shape")
+    ap.add_argument("--ctx", type=int, default=32768, help="context of the kivi_quantize shape")
+    a = ap.parse_args(argv)
+    if not torch.cuda.is_available():
+        raise SystemExit("microbench needs a CUDA device")
+    for name in (sorted(OPS) if a.op == "all" else [a.op]):
+        OPS[name](a)
+
+
+if __name__ == "__main__":
+    main()

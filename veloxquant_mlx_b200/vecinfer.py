@@ -12,7 +12,7 @@ import math
 import numpy as np
 import torch
 
-from ._lib import VqAttendArgs, check, dtype_code, lib, require_cuda, stream_ptr
+from ._lib import VqAttendArgs, VqEncodeArgs, check, dtype_code, lib, require_cuda, stream_ptr
 from .kernels import _FLOAT_DTYPES, _workspace
 
 _INDEX_DTYPES = {torch.uint8: 1, torch.int16: 2, torch.uint16: 2, torch.int32: 4, torch.uint32: 4}
@@ -123,6 +123,92 @@ def dequantize_vq(indices: torch.Tensor, codebook: torch.Tensor, *, out_dtype=No
     return out
 
 
+def vecinfer_quantize_metal(x: torch.Tensor, codebook: torch.Tensor, sub_dim: int) -> torch.Tensor:
+    """``x [..., D] -> int32 [..., D // sub_dim]`` under the reference's kernel-wrapper name
+    (``metal/_vecinfer.py:181-222``)."""
+    return quantize_vq(x, codebook, sub_dim)
+
+
+def vecinfer_dequant_metal(indices: torch.Tensor, codebook: torch.Tensor, out_dtype=None) -> torch.Tensor:
+    """Codebook gather under the reference's kernel-wrapper name (``metal/_vecinfer.py:144-178``)."""
+    return dequantize_vq(indices, codebook, out_dtype=out_dtype)
+
+
+def _encode_decode(who: str, x: torch.Tensor, codebook: torch.Tensor, sub_dim: int, H_mat, smooth, keys: bool,
+                   index_dtype, want_hat: bool = True, hat_dtype=torch.float16):
+    if x.ndim != 4:
+        raise ValueError(f"{who}: {'keys' if keys else 'values'} must be 4D, got {tuple(x.shape)}")
+    B, Hn, S, D = x.shape
+    if D % sub_dim != 0:
+        raise ValueError(f"{who}: D={D} not divisible by sub_dim={sub_dim}")
+    if D > 512:
+        raise ValueError(f"{who}: D={D} > 512 (threadgroup limit)")
+    if x.dtype not in _FLOAT_DTYPES:
+        raise ValueError(f"{who}: unsupported dtype {x.dtype}")
+    require_cuda(x, f"{who}: input")
+    cb, stacked, n_c, sd = _codebook_f32(codebook.to(x.device), who)
+    if n_c == 0 or sd != sub_dim:
+        raise ValueError(f"{who}: codebook must be non-empty [n_centroids, {sub_dim}], got {tuple(codebook.shape)}")
+    n_sub = D // sub_dim
+    if stacked and stacked != n_sub:
+        raise ValueError(f"{who}: {stacked} stacked codebooks for {n_sub} sub-spaces")
+    Hf = sm = None
+    rows = 1
+    if keys and H_mat is not None:
+        Hf = H_mat.to(device=x.device, dtype=torch.float32).contiguous()
+        if tuple(Hf.shape) != (D, D):
+            raise ValueError(f"{who}: H_mat must be [{D}, {D}], got {tuple(Hf.shape)}")
+    if keys and smooth is not None:
+        sm = smooth.to(device=x.device, dtype=torch.float32)
+        sm = sm.reshape(1, D) if sm.ndim == 1 else sm
+        if sm.shape[0] not in (1, Hn):
+            acc = sm[0].clone()  # rows added in order, then one divide: a fixed summation order
+            for r in range(1, sm.shape[0]):
+                acc += sm[r]
+            # tensor / tensor is a true IEEE divide (a Python-scalar divisor becomes a reciprocal multiply)
+            sm = torch.div(acc, torch.full_like(acc, float(sm.shape[0]))).reshape(1, D)
+        sm = sm.contiguous()
+        rows = sm.shape[0]
+    xs = x.contiguous()
+    idx = torch.empty((B, Hn, S, n_sub), dtype=index_dtype, device=x.device)
+    hat = torch.empty((B, Hn, S, D), dtype=hat_dtype, device=x.device) if want_hat else None
+    a = VqEncodeArgs(
+        x=xs.data_ptr(), x_dtype=dtype_code(x.dtype), n_tok=B * Hn * S, D=D, sub_dim=sub_dim,
+        tok_per_head=max(S, 1), n_heads=Hn, codebook=cb.data_ptr(), n_centroids=n_c,
+        stacked_codebooks=1 if stacked else 0, H=Hf.data_ptr() if Hf is not None else None,
+        smooth=sm.data_ptr() if sm is not None else None, smooth_rows=rows,
+        x_hat=hat.data_ptr() if hat is not None else None, hat_dtype=dtype_code(hat_dtype),
+        indices=idx.data_ptr(), index_bytes=_INDEX_DTYPES[index_dtype])
+    fn = lib().vq_vq_encode_decode_keys if keys else lib().vq_vq_encode_decode_values
+    with torch.cuda.device(x.device):
+        check(fn(C.byref(a), stream_ptr(x.device)), who)
+    return hat, idx
+
+
+def vecinfer_encode_decode_metal(keys: torch.Tensor, k_codebook: torch.Tensor, sub_dim: int, H_mat: torch.Tensor,
+                                 smooth: torch.Tensor | None = None):
+    """Fused key encode + decode in one launch: smooth -> WHT -> VQ -> dequant -> inverse WHT ->
+    smooth. Returns ``(k_hat float16 [B,H,S,D], k_indices int32 [B,H,S,n_sub])``
+    (``metal/_vecinfer.py:225-293``). Smooth rows other than 1 or H are averaged to one row."""
+    return _encode_decode("vecinfer_encode_decode_metal", keys, k_codebook, sub_dim, H_mat, smooth, True,
+                          torch.int32)
+
+
+def vecinfer_encode_decode_simple_metal(values: torch.Tensor, v_codebook: torch.Tensor, sub_dim: int):
+    """Fused value quantize + dequantize. Returns ``(v_hat float16, v_indices uint32)``
+    (``metal/_vecinfer.py:296-345``)."""
+    return _encode_decode("vecinfer_encode_decode_simple_metal", values, v_codebook, sub_dim, None, None, False,
+                          torch.uint32)
+
+
+def vecinfer_encode_keys(keys: torch.Tensor, k_codebook: torch.Tensor, sub_dim: int, H_mat, smooth=None, *,
+                         index_dtype=torch.uint8) -> torch.Tensor:
+    """Indices only (the form a memory-bound cache stores): the same launch without the decode
+    half. No counterpart under this name in the reference."""
+    return _encode_decode("vecinfer_encode_keys", keys, k_codebook, sub_dim, H_mat, smooth, True, index_dtype,
+                          want_hat=False)[1]
+
+
 def compute_query_lut(q_tilde: torch.Tensor, codebook: torch.Tensor, sub_dim: int) -> torch.Tensor:
     """``lut[..., s, c] = q_sub[..., s, :] . codebook[c]`` (``allocators/vecinfer.py:341-359``)."""
     *lead, D = q_tilde.shape
@@ -204,4 +290,6 @@ def metal_fused_sdpa(q_tilde, k_indices, k_codebook, v_indices, v_codebook, scal
 
 
 __all__ = ["walsh_hadamard_matrix", "apply_dual_transform_keys", "apply_dual_transform_queries", "quantize_vq",
-           "vecinfer_quantize", "dequantize_vq", "compute_query_lut", "fused_sdpa_vq", "metal_fused_sdpa"]
+           "vecinfer_quantize", "dequantize_vq", "compute_query_lut", "fused_sdpa_vq", "metal_fused_sdpa",
+           "vecinfer_quantize_metal", "vecinfer_dequant_metal", "vecinfer_encode_decode_metal",
+           "vecinfer_encode_decode_simple_metal", "vecinfer_encode_keys"]
