@@ -89,15 +89,71 @@ __device__ __forceinline__ void load_v_row(const CodedParams &p, int64_t tok, in
     }
 }
 
+// Value-row access specialised at compile time so that the loads of several rows can be issued
+// back to back before any of them is used (a run-time switch per row serialises them).
+enum { VM_GENERIC = 0, VM_F16 = 1, VM_BF16 = 2, VM_NIBBLE = 3, VM_VQ8 = 4 };
+
+// Raw 32-bit words one lane holds for one value row.
+template <int DPL, int VM>
+struct VRaw {
+    static constexpr int N = (VM == VM_F16 || VM == VM_BF16) ? DPL / 2 : 1;
+    uint32_t r[N];
+};
+
+template <int DPL, int VM>
+__device__ __forceinline__ VRaw<DPL, VM> load_v_raw(const CodedParams &p, int64_t tok, int lane) {
+    VRaw<DPL, VM> o;
+    if constexpr (VM == VM_F16 || VM == VM_BF16) {
+        const uint16_t *src = reinterpret_cast<const uint16_t *>(p.v) + tok * (DPL * 32) + lane * DPL;
+        if constexpr (DPL == 2) o.r[0] = __ldg(reinterpret_cast<const uint32_t *>(src));
+        else if constexpr (DPL == 4) { const uint2 t = __ldg(reinterpret_cast<const uint2 *>(src)); o.r[0] = t.x; o.r[1] = t.y; }
+        else { const uint4 t = __ldg(reinterpret_cast<const uint4 *>(src)); o.r[0] = t.x; o.r[1] = t.y; o.r[2] = t.z; o.r[3] = t.w; }
+    } else if constexpr (VM == VM_NIBBLE) {
+        const uint8_t *src = reinterpret_cast<const uint8_t *>(p.v) + tok * (DPL * 16) + lane * (DPL / 2);
+        if constexpr (DPL == 2) o.r[0] = __ldg(src);
+        else if constexpr (DPL == 4) o.r[0] = __ldg(reinterpret_cast<const uint16_t *>(src));
+        else o.r[0] = __ldg(reinterpret_cast<const uint32_t *>(src));
+    } else {  // VM_VQ8: this lane's DPL channels lie inside one sub-vector
+        const int nsv = (DPL * 32) / p.v_sub;
+        o.r[0] = __ldg(reinterpret_cast<const uint8_t *>(p.v) + tok * nsv + (lane * DPL) / p.v_sub);
+    }
+    return o;
+}
+
+template <int DPL, int VM>
+__device__ __forceinline__ void decode_v(const CodedParams &p, const VRaw<DPL, VM> &raw, const float *sh_vlut, int lane,
+                                         float (&v)[DPL]) {
+    if constexpr (VM == VM_F16) {
+#pragma unroll
+        for (int i = 0; i < DPL / 2; ++i) {
+            const float2 f = __half22float2(*reinterpret_cast<const __half2 *>(&raw.r[i]));
+            v[2 * i] = f.x; v[2 * i + 1] = f.y;
+        }
+    } else if constexpr (VM == VM_BF16) {
+#pragma unroll
+        for (int i = 0; i < DPL / 2; ++i) {
+            v[2 * i] = __uint_as_float(raw.r[i] << 16); v[2 * i + 1] = __uint_as_float(raw.r[i] & 0xffff0000u);
+        }
+    } else if constexpr (VM == VM_NIBBLE) {
+#pragma unroll
+        for (int i = 0; i < DPL; ++i) v[i] = sh_vlut[(raw.r[0] >> (4 * i)) & 0xFu];
+    } else {
+        const uint32_t c = min(raw.r[0], (uint32_t)(p.v_nc - 1));
+        const float *row = sh_vlut + c * p.v_sub + (lane * DPL) % p.v_sub;
+#pragma unroll
+        for (int i = 0; i < DPL; ++i) v[i] = row[i];
+    }
+}
+
 // One CTA: (context split, kv head x query row x head chunk, batch). All (<= 8) query heads of
 // the kv head are handled together: a key's code is loaded once and scored against every
 // head, a value row is loaded once and accumulated into every head. Warps take alternate
 // 32-key tiles of the split; value rows are fetched eight at a time so that eight
 // independent loads are in flight per lane.
-template <int DPL>
+template <int DPL, int VM>
 __global__ void __launch_bounds__(kWarpsC * 32)
-coded_attend_kernel(const CodedParams p) {
-    extern __shared__ float smem[];
+coded_attend_kernel(const CodedParams p, int key_floats, int vlut_floats) {
+    extern __shared__ __align__(16) float smem[];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int split = blockIdx.x;
     int y = blockIdx.y;
@@ -117,6 +173,12 @@ coded_attend_kernel(const CodedParams p) {
     float *lut = smem;
     uint32_t *sh_qbits = reinterpret_cast<uint32_t *>(smem);
     float *sh_qs = smem + kHeadsC * 8;
+    float *sh_vlut = smem + key_floats;                              // value centroids / codebook
+    float *sh_w = sh_vlut + vlut_floats + warp * (32 * kHeadsC);     // this warp's softmax weights [key][head]
+    if constexpr (VM == VM_NIBBLE || VM == VM_VQ8) {
+        const int n = VM == VM_NIBBLE ? p.v_nc : p.v_nc * p.v_sub;
+        for (int i = threadIdx.x; i < vlut_floats; i += blockDim.x) sh_vlut[i] = i < n ? p.v_codebook[i] : 0.f;
+    }
     if (p.key_mode == KEY_VQ) {
         for (int i = threadIdx.x; i < nh * lut_stride; i += blockDim.x) {
             const int hp = i / lut_stride, r = i % lut_stride;
@@ -213,21 +275,58 @@ coded_attend_kernel(const CodedParams p) {
         if (!any_live) continue;
         // ---- values: eight rows in flight, each accumulated into every head ----------------
         const int n_in_tile = min(32, t_end - tile);
-        for (int l0 = 0; l0 < n_in_tile; l0 += 8) {
-            float vrow[8][DPL];
+        if constexpr (VM == VM_GENERIC) {
+            for (int l0 = 0; l0 < n_in_tile; l0 += 8) {
+                float vrow[8][DPL];
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                const int tl = min(l0 + j, n_in_tile - 1);  // rows past the end get weight 0
-                load_v_row<DPL>(p, bh * p.stride_tok + tile + tl, lane, vrow[j]);
+                for (int j = 0; j < 8; ++j) {
+                    const int tl = min(l0 + j, n_in_tile - 1);  // rows past the end get weight 0
+                    load_v_row<DPL>(p, bh * p.stride_tok + tile + tl, lane, vrow[j]);
+                }
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+#pragma unroll
+                    for (int h = 0; h < kHeadsC; ++h) {
+                        if (h < nh) {
+                            const float wl = (l0 + j < n_in_tile) ? __shfl_sync(0xffffffffu, w[h], l0 + j) : 0.f;
+#pragma unroll
+                            for (int i = 0; i < DPL; ++i) acc[h][i] = fmaf(wl, vrow[j][i], acc[h][i]);
+                        }
+                    }
+                }
             }
+        } else {
+            // weights to shared memory: one broadcast 16-byte read per row and four heads
+            // instead of one shuffle per row and head
+            __syncwarp();
+            *reinterpret_cast<float4 *>(sh_w + lane * kHeadsC) = make_float4(w[0], w[1], w[2], w[3]);
+            *reinterpret_cast<float4 *>(sh_w + lane * kHeadsC + 4) = make_float4(w[4], w[5], w[6], w[7]);
+            __syncwarp();
+            constexpr int R = 8;
+            const int64_t tok0 = bh * p.stride_tok + tile;
+            for (int l0 = 0; l0 < n_in_tile; l0 += R) {
+                VRaw<DPL, VM> raw[R];
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
+                for (int j = 0; j < R; ++j) raw[j] = load_v_raw<DPL, VM>(p, tok0 + min(l0 + j, n_in_tile - 1), lane);
 #pragma unroll
-                for (int h = 0; h < kHeadsC; ++h) {
-                    if (h < nh) {
-                        const float wl = (l0 + j < n_in_tile) ? __shfl_sync(0xffffffffu, w[h], l0 + j) : 0.f;
+                for (int j = 0; j < R; ++j) {
+                    float v[DPL];
+                    decode_v<DPL, VM>(p, raw[j], sh_vlut, lane, v);
+                    // rows past the end of the tile belong to lanes whose weight is already 0
+                    const int wr = l0 + j;
+                    const float4 wa = *reinterpret_cast<const float4 *>(sh_w + wr * kHeadsC);
+                    const float wl4[4] = {wa.x, wa.y, wa.z, wa.w};
 #pragma unroll
-                        for (int i = 0; i < DPL; ++i) acc[h][i] = fmaf(wl, vrow[j][i], acc[h][i]);
+                    for (int h = 0; h < 4; ++h)
+#pragma unroll
+                        for (int i = 0; i < DPL; ++i) acc[h][i] = fmaf(wl4[h], v[i], acc[h][i]);
+                    if (nh > 4) {
+                        const float4 wb = *reinterpret_cast<const float4 *>(sh_w + wr * kHeadsC + 4);
+                        const float wh4[4] = {wb.x, wb.y, wb.z, wb.w};
+#pragma unroll
+                        for (int h = 0; h < 4; ++h)
+#pragma unroll
+                            for (int i = 0; i < DPL; ++i) acc[4 + h][i] = fmaf(wh4[h], v[i], acc[4 + h][i]);
                     }
                 }
             }
@@ -305,21 +404,53 @@ int32_t launch_coded(CodedParams &p, void *workspace, int64_t workspace_bytes, i
         p.part_o = (float *)workspace;
         p.part_ml = p.part_o + rows * p.n_splits * p.D;
     }
+    // Specialised value access where the row layout allows vector loads.
+    const int dpl = p.D / 32;
+    const bool vec_ok = dpl == 2 || dpl == 4 || dpl == 8;
+    int vm = VM_GENERIC;
+    int vlut_floats = 0;
+    if (vec_ok && p.v_mode == V_DENSE && (p.v_dtype == VQ_F16 || p.v_dtype == VQ_BF16) && is_aligned(p.v, 16)) {
+        vm = p.v_dtype == VQ_F16 ? VM_F16 : VM_BF16;
+    } else if (vec_ok && p.v_mode == V_CENT_NIBBLE && is_aligned(p.v, 4)) {
+        vm = VM_NIBBLE;
+        vlut_floats = 16;
+    } else if (vec_ok && p.v_mode == V_VQ && p.v_index_bytes == 1 && p.v_sub % dpl == 0 &&
+               (size_t)p.v_nc * p.v_sub * 4 <= 64 * 1024) {
+        vm = VM_VQ8;
+        vlut_floats = (p.v_nc * p.v_sub + 3) & ~3;
+    }
+    const int key_floats = (int)((std::max(lut_bytes * std::min(hpk, kHeadsC), (size_t)(kHeadsC * 9 * 4)) / 4 + 3) & ~(size_t)3);
+    const size_t main_bytes = ((size_t)key_floats + vlut_floats + (size_t)kWarpsC * 32 * kHeadsC) * sizeof(float);
+    VQ_REQUIRE(main_bytes <= di.smem_optin, VQ_ERR_CAPACITY, "%s: lookup tables of %zu bytes do not fit shared memory", who, main_bytes);
     const size_t red_bytes = ((size_t)kWarpsC * kHeadsC * p.D + 2 * kWarpsC * kHeadsC) * sizeof(float);
-    const size_t smem = std::max(red_bytes, std::max(lut_bytes * std::min(hpk, kHeadsC), (size_t)(kHeadsC * 9 * 4)));
+    const size_t smem = std::max(red_bytes, main_bytes);
     dim3 grid(p.n_splits, (unsigned)gy, p.B);
-#define VQ_CODED(DPL)                                                                                     \
-    case DPL:                                                                                             \
-        if (smem > 48 * 1024)                                                                             \
-            VQ_CHECK_CUDA(cudaFuncSetAttribute(coded_attend_kernel<DPL>,                                   \
-                                               cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));  \
-        coded_attend_kernel<DPL><<<grid, kWarpsC * 32, smem, st>>>(p);                                    \
+#define VQ_CODED_VM(DPL, VM)                                                                               \
+    do {                                                                                                   \
+        if (smem > 48 * 1024)                                                                              \
+            VQ_CHECK_CUDA(cudaFuncSetAttribute(coded_attend_kernel<DPL, VM>,                                \
+                                               cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));   \
+        coded_attend_kernel<DPL, VM><<<grid, kWarpsC * 32, smem, st>>>(p, key_floats, vlut_floats);        \
+    } while (0)
+#define VQ_CODED_FAST(DPL)                                                                                 \
+    case DPL:                                                                                              \
+        switch (vm) {                                                                                      \
+            case VM_F16: VQ_CODED_VM(DPL, VM_F16); break;                                                  \
+            case VM_BF16: VQ_CODED_VM(DPL, VM_BF16); break;                                                \
+            case VM_NIBBLE: VQ_CODED_VM(DPL, VM_NIBBLE); break;                                            \
+            case VM_VQ8: VQ_CODED_VM(DPL, VM_VQ8); break;                                                  \
+            default: VQ_CODED_VM(DPL, VM_GENERIC); break;                                                  \
+        }                                                                                                  \
         break;
-    switch (p.D / 32) {
-        VQ_CODED(1) VQ_CODED(2) VQ_CODED(3) VQ_CODED(4) VQ_CODED(5) VQ_CODED(6) VQ_CODED(7) VQ_CODED(8)
+#define VQ_CODED_GEN(DPL) case DPL: VQ_CODED_VM(DPL, VM_GENERIC); break;
+    switch (dpl) {
+        VQ_CODED_GEN(1) VQ_CODED_FAST(2) VQ_CODED_GEN(3) VQ_CODED_FAST(4) VQ_CODED_GEN(5) VQ_CODED_GEN(6)
+        VQ_CODED_GEN(7) VQ_CODED_FAST(8)
         default: return fail(VQ_ERR_SHAPE, "%s: unsupported head_dim %d", who, p.D);
     }
-#undef VQ_CODED
+#undef VQ_CODED_GEN
+#undef VQ_CODED_FAST
+#undef VQ_CODED_VM
     VQ_CHECK_LAUNCH("coded_attend_kernel");
     if (p.n_splits > 1) return launch_split_merge(p.part_o, p.part_ml, p.n_splits, p.D, p.out, p.out_dtype, rows, st);
     return VQ_OK;
