@@ -150,8 +150,8 @@ __device__ __forceinline__ void decode_v(const CodedParams &p, const VRaw<DPL, V
 // head, a value row is loaded once and accumulated into every head. Warps take alternate
 // 32-key tiles of the split; value rows are fetched eight at a time so that eight
 // independent loads are in flight per lane.
-template <int DPL, int VM>
-__global__ void __launch_bounds__(kWarpsC * 32)
+template <int DPL, int VM, int NH>
+__global__ void __launch_bounds__(kWarpsC * 32, (NH <= 4 && DPL <= 4 && VM != VM_GENERIC) ? 3 : 2)
 coded_attend_kernel(const CodedParams p, int key_floats, int vlut_floats) {
     extern __shared__ __align__(16) float smem[];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -163,7 +163,7 @@ coded_attend_kernel(const CodedParams p, int key_floats, int vlut_floats) {
     const int b = blockIdx.z;
     const int hpk = p.H_q / p.H_kv;
     const int h0 = hc * kHeadsC;
-    const int nh = min(kHeadsC, hpk - h0);
+    const int nh = min(NH, hpk - h0);  // NH = 4 is launched only when hpk <= 4
     const int D = p.D;
     const int64_t bh = (int64_t)b * p.H_kv + hkv;
     const int n_sub = p.key_mode == KEY_VQ ? D / p.k_sub : 0;
@@ -172,9 +172,9 @@ coded_attend_kernel(const CodedParams p, int key_floats, int vlut_floats) {
     // shared: VQ lookup tables [nh][n_sub*n_c] | RaBitQ: query sign words [nh][8] and scales [nh]
     float *lut = smem;
     uint32_t *sh_qbits = reinterpret_cast<uint32_t *>(smem);
-    float *sh_qs = smem + kHeadsC * 8;
+    float *sh_qs = smem + NH * 8;
     float *sh_vlut = smem + key_floats;                              // value centroids / codebook
-    float *sh_w = sh_vlut + vlut_floats + warp * (32 * kHeadsC);     // this warp's softmax weights [key][head]
+    float *sh_w = sh_vlut + vlut_floats + warp * (32 * NH);     // this warp's softmax weights [key][head]
     if constexpr (VM == VM_NIBBLE || VM == VM_VQ8) {
         const int n = VM == VM_NIBBLE ? p.v_nc : p.v_nc * p.v_sub;
         for (int i = threadIdx.x; i < vlut_floats; i += blockDim.x) sh_vlut[i] = i < n ? p.v_codebook[i] : 0.f;
@@ -207,9 +207,9 @@ coded_attend_kernel(const CodedParams p, int key_floats, int vlut_floats) {
     const int q_abs = p.S_kv - p.S_q + sq;
     const int n_words = D / 32;
 
-    float m_run[kHeadsC], l_run[kHeadsC], acc[kHeadsC][DPL];
+    float m_run[NH], l_run[NH], acc[NH][DPL];
 #pragma unroll
-    for (int h = 0; h < kHeadsC; ++h) {
+    for (int h = 0; h < NH; ++h) {
         m_run[h] = -INFINITY; l_run[h] = 0.f;
 #pragma unroll
         for (int i = 0; i < DPL; ++i) acc[h][i] = 0.f;
@@ -221,21 +221,21 @@ coded_attend_kernel(const CodedParams p, int key_floats, int vlut_floats) {
         if (valid && p.causal && t > q_abs) valid = false;
         if (valid && p.window > 0 && q_abs + 1 > p.window && t + p.window < q_abs + 1) valid = false;
         const int64_t tok = bh * p.stride_tok + (valid ? t : t_begin);
-        float w[kHeadsC];
+        float w[NH];
         // ---- scores of this lane's key against every head ---------------------------------
         if (p.key_mode == KEY_VQ) {
 #pragma unroll
-            for (int h = 0; h < kHeadsC; ++h) w[h] = 0.f;
+            for (int h = 0; h < NH; ++h) w[h] = 0.f;
             for (int sub = 0; sub < n_sub; ++sub) {
                 uint32_t c = load_index(p.k_codes, p.k_index_bytes, tok * n_sub + sub);
                 c = min(c, (uint32_t)(p.k_nc - 1));
                 const float *row = lut + sub * p.k_nc + c;
 #pragma unroll
-                for (int h = 0; h < kHeadsC; ++h)
+                for (int h = 0; h < NH; ++h)
                     if (h < nh) w[h] += row[h * lut_stride];
             }
 #pragma unroll
-            for (int h = 0; h < kHeadsC; ++h) w[h] = valid ? w[h] * p.scale : -INFINITY;
+            for (int h = 0; h < NH; ++h) w[h] = valid ? w[h] * p.scale : -INFINITY;
         } else {
             const uint32_t *kb = reinterpret_cast<const uint32_t *>(reinterpret_cast<const uint8_t *>(p.k_codes) + tok * (D / 8));
             uint32_t kw[8];
@@ -244,7 +244,7 @@ coded_attend_kernel(const CodedParams p, int key_floats, int vlut_floats) {
             const float km = p.k_mag[tok];
             const float kc = p.k_const ? p.k_const[tok] : 0.f;
 #pragma unroll
-            for (int h = 0; h < kHeadsC; ++h) {
+            for (int h = 0; h < NH; ++h) {
                 int ham = 0;
 #pragma unroll
                 for (int i = 0; i < 8; ++i)
@@ -256,7 +256,7 @@ coded_attend_kernel(const CodedParams p, int key_floats, int vlut_floats) {
         // ---- online softmax per head ------------------------------------------------------
         bool any_live = false;
 #pragma unroll
-        for (int h = 0; h < kHeadsC; ++h) {
+        for (int h = 0; h < NH; ++h) {
             if (h < nh) {
                 const float tile_max = warp_max(w[h]);
                 if (tile_max == -INFINITY) { w[h] = 0.f; continue; }
@@ -286,7 +286,7 @@ coded_attend_kernel(const CodedParams p, int key_floats, int vlut_floats) {
 #pragma unroll
                 for (int j = 0; j < 8; ++j) {
 #pragma unroll
-                    for (int h = 0; h < kHeadsC; ++h) {
+                    for (int h = 0; h < NH; ++h) {
                         if (h < nh) {
                             const float wl = (l0 + j < n_in_tile) ? __shfl_sync(0xffffffffu, w[h], l0 + j) : 0.f;
 #pragma unroll
@@ -299,35 +299,53 @@ coded_attend_kernel(const CodedParams p, int key_floats, int vlut_floats) {
             // weights to shared memory: one broadcast 16-byte read per row and four heads
             // instead of one shuffle per row and head
             __syncwarp();
-            *reinterpret_cast<float4 *>(sh_w + lane * kHeadsC) = make_float4(w[0], w[1], w[2], w[3]);
-            *reinterpret_cast<float4 *>(sh_w + lane * kHeadsC + 4) = make_float4(w[4], w[5], w[6], w[7]);
+            *reinterpret_cast<float4 *>(sh_w + lane * NH) = make_float4(w[0], w[1], w[2], w[3]);
+            if constexpr (NH == 8) *reinterpret_cast<float4 *>(sh_w + lane * NH + 4) = make_float4(w[4], w[5], w[6], w[7]);
             __syncwarp();
+            // Two batches of R rows are in flight: the next batch is requested before the
+            // current one is consumed.
             constexpr int R = 8;
             const int64_t tok0 = bh * p.stride_tok + tile;
-            for (int l0 = 0; l0 < n_in_tile; l0 += R) {
-                VRaw<DPL, VM> raw[R];
+            VRaw<DPL, VM> raw[R], nxt[R];
 #pragma unroll
-                for (int j = 0; j < R; ++j) raw[j] = load_v_raw<DPL, VM>(p, tok0 + min(l0 + j, n_in_tile - 1), lane);
+            for (int j = 0; j < R; ++j) raw[j] = load_v_raw<DPL, VM>(p, tok0 + min(j, n_in_tile - 1), lane);
+            // (with three CTAs per SM the register budget has no room for the second batch:
+            // there the next batch is requested after the current one is consumed)
+            constexpr bool kAhead = !(NH <= 4 && DPL <= 4);
+#pragma unroll(kAhead ? 4 : 1)
+            for (int l0 = 0; l0 < 32; l0 += R) {
+                if (l0 >= n_in_tile) break;
+                if (kAhead && l0 + R < 32 && l0 + R < n_in_tile) {
+#pragma unroll
+                    for (int j = 0; j < R; ++j) nxt[j] = load_v_raw<DPL, VM>(p, tok0 + min(l0 + R + j, n_in_tile - 1), lane);
+                }
 #pragma unroll
                 for (int j = 0; j < R; ++j) {
                     float v[DPL];
                     decode_v<DPL, VM>(p, raw[j], sh_vlut, lane, v);
                     // rows past the end of the tile belong to lanes whose weight is already 0
                     const int wr = l0 + j;
-                    const float4 wa = *reinterpret_cast<const float4 *>(sh_w + wr * kHeadsC);
+                    const float4 wa = *reinterpret_cast<const float4 *>(sh_w + wr * NH);
                     const float wl4[4] = {wa.x, wa.y, wa.z, wa.w};
 #pragma unroll
                     for (int h = 0; h < 4; ++h)
 #pragma unroll
                         for (int i = 0; i < DPL; ++i) acc[h][i] = fmaf(wl4[h], v[i], acc[h][i]);
-                    if (nh > 4) {
-                        const float4 wb = *reinterpret_cast<const float4 *>(sh_w + wr * kHeadsC + 4);
+                    if constexpr (NH == 8) if (nh > 4) {
+                        const float4 wb = *reinterpret_cast<const float4 *>(sh_w + wr * NH + 4);
                         const float wh4[4] = {wb.x, wb.y, wb.z, wb.w};
 #pragma unroll
                         for (int h = 0; h < 4; ++h)
 #pragma unroll
                             for (int i = 0; i < DPL; ++i) acc[4 + h][i] = fmaf(wh4[h], v[i], acc[4 + h][i]);
                     }
+                }
+                if (kAhead) {
+#pragma unroll
+                    for (int j = 0; j < R; ++j) raw[j] = nxt[j];
+                } else if (l0 + R < 32 && l0 + R < n_in_tile) {
+#pragma unroll
+                    for (int j = 0; j < R; ++j) raw[j] = load_v_raw<DPL, VM>(p, tok0 + min(l0 + R + j, n_in_tile - 1), lane);
                 }
             }
         }
@@ -336,27 +354,27 @@ coded_attend_kernel(const CodedParams p, int key_floats, int vlut_floats) {
     // ---- merge the warps of this CTA -------------------------------------------------------
     __syncthreads();  // the lookup tables are dead: reuse shared memory
     float *red_o = smem;                                   // [warps][heads][D]
-    float *red_m = red_o + kWarpsC * kHeadsC * D;          // [warps][heads]
-    float *red_l = red_m + kWarpsC * kHeadsC;
+    float *red_m = red_o + kWarpsC * NH * D;          // [warps][heads]
+    float *red_l = red_m + kWarpsC * NH;
 #pragma unroll
-    for (int h = 0; h < kHeadsC; ++h) {
+    for (int h = 0; h < NH; ++h) {
         if (h < nh) {
 #pragma unroll
-            for (int i = 0; i < DPL; ++i) red_o[(warp * kHeadsC + h) * D + lane * DPL + i] = acc[h][i];
-            if (lane == 0) { red_m[warp * kHeadsC + h] = m_run[h]; red_l[warp * kHeadsC + h] = l_run[h]; }
+            for (int i = 0; i < DPL; ++i) red_o[(warp * NH + h) * D + lane * DPL + i] = acc[h][i];
+            if (lane == 0) { red_m[warp * NH + h] = m_run[h]; red_l[warp * NH + h] = l_run[h]; }
         }
     }
     __syncthreads();
     for (int i = threadIdx.x; i < nh * D; i += blockDim.x) {
         const int h = i / D, d = i % D;
         float gm = -INFINITY;
-        for (int wq = 0; wq < kWarpsC; ++wq) gm = fmaxf(gm, red_m[wq * kHeadsC + h]);
+        for (int wq = 0; wq < kWarpsC; ++wq) gm = fmaxf(gm, red_m[wq * NH + h]);
         float gl = 0.f, o = 0.f;
         for (int wq = 0; wq < kWarpsC; ++wq) {
-            const float mw = red_m[wq * kHeadsC + h];
+            const float mw = red_m[wq * NH + h];
             const float f = (mw == -INFINITY) ? 0.f : __expf(mw - gm);
-            gl += red_l[wq * kHeadsC + h] * f;
-            o += red_o[(wq * kHeadsC + h) * D + d] * f;
+            gl += red_l[wq * NH + h] * f;
+            o += red_o[(wq * NH + h) * D + d] * f;
         }
         const int64_t qrow = ((int64_t)b * p.H_q + hkv * hpk + h0 + h) * p.S_q + sq;
         if (p.n_splits == 1) {
@@ -373,6 +391,8 @@ coded_attend_kernel(const CodedParams p, int key_floats, int vlut_floats) {
 
 int pick_splits(int requested, int S_kv, int64_t ctas, int sm_count) {
     if (requested > 0) return std::min(requested, 256);
+    // About four CTAs per SM (finer splits cost more in set-up and in the merge than they win
+    // back in the last wave: measured), at least one 32-key tile per warp.
     int64_t want = ceil_div((int64_t)sm_count * 4, std::max<int64_t>(ctas, 1));
     want = std::min<int64_t>(want, ceil_div(S_kv, 256));
     return (int)std::max<int64_t>(1, std::min<int64_t>(want, 256));
@@ -419,18 +439,24 @@ int32_t launch_coded(CodedParams &p, void *workspace, int64_t workspace_bytes, i
         vm = VM_VQ8;
         vlut_floats = (p.v_nc * p.v_sub + 3) & ~3;
     }
-    const int key_floats = (int)((std::max(lut_bytes * std::min(hpk, kHeadsC), (size_t)(kHeadsC * 9 * 4)) / 4 + 3) & ~(size_t)3);
-    const size_t main_bytes = ((size_t)key_floats + vlut_floats + (size_t)kWarpsC * 32 * kHeadsC) * sizeof(float);
+    const int nh_t = hpk <= 4 ? 4 : kHeadsC;  // heads per CTA the kernel is instantiated for
+    const int key_floats = (int)((std::max(lut_bytes * std::min(hpk, kHeadsC), (size_t)(nh_t * 9 * 4)) / 4 + 3) & ~(size_t)3);
+    const size_t main_bytes = ((size_t)key_floats + vlut_floats + (size_t)kWarpsC * 32 * nh_t) * sizeof(float);
     VQ_REQUIRE(main_bytes <= di.smem_optin, VQ_ERR_CAPACITY, "%s: lookup tables of %zu bytes do not fit shared memory", who, main_bytes);
-    const size_t red_bytes = ((size_t)kWarpsC * kHeadsC * p.D + 2 * kWarpsC * kHeadsC) * sizeof(float);
+    const size_t red_bytes = ((size_t)kWarpsC * nh_t * p.D + 2 * kWarpsC * nh_t) * sizeof(float);
     const size_t smem = std::max(red_bytes, main_bytes);
     dim3 grid(p.n_splits, (unsigned)gy, p.B);
-#define VQ_CODED_VM(DPL, VM)                                                                               \
+#define VQ_CODED_VM_N(DPL, VM, NHT)                                                                             \
     do {                                                                                                   \
         if (smem > 48 * 1024)                                                                              \
-            VQ_CHECK_CUDA(cudaFuncSetAttribute(coded_attend_kernel<DPL, VM>,                                \
+            VQ_CHECK_CUDA(cudaFuncSetAttribute(coded_attend_kernel<DPL, VM, NHT>,                                \
                                                cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));   \
-        coded_attend_kernel<DPL, VM><<<grid, kWarpsC * 32, smem, st>>>(p, key_floats, vlut_floats);        \
+        coded_attend_kernel<DPL, VM, NHT><<<grid, kWarpsC * 32, smem, st>>>(p, key_floats, vlut_floats);        \
+    } while (0)
+#define VQ_CODED_VM(DPL, VM)                                                                               \
+    do {                                                                                                   \
+        if (hpk <= 4) VQ_CODED_VM_N(DPL, VM, 4);                                                           \
+        else VQ_CODED_VM_N(DPL, VM, 8);                                                                    \
     } while (0)
 #define VQ_CODED_FAST(DPL)                                                                                 \
     case DPL:                                                                                              \
@@ -451,6 +477,7 @@ int32_t launch_coded(CodedParams &p, void *workspace, int64_t workspace_bytes, i
 #undef VQ_CODED_GEN
 #undef VQ_CODED_FAST
 #undef VQ_CODED_VM
+#undef VQ_CODED_VM_N
     VQ_CHECK_LAUNCH("coded_attend_kernel");
     if (p.n_splits > 1) return launch_split_merge(p.part_o, p.part_ml, p.n_splits, p.D, p.out, p.out_dtype, rows, st);
     return VQ_OK;
