@@ -218,6 +218,11 @@ int32_t vq_vq_quantize(const void *x, int32_t x_dtype, int64_t n, int32_t sub_di
                        const float *codebook, int32_t n_centroids, int32_t n_sub,
                        void *indices, int32_t index_bytes, void *stream);
 
+/* Synchronises the device, then reports (and clears) whether an earlier vq_vq_quantize kernel
+ * abandoned a bounded device-side wait: VQ_ERR_TIMEOUT if so (its indices are then invalid),
+ * VQ_OK otherwise. No counterpart in the reference. */
+int32_t vq_vq_quantize_status(void);
+
 /* Codebook gather: out[i, :] = codebook[min(indices[i], n_c-1), :] (stacked codebooks as
  * above). Replaces dequantize_vq (allocators/vecinfer.py:321-335) and vecinfer_dequant_metal
  * (metal/_vecinfer.py:144-178, metal/src/vecinfer_dequant.metal). */

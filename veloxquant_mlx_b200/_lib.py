@@ -119,6 +119,7 @@ SIGNATURES = {
     "vq_kivi_decode_attend_static": (C.c_int32, [C.POINTER(KiviAttendArgs), C.c_void_p]),
     "vq_vq_quantize": (C.c_int32, [C.c_void_p, C.c_int32, C.c_int64, C.c_int32, C.c_void_p, C.c_int32, C.c_int32,
                                    C.c_void_p, C.c_int32, C.c_void_p]),
+    "vq_vq_quantize_status": (C.c_int32, []),
     "vq_vq_dequant": (C.c_int32, [C.c_void_p, C.c_int32, C.c_int64, C.c_void_p, C.c_int32, C.c_int32, C.c_int32,
                                   C.c_void_p, C.c_int32, C.c_void_p]),
     "vq_vq_attend_workspace_bytes": (C.c_int64, [C.POINTER(VqAttendArgs)]),

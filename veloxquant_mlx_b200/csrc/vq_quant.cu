@@ -106,6 +106,8 @@ extern "C" int32_t vq_vq_quantize(const void *x, int32_t x_dtype, int64_t n, int
     if (n == 0) return VQ_OK;
     VQ_REQUIRE(x && codebook && indices, VQ_ERR_SHAPE, "vq_vq_quantize: NULL argument");
     cudaStream_t st = (cudaStream_t)stream;
+    if (vq_quantize_tc5_supported(x, x_dtype, n, sub_dim, n_centroids, n_sub))
+        return vq_quantize_tc5_launch(x, n, codebook, n_centroids, indices, index_bytes, st);
     if (vq_quantize_mma_supported(x, x_dtype, n, sub_dim, n_centroids, n_sub))
         return vq_quantize_mma_launch(x, x_dtype, n, sub_dim, codebook, n_centroids, n_sub, indices, index_bytes, st);
     switch (x_dtype) {
@@ -133,5 +135,14 @@ extern "C" int32_t vq_vq_dequant(const void *indices, int32_t index_bytes, int64
         default: return fail(VQ_ERR_DTYPE, "vq_vq_dequant: unknown dtype %d", out_dtype);
     }
     VQ_CHECK_LAUNCH("vq_dequant_kernel");
+    return VQ_OK;
+}
+
+extern "C" int32_t vq_vq_quantize_status(void) {
+    using namespace vq;
+    int flag = 0;
+    int32_t rc = vq_quantize_tc5_take_timeout(&flag);
+    if (rc != VQ_OK) return rc;
+    if (flag) return fail(VQ_ERR_TIMEOUT, "vq_vq_quantize: a bounded wait on an MMA-completion barrier gave up");
     return VQ_OK;
 }

@@ -12,9 +12,12 @@
 // Exactness. The reference result is defined by a particular float32 evaluation order
 // (sequential sum of squared differences, first minimum wins). Its rounding and the MMA's
 // differ, so for every sub-vector the kernel finds ALL centroids whose score is within
-//     delta = 2^-15 * (|x|^2 + max|c|^2)
-// of the best score -- a bound several times the sum of both evaluations' worst-case
-// errors. Pass 1 takes the row maximum (two 3-input max per MMA); pass 2 repeats the same
+//     delta = 2^-16 * (|x|^2 + max|c|^2)
+// of the best score. Error budget, relative to |x|^2 + max|c|^2: the MMA adds at most ~20
+// terms with float32 rounding (2^-23 each) to exact products of halves, the centroid's hi+lo
+// split leaves 2^-22: below 2^-18.7; the reference's own sum of squared differences is within
+// 2^-19.7 in these units. Two scores are compared, so orders can differ only within
+// 2 * (2^-18.7 + 2^-19.7) = 2^-17.1: delta is twice that. Pass 1 takes the row maximum (two 3-input max per MMA); pass 2 repeats the same
 // MMAs (bit-identical scores) and counts/identifies scores >= max - delta. One candidate:
 // it is the answer. Several (near-ties, duplicate centroids), or a row that the half-precision
 // operands cannot represent (|x| > 2^15, non-finite), or a codebook outside [2^-4, 2^12]:
@@ -271,7 +274,7 @@ vq_quantize_mma_kernel(const T *__restrict__ x, int64_t n_vec, const float *__re
                 float m = best[mt][r];
                 m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 1));
                 m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 2));
-                thr[mt][r] = m - 3.0517578125e-05f * (thr[mt][r] + cmax2);
+                thr[mt][r] = m - 1.52587890625e-05f * (thr[mt][r] + cmax2);
             }
 
         // ---- pass 2: the same scores again; count and name those within delta of the best --
