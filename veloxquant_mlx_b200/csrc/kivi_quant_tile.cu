@@ -10,71 +10,103 @@
 //                    completes each channel's min/max. Codes of a row's 8 channels are packed
 //                    in-lane into one word: no cross-lane packing.
 //   values (axis 1): a row's 32-channel group is 4 neighbouring lanes: two xor shuffles.
-// Rounding is bit-identical to the reference's float32 divide: the quotient is first
-// estimated with a correctly rounded reciprocal; only if the estimate lies within 2e-4 of a
-// half-integer (where a 2-ulp estimate error could flip round-half-even) is the IEEE divide
-// executed. Compiled with -fmad=false.
+// Extrema are taken on the packed 16-bit values (min/max do not round), two per instruction.
+// Rounding is bit-identical to the reference's float32 divide + round-half-even: the correctly
+// rounded quotient comes from a reciprocal and two fused multiply-adds (see codes8_fast), the
+// rounding from a magic-number add. This file is compiled with -fmad=false; the fused
+// operations it uses are explicit.
 #include "common.cuh"
 #include "kivi_quant_tile.h"
 
 namespace vq {
 namespace {
 
+constexpr float kMagic = 12582912.0f;  // 1.5 * 2^23: x + kMagic rounds x to the nearest-even integer
+
+// ---- packed (two elements per register) min / max and widening -----------------------------
+template <typename T> struct Pk;
+template <> struct Pk<__half> {
+    using t2 = __half2;
+    static __device__ __forceinline__ float2 widen(uint32_t w) { return __half22float2(*reinterpret_cast<const __half2 *>(&w)); }
+};
+template <> struct Pk<__nv_bfloat16> {
+    using t2 = __nv_bfloat162;
+    static __device__ __forceinline__ float2 widen(uint32_t w) {
+        return make_float2(__uint_as_float(w << 16), __uint_as_float(w & 0xffff0000u));
+    }
+};
 template <typename T>
-__device__ __forceinline__ void unpack8(const uint4 &r, float (&v)[8]);
-template <>
-__device__ __forceinline__ void unpack8<__half>(const uint4 &r, float (&v)[8]) {
-    const __half2 *h = reinterpret_cast<const __half2 *>(&r);
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        const float2 f = __half22float2(h[i]);
-        v[2 * i] = f.x;
-        v[2 * i + 1] = f.y;
-    }
+__device__ __forceinline__ uint32_t pmin(uint32_t a, uint32_t b) {
+    using t2 = typename Pk<T>::t2;
+    t2 r = __hmin2(*reinterpret_cast<const t2 *>(&a), *reinterpret_cast<const t2 *>(&b));
+    return *reinterpret_cast<uint32_t *>(&r);
 }
-template <>
-__device__ __forceinline__ void unpack8<__nv_bfloat16>(const uint4 &r, float (&v)[8]) {
-    const uint32_t w[4] = {r.x, r.y, r.z, r.w};
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        v[2 * i] = __uint_as_float(w[i] << 16);
-        v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
-    }
+template <typename T>
+__device__ __forceinline__ uint32_t pmax(uint32_t a, uint32_t b) {
+    using t2 = typename Pk<T>::t2;
+    t2 r = __hmax2(*reinterpret_cast<const t2 *>(&a), *reinterpret_cast<const t2 *>(&b));
+    return *reinterpret_cast<uint32_t *>(&r);
 }
 
-__device__ __forceinline__ float code_of(float v, float gmin, float scale, float rcp, float levels) {
-    const float d = __fsub_rn(v, gmin);
-    const float t = __fmul_rn(d, rcp);
-    float q = rintf(t);
-    if (fabsf(fabsf(__fsub_rn(t, q)) - 0.5f) < 2e-4f) q = rintf(__fdiv_rn(d, scale));  // near a tie: exact divide
-    return fminf(fmaxf(q, 0.0f), levels);
+// Codes of 8 neighbouring channels of one row, packed into `SB`-bit fields (LSB first).
+// The IEEE quotient (v - min) / scale is produced without the divide instruction: with
+// rc = RN(1/scale) (correctly rounded), t0 = RN(d*rc), r = d - scale*t0 (exact, one fma),
+// RN(t0 + r*rc) is the correctly rounded quotient (Markstein's theorem; cross-checked against
+// the divide on 8e10 operand pairs of this range, ties included). It is rounded to the
+// nearest-even integer by the magic-number add; the integer then sits in the low mantissa
+// bits of that sum and is shifted into place by an integer multiply-add. 0 <= quotient <=
+// levels for finite input, so no clamp; `odd` reports a non-finite or out-of-range quotient
+// (non-finite input), for which the caller falls back to the clamped divide.
+template <int SB>
+__device__ __forceinline__ uint64_t codes8_fast(const float (&v)[8], const float (&mn)[8], const float (&sc)[8],
+                                                const float (&rc)[8], float levels, bool &odd) {
+    uint32_t lo = 0, hi = 0;
+    bool bad = false;
+    const float lim = levels + 0.25f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        const float d = __fsub_rn(v[j], mn[j]);
+        const float t0 = __fmul_rn(d, rc[j]);
+        const float r = __fmaf_rn(-sc[j], t0, d);
+        const float t = __fmaf_rn(r, rc[j], t0);
+        bad |= !(t < lim);  // NaN too; a finite quotient is at most levels * (1 + 2^-22)
+        const uint32_t bits = __float_as_uint(__fadd_rn(t, kMagic));  // 0x4B400000 + code
+        if (SB == 8 && j >= 4) hi += bits << (8 * (j - 4));
+        else lo += bits << (SB * j);
+    }
+    odd = bad;
+    // remove the exponent bits that rode along (modulo 2^32, like the sums above)
+    uint32_t c_lo = 0, c_hi = 0;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        if (SB == 8 && j >= 4) c_hi += 0x4B400000u << (8 * (j - 4));
+        else c_lo += 0x4B400000u << (SB * j);
+    }
+    return ((uint64_t)(hi - c_hi) << 32) | (uint32_t)(lo - c_lo);
 }
 
 template <int SB>
-__device__ __forceinline__ void store_codes(uint8_t *row, int cl, const float (&q)[8]) {
-    if constexpr (SB == 4) {
-        uint32_t w = 0;
+__device__ __forceinline__ uint64_t codes8_exact(const float (&v)[8], const float (&mn)[8], const float (&sc)[8], float levels) {
+    uint32_t lo = 0, hi = 0;
 #pragma unroll
-        for (int j = 0; j < 8; ++j) w |= ((uint32_t)q[j]) << (4 * j);
-        reinterpret_cast<uint32_t *>(row)[cl] = w;
-    } else if constexpr (SB == 2) {
-        uint32_t w = 0;
-#pragma unroll
-        for (int j = 0; j < 8; ++j) w |= ((uint32_t)q[j]) << (2 * j);
-        reinterpret_cast<uint16_t *>(row)[cl] = (uint16_t)w;
-    } else {
-        uint32_t w0 = 0, w1 = 0;
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            w0 |= ((uint32_t)q[j]) << (8 * j);
-            w1 |= ((uint32_t)q[4 + j]) << (8 * j);
-        }
-        reinterpret_cast<uint2 *>(row)[cl] = make_uint2(w0, w1);
+    for (int j = 0; j < 8; ++j) {
+        const float q = fminf(fmaxf(rintf(__fdiv_rn(__fsub_rn(v[j], mn[j]), sc[j])), 0.0f), levels);
+        const uint32_t c = (uint32_t)q;
+        if (SB == 8 && j >= 4) hi |= c << (8 * (j - 4));
+        else lo |= c << (SB * j);
     }
+    return ((uint64_t)hi << 32) | lo;
+}
+
+template <int SB>
+__device__ __forceinline__ void store_packed(uint8_t *row, int cl, uint64_t w) {
+    if constexpr (SB == 4) reinterpret_cast<uint32_t *>(row)[cl] = (uint32_t)w;
+    else if constexpr (SB == 2) reinterpret_cast<uint16_t *>(row)[cl] = (uint16_t)w;
+    else reinterpret_cast<uint2 *>(row)[cl] = make_uint2((uint32_t)w, (uint32_t)(w >> 32));
 }
 
 template <typename T, int SB, int AXIS>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(128, 4)
 kivi_quant_tile_kernel(const T *__restrict__ x, int64_t x_stride_bh, int64_t n_tok, int64_t tiles_per_bh,
                        int64_t n_tiles, float levels, float eps, uint8_t *__restrict__ codes,
                        int64_t codes_stride_bh, float *__restrict__ scale, float *__restrict__ zero,
@@ -97,23 +129,24 @@ kivi_quant_tile_kernel(const T *__restrict__ x, int64_t x_stride_bh, int64_t n_t
     }
 
     if constexpr (AXIS == 0) {
-        float mn[8], mx[8];
+        // per-channel extrema over this lane's 16 rows, two channels per register
+        uint32_t mnp[4] = {raw[0].x, raw[0].y, raw[0].z, raw[0].w}, mxp[4] = {raw[0].x, raw[0].y, raw[0].z, raw[0].w};
 #pragma unroll
-        for (int j = 0; j < 8; ++j) { mn[j] = INFINITY; mx[j] = -INFINITY; }
+        for (int i = 1; i < 16; ++i) {
+            const uint32_t w[4] = {raw[i].x, raw[i].y, raw[i].z, raw[i].w};
 #pragma unroll
-        for (int i = 0; i < 16; ++i) {
-            float v[8];
-            unpack8<T>(raw[i], v);
-#pragma unroll
-            for (int j = 0; j < 8; ++j) { mn[j] = fminf(mn[j], v[j]); mx[j] = fmaxf(mx[j], v[j]); }
+            for (int k = 0; k < 4; ++k) { mnp[k] = pmin<T>(mnp[k], w[k]); mxp[k] = pmax<T>(mxp[k], w[k]); }
         }
-        float sc[8], rc[8];
+        float mn[8], sc[8], rc[8];
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-            mn[j] = fminf(mn[j], __shfl_xor_sync(0xffffffffu, mn[j], 16));
-            mx[j] = fmaxf(mx[j], __shfl_xor_sync(0xffffffffu, mx[j], 16));
-            sc[j] = fmaxf(__fdiv_rn(__fsub_rn(mx[j], mn[j]), levels), eps);
-            rc[j] = __frcp_rn(sc[j]);
+        for (int k = 0; k < 4; ++k) {
+            const uint32_t on = __shfl_xor_sync(0xffffffffu, mnp[k], 16), ox = __shfl_xor_sync(0xffffffffu, mxp[k], 16);
+            const float2 fn = Pk<T>::widen(pmin<T>(mnp[k], on)), fx = Pk<T>::widen(pmax<T>(mxp[k], ox));
+            mn[2 * k] = fn.x; mn[2 * k + 1] = fn.y;
+            sc[2 * k] = fmaxf(__fdiv_rn(__fsub_rn(fx.x, fn.x), levels), eps);
+            sc[2 * k + 1] = fmaxf(__fdiv_rn(__fsub_rn(fx.y, fn.y), levels), eps);
+            rc[2 * k] = __frcp_rn(sc[2 * k]);
+            rc[2 * k + 1] = __frcp_rn(sc[2 * k + 1]);
         }
         if (hf == 0) {
             float4 *ps = reinterpret_cast<float4 *>(scale + bh * param_stride_bh + tile * D + 8 * cl);
@@ -123,36 +156,46 @@ kivi_quant_tile_kernel(const T *__restrict__ x, int64_t x_stride_bh, int64_t n_t
         }
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
-            float v[8], q[8];
-            unpack8<T>(raw[i], v);
+            const uint32_t w[4] = {raw[i].x, raw[i].y, raw[i].z, raw[i].w};
+            float v[8];
 #pragma unroll
-            for (int j = 0; j < 8; ++j) q[j] = code_of(v[j], mn[j], sc[j], rc[j], levels);
-            store_codes<SB>(cb + (int64_t)(2 * i + hf) * RB, cl, q);
+            for (int k = 0; k < 4; ++k) { const float2 f = Pk<T>::widen(w[k]); v[2 * k] = f.x; v[2 * k + 1] = f.y; }
+            bool odd;
+            uint64_t packed = codes8_fast<SB>(v, mn, sc, rc, levels, odd);
+            if (odd) packed = codes8_exact<SB>(v, mn, sc, levels);
+            store_packed<SB>(cb + (int64_t)(2 * i + hf) * RB, cl, packed);
         }
     } else {
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
             const int row = 2 * i + hf;
-            float v[8], q[8];
-            unpack8<T>(raw[i], v);
-            float mn = v[0], mx = v[0];
-#pragma unroll
-            for (int j = 1; j < 8; ++j) { mn = fminf(mn, v[j]); mx = fmaxf(mx, v[j]); }
-            mn = fminf(mn, __shfl_xor_sync(0xffffffffu, mn, 1));
-            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
-            mn = fminf(mn, __shfl_xor_sync(0xffffffffu, mn, 2));
-            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
-            const float sc = fmaxf(__fdiv_rn(__fsub_rn(mx, mn), levels), eps);
-            const float rc = __frcp_rn(sc);
+            const uint32_t w[4] = {raw[i].x, raw[i].y, raw[i].z, raw[i].w};
+            // extrema of the row's 32-channel group: 8 channels here, then the 3 neighbouring lanes
+            uint32_t pn = pmin<T>(pmin<T>(w[0], w[1]), pmin<T>(w[2], w[3]));
+            uint32_t px = pmax<T>(pmax<T>(w[0], w[1]), pmax<T>(w[2], w[3]));
+            pn = pmin<T>(pn, __shfl_xor_sync(0xffffffffu, pn, 1));
+            px = pmax<T>(px, __shfl_xor_sync(0xffffffffu, px, 1));
+            pn = pmin<T>(pn, __shfl_xor_sync(0xffffffffu, pn, 2));
+            px = pmax<T>(px, __shfl_xor_sync(0xffffffffu, px, 2));
+            const float2 fn = Pk<T>::widen(pn), fx = Pk<T>::widen(px);
+            const float mn1 = fminf(fn.x, fn.y), mx1 = fmaxf(fx.x, fx.y);
+            const float sc1 = fmaxf(__fdiv_rn(__fsub_rn(mx1, mn1), levels), eps);
+            const float rc1 = __frcp_rn(sc1);
             if (tok0 + row < n_tok) {
                 if ((cl & 3) == 0) {
                     const int64_t pidx = bh * param_stride_bh + (tok0 + row) * 4 + (cl >> 2);
-                    scale[pidx] = sc;
-                    zero[pidx] = mn;
+                    scale[pidx] = sc1;
+                    zero[pidx] = mn1;
                 }
+                float v[8], mn[8], sc[8], rc[8];
 #pragma unroll
-                for (int j = 0; j < 8; ++j) q[j] = code_of(v[j], mn, sc, rc, levels);
-                store_codes<SB>(cb + (int64_t)row * RB, cl, q);
+                for (int k = 0; k < 4; ++k) { const float2 f = Pk<T>::widen(w[k]); v[2 * k] = f.x; v[2 * k + 1] = f.y; }
+#pragma unroll
+                for (int j = 0; j < 8; ++j) { mn[j] = mn1; sc[j] = sc1; rc[j] = rc1; }
+                bool odd;
+                uint64_t packed = codes8_fast<SB>(v, mn, sc, rc, levels, odd);
+                if (odd) packed = codes8_exact<SB>(v, mn, sc, levels);
+                store_packed<SB>(cb + (int64_t)row * RB, cl, packed);
             }
         }
     }
