@@ -215,7 +215,7 @@ extern "C" int64_t vq_kivi_attend_workspace_bytes(const vq_kivi_attend_args *arg
     const int64_t rows = (int64_t)a.B * a.H_q * a.S_q;
     int64_t splits = general_splits(a, di.sm_count);
     if (a.variant != 1 && a.H_kv >= 1 && a.H_q % a.H_kv == 0 && kivi_attend_mma_supported(a) == nullptr)
-        splits = std::max<int64_t>(splits, kivi_attend_mma_splits(a, di) + 1);
+        splits = std::max<int64_t>(splits, kivi_attend_mma_splits(a, di) + kivi_attend_mma_tail_parts(a));
     return rows * splits * ((int64_t)a.D + 2) * (int64_t)sizeof(float) + 256;
 }
 

@@ -24,8 +24,8 @@
 // an mbarrier) into a 2- to 4-stage shared-memory ring, so HBM reads stay in flight while the
 // warps unpack. Warp w owns token group w of each tile (32 tokens = one K scale group).
 // The context is split across CTAs; each writes an unnormalised partial (m, l, o) and a
-// small second kernel merges them. The unquantized tail is one more partial from a
-// CUDA-core CTA in the same launch.
+// small second kernel merges them. The unquantized tail adds a few more partials from
+// CUDA-core CTAs in the same launch.
 #include <algorithm>
 #include <cstdlib>
 
@@ -173,15 +173,20 @@ struct Params {
     int hpk;
     int n_chunks;       // ceil(hpk / 4)
     int n_splits;       // quantized-context splits
-    int n_parts;        // n_splits + (tail present)
+    int n_tail;         // CTAs that attend the unquantized tail (0 if there is none)
+    int n_parts;        // n_splits + n_tail
     int groups_total;     // n_quant / 32
     int groups_per_warp;  // consecutive groups owned by one warp
     float *part_o;      // [B*H_kv][n_parts][hpk][128]
     float *part_ml;     // [B*H_kv][n_parts][hpk][2]
 };
 
-// ---- tail (unquantized tokens): CUDA cores, one CTA per (batch, kv head) ------------------
-__device__ void tail_partial(const Params &p, uint8_t *smem_raw, int b, int hkv) {
+// ---- tail (unquantized tokens): CUDA cores, n_tail CTAs per (batch, kv head) ---------------
+// Tail CTA `ti` takes an equal slice of the tail tokens; inside it each warp takes every fourth
+// token. The per-token loop is latency-bound, so on short contexts (where the tail is what the
+// launch waits for) the tail is spread over several CTAs. (Loading several tokens ahead inside
+// this function changed the register allocation of the main path and cost it 3-10 %: measured.)
+__device__ void tail_partial(const Params &p, uint8_t *smem_raw, int b, int hkv, int ti) {
     const vq_kivi_attend_args &a = p.a;
     float *sh_q = reinterpret_cast<float *>(smem_raw);           // [8][128]
     float *sh_o = sh_q + kMaxHeads * kD;                         // [4][8][128]
@@ -203,7 +208,9 @@ __device__ void tail_partial(const Params &p, uint8_t *smem_raw, int b, int hkv)
         l[hp] = 0.f;
         o[hp][0] = o[hp][1] = o[hp][2] = o[hp][3] = 0.f;
     }
-    for (int t = warp; t < a.n_res; t += kWarps) {
+    const int per_cta = (a.n_res + p.n_tail - 1) / p.n_tail;
+    const int t_begin = ti * per_cta, t_end = min(a.n_res, t_begin + per_cta);
+    for (int t = t_begin + warp; t < t_end; t += kWarps) {
         const int64_t r = bh * a.res_stride_bh + (int64_t)t * kD + lane * 4;
         float kd[4], vd[4];
 #pragma unroll
@@ -234,7 +241,7 @@ __device__ void tail_partial(const Params &p, uint8_t *smem_raw, int b, int hkv)
         }
     }
     __syncthreads();
-    const int part = p.n_parts - 1;
+    const int part = p.n_splits + ti;
     for (int i = threadIdx.x; i < hpk * kD; i += blockDim.x) {
         const int hp = i / kD, d = i % kD;
         float gm = -INFINITY;
@@ -264,8 +271,8 @@ kivi_attend_mma_kernel(const __grid_constant__ Params p) {
     extern __shared__ __align__(128) uint8_t smem_raw[];
     const vq_kivi_attend_args &a = p.a;
     const int b = blockIdx.z, hkv = blockIdx.y;
-    if ((int)blockIdx.x >= p.n_splits * p.n_chunks) {  // the tail CTA
-        tail_partial(p, smem_raw, b, hkv);
+    if ((int)blockIdx.x >= p.n_splits * p.n_chunks) {  // a tail CTA
+        tail_partial(p, smem_raw, b, hkv, (int)blockIdx.x - p.n_splits * p.n_chunks);
         return;
     }
     const int split = blockIdx.x / p.n_chunks;
@@ -786,6 +793,11 @@ const char *kivi_attend_mma_supported(const vq_kivi_attend_args &a) {
 
 int kivi_attend_mma_splits(const vq_kivi_attend_args &a, const DeviceInfo &di) { return choose_splits(a, di); }
 
+// At most one tail CTA per 32 unquantized tokens and 8 in all (an upper bound: the launch may use one).
+int kivi_attend_mma_tail_parts(const vq_kivi_attend_args &a) {
+    return a.n_res > 0 ? (int)std::min<int64_t>(8, ceil_div(a.n_res, 32)) : 0;
+}
+
 int32_t kivi_attend_mma_take_timeout(int *flag) {
     int zero = 0;
     VQ_CHECK_CUDA(cudaMemcpyFromSymbol(flag, g_attend_timeout, sizeof(int)));
@@ -803,7 +815,10 @@ int32_t kivi_attend_mma_launch(const vq_kivi_attend_args &a, const DeviceInfo &d
     p.groups_per_warp = (int)ceil_div(p.groups_total, (int64_t)p.n_splits * kWarps);
     // a split count that leaves trailing splits empty is trimmed
     p.n_splits = (int)ceil_div(p.groups_total, (int64_t)p.groups_per_warp * kWarps);
-    p.n_parts = p.n_splits + (a.n_res > 0 ? 1 : 0);
+    // Several tail CTAs only where the quantized part is short enough for a single tail CTA to
+    // be what the launch waits for; on long contexts they would only take slots from the rest.
+    p.n_tail = p.groups_per_warp <= 8 ? kivi_attend_mma_tail_parts(a) : std::min(1, kivi_attend_mma_tail_parts(a));
+    p.n_parts = p.n_splits + p.n_tail;
     const int64_t recs = (int64_t)a.B * a.H_kv * p.n_parts * p.hpk;
     const int64_t need = recs * (kD + 2) * (int64_t)sizeof(float);
     VQ_REQUIRE(a.workspace != nullptr && a.workspace_bytes >= need, VQ_ERR_CAPACITY,
@@ -813,7 +828,7 @@ int32_t kivi_attend_mma_launch(const vq_kivi_attend_args &a, const DeviceInfo &d
     p.part_o = (float *)a.workspace;
     p.part_ml = p.part_o + recs * kD;
 
-    dim3 grid(p.n_splits * p.n_chunks + (a.n_res > 0 ? 1 : 0), a.H_kv, a.B);
+    dim3 grid(p.n_splits * p.n_chunks + p.n_tail, a.H_kv, a.B);
     const int32_t rc = a.store_bits == 4 ? launch_bits<4>(p, grid, st) : launch_bits<2>(p, grid, st);
     if (rc != VQ_OK) return rc;
     kivi_attend_mma_merge_kernel<<<(unsigned)((int64_t)a.B * a.H_q), kD, 0, st>>>(p);

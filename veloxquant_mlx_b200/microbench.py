@@ -25,14 +25,32 @@ from . import vecinfer as vi
 _DT = {"float16": torch.float16, "bfloat16": torch.bfloat16, "float32": torch.float32}
 
 
+_USE_GRAPH = False
+
+
 def _time_us(fn, iters: int) -> float:
+    """Microseconds per call. With ``--graph`` the call is captured once into a CUDA graph and the
+    graph is replayed, which takes the Python and launch overhead out of short operations."""
     for _ in range(3):
         fn()
     torch.cuda.synchronize()
+    run = fn
+    if _USE_GRAPH:
+        g = torch.cuda.CUDAGraph()
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            fn()
+        torch.cuda.current_stream().wait_stream(side)
+        with torch.cuda.graph(g):
+            fn()
+        run = g.replay
+        run()
+        torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for _ in range(iters):
-        fn()
+        run()
     e1.record()
     torch.cuda.synchronize()
     return e0.elapsed_time(e1) / iters * 1e3
@@ -107,7 +125,25 @@ def op_rabitq(a):
     _line("rabitq_attend", f"B={B} H_q=32 H_kv={H} S={S} dense f16 values", us, nbytes=B * H * S * (D // 8 + 4 + 2 * D))
 
 
-OPS = {"kivi_quantize": op_kivi_quantize, "vq_quantize": op_vq_quantize, "vq_encode": op_vq_encode,
+def op_kivi_attend(a):
+    """Decode attention over a KIVI cache at the small BASELINE shapes (config 1 and config 5, one layer)."""
+    from .cache import KVCacheConfig, KVCacheFactory
+
+    for name, B, Hq, Hkv, S, bits in (("config1", 1, 32, 8, 4096, 2), ("config5", 4, 40, 8, 16384 + 256, 2)):
+        cache = KVCacheFactory.create(KVCacheConfig(method="kivi", bit_width_inlier=bits, fused_sdpa_memory_bound=True))
+        kk = torch.randn(B, Hkv, S, 128, device="cuda", dtype=torch.float16)
+        vv = torch.randn(B, Hkv, S, 128, device="cuda", dtype=torch.float16)
+        cache.update_and_fetch(kk, vv)
+        q = torch.randn(B, Hq, 1, 128, device="cuda", dtype=torch.float16)
+        out = torch.empty_like(q)
+        us = _time_us(lambda: cache.fused_sdpa(q, 128 ** -0.5, out=out), a.iters)
+        nq = cache._n_quantized
+        R = S - nq
+        nb = B * (Hkv * (2 * nq * 128 * bits // 8 + (nq // 32) * 128 * 8 + nq * 4 * 8 + 2 * R * 128 * 2) + 2 * Hq * 128 * 2)
+        _line("kivi_attend", f"{name}: B={B} H_q={Hq} H_kv={Hkv} S={S} b={bits}", us, nbytes=nb)
+
+
+OPS = {"kivi_attend": op_kivi_attend, "kivi_quantize": op_kivi_quantize, "vq_quantize": op_vq_quantize, "vq_encode": op_vq_encode,
        "vq_attend": op_vq_attend, "rabitq": op_rabitq}
 
 
@@ -118,7 +154,10 @@ def main(argv=None):
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--batch", type=int, default=4, help="batch of the kivi_quantize shape")
     ap.add_argument("--ctx", type=int, default=32768, help="context of the kivi_quantize shape")
+    ap.add_argument("--graph", action="store_true", help="time CUDA-graph replays (GPU time without launch overhead)")
     a = ap.parse_args(argv)
+    global _USE_GRAPH
+    _USE_GRAPH = a.graph
     if not torch.cuda.is_available():
         raise SystemExit("microbench needs a CUDA device")
     for name in (sorted(OPS) if a.op == "all" else [a.op]):
