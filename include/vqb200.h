@@ -172,7 +172,7 @@ int32_t vq_predecoded_attend(const vq_kivi_attend_args *args, void *stream);
  *   part_ml float32 [rows][n_splits][2]   (m = max score of the split or -inf if it saw no
  *                                          slot, l = sum_s exp(score_s - m))
  *   out[row, :] = sum_j part_o[row][j] * exp(m_j - M) / sum_j l_j * exp(m_j - M), M = max_j m_j
- * Lets a caller that spreads one context over several calls (or devices) combine them. The
+ * n_splits <= 256. Lets a caller that spreads one context over several calls (or devices) combine them. The
  * reference merges its SIMD-group partials inside the kernel
  * (metal/src/scalar_affine_attend.metal:120-175); it has no separate entry point. */
 int32_t vq_lse_merge(const float *part_o, const float *part_ml, int64_t rows, int32_t n_splits,

@@ -180,14 +180,43 @@ coded_attend_kernel(const CodedParams p, int key_floats, int vlut_floats) {
         for (int i = threadIdx.x; i < vlut_floats; i += blockDim.x) sh_vlut[i] = i < n ? p.v_codebook[i] : 0.f;
     }
     if (p.key_mode == KEY_VQ) {
-        for (int i = threadIdx.x; i < nh * lut_stride; i += blockDim.x) {
-            const int hp = i / lut_stride, r = i % lut_stride;
-            const int s = r / p.k_nc, c = r % p.k_nc;
+        // Query rows to shared memory first; then thread c holds centroid c in registers and
+        // fills lut[head][sub][c] for every head and sub-space (writes are conflict-free, the
+        // query values are broadcast reads).
+        float *sh_q = lut + nh * lut_stride;  // [nh][D]
+        for (int i = threadIdx.x; i < nh * D; i += blockDim.x) {
+            const int hp = i / D, d = i % D;
             const int64_t qrow = ((int64_t)b * p.H_q + hkv * hpk + h0 + hp) * p.S_q + sq;
-            const float *cb = p.k_codebook + ((int64_t)(p.k_stacked ? s : 0) * p.k_nc + c) * p.k_sub;
-            float dot = 0.f;
-            for (int e = 0; e < p.k_sub; ++e) dot += load_as_f32(p.q, p.q_dtype, qrow * D + s * p.k_sub + e) * cb[e];
-            lut[i] = dot;
+            sh_q[i] = load_as_f32(p.q, p.q_dtype, qrow * D + d);
+        }
+        __syncthreads();
+        for (int c = threadIdx.x; c < p.k_nc && p.k_sub > 16; c += blockDim.x) {  // wide sub-vectors: no register copy
+            for (int s = 0; s < n_sub; ++s) {
+                const float *cb = p.k_codebook + ((int64_t)(p.k_stacked ? s : 0) * p.k_nc + c) * p.k_sub;
+                for (int hp = 0; hp < nh; ++hp) {
+                    float dot = 0.f;
+                    for (int e = 0; e < p.k_sub; ++e) dot += sh_q[hp * D + s * p.k_sub + e] * cb[e];
+                    lut[hp * lut_stride + s * p.k_nc + c] = dot;
+                }
+            }
+        }
+        for (int c = threadIdx.x; c < p.k_nc && p.k_sub <= 16; c += blockDim.x) {
+            float cbr[16];
+            for (int s = 0; s < n_sub; ++s) {
+                if (s == 0 || p.k_stacked) {
+                    const float *cb = p.k_codebook + ((int64_t)(p.k_stacked ? s : 0) * p.k_nc + c) * p.k_sub;
+#pragma unroll
+                    for (int e = 0; e < 16; ++e) cbr[e] = e < p.k_sub ? cb[e] : 0.f;
+                }
+                for (int hp = 0; hp < nh; ++hp) {
+                    const float *qs_ = sh_q + hp * D + s * p.k_sub;
+                    float dot = 0.f;
+#pragma unroll
+                    for (int e = 0; e < 16; ++e)
+                        if (e < p.k_sub) dot += qs_[e] * cbr[e];
+                    lut[hp * lut_stride + s * p.k_nc + c] = dot;
+                }
+            }
         }
     } else if (warp < nh) {
         const int64_t qrow = ((int64_t)b * p.H_q + hkv * hpk + h0 + warp) * p.S_q + sq;
@@ -440,7 +469,8 @@ int32_t launch_coded(CodedParams &p, void *workspace, int64_t workspace_bytes, i
         vlut_floats = (p.v_nc * p.v_sub + 3) & ~3;
     }
     const int nh_t = hpk <= 4 ? 4 : kHeadsC;  // heads per CTA the kernel is instantiated for
-    const int key_floats = (int)((std::max(lut_bytes * std::min(hpk, kHeadsC), (size_t)(nh_t * 9 * 4)) / 4 + 3) & ~(size_t)3);
+    const size_t vq_key_bytes = p.key_mode == KEY_VQ ? lut_bytes * std::min(hpk, kHeadsC) + (size_t)nh_t * p.D * 4 : 0;
+    const int key_floats = (int)((std::max(vq_key_bytes, (size_t)(nh_t * 9 * 4)) / 4 + 3) & ~(size_t)3);
     const size_t main_bytes = ((size_t)key_floats + vlut_floats + (size_t)kWarpsC * 32 * nh_t) * sizeof(float);
     VQ_REQUIRE(main_bytes <= di.smem_optin, VQ_ERR_CAPACITY, "%s: lookup tables of %zu bytes do not fit shared memory", who, main_bytes);
     const size_t red_bytes = ((size_t)kWarpsC * nh_t * p.D + 2 * kWarpsC * nh_t) * sizeof(float);

@@ -141,30 +141,55 @@ kivi_attend_general_kernel(const vq_kivi_attend_args a, int n_splits, int n_head
     }
 }
 
-// Combine the per-split partial softmaxes: one CTA per output row.
-__global__ void kivi_attend_merge_kernel(const float *__restrict__ part_o, const float *__restrict__ part_ml,
-                                         int n_splits, int D, void *__restrict__ out, int out_dtype) {
+// Combine the per-split partial softmaxes: one CTA per output row. The split weights
+// exp(m_s - M) are computed once into shared memory (n_splits <= 256); the sum over splits is
+// unrolled so that several independent loads are in flight (the loop is latency-bound).
+__global__ void __launch_bounds__(128)
+kivi_attend_merge_kernel(const float *__restrict__ part_o, const float *__restrict__ part_ml,
+                         int n_splits, int D, void *__restrict__ out, int out_dtype) {
+    __shared__ float sh_w[256];
+    __shared__ float sh_red[4];
     const int64_t row = blockIdx.x;
-    float gm = -INFINITY;
-    for (int s = 0; s < n_splits; ++s) gm = fmaxf(gm, part_ml[(row * n_splits + s) * 2]);
-    float gl = 0.f;
-    for (int s = 0; s < n_splits; ++s) {
-        const float m = part_ml[(row * n_splits + s) * 2];
-        gl += (m == -INFINITY) ? 0.f : part_ml[(row * n_splits + s) * 2 + 1] * __expf(m - gm);
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const float *ml = part_ml + row * n_splits * 2;
+    float m = -INFINITY;
+    for (int s = tid; s < n_splits; s += 128) m = fmaxf(m, ml[2 * s]);
+    m = warp_max(m);
+    if (lane == 0) sh_red[warp] = m;
+    __syncthreads();
+    const float gm = fmaxf(fmaxf(sh_red[0], sh_red[1]), fmaxf(sh_red[2], sh_red[3]));
+    __syncthreads();
+    float l = 0.f;
+    for (int s = tid; s < n_splits; s += 128) {
+        const float ms = ml[2 * s];
+        const float w = (ms == -INFINITY) ? 0.f : __expf(ms - gm);
+        sh_w[s] = w;
+        l += ml[2 * s + 1] * w;
     }
-    for (int d = threadIdx.x; d < D; d += blockDim.x) {
-        float o = 0.f;
-        for (int s = 0; s < n_splits; ++s) {
-            const float m = part_ml[(row * n_splits + s) * 2];
-            if (m != -INFINITY) o += part_o[(row * n_splits + s) * D + d] * __expf(m - gm);
+    l = warp_sum(l);
+    if (lane == 0) sh_red[warp] = l;
+    __syncthreads();
+    const float gl = (sh_red[0] + sh_red[1]) + (sh_red[2] + sh_red[3]);
+    const float *po = part_o + row * n_splits * D;
+    for (int d = tid; d < D; d += 128) {
+        float acc = 0.f;
+        int s = 0;
+        for (; s + 8 <= n_splits; s += 8) {
+            float v[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) v[u] = po[(int64_t)(s + u) * D + d];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) acc = fmaf(v[u], sh_w[s + u], acc);
         }
-        store_from_f32(out, out_dtype, row * D + d, o / gl);
+        for (; s < n_splits; ++s) acc = fmaf(po[(int64_t)s * D + d], sh_w[s], acc);
+        store_from_f32(out, out_dtype, row * D + d, acc / gl);
     }
 }
 
 int32_t launch_split_merge(const float *part_o, const float *part_ml, int n_splits, int D, void *out,
                            int out_dtype, int64_t rows, cudaStream_t st) {
     VQ_REQUIRE(rows < (1ll << 31), VQ_ERR_SHAPE, "split merge: too many output rows");
+    VQ_REQUIRE(n_splits <= 256, VQ_ERR_SHAPE, "split merge: at most 256 splits, got %d", n_splits);
     kivi_attend_merge_kernel<<<(unsigned)rows, 128, 0, st>>>(part_o, part_ml, n_splits, D, out, out_dtype);
     VQ_CHECK_LAUNCH("kivi_attend_merge_kernel");
     return VQ_OK;
@@ -193,7 +218,7 @@ static int32_t validate(const vq_kivi_attend_args &a) {
 }
 
 static int general_splits(const vq_kivi_attend_args &a, int sm_count) {
-    if (a.n_splits > 0) return a.n_splits;
+    if (a.n_splits > 0) return std::min(a.n_splits, 256);
     const int total = a.n_quant + a.n_res;
     const int hpk = a.H_q / a.H_kv;
     const int64_t ctas = (int64_t)a.B * a.H_kv * a.S_q * ceil_div(hpk, kGenHeads);
