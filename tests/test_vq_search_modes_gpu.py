@@ -1,6 +1,7 @@
-"""The tcgen05 / tensor-memory nearest-centroid search (opt-in: VQ_VQ_SEARCH=tc5) must return
-exactly the indices of the reference evaluation order. The switch is read once per process,
-so the check runs in a child process."""
+"""Each nearest-centroid search pinned with VQ_VQ_SEARCH -- tc5 (tcgen05 + tensor memory), mma
+(warp-level MMAs), exact (CUDA cores) -- must return exactly the indices of the reference
+evaluation order on the same inputs. The switch is read once per process, so each mode is
+checked in a child process."""
 
 from __future__ import annotations
 
@@ -45,11 +46,12 @@ cbr = rng.standard_normal((256, 8)).astype(np.float32)
 check(xb, cbr, "bad rows")
 check(xb, cbr * 100, "large codebook")
 check(xb, np.zeros((16, 8), np.float32), "zero codebook")
-print("tc5 ok")
+print("search ok")
 """
 
 
-def test_tcgen05_search_matches_the_reference_order():
-    env = dict(os.environ, VQ_VQ_SEARCH="tc5")
+@pytest.mark.parametrize("mode", ["tc5", "mma", "exact"])
+def test_pinned_search_matches_the_reference_order(mode):
+    env = dict(os.environ, VQ_VQ_SEARCH=mode)
     out = subprocess.run([sys.executable, "-c", _CHILD % ROOT], env=env, capture_output=True, text=True, timeout=600)
-    assert out.returncode == 0 and "tc5 ok" in out.stdout, out.stdout[-2000:] + out.stderr[-4000:]
+    assert out.returncode == 0 and "search ok" in out.stdout, out.stdout[-2000:] + out.stderr[-4000:]

@@ -149,6 +149,7 @@ struct Tc5Smem {
     uint32_t tmem_base;
     float cmax2;
     int cb_bad;
+    int timeout;
 };
 
 constexpr int kThreads = 2 * kRows;  // two warpgroups: each owns one half of the columns of every row
@@ -225,7 +226,7 @@ vq_quantize_tc5_kernel(const __half *__restrict__ x, int64_t n, const float *__r
     const int N = n_c;                 // a multiple of 16, <= 256
 
     // ---- one-time set-up: operand tiles that do not change, barrier, tensor memory ----------
-    if (tid == 0) { sm.cmax2 = 0.f; sm.cb_bad = 0; }
+    if (tid == 0) { sm.cmax2 = 0.f; sm.cb_bad = 0; sm.timeout = 0; }
     __syncthreads();
     for (int i = tid; i < 2 * kRows * 16 / 4; i += kThreads) reinterpret_cast<uint32_t *>(sm.a2)[i] = 0u;
     for (int i = tid; i < 2 * 256 * 16 / 4; i += kThreads) reinterpret_cast<uint32_t *>(sm.b2)[i] = 0u;
@@ -340,8 +341,15 @@ vq_quantize_tc5_kernel(const __half *__restrict__ x, int64_t n, const float *__r
                 bad |= !(fabsf(f.x) <= 32768.f && fabsf(f.y) <= 32768.f);
             }
         }
-        if (!timed_out && !mbar_wait(bar, phase)) timed_out = true;
+        // One thread polls the completion barrier; the others block on the CTA barrier, which
+        // costs no issue slots (256 spinning threads took a fifth of the SM's issue slots away
+        // from the other CTA's epilogue).
+        if (tid == 0) {
+            if (!timed_out && !mbar_wait(bar, phase)) sm.timeout = 1;
+        }
         phase ^= 1u;
+        __syncthreads();
+        timed_out = sm.timeout != 0;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 
         // ---- pass 1: the row's best score (each half of the columns, then exchanged) ----------
@@ -388,11 +396,13 @@ vq_quantize_tc5_kernel(const __half *__restrict__ x, int64_t n, const float *__r
 }  // namespace
 
 bool vq_quantize_tc5_supported(const void *x, int32_t x_dtype, int64_t n, int32_t sub_dim, int32_t n_c, int32_t n_sub) {
-    static const char *mode = std::getenv("VQ_VQ_SEARCH");
-    if (!(mode && std::strcmp(mode, "tc5") == 0)) return false;  // opt-in until it is the measured default
+    static const char *mode = std::getenv("VQ_VQ_SEARCH");  // "exact" / "mma" / "tc5" pin one search
+    if (mode && (std::strcmp(mode, "exact") == 0 || std::strcmp(mode, "mma") == 0)) return false;
     if (x_dtype != VQ_F16 || sub_dim != kSub || n_sub != 0) return false;
     if (n_c < 16 || n_c > 256 || n_c % 16) return false;
-    return is_aligned(x, 16) && n >= 1;
+    if (!is_aligned(x, 16)) return false;
+    const bool forced = mode && std::strcmp(mode, "tc5") == 0;
+    return forced ? n >= 1 : n >= 4096;  // small inputs: the CUDA-core search has no set-up cost
 }
 
 int32_t vq_quantize_tc5_launch(const void *x, int64_t n, const float *cb, int32_t n_c, void *indices, int32_t index_bytes,
