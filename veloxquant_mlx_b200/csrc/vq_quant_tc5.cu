@@ -308,16 +308,44 @@ vq_quantize_tc5_kernel(const __half *__restrict__ x, int64_t n, const float *__r
         asm volatile("cp.async.commit_group;" ::: "memory");
     };
 
+    // Per tile: [barrier A] MMAs of this tile issued | results of the previous tile written, next
+    // tile of x requested, row norms | [barrier B] MMAs done | pass 1 | [barrier C] | pass 2.
+    // The MMAs therefore run under the previous tile's result handling.
     int64_t tile = blockIdx.x;
     if (tile < n_tiles) fetch(tile, 0);
     uint32_t phase = 0;
     bool timed_out = false;
+    // results of the previous tile, finished after barrier A of the next one
+    float prev_acc = 0.f, prev_base = 0.f;
+    bool prev_bad = false, have_prev = false;
+    int64_t prev_tile = 0;
+    auto finish_prev = [&]() {
+        if (!have_prev || half != 0) return;
+        const int64_t row = prev_tile * kRows + r;
+        const float acc = prev_acc + sm.xch_acc[r], base = prev_base + sm.xch_base[r];
+        const bool slow = prev_bad || !(acc >= 65536.f && acc < 131072.f);
+        uint32_t idx = (uint32_t)((int)acc - 65536 + (int)base) & 0xffffu;
+        // rows that need the reference order: the whole warp works on each in turn
+        uint32_t slow_mask = __ballot_sync(0xffffffffu, slow && row < n && !timed_out);
+        while (slow_mask) {
+            const int src = __ffs(slow_mask) - 1;
+            slow_mask &= slow_mask - 1;
+            const int64_t srow = prev_tile * kRows + warp * 32 + src;
+            const uint32_t e = exact_row8(x + srow * kSub, cb, n_c, lane);
+            if (lane == src) idx = e;
+        }
+        if (row < n && !timed_out) {
+            if (index_bytes == 1) reinterpret_cast<uint8_t *>(indices)[row] = (uint8_t)idx;
+            else if (index_bytes == 2) reinterpret_cast<uint16_t *>(indices)[row] = (uint16_t)idx;
+            else reinterpret_cast<uint32_t *>(indices)[row] = idx;
+        }
+    };
     for (int it = 0; tile < n_tiles; tile += gridDim.x, ++it) {
         const int stage = it & 1;
         asm volatile("cp.async.wait_group 0;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-        __syncthreads();  // the tile of x is in place; the previous epilogue has released tensor memory
+        __syncthreads();  // A: this tile of x is in place; pass 2 of the previous tile has released tensor memory
         if (tid == 0) {
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const uint64_t desc_a = make_desc(smem_u32(sm.a[stage][0]), lbo_a, sbo_a);
@@ -325,10 +353,10 @@ vq_quantize_tc5_kernel(const __half *__restrict__ x, int64_t n, const float *__r
             mma_f16_ss(tmem, desc_a2, desc_b2, idesc, 1u);
             asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
         }
+        finish_prev();
         if (tile + gridDim.x < n_tiles) fetch(tile + gridDim.x, stage ^ 1);
 
         // this thread's row: squared norm and range check from the shared-memory copy
-        const int64_t row = tile * kRows + r;
         float xn = 0.f;
         bool bad = !cb_ok;
         {
@@ -348,41 +376,24 @@ vq_quantize_tc5_kernel(const __half *__restrict__ x, int64_t n, const float *__r
             if (!timed_out && !mbar_wait(bar, phase)) sm.timeout = 1;
         }
         phase ^= 1u;
-        __syncthreads();
+        __syncthreads();  // B
         timed_out = sm.timeout != 0;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 
         // ---- pass 1: the row's best score (each half of the columns, then exchanged) ----------
         sm.xch_m[half][r] = timed_out ? 0.f : pass_max(taddr, c_lo, c_hi);
-        __syncthreads();
+        __syncthreads();  // C
         const float m = fmaxf(sm.xch_m[0][r], sm.xch_m[1][r]);
         const float thr = m - 1.52587890625e-05f * (xn + cmax2);
         // ---- pass 2: count and name the scores within delta of it ----------------------------
         float acc = 0.f, base = 0.f;
         if (!timed_out) pass_count(taddr, c_lo, c_hi, thr, acc, base);
         if (half) { sm.xch_acc[r] = acc; sm.xch_base[r] = base; }
-        __syncthreads();
-        if (half == 0) {
-            acc += sm.xch_acc[r];
-            base += sm.xch_base[r];
-            const bool slow = bad || !(acc >= 65536.f && acc < 131072.f);
-            uint32_t idx = (uint32_t)((int)acc - 65536 + (int)base) & 0xffffu;
-            // rows that need the reference order: the whole warp works on each in turn
-            uint32_t slow_mask = __ballot_sync(0xffffffffu, slow && row < n && !timed_out);
-            while (slow_mask) {
-                const int src = __ffs(slow_mask) - 1;
-                slow_mask &= slow_mask - 1;
-                const int64_t srow = tile * kRows + warp * 32 + src;
-                const uint32_t e = exact_row8(x + srow * kSub, cb, n_c, lane);
-                if (lane == src) idx = e;
-            }
-            if (row < n && !timed_out) {
-                if (index_bytes == 1) reinterpret_cast<uint8_t *>(indices)[row] = (uint8_t)idx;
-                else if (index_bytes == 2) reinterpret_cast<uint16_t *>(indices)[row] = (uint16_t)idx;
-                else reinterpret_cast<uint32_t *>(indices)[row] = idx;
-            }
-        }
+        prev_acc = acc; prev_base = base; prev_bad = bad; prev_tile = tile; have_prev = true;
     }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    finish_prev();
     if (timed_out && lane == 0) atomicExch(&g_tc5_timeout, 1);
     // ---- release tensor memory on every path ---------------------------------------------------
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
