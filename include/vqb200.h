@@ -156,7 +156,7 @@ typedef struct vq_kivi_attend_args {
 int64_t vq_kivi_attend_workspace_bytes(const vq_kivi_attend_args *args);
 int32_t vq_kivi_decode_attend(const vq_kivi_attend_args *args, void *stream);
 /* Synchronises the device, then reports (and clears) whether any earlier
- * vq_kivi_decode_attend kernel abandoned a bounded device-side wait: VQ_ERR_TIMEOUT if so
+ * vq_kivi_decode_attend or vq_rabitq_decode_attend kernel abandoned a bounded device-side wait: VQ_ERR_TIMEOUT if so
  * (its output is then invalid), VQ_OK otherwise. No counterpart in the reference (its
  * kernels have no device-side waits). */
 int32_t vq_kivi_attend_status(void);

@@ -140,5 +140,6 @@ def test_rabitq_cache_matches_oracle_and_composes():
     assert np.all(err <= 2e-3 + 1e-2 * np.abs(ref)), err.max()
     d = _make("rabitq", head_dim=D, seed=7)
     d.state = c.state
-    assert torch.equal(d.fused_sdpa(q, scale), out)
+    # the restored cache holds exact-size buffers, which take the plain-load kernel: same math, other summation order
+    torch.testing.assert_close(d.fused_sdpa(q, scale).float(), out.float(), atol=2e-3, rtol=1e-2)
     assert c.trim(10) == 10 and c.offset == S - 10

@@ -170,3 +170,31 @@ def test_encode_then_attend_composes():
     ref = o_rq.reference_attend(q, q_scale, bits.cpu().numpy().reshape(B, H, S, D // 8),
                                 mag.cpu().numpy().reshape(B, H, S), np.zeros((B, H, S), np.float32), v)
     assert np.all(np.abs(out.float().cpu().numpy() - ref) <= 2e-3 + 1e-2 * np.abs(ref))
+
+
+@pytest.mark.parametrize("dt", ["float16", "bfloat16"])
+@pytest.mark.parametrize("H,H_kv,S_q", [(8, 8, 1), (8, 2, 2), (16, 2, 1)])
+@pytest.mark.parametrize("S,cap", [(32, 32), (1000, 1024), (4097, 4352)])
+def test_staged_kernel_dense_values(dt, H, H_kv, S_q, S, cap):
+    """Buffers that hold whole 32-key tiles take the bulk-copy staged kernel (head_dim 128, dense
+    16-bit values); the same data in buffers that do not must give the same answer."""
+    r = _r()
+    B, D = 2, 128
+    tdt = torch.float16 if dt == "float16" else torch.bfloat16
+    q, q_scale, k_bits, k_mag, k_const, _, _ = _attend_inputs(B, H, S_q, cap, D, seed=S + H + S_q, H_kv=H_kv)
+    v = torch.from_numpy(np.random.default_rng(S).standard_normal((B, H_kv, cap, D)).astype(np.float32)).to(tdt)
+    for kc in (k_const, None):
+        out = r.rabitq_fused_attend(_t(q), _t(q_scale), _t(k_bits), _t(k_mag), None if kc is None else _t(kc),
+                                    v.to(DEV), None, s_kv=S)
+        ref = o_rq.reference_attend(q, q_scale, k_bits[:, :, :S], k_mag[:, :, :S],
+                                    np.zeros((B, H_kv, S), np.float32) if kc is None else kc[:, :, :S],
+                                    v[:, :, :S].float().numpy())
+        got = out.float().cpu().numpy()
+        assert np.all(np.abs(got - ref) <= 2e-3 + 1e-2 * np.abs(ref)), np.abs(got - ref).max()
+        # exact-size buffers with an odd length cannot be staged
+        if S % 4:
+            plain = r.rabitq_fused_attend(_t(q), _t(q_scale), _t(k_bits[:, :, :S].copy()), _t(k_mag[:, :, :S].copy()),
+                                          None if kc is None else _t(kc[:, :, :S].copy()), v[:, :, :S].contiguous().to(DEV), None)
+            torch.testing.assert_close(out.float(), plain.float(), atol=2e-3, rtol=1e-2)
+    from veloxquant_mlx_b200._lib import lib
+    assert lib().vq_kivi_attend_status() == 0

@@ -418,6 +418,233 @@ coded_attend_kernel(const CodedParams p, int key_floats, int vlut_floats) {
     }
 }
 
+// ---- RaBitQ over dense 16-bit values, head_dim 128: staged through shared memory ------------
+// The same attention as coded_attend_kernel for the serving shape, with the key bits, key
+// magnitudes (and constants) and the value rows of each 32-key tile brought in by the bulk
+// async-copy engine: every warp runs its own two-stage cp.async.bulk + mbarrier pipeline
+// (4 contiguous pieces per tile, 8.7-8.9 KB), so HBM reads stay in flight while the warp
+// scores and accumulates. Waits are bounded; a timeout raises a device flag that
+// vq_kivi_attend_status() reports.
+constexpr int kStWarps = 4, kStStages = 2;
+constexpr int kStMag = 512, kStConst = 640, kStV = 768, kStBytes = 768 + 32 * 256;  // one warp, one stage
+constexpr uint32_t kStSpin = 1u << 18;
+__device__ int g_coded_timeout = 0;
+
+__device__ __forceinline__ uint32_t st_smem_u32(const void *ptr) { return (uint32_t)__cvta_generic_to_shared(ptr); }
+__device__ __forceinline__ bool st_mbar_wait(uint32_t bar, uint32_t parity) {
+    for (uint32_t i = 0; i < kStSpin; ++i) {
+        uint32_t ok;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+        if (ok) return true;
+    }
+    return false;
+}
+__device__ __forceinline__ void st_bulk_g2s(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst), "l"(src),
+                 "r"(bytes), "r"(bar) : "memory");
+}
+
+template <bool VBF16, int NH>
+__global__ void __launch_bounds__(kStWarps * 32, 3)
+rabitq_attend_staged_kernel(const CodedParams p) {
+    extern __shared__ __align__(128) uint8_t st_raw[];
+    constexpr int D = 128, DPL = 4;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int split = blockIdx.x;
+    int y = blockIdx.y;
+    const int hc = y % p.n_head_chunks; y /= p.n_head_chunks;
+    const int sq = y % p.S_q;
+    const int hkv = y / p.S_q;
+    const int b = blockIdx.z;
+    const int hpk = p.H_q / p.H_kv;
+    const int h0 = hc * kHeadsC;
+    const int nh = min(NH, hpk - h0);
+    const int64_t bh = (int64_t)b * p.H_kv + hkv;
+
+    // shared: barriers | query sign words [NH][4] | query scales [NH] | weights [warp][32][NH] | stages
+    uint64_t *bars = reinterpret_cast<uint64_t *>(st_raw);
+    uint32_t *sh_qbits = reinterpret_cast<uint32_t *>(st_raw + 64);
+    float *sh_qs = reinterpret_cast<float *>(st_raw + 64 + NH * 16);
+    float *sh_w = reinterpret_cast<float *>(st_raw + 256) + warp * (32 * NH);
+    uint8_t *stages = st_raw + 256 + kStWarps * 32 * NH * 4 + (size_t)warp * kStStages * kStBytes;
+    const uint32_t wbar0 = st_smem_u32(bars) + 8u * (warp * kStStages);
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < kStWarps * kStStages; ++i)
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(st_smem_u32(bars) + 8u * i));
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    for (int h = warp; h < nh; h += kStWarps) {
+        const int64_t qrow = ((int64_t)b * p.H_q + hkv * hpk + h0 + h) * p.S_q + sq;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+            const float v = load_as_f32(p.q, p.q_dtype, qrow * D + 32 * w + lane);
+            const uint32_t bits = __ballot_sync(0xffffffffu, v >= 0.f);
+            if (lane == 0) sh_qbits[h * 4 + w] = bits;
+        }
+        if (lane == 0) sh_qs[h] = p.q_scale[qrow];
+    }
+    __syncthreads();
+
+    // this CTA's keys: whole 32-key tiles; warp w takes tiles w, w + 4, ...
+    const int chunk = (((p.S_kv + p.n_splits - 1) / p.n_splits) + 31) & ~31;
+    const int t_begin = split * chunk;
+    const int t_end = min(p.S_kv, t_begin + chunk);
+    const int n_tiles = t_begin < t_end ? (t_end - t_begin + 31) / 32 : 0;
+    const int n_local = warp < n_tiles ? (n_tiles - warp + kStWarps - 1) / kStWarps : 0;
+    const uint8_t *kb_g = reinterpret_cast<const uint8_t *>(p.k_codes) + bh * p.stride_tok * 16;
+    const float *km_g = p.k_mag + bh * p.stride_tok;
+    const float *kc_g = p.k_const ? p.k_const + bh * p.stride_tok : nullptr;
+    const uint8_t *v_g = reinterpret_cast<const uint8_t *>(p.v) + bh * p.stride_tok * 256;
+
+    auto issue = [&](int j) {  // lane 0 only
+        const int64_t tile = t_begin + 32 * (warp + kStWarps * j);
+        const int stage = j % kStStages;
+        const uint32_t bar = wbar0 + 8u * stage;
+        const uint32_t dst = st_smem_u32(stages + (size_t)stage * kStBytes);
+        const uint32_t bytes = 512 + 128 + (kc_g ? 128 : 0) + 32 * 256;
+        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+        st_bulk_g2s(dst, kb_g + tile * 16, 512, bar);
+        st_bulk_g2s(dst + kStMag, km_g + tile, 128, bar);
+        if (kc_g) st_bulk_g2s(dst + kStConst, kc_g + tile, 128, bar);
+        st_bulk_g2s(dst + kStV, v_g + tile * 256, 32 * 256, bar);
+    };
+    if (lane == 0)
+        for (int j = 0; j < kStStages - 1 && j < n_local; ++j) issue(j);
+
+    float m_run[NH], l_run[NH], acc[NH][DPL];
+#pragma unroll
+    for (int h = 0; h < NH; ++h) {
+        m_run[h] = -INFINITY; l_run[h] = 0.f;
+#pragma unroll
+        for (int i = 0; i < DPL; ++i) acc[h][i] = 0.f;
+    }
+    bool timed_out = false;
+    for (int j = 0; j < n_local; ++j) {
+        __syncwarp();  // every lane is done with the stage that is refilled next
+        if (lane == 0 && j + kStStages - 1 < n_local) {
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            issue(j + kStStages - 1);
+        }
+        const int stage = j % kStStages;
+        if (!timed_out && !st_mbar_wait(wbar0 + 8u * stage, (uint32_t)((j / kStStages) & 1))) timed_out = true;
+        const uint8_t *st = stages + (size_t)stage * kStBytes;
+        const int tile = t_begin + 32 * (warp + kStWarps * j);
+        const bool valid = tile + lane < t_end;
+        // ---- scores of this lane's key against every head ---------------------------------
+        const uint4 kw = *reinterpret_cast<const uint4 *>(st + lane * 16);
+        const float km = reinterpret_cast<const float *>(st + kStMag)[lane];
+        const float kc = kc_g ? reinterpret_cast<const float *>(st + kStConst)[lane] : 0.f;
+        float w[NH];
+#pragma unroll
+        for (int h = 0; h < NH; ++h) {
+            const uint32_t *qb = sh_qbits + (h < nh ? h : 0) * 4;
+            const int ham = __popc(qb[0] ^ kw.x) + __popc(qb[1] ^ kw.y) + __popc(qb[2] ^ kw.z) + __popc(qb[3] ^ kw.w);
+            const float s = ((float)D - 2.0f * (float)ham) * sh_qs[h < nh ? h : 0] * km + kc;
+            w[h] = valid ? s : -INFINITY;
+        }
+        // ---- online softmax per head ------------------------------------------------------
+#pragma unroll
+        for (int h = 0; h < NH; ++h) {
+            if (h < nh) {
+                const float tile_max = warp_max(w[h]);  // at least lane 0 of a tile is valid
+                const float m_new = fmaxf(m_run[h], tile_max);
+                const float factor = (m_run[h] == -INFINITY) ? 0.f : __expf(m_run[h] - m_new);
+                m_run[h] = m_new;
+                w[h] = valid ? __expf(w[h] - m_new) : 0.f;
+                l_run[h] = l_run[h] * factor + warp_sum(w[h]);
+#pragma unroll
+                for (int i = 0; i < DPL; ++i) acc[h][i] *= factor;
+            } else {
+                w[h] = 0.f;
+            }
+        }
+        // ---- values from shared memory: one 8-byte read per row and lane --------------------
+        __syncwarp();
+        *reinterpret_cast<float4 *>(sh_w + lane * NH) = make_float4(w[0], w[1], w[2], w[3]);
+        if constexpr (NH == 8) *reinterpret_cast<float4 *>(sh_w + lane * NH + 4) = make_float4(w[4], w[5], w[6], w[7]);
+        __syncwarp();
+#pragma unroll 8
+        for (int r = 0; r < 32; ++r) {
+            const uint2 raw = *reinterpret_cast<const uint2 *>(st + kStV + r * 256 + lane * 8);
+            float v[4];
+            if constexpr (VBF16) {
+                v[0] = __uint_as_float(raw.x << 16); v[1] = __uint_as_float(raw.x & 0xffff0000u);
+                v[2] = __uint_as_float(raw.y << 16); v[3] = __uint_as_float(raw.y & 0xffff0000u);
+            } else {
+                const float2 f0 = __half22float2(*reinterpret_cast<const __half2 *>(&raw.x));
+                const float2 f1 = __half22float2(*reinterpret_cast<const __half2 *>(&raw.y));
+                v[0] = f0.x; v[1] = f0.y; v[2] = f1.x; v[3] = f1.y;
+            }
+            const float4 wa = *reinterpret_cast<const float4 *>(sh_w + r * NH);
+            const float wl4[4] = {wa.x, wa.y, wa.z, wa.w};
+#pragma unroll
+            for (int h = 0; h < 4; ++h)
+#pragma unroll
+                for (int i = 0; i < DPL; ++i) acc[h][i] = fmaf(wl4[h], v[i], acc[h][i]);
+            if constexpr (NH == 8) {
+                const float4 wb = *reinterpret_cast<const float4 *>(sh_w + r * NH + 4);
+                const float wh4[4] = {wb.x, wb.y, wb.z, wb.w};
+#pragma unroll
+                for (int h = 0; h < 4; ++h)
+#pragma unroll
+                    for (int i = 0; i < DPL; ++i) acc[4 + h][i] = fmaf(wh4[h], v[i], acc[4 + h][i]);
+            }
+        }
+    }
+    if (timed_out && lane == 0) atomicExch(&g_coded_timeout, 1);
+
+    // ---- merge the warps of this CTA (the stages are drained: reuse them) ----------------------
+    __syncthreads();
+    float *red_o = reinterpret_cast<float *>(st_raw + 256 + kStWarps * 32 * NH * 4);  // [warps][heads][D]
+    float *red_m = red_o + kStWarps * NH * D;
+    float *red_l = red_m + kStWarps * NH;
+#pragma unroll
+    for (int h = 0; h < NH; ++h) {
+        if (h < nh) {
+#pragma unroll
+            for (int i = 0; i < DPL; ++i) red_o[(warp * NH + h) * D + lane * DPL + i] = acc[h][i];
+            if (lane == 0) { red_m[warp * NH + h] = m_run[h]; red_l[warp * NH + h] = l_run[h]; }
+        }
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < nh * D; i += blockDim.x) {
+        const int h = i / D, d = i % D;
+        float gm = -INFINITY;
+        for (int wq = 0; wq < kStWarps; ++wq) gm = fmaxf(gm, red_m[wq * NH + h]);
+        float gl = 0.f, o = 0.f;
+        for (int wq = 0; wq < kStWarps; ++wq) {
+            const float mw = red_m[wq * NH + h];
+            const float f = (mw == -INFINITY) ? 0.f : __expf(mw - gm);
+            gl += red_l[wq * NH + h] * f;
+            o += red_o[(wq * NH + h) * D + d] * f;
+        }
+        const int64_t qrow = ((int64_t)b * p.H_q + hkv * hpk + h0 + h) * p.S_q + sq;
+        if (p.n_splits == 1) {
+            store_from_f32(p.out, p.out_dtype, qrow * D + d, o / fmaxf(gl, 1e-20f));
+        } else {
+            p.part_o[(qrow * p.n_splits + split) * D + d] = o;
+            if (d == 0) {
+                p.part_ml[(qrow * p.n_splits + split) * 2] = gm;
+                p.part_ml[(qrow * p.n_splits + split) * 2 + 1] = gl;
+            }
+        }
+    }
+}
+
+// Can `p` take the staged kernel? Whole tiles are copied, so the buffers must hold the context
+// rounded up to 32 keys, and every copied piece must start on a 16-byte boundary.
+bool staged_ok(const CodedParams &p) {
+    if (p.key_mode != KEY_RABITQ || p.D != 128 || p.v_mode != V_DENSE) return false;
+    if (p.v_dtype != VQ_F16 && p.v_dtype != VQ_BF16) return false;
+    if (p.stride_tok % 4 || p.stride_tok < (((int64_t)p.S_kv + 31) & ~(int64_t)31)) return false;
+    if (!is_aligned(p.k_codes, 16) || !is_aligned(p.k_mag, 16) || !is_aligned(p.v, 16)) return false;
+    if (p.k_const && !is_aligned(p.k_const, 16)) return false;
+    return true;
+}
+
 int pick_splits(int requested, int S_kv, int64_t ctas, int sm_count) {
     if (requested > 0) return std::min(requested, 256);
     // About four CTAs per SM (finer splits cost more in set-up and in the merge than they win
@@ -452,6 +679,24 @@ int32_t launch_coded(CodedParams &p, void *workspace, int64_t workspace_bytes, i
                    "%s: workspace of %lld bytes needed, %lld given", who, (long long)need, (long long)workspace_bytes);
         p.part_o = (float *)workspace;
         p.part_ml = p.part_o + rows * p.n_splits * p.D;
+    }
+    if (staged_ok(p)) {
+        const int nh_s = hpk <= 4 ? 4 : kHeadsC;
+        const size_t st_red = ((size_t)kStWarps * nh_s * p.D + 2 * kStWarps * nh_s) * sizeof(float);
+        const size_t st_smem = 256 + (size_t)kStWarps * 32 * nh_s * 4 + std::max((size_t)kStWarps * kStStages * kStBytes, st_red);
+        dim3 sgrid(p.n_splits, (unsigned)gy, p.B);
+#define VQ_STAGED(BF, NHT)                                                                                      \
+    do {                                                                                                        \
+        VQ_CHECK_CUDA(cudaFuncSetAttribute(rabitq_attend_staged_kernel<BF, NHT>,                                 \
+                                           cudaFuncAttributeMaxDynamicSharedMemorySize, (int)st_smem));         \
+        rabitq_attend_staged_kernel<BF, NHT><<<sgrid, kStWarps * 32, st_smem, st>>>(p);                         \
+    } while (0)
+        if (p.v_dtype == VQ_BF16) { if (nh_s == 4) VQ_STAGED(true, 4); else VQ_STAGED(true, 8); }
+        else { if (nh_s == 4) VQ_STAGED(false, 4); else VQ_STAGED(false, 8); }
+#undef VQ_STAGED
+        VQ_CHECK_LAUNCH("rabitq_attend_staged_kernel");
+        if (p.n_splits > 1) return launch_split_merge(p.part_o, p.part_ml, p.n_splits, p.D, p.out, p.out_dtype, rows, st);
+        return VQ_OK;
     }
     // Specialised value access where the row layout allows vector loads.
     const int dpl = p.D / 32;
@@ -520,6 +765,14 @@ int64_t coded_workspace(int B, int H_q, int S_q, int D, int n_splits) {
 }
 
 }  // namespace
+
+int32_t coded_attend_take_timeout(int *flag) {
+    int zero = 0;
+    VQ_CHECK_CUDA(cudaMemcpyFromSymbol(flag, g_coded_timeout, sizeof(int)));
+    if (*flag) VQ_CHECK_CUDA(cudaMemcpyToSymbol(g_coded_timeout, &zero, sizeof(int)));
+    return VQ_OK;
+}
+
 }  // namespace vq
 
 extern "C" int64_t vq_vq_attend_workspace_bytes(const vq_vq_attend_args *a) {

@@ -246,10 +246,13 @@ extern "C" int64_t vq_kivi_attend_workspace_bytes(const vq_kivi_attend_args *arg
 
 extern "C" int32_t vq_kivi_attend_status(void) {
     using namespace vq;
-    int flag = 0;
+    int flag = 0, flag2 = 0;
     int32_t rc = kivi_attend_mma_take_timeout(&flag);
     if (rc != VQ_OK) return rc;
+    rc = coded_attend_take_timeout(&flag2);
+    if (rc != VQ_OK) return rc;
     if (flag) return fail(VQ_ERR_TIMEOUT, "vq_kivi_decode_attend: a bounded wait on a bulk-copy barrier gave up");
+    if (flag2) return fail(VQ_ERR_TIMEOUT, "vq_rabitq_decode_attend: a bounded wait on a bulk-copy barrier gave up");
     return VQ_OK;
 }
 
