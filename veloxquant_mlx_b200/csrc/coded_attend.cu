@@ -645,6 +645,23 @@ bool staged_ok(const CodedParams &p) {
     return true;
 }
 
+// Split count for a kernel that keeps `per_sm` CTAs of this kind resident per SM: the count
+// that minimises (waves of CTAs) x (keys per CTA + a fixed set-up cost in keys), so that the
+// last wave is not mostly idle. `unit` = keys per indivisible piece of a split.
+int pick_splits_waves(int requested, int S_kv, int64_t ctas, int sm_count, int per_sm, int unit) {
+    if (requested > 0) return std::min(requested, 256);
+    const int64_t slots = (int64_t)sm_count * per_sm;
+    const int max_splits = (int)std::max<int64_t>(1, std::min<int64_t>(256, ceil_div(S_kv, 8 * unit)));
+    int best = 1;
+    int64_t best_cost = INT64_MAX;
+    for (int n = 1; n <= max_splits; ++n) {
+        const int64_t per_cta = ceil_div(ceil_div(S_kv, n), unit) * unit + 96;
+        const int64_t cost = ceil_div(ctas * n, slots) * per_cta;
+        if (cost < best_cost) { best_cost = cost; best = n; }
+    }
+    return best;
+}
+
 int pick_splits(int requested, int S_kv, int64_t ctas, int sm_count) {
     if (requested > 0) return std::min(requested, 256);
     // About four CTAs per SM (finer splits cost more in set-up and in the merge than they win
@@ -671,7 +688,8 @@ int32_t launch_coded(CodedParams &p, void *workspace, int64_t workspace_bytes, i
     p.n_head_chunks = (int)ceil_div(hpk, kHeadsC);
     const int64_t gy = (int64_t)p.H_kv * p.S_q * p.n_head_chunks;
     VQ_REQUIRE(gy <= 65535 && p.B <= 65535, VQ_ERR_SHAPE, "%s: grid too large", who);
-    p.n_splits = pick_splits(requested_splits, p.S_kv, gy * p.B, di.sm_count);
+    p.n_splits = staged_ok(p) ? pick_splits_waves(requested_splits, p.S_kv, gy * p.B, di.sm_count, 3, 32)
+                              : pick_splits(requested_splits, p.S_kv, gy * p.B, di.sm_count);
     const int64_t rows = (int64_t)p.B * p.H_q * p.S_q;
     if (p.n_splits > 1) {
         const int64_t need = rows * p.n_splits * ((int64_t)p.D + 2) * (int64_t)sizeof(float);
