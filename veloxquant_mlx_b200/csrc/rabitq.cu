@@ -7,6 +7,7 @@
 // operation on the same operands and the result is bit-identical however the pairs are
 // spread over lanes. Sign bits are packed with ballots (32 bits = 4 output bytes).
 #include <algorithm>
+#include <type_traits>
 
 #include "common.cuh"
 
@@ -66,11 +67,47 @@ rabitq_encode_kernel(const T *__restrict__ keys, int64_t n, int D, const float *
 // larger strides pair lane l with lane l ^ (stride / EPL) through a shuffle. Every pair is
 // still (lower + upper, lower - upper), so the result is bit-identical to the shared-memory
 // kernel and to the reference's sequential loop.
+// EPL consecutive elements as floats with the widest aligned load (the caller guarantees a
+// 16-byte aligned base; rows are D elements apart, so EPL * sizeof(T) divides every offset).
+template <typename T, int EPL>
+__device__ __forceinline__ void load_epl(const T *p, float (&v)[EPL]) {
+    if constexpr (sizeof(T) == 4) {
+        if constexpr (EPL % 4 == 0) {
+#pragma unroll
+            for (int i = 0; i < EPL / 4; ++i) {
+                const float4 f = __ldg(reinterpret_cast<const float4 *>(p) + i);
+                v[4 * i] = f.x; v[4 * i + 1] = f.y; v[4 * i + 2] = f.z; v[4 * i + 3] = f.w;
+            }
+        } else if constexpr (EPL == 2) {
+            const float2 f = __ldg(reinterpret_cast<const float2 *>(p));
+            v[0] = f.x; v[1] = f.y;
+        } else {
+            v[0] = __ldg(reinterpret_cast<const float *>(p));
+        }
+    } else {
+        uint32_t w[(EPL + 1) / 2];
+        if constexpr (EPL == 8) { const uint4 t = __ldg(reinterpret_cast<const uint4 *>(p)); w[0] = t.x; w[1] = t.y; w[2] = t.z; w[3] = t.w; }
+        else if constexpr (EPL == 4) { const uint2 t = __ldg(reinterpret_cast<const uint2 *>(p)); w[0] = t.x; w[1] = t.y; }
+        else if constexpr (EPL == 2) { w[0] = __ldg(reinterpret_cast<const uint32_t *>(p)); }
+        else { v[0] = to_f32<T>(*p); return; }
+#pragma unroll
+        for (int i = 0; i < EPL / 2; ++i) {
+            if constexpr (std::is_same<T, __half>::value) {
+                const float2 f = __half22float2(*reinterpret_cast<const __half2 *>(&w[i]));
+                v[2 * i] = f.x; v[2 * i + 1] = f.y;
+            } else {
+                v[2 * i] = __uint_as_float(w[i] << 16); v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+            }
+        }
+    }
+}
+
 template <typename T, int EPL>
 __global__ void __launch_bounds__(128)
 rabitq_encode_reg_kernel(const T *__restrict__ keys, int64_t n, const float *__restrict__ diag, int rotate,
                          uint8_t *__restrict__ bits, float *__restrict__ mag) {
     constexpr int D = 32 * EPL;
+    constexpr int R = EPL <= 4 ? 4 : 2;  // rows a warp carries at once: loads in flight and independent butterfly chains
     const int lane = threadIdx.x & 31;
     const int64_t warp_id = (int64_t)blockIdx.x * 4 + (threadIdx.x >> 5);
     const int64_t n_warps = (int64_t)gridDim.x * 4;
@@ -78,50 +115,69 @@ rabitq_encode_reg_kernel(const T *__restrict__ keys, int64_t n, const float *__r
 #pragma unroll
     for (int j = 0; j < EPL; ++j) dg[j] = rotate ? diag[EPL * lane + j] : 1.f;
     const float den = sqrtf((float)D);
-    for (int64_t row = warp_id; row < n; row += n_warps) {
-        float v[EPL];
+    const float rden = __frcp_rn(den);
+    for (int64_t row0 = warp_id * R; row0 < n; row0 += n_warps * R) {
+        float v[R][EPL];
 #pragma unroll
-        for (int j = 0; j < EPL; ++j) v[j] = to_f32<T>(keys[row * D + EPL * lane + j]);
+        for (int r = 0; r < R; ++r) load_epl<T, EPL>(keys + min(row0 + r, n - 1) * D + EPL * lane, v[r]);
         if (rotate) {
 #pragma unroll
-            for (int j = 0; j < EPL; ++j) v[j] = __fmul_rn(v[j], dg[j]);
+            for (int r = 0; r < R; ++r)
+#pragma unroll
+                for (int j = 0; j < EPL; ++j) v[r][j] = __fmul_rn(v[r][j], dg[j]);
 #pragma unroll
             for (int s = 1; s < EPL; s <<= 1) {
 #pragma unroll
-                for (int j = 0; j < EPL; ++j) {
-                    if ((j & s) == 0) {
-                        const float a = v[j], b2 = v[j + s];
-                        v[j] = __fadd_rn(a, b2);
-                        v[j + s] = __fsub_rn(a, b2);
+                for (int r = 0; r < R; ++r)
+#pragma unroll
+                    for (int j = 0; j < EPL; ++j) {
+                        if ((j & s) == 0) {
+                            const float a = v[r][j], b2 = v[r][j + s];
+                            v[r][j] = __fadd_rn(a, b2);
+                            v[r][j + s] = __fsub_rn(a, b2);
+                        }
                     }
-                }
             }
 #pragma unroll
             for (int m = 1; m < 32; m <<= 1) {
                 const bool upper = lane & m;
 #pragma unroll
-                for (int j = 0; j < EPL; ++j) {
-                    const float other = __shfl_xor_sync(0xffffffffu, v[j], m);
-                    v[j] = upper ? __fsub_rn(other, v[j]) : __fadd_rn(v[j], other);
-                }
+                for (int r = 0; r < R; ++r)
+#pragma unroll
+                    for (int j = 0; j < EPL; ++j) {
+                        const float other = __shfl_xor_sync(0xffffffffu, v[r][j], m);
+                        v[r][j] = upper ? __fsub_rn(other, v[r][j]) : __fadd_rn(v[r][j], other);
+                    }
             }
+            // v / sqrt(D), correctly rounded without the divide: rc = RN(1/den), t0 = RN(v*rc),
+            // r = v - den*t0 (exact in one fma), RN(t0 + r*rc) is the IEEE quotient (Markstein).
 #pragma unroll
-            for (int j = 0; j < EPL; ++j) v[j] = __fdiv_rn(v[j], den);
-        }
-        float l1 = 0.f;
-        uint32_t mine = 0;
+            for (int r = 0; r < R; ++r)
 #pragma unroll
-        for (int j = 0; j < EPL; ++j) {
-            l1 += fabsf(v[j]);
-            mine |= (v[j] >= 0.f ? 1u : 0u) << j;
+                for (int j = 0; j < EPL; ++j) {
+                    const float t0 = __fmul_rn(v[r][j], rden);
+                    v[r][j] = __fmaf_rn(__fmaf_rn(-den, t0, v[r][j]), rden, t0);
+                }
         }
         constexpr int LPW = 32 / EPL;  // lanes per 32-bit output word
-        uint32_t word = mine << (EPL * (lane % LPW));
 #pragma unroll
-        for (int m = 1; m < LPW; m <<= 1) word |= __shfl_xor_sync(0xffffffffu, word, m);
-        if (lane % LPW == 0) reinterpret_cast<uint32_t *>(bits + row * (D / 8))[lane / LPW] = word;
-        l1 = warp_sum(l1);
-        if (lane == 0) mag[row] = l1 / (float)D;
+        for (int r = 0; r < R; ++r) {
+            float l1 = 0.f;
+            uint32_t mine = 0;
+#pragma unroll
+            for (int j = 0; j < EPL; ++j) {
+                l1 += fabsf(v[r][j]);
+                mine |= (v[r][j] >= 0.f ? 1u : 0u) << j;
+            }
+            uint32_t word = mine << (EPL * (lane % LPW));
+#pragma unroll
+            for (int m = 1; m < LPW; m <<= 1) word |= __shfl_xor_sync(0xffffffffu, word, m);
+            l1 = warp_sum(l1);
+            if (row0 + r < n) {
+                if (lane % LPW == 0) reinterpret_cast<uint32_t *>(bits + (row0 + r) * (D / 8))[lane / LPW] = word;
+                if (lane == 0) mag[row0 + r] = l1 / (float)D;
+            }
+        }
     }
 }
 
@@ -154,8 +210,8 @@ extern "C" int32_t vq_rabitq_encode(const void *keys, int32_t dtype, int64_t n, 
     VQ_REQUIRE(!rotate || diag != nullptr, VQ_ERR_SHAPE, "rabitq_encode: diag is NULL");
     if (n == 0) return VQ_OK;
     cudaStream_t st = (cudaStream_t)stream;
-    if ((D == 32 || D == 64 || D == 128 || D == 256) && is_aligned(bits, 4)) {
-        const unsigned rb = (unsigned)std::min<int64_t>(ceil_div(n, 4), 148 * 32);
+    if ((D == 32 || D == 64 || D == 128 || D == 256) && is_aligned(bits, 4) && is_aligned(keys, 16)) {
+        const unsigned rb = (unsigned)std::min<int64_t>(ceil_div(n, 16), 148 * 16);
 #define VQ_ENC(TT, EPL) rabitq_encode_reg_kernel<TT, EPL><<<rb, 128, 0, st>>>((const TT *)keys, n, diag, rotate, bits, mag)
 #define VQ_ENC_D(TT)                                                                   \
     switch (D) {                                                                       \
