@@ -61,7 +61,7 @@ def extract_functions(path: str, names, extra_ns=None):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", required=True, help="root of a checkout of the reference project")
     args = ap.parse_args()
     R = args.reference
     pkg = os.path.join(R, "veloxquant_mlx")

@@ -1,4 +1,4 @@
-"""Parity at the full BASELINE sizes through properties that do not need the oracle to run at
+"""Parity at the full benchmark sizes through properties that do not need the oracle to run at
 that size: quantize -> dequantize error bounds, exact reconstruction of constant groups,
 softmax weights summing to one (constant values come back exactly), identical inputs in
 different batch slots giving identical outputs, independence from the context split count,
@@ -107,7 +107,7 @@ def test_full_size_layer_properties(name, B, H_q, H_kv, S, bits, dtype):
 
 
 def test_full_size_rabitq_config4_properties():
-    """BASELINE config 4 at full size: batch 8, 8 KV heads, 16384 keys of dim 128, 32 query heads."""
+    """benchmark config 4 at full size: batch 8, 8 KV heads, 16384 keys of dim 128, 32 query heads."""
     from oracle import rabitq as o_rq
     from veloxquant_mlx_b200 import rabitq as rq
 

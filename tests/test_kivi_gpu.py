@@ -346,7 +346,7 @@ def test_mma_attend_parity(b, H, H_kv, n_quant, n_res):
 @pytest.mark.parametrize("b", [2, 4])
 @pytest.mark.parametrize("dt", ["float16", "bfloat16"])
 def test_mma_attend_config1_with_outlier_channels(b, dt):
-    """BASELINE config 1 shape: B=1, 8 kv heads, 32 q heads, S=4096, residual 128, outliers x20."""
+    """benchmark config 1 shape: B=1, 8 kv heads, 32 q heads, S=4096, residual 128, outliers x20."""
     rng = np.random.default_rng(0)
     args, ref = _packed_case(rng, 1, 32, 8, 4096 - 128, 128, b, dt, outliers=True)
     qt, kc, ks, kz, vc, vs, vz, k_res, v_res = args

@@ -54,7 +54,7 @@ def test_encode_matches_golden_and_config4_shape():
         bits, mag = r.rabitq_encode(_t(z[f"{tag}_keys"]), _t(z[f"{tag}_diag"]))
         np.testing.assert_array_equal(bits.cpu().numpy(), z[f"{tag}_bits"])
         np.testing.assert_allclose(mag.cpu().numpy(), z[f"{tag}_mag"], rtol=1e-4)
-    # BASELINE config 4: keys fp16 [8, 16384, 128] (one batch item), seeded rotation
+    # benchmark config 4: keys fp16 [8, 16384, 128] (one batch item), seeded rotation
     rng = np.random.default_rng(4)
     keys = rng.standard_normal((8 * 16384, 128)).astype(np.float16)
     diag = r.make_hadamard_diagonal(128, seed=42)
@@ -65,7 +65,7 @@ def test_encode_matches_golden_and_config4_shape():
     np.testing.assert_allclose(mag.cpu().numpy(), omag, rtol=1e-4)
     # the "sign bits packed into uint32" view is the same bytes on a little-endian machine
     assert bits.view(torch.int32).shape == (8 * 16384, 4)
-    # dense QR rotation (the variant BASELINE config 4 words): rotate with a GEMM, then pack
+    # dense QR rotation (the variant benchmark config 4 words): rotate with a GEMM, then pack
     rot = r.make_rotation_matrix(128, seed=42).astype(np.float32)
     np.testing.assert_array_equal(rot, z["rot_d128_s42"])
     y = (_t(keys[:4096]).float() @ _t(rot).T).contiguous()
@@ -134,7 +134,7 @@ def test_attend_golden_fixture_gqa_dense_values_and_errors():
         g = lambda k: _t(z[f"{tag}_{k}"])  # noqa: E731
         out = r.rabitq_fused_attend(g("q"), g("q_scale"), g("k_bits"), g("k_mag"), g("k_const"), g("v_idx"), g("v_cents"))
         np.testing.assert_allclose(out.float().cpu().numpy(), z[f"{tag}_out"], atol=1e-2, rtol=1e-2)
-    # BASELINE config 4 form: 32 query heads over 8 kv heads, fp16 values, no k_const,
+    # benchmark config 4 form: 32 query heads over 8 kv heads, fp16 values, no k_const,
     # buffers larger than the live context
     B, H, H_kv, S, cap, D = 2, 32, 8, 2000, 2048, 128
     q, q_scale, k_bits, k_mag, _, _, _ = _attend_inputs(B, H, 1, cap, D, seed=9, H_kv=H_kv)

@@ -51,7 +51,7 @@ def test_quantize_vq_bit_exact(dt, sub_dim, n_c):
 def test_quantize_vq_config2_shape_and_ties_and_large_magnitude():
     v = _v()
     rng = np.random.default_rng(0)
-    # BASELINE config 2: keys fp16 [8, 4096, 128], sub_dim 8, 256 centroids fp16
+    # benchmark config 2: keys fp16 [8, 4096, 128], sub_dim 8, 256 centroids fp16
     keys, k32 = _cast(rng.standard_normal((8, 4096, 128)).astype(np.float32), "float16")
     cb, cb32 = _cast(np.random.default_rng(42).standard_normal((256, 8)).astype(np.float32), "float16")
     got = v.quantize_vq(keys, cb, 8, index_dtype=torch.uint8)
@@ -64,7 +64,7 @@ def test_quantize_vq_config2_shape_and_ties_and_large_magnitude():
     big, b32 = _cast((rng.standard_normal((64, 32)) * 100).astype(np.float32), "float16")
     cbb, cbb32 = _cast((rng.standard_normal((16, 4)) * 100).astype(np.float32), "float16")
     np.testing.assert_array_equal(v.quantize_vq(big, cbb, 4).cpu().numpy(), o_vq.quantize_vq(b32, cbb32, 4))
-    # per-sub-space codebooks (BASELINE config 2 wording: each subspace has its own 256 centroids)
+    # per-sub-space codebooks (benchmark config 2 wording: each subspace has its own 256 centroids)
     cbs, cbs32 = _cast(rng.standard_normal((16, 256, 8)).astype(np.float32), "float16")
     got = v.quantize_vq(keys[:2, :300], cbs, 8)
     np.testing.assert_array_equal(got.cpu().numpy(), o_vq.quantize_vq(k32[:2, :300], cbs32, 8))
@@ -137,7 +137,7 @@ def test_fused_sdpa_vq_matches_oracle(causal, window, H_q, H_kv, S_q, S_kv):
 
 
 def test_fused_sdpa_vq_long_context_dense_values_and_capacity():
-    """BASELINE config 2: VQ keys, fp16 values [8, 4096, 128], 32 query heads; buffers larger
+    """benchmark config 2: VQ keys, fp16 values [8, 4096, 128], 32 query heads; buffers larger
     than the live context."""
     rng = np.random.default_rng(5)
     v = _v()

@@ -126,7 +126,7 @@ def op_rabitq(a):
 
 
 def op_kivi_attend(a):
-    """Decode attention over a KIVI cache at the small BASELINE shapes (config 1 and config 5, one layer)."""
+    """Decode attention over a KIVI cache at the small benchmark shapes (config 1 and config 5, one layer)."""
     from .cache import KVCacheConfig, KVCacheFactory
 
     for name, B, Hq, Hkv, S, bits in (("config1", 1, 32, 8, 4096, 2), ("config5", 4, 40, 8, 16384 + 256, 2)):
