@@ -359,9 +359,12 @@ kivi_attend_mma_kernel(const __grid_constant__ Params p) {
     float o[8][4];
 #pragma unroll
     for (int i = 0; i < 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
-    float oz[2][4];  // sum_t P[t,h] * v_zero[t, group]
+    // sum_t P[t,h] * v_zero[t, group] for this lane's two channel groups 2*(c>>1), 2*(c>>1)+1
+    // (lanes c and c^2 hold the same P values and share the four groups between them)
+    float oz[2][2];
 #pragma unroll
-    for (int i = 0; i < 4; ++i) oz[0][i] = oz[1][i] = 0.f;
+    for (int i = 0; i < 2; ++i) oz[0][i] = oz[1][i] = 0.f;
+    const int q2 = c >> 1;
     float m_run[2] = {-INFINITY, -INFINITY};
     float l_run[2] = {0.f, 0.f};
     const float sc = a.scale * 1.4426950408889634f;  // scores kept in the log2 domain
@@ -507,7 +510,7 @@ kivi_attend_mma_kernel(const __grid_constant__ Params p) {
                     o[i][1] *= corr[1]; o[i][3] *= corr[1];
                 }
 #pragma unroll
-                for (int i = 0; i < 4; ++i) { oz[0][i] *= corr[0]; oz[1][i] *= corr[1]; }
+                for (int i = 0; i < 2; ++i) { oz[0][i] *= corr[0]; oz[1][i] *= corr[1]; }
             }
         }
 
@@ -517,23 +520,33 @@ kivi_attend_mma_kernel(const __grid_constant__ Params p) {
             const int t0 = 16 * mt;
             uint32_t pbw[4][2];  // [channel group][tokens 0-7 / 8-15 of the m-tile]
             {
-                const float4 vsa = *reinterpret_cast<const float4 *>(st + C::VS_OFF + (t0 + g) * 16);
-                const float4 vsb = *reinterpret_cast<const float4 *>(st + C::VS_OFF + (t0 + g + 8) * 16);
-                const float4 vza = *reinterpret_cast<const float4 *>(st + C::VZ_OFF + (t0 + g) * 16);
-                const float4 vzb = *reinterpret_cast<const float4 *>(st + C::VZ_OFF + (t0 + g + 8) * 16);
-                const float sa[4] = {vsa.x, vsa.y, vsa.z, vsa.w}, sbv[4] = {vsb.x, vsb.y, vsb.z, vsb.w};
-                const float za[4] = {vza.x, vza.y, vza.z, vza.w}, zb[4] = {vzb.x, vzb.y, vzb.z, vzb.w};
+                // Lanes c and c^2 hold the same four P values. Each forms the products with the
+                // value scales of two of the four channel groups (hi and lo halves of both),
+                // then they swap what the other needs: lanes c < 2 feed the high halves of all
+                // four groups into the transpose, lanes c >= 2 the low halves.
+                const float2 sa = *reinterpret_cast<const float2 *>(st + C::VS_OFF + (t0 + g) * 16 + 8 * q2);
+                const float2 sbv = *reinterpret_cast<const float2 *>(st + C::VS_OFF + (t0 + g + 8) * 16 + 8 * q2);
+                const float2 za = *reinterpret_cast<const float2 *>(st + C::VZ_OFF + (t0 + g) * 16 + 8 * q2);
+                const float2 zb = *reinterpret_cast<const float2 *>(st + C::VZ_OFF + (t0 + g + 8) * 16 + 8 * q2);
+                const float sa2[2] = {sa.x, sa.y}, sb2[2] = {sbv.x, sbv.y};
+                const float za2[2] = {za.x, za.y}, zb2[2] = {zb.x, zb.y};
                 const float pa0 = pr[mt][0], pa1 = pr[mt][1], pb0 = pr[mt][2], pb1 = pr[mt][3];
+                const bool low_lane = c < 2;
 #pragma unroll
-                for (int gd = 0; gd < 4; ++gd) {
-                    oz[0][gd] = fmaf(pa0, za[gd], fmaf(pb0, zb[gd], oz[0][gd]));
-                    oz[1][gd] = fmaf(pa1, za[gd], fmaf(pb1, zb[gd], oz[1][gd]));
+                for (int j = 0; j < 2; ++j) {
+                    oz[0][j] = fmaf(pa0, za2[j], fmaf(pb0, zb2[j], oz[0][j]));
+                    oz[1][j] = fmaf(pa1, za2[j], fmaf(pb1, zb2[j], oz[1][j]));
                     uint32_t ha, la, hb, lb;
-                    split_h2(pa0 * sa[gd], pa1 * sa[gd], ha, la);
-                    split_h2(pb0 * sbv[gd], pb1 * sbv[gd], hb, lb);
+                    split_h2(pa0 * sa2[j], pa1 * sa2[j], ha, la);
+                    split_h2(pb0 * sb2[j], pb1 * sb2[j], hb, lb);
+                    // what the partner lane needs from here / what this lane needs from there
+                    const uint32_t ra = __shfl_xor_sync(0xffffffffu, low_lane ? la : ha, 2);
+                    const uint32_t rb = __shfl_xor_sync(0xffffffffu, low_lane ? lb : hb, 2);
                     // P tile (tokens x heads) -> B operand (tokens on K, heads on N): 8x8 transpose
-                    pbw[gd][0] = movmatrix_trans(c < 2 ? ha : la);
-                    pbw[gd][1] = movmatrix_trans(c < 2 ? hb : lb);
+                    pbw[j][0] = movmatrix_trans(low_lane ? ha : ra);      // groups 0, 1
+                    pbw[j][1] = movmatrix_trans(low_lane ? hb : rb);
+                    pbw[2 + j][0] = movmatrix_trans(low_lane ? ra : la);  // groups 2, 3
+                    pbw[2 + j][1] = movmatrix_trans(low_lane ? rb : lb);
                 }
             }
 #pragma unroll
@@ -584,7 +597,7 @@ kivi_attend_mma_kernel(const __grid_constant__ Params p) {
         v += __shfl_xor_sync(0xffffffffu, v, 16);
         l_run[hh] = v;
 #pragma unroll
-        for (int gd = 0; gd < 4; ++gd) {
+        for (int gd = 0; gd < 2; ++gd) {
             float z = oz[hh][gd];
             z += __shfl_xor_sync(0xffffffffu, z, 4);
             z += __shfl_xor_sync(0xffffffffu, z, 8);
@@ -625,10 +638,14 @@ kivi_attend_mma_kernel(const __grid_constant__ Params p) {
             for (int hh = 0; hh < 2; ++hh) {
                 red_m[warp * kChunkHeads + hpair + hh] = m_run[hh];
                 red_l[warp * kChunkHeads + hpair + hh] = l_run[hh];
-#pragma unroll
-                for (int gd = 0; gd < 4; ++gd) red_z[(warp * kChunkHeads + hpair + hh) * 4 + gd] = oz[hh][gd];
             }
         }
+    }
+    if (g == 0) {  // every lane c holds the zero-point sums of its own two channel groups
+#pragma unroll
+        for (int hh = 0; hh < 2; ++hh)
+#pragma unroll
+            for (int j = 0; j < 2; ++j) red_z[(warp * kChunkHeads + hpair + hh) * 4 + 2 * q2 + j] = oz[hh][j];
     }
     __syncwarp();
     if (c >= 2) {  // then add the low-half columns
