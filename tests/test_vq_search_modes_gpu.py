@@ -24,7 +24,7 @@ from oracle import vq as o_vq
 rng = np.random.default_rng(0)
 def check(x32, cb, tag):
     x = torch.from_numpy(x32).half()
-    got = vi.quantize_vq(x.cuda(), torch.from_numpy(cb).cuda(), 8, index_dtype=torch.uint8 if cb.shape[0] <= 256 else torch.int32)
+    got = vi.quantize_vq(x.cuda(), torch.from_numpy(cb).cuda(), 8, index_dtype=torch.uint8 if cb.shape[-2] <= 256 else torch.int32)
     assert lib().vq_vq_quantize_status() == 0, tag
     want = o_vq.quantize_vq(x.float().numpy(), cb, 8)
     bad = int((got.cpu().numpy().astype(np.int32) != want).sum())
@@ -46,6 +46,10 @@ cbr = rng.standard_normal((256, 8)).astype(np.float32)
 check(xb, cbr, "bad rows")
 check(xb, cbr * 100, "large codebook")
 check(xb, np.zeros((16, 8), np.float32), "zero codebook")
+# one codebook per sub-space (the second benchmark configuration's wording): 16 sub-spaces of dim 8
+xs = rng.standard_normal((2, 300, 128)).astype(np.float32)
+cbs = rng.standard_normal((16, 256, 8)).astype(np.float32); cbs[5, 100] = cbs[5, 3]
+check(xs, cbs, "per-sub-space codebooks")
 print("search ok")
 """
 

@@ -1,6 +1,6 @@
 // VecInfer nearest-centroid search on the 5th-generation tensor cores (tcgen05 + TMEM), with
 // the exact answer. f16 input, sub_dim 8, 16..256 centroids (a multiple of 16), one shared
-// codebook; vq_quant_mma.cu covers the other shapes with warp-level MMAs.
+// codebook or one per sub-space; vq_quant_mma.cu covers the other shapes with warp-level MMAs.
 //
 // Per 128-row tile one CTA issues two 128 x N x 16 MMAs into a 128-lane x N-column float32
 // accumulator in tensor memory:
@@ -216,8 +216,14 @@ __device__ __forceinline__ void pass_count(uint32_t taddr, int c_lo, int c_hi, f
 }
 
 __global__ void __launch_bounds__(kThreads, 2)
-vq_quantize_tc5_kernel(const __half *__restrict__ x, int64_t n, const float *__restrict__ cb, int n_c,
+vq_quantize_tc5_kernel(const __half *__restrict__ x, int64_t n_vec, const float *__restrict__ cb_all, int n_c, int n_sub,
                        void *__restrict__ indices, int index_bytes) {
+    // With one codebook per sub-space (n_sub > 0) a CTA works on sub-space blockIdx.y only: its
+    // rows are the sub-vectors sub, sub + n_sub, ... (row i is sub-vector i * vstride + sub).
+    const int sub = n_sub > 0 ? blockIdx.y : 0;
+    const int64_t vstride = n_sub > 0 ? n_sub : 1;
+    const int64_t n = n_sub > 0 ? (n_vec + n_sub - 1 - sub) / n_sub : n_vec;
+    const float *__restrict__ cb = cb_all + (int64_t)sub * n_c * kSub;
     extern __shared__ __align__(128) uint8_t smem_raw[];
     Tc5Smem &sm = *reinterpret_cast<Tc5Smem *>(smem_raw);
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -300,7 +306,7 @@ vq_quantize_tc5_kernel(const __half *__restrict__ x, int64_t n, const float *__r
     auto fetch = [&](int64_t tile, int stage) {
         if (tid < kRows) {
             const int64_t row = min(tile * kRows + tid, n - 1);
-            const __half *src = x + row * kSub;
+            const __half *src = x + (row * vstride + sub) * kSub;
             const uint32_t d0 = smem_u32(sm.a[stage][0] + tid * 16), d1 = smem_u32(sm.a[stage][1] + tid * 16);
             asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d0), "l"(src) : "memory");
             asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d1), "l"(src) : "memory");
@@ -331,13 +337,14 @@ vq_quantize_tc5_kernel(const __half *__restrict__ x, int64_t n, const float *__r
             const int src = __ffs(slow_mask) - 1;
             slow_mask &= slow_mask - 1;
             const int64_t srow = prev_tile * kRows + warp * 32 + src;
-            const uint32_t e = exact_row8(x + srow * kSub, cb, n_c, lane);
+            const uint32_t e = exact_row8(x + (srow * vstride + sub) * kSub, cb, n_c, lane);
             if (lane == src) idx = e;
         }
         if (row < n && !timed_out) {
-            if (index_bytes == 1) reinterpret_cast<uint8_t *>(indices)[row] = (uint8_t)idx;
-            else if (index_bytes == 2) reinterpret_cast<uint16_t *>(indices)[row] = (uint16_t)idx;
-            else reinterpret_cast<uint32_t *>(indices)[row] = idx;
+            const int64_t o = row * vstride + sub;
+            if (index_bytes == 1) reinterpret_cast<uint8_t *>(indices)[o] = (uint8_t)idx;
+            else if (index_bytes == 2) reinterpret_cast<uint16_t *>(indices)[o] = (uint16_t)idx;
+            else reinterpret_cast<uint32_t *>(indices)[o] = idx;
         }
     };
     for (int it = 0; tile < n_tiles; tile += gridDim.x, ++it) {
@@ -409,15 +416,15 @@ vq_quantize_tc5_kernel(const __half *__restrict__ x, int64_t n, const float *__r
 bool vq_quantize_tc5_supported(const void *x, int32_t x_dtype, int64_t n, int32_t sub_dim, int32_t n_c, int32_t n_sub) {
     static const char *mode = std::getenv("VQ_VQ_SEARCH");  // "exact" / "mma" / "tc5" pin one search
     if (mode && (std::strcmp(mode, "exact") == 0 || std::strcmp(mode, "mma") == 0)) return false;
-    if (x_dtype != VQ_F16 || sub_dim != kSub || n_sub != 0) return false;
+    if (x_dtype != VQ_F16 || sub_dim != kSub || n_sub < 0 || n_sub > 65535) return false;
     if (n_c < 16 || n_c > 256 || n_c % 16) return false;
     if (!is_aligned(x, 16)) return false;
     const bool forced = mode && std::strcmp(mode, "tc5") == 0;
     return forced ? n >= 1 : n >= 4096;  // small inputs: the CUDA-core search has no set-up cost
 }
 
-int32_t vq_quantize_tc5_launch(const void *x, int64_t n, const float *cb, int32_t n_c, void *indices, int32_t index_bytes,
-                               cudaStream_t st) {
+int32_t vq_quantize_tc5_launch(const void *x, int64_t n, const float *cb, int32_t n_c, int32_t n_sub, void *indices,
+                               int32_t index_bytes, cudaStream_t st) {
     DeviceInfo di;
     int32_t rc = device_info(&di);
     if (rc != VQ_OK) return rc;
@@ -425,9 +432,11 @@ int32_t vq_quantize_tc5_launch(const void *x, int64_t n, const float *cb, int32_
     // request is padded so that a third CTA (which would wait for columns) cannot be resident.
     const size_t smem = std::max(sizeof(Tc5Smem) + 128, (size_t)80 * 1024);
     VQ_CHECK_CUDA(cudaFuncSetAttribute(vq_quantize_tc5_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    const int64_t n_tiles = ceil_div(n, kRows);
-    const unsigned blocks = (unsigned)std::max<int64_t>(1, std::min<int64_t>(n_tiles, (int64_t)di.sm_count * 2));
-    vq_quantize_tc5_kernel<<<blocks, kThreads, smem, st>>>((const __half *)x, n, cb, n_c, indices, index_bytes);
+    const int ny = n_sub > 0 ? n_sub : 1;
+    const int64_t n_tiles = ceil_div(ceil_div(n, ny), kRows);
+    const int64_t fill = std::max<int64_t>(1, ceil_div((int64_t)di.sm_count * 2, ny));  // CTAs per sub-space for two per SM
+    const unsigned blocks = (unsigned)std::max<int64_t>(1, std::min<int64_t>(n_tiles, fill));
+    vq_quantize_tc5_kernel<<<dim3(blocks, ny), kThreads, smem, st>>>((const __half *)x, n, cb, n_c, n_sub, indices, index_bytes);
     VQ_CHECK_LAUNCH("vq_quantize_tc5_kernel");
     return VQ_OK;
 }
