@@ -23,6 +23,13 @@ namespace {
 
 constexpr float kMagic = 12582912.0f;  // 1.5 * 2^23: x + kMagic rounds x to the nearest-even integer
 
+// a / b correctly rounded (== __fdiv_rn) from rb = RN(1/b): t0 = RN(a*rb), r = a - b*t0 (exact
+// in one fma), RN(t0 + r*rb). Used where the divisor is shared by many quotients.
+__device__ __forceinline__ float div_by(float a, float b, float rb) {
+    const float t0 = __fmul_rn(a, rb);
+    return __fmaf_rn(__fmaf_rn(-b, t0, a), rb, t0);
+}
+
 // ---- packed (two elements per register) min / max and widening -----------------------------
 template <typename T> struct Pk;
 template <> struct Pk<__half> {
@@ -118,6 +125,7 @@ kivi_quant_tile_kernel(const T *__restrict__ x, int64_t x_stride_bh, int64_t n_t
     const int64_t bh = tile_id / tiles_per_bh, tile = tile_id % tiles_per_bh;
     const int64_t tok0 = tile * 32;
     const int hf = lane >> 4, cl = lane & 15;
+    const float rlev = __frcp_rn(levels);
     const T *xb = x + bh * x_stride_bh + tok0 * D + 8 * cl;
     uint8_t *cb = codes + bh * codes_stride_bh + tok0 * RB;
 
@@ -143,8 +151,8 @@ kivi_quant_tile_kernel(const T *__restrict__ x, int64_t x_stride_bh, int64_t n_t
             const uint32_t on = __shfl_xor_sync(0xffffffffu, mnp[k], 16), ox = __shfl_xor_sync(0xffffffffu, mxp[k], 16);
             const float2 fn = Pk<T>::widen(pmin<T>(mnp[k], on)), fx = Pk<T>::widen(pmax<T>(mxp[k], ox));
             mn[2 * k] = fn.x; mn[2 * k + 1] = fn.y;
-            sc[2 * k] = fmaxf(__fdiv_rn(__fsub_rn(fx.x, fn.x), levels), eps);
-            sc[2 * k + 1] = fmaxf(__fdiv_rn(__fsub_rn(fx.y, fn.y), levels), eps);
+            sc[2 * k] = fmaxf(div_by(__fsub_rn(fx.x, fn.x), levels, rlev), eps);
+            sc[2 * k + 1] = fmaxf(div_by(__fsub_rn(fx.y, fn.y), levels, rlev), eps);
             rc[2 * k] = __frcp_rn(sc[2 * k]);
             rc[2 * k + 1] = __frcp_rn(sc[2 * k + 1]);
         }
@@ -179,7 +187,7 @@ kivi_quant_tile_kernel(const T *__restrict__ x, int64_t x_stride_bh, int64_t n_t
             px = pmax<T>(px, __shfl_xor_sync(0xffffffffu, px, 2));
             const float2 fn = Pk<T>::widen(pn), fx = Pk<T>::widen(px);
             const float mn1 = fminf(fn.x, fn.y), mx1 = fmaxf(fx.x, fx.y);
-            const float sc1 = fmaxf(__fdiv_rn(__fsub_rn(mx1, mn1), levels), eps);
+            const float sc1 = fmaxf(div_by(__fsub_rn(mx1, mn1), levels, rlev), eps);
             const float rc1 = __frcp_rn(sc1);
             if (tok0 + row < n_tok) {
                 if ((cl & 3) == 0) {
