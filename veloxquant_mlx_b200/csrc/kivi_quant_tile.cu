@@ -27,7 +27,8 @@ constexpr float kMagic = 12582912.0f;  // 1.5 * 2^23: x + kMagic rounds x to the
 // in one fma), RN(t0 + r*rb). Used where the divisor is shared by many quotients.
 __device__ __forceinline__ float div_by(float a, float b, float rb) {
     const float t0 = __fmul_rn(a, rb);
-    return __fmaf_rn(__fmaf_rn(-b, t0, a), rb, t0);
+    const float q = __fmaf_rn(__fmaf_rn(-b, t0, a), rb, t0);
+    return fabsf(t0) < INFINITY ? q : t0;  // an infinite or NaN quotient stays what the divide gives
 }
 
 // ---- packed (two elements per register) min / max and widening -----------------------------
