@@ -181,6 +181,72 @@ rabitq_encode_reg_kernel(const T *__restrict__ keys, int64_t n, const float *__r
     }
 }
 
+// D = 32 * LPR with 32 consecutive elements per lane: LPR lanes share a key row, a warp carries
+// 32 / LPR rows. The five butterfly stages with stride < 32 pair registers of one lane, only
+// the log2(LPR) widest stages cross lanes (2 of 7 stages at D = 128, against 5 of 7 with four
+// elements per lane), and a lane's 32 sign bits are one whole output word. Every pair is
+// still (lower + upper, lower - upper): bit-identical to the sequential Sylvester loop.
+template <typename T, int LPR>
+__global__ void __launch_bounds__(128)
+rabitq_encode_wide_kernel(const T *__restrict__ keys, int64_t n, const float *__restrict__ diag,
+                          uint8_t *__restrict__ bits, float *__restrict__ mag) {
+    constexpr int D = 32 * LPR, RPW = 32 / LPR;
+    const int lane = threadIdx.x & 31;
+    const int part = lane % LPR, rsub = lane / LPR;  // which 32 elements of which of the warp's rows
+    const int64_t warp_id = (int64_t)blockIdx.x * 4 + (threadIdx.x >> 5);
+    const int64_t n_warps = (int64_t)gridDim.x * 4;
+    float dg[32];
+#pragma unroll
+    for (int j = 0; j < 32; ++j) dg[j] = diag[32 * part + j];
+    const float den = sqrtf((float)D), rden = __frcp_rn(den);
+    for (int64_t row0 = warp_id * RPW; row0 < n; row0 += n_warps * RPW) {
+        const int64_t row = min(row0 + rsub, n - 1);
+        float v[32];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            float t[8];
+            load_epl<T, 8>(keys + row * D + 32 * part + 8 * k, t);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) v[8 * k + j] = __fmul_rn(t[j], dg[8 * k + j]);
+        }
+#pragma unroll
+        for (int s = 1; s < 32; s <<= 1) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+                if ((j & s) == 0) {
+                    const float a = v[j], b2 = v[j + s];
+                    v[j] = __fadd_rn(a, b2);
+                    v[j + s] = __fsub_rn(a, b2);
+                }
+            }
+        }
+#pragma unroll
+        for (int m = 1; m < LPR; m <<= 1) {
+            const bool upper = part & m;
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+                const float other = __shfl_xor_sync(0xffffffffu, v[j], m);
+                v[j] = upper ? __fsub_rn(other, v[j]) : __fadd_rn(v[j], other);
+            }
+        }
+        float l1 = 0.f;
+        uint32_t word = 0;
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+            const float t0 = __fmul_rn(v[j], rden);
+            const float y = __fmaf_rn(__fmaf_rn(-den, t0, v[j]), rden, t0);  // v / sqrt(D), correctly rounded
+            l1 += fabsf(y);
+            word |= (y >= 0.f ? 1u : 0u) << j;
+        }
+#pragma unroll
+        for (int m = 1; m < LPR; m <<= 1) l1 += __shfl_xor_sync(0xffffffffu, l1, m);
+        if (row0 + rsub < n) {
+            reinterpret_cast<uint32_t *>(bits + (row0 + rsub) * (D / 8))[part] = word;
+            if (part == 0) mag[row0 + rsub] = l1 / (float)D;
+        }
+    }
+}
+
 __global__ void rabitq_pack_values_kernel(const uint8_t *__restrict__ v_idx, int64_t n_out,
                                           uint8_t *__restrict__ packed) {
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n_out;
@@ -210,6 +276,25 @@ extern "C" int32_t vq_rabitq_encode(const void *keys, int32_t dtype, int64_t n, 
     VQ_REQUIRE(!rotate || diag != nullptr, VQ_ERR_SHAPE, "rabitq_encode: diag is NULL");
     if (n == 0) return VQ_OK;
     cudaStream_t st = (cudaStream_t)stream;
+    if ((D == 64 || D == 128 || D == 256) && rotate && is_aligned(bits, 4) && is_aligned(keys, 16)) {
+        const int rpw = 32 / (D / 32);
+        const unsigned rb = (unsigned)std::min<int64_t>(ceil_div(n, 4 * rpw), 148 * 16);
+#define VQ_ENCW(TT)                                                                                              \
+    switch (D) {                                                                                                 \
+        case 64: rabitq_encode_wide_kernel<TT, 2><<<rb, 128, 0, st>>>((const TT *)keys, n, diag, bits, mag); break;  \
+        case 128: rabitq_encode_wide_kernel<TT, 4><<<rb, 128, 0, st>>>((const TT *)keys, n, diag, bits, mag); break; \
+        default: rabitq_encode_wide_kernel<TT, 8><<<rb, 128, 0, st>>>((const TT *)keys, n, diag, bits, mag); break;  \
+    }
+        switch (dtype) {
+            case VQ_F16: VQ_ENCW(__half); break;
+            case VQ_BF16: VQ_ENCW(__nv_bfloat16); break;
+            case VQ_F32: VQ_ENCW(float); break;
+            default: return fail(VQ_ERR_DTYPE, "rabitq_encode: unknown dtype %d", dtype);
+        }
+#undef VQ_ENCW
+        VQ_CHECK_LAUNCH("rabitq_encode_wide_kernel");
+        return VQ_OK;
+    }
     if ((D == 32 || D == 64 || D == 128 || D == 256) && is_aligned(bits, 4) && is_aligned(keys, 16)) {
         const unsigned rb = (unsigned)std::min<int64_t>(ceil_div(n, 16), 148 * 16);
 #define VQ_ENC(TT, EPL) rabitq_encode_reg_kernel<TT, EPL><<<rb, 128, 0, st>>>((const TT *)keys, n, diag, rotate, bits, mag)
