@@ -107,7 +107,7 @@ extern "C" int32_t vq_vq_quantize(const void *x, int32_t x_dtype, int64_t n, int
     VQ_REQUIRE(x && codebook && indices, VQ_ERR_SHAPE, "vq_vq_quantize: NULL argument");
     cudaStream_t st = (cudaStream_t)stream;
     if (vq_quantize_tc5_supported(x, x_dtype, n, sub_dim, n_centroids, n_sub))
-        return vq_quantize_tc5_launch(x, n, codebook, n_centroids, n_sub, indices, index_bytes, st);
+        return vq_quantize_tc5_launch(x, x_dtype, n, codebook, n_centroids, n_sub, indices, index_bytes, st);
     if (vq_quantize_mma_supported(x, x_dtype, n, sub_dim, n_centroids, n_sub))
         return vq_quantize_mma_launch(x, x_dtype, n, sub_dim, codebook, n_centroids, n_sub, indices, index_bytes, st);
     switch (x_dtype) {

@@ -1,5 +1,5 @@
 // VecInfer nearest-centroid search on the 5th-generation tensor cores (tcgen05 + TMEM), with
-// the exact answer. f16 input, sub_dim 8, 16..256 centroids (a multiple of 16), one shared
+// the exact answer. f16 or bf16 input, sub_dim 8, 16..256 centroids (a multiple of 16), one shared
 // codebook or one per sub-space; vq_quant_mma.cu covers the other shapes with warp-level MMAs.
 //
 // Per 128-row tile one CTA issues two 128 x N x 16 MMAs into a 128-lane x N-column float32
@@ -24,6 +24,7 @@
 #include <algorithm>
 #include <cstdlib>
 #include <cstring>
+#include <type_traits>
 
 #include "common.cuh"
 #include "vq_quant_mma.h"
@@ -51,8 +52,10 @@ __device__ __forceinline__ uint64_t make_desc(uint32_t addr, uint32_t lbo, uint3
 }
 
 // Instruction descriptor for kind::f16: f16 x f16 -> f32, both operands K-major, M x N.
-__device__ __forceinline__ uint32_t make_idesc(int M, int N) {
-    return (1u << 4) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
+// (operand format field: 0 = f16, 1 = bf16)
+__device__ __forceinline__ uint32_t make_idesc(int M, int N, bool bf16) {
+    const uint32_t fmt = bf16 ? 1u : 0u;
+    return (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
 }
 
 __device__ __forceinline__ void mma_f16_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
@@ -112,10 +115,11 @@ __device__ __forceinline__ float max3(float a, float b, float c) {
 }
 
 // The reference evaluation order for one row, spread over the warp (see vq_quant_mma.cu).
-__device__ uint32_t exact_row8(const __half *xrow, const float *__restrict__ cb, int n_c, int lane) {
+template <typename T>
+__device__ uint32_t exact_row8(const T *xrow, const float *__restrict__ cb, int n_c, int lane) {
     float xv[kSub];
 #pragma unroll
-    for (int i = 0; i < kSub; ++i) xv[i] = __half2float(xrow[i]);
+    for (int i = 0; i < kSub; ++i) xv[i] = to_f32<T>(xrow[i]);
     float best = INFINITY;
     uint32_t best_idx = 0xffffffffu;
     for (int c = lane; c < n_c; c += 32) {
@@ -139,9 +143,9 @@ __device__ uint32_t exact_row8(const __half *xrow, const float *__restrict__ cb,
 struct Tc5Smem {
     // every operand region starts on a 128-byte boundary
     uint8_t a[2][2][kRows * 16];   // [stage][K chunk]: the tile of x, twice (K = 16 = x | x)
-    uint8_t a2[2][kRows * 16];     // [K chunk]: rows of (1 1 1 0 0 0 0 0 | 0 ...)
-    uint8_t b1[2][256 * 16];       // [K chunk]: c_hi | c_lo
-    uint8_t b2[2][256 * 16];       // [K chunk]: (h0 h1 h2 0 ...) | 0
+    uint8_t a2[2][kRows * 16];     // [K chunk]: rows of (1 1 1 0 0 0 0 0 | 0 ...); bf16: four ones, chunk 0 only
+    uint8_t b1[2][256 * 16];       // [K chunk]: centroid piece 0 | piece 1
+    uint8_t b2[2][256 * 16];       // [K chunk]: (h0 h1 h2 0 ...) | 0; bf16: centroid piece 2 | (h0 h1 h2 h3 0 ...)
     float xch_m[2][kRows];         // row maxima of the two column halves
     float xch_acc[kRows];          // pass-2 results of the upper column half
     float xch_base[kRows];
@@ -215,8 +219,12 @@ __device__ __forceinline__ void pass_count(uint32_t taddr, int c_lo, int c_hi, f
     }
 }
 
+// T = __half: operands in f16, centroid = 2 pieces (K slots: x|x against c0|c1, then 1 1 1 against
+// the three pieces of h). T = __nv_bfloat16: operands in bf16, whose 8-bit mantissa needs 3
+// pieces per centroid and 4 for h: x|x against c0|c1, then x|1 1 1 1 against c2|h0 h1 h2 h3.
+template <typename T>
 __global__ void __launch_bounds__(kThreads, 2)
-vq_quantize_tc5_kernel(const __half *__restrict__ x, int64_t n_vec, const float *__restrict__ cb_all, int n_c, int n_sub,
+vq_quantize_tc5_kernel(const T *__restrict__ x, int64_t n_vec, const float *__restrict__ cb_all, int n_c, int n_sub,
                        void *__restrict__ indices, int index_bytes) {
     // With one codebook per sub-space (n_sub > 0) a CTA works on sub-space blockIdx.y only: its
     // rows are the sub-vectors sub, sub + n_sub, ... (row i is sub-vector i * vstride + sub).
@@ -237,33 +245,40 @@ vq_quantize_tc5_kernel(const __half *__restrict__ x, int64_t n_vec, const float 
     for (int i = tid; i < 2 * kRows * 16 / 4; i += kThreads) reinterpret_cast<uint32_t *>(sm.a2)[i] = 0u;
     for (int i = tid; i < 2 * 256 * 16 / 4; i += kThreads) reinterpret_cast<uint32_t *>(sm.b2)[i] = 0u;
     __syncthreads();
+    constexpr bool BF = std::is_same<T, __nv_bfloat16>::value;
     if (tid < kRows) {
-        // a2 chunk 0: every row starts with three ones
-        __half *row = reinterpret_cast<__half *>(sm.a2[0] + tid * 16);
-        row[0] = row[1] = row[2] = __float2half_rn(1.f);
+        // a2 chunk 0: every row starts with three (bf16: four) ones
+        T *row = reinterpret_cast<T *>(sm.a2[0] + tid * 16);
+        row[0] = row[1] = row[2] = from_f32<T>(1.f);
+        if (BF) row[3] = from_f32<T>(1.f);
     }
     for (int c = tid; c < N; c += kThreads) {
         float s2 = 0.f, mx = 0.f;
         bool bad = false;
-        __half *hi = reinterpret_cast<__half *>(sm.b1[0] + c * 16);
-        __half *lo = reinterpret_cast<__half *>(sm.b1[1] + c * 16);
+        T *p0 = reinterpret_cast<T *>(sm.b1[0] + c * 16);
+        T *p1 = reinterpret_cast<T *>(sm.b1[1] + c * 16);
+        T *p2 = reinterpret_cast<T *>(sm.b2[0] + c * 16);  // bf16 only: third piece
 #pragma unroll
         for (int k = 0; k < kSub; ++k) {
             const float v = cb[(int64_t)c * kSub + k];
             s2 = fmaf(v, v, s2);
             mx = fmaxf(mx, fabsf(v));
             bad |= !(fabsf(v) <= 64.f);
-            const __half h = __float2half_rn(v);
-            hi[k] = h;
-            lo[k] = __float2half_rn(v - __half2float(h));
+            const T a0 = from_f32<T>(v);
+            const float r1 = v - to_f32<T>(a0);
+            const T a1 = from_f32<T>(r1);
+            p0[k] = a0;
+            p1[k] = a1;
+            if (BF) p2[k] = from_f32<T>(r1 - to_f32<T>(a1));
         }
         float h = -0.5f * s2;
-        __half *hrow = reinterpret_cast<__half *>(sm.b2[0] + c * 16);
+        // f16: h pieces in K chunk 0 of the second MMA; bf16: in its chunk 1 (chunk 0 holds c2)
+        T *hrow = reinterpret_cast<T *>(sm.b2[BF ? 1 : 0] + c * 16);
 #pragma unroll
-        for (int k = 0; k < 3; ++k) {
-            const __half hk = __float2half_rn(h);
+        for (int k = 0; k < (BF ? 4 : 3); ++k) {
+            const T hk = from_f32<T>(h);
             hrow[k] = hk;
-            h -= __half2float(hk);
+            h -= to_f32<T>(hk);
         }
         atomicMax(reinterpret_cast<int *>(&sm.cmax2), __float_as_int(mx * mx));
         if (bad) sm.cb_bad = 1;
@@ -293,7 +308,7 @@ vq_quantize_tc5_kernel(const __half *__restrict__ x, int64_t n_vec, const float 
     const uint64_t desc_a2 = make_desc(smem_u32(sm.a2[0]), lbo_a, sbo_a);
     const uint64_t desc_b1 = make_desc(smem_u32(sm.b1[0]), lbo_b, sbo_b);
     const uint64_t desc_b2 = make_desc(smem_u32(sm.b2[0]), lbo_b, sbo_b);
-    const uint32_t idesc = make_idesc(kRows, N);
+    const uint32_t idesc = make_idesc(kRows, N, BF);
     const uint32_t bar = smem_u32(&sm.bar);
 
     // columns of this thread: the lower or the upper half (in whole 32-column chunks)
@@ -306,7 +321,7 @@ vq_quantize_tc5_kernel(const __half *__restrict__ x, int64_t n_vec, const float 
     auto fetch = [&](int64_t tile, int stage) {
         if (tid < kRows) {
             const int64_t row = min(tile * kRows + tid, n - 1);
-            const __half *src = x + (row * vstride + sub) * kSub;
+            const T *src = x + (row * vstride + sub) * kSub;
             const uint32_t d0 = smem_u32(sm.a[stage][0] + tid * 16), d1 = smem_u32(sm.a[stage][1] + tid * 16);
             asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d0), "l"(src) : "memory");
             asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d1), "l"(src) : "memory");
@@ -357,7 +372,13 @@ vq_quantize_tc5_kernel(const __half *__restrict__ x, int64_t n_vec, const float 
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const uint64_t desc_a = make_desc(smem_u32(sm.a[stage][0]), lbo_a, sbo_a);
             mma_f16_ss(tmem, desc_a, desc_b1, idesc, 0u);
-            mma_f16_ss(tmem, desc_a2, desc_b2, idesc, 1u);
+            if (BF) {
+                // second MMA of the bf16 form: x again (against c2) | the constant ones (against h)
+                const uint32_t a0 = smem_u32(sm.a[stage][0]);
+                mma_f16_ss(tmem, make_desc(a0, smem_u32(sm.a2[0]) - a0, sbo_a), desc_b2, idesc, 1u);
+            } else {
+                mma_f16_ss(tmem, desc_a2, desc_b2, idesc, 1u);
+            }
             asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
         }
         finish_prev();
@@ -371,7 +392,9 @@ vq_quantize_tc5_kernel(const __half *__restrict__ x, int64_t n_vec, const float 
             const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
-                const float2 f = __half22float2(*reinterpret_cast<const __half2 *>(&w[i]));
+                float2 f;
+                if (BF) f = make_float2(__uint_as_float(w[i] << 16), __uint_as_float(w[i] & 0xffff0000u));
+                else f = __half22float2(*reinterpret_cast<const __half2 *>(&w[i]));
                 xn = fmaf(f.x, f.x, fmaf(f.y, f.y, xn));
                 bad |= !(fabsf(f.x) <= 32768.f && fabsf(f.y) <= 32768.f);
             }
@@ -391,7 +414,8 @@ vq_quantize_tc5_kernel(const __half *__restrict__ x, int64_t n_vec, const float 
         sm.xch_m[half][r] = timed_out ? 0.f : pass_max(taddr, c_lo, c_hi);
         __syncthreads();  // C
         const float m = fmaxf(sm.xch_m[0][r], sm.xch_m[1][r]);
-        const float thr = m - 1.52587890625e-05f * (xn + cmax2);
+        // bf16: ~30 float32 roundings per score instead of ~20: the margin is doubled
+        const float thr = m - (BF ? 3.0517578125e-05f : 1.52587890625e-05f) * (xn + cmax2);
         // ---- pass 2: count and name the scores within delta of it ----------------------------
         float acc = 0.f, base = 0.f;
         if (!timed_out) pass_count(taddr, c_lo, c_hi, thr, acc, base);
@@ -416,27 +440,31 @@ vq_quantize_tc5_kernel(const __half *__restrict__ x, int64_t n_vec, const float 
 bool vq_quantize_tc5_supported(const void *x, int32_t x_dtype, int64_t n, int32_t sub_dim, int32_t n_c, int32_t n_sub) {
     static const char *mode = std::getenv("VQ_VQ_SEARCH");  // "exact" / "mma" / "tc5" pin one search
     if (mode && (std::strcmp(mode, "exact") == 0 || std::strcmp(mode, "mma") == 0)) return false;
-    if (x_dtype != VQ_F16 || sub_dim != kSub || n_sub < 0 || n_sub > 65535) return false;
+    if ((x_dtype != VQ_F16 && x_dtype != VQ_BF16) || sub_dim != kSub || n_sub < 0 || n_sub > 65535) return false;
     if (n_c < 16 || n_c > 256 || n_c % 16) return false;
     if (!is_aligned(x, 16)) return false;
     const bool forced = mode && std::strcmp(mode, "tc5") == 0;
     return forced ? n >= 1 : n >= 4096;  // small inputs: the CUDA-core search has no set-up cost
 }
 
-int32_t vq_quantize_tc5_launch(const void *x, int64_t n, const float *cb, int32_t n_c, int32_t n_sub, void *indices,
-                               int32_t index_bytes, cudaStream_t st) {
+int32_t vq_quantize_tc5_launch(const void *x, int32_t x_dtype, int64_t n, const float *cb, int32_t n_c, int32_t n_sub,
+                               void *indices, int32_t index_bytes, cudaStream_t st) {
     DeviceInfo di;
     int32_t rc = device_info(&di);
     if (rc != VQ_OK) return rc;
     // Two CTAs per SM: each holds 256 of the SM's 512 accumulator columns. The shared-memory
     // request is padded so that a third CTA (which would wait for columns) cannot be resident.
     const size_t smem = std::max(sizeof(Tc5Smem) + 128, (size_t)80 * 1024);
-    VQ_CHECK_CUDA(cudaFuncSetAttribute(vq_quantize_tc5_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    VQ_CHECK_CUDA(cudaFuncSetAttribute(vq_quantize_tc5_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    VQ_CHECK_CUDA(cudaFuncSetAttribute(vq_quantize_tc5_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     const int ny = n_sub > 0 ? n_sub : 1;
     const int64_t n_tiles = ceil_div(ceil_div(n, ny), kRows);
     const int64_t fill = std::max<int64_t>(1, ceil_div((int64_t)di.sm_count * 2, ny));  // CTAs per sub-space for two per SM
     const unsigned blocks = (unsigned)std::max<int64_t>(1, std::min<int64_t>(n_tiles, fill));
-    vq_quantize_tc5_kernel<<<dim3(blocks, ny), kThreads, smem, st>>>((const __half *)x, n, cb, n_c, n_sub, indices, index_bytes);
+    if (x_dtype == VQ_BF16)
+        vq_quantize_tc5_kernel<__nv_bfloat16><<<dim3(blocks, ny), kThreads, smem, st>>>((const __nv_bfloat16 *)x, n, cb, n_c, n_sub, indices, index_bytes);
+    else
+        vq_quantize_tc5_kernel<__half><<<dim3(blocks, ny), kThreads, smem, st>>>((const __half *)x, n, cb, n_c, n_sub, indices, index_bytes);
     VQ_CHECK_LAUNCH("vq_quantize_tc5_kernel");
     return VQ_OK;
 }
