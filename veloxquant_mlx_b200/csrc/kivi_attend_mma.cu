@@ -18,16 +18,23 @@
 // head with 5..8 query heads is covered by two CTAs (the second read hits L2).
 // Warp-level MMAs are used (not tcgen05) because the A operand is born in registers.
 //
-// Data movement: one CTA owns a contiguous run of 128-token tiles of one (batch, kv head).
-// Per tile six contiguous pieces (K codes, V codes, K scale/zero for 4 groups, V scale/zero
-// for 128 tokens) are fetched by the bulk async-copy engine (cp.async.bulk, completion on
-// an mbarrier) into a 2- to 4-stage shared-memory ring, so HBM reads stay in flight while the
-// warps unpack. Warp w owns token group w of each tile (32 tokens = one K scale group).
+// Data movement: each warp owns a contiguous run of 32-token groups of one (batch, kv head).
+// Per group six contiguous pieces (K codes, V codes, K scale/zero, V scale/zero) are fetched
+// by the bulk async-copy engine (completion on an mbarrier) into the warp's own 2- to 4-stage
+// shared-memory ring, so HBM reads stay in flight while the warp unpacks. Five pieces are
+// linear copies (cp.async.bulk). The V codes go through a tensor map (cp.async.bulk.tensor)
+// that views the packed rows as 128-byte lines and stores them with the 128-byte swizzle: the
+// transposing ldmatrix reads of V (8 token rows, one 16-byte segment each) then fall on 8
+// different bank groups instead of 2 (rows are only 64 or 32 bytes apart), which took a
+// quarter of the kernel's shared-memory wavefronts away.
 // The context is split across CTAs; each writes an unnormalised partial (m, l, o) and a
 // small second kernel merges them. The unquantized tail adds a few more partials from
 // CUDA-core CTAs in the same launch.
+#include <cuda.h>
+
 #include <algorithm>
 #include <cstdlib>
+#include <cstring>
 
 #include "kivi_attend.h"
 
@@ -60,7 +67,9 @@ struct Cfg {
     static constexpr int VS_OFF = KZ_OFF + 512;
     static constexpr int VZ_OFF = VS_OFF + 512;
     static constexpr int STAGE_BYTES = VZ_OFF + 512;  // one warp, one stage: 6144 / 4096
-    static constexpr int smem_bytes(int stages) { return 128 + kWarps * stages * STAGE_BYTES; }
+    static constexpr int VROWS = kGroup * RB / 128;   // 128-byte lines of one group's V codes: 16 / 8
+    // stages first (1024-byte aligned, as the swizzle pattern repeats every 1024 bytes), barriers after
+    static constexpr int smem_bytes(int stages) { return kWarps * stages * STAGE_BYTES + 128; }
 };
 
 // ---- PTX helpers ------------------------------------------------------------------------
@@ -94,6 +103,17 @@ __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void *src, uint32_t
         "l"(src), "r"(bytes), "r"(bar)
         : "memory");
 }
+// Tiled copy of one box of a rank-3 tensor map (x: bytes within a 128-byte line, always 0 here;
+// y: line; z: (batch, kv head)).
+__device__ __forceinline__ void tensor_g2s(uint32_t dst, const CUtensorMap *map, int x, int y, int z, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];" ::"r"(dst),
+        "l"(map), "r"(x), "r"(y), "r"(z), "r"(bar)
+        : "memory");
+}
+// Byte offset inside a 128-byte-swizzled tile (tile base 1024-byte aligned) of linear offset `lin`:
+// the 16-byte chunk index (bits 4-6) is XORed with the line index modulo 8 (bits 7-9).
+__device__ __forceinline__ uint32_t swz128(uint32_t lin) { return lin ^ (((lin >> 7) & 7u) << 4); }
 __device__ __forceinline__ uint32_t pack_h2(float lo, float hi) {
     __half2 h = __floats2half2_rn(lo, hi);
     return *reinterpret_cast<uint32_t *>(&h);
@@ -169,6 +189,7 @@ __device__ __forceinline__ float fast_exp2(float x) {
 }
 
 struct Params {
+    alignas(64) CUtensorMap v_map;  // V codes as [batch*kv head][lines of 128 bytes][128], swizzled boxes of one group
     vq_kivi_attend_args a;
     int hpk;
     int n_chunks;       // ceil(hpk / 4)
@@ -268,7 +289,7 @@ template <int BITS, int STAGES>
 __global__ void __launch_bounds__(kWarps * 32, 4)
 kivi_attend_mma_kernel(const __grid_constant__ Params p) {
     using C = Cfg<BITS>;
-    extern __shared__ __align__(128) uint8_t smem_raw[];
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
     const vq_kivi_attend_args &a = p.a;
     const int b = blockIdx.z, hkv = blockIdx.y;
     if ((int)blockIdx.x >= p.n_splits * p.n_chunks) {  // a tail CTA
@@ -283,9 +304,13 @@ kivi_attend_mma_kernel(const __grid_constant__ Params p) {
     const int hpk = p.hpk;
     const int64_t bh = (int64_t)b * a.H_kv + hkv;
 
-    uint64_t *bars = reinterpret_cast<uint64_t *>(smem_raw);
-    uint8_t *stages = smem_raw + 128;
+    uint8_t *stages = smem_raw;
+    uint64_t *bars = reinterpret_cast<uint64_t *>(smem_raw + kWarps * STAGES * C::STAGE_BYTES);
     const uint32_t bar0 = smem_u32(bars);
+    if (smem_u32(stages) & 1023u) {  // the swizzled addressing below assumes this; never seen
+        if (tid == 0) atomicExch(&g_attend_timeout, 2);
+        return;
+    }
 
     // Each warp owns a contiguous run of 32-token groups and runs its own copy pipeline:
     // no CTA-wide synchronisation until the final merge.
@@ -295,14 +320,16 @@ kivi_attend_mma_kernel(const __grid_constant__ Params p) {
     const uint32_t wbar0 = bar0 + 8u * (warp * STAGES);
     uint8_t *wstages = stages + (size_t)warp * STAGES * C::STAGE_BYTES;
 
-    const uint8_t *kc_g = a.k_codes + bh * a.k_codes_stride_bh;
-    const uint8_t *vc_g = a.v_codes + bh * a.v_codes_stride_bh;
-    const float *ks_g = a.k_scale + bh * a.k_param_stride_bh;
-    const float *kz_g = a.k_zero + bh * a.k_param_stride_bh;
-    const float *vs_g = a.v_scale + bh * a.v_param_stride_bh;
-    const float *vz_g = a.v_zero + bh * a.v_param_stride_bh;
-
     auto issue_group = [&](int local_idx) {  // called by lane 0 only
+        // The source addresses are rebuilt from the kernel parameters on every call (the opaque copy
+        // of bh keeps them from being hoisted): ten registers less held across the main loop.
+        int64_t bhv = bh;
+        asm volatile("" : "+l"(bhv));
+        const uint8_t *kc_g = a.k_codes + bhv * a.k_codes_stride_bh;
+        const float *ks_g = a.k_scale + bhv * a.k_param_stride_bh;
+        const float *kz_g = a.k_zero + bhv * a.k_param_stride_bh;
+        const float *vs_g = a.v_scale + bhv * a.v_param_stride_bh;
+        const float *vz_g = a.v_zero + bhv * a.v_param_stride_bh;
         const int64_t grp = grp_begin + local_idx;
         const int64_t tok0 = grp * kGroup;
         const int stage = local_idx % STAGES;
@@ -311,7 +338,7 @@ kivi_attend_mma_kernel(const __grid_constant__ Params p) {
         constexpr uint32_t code_bytes = kGroup * C::RB;
         mbar_expect_tx(bar, 2 * code_bytes + 4 * 512);
         bulk_g2s(dst + C::KC_OFF, kc_g + tok0 * C::RB, code_bytes, bar);
-        bulk_g2s(dst + C::VC_OFF, vc_g + tok0 * C::RB, code_bytes, bar);
+        tensor_g2s(dst + C::VC_OFF, &p.v_map, 0, (int)grp * C::VROWS, (int)bhv, bar);
         bulk_g2s(dst + C::KS_OFF, ks_g + grp * kD, 512, bar);
         bulk_g2s(dst + C::KZ_OFF, kz_g + grp * kD, 512, bar);
         bulk_g2s(dst + C::VS_OFF, vs_g + tok0 * 4, 512, bar);
@@ -356,6 +383,18 @@ kivi_attend_mma_kernel(const __grid_constant__ Params p) {
     const uint32_t v_sel = (g & 1) ? 0x7351u : 0x6240u;
     const int v_src = ((g >> 1) << 2) | c;
 
+    // ldmatrix row address of this lane inside the swizzled V tile: token 16*mt + 8*(mi&1) + r,
+    // 16-byte segment sb + (mi>>1); sb is 0 or 2, i.e. bit 5 of the linear offset (clear in the lane's
+    // part), so it is XORed in after the swizzle rather than added
+    // (4-bit: the second m-tile is 1024 bytes on, which leaves the XORed bits alone as well)
+    // (recomputed per group from the lane index: a handful of integer operations against a register
+    // held across the whole loop, which this kernel does not have to spare)
+    auto v_offset = [&](int mt) {
+        uint32_t ln = (uint32_t)lane;
+        asm volatile("" : "+r"(ln));
+        const uint32_t v_lin = ((8 * ((ln >> 3) & 1) + (ln & 7)) * C::RB + 16 * (ln >> 4));
+        return (BITS == 4) ? swz128(v_lin) + mt * 16 * C::RB : swz128(v_lin + mt * 16 * C::RB);
+    };
     float o[8][4];
 #pragma unroll
     for (int i = 0; i < 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
@@ -518,6 +557,7 @@ kivi_attend_mma_kernel(const __grid_constant__ Params p) {
 #pragma unroll
         for (int mt = 0; mt < 2; ++mt) {
             const int t0 = 16 * mt;
+            const uint32_t v_off = v_offset(mt);
             uint32_t pbw[4][2];  // [channel group][tokens 0-7 / 8-15 of the m-tile]
             {
                 // Lanes c and c^2 hold the same four P values. Each forms the products with the
@@ -552,11 +592,7 @@ kivi_attend_mma_kernel(const __grid_constant__ Params p) {
 #pragma unroll
             for (int sb = 0; sb < C::NSEG; sb += 2) {
                 uint32_t R[4];  // [segment sb + i/2][token block i%2]
-                {
-                    const int mi = lane >> 3, r = lane & 7;
-                    const uint32_t addr = smem_u32(st + C::VC_OFF + (t0 + 8 * (mi & 1) + r) * C::RB + 16 * (sb + (mi >> 1)));
-                    ldmatrix_x4_trans(R, addr);
-                }
+                ldmatrix_x4_trans(R, smem_u32(st + C::VC_OFF) + (v_off ^ (16 * sb)));
                 if constexpr (BITS == 2) {
                     // A 16-bit unit holds 8 channels, so the 8 lanes of a column span two
                     // channel groups. Regroup bytes so each lane holds channels 4g..4g+3 of
@@ -822,8 +858,57 @@ int32_t kivi_attend_mma_take_timeout(int *flag) {
     return VQ_OK;
 }
 
+// The driver's tensor-map encoder, looked up once through the runtime (no link against libcuda).
+using EncodeTiledFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                   const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static EncodeTiledFn encode_tiled_fn() {
+    static EncodeTiledFn fn = [] {
+        void *ptr = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) != cudaSuccess ||
+            qres != cudaDriverEntryPointSuccess)
+            ptr = nullptr;
+        return (EncodeTiledFn)ptr;
+    }();
+    return fn;
+}
+
+// V codes of all (batch, kv head) units as a rank-3 byte tensor [n_bh][lines][128]: a unit's rows
+// are contiguous, so 128 bytes hold 2 (4-bit) or 4 (2-bit) token rows; one box = one 32-token group.
+static int32_t make_v_map(const vq_kivi_attend_args &a, CUtensorMap *map) {
+    struct Key { const void *ptr; int64_t stride, n_quant; int32_t bits, n_bh; };
+    thread_local Key last_key = {nullptr, 0, 0, 0, 0};
+    thread_local CUtensorMap last_map;
+    const Key key = {a.v_codes, a.v_codes_stride_bh, a.n_quant, a.store_bits, a.B * a.H_kv};
+    if (key.ptr == last_key.ptr && key.stride == last_key.stride && key.n_quant == last_key.n_quant &&
+        key.bits == last_key.bits && key.n_bh == last_key.n_bh) {
+        *map = last_map;
+        return VQ_OK;
+    }
+    EncodeTiledFn enc = encode_tiled_fn();
+    VQ_REQUIRE(enc != nullptr, VQ_ERR_CUDA, "vq_kivi_decode_attend: the driver does not export cuTensorMapEncodeTiled");
+    const int rb = kD * a.store_bits / 8;
+    const cuuint64_t dims[3] = {128, (cuuint64_t)(a.n_quant * rb / 128), (cuuint64_t)key.n_bh};
+    // (the stride of a dimension of extent 1 is not used for addressing but is still checked)
+    const cuuint64_t strides[2] = {128, (cuuint64_t)std::max<int64_t>(a.v_codes_stride_bh, 128)};
+    const cuuint32_t box[3] = {128, (cuuint32_t)(kGroup * rb / 128), 1};
+    const cuuint32_t estr[3] = {1, 1, 1};
+    const CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<uint8_t *>(a.v_codes), dims, strides, box, estr,
+                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    VQ_REQUIRE(r == CUDA_SUCCESS, VQ_ERR_CUDA, "vq_kivi_decode_attend: cuTensorMapEncodeTiled failed (%d)", (int)r);
+    last_key = key;
+    last_map = *map;
+    return VQ_OK;
+}
+
 int32_t kivi_attend_mma_launch(const vq_kivi_attend_args &a, const DeviceInfo &di, cudaStream_t st) {
     Params p;
+    {
+        const int32_t rc = make_v_map(a, &p.v_map);
+        if (rc != VQ_OK) return rc;
+    }
     p.a = a;
     p.hpk = a.H_q / a.H_kv;
     p.n_chunks = (int)ceil_div(p.hpk, kChunkHeads);
