@@ -33,6 +33,7 @@
 #include <cuda.h>
 
 #include <algorithm>
+#include <cmath>
 #include <cstdlib>
 #include <cstring>
 
@@ -798,8 +799,24 @@ int choose_splits(const vq_kivi_attend_args &a, const DeviceInfo &di) {
     // Aim for several waves of CTAs so the last, partly filled wave costs little, but keep
     // at least 4 tiles per CTA so pipeline fill and the partial write stay amortised.
     int64_t want = std::max<int64_t>(1, (slots * tuned_waves()) / units);
-    want = std::min<int64_t>(want, std::max(1, tiles / 4));
-    return (int)std::min<int64_t>(want, kMergeMaxParts - 8);
+    const int64_t cap = std::min<int64_t>(std::max(1, tiles / 4), kMergeMaxParts - 8);
+    want = std::min<int64_t>(want, cap);
+    // With more than a wave of CTAs, what is lost is the partly filled last wave: among the
+    // counts near `want` take the one that fills its last wave best (a tail CTA runs about half
+    // as long as a main one; a slight preference for fewer, longer CTAs). Measured at batch 16,
+    // 8 kv heads, 32K context: 9 splits (2.05 waves) 194 us, 8 or 12..13 splits 188 us.
+    if (units * want >= slots) {
+        const double tails = a.n_res > 0 ? 0.5 * (double)a.B * a.H_kv : 0.0;
+        double best_score = -1.0;
+        int64_t best = want;
+        for (int64_t s = std::max<int64_t>(2, want - 2); s <= std::min<int64_t>(want + 4, cap); ++s) {
+            const double waves = ((double)units * s + tails) / (double)slots;
+            const double score = waves / std::ceil(waves) - 0.01 * (double)std::llabs(s - want);
+            if (score > best_score) { best_score = score; best = s; }
+        }
+        want = best;
+    }
+    return (int)want;
 }
 
 template <int BITS, int STAGES>
