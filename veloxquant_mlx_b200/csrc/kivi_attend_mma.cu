@@ -299,7 +299,10 @@ kivi_attend_mma_kernel(const __grid_constant__ Params p) {
     }
     const int split = blockIdx.x / p.n_chunks;
     const int h0 = (blockIdx.x % p.n_chunks) * kChunkHeads;  // first head of this CTA's chunk
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int tid = threadIdx.x, lane = tid & 31;
+    // (read through a shuffle so that the compiler knows the warp index is the same in all lanes:
+    // the pipeline's addresses, barriers and loop counters then live in uniform registers)
+    const int warp = __shfl_sync(0xffffffffu, tid >> 5, 0);
     const int g = lane >> 2, c = lane & 3;
     const int hd = g & 3, half_id = g >> 2;
     const int hpk = p.hpk;
@@ -322,10 +325,7 @@ kivi_attend_mma_kernel(const __grid_constant__ Params p) {
     uint8_t *wstages = stages + (size_t)warp * STAGES * C::STAGE_BYTES;
 
     auto issue_group = [&](int local_idx) {  // called by lane 0 only
-        // The source addresses are rebuilt from the kernel parameters on every call (the opaque copy
-        // of bh keeps them from being hoisted): ten registers less held across the main loop.
-        int64_t bhv = bh;
-        asm volatile("" : "+l"(bhv));
+        const int64_t bhv = bh;
         const uint8_t *kc_g = a.k_codes + bhv * a.k_codes_stride_bh;
         const float *ks_g = a.k_scale + bhv * a.k_param_stride_bh;
         const float *kz_g = a.k_zero + bhv * a.k_param_stride_bh;
