@@ -63,10 +63,11 @@ struct Cfg {
     static constexpr int NSEG = RB / 16;         // 16-byte segments per row: 4 / 2
     static constexpr int KC_OFF = 0;
     static constexpr int VC_OFF = kGroup * RB;
+    // (K scale and K zero tiles are swizzled and start on 1024-byte boundaries: same offsets in both)
     static constexpr int KS_OFF = 2 * kGroup * RB;
-    static constexpr int KZ_OFF = KS_OFF + 512;
-    static constexpr int VS_OFF = KZ_OFF + 512;
-    static constexpr int VZ_OFF = VS_OFF + 512;
+    static constexpr int VS_OFF = KS_OFF + 512;
+    static constexpr int KZ_OFF = VS_OFF + 512;
+    static constexpr int VZ_OFF = KZ_OFF + 512;
     static constexpr int STAGE_BYTES = VZ_OFF + 512;  // one warp, one stage: 6144 / 4096
     static constexpr int VROWS = kGroup * RB / 128;   // 128-byte lines of one group's V codes: 16 / 8
     // stages first (1024-byte aligned, as the swizzle pattern repeats every 1024 bytes), barriers after
@@ -190,7 +191,9 @@ __device__ __forceinline__ float fast_exp2(float x) {
 }
 
 struct Params {
-    alignas(64) CUtensorMap v_map;  // V codes as [batch*kv head][lines of 128 bytes][128], swizzled boxes of one group
+    alignas(64) CUtensorMap v_map;   // V codes as [batch*kv head][lines of 128 bytes][128], swizzled boxes of one group
+    alignas(64) CUtensorMap ks_map;  // K scales as [batch*kv head][4 lines per group][32 floats], swizzled boxes of one group
+    alignas(64) CUtensorMap kz_map;  // K zeros, likewise
     vq_kivi_attend_args a;
     int hpk;
     int n_chunks;       // ceil(hpk / 4)
@@ -327,8 +330,6 @@ kivi_attend_mma_kernel(const __grid_constant__ Params p) {
     auto issue_group = [&](int local_idx) {  // called by lane 0 only
         const int64_t bhv = bh;
         const uint8_t *kc_g = a.k_codes + bhv * a.k_codes_stride_bh;
-        const float *ks_g = a.k_scale + bhv * a.k_param_stride_bh;
-        const float *kz_g = a.k_zero + bhv * a.k_param_stride_bh;
         const float *vs_g = a.v_scale + bhv * a.v_param_stride_bh;
         const float *vz_g = a.v_zero + bhv * a.v_param_stride_bh;
         const int64_t grp = grp_begin + local_idx;
@@ -340,8 +341,8 @@ kivi_attend_mma_kernel(const __grid_constant__ Params p) {
         mbar_expect_tx(bar, 2 * code_bytes + 4 * 512);
         bulk_g2s(dst + C::KC_OFF, kc_g + tok0 * C::RB, code_bytes, bar);
         tensor_g2s(dst + C::VC_OFF, &p.v_map, 0, (int)grp * C::VROWS, (int)bhv, bar);
-        bulk_g2s(dst + C::KS_OFF, ks_g + grp * kD, 512, bar);
-        bulk_g2s(dst + C::KZ_OFF, kz_g + grp * kD, 512, bar);
+        tensor_g2s(dst + C::KS_OFF, &p.ks_map, 0, (int)grp * 4, (int)bhv, bar);
+        tensor_g2s(dst + C::KZ_OFF, &p.kz_map, 0, (int)grp * 4, (int)bhv, bar);
         bulk_g2s(dst + C::VS_OFF, vs_g + tok0 * 4, 512, bar);
         bulk_g2s(dst + C::VZ_OFF, vz_g + tok0 * 4, 512, bar);
     };
@@ -357,27 +358,21 @@ kivi_attend_mma_kernel(const __grid_constant__ Params p) {
 
     // This lane's 16 query channels (head hd) are channels 32c + 16*half_id + [0, 16), handled
     // as four blocks of 4. Unpacked K register (pair p, element e) couples the blocks
-    // blk(p, 0) and blk(p, 1). To keep the four lanes c of a quarter-warp on distinct
-    // shared-memory banks when they read their scales (their chunks are 128 B apart), slot
-    // (ps, ms) of lane c holds block blk(ps ^ (c >> 1), ms ^ (c & 1)); the permutation is
-    // undone with selects when the fragments are assembled. qd is pre-divided by the code
-    // weight of its element so that (code * weight) * (q * scale / weight) needs no fix-up.
-    const int c0 = c & 1, c1 = c >> 1;
-    int blk_off[4];  // float offset of the block held by slot s = 2*ps + ms
+    // blk(p, 0) and blk(p, 1). The four lanes c of a quarter-warp read chunks that are 128 bytes
+    // apart, which in a linear tile is the same bank for all four; the scale and zero tiles are
+    // therefore fetched through a tensor map with the 128-byte swizzle (16-byte block j of line
+    // c sits at j ^ c), and sc_off is where this lane finds its block L. qd is pre-divided by
+    // the code weight of its element so that (code * weight) * (q * scale / weight) needs no fix-up.
+    uint32_t sc_off[4];
 #pragma unroll
-    for (int s = 0; s < 4; ++s) {
-        const int pt = (s >> 1) ^ c1, mt_ = (s & 1) ^ c0;
-        blk_off[s] = 4 * ((BITS == 4) ? 2 * pt + mt_ : pt + 2 * mt_);
-    }
+    for (int L = 0; L < 4; ++L) sc_off[L] = (uint32_t)(128 * c + 16 * ((4 * half_id + L) ^ c));
     float qd[16];
     {
         const bool live = h0 + hd < hpk;
         const int64_t qbase = ((int64_t)b * a.H_q + hkv * hpk + h0 + hd) * kD + 32 * c + 16 * half_id;
 #pragma unroll
-        for (int s = 0; s < 4; ++s)
-#pragma unroll
-            for (int e = 0; e < 4; ++e)
-                qd[4 * s + e] = live ? load_as_f32(a.q, a.q_dtype, qbase + blk_off[s] + e) / code_weight<BITS>(e) : 0.f;
+        for (int i = 0; i < 16; ++i)
+            qd[i] = live ? load_as_f32(a.q, a.q_dtype, qbase + i) / code_weight<BITS>(i & 3) : 0.f;
     }
     // 2-bit only: byte selector that regroups ldmatrix output so that one register holds
     // 4 channels of each of two neighbouring channel groups (see the PV section).
@@ -429,37 +424,26 @@ kivi_attend_mma_kernel(const __grid_constant__ Params p) {
         uint32_t qf[16];
         float ck[2];
         {
-            const float *ks = reinterpret_cast<const float *>(st + C::KS_OFF) + 32 * c + 16 * half_id;
-            const float *kz = reinterpret_cast<const float *>(st + C::KZ_OFF) + 32 * c + 16 * half_id;
             float x[16];
             float cp[4] = {0.f, 0.f, 0.f, 0.f};  // per element index: sum q/weight * k_zero
 #pragma unroll
-            for (int s = 0; s < 4; ++s) {
-                const float4 s4 = *reinterpret_cast<const float4 *>(ks + blk_off[s]);
-                const float4 z4 = *reinterpret_cast<const float4 *>(kz + blk_off[s]);
-                x[4 * s + 0] = qd[4 * s + 0] * s4.x; x[4 * s + 1] = qd[4 * s + 1] * s4.y;
-                x[4 * s + 2] = qd[4 * s + 2] * s4.z; x[4 * s + 3] = qd[4 * s + 3] * s4.w;
-                cp[0] = fmaf(qd[4 * s + 0], z4.x, cp[0]); cp[1] = fmaf(qd[4 * s + 1], z4.y, cp[1]);
-                cp[2] = fmaf(qd[4 * s + 2], z4.z, cp[2]); cp[3] = fmaf(qd[4 * s + 3], z4.w, cp[3]);
+            for (int L = 0; L < 4; ++L) {
+                const float4 s4 = *reinterpret_cast<const float4 *>(st + C::KS_OFF + sc_off[L]);
+                const float4 z4 = *reinterpret_cast<const float4 *>(st + C::KZ_OFF + sc_off[L]);
+                x[4 * L + 0] = qd[4 * L + 0] * s4.x; x[4 * L + 1] = qd[4 * L + 1] * s4.y;
+                x[4 * L + 2] = qd[4 * L + 2] * s4.z; x[4 * L + 3] = qd[4 * L + 3] * s4.w;
+                cp[0] = fmaf(qd[4 * L + 0], z4.x, cp[0]); cp[1] = fmaf(qd[4 * L + 1], z4.y, cp[1]);
+                cp[2] = fmaf(qd[4 * L + 2], z4.z, cp[2]); cp[3] = fmaf(qd[4 * L + 3], z4.w, cp[3]);
             }
             float cpart = cp[0] * code_weight<BITS>(0) + cp[1] * code_weight<BITS>(1) +
                           cp[2] * code_weight<BITS>(2) + cp[3] * code_weight<BITS>(3);
-            uint32_t t_hi[2][4], t_lo[2][4];  // [slot pair ps][element]
-#pragma unroll
-            for (int ps = 0; ps < 2; ++ps) {
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const float m0 = x[4 * (2 * ps) + e], m1 = x[4 * (2 * ps + 1) + e];
-                    split_h2(c0 ? m1 : m0, c0 ? m0 : m1, t_hi[ps][e], t_lo[ps][e]);
-                }
-            }
             uint32_t own_hi[8], own_lo[8], recv[8];
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                own_hi[e] = c1 ? t_hi[1][e] : t_hi[0][e];
-                own_hi[4 + e] = c1 ? t_hi[0][e] : t_hi[1][e];
-                own_lo[e] = c1 ? t_lo[1][e] : t_lo[0][e];
-                own_lo[4 + e] = c1 ? t_lo[0][e] : t_lo[1][e];
+            for (int pt = 0; pt < 2; ++pt) {
+                // the two blocks that unpacked register pair pt couples
+                const int L0 = (BITS == 4) ? 2 * pt : pt, L1 = (BITS == 4) ? 2 * pt + 1 : pt + 2;
+#pragma unroll
+                for (int e = 0; e < 4; ++e) split_h2(x[4 * L0 + e], x[4 * L1 + e], own_hi[4 * pt + e], own_lo[4 * pt + e]);
             }
 #pragma unroll
             for (int ii = 0; ii < 8; ++ii) {
@@ -891,39 +875,47 @@ static EncodeTiledFn encode_tiled_fn() {
     return fn;
 }
 
-// V codes of all (batch, kv head) units as a rank-3 byte tensor [n_bh][lines][128]: a unit's rows
-// are contiguous, so 128 bytes hold 2 (4-bit) or 4 (2-bit) token rows; one box = one 32-token group.
-static int32_t make_v_map(const vq_kivi_attend_args &a, CUtensorMap *map) {
-    struct Key { const void *ptr; int64_t stride, n_quant; int32_t bits, n_bh; };
-    thread_local Key last_key = {nullptr, 0, 0, 0, 0};
-    thread_local CUtensorMap last_map;
-    const Key key = {a.v_codes, a.v_codes_stride_bh, a.n_quant, a.store_bits, a.B * a.H_kv};
-    if (key.ptr == last_key.ptr && key.stride == last_key.stride && key.n_quant == last_key.n_quant &&
-        key.bits == last_key.bits && key.n_bh == last_key.n_bh) {
-        *map = last_map;
+// A per-(batch, kv head) array of 128-byte lines as a rank-3 byte tensor [n_bh][lines][128] whose
+// boxes (`box_lines` lines) are stored with the 128-byte swizzle. Used for the V codes (a unit's
+// rows are contiguous, so a line holds 2 (4-bit) or 4 (2-bit) token rows; one box = one 32-token
+// group) and for the K scales / zeros (4 lines of 32 floats per group). The last encoding of
+// each of the three uses is kept per thread: a decode loop calls with the same buffers again.
+static int32_t make_line_map(int slot, const void *base, int64_t lines, int64_t stride_bh_bytes, int32_t n_bh,
+                             int32_t box_lines, CUtensorMap *map) {
+    struct Key { const void *ptr; int64_t lines, stride; int32_t n_bh, box; };
+    thread_local Key last_key[3] = {};
+    thread_local CUtensorMap last_map[3];
+    const Key key = {base, lines, stride_bh_bytes, n_bh, box_lines};
+    Key &lk = last_key[slot];
+    if (key.ptr == lk.ptr && key.lines == lk.lines && key.stride == lk.stride && key.n_bh == lk.n_bh && key.box == lk.box) {
+        *map = last_map[slot];
         return VQ_OK;
     }
     EncodeTiledFn enc = encode_tiled_fn();
     VQ_REQUIRE(enc != nullptr, VQ_ERR_CUDA, "vq_kivi_decode_attend: the driver does not export cuTensorMapEncodeTiled");
-    const int rb = kD * a.store_bits / 8;
-    const cuuint64_t dims[3] = {128, (cuuint64_t)(a.n_quant * rb / 128), (cuuint64_t)key.n_bh};
+    const cuuint64_t dims[3] = {128, (cuuint64_t)lines, (cuuint64_t)n_bh};
     // (the stride of a dimension of extent 1 is not used for addressing but is still checked)
-    const cuuint64_t strides[2] = {128, (cuuint64_t)std::max<int64_t>(a.v_codes_stride_bh, 128)};
-    const cuuint32_t box[3] = {128, (cuuint32_t)(kGroup * rb / 128), 1};
+    const cuuint64_t strides[2] = {128, (cuuint64_t)std::max<int64_t>(stride_bh_bytes, 128)};
+    const cuuint32_t box[3] = {128, (cuuint32_t)box_lines, 1};
     const cuuint32_t estr[3] = {1, 1, 1};
-    const CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<uint8_t *>(a.v_codes), dims, strides, box, estr,
+    const CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void *>(base), dims, strides, box, estr,
                            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     VQ_REQUIRE(r == CUDA_SUCCESS, VQ_ERR_CUDA, "vq_kivi_decode_attend: cuTensorMapEncodeTiled failed (%d)", (int)r);
-    last_key = key;
-    last_map = *map;
+    lk = key;
+    last_map[slot] = *map;
     return VQ_OK;
 }
 
 int32_t kivi_attend_mma_launch(const vq_kivi_attend_args &a, const DeviceInfo &di, cudaStream_t st) {
     Params p;
     {
-        const int32_t rc = make_v_map(a, &p.v_map);
+        const int rb = kD * a.store_bits / 8;
+        const int32_t n_bh = a.B * a.H_kv;
+        const int64_t groups = a.n_quant / kGroup;
+        int32_t rc = make_line_map(0, a.v_codes, a.n_quant * rb / 128, a.v_codes_stride_bh, n_bh, kGroup * rb / 128, &p.v_map);
+        if (rc == VQ_OK) rc = make_line_map(1, a.k_scale, groups * 4, a.k_param_stride_bh * 4, n_bh, 4, &p.ks_map);
+        if (rc == VQ_OK) rc = make_line_map(2, a.k_zero, groups * 4, a.k_param_stride_bh * 4, n_bh, 4, &p.kz_map);
         if (rc != VQ_OK) return rc;
     }
     p.a = a;
