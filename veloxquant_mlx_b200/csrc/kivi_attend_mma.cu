@@ -361,11 +361,10 @@ kivi_attend_mma_kernel(const __grid_constant__ Params p) {
     // blk(p, 0) and blk(p, 1). The four lanes c of a quarter-warp read chunks that are 128 bytes
     // apart, which in a linear tile is the same bank for all four; the scale and zero tiles are
     // therefore fetched through a tensor map with the 128-byte swizzle (16-byte block j of line
-    // c sits at j ^ c), and sc_off is where this lane finds its block L. qd is pre-divided by
+    // c sits at j ^ c), and sc_off0 is where this lane finds its block 0. qd is pre-divided by
     // the code weight of its element so that (code * weight) * (q * scale / weight) needs no fix-up.
-    uint32_t sc_off[4];
-#pragma unroll
-    for (int L = 0; L < 4; ++L) sc_off[L] = (uint32_t)(128 * c + 16 * ((4 * half_id + L) ^ c));
+    // Block L is at sc_off0 ^ 16L: L only touches the two bits that hold c.
+    const uint32_t sc_off0 = (uint32_t)(128 * c + 16 * ((4 * half_id) ^ c));
     float qd[16];
     {
         const bool live = h0 + hd < hpk;
@@ -383,14 +382,10 @@ kivi_attend_mma_kernel(const __grid_constant__ Params p) {
     // 16-byte segment sb + (mi>>1); sb is 0 or 2, i.e. bit 5 of the linear offset (clear in the lane's
     // part), so it is XORed in after the swizzle rather than added
     // (4-bit: the second m-tile is 1024 bytes on, which leaves the XORed bits alone as well)
-    // (recomputed per group from the lane index: a handful of integer operations against a register
-    // held across the whole loop, which this kernel does not have to spare)
-    auto v_offset = [&](int mt) {
-        uint32_t ln = (uint32_t)lane;
-        asm volatile("" : "+r"(ln));
-        const uint32_t v_lin = ((8 * ((ln >> 3) & 1) + (ln & 7)) * C::RB + 16 * (ln >> 4));
-        return (BITS == 4) ? swz128(v_lin) + mt * 16 * C::RB : swz128(v_lin + mt * 16 * C::RB);
-    };
+    // (4-bit: the second m-tile is 1024 bytes on, which leaves the XORed bits alone as well)
+    const uint32_t v_lin = (uint32_t)((8 * ((lane >> 3) & 1) + (lane & 7)) * C::RB + 16 * (lane >> 4));
+    const uint32_t v_off0 = swz128(v_lin);
+    const uint32_t v_off1 = (BITS == 4) ? v_off0 + 16 * C::RB : swz128(v_lin + 16 * C::RB);
     float o[8][4];
 #pragma unroll
     for (int i = 0; i < 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
@@ -428,8 +423,8 @@ kivi_attend_mma_kernel(const __grid_constant__ Params p) {
             float cp[4] = {0.f, 0.f, 0.f, 0.f};  // per element index: sum q/weight * k_zero
 #pragma unroll
             for (int L = 0; L < 4; ++L) {
-                const float4 s4 = *reinterpret_cast<const float4 *>(st + C::KS_OFF + sc_off[L]);
-                const float4 z4 = *reinterpret_cast<const float4 *>(st + C::KZ_OFF + sc_off[L]);
+                const float4 s4 = *reinterpret_cast<const float4 *>(st + C::KS_OFF + (sc_off0 ^ (16u * L)));
+                const float4 z4 = *reinterpret_cast<const float4 *>(st + C::KZ_OFF + (sc_off0 ^ (16u * L)));
                 x[4 * L + 0] = qd[4 * L + 0] * s4.x; x[4 * L + 1] = qd[4 * L + 1] * s4.y;
                 x[4 * L + 2] = qd[4 * L + 2] * s4.z; x[4 * L + 3] = qd[4 * L + 3] * s4.w;
                 cp[0] = fmaf(qd[4 * L + 0], z4.x, cp[0]); cp[1] = fmaf(qd[4 * L + 1], z4.y, cp[1]);
@@ -542,7 +537,7 @@ kivi_attend_mma_kernel(const __grid_constant__ Params p) {
 #pragma unroll
         for (int mt = 0; mt < 2; ++mt) {
             const int t0 = 16 * mt;
-            const uint32_t v_off = v_offset(mt);
+            const uint32_t v_off = mt ? v_off1 : v_off0;
             uint32_t pbw[4][2];  // [channel group][tokens 0-7 / 8-15 of the m-tile]
             {
                 // Lanes c and c^2 hold the same four P values. Each forms the products with the
