@@ -129,6 +129,11 @@ __device__ __forceinline__ void split_h2(float x0, float x1, uint32_t &hi, uint3
     const float2 h = unpack_h2(hi);
     lo = pack_h2(x0 - h.x, x1 - h.y);
 }
+// (half(x), half(x - half(x))) in one register: the column pair (2c, 2c+1) of one value.
+__device__ __forceinline__ uint32_t split_pack(float x) {
+    const float h = __half2float(__float2half_rn(x));
+    return pack_h2(x, x - h);
+}
 __device__ __forceinline__ void mma_f16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                         uint32_t b0, uint32_t b1) {
     asm volatile(
@@ -286,9 +291,10 @@ __device__ void tail_partial(const Params &p, uint8_t *smem_raw, int b, int hkv,
 
 // ---- main kernel ----------------------------------------------------------------------------
 // Lane roles (g = lane / 4, c = lane % 4):
-//   as a B-operand column (n = g): query head g % 4, high half if g < 4, low half otherwise;
-//   as an accumulator column pair (cols 2c, 2c+1): heads 2(c%2), 2(c%2)+1, high halves if
-//   c < 2, low halves otherwise (lanes c and c^2 hold the two halves of the same heads).
+//   as a B-operand column (n = g): query head g / 2, high half if g is even, low half otherwise;
+//   as an accumulator column pair (cols 2c, 2c+1): the high and the low half of head c, so
+//   a lane adds its two columns and owns ONE head for its rows: no exchange between lanes for
+//   the hi + lo sums, and the softmax of a head is computed once (by the 8 lanes g of column c).
 template <int BITS, int STAGES>
 __global__ void __launch_bounds__(kWarps * 32, 4)
 kivi_attend_mma_kernel(const __grid_constant__ Params p) {
@@ -307,7 +313,7 @@ kivi_attend_mma_kernel(const __grid_constant__ Params p) {
     // the pipeline's addresses, barriers and loop counters then live in uniform registers)
     const int warp = __shfl_sync(0xffffffffu, tid >> 5, 0);
     const int g = lane >> 2, c = lane & 3;
-    const int hd = g & 3, half_id = g >> 2;
+    const int hd = g >> 1, half_id = g & 1;
     const int hpk = p.hpk;
     const int64_t bh = (int64_t)b * a.H_kv + hkv;
 
@@ -389,14 +395,9 @@ kivi_attend_mma_kernel(const __grid_constant__ Params p) {
     float o[8][4];
 #pragma unroll
     for (int i = 0; i < 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
-    // sum_t P[t,h] * v_zero[t, group] for this lane's two channel groups 2*(c>>1), 2*(c>>1)+1
-    // (lanes c and c^2 hold the same P values and share the four groups between them)
-    float oz[2][2];
-#pragma unroll
-    for (int i = 0; i < 2; ++i) oz[0][i] = oz[1][i] = 0.f;
-    const int q2 = c >> 1;
-    float m_run[2] = {-INFINITY, -INFINITY};
-    float l_run[2] = {0.f, 0.f};
+    // sum_t P[t, head c] * v_zero[t, group] over this lane's tokens, for the four channel groups
+    float oz[4] = {0.f, 0.f, 0.f, 0.f};
+    float m_run = -INFINITY, l_run = 0.f;  // of head c
     const float sc = a.scale * 1.4426950408889634f;  // scores kept in the log2 domain
     bool timed_out = false;
 
@@ -414,10 +415,10 @@ kivi_attend_mma_kernel(const __grid_constant__ Params p) {
         const uint8_t *st = wstages + (size_t)stage * C::STAGE_BYTES;
 
         // ---- B operand of QK^T for this group: q*k_scale split into hi/lo halves ----------
-        // Lanes g and g^4 share a head; each computes both halves for 16 of the 32 channels
+        // Lanes g and g^1 share a head; each computes both halves for 16 of the 32 channels
         // of chunk c and they swap what the other needs.
         uint32_t qf[16];
-        float ck[2];
+        float ck;
         {
             float x[16];
             float cp[4] = {0.f, 0.f, 0.f, 0.f};  // per element index: sum q/weight * k_zero
@@ -443,7 +444,7 @@ kivi_attend_mma_kernel(const __grid_constant__ Params p) {
 #pragma unroll
             for (int ii = 0; ii < 8; ++ii) {
                 const uint32_t send = half_id ? own_hi[ii] : own_lo[ii];
-                recv[ii] = __shfl_xor_sync(0xffffffffu, send, 16);
+                recv[ii] = __shfl_xor_sync(0xffffffffu, send, 4);
             }
 #pragma unroll
             for (int ii = 0; ii < 8; ++ii) {
@@ -453,9 +454,8 @@ kivi_attend_mma_kernel(const __grid_constant__ Params p) {
             // zero-point term sum_d q[d]*k_zero[d] of head hd: reduce over c and the half pair
             cpart += __shfl_xor_sync(0xffffffffu, cpart, 1);
             cpart += __shfl_xor_sync(0xffffffffu, cpart, 2);
-            cpart += __shfl_xor_sync(0xffffffffu, cpart, 16);
-            ck[0] = __shfl_sync(0xffffffffu, cpart, (2 * (c & 1)) << 2);
-            ck[1] = __shfl_sync(0xffffffffu, cpart, (2 * (c & 1) + 1) << 2);
+            cpart += __shfl_xor_sync(0xffffffffu, cpart, 4);
+            ck = __shfl_sync(0xffffffffu, cpart, 8 * c);  // head c is computed by lanes g = 2c, 2c+1
         }
 
         // ---- S = codes . (q*k_scale)  for this warp's 32 tokens -----------------------------
@@ -488,48 +488,38 @@ kivi_attend_mma_kernel(const __grid_constant__ Params p) {
             }
         }
 
-        // ---- online softmax; this thread ends up with heads 2(c%2), 2(c%2)+1 --------------
-        float pr[2][4];
+        // ---- online softmax of head c over this lane's four tokens and the 8 lanes g ---------
+        float pr[2][2];  // [m-tile][token g / g + 8]
         {
 #pragma unroll
             for (int mt = 0; mt < 2; ++mt) {
-#pragma unroll
-                for (int r = 0; r < 4; ++r) {
-                    float s = s_acc[mt][r];
-                    s += __shfl_xor_sync(0xffffffffu, s, 2);  // high-half + low-half columns
-                    // the MMA saw codes * 2^-24; undo that and add the zero-point term
-                    pr[mt][r] = fmaf(s, sc * kTwo24, ck[r & 1] * sc);
-                }
+                // high-half + low-half column; the MMA saw codes * 2^-24: undo that and add the
+                // zero-point term
+                pr[mt][0] = fmaf(s_acc[mt][0] + s_acc[mt][1], sc * kTwo24, ck * sc);
+                pr[mt][1] = fmaf(s_acc[mt][2] + s_acc[mt][3], sc * kTwo24, ck * sc);
             }
-            float corr[2];
+            float v = fmaxf(fmaxf(pr[0][0], pr[0][1]), fmaxf(pr[1][0], pr[1][1]));
+            v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 4));
+            v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 8));
+            v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 16));
+            const float mn = fmaxf(m_run, v);
+            const float corr = fast_exp2(m_run - mn);
+            m_run = mn;
 #pragma unroll
-            for (int hh = 0; hh < 2; ++hh) {
-                float v = fmaxf(fmaxf(pr[0][hh], pr[0][hh + 2]), fmaxf(pr[1][hh], pr[1][hh + 2]));
-                v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 4));
-                v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 8));
-                v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 16));
-                const float mn = fmaxf(m_run[hh], v);
-                corr[hh] = fast_exp2(m_run[hh] - mn);
-                m_run[hh] = mn;
-                float sum = 0.f;
-#pragma unroll
-                for (int mt = 0; mt < 2; ++mt) {
-                    pr[mt][hh] = fast_exp2(pr[mt][hh] - mn);
-                    pr[mt][hh + 2] = fast_exp2(pr[mt][hh + 2] - mn);
-                    sum += pr[mt][hh] + pr[mt][hh + 2];
-                }
-                l_run[hh] = l_run[hh] * corr[hh] + sum;
+            for (int mt = 0; mt < 2; ++mt) {
+                pr[mt][0] = fast_exp2(pr[mt][0] - mn);
+                pr[mt][1] = fast_exp2(pr[mt][1] - mn);
             }
+            l_run = l_run * corr + ((pr[0][0] + pr[0][1]) + (pr[1][0] + pr[1][1]));
             // The running maxima settle after the first few groups; skip the rescale of the
-            // 40 accumulators whenever no lane's maximum moved (warp-uniform branch).
-            if (__any_sync(0xffffffffu, corr[0] != 1.f || corr[1] != 1.f)) {
+            // 36 accumulators whenever no lane's maximum moved (warp-uniform branch).
+            if (__any_sync(0xffffffffu, corr != 1.f)) {
 #pragma unroll
                 for (int i = 0; i < 8; ++i) {
-                    o[i][0] *= corr[0]; o[i][2] *= corr[0];
-                    o[i][1] *= corr[1]; o[i][3] *= corr[1];
+                    o[i][0] *= corr; o[i][1] *= corr; o[i][2] *= corr; o[i][3] *= corr;
                 }
 #pragma unroll
-                for (int i = 0; i < 2; ++i) { oz[0][i] *= corr[0]; oz[1][i] *= corr[1]; }
+                for (int j = 0; j < 4; ++j) oz[j] *= corr;
             }
         }
 
@@ -540,33 +530,21 @@ kivi_attend_mma_kernel(const __grid_constant__ Params p) {
             const uint32_t v_off = mt ? v_off1 : v_off0;
             uint32_t pbw[4][2];  // [channel group][tokens 0-7 / 8-15 of the m-tile]
             {
-                // Lanes c and c^2 hold the same four P values. Each forms the products with the
-                // value scales of two of the four channel groups (hi and lo halves of both),
-                // then they swap what the other needs: lanes c < 2 feed the high halves of all
-                // four groups into the transpose, lanes c >= 2 the low halves.
-                const float2 sa = *reinterpret_cast<const float2 *>(st + C::VS_OFF + (t0 + g) * 16 + 8 * q2);
-                const float2 sbv = *reinterpret_cast<const float2 *>(st + C::VS_OFF + (t0 + g + 8) * 16 + 8 * q2);
-                const float2 za = *reinterpret_cast<const float2 *>(st + C::VZ_OFF + (t0 + g) * 16 + 8 * q2);
-                const float2 zb = *reinterpret_cast<const float2 *>(st + C::VZ_OFF + (t0 + g + 8) * 16 + 8 * q2);
-                const float sa2[2] = {sa.x, sa.y}, sb2[2] = {sbv.x, sbv.y};
-                const float za2[2] = {za.x, za.y}, zb2[2] = {zb.x, zb.y};
-                const float pa0 = pr[mt][0], pa1 = pr[mt][1], pb0 = pr[mt][2], pb1 = pr[mt][3];
-                const bool low_lane = c < 2;
+                // P[token, head c] times the token's four value scales, each product split into
+                // (hi, lo) = this lane's column pair; the 8x8 transpose turns the P tile
+                // (tokens x columns) into the B operand (tokens on K, columns on N).
+                const float4 sa = *reinterpret_cast<const float4 *>(st + C::VS_OFF + (t0 + g) * 16);
+                const float4 sbv = *reinterpret_cast<const float4 *>(st + C::VS_OFF + (t0 + g + 8) * 16);
+                const float4 za = *reinterpret_cast<const float4 *>(st + C::VZ_OFF + (t0 + g) * 16);
+                const float4 zb = *reinterpret_cast<const float4 *>(st + C::VZ_OFF + (t0 + g + 8) * 16);
+                const float sa4[4] = {sa.x, sa.y, sa.z, sa.w}, sb4[4] = {sbv.x, sbv.y, sbv.z, sbv.w};
+                const float za4[4] = {za.x, za.y, za.z, za.w}, zb4[4] = {zb.x, zb.y, zb.z, zb.w};
+                const float pa = pr[mt][0], pb = pr[mt][1];
 #pragma unroll
-                for (int j = 0; j < 2; ++j) {
-                    oz[0][j] = fmaf(pa0, za2[j], fmaf(pb0, zb2[j], oz[0][j]));
-                    oz[1][j] = fmaf(pa1, za2[j], fmaf(pb1, zb2[j], oz[1][j]));
-                    uint32_t ha, la, hb, lb;
-                    split_h2(pa0 * sa2[j], pa1 * sa2[j], ha, la);
-                    split_h2(pb0 * sb2[j], pb1 * sb2[j], hb, lb);
-                    // what the partner lane needs from here / what this lane needs from there
-                    const uint32_t ra = __shfl_xor_sync(0xffffffffu, low_lane ? la : ha, 2);
-                    const uint32_t rb = __shfl_xor_sync(0xffffffffu, low_lane ? lb : hb, 2);
-                    // P tile (tokens x heads) -> B operand (tokens on K, heads on N): 8x8 transpose
-                    pbw[j][0] = movmatrix_trans(low_lane ? ha : ra);      // groups 0, 1
-                    pbw[j][1] = movmatrix_trans(low_lane ? hb : rb);
-                    pbw[2 + j][0] = movmatrix_trans(low_lane ? ra : la);  // groups 2, 3
-                    pbw[2 + j][1] = movmatrix_trans(low_lane ? rb : lb);
+                for (int j = 0; j < 4; ++j) {
+                    oz[j] = fmaf(pa, za4[j], fmaf(pb, zb4[j], oz[j]));
+                    pbw[j][0] = movmatrix_trans(split_pack(pa * sa4[j]));
+                    pbw[j][1] = movmatrix_trans(split_pack(pb * sb4[j]));
                 }
             }
 #pragma unroll
@@ -605,72 +583,45 @@ kivi_attend_mma_kernel(const __grid_constant__ Params p) {
     if (timed_out && lane == 0) atomicExch(&g_attend_timeout, 1);
 
     // ---- merge the four warps, write this split's partial -----------------------------------
+    l_run += __shfl_xor_sync(0xffffffffu, l_run, 4);
+    l_run += __shfl_xor_sync(0xffffffffu, l_run, 8);
+    l_run += __shfl_xor_sync(0xffffffffu, l_run, 16);
 #pragma unroll
-    for (int hh = 0; hh < 2; ++hh) {
-        float v = l_run[hh];
-        v += __shfl_xor_sync(0xffffffffu, v, 4);
-        v += __shfl_xor_sync(0xffffffffu, v, 8);
-        v += __shfl_xor_sync(0xffffffffu, v, 16);
-        l_run[hh] = v;
-#pragma unroll
-        for (int gd = 0; gd < 2; ++gd) {
-            float z = oz[hh][gd];
-            z += __shfl_xor_sync(0xffffffffu, z, 4);
-            z += __shfl_xor_sync(0xffffffffu, z, 8);
-            z += __shfl_xor_sync(0xffffffffu, z, 16);
-            oz[hh][gd] = z;
-        }
+    for (int j = 0; j < 4; ++j) {
+        float z = oz[j];
+        z += __shfl_xor_sync(0xffffffffu, z, 4);
+        z += __shfl_xor_sync(0xffffffffu, z, 8);
+        z += __shfl_xor_sync(0xffffffffu, z, 16);
+        oz[j] = z;
     }
     __syncthreads();  // all stages are drained: reuse them for the reduction
     float *red_o = reinterpret_cast<float *>(stages);               // [4 warps][4 heads][128]
     float *red_z = red_o + kWarps * kChunkHeads * kD;               // [4][4][4 groups]
     float *red_m = red_z + kWarps * kChunkHeads * 4;                // [4][4]
     float *red_l = red_m + kWarps * kChunkHeads;                    // [4][4]
-    const int hpair = 2 * (c & 1);
     // channel of accumulator rows g / g+8 of MMA i
     auto chan = [&](int i) {
         const int seg = i / (C::CU / 2), u = i % (C::CU / 2);
         if constexpr (BITS == 4) return 32 * seg + 4 * g + 2 * u;
         else return 64 * seg + 32 * (u >> 1) + 4 * g + 2 * (u & 1);
     };
-    // Accumulator rows saw codes * weight * 2^-24 (see unpack_word): undo per row.
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-        const int u = i % (C::CU / 2);
-        const float f0 = kTwo24 / code_weight<BITS>(2 * u), f1 = kTwo24 / code_weight<BITS>(2 * u + 1);
-        o[i][0] *= f0; o[i][1] *= f0;
-        o[i][2] *= f1; o[i][3] *= f1;
-    }
-    if (c < 2) {  // high-half columns first
+    {
+        // Accumulator rows saw codes * weight * 2^-24 (see unpack_word): undo per row; the two
+        // columns of a row are the high- and low-half contributions of head c.
+        float *base = red_o + (warp * kChunkHeads + c) * kD;
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
+            const int u = i % (C::CU / 2);
+            const float f0 = kTwo24 / code_weight<BITS>(2 * u), f1 = kTwo24 / code_weight<BITS>(2 * u + 1);
             const int d0 = chan(i);
-            float *base = red_o + (warp * kChunkHeads + hpair) * kD;
-            base[d0] = o[i][0]; base[kD + d0] = o[i][1];
-            base[d0 + 1] = o[i][2]; base[kD + d0 + 1] = o[i][3];
+            base[d0] = (o[i][0] + o[i][1]) * f0;
+            base[d0 + 1] = (o[i][2] + o[i][3]) * f1;
         }
         if (g == 0) {
+            red_m[warp * kChunkHeads + c] = m_run;
+            red_l[warp * kChunkHeads + c] = l_run;
 #pragma unroll
-            for (int hh = 0; hh < 2; ++hh) {
-                red_m[warp * kChunkHeads + hpair + hh] = m_run[hh];
-                red_l[warp * kChunkHeads + hpair + hh] = l_run[hh];
-            }
-        }
-    }
-    if (g == 0) {  // every lane c holds the zero-point sums of its own two channel groups
-#pragma unroll
-        for (int hh = 0; hh < 2; ++hh)
-#pragma unroll
-            for (int j = 0; j < 2; ++j) red_z[(warp * kChunkHeads + hpair + hh) * 4 + 2 * q2 + j] = oz[hh][j];
-    }
-    __syncwarp();
-    if (c >= 2) {  // then add the low-half columns
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            const int d0 = chan(i);
-            float *base = red_o + (warp * kChunkHeads + hpair) * kD;
-            base[d0] += o[i][0]; base[kD + d0] += o[i][1];
-            base[d0 + 1] += o[i][2]; base[kD + d0 + 1] += o[i][3];
+            for (int j = 0; j < 4; ++j) red_z[(warp * kChunkHeads + c) * 4 + j] = oz[j];
         }
     }
     __syncthreads();
