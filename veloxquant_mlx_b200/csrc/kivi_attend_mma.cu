@@ -302,6 +302,8 @@ kivi_attend_mma_kernel(const __grid_constant__ Params p) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     const vq_kivi_attend_args &a = p.a;
     const int b = blockIdx.z, hkv = blockIdx.y;
+    // the merge kernel may be made resident as soon as every CTA of this grid has started
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     if ((int)blockIdx.x >= p.n_splits * p.n_chunks) {  // a tail CTA
         tail_partial(p, smem_raw, b, hkv, (int)blockIdx.x - p.n_splits * p.n_chunks);
         return;
@@ -658,6 +660,9 @@ __global__ void __launch_bounds__(kD) kivi_attend_mma_merge_kernel(const __grid_
     const int b = (int)(bh / a.H_kv), hkv = (int)(bh % a.H_kv);
     const int d = threadIdx.x, lane = d & 31, warp = d >> 5;
     const int64_t rec0 = bh * p.n_parts * p.hpk + hp;  // record of part s: rec0 + s * hpk
+    // launched as a programmatic dependent of the main kernel: its partials are complete and
+    // visible only after this wait
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     // global maximum over parts
     float m = -INFINITY;
     for (int s = d; s < p.n_parts; s += kD) m = fmaxf(m, p.part_ml[(rec0 + (int64_t)s * p.hpk) * 2]);
@@ -888,8 +893,19 @@ int32_t kivi_attend_mma_launch(const vq_kivi_attend_args &a, const DeviceInfo &d
     dim3 grid(p.n_splits * p.n_chunks + p.n_tail, a.H_kv, a.B);
     const int32_t rc = a.store_bits == 4 ? launch_bits<4>(p, grid, st) : launch_bits<2>(p, grid, st);
     if (rc != VQ_OK) return rc;
-    kivi_attend_mma_merge_kernel<<<(unsigned)((int64_t)a.B * a.H_q), kD, 0, st>>>(p);
-    VQ_CHECK_LAUNCH("kivi_attend_mma_merge_kernel");
+    // Programmatic dependent launch: the merge CTAs become resident while the last main CTAs
+    // drain and wait (griddepcontrol.wait) until the main grid has completed and flushed.
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)((int64_t)a.B * a.H_q));
+    cfg.blockDim = dim3(kD);
+    cfg.dynamicSmemBytes = 0;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    VQ_CHECK_CUDA(cudaLaunchKernelEx(&cfg, kivi_attend_mma_merge_kernel, p));
     return VQ_OK;
 }
 
