@@ -648,8 +648,8 @@ kivi_attend_mma_kernel(const __grid_constant__ Params p) {
 }
 
 // One CTA per (batch, query head): combine the partials (log2-domain maxima). The split
-// weights are computed once into shared memory; the accumulation over splits is unrolled so
-// that several independent loads are in flight per thread (the loop is latency-bound).
+// weights are computed once into shared memory; the kernel is latency-bound, so the loads of
+// the (max, sum) pairs and of the first output partials are all issued up front.
 constexpr int kMergeMaxParts = 520;
 __global__ void __launch_bounds__(kD) kivi_attend_mma_merge_kernel(const __grid_constant__ Params p) {
     __shared__ float sh_w[kMergeMaxParts];
@@ -663,9 +663,24 @@ __global__ void __launch_bounds__(kD) kivi_attend_mma_merge_kernel(const __grid_
     // launched as a programmatic dependent of the main kernel: its partials are complete and
     // visible only after this wait
     asm volatile("griddepcontrol.wait;" ::: "memory");
+    // One round trip to memory instead of three: every thread reads the (max, sum) pairs of its
+    // parts once, and the first 16 output partials are requested before the weights are known.
+    constexpr int kMl = (kMergeMaxParts + kD - 1) / kD;
+    constexpr int kAheadParts = 16;
+    float2 ml[kMl];
+#pragma unroll
+    for (int i = 0; i < kMl; ++i) {
+        const int s = d + i * kD;
+        ml[i] = s < p.n_parts ? *reinterpret_cast<const float2 *>(p.part_ml + (rec0 + (int64_t)s * p.hpk) * 2)
+                              : make_float2(-INFINITY, 0.f);
+    }
+    float v[kAheadParts];
+#pragma unroll
+    for (int j = 0; j < kAheadParts; ++j) v[j] = j < p.n_parts ? p.part_o[(rec0 + (int64_t)j * p.hpk) * kD + d] : 0.f;
     // global maximum over parts
     float m = -INFINITY;
-    for (int s = d; s < p.n_parts; s += kD) m = fmaxf(m, p.part_ml[(rec0 + (int64_t)s * p.hpk) * 2]);
+#pragma unroll
+    for (int i = 0; i < kMl; ++i) m = fmaxf(m, ml[i].x);
     m = warp_max(m);
     if (lane == 0) sh_red[warp] = m;
     __syncthreads();
@@ -673,24 +688,30 @@ __global__ void __launch_bounds__(kD) kivi_attend_mma_merge_kernel(const __grid_
     __syncthreads();
     // per-part weight, and the denominator
     float l = 0.f;
-    for (int s = d; s < p.n_parts; s += kD) {
-        const float ms = p.part_ml[(rec0 + (int64_t)s * p.hpk) * 2];
-        const float w = (ms == -INFINITY) ? 0.f : exp2f(ms - gm);
-        sh_w[s] = w;
-        l += w * p.part_ml[(rec0 + (int64_t)s * p.hpk) * 2 + 1];
+#pragma unroll
+    for (int i = 0; i < kMl; ++i) {
+        const int s = d + i * kD;
+        if (s < p.n_parts) {
+            const float w = (ml[i].x == -INFINITY) ? 0.f : exp2f(ml[i].x - gm);
+            sh_w[s] = w;
+            l += w * ml[i].y;
+        }
     }
     l = warp_sum(l);
     if (lane == 0) sh_red[warp] = l;
     __syncthreads();
     const float gl = sh_red[0] + sh_red[1] + sh_red[2] + sh_red[3];
     float acc = 0.f;
-    int s = 0;
+#pragma unroll
+    for (int j = 0; j < kAheadParts; ++j)
+        if (j < p.n_parts) acc = fmaf(v[j], sh_w[j], acc);
+    int s = kAheadParts;
     for (; s + 8 <= p.n_parts; s += 8) {
-        float v[8];
+        float u[8];
 #pragma unroll
-        for (int j = 0; j < 8; ++j) v[j] = p.part_o[(rec0 + (int64_t)(s + j) * p.hpk) * kD + d];
+        for (int j = 0; j < 8; ++j) u[j] = p.part_o[(rec0 + (int64_t)(s + j) * p.hpk) * kD + d];
 #pragma unroll
-        for (int j = 0; j < 8; ++j) acc = fmaf(v[j], sh_w[s + j], acc);
+        for (int j = 0; j < 8; ++j) acc = fmaf(u[j], sh_w[s + j], acc);
     }
     for (; s < p.n_parts; ++s) acc = fmaf(p.part_o[(rec0 + (int64_t)s * p.hpk) * kD + d], sh_w[s], acc);
     const int64_t row = (int64_t)b * a.H_q + hkv * p.hpk + hp;
