@@ -28,8 +28,8 @@
 // different bank groups instead of 2 (rows are only 64 or 32 bytes apart), which took a
 // quarter of the kernel's shared-memory wavefronts away.
 // The context is split across CTAs; each writes an unnormalised partial (m, l, o) and a
-// small second kernel merges them. The unquantized tail adds a few more partials from
-// CUDA-core CTAs in the same launch.
+// small kernel merges them. The unquantized tail adds a few more partials from a CUDA-core
+// kernel that runs while the main grid drains (programmatic dependent launch).
 #include <cuda.h>
 
 #include <algorithm>
@@ -212,20 +212,38 @@ struct Params {
 };
 
 // ---- tail (unquantized tokens): CUDA cores, n_tail CTAs per (batch, kv head) ---------------
-// Tail CTA `ti` takes an equal slice of the tail tokens; inside it each warp takes every fourth
-// token. The per-token loop is latency-bound, so on short contexts (where the tail is what the
-// launch waits for) the tail is spread over several CTAs. (Loading several tokens ahead inside
-// this function changed the register allocation of the main path and cost it 3-10 %: measured.)
-__device__ void tail_partial(const Params &p, uint8_t *smem_raw, int b, int hkv, int ti) {
+// A kernel of its own, launched after the main kernel as its programmatic dependent: its CTAs
+// become resident once every main CTA has started, i.e. they run on the SMs that the draining
+// main grid leaves idle, and they need nothing the main grid writes. Before it exits, each CTA
+// waits for the main grid (griddepcontrol.wait), so that the merge kernel, which waits for THIS
+// grid, also sees the main grid's partials complete. Tail CTA `ti` takes an equal slice of the
+// tail tokens; inside it each warp takes every fourth token, four tokens' rows in flight.
+template <typename T>
+__device__ __forceinline__ void load_row4(const T *p, float (&d)[4]) {
+    if constexpr (sizeof(T) == 2) {
+        const uint2 raw = *reinterpret_cast<const uint2 *>(p);
+        const T *h = reinterpret_cast<const T *>(&raw);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) d[i] = to_f32<T>(h[i]);
+    } else {
+        const float4 v = *reinterpret_cast<const float4 *>(p);
+        d[0] = v.x; d[1] = v.y; d[2] = v.z; d[3] = v.w;
+    }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kWarps * 32) kivi_attend_tail_kernel(const __grid_constant__ Params p) {
+    constexpr int kAheadTok = 4;
+    __shared__ __align__(16) float sh_q[kMaxHeads * kD];
+    __shared__ __align__(16) float sh_o[kWarps * kMaxHeads * kD];
+    __shared__ float sh_m[kWarps * kMaxHeads], sh_l[kWarps * kMaxHeads];
     const vq_kivi_attend_args &a = p.a;
-    float *sh_q = reinterpret_cast<float *>(smem_raw);           // [8][128]
-    float *sh_o = sh_q + kMaxHeads * kD;                         // [4][8][128]
-    float *sh_m = sh_o + kWarps * kMaxHeads * kD;                // [4][8]
-    float *sh_l = sh_m + kWarps * kMaxHeads;                     // [4][8]
+    const int ti = blockIdx.x, hkv = blockIdx.y, b = blockIdx.z;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int hpk = p.hpk;
     const int64_t bh = (int64_t)b * a.H_kv + hkv;
     const float sc = a.scale * 1.4426950408889634f;
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");  // the merge kernel may become resident
     for (int i = threadIdx.x; i < hpk * kD; i += blockDim.x) {
         const int hp = i / kD, d = i % kD;
         sh_q[i] = load_as_f32(a.q, a.q_dtype, ((int64_t)b * a.H_q + hkv * hpk + hp) * kD + d) * sc;
@@ -240,25 +258,31 @@ __device__ void tail_partial(const Params &p, uint8_t *smem_raw, int b, int hkv,
     }
     const int per_cta = (a.n_res + p.n_tail - 1) / p.n_tail;
     const int t_begin = ti * per_cta, t_end = min(a.n_res, t_begin + per_cta);
-    for (int t = t_begin + warp; t < t_end; t += kWarps) {
-        const int64_t r = bh * a.res_stride_bh + (int64_t)t * kD + lane * 4;
-        float kd[4], vd[4];
+    const T *kr = reinterpret_cast<const T *>(a.k_res) + bh * a.res_stride_bh + lane * 4;
+    const T *vr = reinterpret_cast<const T *>(a.v_res) + bh * a.res_stride_bh + lane * 4;
+    for (int t0 = t_begin + warp; t0 < t_end; t0 += kWarps * kAheadTok) {
+        float kd[kAheadTok][4], vd[kAheadTok][4];
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            kd[i] = load_as_f32(a.k_res, a.res_dtype, r + i);
-            vd[i] = load_as_f32(a.v_res, a.res_dtype, r + i);
+        for (int j = 0; j < kAheadTok; ++j) {
+            const int t = min(t0 + j * kWarps, t_end - 1);  // (a repeated row past the end is skipped below)
+            load_row4<T>(kr + (int64_t)t * kD, kd[j]);
+            load_row4<T>(vr + (int64_t)t * kD, vd[j]);
         }
 #pragma unroll
-        for (int hp = 0; hp < kMaxHeads; ++hp) {
-            if (hp < hpk) {
-                const float4 qv = *reinterpret_cast<const float4 *>(sh_q + hp * kD + lane * 4);
-                float s = warp_sum(qv.x * kd[0] + qv.y * kd[1] + qv.z * kd[2] + qv.w * kd[3]);
-                const float mn = fmaxf(m[hp], s);
-                const float f = exp2f(m[hp] - mn), w = exp2f(s - mn);
-                l[hp] = l[hp] * f + w;
-                m[hp] = mn;
+        for (int j = 0; j < kAheadTok; ++j) {
+            if (t0 + j * kWarps >= t_end) break;
 #pragma unroll
-                for (int i = 0; i < 4; ++i) o[hp][i] = o[hp][i] * f + w * vd[i];
+            for (int hp = 0; hp < kMaxHeads; ++hp) {
+                if (hp < hpk) {
+                    const float4 qv = *reinterpret_cast<const float4 *>(sh_q + hp * kD + lane * 4);
+                    const float sv = warp_sum(qv.x * kd[j][0] + qv.y * kd[j][1] + qv.z * kd[j][2] + qv.w * kd[j][3]);
+                    const float mn = fmaxf(m[hp], sv);
+                    const float f = exp2f(m[hp] - mn), w = exp2f(sv - mn);
+                    l[hp] = l[hp] * f + w;
+                    m[hp] = mn;
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) o[hp][i] = o[hp][i] * f + w * vd[j][i];
+                }
             }
         }
     }
@@ -287,6 +311,8 @@ __device__ void tail_partial(const Params &p, uint8_t *smem_raw, int b, int hkv,
         p.part_o[rec * kD + d] = acc;
         if (d == 0) { p.part_ml[rec * 2] = gm; p.part_ml[rec * 2 + 1] = gl; }
     }
+    // this grid completes only after the main grid has (see the note above the kernel)
+    asm volatile("griddepcontrol.wait;" ::: "memory");
 }
 
 // ---- main kernel ----------------------------------------------------------------------------
@@ -302,12 +328,8 @@ kivi_attend_mma_kernel(const __grid_constant__ Params p) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     const vq_kivi_attend_args &a = p.a;
     const int b = blockIdx.z, hkv = blockIdx.y;
-    // the merge kernel may be made resident as soon as every CTA of this grid has started
+    // the tail and merge kernels may be made resident as soon as every CTA of this grid has started
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-    if ((int)blockIdx.x >= p.n_splits * p.n_chunks) {  // a tail CTA
-        tail_partial(p, smem_raw, b, hkv, (int)blockIdx.x - p.n_splits * p.n_chunks);
-        return;
-    }
     const int split = blockIdx.x / p.n_chunks;
     const int h0 = (blockIdx.x % p.n_chunks) * kChunkHeads;  // first head of this CTA's chunk
     const int tid = threadIdx.x, lane = tid & 31;
@@ -738,8 +760,7 @@ int tuned_waves() {
 }
 
 int smem_for(int bits, int stages) {
-    const int tail_smem = (kMaxHeads * kD + kWarps * kMaxHeads * kD + 2 * kWarps * kMaxHeads) * 4;
-    return std::max(bits == 4 ? Cfg<4>::smem_bytes(stages) : Cfg<2>::smem_bytes(stages), tail_smem);
+    return bits == 4 ? Cfg<4>::smem_bytes(stages) : Cfg<2>::smem_bytes(stages);
 }
 
 int choose_splits(const vq_kivi_attend_args &a, const DeviceInfo &di) {
@@ -762,7 +783,7 @@ int choose_splits(const vq_kivi_attend_args &a, const DeviceInfo &di) {
     // as long as a main one; a slight preference for fewer, longer CTAs). Measured at batch 16,
     // 8 kv heads, 32K context: 9 splits (2.05 waves) 194 us, 8 or 12..13 splits 188 us.
     if (units * want >= slots) {
-        const double tails = a.n_res > 0 ? 0.5 * (double)a.B * a.H_kv : 0.0;
+        const double tails = 0.0;  // the tail runs as a kernel of its own
         double best_score = -1.0;
         int64_t best = want;
         for (int64_t s = std::max<int64_t>(2, want - 2); s <= std::min<int64_t>(want + 4, cap); ++s) {
@@ -814,6 +835,8 @@ const char *kivi_attend_mma_supported(const vq_kivi_attend_args &a) {
         return "scale/zero buffers must be 16-byte aligned";
     if (a.n_res > 0 && a.res_dtype != VQ_F16 && a.res_dtype != VQ_BF16 && a.res_dtype != VQ_F32)
         return "bad residual dtype";
+    if (a.n_res > 0 && (!is_aligned(a.k_res, 16) || !is_aligned(a.v_res, 16) || a.res_stride_bh % 8))
+        return "residual buffers must be 16-byte aligned";
     return nullptr;
 }
 
@@ -898,9 +921,7 @@ int32_t kivi_attend_mma_launch(const vq_kivi_attend_args &a, const DeviceInfo &d
     p.groups_per_warp = (int)ceil_div(p.groups_total, (int64_t)p.n_splits * kWarps);
     // a split count that leaves trailing splits empty is trimmed
     p.n_splits = (int)ceil_div(p.groups_total, (int64_t)p.groups_per_warp * kWarps);
-    // Several tail CTAs only where the quantized part is short enough for a single tail CTA to
-    // be what the launch waits for; on long contexts they would only take slots from the rest.
-    p.n_tail = p.groups_per_warp <= 8 ? kivi_attend_mma_tail_parts(a) : std::min(1, kivi_attend_mma_tail_parts(a));
+    p.n_tail = kivi_attend_mma_tail_parts(a);
     p.n_parts = p.n_splits + p.n_tail;
     const int64_t recs = (int64_t)a.B * a.H_kv * p.n_parts * p.hpk;
     const int64_t need = recs * (kD + 2) * (int64_t)sizeof(float);
@@ -911,13 +932,13 @@ int32_t kivi_attend_mma_launch(const vq_kivi_attend_args &a, const DeviceInfo &d
     p.part_o = (float *)a.workspace;
     p.part_ml = p.part_o + recs * kD;
 
-    dim3 grid(p.n_splits * p.n_chunks + p.n_tail, a.H_kv, a.B);
+    dim3 grid(p.n_splits * p.n_chunks, a.H_kv, a.B);
     const int32_t rc = a.store_bits == 4 ? launch_bits<4>(p, grid, st) : launch_bits<2>(p, grid, st);
     if (rc != VQ_OK) return rc;
-    // Programmatic dependent launch: the merge CTAs become resident while the last main CTAs
-    // drain and wait (griddepcontrol.wait) until the main grid has completed and flushed.
+    // Programmatic dependent launches: the tail CTAs, then the merge CTAs, become resident while
+    // the last main CTAs drain. The tail grid ends with griddepcontrol.wait (on the main grid),
+    // the merge grid starts with it (on the tail grid, or on the main grid if there is no tail).
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((unsigned)((int64_t)a.B * a.H_q));
     cfg.blockDim = dim3(kD);
     cfg.dynamicSmemBytes = 0;
     cfg.stream = st;
@@ -926,6 +947,13 @@ int32_t kivi_attend_mma_launch(const vq_kivi_attend_args &a, const DeviceInfo &d
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
+    if (p.n_tail > 0) {
+        cfg.gridDim = dim3(p.n_tail, a.H_kv, a.B);
+        if (a.res_dtype == VQ_F16) VQ_CHECK_CUDA(cudaLaunchKernelEx(&cfg, kivi_attend_tail_kernel<__half>, p));
+        else if (a.res_dtype == VQ_BF16) VQ_CHECK_CUDA(cudaLaunchKernelEx(&cfg, kivi_attend_tail_kernel<__nv_bfloat16>, p));
+        else VQ_CHECK_CUDA(cudaLaunchKernelEx(&cfg, kivi_attend_tail_kernel<float>, p));
+    }
+    cfg.gridDim = dim3((unsigned)((int64_t)a.B * a.H_q));
     VQ_CHECK_CUDA(cudaLaunchKernelEx(&cfg, kivi_attend_mma_merge_kernel, p));
     return VQ_OK;
 }
