@@ -102,6 +102,24 @@ def test_decode_tokens_age_out_with_small_groups():
     assert max(sizes) <= (4 + 4) * 128 * 2 * 2 and c.offset == 22
 
 
+def test_append_of_two_slices_of_one_buffer_equals_separate_tensors():
+    """K and V that arrive as two slices of one tensor (a fused projection's output) are appended
+    by one copy; the cache contents must not depend on that."""
+    a, b = _make(residual_length=8, kivi_group_size=4), _make(residual_length=8, kivi_group_size=4)
+    for t in range(15):
+        buf = torch.randn(3, 2, 2, 1, 128, device=DEV, dtype=torch.float16,
+                          generator=torch.Generator(device=DEV).manual_seed(40 + t))
+        k, v = buf[1], buf[2]                   # same storage, fixed offset
+        a.update_and_fetch(k, v)
+        b.update_and_fetch(k.clone(), v.clone())  # two storages
+        if t == 3:  # a pair in reversed order (values before keys) must take the two-copy path
+            a.update_and_fetch(buf[2], buf[1])
+            b.update_and_fetch(buf[2].clone(), buf[1].clone())
+    ka, va = a._materialize()
+    kb, vb = b._materialize()
+    assert torch.equal(ka, kb) and torch.equal(va, vb) and a.offset == b.offset == 16
+
+
 @pytest.mark.parametrize("b", [2, 4])
 @pytest.mark.parametrize("memory_bound", [False, True])
 def test_fused_sdpa_matches_oracle(b, memory_bound):

@@ -235,6 +235,19 @@ def _native_only(config, who: str) -> None:
 # ----------------------------------------------------------------------------------------
 # KIVI
 # ----------------------------------------------------------------------------------------
+def _paired_view(keys: torch.Tensor, values: torch.Tensor):
+    """``[2, *keys.shape]`` view over both tensors if ``values`` is ``keys`` shifted by a fixed
+    positive offset inside one storage (two slices of one buffer), else ``None``."""
+    if keys.dtype != values.dtype or keys.stride() != values.stride() or keys.shape != values.shape:
+        return None
+    if keys.untyped_storage().data_ptr() != values.untyped_storage().data_ptr():
+        return None
+    delta = values.storage_offset() - keys.storage_offset()
+    if delta <= 0:
+        return None
+    return torch.as_strided(keys, (2, *keys.shape), (delta, *keys.stride()), keys.storage_offset())
+
+
 class KIVIKVCache:
     """Packed KIVI cache: per-channel keys, per-token values, fp residual window.
 
@@ -273,7 +286,7 @@ class KIVIKVCache:
         self._cap = 0
         self._k_codes = self._v_codes = None
         self._k_scale = self._k_zero = self._v_scale = self._v_zero = None
-        self._k_res = self._v_res = None
+        self._kv_res = self._k_res = self._v_res = None
         self._shape_bhd = (1, 1, self._head_dim)
         self._dtype = None
         # byte accounting (same definitions as the reference's properties)
@@ -319,12 +332,14 @@ class KIVIKVCache:
         if self._k_res is not None and self._k_res.shape[2] >= n:
             return
         cap = max(self._residual_length + 2 * self._group_size, n)
-        k = torch.empty((B, H, cap, D), dtype=dtype, device=device)
-        v = torch.empty((B, H, cap, D), dtype=dtype, device=device)
+        # one allocation for both, so that a K/V pair that arrives as two slices of one tensor
+        # (a fused QKV projection's output) is appended by a single copy
+        kv = torch.empty((2, B, H, cap, D), dtype=dtype, device=device)
+        k, v = kv[0], kv[1]
         if self._k_res is not None and self._n_res:
             k[:, :, : self._n_res] = self._k_res[:, :, : self._n_res]
             v[:, :, : self._n_res] = self._v_res[:, :, : self._n_res]
-        self._k_res, self._v_res = k, v
+        self._kv_res, self._k_res, self._v_res = kv, k, v
 
     # -- protocol ----------------------------------------------------------------------
     def update_and_fetch(self, keys: torch.Tensor, values: torch.Tensor):
@@ -345,8 +360,12 @@ class KIVIKVCache:
         n_flush = new_boundary - self._n_quantized
         if n_flush <= 0:
             self._ensure_residual(B, H, D, self._n_res + S, dev, keys.dtype)
-            self._k_res[:, :, self._n_res : self._n_res + S] = keys
-            self._v_res[:, :, self._n_res : self._n_res + S] = values
+            pair = _paired_view(keys, values)
+            if pair is not None:
+                self._kv_res[:, :, :, self._n_res : self._n_res + S] = pair
+            else:
+                self._k_res[:, :, self._n_res : self._n_res + S] = keys
+                self._v_res[:, :, self._n_res : self._n_res + S] = values
             self._n_res += S
         else:
             # Rows to flush are the oldest unquantized ones: the residual first, then the
@@ -500,7 +519,7 @@ class KIVIKVCache:
             self._k_scale[:, :, : nq // g], self._k_zero[:, :, : nq // g] = ks, kz
             self._v_scale[:, :, :nq], self._v_zero[:, :, :nq] = vs, vz
         self._n_quantized = nq
-        self._k_res = self._v_res = None
+        self._kv_res = self._k_res = self._v_res = None
         self._n_res = 0
         self._ensure_residual(B, H, D, n_res, kr.device, kr.dtype)
         self._k_res[:, :, :n_res], self._v_res[:, :, :n_res] = kr, vr
