@@ -343,6 +343,21 @@ def test_mma_attend_parity(b, H, H_kv, n_quant, n_res):
     _assert_attn_close(out3.float().cpu().numpy(), ref)
 
 
+@pytest.mark.parametrize("n_res", [1, 3, 4, 17, 33, 255])
+@pytest.mark.parametrize("dt", ["float16", "bfloat16", "float32"])
+def test_mma_attend_tail_kernel_edges(n_res, dt):
+    """The unquantized tail is attended by a kernel of its own (four token rows in flight per
+    warp, up to 8 CTAs per unit): tail lengths around its unroll and slice boundaries, all three
+    residual dtypes, 8 query heads per KV head."""
+    rng = np.random.default_rng(1000 + n_res)
+    (qt, kc, ks, kz, vc, vs, vz, k_res, v_res), ref = _packed_case(rng, 2, 16, 2, 96, n_res, 4, dt)
+    out = _k().kivi_decode_attend(qt, kc, ks, kz, vc, vs, vz, 32, 1.0 / math.sqrt(128), store_bits=4,
+                                  k_res=k_res, v_res=v_res, variant=2)
+    _assert_attn_close(out.float().cpu().numpy(), ref)
+    from veloxquant_mlx_b200 import _lib
+    _lib.check(_lib.lib().vq_kivi_attend_status(), "status")
+
+
 @pytest.mark.parametrize("b", [2, 4])
 @pytest.mark.parametrize("dt", ["float16", "bfloat16"])
 def test_mma_attend_config1_with_outlier_channels(b, dt):
