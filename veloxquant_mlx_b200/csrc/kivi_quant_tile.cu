@@ -174,37 +174,80 @@ kivi_quant_tile_kernel(const T *__restrict__ x, int64_t x_stride_bh, int64_t n_t
             if (odd) packed = codes8_exact<SB>(v, mn, sc, levels);
             store_packed<SB>(cb + (int64_t)(2 * i + hf) * RB, cl, packed);
         }
-    } else {
+    }
+}
+
+// Values (one scale per token row and 32-channel group): a lane owns whole groups, so the
+// extrema need no exchange between lanes and the scale arithmetic is done once per 32
+// elements. Lane l takes group l % 4 of rows l / 4 + 8 i (i = 0..3) of the warp's 32-row tile:
+// 64 contiguous input bytes, RB / 4 contiguous code bytes, one scale and one zero each.
+template <typename T, int SB>
+__global__ void __launch_bounds__(128, 4)
+kivi_quant_tile_values_kernel(const T *__restrict__ x, int64_t x_stride_bh, int64_t n_tok, int64_t tiles_per_bh,
+                              int64_t n_tiles, float levels, float eps, uint8_t *__restrict__ codes,
+                              int64_t codes_stride_bh, float *__restrict__ scale, float *__restrict__ zero,
+                              int64_t param_stride_bh) {
+    constexpr int D = 128, RB = D * SB / 8;
+    const int lane = threadIdx.x & 31;
+    const int64_t tile_id = (int64_t)blockIdx.x * 4 + (threadIdx.x >> 5);
+    if (tile_id >= n_tiles) return;
+    const int64_t bh = tile_id / tiles_per_bh, tile = tile_id % tiles_per_bh;
+    const int64_t tok0 = tile * 32;
+    const int gq = lane & 3, r0 = lane >> 2;
+    const float rlev = __frcp_rn(levels);
+    const T *xb = x + bh * x_stride_bh + tok0 * D + 32 * gq;
+    uint8_t *cb = codes + bh * codes_stride_bh + tok0 * RB + gq * (RB / 4);
+
+    uint4 raw[4][4];
 #pragma unroll
-        for (int i = 0; i < 16; ++i) {
-            const int row = 2 * i + hf;
-            const uint32_t w[4] = {raw[i].x, raw[i].y, raw[i].z, raw[i].w};
-            // extrema of the row's 32-channel group: 8 channels here, then the 3 neighbouring lanes
-            uint32_t pn = pmin<T>(pmin<T>(w[0], w[1]), pmin<T>(w[2], w[3]));
-            uint32_t px = pmax<T>(pmax<T>(w[0], w[1]), pmax<T>(w[2], w[3]));
-            pn = pmin<T>(pn, __shfl_xor_sync(0xffffffffu, pn, 1));
-            px = pmax<T>(px, __shfl_xor_sync(0xffffffffu, px, 1));
-            pn = pmin<T>(pn, __shfl_xor_sync(0xffffffffu, pn, 2));
-            px = pmax<T>(px, __shfl_xor_sync(0xffffffffu, px, 2));
-            const float2 fn = Pk<T>::widen(pn), fx = Pk<T>::widen(px);
-            const float mn1 = fminf(fn.x, fn.y), mx1 = fmaxf(fx.x, fx.y);
-            const float sc1 = fmaxf(div_by(__fsub_rn(mx1, mn1), levels, rlev), eps);
-            const float rc1 = __frcp_rn(sc1);
-            if (tok0 + row < n_tok) {
-                if ((cl & 3) == 0) {
-                    const int64_t pidx = bh * param_stride_bh + (tok0 + row) * 4 + (cl >> 2);
-                    scale[pidx] = sc1;
-                    zero[pidx] = mn1;
-                }
-                float v[8], mn[8], sc[8], rc[8];
+    for (int i = 0; i < 4; ++i) {
+        const int row = r0 + 8 * i;
+        const bool live = tok0 + row < n_tok;
 #pragma unroll
-                for (int k = 0; k < 4; ++k) { const float2 f = Pk<T>::widen(w[k]); v[2 * k] = f.x; v[2 * k + 1] = f.y; }
+        for (int k = 0; k < 4; ++k)
+            raw[i][k] = live ? __ldg(reinterpret_cast<const uint4 *>(xb + (int64_t)row * D) + k) : make_uint4(0, 0, 0, 0);
+    }
 #pragma unroll
-                for (int j = 0; j < 8; ++j) { mn[j] = mn1; sc[j] = sc1; rc[j] = rc1; }
+    for (int i = 0; i < 4; ++i) {
+        const int row = r0 + 8 * i;
+        uint32_t pn = raw[i][0].x, px = raw[i][0].x;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const uint32_t w[4] = {raw[i][k].x, raw[i][k].y, raw[i][k].z, raw[i][k].w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) { pn = pmin<T>(pn, w[e]); px = pmax<T>(px, w[e]); }
+        }
+        const float2 fn = Pk<T>::widen(pn), fx = Pk<T>::widen(px);
+        const float mn1 = fminf(fn.x, fn.y), mx1 = fmaxf(fx.x, fx.y);
+        const float sc1 = fmaxf(div_by(__fsub_rn(mx1, mn1), levels, rlev), eps);
+        const float rc1 = __frcp_rn(sc1);
+        if (tok0 + row < n_tok) {
+            const int64_t pidx = bh * param_stride_bh + (tok0 + row) * 4 + gq;
+            scale[pidx] = sc1;
+            zero[pidx] = mn1;
+            float mn[8], sc[8], rc[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) { mn[j] = mn1; sc[j] = sc1; rc[j] = rc1; }
+            uint64_t packed[4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const uint32_t w[4] = {raw[i][k].x, raw[i][k].y, raw[i][k].z, raw[i][k].w};
+                float v[8];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) { const float2 f = Pk<T>::widen(w[e]); v[2 * e] = f.x; v[2 * e + 1] = f.y; }
                 bool odd;
-                uint64_t packed = codes8_fast<SB>(v, mn, sc, rc, levels, odd);
-                if (odd) packed = codes8_exact<SB>(v, mn, sc, levels);
-                store_packed<SB>(cb + (int64_t)row * RB, cl, packed);
+                packed[k] = codes8_fast<SB>(v, mn, sc, rc, levels, odd);
+                if (odd) packed[k] = codes8_exact<SB>(v, mn, sc, levels);
+            }
+            uint8_t *dst = cb + (int64_t)row * RB;
+            if constexpr (SB == 4) {
+                *reinterpret_cast<uint4 *>(dst) = make_uint4((uint32_t)packed[0], (uint32_t)packed[1], (uint32_t)packed[2], (uint32_t)packed[3]);
+            } else if constexpr (SB == 2) {
+                *reinterpret_cast<uint2 *>(dst) = make_uint2((uint32_t)packed[0] | ((uint32_t)packed[1] << 16),
+                                                             (uint32_t)packed[2] | ((uint32_t)packed[3] << 16));
+            } else {
+                reinterpret_cast<uint4 *>(dst)[0] = make_uint4((uint32_t)packed[0], (uint32_t)(packed[0] >> 32), (uint32_t)packed[1], (uint32_t)(packed[1] >> 32));
+                reinterpret_cast<uint4 *>(dst)[1] = make_uint4((uint32_t)packed[2], (uint32_t)(packed[2] >> 32), (uint32_t)packed[3], (uint32_t)(packed[3] >> 32));
             }
         }
     }
@@ -221,7 +264,7 @@ int32_t launch_tile(const vq_kivi_quant_args &a, cudaStream_t st) {
             (const T *)a.x, a.x_stride_bh, a.n_tok, tiles_per_bh, n_tiles, (float)a.levels, a.eps, a.codes,
             a.codes_stride_bh, a.scale, a.zero, a.param_stride_bh);
     else
-        kivi_quant_tile_kernel<T, SB, 1><<<(unsigned)blocks, 128, 0, st>>>(
+        kivi_quant_tile_values_kernel<T, SB><<<(unsigned)blocks, 128, 0, st>>>(
             (const T *)a.x, a.x_stride_bh, a.n_tok, tiles_per_bh, n_tiles, (float)a.levels, a.eps, a.codes,
             a.codes_stride_bh, a.scale, a.zero, a.param_stride_bh);
     VQ_CHECK_LAUNCH("kivi_quant_tile_kernel");
@@ -247,7 +290,7 @@ bool kivi_quant_tile_supported(const vq_kivi_quant_args &a) {
     if (a.axis == 0 && a.n_tok % 32) return false;
     if (!is_aligned(a.x, 16) || a.x_stride_bh % 8) return false;
     const int rb = 128 * a.store_bits / 8;
-    if (!is_aligned(a.codes, 8) || a.codes_stride_bh % 8 || rb % 8) return false;
+    if (!is_aligned(a.codes, 16) || a.codes_stride_bh % 16 || rb % 8) return false;
     if (!is_aligned(a.scale, 16) || !is_aligned(a.zero, 16) || a.param_stride_bh % 4) return false;
     return true;
 }
