@@ -155,6 +155,7 @@ __global__ void __launch_bounds__(kWarpsC * 32, (NH <= 4 && DPL <= 4 && VM != VM
 coded_attend_kernel(const CodedParams p, int key_floats, int vlut_floats) {
     extern __shared__ __align__(16) float smem[];
     const int lane = threadIdx.x & 31, warp = __shfl_sync(0xffffffffu, threadIdx.x >> 5, 0);  // (known warp-uniform)
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");  // the merge kernel may become resident
     const int split = blockIdx.x;
     int y = blockIdx.y;
     const int hc = y % p.n_head_chunks; y /= p.n_head_chunks;
@@ -452,6 +453,7 @@ rabitq_attend_staged_kernel(const CodedParams p) {
     extern __shared__ __align__(128) uint8_t st_raw[];
     constexpr int D = 128, DPL = 4;
     const int lane = threadIdx.x & 31, warp = __shfl_sync(0xffffffffu, threadIdx.x >> 5, 0);  // (known warp-uniform)
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");  // the merge kernel may become resident
     const int split = blockIdx.x;
     int y = blockIdx.y;
     const int hc = y % p.n_head_chunks; y /= p.n_head_chunks;

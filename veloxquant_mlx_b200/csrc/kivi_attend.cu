@@ -23,6 +23,7 @@ kivi_attend_general_kernel(const vq_kivi_attend_args a, int n_splits, int n_head
     __shared__ float sh_m[kGenWarps][kGenHeads];
     __shared__ float sh_l[kGenWarps][kGenHeads];
 
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");  // the merge kernel may become resident
     const int split = blockIdx.x;
     const int hpk = a.H_q / a.H_kv;
     int y = blockIdx.y;
@@ -152,28 +153,48 @@ kivi_attend_merge_kernel(const float *__restrict__ part_o, const float *__restri
     const int64_t row = blockIdx.x;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const float *ml = part_ml + row * n_splits * 2;
-    float m = -INFINITY;
-    for (int s = tid; s < n_splits; s += 128) m = fmaxf(m, ml[2 * s]);
-    m = warp_max(m);
+    const float *po = part_o + row * n_splits * D;
+    // the partials are complete and visible only after the grid that wrote them has finished
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    // One round trip to memory: the (max, sum) pairs of this thread's splits (at most two) and
+    // the first 8 partial rows of its first output column are requested together.
+    float2 mls[2];
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        const int s = tid + 128 * i;
+        mls[i] = s < n_splits ? make_float2(ml[2 * s], ml[2 * s + 1]) : make_float2(-INFINITY, 0.f);
+    }
+    float first[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) first[u] = (u < n_splits && tid < D) ? po[(int64_t)u * D + tid] : 0.f;
+    float m = warp_max(fmaxf(mls[0].x, mls[1].x));
     if (lane == 0) sh_red[warp] = m;
     __syncthreads();
     const float gm = fmaxf(fmaxf(sh_red[0], sh_red[1]), fmaxf(sh_red[2], sh_red[3]));
     __syncthreads();
     float l = 0.f;
-    for (int s = tid; s < n_splits; s += 128) {
-        const float ms = ml[2 * s];
-        const float w = (ms == -INFINITY) ? 0.f : __expf(ms - gm);
-        sh_w[s] = w;
-        l += ml[2 * s + 1] * w;
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        const int s = tid + 128 * i;
+        if (s < n_splits) {
+            const float w = (mls[i].x == -INFINITY) ? 0.f : __expf(mls[i].x - gm);
+            sh_w[s] = w;
+            l += mls[i].y * w;
+        }
     }
     l = warp_sum(l);
     if (lane == 0) sh_red[warp] = l;
     __syncthreads();
     const float gl = (sh_red[0] + sh_red[1]) + (sh_red[2] + sh_red[3]);
-    const float *po = part_o + row * n_splits * D;
     for (int d = tid; d < D; d += 128) {
         float acc = 0.f;
         int s = 0;
+        if (d == tid) {  // the rows requested up front
+#pragma unroll
+            for (int u = 0; u < 8; ++u)
+                if (u < n_splits) acc = fmaf(first[u], sh_w[u], acc);
+            s = min(8, n_splits);
+        }
         for (; s + 8 <= n_splits; s += 8) {
             float v[8];
 #pragma unroll
@@ -190,8 +211,19 @@ int32_t launch_split_merge(const float *part_o, const float *part_ml, int n_spli
                            int out_dtype, int64_t rows, cudaStream_t st) {
     VQ_REQUIRE(rows < (1ll << 31), VQ_ERR_SHAPE, "split merge: too many output rows");
     VQ_REQUIRE(n_splits <= 256, VQ_ERR_SHAPE, "split merge: at most 256 splits, got %d", n_splits);
-    kivi_attend_merge_kernel<<<(unsigned)rows, 128, 0, st>>>(part_o, part_ml, n_splits, D, out, out_dtype);
-    VQ_CHECK_LAUNCH("kivi_attend_merge_kernel");
+    // Launched as a programmatic dependent of whatever precedes it in the stream (the kernel that
+    // writes the partials): its CTAs may become resident while that grid drains; the kernel's
+    // first instruction waits for the grid's completion.
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)rows);
+    cfg.blockDim = dim3(128);
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    VQ_CHECK_CUDA(cudaLaunchKernelEx(&cfg, kivi_attend_merge_kernel, part_o, part_ml, n_splits, D, out, out_dtype));
     return VQ_OK;
 }
 
