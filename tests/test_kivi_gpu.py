@@ -358,6 +358,44 @@ def test_mma_attend_tail_kernel_edges(n_res, dt):
     _lib.check(_lib.lib().vq_kivi_attend_status(), "status")
 
 
+def test_mma_attend_replayed_from_a_cuda_graph():
+    """The call issues three kernels chained by programmatic dependent launch (main -> tail ->
+    merge). Captured into a CUDA graph and replayed several times back to back (so that one
+    replay's main kernel follows the previous replay's merge), the output must be that of the
+    plain call, bit for bit, also after the query changed in place."""
+    rng = np.random.default_rng(77)
+    (qt, kc, ks, kz, vc, vs, vz, k_res, v_res), ref = _packed_case(rng, 2, 8, 2, 2048, 100, 4, "float16")
+    k = _k()
+    out = torch.empty_like(qt)
+    call = lambda: k.kivi_decode_attend(qt, kc, ks, kz, vc, vs, vz, 32, 1.0 / math.sqrt(128), store_bits=4,
+                                        k_res=k_res, v_res=v_res, variant=2, out=out)
+    call()
+    eager = out.clone()
+    _assert_attn_close(eager.float().cpu().numpy(), ref)
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        call()
+    torch.cuda.current_stream().wait_stream(side)
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        call()
+    out.zero_()
+    for _ in range(5):
+        g.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(out, eager)
+    qt.mul_(-0.5)  # same buffers, new contents
+    for _ in range(3):
+        g.replay()
+    torch.cuda.synchronize()
+    replayed = out.clone()
+    call()
+    assert torch.equal(replayed, out)
+    from veloxquant_mlx_b200 import _lib
+    _lib.check(_lib.lib().vq_kivi_attend_status(), "status")
+
+
 @pytest.mark.parametrize("b", [2, 4])
 @pytest.mark.parametrize("dt", ["float16", "bfloat16"])
 def test_mma_attend_config1_with_outlier_channels(b, dt):
