@@ -96,6 +96,17 @@ int32_t vq_kivi_quantize(const vq_kivi_quant_args *args, void *stream);
  * written too when given. */
 int32_t vq_kivi_quantize_pack(const vq_kivi_quant_args *args, void *stream);
 int32_t vq_kivi_quant_dequant(const vq_kivi_quant_args *args, void *stream);
+/* Store the incoming block of a KIVI cache update: n_new rows per slab of keys AND values are
+ * copied behind the rows already held in the unquantized residual buffers, in one launch (the
+ * reference's cache stores the block through its parent class before it quantizes what aged
+ * out: veloxquant_mlx/cache/kivi_cache.py:250). Row r of slab s is read at
+ * k_new + (s*new_stride_bh + r*head_dim) elements and written to
+ * k_res + (s*res_stride_bh + (tok_offset + r)*head_dim) elements; likewise for the values.
+ * dtype: VQ_F16, VQ_BF16 or VQ_F32. Rows must be multiples of 16 bytes, the four pointers
+ * 16-byte aligned and both strides multiples of 16 bytes (VQ_ERR_ALIGN otherwise). */
+int32_t vq_kivi_append(const void *k_new, const void *v_new, int64_t new_stride_bh, void *k_res, void *v_res,
+                       int64_t res_stride_bh, int64_t n_bh, int64_t n_new, int64_t tok_offset, int32_t head_dim,
+                       int32_t dtype, void *stream);
 
 /* Flat dequantization code*scale+zero of one K (axis 0) or V (axis 1) tensor to
  * f16/bf16/f32. Replaces scalar_decode_once (veloxquant_mlx/metal/_scalar_attend.py:650-699,

@@ -102,6 +102,31 @@ def test_decode_tokens_age_out_with_small_groups():
     assert max(sizes) <= (4 + 4) * 128 * 2 * 2 and c.offset == 22
 
 
+@pytest.mark.parametrize("dt", [torch.float16, torch.bfloat16, torch.float32])
+def test_append_kernel_copies_both_tensors_and_declines_odd_layouts(dt):
+    from veloxquant_mlx_b200 import kernels as k
+    g = torch.Generator(device=DEV).manual_seed(5)
+    B, H, cap, D = 3, 2, 40, 128
+    k_res = torch.zeros(B, H, cap, D, device=DEV, dtype=dt)
+    v_res = torch.zeros(B, H, cap, D, device=DEV, dtype=dt)
+    want_k, want_v = k_res.clone(), v_res.clone()
+    pos = 0
+    for S in (1, 5, 1, 16):
+        big = torch.randn(2, B, H, S + 3, D, device=DEV, dtype=torch.float32, generator=g).to(dt)
+        keys, values = big[0, :, :, 1:S + 1], big[1, :, :, 1:S + 1]  # evenly spaced slabs, not contiguous
+        assert k.kivi_append(keys, values, k_res, v_res, pos)
+        want_k[:, :, pos:pos + S], want_v[:, :, pos:pos + S] = keys, values
+        pos += S
+    assert torch.equal(k_res, want_k) and torch.equal(v_res, want_v)
+    # layouts the kernel does not take are declined, nothing is written
+    odd = torch.randn(B, H, 1, D + 8, device=DEV, dtype=torch.float32).to(dt)[..., 4:D + 4]  # rows not 16-byte aligned / strided
+    before = k_res.clone()
+    assert not k.kivi_append(odd, odd, k_res, v_res, pos)
+    assert not k.kivi_append(keys[:, :, :1].transpose(0, 1), values[:, :, :1].transpose(0, 1), k_res.transpose(0, 1), v_res.transpose(0, 1), pos)
+    assert not k.kivi_append(keys, values, k_res, v_res, cap - 1)  # would run past the buffer
+    assert torch.equal(k_res, before)
+
+
 def test_append_of_two_slices_of_one_buffer_equals_separate_tensors():
     """K and V that arrive as two slices of one tensor (a fused projection's output) are appended
     by one copy; the cache contents must not depend on that."""

@@ -360,12 +360,13 @@ class KIVIKVCache:
         n_flush = new_boundary - self._n_quantized
         if n_flush <= 0:
             self._ensure_residual(B, H, D, self._n_res + S, dev, keys.dtype)
-            pair = _paired_view(keys, values)
-            if pair is not None:
-                self._kv_res[:, :, :, self._n_res : self._n_res + S] = pair
-            else:
-                self._k_res[:, :, self._n_res : self._n_res + S] = keys
-                self._v_res[:, :, self._n_res : self._n_res + S] = values
+            if not kernels.kivi_append(keys, values, self._k_res, self._v_res, self._n_res):
+                pair = _paired_view(keys, values)
+                if pair is not None:
+                    self._kv_res[:, :, :, self._n_res : self._n_res + S] = pair
+                else:
+                    self._k_res[:, :, self._n_res : self._n_res + S] = keys
+                    self._v_res[:, :, self._n_res : self._n_res + S] = values
             self._n_res += S
         else:
             # Rows to flush are the oldest unquantized ones: the residual first, then the

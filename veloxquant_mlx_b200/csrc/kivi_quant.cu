@@ -265,6 +265,58 @@ extern "C" int32_t vq_kivi_quantize_pack(const vq_kivi_quant_args *args, void *s
     return vq_kivi_quantize(&a, stream);
 }
 
+namespace vq {
+// One thread per 16-byte chunk of a new row, keys and values alike. Launched as a programmatic
+// dependent of whatever precedes it in the stream (its first instruction waits for that work),
+// and it lets the kernel that follows become resident early in turn: in a decode loop the copy
+// then costs little more than its own run time.
+__global__ void __launch_bounds__(256)
+kivi_append_kernel(const uint4 *__restrict__ k_new, const uint4 *__restrict__ v_new, int64_t new_stride_bh,
+                   uint4 *__restrict__ k_res, uint4 *__restrict__ v_res, int64_t res_stride_bh, int64_t n_bh,
+                   int64_t n_new, int64_t tok_offset, int row_chunks) {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    const int64_t per_slab = n_new * row_chunks;
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n_bh * per_slab) return;
+    const int64_t s = i / per_slab, off = i % per_slab;  // strides are in 16-byte chunks here
+    const int64_t src = s * new_stride_bh + off, dst = s * res_stride_bh + tok_offset * row_chunks + off;
+    const uint4 kv = k_new[src], vv = v_new[src];
+    k_res[dst] = kv;
+    v_res[dst] = vv;
+}
+}  // namespace vq
+
+extern "C" int32_t vq_kivi_append(const void *k_new, const void *v_new, int64_t new_stride_bh, void *k_res, void *v_res,
+                                  int64_t res_stride_bh, int64_t n_bh, int64_t n_new, int64_t tok_offset,
+                                  int32_t head_dim, int32_t dtype, void *stream) {
+    using namespace vq;
+    VQ_REQUIRE(k_new && v_new && k_res && v_res, VQ_ERR_SHAPE, "vq_kivi_append: a buffer is NULL");
+    VQ_REQUIRE(dtype == VQ_F16 || dtype == VQ_BF16 || dtype == VQ_F32, VQ_ERR_DTYPE, "vq_kivi_append: bad dtype %d", dtype);
+    VQ_REQUIRE(n_bh >= 0 && n_new >= 0 && tok_offset >= 0 && head_dim >= 1, VQ_ERR_SHAPE, "vq_kivi_append: negative size");
+    const int64_t es = dtype == VQ_F32 ? 4 : 2;
+    VQ_REQUIRE((head_dim * es) % 16 == 0 && (new_stride_bh * es) % 16 == 0 && (res_stride_bh * es) % 16 == 0 &&
+                   is_aligned(k_new, 16) && is_aligned(v_new, 16) && is_aligned(k_res, 16) && is_aligned(v_res, 16),
+               VQ_ERR_ALIGN, "vq_kivi_append: rows, strides and pointers must be multiples of 16 bytes");
+    const int row_chunks = (int)(head_dim * es / 16);
+    const int64_t total = n_bh * n_new * row_chunks;
+    if (total == 0) return VQ_OK;
+    VQ_REQUIRE(ceil_div(total, 256) < (1ll << 31), VQ_ERR_SHAPE, "vq_kivi_append: block too large for one launch");
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)ceil_div(total, 256));
+    cfg.blockDim = dim3(256);
+    cfg.stream = (cudaStream_t)stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    VQ_CHECK_CUDA(cudaLaunchKernelEx(&cfg, kivi_append_kernel, (const uint4 *)k_new, (const uint4 *)v_new,
+                                     new_stride_bh * es / 16, (uint4 *)k_res, (uint4 *)v_res, res_stride_bh * es / 16, n_bh,
+                                     n_new, tok_offset, row_chunks));
+    return VQ_OK;
+}
+
 extern "C" int32_t vq_kivi_quant_dequant(const vq_kivi_quant_args *args, void *stream) {
     using namespace vq;
     VQ_REQUIRE(args != nullptr, VQ_ERR_SHAPE, "vq_kivi_quant_dequant: args is NULL");

@@ -68,6 +68,42 @@ def _slab_view(x: torch.Tensor, name: str):
 # KIVI quantization
 # ----------------------------------------------------------------------------------------
 
+def kivi_append(keys: torch.Tensor, values: torch.Tensor, k_res: torch.Tensor, v_res: torch.Tensor,
+                tok_offset: int) -> bool:
+    """Copy the block ``keys/values [B,H,S,D]`` behind row ``tok_offset`` of the residual buffers
+    ``k_res/v_res [B,H,cap,D]``, both in one launch (the store of the incoming block in the
+    reference's ``KIVIKVCache.update_and_fetch``, ``cache/kivi_cache.py:250``). Returns ``False``
+    without doing anything when the layout is not one the kernel takes (rows, strides and
+    pointers must be multiples of 16 bytes, slabs evenly spaced); the caller then copies with
+    torch."""
+    B, H, S, D = keys.shape
+    es = keys.element_size()
+    if keys.dtype not in _FLOAT_DTYPES or not (keys.dtype == values.dtype == k_res.dtype == v_res.dtype):
+        return False
+    if not (keys.is_cuda and values.is_cuda and k_res.is_cuda and v_res.is_cuda) or S == 0:
+        return False
+    if tok_offset + S > k_res.shape[2] or k_res.shape != v_res.shape or values.shape != keys.shape:
+        return False
+
+    def slabs(t):  # elements between (batch, head) slabs if they are evenly spaced, else None
+        if t.stride(3) != 1 or t.stride(2) != D:
+            return None
+        if t.shape[0] > 1 and t.stride(0) != t.shape[1] * t.stride(1):
+            return None
+        return t.stride(1) if t.shape[1] > 1 else (t.stride(0) if t.shape[0] > 1 else t.shape[2] * D)
+
+    sn, sv, rk, rv = slabs(keys), slabs(values), slabs(k_res), slabs(v_res)
+    if None in (sn, sv, rk, rv) or sn != sv or rk != rv:
+        return False
+    if (D * es) % 16 or (sn * es) % 16 or (rk * es) % 16:
+        return False
+    if any(t.data_ptr() % 16 for t in (keys, values, k_res, v_res)):
+        return False
+    check(lib().vq_kivi_append(keys.data_ptr(), values.data_ptr(), sn, k_res.data_ptr(), v_res.data_ptr(), rk, B * H, S,
+                               int(tok_offset), D, dtype_code(keys.dtype), stream_ptr(keys.device)), "kivi_append")
+    return True
+
+
 def kivi_group_quant_dequant(x: torch.Tensor, axis: int, group_size: int, levels: int,
                              eps: float = 1e-8) -> torch.Tensor:
     """Round-trip ``x [..., S, D]`` through KIVI asymmetric group quantization.
