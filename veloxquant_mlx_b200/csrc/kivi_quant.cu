@@ -266,16 +266,11 @@ extern "C" int32_t vq_kivi_quantize_pack(const vq_kivi_quant_args *args, void *s
 }
 
 namespace vq {
-// One thread per 16-byte chunk of a new row, keys and values alike. Launched as a programmatic
-// dependent of whatever precedes it in the stream (its first instruction waits for that work),
-// and it lets the kernel that follows become resident early in turn: in a decode loop the copy
-// then costs little more than its own run time.
+// One thread per 16-byte chunk of a new row, keys and values alike.
 __global__ void __launch_bounds__(256)
 kivi_append_kernel(const uint4 *__restrict__ k_new, const uint4 *__restrict__ v_new, int64_t new_stride_bh,
                    uint4 *__restrict__ k_res, uint4 *__restrict__ v_res, int64_t res_stride_bh, int64_t n_bh,
                    int64_t n_new, int64_t tok_offset, int row_chunks) {
-    asm volatile("griddepcontrol.wait;" ::: "memory");
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const int64_t per_slab = n_new * row_chunks;
     const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n_bh * per_slab) return;
@@ -302,18 +297,10 @@ extern "C" int32_t vq_kivi_append(const void *k_new, const void *v_new, int64_t 
     const int64_t total = n_bh * n_new * row_chunks;
     if (total == 0) return VQ_OK;
     VQ_REQUIRE(ceil_div(total, 256) < (1ll << 31), VQ_ERR_SHAPE, "vq_kivi_append: block too large for one launch");
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((unsigned)ceil_div(total, 256));
-    cfg.blockDim = dim3(256);
-    cfg.stream = (cudaStream_t)stream;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
-    VQ_CHECK_CUDA(cudaLaunchKernelEx(&cfg, kivi_append_kernel, (const uint4 *)k_new, (const uint4 *)v_new,
-                                     new_stride_bh * es / 16, (uint4 *)k_res, (uint4 *)v_res, res_stride_bh * es / 16, n_bh,
-                                     n_new, tok_offset, row_chunks));
+    kivi_append_kernel<<<(unsigned)ceil_div(total, 256), 256, 0, (cudaStream_t)stream>>>(
+        (const uint4 *)k_new, (const uint4 *)v_new, new_stride_bh * es / 16, (uint4 *)k_res, (uint4 *)v_res,
+        res_stride_bh * es / 16, n_bh, n_new, tok_offset, row_chunks);
+    VQ_CHECK_LAUNCH("kivi_append_kernel");
     return VQ_OK;
 }
 
