@@ -358,6 +358,32 @@ def test_mma_attend_tail_kernel_edges(n_res, dt):
     _lib.check(_lib.lib().vq_kivi_attend_status(), "status")
 
 
+def test_back_to_back_calls_with_different_inputs_do_not_interfere():
+    """Calls on different caches issued back to back without synchronisation (their scratch
+    buffers are handed from one call to the next by the allocator) must each return what the same
+    call returns in isolation, bit for bit."""
+    k = _k()
+    cases = [_packed_case(np.random.default_rng(300 + i), 2, 8, 2, 1024 + 32 * i, 40 + 9 * i, 4, "float16")[0] for i in range(4)]
+
+    def call(a):
+        qt, kc, ks, kz, vc, vs, vz, k_res, v_res = a
+        return k.kivi_decode_attend(qt, kc, ks, kz, vc, vs, vz, 32, 1.0 / math.sqrt(128), store_bits=4,
+                                    k_res=k_res, v_res=v_res, variant=2)
+
+    alone = []
+    for a in cases:
+        o = call(a)
+        torch.cuda.synchronize()
+        alone.append(o.clone())
+    for _ in range(20):
+        outs = [call(a) for a in cases]
+    torch.cuda.synchronize()
+    for o, r in zip(outs, alone):
+        assert torch.equal(o, r)
+    from veloxquant_mlx_b200 import _lib
+    _lib.check(_lib.lib().vq_kivi_attend_status(), "status")
+
+
 def test_mma_attend_replayed_from_a_cuda_graph():
     """The call issues three kernels chained by programmatic dependent launch (main -> tail ->
     merge). Captured into a CUDA graph and replayed several times back to back (so that one
