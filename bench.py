@@ -5,21 +5,28 @@
 
 Workload (default): the Llama-3.1-8B-shaped decode configuration -- 32 layers, 32 query
 heads, 8 KV heads, head_dim 128, KIVI 4-bit keys (per channel) and values (per token),
-group 32, a 128-token bf16 residual window, batch 16 per GPU, context 32768, bf16
-activations, K/V ~ N(0,1) with 4 outlier channels per head scaled x20. A "step" is one
-decode step of the attention path: for each layer, fused dequant + attention of one new
-query token over that layer's packed cache (no model weights are involved).
+group 32, a 128-token bf16 residual window, batch 16, context 32768, bf16 activations,
+K/V ~ N(0,1) with 4 outlier channels per head scaled x20. A "step" is one decode step of the
+attention path: for each layer, fused dequant + attention of one new query token over that
+layer's packed cache (no model weights are involved).
 
-Scaling across GPUs is weak: every rank holds its own batch shard of 16 sequences (the
-(batch, kv head) units are independent, so attention needs no collective); for N > 1 each
-layer's output is all-gathered over NCCL, overlapped with the next layer's attention.
+Scaling across GPUs is STRONG: the one batch of 16 sequences is partitioned over the ranks by
+(batch, kv head) unit (128 units -> 128/N per GPU; `veloxquant_mlx_b200.sharding`). Attention
+needs no collective; each layer's output rows are delivered to every rank by the attention
+kernel's merge step itself (stores to peer-mapped buffers + an arrival flag with a bounded
+wait), or with `--gather nccl` by an NCCL all-gather on a side stream. The per-step kernel
+sequence is captured once into a CUDA graph and replayed.
 
-One JSON line is printed by rank 0. `value` is KV GB/s: algorithmic bytes of packed
-codes, scales, zero-points, residual window, queries and outputs that one step must move,
-divided by the step time, summed over ranks. `e2e` is the same metric through the cache
-interface with host buffers (query and new K/V token copied in, output copied out, every
-step). `--impl reference` times the CPU oracle (a NumPy restatement of the reference's
-path; the reference's own MLX code cannot be installed on this box) on a bounded sample.
+One JSON line is printed by rank 0. `value` is KV GB/s: algorithmic bytes of packed codes,
+scales, zero-points, residual window, queries and outputs that one step of the WHOLE batch
+must move, divided by the step time (max over ranks; median over repeated blocks of
+`--steps` steps). `e2e` is the same metric through the cache interface with host buffers
+(query and new K/V token copied in, output copied out, every step; the run crosses
+quantize-on-append flushes). `extra` carries further figures measured in the same run: the
+same shape at 2 bits, quantize-on-append throughput, the Qwen2.5-32B-shaped prefill + decode
+configuration, the weak-scaling (replicated batch) figure, `quantize_vq` and RaBitQ.
+`--impl reference` times the CPU oracle (a NumPy restatement of the reference's path; the
+reference's own MLX code cannot be installed on this box) on a bounded sample.
 """
 
 from __future__ import annotations
@@ -60,17 +67,30 @@ def workload(args):
     return w
 
 
-def algorithmic_bytes_per_layer(w, batch=None):
+def config_of(w, n_gpus):
+    """The `config` object of the JSON line; both arms print the same keys and values."""
+    units = w["batch"] * w["H_kv"]
+    return {"workload": w["name"], **{k: w[k] for k in ("layers", "batch", "ctx", "bits", "group", "residual", "H_q", "H_kv", "D")},
+            "global_batch": w["batch"],
+            "parallelism": f"{units} (batch, kv head) units block-partitioned over {n_gpus} GPU(s)",
+            "l2": "inputs larger than L2: each layer's packed KV is read once per step and the layers are distinct buffers"}
+
+
+def algorithmic_bytes_per_layer(w, batch=None, bits=None, n_quant=None, n_res=None):
     """Bytes one layer's attend must move: packed codes + fp32 params + residual + q + out."""
     B = w["batch"] if batch is None else batch
-    D, g, b, Sq, R = w["D"], w["group"], w["bits"], w["n_quant"], w["n_res"]
+    b = w["bits"] if bits is None else bits
+    D, g = w["D"], w["group"]
+    Sq = w["n_quant"] if n_quant is None else n_quant
+    R = w["n_res"] if n_res is None else n_res
     per_head = (Sq * D * b // 8 + (Sq // g) * D * 8) + (Sq * D * b // 8 + Sq * (D // g) * 8) + 2 * R * D * 2
     return B * (w["H_kv"] * per_head + 2 * w["H_q"] * D * 2)
 
 
 # ----------------------------------------------------------------------------- clocks
 class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    """Samples SM clocks and throttle reasons (NVML in-process, else nvidia-smi) while the timed
+    region runs."""
 
     QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
@@ -83,7 +103,6 @@ class ClockSampler:
         self.nvml = None
 
     def _start_nvml(self):
-        """Preferred: poll NVML in-process (no pipe buffering between us and the samples)."""
         import pynvml
 
         pynvml.nvmlInit()
@@ -136,14 +155,25 @@ class ClockSampler:
         for line in self.proc.stdout:
             self.lines.append(line.strip())
 
+    @staticmethod
+    def _summary(sm, mx, power, reasons, source):
+        out = {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": mx,
+               "power_w_max": max(power) if power else None, "samples": len(sm), "reasons": sorted(reasons),
+               "source": source}
+        if sm:
+            # samples binned by SM clock (100 MHz bins): how long the run spent at which clock
+            bins = {}
+            for v in sm:
+                key = int(v // 100) * 100
+                bins[key] = bins.get(key, 0) + 1
+            out["sm_mhz_bins"] = {f"{k}-{k + 99}": n for k, n in sorted(bins.items())}
+        return out
+
     def stop(self):
         if self.nvml is not None:
             self.nvml["stop"] = True
             self.thread.join(timeout=2)
-            sm = self.nvml["sm"]
-            return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": float(self.nvml["max"]),
-                    "power_w_max": max(self.nvml["power"]) if self.nvml["power"] else None,
-                    "samples": len(sm), "reasons": sorted(self.nvml["reasons"]), "source": "nvml"}
+            return self._summary(self.nvml["sm"], float(self.nvml["max"]), self.nvml["power"], self.nvml["reasons"], "nvml")
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
         self.proc.terminate()
@@ -164,17 +194,23 @@ class ClockSampler:
             for nm, val in zip(names, f[5:9]):
                 if val.lower().startswith("active"):
                     reasons.add(nm)
-        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "power_w_max": max(power) if power else None, "samples": len(sm), "reasons": sorted(reasons)}
+        return self._summary(sm, max(mx) if mx else None, power, reasons, "nvidia-smi")
 
 
 def ncu_traffic(w):
-    """dram__bytes_read.sum + dram__bytes_write.sum of one launch of the attend kernel, from
-    the ncu capture summarised in profiles/kivi_attend_mma_llama8b_decode.md (same per-layer
-    shape as the default workload); None for shapes that were not captured."""
-    if (w["batch"], w["ctx"], w["H_kv"], w["H_q"], w["D"], w["group"], w["residual"]) != (16, 32768, 8, 32, 128, 32, 128):
+    """dram__bytes_read.sum + dram__bytes_write.sum of one launch of the attend kernel, read from
+    the data file kept beside the ncu summary of that capture (same per-layer shape as the
+    default workload); None for shapes that were not captured."""
+    path = os.path.join(ROOT, "profiles", "kivi_attend_mma_llama8b_decode.traffic.json")
+    try:
+        rec = json.load(open(path))
+    except (OSError, ValueError):
         return None
-    return {4: 802_324_992 + 5_432_832, 2: 535_003_904 + 5_901_312}.get(w["bits"])
+    shape = [w["batch"], w["ctx"], w["H_kv"], w["H_q"], w["D"], w["group"], w["residual"]]
+    if rec.get("shape") != shape:
+        return None
+    per_bits = rec.get("dram_bytes_per_launch", {}).get(str(w["bits"]))
+    return None if per_bits is None else int(per_bits["read"]) + int(per_bits["write"])
 
 
 def measured_peak():
@@ -187,11 +223,19 @@ def measured_peak():
     return 6650.0, "fallback"
 
 
+def measured_tensor_peak():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        return float(json.load(open(p))["bf16_tflops"]), "measured (burst)"
+    except Exception:
+        return 1590.0, "fallback"
+
+
 # ----------------------------------------------------------------------------- CPU oracle arm
 def cpu_reference_sample(w, seconds_budget=20.0, seed=0):
     """Time the oracle (NumPy restatement of the reference's KIVI quantize + attend) on a
-    bounded sample of the workload: one layer, as many sequences of the batch as fit the
-    budget. Returns (GB/s by the same algorithmic-bytes formula, sample description, cores)."""
+    bounded sample of the workload: one layer, one sequence of the batch. Returns (GB/s by the
+    same algorithmic-bytes formula, sample description, cores, seconds per run)."""
     from oracle import kivi as ok
 
     rng = np.random.default_rng(seed)
@@ -238,8 +282,8 @@ def run_reference(args):
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": 1e3 * t_all / max(args.steps, 1), "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": w["dtype"], "data": "synthetic",
-        "config": {"workload": w["name"], **{k: w[k] for k in ("layers", "batch", "ctx", "bits", "group", "residual", "H_q", "H_kv", "D")}},
+        "scaling": "strong", "vs_baseline": None, "dtype": w["dtype"], "data": "synthetic",
+        "config": config_of(w, args.gpus),
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
@@ -247,27 +291,87 @@ def run_reference(args):
 
 
 # ----------------------------------------------------------------------------- our arm
-def build_cache(torch, w, device, seed, dtype):
-    """One layer's cache, filled by a prefill append of seeded synthetic K/V: quantize-on-write
-    through the public cache interface (packed codes + fp32 params + residual window)."""
-    from veloxquant_mlx_b200.cache import KVCacheConfig, KVCacheFactory
-
-    B, H_kv, D = w["batch"], w["H_kv"], w["D"]
+def synth_kv(torch, shape, device, seed, dtype):
+    """Seeded synthetic K and V: N(0,1) with 4 outlier channels scaled x20."""
     gen = torch.Generator(device=device)
     gen.manual_seed(seed)
-    ch = torch.randperm(D, generator=gen, device=device)[:4]
+    ch = torch.randperm(shape[-1], generator=gen, device=device)[:4]
     kv = []
     for _ in range(2):
-        x = torch.randn((B, H_kv, w["ctx"], D), generator=gen, device=device, dtype=torch.float32)
+        x = torch.randn(shape, generator=gen, device=device, dtype=torch.float32)
         x[..., ch] *= 20.0
         kv.append(x.to(dtype))
         del x
-    cache = KVCacheFactory.create(KVCacheConfig(
-        method="kivi", head_dim=D, bit_width_inlier=w["bits"], kivi_group_size=w["group"],
-        residual_length=w["residual"], fused_sdpa_memory_bound=True))
-    cache.update_and_fetch(kv[0], kv[1])
+    return kv
+
+
+def new_cache(w, bits=None):
+    from veloxquant_mlx_b200.cache import KVCacheConfig, KVCacheFactory
+
+    return KVCacheFactory.create(KVCacheConfig(
+        method="kivi", head_dim=w["D"], bit_width_inlier=w["bits"] if bits is None else bits,
+        kivi_group_size=w["group"], residual_length=w["residual"], fused_sdpa_memory_bound=True))
+
+
+def build_cache(torch, w, shape_bh, device, seed, dtype, bits=None):
+    """One layer's cache, filled by a prefill append of seeded synthetic K/V: quantize-on-write
+    through the public cache interface (packed codes + fp32 params + residual window)."""
+    k, v = synth_kv(torch, (*shape_bh, w["ctx"], w["D"]), device, seed, dtype)
+    cache = new_cache(w, bits)
+    cache.update_and_fetch(k, v)
     assert cache._n_quantized == w["n_quant"] and cache.offset == w["ctx"]
     return cache
+
+
+class Timer:
+    """Blocks of `steps` steps, each bracketed by barrier + synchronize and CUDA events on the
+    launching stream; per block the max over ranks; the result is the list of ms per step."""
+
+    def __init__(self, torch, dist, world, device):
+        self.torch, self.dist, self.world, self.device = torch, dist, world, device
+
+    def barrier(self):
+        self.torch.cuda.synchronize()
+        if self.world > 1:
+            self.dist.barrier()
+        self.torch.cuda.synchronize()
+
+    def blocks(self, fn, steps, n_blocks):
+        torch = self.torch
+        out = []
+        for _ in range(n_blocks):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            self.barrier()
+            e0.record()
+            for _ in range(steps):
+                fn()
+            e1.record()
+            self.barrier()
+            t = torch.tensor([e0.elapsed_time(e1)], device=self.device, dtype=torch.float64)
+            if self.world > 1:
+                self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX)
+            out.append(float(t.item()) / steps)
+        return out
+
+
+def stats(ms_list):
+    return {"median": float(np.median(ms_list)), "min": float(np.min(ms_list)), "max": float(np.max(ms_list)),
+            "blocks": len(ms_list)}
+
+
+def capture(torch, fn):
+    """fn captured into a CUDA graph (after a warm-up on a side stream); returns the replay."""
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        fn()
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        fn()
+    torch.cuda.synchronize()
+    return g
 
 
 def run_ours(args):
@@ -283,63 +387,203 @@ def run_ours(args):
     device = torch.device("cuda", local_rank)
     if world > 1:
         dist.init_process_group("nccl", device_id=device)
+    from veloxquant_mlx_b200 import kernels as vk
+    from veloxquant_mlx_b200 import sharding
+
     w = workload(args)
     dtype = torch.bfloat16 if w["dtype"] == "bf16" else torch.float16
     L, B, H_q, H_kv, D = w["layers"], w["batch"], w["H_q"], w["H_kv"], w["D"]
+    hpk = H_q // H_kv
     scale = 1.0 / math.sqrt(D)
+    timer = Timer(torch, dist, world, device)
+    notes = []
 
-    caches = [build_cache(torch, w, device, 1000 * rank + l, dtype) for l in range(L)]
+    # ---- the partition: this rank's (batch, kv head) units ----------------------------------
+    plan = sharding.plan_shards(B, H_kv, world, rank)
+    if world == 1:
+        shape_bh, q_shape = (B, H_kv), (B, H_q, 1, D)
+    else:
+        shape_bh, q_shape = (plan.size, 1), (plan.size, hpk, 1, D)
+    frac_local = plan.size / plan.units  # share of the whole problem this rank attends
+
+    gather_mode = "none" if world == 1 else args.gather
+    px = None
+    if gather_mode == "peer":
+        try:
+            px = sharding.PeerExchange(plan, L, hpk, D, dtype, device)
+            ok = torch.tensor([1], device=device)
+        except Exception as e:  # the benchmark still has to produce its line
+            notes.append(f"peer exchange unavailable on rank {rank}: {e}")
+            ok = torch.tensor([0], device=device)
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+        if int(ok.item()) == 0:
+            px = None
+            gather_mode = "nccl"
+            notes.append("fell back to the NCCL all-gather")
+
+    caches = [build_cache(torch, w, shape_bh, device, 1000 * l + rank, dtype) for l in range(L)]
     gen = torch.Generator(device=device)
     gen.manual_seed(7 + rank)
-    qs = [torch.randn((B, H_q, 1, D), generator=gen, device=device, dtype=torch.float32).to(dtype) for _ in range(L)]
-    outs = [torch.empty((B, H_q, 1, D), device=device, dtype=dtype) for _ in range(L)]
-    gathered = [torch.empty((world * B, H_q, 1, D), device=device, dtype=dtype) for _ in range(L)] if world > 1 else None
-    comm_stream = torch.cuda.Stream(device) if world > 1 else None
+    qs = [torch.randn(q_shape, generator=gen, device=device, dtype=torch.float32).to(dtype) for _ in range(L)]
+    outs = [torch.empty(q_shape, device=device, dtype=dtype) for _ in range(L)]
+    comm_stream = torch.cuda.Stream(device) if gather_mode == "nccl" else None
+    gathered = [torch.empty((B, H_q, 1, D), device=device, dtype=dtype) for _ in range(L)] if gather_mode == "nccl" else None
     torch.cuda.synchronize()
 
-    def gather(l):
+    def nccl_gather(l):
         ev = torch.cuda.Event()
         ev.record()
         with torch.cuda.stream(comm_stream):
             comm_stream.wait_event(ev)
-            dist.all_gather_into_tensor(gathered[l], outs[l])
+            sharding.gather_layer_output(outs[l], plan, out=gathered[l])
 
-    def step():
-        for l in range(L):
-            caches[l].fused_sdpa(qs[l], scale, out=outs[l])
-            if world > 1:
-                gather(l)
-        if world > 1:
-            torch.cuda.current_stream().wait_stream(comm_stream)
+    def make_step(with_gather=True):
+        def step():
+            for l in range(L):
+                g = px.layer(l) if (px is not None and with_gather) else None
+                # (the queries and caches of this loop are static: nothing the kernel reads is
+                # written by the work right before it, which is what overlap_previous requires)
+                caches[l].fused_sdpa(qs[l], scale, out=outs[l], overlap_previous=True, gather=g)
+                if g is not None:
+                    px.wait(l)
+                elif gather_mode == "nccl" and with_gather:
+                    nccl_gather(l)
+            if gather_mode == "nccl" and with_gather:
+                torch.cuda.current_stream().wait_stream(comm_stream)
+        return step
 
-    # End-to-end step through the cache interface with HOST buffers: per layer the query and
-    # the new token's K/V come from pinned host memory, the token is appended (quantized when
-    # a group ages out of the residual window), attention runs over the packed cache, and the
-    # layer's output goes back to pinned host memory.
-    host = {
-        "q": [torch.randn((B, H_q, 1, D), dtype=torch.float32).to(dtype) for _ in range(L)],
-        "k": [torch.randn((B, H_kv, 1, D), dtype=torch.float32).to(dtype) for _ in range(L)],
-        "v": [torch.randn((B, H_kv, 1, D), dtype=torch.float32).to(dtype) for _ in range(L)],
-        "o": [torch.empty((B, H_q, 1, D), dtype=dtype).pin_memory() for _ in range(L)],
-    }
-    # The copies run on their own streams so that later layers' inputs travel while layer l is
-    # attended: per layer ONE pinned staging buffer (query, key, value back to back: one copy per
-    # layer) with its device twin and an event; uploads are issued two layers ahead of the
-    # compute launches (issuing all of them first would leave the GPU idle while the host
-    # enqueues 32 layers of copies); the compute stream waits for the event of the layer it is
-    # about to run, the download stream for the layer's attention.
-    n_q, n_kv = B * H_q * D, B * H_kv * D
+    step = make_step()
+    for _ in range(max(args.warmup, 3)):
+        step()
+    timer.barrier()
+    vk.attend_status()
+    run = step
+    graphed = False
+    if gather_mode != "nccl" and not args.no_graph:
+        try:
+            run = capture(torch, step).replay
+            graphed = True
+        except Exception as e:
+            notes.append(f"graph capture failed, timing eager launches: {e}")
+            run = step
+    for _ in range(max(args.warmup, 3)):
+        run()
+    timer.barrier()
+
+    # timed region: >= 1 s of GPU work in blocks of `steps` steps (at least 5 blocks, at most 40)
+    probe = timer.blocks(run, args.steps, 1)[0]
+    n_blocks = int(min(40, max(5, math.ceil(1000.0 / max(probe * args.steps, 1e-3)))))
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    ms_blocks = timer.blocks(run, args.steps, n_blocks)
+    clocks = sampler.stop() if rank == 0 else None
+    ms_step = float(np.median(ms_blocks))
+    vk.attend_status()
+
+    # the collective's share: the same step without publishing / gathering the outputs
+    gather_info = None
+    if world > 1:
+        bare = make_step(with_gather=False)
+        bare_run = bare
+        if graphed:
+            try:
+                bare_run = capture(torch, bare).replay
+            except Exception:
+                bare_run = bare
+        for _ in range(3):
+            bare_run()
+        ms_bare = float(np.median(timer.blocks(bare_run, args.steps, max(5, n_blocks // 2))))
+        gather_info = {"mode": gather_mode, "ms_per_step_without_gather": ms_bare,
+                       "share_of_step": max(0.0, 1.0 - ms_bare / ms_step),
+                       "bytes_per_rank_per_layer": plan.size * hpk * D * outs[0].element_size()}
+        if px is not None:
+            # the gathered tensors must hold every rank's rows: compare with an NCCL all-gather
+            worst = 0.0
+            for l in (0, L - 1):
+                ref = sharding.gather_layer_output(outs[l], plan)
+                worst = max(worst, float((px.output(l).float() - ref.float()).abs().max().item()))
+            gather_info["max_abs_diff_vs_nccl_allgather"] = worst
+
+    # ---- extras measured in the same run -----------------------------------------------------
+    extra = {}
+    peak, peak_kind = measured_peak()
+    if not args.no_extras:
+        extra = run_extras(torch, dist, timer, w, plan, world, rank, device, dtype, px, args, peak)
+
+    # ---- end-to-end arm (after the kernel arm, so the cache contents above stay fixed)
+    e2e = None
+    if not args.no_e2e:
+        e2e = run_e2e(torch, dist, timer, w, plan, world, device, dtype, caches, outs, px, gather_mode, nccl_gather,
+                      comm_stream, q_shape, shape_bh, args)
+    vk.attend_status()
+
+    if rank == 0:
+        bytes_layer = algorithmic_bytes_per_layer(w)
+        bytes_step = bytes_layer * L
+        value = bytes_step / (ms_step * 1e-3) / 1e9
+        per_launch_s = ms_step * 1e-3 / L
+        achieved = frac_local * bytes_layer / per_launch_s / 1e9
+        cpu = None
+        if world == 1 and not args.no_cpu_baseline:
+            gbs, sample, cores, _ = cpu_reference_sample(w, seconds_budget=15.0)
+            cpu = {"value": gbs, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample}
+        if clocks and clocks.get("sm_mhz"):
+            clocks["ms_per_step_x_sm_mhz"] = ms_step * clocks["sm_mhz"]
+        launches_per_layer = 3 + (1 if px is not None else 0)
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": w["dtype"], "data": "synthetic",
+            "config": config_of(w, world),
+            "ms_per_step_blocks": stats(ms_blocks),
+            "tokens_per_s": B / (ms_step * 1e-3),
+            "pct_of_hbm_peak": 100.0 * (value / world) / peak,
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                         "peak_kind": peak_kind + " (burst copy)", "traffic": ncu_traffic(w) if world == 1 else None,
+                         "kernel": f"kivi_attend_mma_kernel<{w['bits']}> (+ tail kernel under its drain, + merge; duration = step time / layers)",
+                         "algorithmic_bytes_per_launch": int(frac_local * bytes_layer)},
+            "cpu_baseline": cpu,
+            "e2e": e2e,
+            "gather": gather_info,
+            "extra": extra,
+            "launch": {"cuda_graph": graphed, "overlap_previous": True},
+            "gpu_launches": launches_per_layer * L * args.steps,  # main, tail, merge (+ arrival wait) per layer
+            "clocks": clocks,
+            "notes": notes,
+        }
+        print(json.dumps(line), flush=True)
+    if px is not None:
+        px.close()
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def run_e2e(torch, dist, timer, w, plan, world, device, dtype, caches, outs, px, gather_mode, nccl_gather, comm_stream,
+            q_shape, shape_bh, args):
+    """End-to-end step through the cache interface with HOST buffers: per layer the query and the
+    new token's K/V come from pinned host memory, the token is appended (and, every `group`
+    steps, the group that aged out of the residual window is quantized into the packed store),
+    attention runs over the packed cache, and the layer's output goes back to pinned host memory.
+    The copies run on their own streams: per layer ONE pinned staging buffer (query, key, value
+    back to back) with its device twin and an event; uploads are issued two layers ahead of the
+    compute launches; the compute stream waits for the event of the layer it is about to run,
+    the download stream for the layer's attention."""
+    L, D = w["layers"], w["D"]
+    scale = 1.0 / math.sqrt(D)
+    kv_shape = (*shape_bh, 1, D)
+    n_q = int(np.prod(q_shape))
+    n_kv = int(np.prod(kv_shape))
+    host_o = [torch.empty(q_shape, dtype=dtype).pin_memory() for _ in range(L)]
     host_in = [torch.empty(n_q + 2 * n_kv, dtype=dtype).pin_memory() for _ in range(L)]
     dev_in = [torch.empty(n_q + 2 * n_kv, device=device, dtype=dtype) for _ in range(L)]
     for l in range(L):
-        host_in[l][:n_q].copy_(host["q"][l].reshape(-1))
-        host_in[l][n_q:n_q + n_kv].copy_(host["k"][l].reshape(-1))
-        host_in[l][n_q + n_kv:].copy_(host["v"][l].reshape(-1))
-    dq = [t[:n_q].view(B, H_q, 1, D) for t in dev_in]
-    dk = [t[n_q:n_q + n_kv].view(B, H_kv, 1, D) for t in dev_in]
-    dv = [t[n_q + n_kv:].view(B, H_kv, 1, D) for t in dev_in]
+        host_in[l].copy_(torch.randn(n_q + 2 * n_kv, dtype=torch.float32).to(dtype))
+    dq = [t[:n_q].view(q_shape) for t in dev_in]
+    dk = [t[n_q:n_q + n_kv].view(kv_shape) for t in dev_in]
+    dv = [t[n_q + n_kv:].view(kv_shape) for t in dev_in]
     h2d_bytes = L * dev_in[0].numel() * dev_in[0].element_size()
-    d2h_bytes = L * dq[0].numel() * dq[0].element_size()
+    d2h_bytes = L * n_q * dev_in[0].element_size()
     up_stream, down_stream = torch.cuda.Stream(device), torch.cuda.Stream(device)
     ev_in = [torch.cuda.Event() for _ in range(L)]
     ev_done = [torch.cuda.Event() for _ in range(L)]
@@ -360,101 +604,248 @@ def run_ours(args):
                 upload(l + ahead)
             main.wait_event(ev_in[l])
             caches[l].update_and_fetch(dk[l], dv[l])
-            caches[l].fused_sdpa(dq[l], scale, out=outs[l])
+            caches[l].fused_sdpa(dq[l], scale, out=outs[l], gather=px.layer(l) if px is not None else None)
+            if px is not None:
+                px.wait(l)
             ev_done[l].record(main)
             with torch.cuda.stream(down_stream):
                 down_stream.wait_event(ev_done[l])
-                host["o"][l].copy_(outs[l], non_blocking=True)
-            if world > 1:
-                gather(l)
-        if world > 1:
+                host_o[l].copy_(outs[l], non_blocking=True)
+            if gather_mode == "nccl":
+                nccl_gather(l)
+        if gather_mode == "nccl":
             main.wait_stream(comm_stream)
         main.wait_stream(down_stream)
         torch.cuda.synchronize()  # the host reads this step's outputs
 
-    def barrier():
+    g = w["group"]
+    # warm up until 10 steps before the next flush, so that every block of >= 10 steps that
+    # follows crosses quantize-on-append flushes at a known step
+    n_warm = 3
+    while (caches[0].offset + n_warm + 10) % g:
+        n_warm += 1
+    for _ in range(n_warm):
+        e2e_step()
+    timer.barrier()
+    n_steps = max(args.steps, g) * 2  # two flush periods at least
+    alloc0 = torch.cuda.memory_stats(device).get("allocation.all.allocated", 0)
+    per_step = []
+    flush_steps = []
+    t_all0 = time.perf_counter()
+    timer.barrier()
+    for i in range(n_steps):
+        nq_before = caches[0]._n_quantized
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        e2e_step()
+        e1.record()
         torch.cuda.synchronize()
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-
-    for _ in range(max(args.warmup, 3)):
-        step()
-    barrier()
-    sampler = ClockSampler(local_rank)
-    if rank == 0:
-        sampler.start()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    barrier()
-    e0.record()
-    for _ in range(args.steps):
-        step()
-    e1.record()
-    barrier()
-    ms = e0.elapsed_time(e1)
-    clocks = sampler.stop() if rank == 0 else None
-    t = torch.tensor([ms], device=device, dtype=torch.float64)
+        per_step.append(e0.elapsed_time(e1))
+        if caches[0]._n_quantized != nq_before:
+            flush_steps.append(i)
+    timer.barrier()
+    alloc1 = torch.cuda.memory_stats(device).get("allocation.all.allocated", 0)
+    wall_ms = (time.perf_counter() - t_all0) * 1e3 / n_steps
+    t = torch.tensor([float(np.mean(per_step)), float(np.median(per_step)),
+                      float(np.mean([per_step[i] for i in flush_steps])) if flush_steps else 0.0],
+                     device=device, dtype=torch.float64)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms_total = float(t.item())
-    ms_step = ms_total / args.steps
+    mean_ms, median_ms, flush_ms = (float(x) for x in t.tolist())
+    bytes_step = algorithmic_bytes_per_layer(w, n_quant=caches[0]._n_quantized, n_res=caches[0]._n_res) * L
+    return {
+        "value": bytes_step / (mean_ms * 1e-3) / 1e9, "unit": UNIT, "ms_per_step": mean_ms,
+        "ms_per_step_median": median_ms, "flush_step_ms": flush_ms, "steps_timed": n_steps,
+        "flush_steps_in_timed_region": len(flush_steps), "wall_ms_per_step": wall_ms,
+        "tokens_per_s": w["batch"] / (mean_ms * 1e-3),
+        "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": d2h_bytes,
+        "torch_allocations_in_timed_region": int(alloc1 - alloc0),
+        "path": "KIVIKVCache.update_and_fetch(new token; quantize-on-append flush every group) + "
+                "KIVIKVCache.fused_sdpa per layer; pinned host buffers, uploads and downloads on their own "
+                "streams; value = mean over all timed steps, flush steps included",
+    }
 
-    # ---- end-to-end arm (after the kernel arm, so the cache contents above stay fixed)
-    e2e_ms = None
-    if not args.no_e2e:
+
+def run_extras(torch, dist, timer, w, plan, world, rank, device, dtype, px, args, peak):
+    """Further figures of the same run (each a few seconds at most)."""
+    from veloxquant_mlx_b200 import kernels as vk
+
+    extra = {}
+    L, B, H_q, H_kv, D = w["layers"], w["batch"], w["H_q"], w["H_kv"], w["D"]
+    hpk = H_q // H_kv
+    scale = 1.0 / math.sqrt(D)
+
+    def graph_time(fn, steps, blocks=5):
+        try:
+            run = capture(torch, fn).replay
+        except Exception:
+            run = fn
         for _ in range(3):
-            e2e_step()
-        barrier()
-        f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        f0.record()
-        for _ in range(args.steps):
-            e2e_step()
-        f1.record()
-        barrier()
-        te = torch.tensor([f0.elapsed_time(f1)], device=device, dtype=torch.float64)
-        if world > 1:
-            dist.all_reduce(te, op=dist.ReduceOp.MAX)
-        e2e_ms = float(te.item()) / args.steps
+            run()
+        return float(np.median(timer.blocks(run, steps, blocks)))
 
-    from veloxquant_mlx_b200 import _lib
-    _lib.check(_lib.lib().vq_kivi_attend_status(), "bench")
+    if world == 1 and w["name"] == "llama3.1-8b-decode-kivi4" and w["bits"] == 4:
+        # -- the same shape with 2-bit codes (the width the >= 70 % of HBM target is quoted on)
+        c2 = [build_cache(torch, w, (B, H_kv), device, 5000 + l, dtype, bits=2) for l in range(L)]
+        q2 = [torch.randn((B, H_q, 1, D), device=device, dtype=torch.float32).to(dtype) for _ in range(L)]
+        o2 = [torch.empty((B, H_q, 1, D), device=device, dtype=dtype) for _ in range(L)]
 
-    if rank == 0:
-        bytes_layer = algorithmic_bytes_per_layer(w)
-        bytes_step = bytes_layer * L
-        value = world * bytes_step / (ms_step * 1e-3) / 1e9
-        peak, peak_kind = measured_peak()
-        per_launch_s = ms_step * 1e-3 / L
-        achieved = bytes_layer / per_launch_s / 1e9
-        cpu = None
-        if world == 1 and not args.no_cpu_baseline:
-            gbs, sample, cores, _ = cpu_reference_sample(w, seconds_budget=15.0)
-            cpu = {"value": gbs, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample}
-        line = {
-            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
-            "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
-            "vs_baseline": None, "dtype": w["dtype"], "data": "synthetic",
-            "config": {"workload": w["name"], **{k: w[k] for k in ("layers", "batch", "ctx", "bits", "group", "residual", "H_q", "H_kv", "D")},
-                       "global_batch": world * B, "parallelism": f"dp{world} over (batch, kv head) units",
-                       "l2": "inputs larger than L2: each layer's packed KV is read once per step and 32 distinct layers are cycled"},
-            "tokens_per_s": world * B / (ms_step * 1e-3),
-            "pct_of_hbm_peak": 100.0 * (value / world) / peak,
-            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                         "peak_kind": peak_kind + " (burst copy)", "traffic": ncu_traffic(w),
-                         "kernel": f"kivi_attend_mma_kernel<{w['bits']}> (+ tail kernel under its drain, + merge; duration = step time / layers)",
-                         "algorithmic_bytes_per_launch": bytes_layer},
-            "cpu_baseline": cpu,
-            "e2e": None if e2e_ms is None else {
-                "value": world * bytes_step / (e2e_ms * 1e-3) / 1e9, "unit": UNIT, "ms_per_step": e2e_ms,
-                "tokens_per_s": world * B / (e2e_ms * 1e-3),
-                "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": d2h_bytes,
-                "path": "KIVIKVCache.update_and_fetch(new token) + KIVIKVCache.fused_sdpa per layer; pinned host buffers, uploads and downloads on their own streams"},
-            "gpu_launches": 3 * L * args.steps,  # main, tail and merge kernel per layer
-            "clocks": clocks,
-        }
-        print(json.dumps(line), flush=True)
+        def step2():
+            for l in range(L):
+                c2[l].fused_sdpa(q2[l], scale, out=o2[l], overlap_previous=True)
+
+        ms = graph_time(step2, args.steps, 10)
+        bl = algorithmic_bytes_per_layer(w, bits=2)
+        extra["kivi2"] = {"workload": "the default shape with 2-bit codes", "ms_per_step": ms,
+                          "value": bl * L / (ms * 1e-3) / 1e9, "unit": UNIT,
+                          "frac": bl * L / (ms * 1e-3) / 1e9 / peak, "tokens_per_s": B / (ms * 1e-3),
+                          "algorithmic_bytes_per_launch": bl}
+        del c2, q2, o2
+        torch.cuda.empty_cache()
+
+        # -- quantize-on-append: one layer's prefill block, K (per channel) and V (per token)
+        k, v = synth_kv(torch, (B, H_kv, w["ctx"], D), device, 99, dtype)
+        n = k.numel()
+        for bits in (4, 2):
+            for axis, name, x in ((-2, "keys", k), (-1, "values", v)):
+                codes, sc, zr = vk.kivi_quantize(x, axis, w["group"], bits)
+                ms = graph_time(lambda: vk.kivi_quantize_into(x, axis, w["group"], bits, codes=codes, scale=sc, zero=zr), 5)
+                nb = n * x.element_size() + n * bits // 8 + (n // w["group"]) * 8
+                extra[f"quantize_{name}_{bits}bit"] = {"shape": list(x.shape), "us": ms * 1e3, "GBps": nb / (ms * 1e-3) / 1e9,
+                                                       "frac": nb / (ms * 1e-3) / 1e9 / peak, "bytes": nb}
+        del k, v
+        torch.cuda.empty_cache()
+
+        # -- quantize_vq (the dense contraction): config 2 and a long one
+        from veloxquant_mlx_b200 import vecinfer as vi
+        tpeak, tkind = measured_tensor_peak()
+        for S in (4096, 65536):
+            keys = torch.randn(8, S, 128, device=device).to(torch.float16)
+            cb = torch.randn(256, 8, device=device)
+            ms = graph_time(lambda: vi.quantize_vq(keys, cb, 8, index_dtype=torch.uint8), 5)
+            fl = 2 * 8 * S * 16 * 256 * 8
+            extra[f"quantize_vq_S{S}"] = {"shape": [8, S, 128], "us": ms * 1e3, "useful_TFLOPs": fl / (ms * 1e-3) / 1e12,
+                                          "frac_of_bf16_peak": fl / (ms * 1e-3) / 1e12 / tpeak, "peak_kind": tkind}
+        vk.quantize_status()
+
+        # -- RaBitQ config 4: encode and attend
+        from veloxquant_mlx_b200 import rabitq as rq
+        Br, Hr, Sr = 8, 8, 16384
+        keys = torch.randn(Br * Hr * Sr, D, device=device, dtype=torch.float16)
+        diag = torch.from_numpy(rq.make_hadamard_diagonal(D)).to(device)
+        ms = graph_time(lambda: rq.rabitq_encode(keys, diag), 5)
+        nb = keys.numel() * 2 + keys.shape[0] * (D // 8 + 4)
+        extra["rabitq_encode"] = {"rows": keys.shape[0], "us": ms * 1e3, "GBps": nb / (ms * 1e-3) / 1e9, "frac": nb / (ms * 1e-3) / 1e9 / peak}
+        bits_, mag = rq.rabitq_encode(keys, diag)
+        vv = torch.randn(Br, Hr, Sr, D, device=device, dtype=torch.float16)
+        qq = torch.randn(Br, 32, 1, D, device=device, dtype=torch.float16)
+        qsc = torch.full((Br, 32, 1), 0.01, device=device)
+        ms = graph_time(lambda: rq.rabitq_fused_attend(qq, qsc, bits_.view(Br, Hr, Sr, D // 8), mag.view(Br, Hr, Sr), None, vv, None), 5)
+        nb = Br * Hr * Sr * (D // 8 + 4 + 2 * D)
+        extra["rabitq_attend"] = {"shape": [Br, Hr, Sr, D], "us": ms * 1e3, "GBps": nb / (ms * 1e-3) / 1e9, "frac": nb / (ms * 1e-3) / 1e9 / peak}
+        del keys, vv, bits_, mag
+        torch.cuda.empty_cache()
+
+    if world > 1 and w["name"] == "llama3.1-8b-decode-kivi4":
+        # -- weak scaling (secondary): every rank attends a whole batch of its own, no exchange
+        cw = [build_cache(torch, w, (B, H_kv), device, 9000 + 1000 * l + rank, dtype) for l in range(L)]
+        qw = [torch.randn((B, H_q, 1, D), device=device, dtype=torch.float32).to(dtype) for _ in range(L)]
+        ow = [torch.empty((B, H_q, 1, D), device=device, dtype=dtype) for _ in range(L)]
+
+        def stepw():
+            for l in range(L):
+                cw[l].fused_sdpa(qw[l], scale, out=ow[l], overlap_previous=True)
+
+        ms = graph_time(stepw, args.steps, 10)
+        bl = algorithmic_bytes_per_layer(w)
+        extra["weak_scaling"] = {"what": "replicated mode: every rank attends its own batch of 16, no output exchange",
+                                 "global_batch": world * B, "ms_per_step": ms,
+                                 "value": world * bl * L / (ms * 1e-3) / 1e9, "unit": UNIT,
+                                 "tokens_per_s": world * B / (ms * 1e-3)}
+        del cw, qw, ow
+        torch.cuda.empty_cache()
+
+    if w["name"] == "llama3.1-8b-decode-kivi4" and not args.no_c5:
+        extra["qwen32b_prefill_decode"] = run_c5(torch, dist, timer, plan.world, rank, device, dtype, args)
+    return extra
+
+
+def run_c5(torch, dist, timer, world, rank, device, dtype, args):
+    """The Qwen2.5-32B-shaped configuration: 64 layers, 40 query heads, 8 KV heads, batch 4, a
+    16384-token prompt quantized on write (KIVI 2-bit), then 256 decode steps (append + attend)
+    over the packed cache, the 32 (batch, kv head) units partitioned over the ranks."""
+    from veloxquant_mlx_b200 import kernels as vk
+    from veloxquant_mlx_b200 import sharding
+
+    class A:  # the c5 workload through the same helper
+        workload, layers, batch, ctx, bits = "c5", args.c5_layers, None, 16384, None
+
+    w = workload(A)
+    L, B, H_q, H_kv, D = w["layers"], w["batch"], w["H_q"], w["H_kv"], w["D"]
+    hpk = H_q // H_kv
+    plan = sharding.plan_shards(B, H_kv, world, rank)
+    shape_bh = (B, H_kv) if world == 1 else (plan.size, 1)
+    q_shape = (B, H_q, 1, D) if world == 1 else (plan.size, hpk, 1, D)
+    scale = 1.0 / math.sqrt(D)
+    S = 16384
+    k, v = synth_kv(torch, (*shape_bh, S, D), device, 77 + rank, dtype)
+    caches = [new_cache(w) for _ in range(L)]
+    # warm the quantize kernels on a scratch cache (first-launch cost is not the prompt's)
+    new_cache(w).update_and_fetch(k, v)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    timer.barrier()
+    e0.record()
+    for l in range(L):
+        caches[l].update_and_fetch(k, v)
+    e1.record()
+    timer.barrier()
+    t = torch.tensor([e0.elapsed_time(e1)], device=device, dtype=torch.float64)
     if world > 1:
-        dist.destroy_process_group()
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    prefill_ms = float(t.item())
+    n = B * H_kv * S * D  # elements of K (and of V) per layer, whole batch
+    prefill_bytes = L * 2 * (n * 2 + n * w["bits"] // 8 + (n // w["group"]) * 8)
+    del k, v
+    px = None
+    if world > 1 and args.gather == "peer":
+        try:
+            px = sharding.PeerExchange(plan, L, hpk, D, dtype, device)
+            ok = torch.tensor([1], device=device)
+        except Exception:
+            ok = torch.tensor([0], device=device)
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+        if int(ok.item()) == 0:
+            px = None
+    n_dec = args.c5_decode_steps
+    qs = [torch.randn(q_shape, device=device, dtype=torch.float32).to(dtype) for _ in range(L)]
+    kn = torch.randn((*shape_bh, 1, D), device=device, dtype=torch.float32).to(dtype)
+    vn = torch.randn((*shape_bh, 1, D), device=device, dtype=torch.float32).to(dtype)
+    outs = [torch.empty(q_shape, device=device, dtype=dtype) for _ in range(L)]
+
+    def dec_step():
+        for l in range(L):
+            caches[l].update_and_fetch(kn, vn)
+            caches[l].fused_sdpa(qs[l], scale, out=outs[l], gather=px.layer(l) if px is not None else None)
+            if px is not None:
+                px.wait(l)
+
+    for _ in range(3):
+        dec_step()
+    ms = timer.blocks(dec_step, n_dec - 3, 1)[0]
+    vk.attend_status()
+    ctx_end = caches[0].offset
+    wq = dict(w, ctx=ctx_end)
+    wq["n_quant"], wq["n_res"] = caches[0]._n_quantized, caches[0]._n_res
+    bl = algorithmic_bytes_per_layer(wq)
+    if px is not None:
+        px.close()
+    return {"workload": w["name"], "layers": L, "batch": B, "prompt": S, "decode_steps": n_dec, "bits": w["bits"],
+            "prefill_ms": prefill_ms, "prefill_quantize_GBps": prefill_bytes / (prefill_ms * 1e-3) / 1e9,
+            "prefill_tokens_per_s": B * S / (prefill_ms * 1e-3),
+            "decode_ms_per_step": ms, "decode_tokens_per_s": B / (ms * 1e-3),
+            "decode_value": bl * L / (ms * 1e-3) / 1e9, "unit": UNIT,
+            "units_per_rank": plan.size, "gather": "peer" if px is not None else ("none" if world == 1 else "not gathered"),
+            "note": "decode steps are eager launches through update_and_fetch + fused_sdpa (host-bound at this size)"}
 
 
 def main():
@@ -468,8 +859,15 @@ def main():
     ap.add_argument("--batch", type=int, default=None)
     ap.add_argument("--ctx", type=int, default=None)
     ap.add_argument("--bits", type=int, default=None)
+    ap.add_argument("--gather", default="peer", choices=["peer", "nccl"],
+                    help="how a layer's output rows reach every rank when N > 1")
+    ap.add_argument("--no-graph", action="store_true", help="time eager launches instead of graph replays")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-extras", action="store_true")
+    ap.add_argument("--no-c5", action="store_true")
+    ap.add_argument("--c5-layers", type=int, default=64)
+    ap.add_argument("--c5-decode-steps", type=int, default=256)
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

@@ -7,7 +7,7 @@
  * Conventions
  *   - Every pointer is a DEVICE pointer owned by the caller unless stated otherwise; the
  *     library never allocates. Scratch memory is passed in as `workspace`, sized by the
- *     matching `*_workspace_bytes` query.
+ *     matching `*_workspace_bytes` query. Successive calls on one stream may share a workspace.
  *   - Every call is asynchronous on `stream` (a cudaStream_t passed as void*; NULL = the
  *     legacy default stream) and returns a vq_status (0 = ok, negative = error). After a
  *     non-zero return `vq_last_error()` holds a thread-local, human-readable reason.
@@ -48,6 +48,23 @@ typedef enum vq_dtype { VQ_F16 = 0, VQ_BF16 = 1, VQ_F32 = 2 } vq_dtype;
 int32_t vq_version(void);
 /* Thread-local message for the last non-zero status returned on this thread. */
 const char *vq_last_error(void);
+
+/* Process-wide tuning and self-test knobs (for measurement sweeps and the library's own tests;
+ * the defaults are what the kernels were tuned with). Returns the previous value, or
+ * INT32_MIN for an unknown knob or a value out of range. No counterpart in the reference. */
+typedef enum vq_knob {
+    VQ_KNOB_ATTEND_STAGES = 0,   /* bulk-copy pipeline depth of the decode attend: 2..4 (2) */
+    VQ_KNOB_ATTEND_WAVES = 1,    /* waves of CTAs the split count aims at: 1..32 (2) */
+    VQ_KNOB_VQ_SEARCH = 2,       /* vq_vq_quantize search: 0 choose, 1 tcgen05, 2 mma.sync, 3 exact */
+    VQ_KNOB_ATTEND_WAIT_TEST = 3,/* 1: in the NEXT vq_kivi_decode_attend (tensor-core kernel) every warp
+                                    also waits, with 1024 polls, on a barrier that nothing arms: the
+                                    bounded wait runs out, the kernel finishes normally and
+                                    vq_kivi_attend_status reports VQ_ERR_TIMEOUT once (one-shot
+                                    self-test of that path; nothing faults or hangs) */
+    VQ_KNOB_VQ_WAIT_TEST = 4     /* 1: the same for the NEXT tcgen05 vq_vq_quantize launch and
+                                    vq_vq_quantize_status */
+} vq_knob;
+int32_t vq_tune(int32_t knob, int32_t value);
 
 /* ------------------------------------------------------------------------------------
  * KIVI asymmetric group quantization
@@ -129,7 +146,8 @@ int32_t vq_kivi_dequant(const vq_kivi_dequant_args *args, void *stream);
  * unquantized tail (the residual window) attended in the same call.
  *   out[b,h,sq,:] = softmax_s( scale * q[b,h,sq,:] . K_hat[b,hk,s,:] ) . V_hat[b,hk,s,:]
  * with hk = h / (H_q/H_kv) (contiguous GQA blocks), K_hat = code*k_scale+k_zero for
- * s < n_quant and the tail rows after that. No mask: every query row sees every slot.
+ * s < n_quant and the tail rows after that. No mask (every query row sees every slot) unless
+ * VQ_ATTEND_CAUSAL is set in `flags`.
  *
  * Replaces scalar_fused_decode_attend (veloxquant_mlx/metal/_scalar_attend.py:370-493,
  * metal/src/scalar_affine_attend.metal:8-175) and scalar_predecoded_attend
@@ -163,12 +181,28 @@ typedef struct vq_kivi_attend_args {
     int32_t n_splits;         /* context splits per (b, kv head); 0 = choose */
     int32_t variant;          /* 0 = choose; 1 = force the general CUDA-core kernel;
                                  2 = force the tensor-core kernel (error if unsupported) */
+    int32_t flags;            /* VQ_ATTEND_* bits, 0 = none */
+    int32_t reserved;         /* must be 0 */
+    const struct vq_peer_gather *gather; /* NULL, or where the output rows are also published
+                                 to the other ranks of a sharded run (see vq_peer_gather) */
 } vq_kivi_attend_args;
+/* The attention kernel may begin while the work that precedes this call on the stream is still
+ * running (programmatic dependent launch): its prologue and its reads of the packed cache then
+ * hide the previous kernels' drain, e.g. the previous layer's vq_kivi_decode_attend. The caller
+ * promises that every INPUT of this call (q, codes, scales, zeros, residual rows) was complete
+ * before that preceding work was launched. `workspace` and `out` are exempt: the library orders
+ * its own accesses to them, so back-to-back calls may share one workspace. Tensor-core kernel
+ * only; ignored by the general kernel. */
+#define VQ_ATTEND_OVERLAP_PREVIOUS 1
+/* Tail-aligned causal mask for S_q > 1: query row r sits at slot n_quant + n_res - S_q + r and
+ * sees the slots up to its own (the mask of metal_fused_sdpa, veloxquant_mlx/metal/
+ * fused_sdpa.py:200-299, applied to the KIVI store; S_q <= n_quant + n_res). General kernel. */
+#define VQ_ATTEND_CAUSAL 2
 int64_t vq_kivi_attend_workspace_bytes(const vq_kivi_attend_args *args);
 int32_t vq_kivi_decode_attend(const vq_kivi_attend_args *args, void *stream);
 /* Synchronises the device, then reports (and clears) whether any earlier
- * vq_kivi_decode_attend or vq_rabitq_decode_attend kernel abandoned a bounded device-side wait: VQ_ERR_TIMEOUT if so
- * (its output is then invalid), VQ_OK otherwise. No counterpart in the reference (its
+ * vq_kivi_decode_attend, vq_rabitq_decode_attend or vq_peer_gather_wait kernel abandoned a
+ * bounded device-side wait: VQ_ERR_TIMEOUT if so (its output is then invalid), VQ_OK otherwise. No counterpart in the reference (its
  * kernels have no device-side waits). */
 int32_t vq_kivi_attend_status(void);
 
@@ -189,16 +223,60 @@ int32_t vq_predecoded_attend(const vq_kivi_attend_args *args, void *stream);
 int32_t vq_lse_merge(const float *part_o, const float *part_ml, int64_t rows, int32_t n_splits,
                      int32_t D, void *out, int32_t out_dtype, void *stream);
 
+/* ------------------------------------------------------------------------------------
+ * Sharded decode: publishing a rank's output rows to its peers
+ *
+ * (batch, kv head) units are independent, so a decode step sharded over several GPUs of one
+ * node needs no collective inside attention; each rank only has to deliver its rows of the
+ * layer's output [B*H_q*S_q, D] to every rank. With `gather` set, the merge step of
+ * vq_kivi_decode_attend stores its rows straight into every rank's copy of the gathered tensor
+ * (plain stores to peer-mapped addresses over NVLink; no multicast, no bulk-copy engine) and
+ * then raises an arrival word on every rank. vq_peer_gather_wait is the consumer side: a
+ * one-CTA kernel that returns once all ranks' rows of the current round have arrived, or
+ * gives up after a bounded number of polls (vq_kivi_attend_status then reports VQ_ERR_TIMEOUT).
+ * Rounds are counted on the device (`state`), so a captured CUDA graph can be replayed.
+ * The reference has no multi-device code; there is no counterpart.
+ * ---------------------------------------------------------------------------------- */
+#define VQ_MAX_PEERS 16
+typedef struct vq_peer_gather {
+    int32_t world, rank;          /* 1 <= world <= VQ_MAX_PEERS: every rank receives the rows */
+    int32_t n_sources;            /* ranks 0..n_sources-1 publish rows (ranks beyond hold replicas
+                                     and publish nothing); 1 <= n_sources <= world */
+    int32_t reserved;             /* must be 0 */
+    int64_t row_offset;           /* first row of this call's rows inside the gathered tensor */
+    void *out[VQ_MAX_PEERS];      /* base of the gathered tensor on each rank (own entry included),
+                                     out_dtype, rows of D elements, 16-byte aligned */
+    uint32_t *flags[VQ_MAX_PEERS];/* arrival words on each rank: uint32[world]; this rank
+                                     writes entry `rank` of every array */
+    uint32_t *state;              /* this rank's round counters: uint32[4], zeroed once by the
+                                     caller together with its `flags` array */
+} vq_peer_gather;
+/* Waits on `stream` until the rows of the next round have arrived from every publishing rank
+ * in this rank's gathered tensor. Call it once per vq_kivi_decode_attend that was given the same `gather`. */
+int32_t vq_peer_gather_wait(const vq_peer_gather *gather, void *stream);
+/* Inter-process handle of the device allocation that contains `ptr` (cudaIpcGetMemHandle) and
+ * the offset of `ptr` inside it, for a peer process to map. `handle` receives 64 bytes. The
+ * memory must come from cudaMalloc (PyTorch's default allocator qualifies). */
+int32_t vq_peer_export(const void *ptr, void *handle, int64_t *offset);
+/* Maps a peer process's allocation into this process (cudaIpcOpenMemHandle, peer access
+ * enabled lazily): `*base` is its first byte. Open each allocation once per process. */
+int32_t vq_peer_open(const void *handle, void **base);
+int32_t vq_peer_close(void *base);
+
 /* The same operation as vq_kivi_decode_attend for callers that cannot allocate device
  * memory (a frozen memory pool, a host runtime that owns all allocations, a path where a
  * synchronising, fallible cudaMalloc is not acceptable). It has no counterpart in the
  * reference. `workspace` / `workspace_bytes` in `args` are ignored: the split partials go
- * into an array built into the library (VQ_KIVI_STATIC_SCRATCH_BYTES,
- * 8 MiB, resident on every GPU that loads the library until the process exits). The call
- * allocates nothing and returns VQ_ERR_CAPACITY, with the needed and available sizes in
- * vq_last_error(), when vq_kivi_attend_workspace_bytes(args) exceeds that capacity.
- *  - The first call on each device looks up the array's device address (one-time set-up,
- *    done with that device current); make that first call before starting a stream capture.
+ * into an array built into the library (VQ_KIVI_STATIC_SCRATCH_BYTES, 8 MiB per GPU, held
+ * until the process exits). After its one-time set-up on a device the call allocates nothing;
+ * it returns VQ_ERR_CAPACITY, with the needed and available sizes in vq_last_error(), when
+ * vq_kivi_attend_workspace_bytes(args) exceeds that capacity.
+ *  - The FIRST call on each device looks up the array's device address (done with that device
+ *    current). With CUDA's default lazy module loading this look-up is also the moment the
+ *    driver loads the array's module on that device and sets aside its 8 MiB, so that first
+ *    call can fail with VQ_ERR_CUDA (out of memory). Make it once per device while device
+ *    memory may still be taken -- before the memory pool is frozen, before the first request,
+ *    and before any stream capture. Every later call on that device allocates nothing.
  *  - All calls on a device share the one array. Calls must not overlap on the GPU (issue
  *    them on one stream, or order them with events): overlapping calls race on it. Nothing
  *    in it needs clearing between calls; every record read is written by the same call. */

@@ -124,8 +124,13 @@ def quantization_boundary(offset: int, residual_length: int, g: int) -> int:
 
 
 def reference_attend(q, kc, ks, kz, vc, vs, vz, g: int, scale: float,
-                     k_res=None, v_res=None) -> np.ndarray:
+                     k_res=None, v_res=None, causal: bool = False) -> np.ndarray:
     """Dense fp32 softmax attention over dequantized K/V (+ optional fp16 tail).
+
+    ``causal=True`` applies the tail-aligned causal mask the reference uses for attention
+    over compressed caches (query row ``r`` of ``S_q`` sits at slot ``S_kv - S_q + r`` and
+    sees slots up to its own: ``tests/cache/test_vecinfer_fused_sdpa.py:69-115``,
+    ``metal/fused_sdpa.py:200-299``).
 
     ``q [B,H_q,S_q,D]``; quantized tensors carry ``H_kv`` heads; GQA uses
     contiguous blocks (``np.repeat`` along the head axis). No mask: every query
@@ -151,6 +156,10 @@ def reference_attend(q, kc, ks, kz, vc, vs, vz, g: int, scale: float,
         k_hat = np.repeat(k_hat, rep, axis=1)
         v_hat = np.repeat(v_hat, rep, axis=1)
     scores = np.einsum("bhqd,bhsd->bhqs", q.astype(np.float32), k_hat) * np.float32(scale)
+    if causal:
+        S_kv = k_hat.shape[2]
+        q_abs = S_kv - S_q + np.arange(S_q)[:, None]
+        scores = np.where(np.arange(S_kv)[None, :] <= q_abs, scores, -np.inf)
     scores = scores - scores.max(axis=-1, keepdims=True)
     w = np.exp(scores)
     w = w / w.sum(axis=-1, keepdims=True)

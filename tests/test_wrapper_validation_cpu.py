@@ -1,0 +1,84 @@
+"""Argument validation of the kernel wrappers happens on the host, before any pointer reaches
+the native library: a wrong-shaped output or a too-short parameter buffer must be a
+``ValueError``, never an out-of-bounds device access. None of these calls needs a GPU (the
+checks come before the device check)."""
+
+from __future__ import annotations
+
+import pytest
+import torch
+
+from veloxquant_mlx_b200 import kernels as k
+
+B, H_q, H_kv, D, g, bits, cap = 2, 8, 2, 128, 32, 4, 64
+
+
+def _attend_inputs():
+    rb = D * bits // 8
+    return dict(
+        q=torch.zeros(B, H_q, 1, D, dtype=torch.float16),
+        k_codes=torch.zeros(B, H_kv, cap, rb, dtype=torch.uint8),
+        k_scale=torch.ones(B, H_kv, cap // g, D), k_zero=torch.zeros(B, H_kv, cap // g, D),
+        v_codes=torch.zeros(B, H_kv, cap, rb, dtype=torch.uint8),
+        v_scale=torch.ones(B, H_kv, cap, D // g), v_zero=torch.zeros(B, H_kv, cap, D // g),
+    )
+
+
+def _call(t, **kw):
+    return k.kivi_decode_attend(t["q"], t["k_codes"], t["k_scale"], t["k_zero"], t["v_codes"], t["v_scale"],
+                                t["v_zero"], g, 0.1, store_bits=bits, **kw)
+
+
+def test_well_formed_cpu_call_reaches_the_device_check_only():
+    from veloxquant_mlx_b200 import VQLibraryError
+
+    with pytest.raises(VQLibraryError, match="must be a CUDA tensor"):
+        _call(_attend_inputs())
+
+
+@pytest.mark.parametrize("mutate,match", [
+    (lambda t: t.update(out=torch.zeros(B, H_q, 1, D // 2, dtype=torch.float16)), "out must be a contiguous"),
+    (lambda t: t.update(out=torch.zeros(B, H_q, 2, D, dtype=torch.float16)[:, :, :1]), "out must be a contiguous"),
+    (lambda t: t.update(out=torch.zeros(B, H_q, 1, D, dtype=torch.int32)), "unsupported out dtype"),
+    (lambda t: t.update(k_scale=t["k_scale"][:, :, :1], k_zero=t["k_zero"][:, :, :1]), "k_scale/k_zero"),
+    (lambda t: t.update(k_zero=t["k_zero"][:, :, :1]), "k_scale/k_zero"),
+    (lambda t: t.update(k_scale=t["k_scale"][..., :64], k_zero=t["k_zero"][..., :64]), "k_scale/k_zero"),
+    (lambda t: t.update(v_scale=t["v_scale"][:, :, :32], v_zero=t["v_zero"][:, :, :32]), "v_scale/v_zero"),
+    (lambda t: t.update(v_scale=t["v_scale"][..., :2], v_zero=t["v_zero"][..., :2]), "v_scale/v_zero"),
+    (lambda t: t.update(v_codes=t["v_codes"][:1]), "v_codes shape"),
+    (lambda t: t.update(v_codes=t["v_codes"][..., :32]), "v_codes shape"),
+    (lambda t: t.update(k_scale=t["k_scale"].double()), "k_scale must be a float32"),
+    (lambda t: t.update(k_codes=t["k_codes"].to(torch.int8)), "must be uint8"),
+    (lambda t: t.update(gather=object()), "gather must be"),
+])
+def test_decode_attend_rejects_malformed_buffers_before_any_launch(mutate, match):
+    t = _attend_inputs()
+    extra = {}
+    probe = dict(t)
+    mutate(probe)
+    for key in ("out", "gather"):
+        if key in probe:
+            extra[key] = probe.pop(key)
+    with pytest.raises(ValueError, match=match):
+        _call(probe, **extra)
+
+
+def test_decode_attend_rejects_bad_residual_rows():
+    t = _attend_inputs()
+    res = torch.zeros(B, H_kv, 16, D, dtype=torch.float16)
+    with pytest.raises(ValueError, match="exceed the residual buffers"):
+        _call(t, k_res=res, v_res=res, n_res=10, res_offset=8)
+    with pytest.raises(ValueError, match="k_res / v_res must be"):
+        _call(t, k_res=res[:1], v_res=res[:1])
+
+
+def test_quantize_into_rejects_buffers_of_another_batch_or_head_count():
+    x = torch.zeros(B, H_kv, 32, D, dtype=torch.float16)
+    codes = torch.zeros(B, H_kv, 64, D * bits // 8, dtype=torch.uint8)
+    scale = torch.zeros(B, H_kv, 2, D)
+    with pytest.raises(ValueError, match="leading"):
+        k.kivi_quantize_into(x, -2, g, bits, codes=codes[:1], scale=scale, zero=scale.clone())
+    with pytest.raises(ValueError, match="leading"):
+        k.kivi_quantize_into(x, -2, g, bits, codes=codes, scale=scale[:, :1].contiguous(), zero=scale[:, :1].clone())
+    with pytest.raises(ValueError, match="contiguous uint8"):
+        k.kivi_quantize_into(x, -2, g, bits, codes=codes[..., :32], scale=scale, zero=scale.clone())

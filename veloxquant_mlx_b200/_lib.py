@@ -61,6 +61,22 @@ class KiviAttendArgs(C.Structure):
         ("k_res", C.c_void_p), ("v_res", C.c_void_p), ("res_dtype", C.c_int32), ("res_stride_bh", C.c_int64),
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_int64),
         ("n_splits", C.c_int32), ("variant", C.c_int32),
+        ("flags", C.c_int32), ("reserved", C.c_int32), ("gather", C.c_void_p),
+    ]
+
+
+VQ_ATTEND_OVERLAP_PREVIOUS = 1
+VQ_ATTEND_CAUSAL = 2
+VQ_MAX_PEERS = 16
+(VQ_KNOB_ATTEND_STAGES, VQ_KNOB_ATTEND_WAVES, VQ_KNOB_VQ_SEARCH, VQ_KNOB_ATTEND_WAIT_TEST,
+ VQ_KNOB_VQ_WAIT_TEST) = range(5)
+
+
+class PeerGather(C.Structure):
+    _fields_ = [
+        ("world", C.c_int32), ("rank", C.c_int32), ("n_sources", C.c_int32), ("reserved", C.c_int32),
+        ("row_offset", C.c_int64),
+        ("out", C.c_void_p * VQ_MAX_PEERS), ("flags", C.c_void_p * VQ_MAX_PEERS), ("state", C.c_void_p),
     ]
 
 
@@ -104,6 +120,11 @@ class VqEncodeArgs(C.Structure):
 SIGNATURES = {
     "vq_version": (C.c_int32, []),
     "vq_last_error": (C.c_char_p, []),
+    "vq_tune": (C.c_int32, [C.c_int32, C.c_int32]),
+    "vq_peer_gather_wait": (C.c_int32, [C.POINTER(PeerGather), C.c_void_p]),
+    "vq_peer_export": (C.c_int32, [C.c_void_p, C.c_void_p, C.POINTER(C.c_int64)]),
+    "vq_peer_open": (C.c_int32, [C.c_void_p, C.POINTER(C.c_void_p)]),
+    "vq_peer_close": (C.c_int32, [C.c_void_p]),
     "vq_kivi_quantize": (C.c_int32, [C.POINTER(KiviQuantArgs), C.c_void_p]),
     "vq_kivi_quantize_pack": (C.c_int32, [C.POINTER(KiviQuantArgs), C.c_void_p]),
     "vq_kivi_quant_dequant": (C.c_int32, [C.POINTER(KiviQuantArgs), C.c_void_p]),

@@ -29,6 +29,7 @@ SOURCES = [
     ("kivi_attend.cu", []),
     ("kivi_attend_mma.cu", []),
     ("kivi_attend_static.cu", []),
+    ("peer_gather.cu", []),
     ("vq_quant.cu", ["-fmad=false"]),
     ("vq_encode.cu", ["-fmad=false"]),
     ("vq_quant_mma.cu", []),

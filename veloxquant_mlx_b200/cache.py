@@ -252,8 +252,11 @@ class KIVIKVCache:
     """Packed KIVI cache: per-channel keys, per-token values, fp residual window.
 
     Storage (grown geometrically): packed codes ``u8 [B,H,cap,D*sb/8]``, key params
-    ``f32 [B,H,cap/g,D]``, value params ``f32 [B,H,cap,D/g]``, residual ``[B,H,R+g+.., D]``
-    in the activation dtype. Quantization policy = ``KIVIKVCache._quantization_boundary``
+    ``f32 [B,H,cap/g,D]``, value params ``f32 [B,H,cap,D/g]``, residual ``[B,H,2(R+g)+g.., D]``
+    in the activation dtype: the live rows are ``[_res_lo, _res_lo + _n_res)``; a flush
+    quantizes the oldest rows where they lie and advances ``_res_lo``, and the live rows move
+    back to the front (one copy, into rows they do not overlap) only when the buffer's end is
+    reached, so a decode step allocates nothing. Quantization policy = ``KIVIKVCache._quantization_boundary``
     of the reference (``cache/kivi_cache.py:206-225``): after each append, tokens older than
     ``residual_length`` are flushed in whole ``group_size`` blocks, so one-shot prefill and
     token-by-token decode quantize identical groups. Never exposes ``.bits``.
@@ -283,6 +286,7 @@ class KIVIKVCache:
         self.offset = 0
         self._n_quantized = 0
         self._n_res = 0
+        self._res_lo = 0
         self._cap = 0
         self._k_codes = self._v_codes = None
         self._k_scale = self._k_zero = self._v_scale = self._v_zero = None
@@ -329,17 +333,51 @@ class KIVIKVCache:
         self._cap = new_cap
 
     def _ensure_residual(self, B, H, D, n, device, dtype) -> None:
+        """Room for ``n`` live rows starting at row 0 (a larger buffer is allocated, and the
+        live rows are moved to its front, only when ``n`` exceeds the capacity)."""
         if self._k_res is not None and self._k_res.shape[2] >= n:
             return
-        cap = max(self._residual_length + 2 * self._group_size, n)
+        cap = max(2 * (self._residual_length + self._group_size) + self._group_size, n)
         # one allocation for both, so that a K/V pair that arrives as two slices of one tensor
         # (a fused QKV projection's output) is appended by a single copy
         kv = torch.empty((2, B, H, cap, D), dtype=dtype, device=device)
-        k, v = kv[0], kv[1]
-        if self._k_res is not None and self._n_res:
-            k[:, :, : self._n_res] = self._k_res[:, :, : self._n_res]
-            v[:, :, : self._n_res] = self._v_res[:, :, : self._n_res]
-        self._kv_res, self._k_res, self._v_res = kv, k, v
+        if self._kv_res is not None and self._n_res:
+            kv[:, :, :, : self._n_res] = self._kv_res[:, :, :, self._res_lo : self._res_lo + self._n_res]
+        self._kv_res, self._k_res, self._v_res = kv, kv[0], kv[1]
+        self._res_lo = 0
+
+    def _make_room(self, B, H, D, S, device, dtype) -> None:
+        """Make rows ``[_res_lo + _n_res, +S)`` of the residual buffer exist."""
+        if self._k_res is None or self._n_res + S > self._k_res.shape[2]:
+            self._ensure_residual(B, H, D, self._n_res + S, device, dtype)
+        elif self._res_lo + self._n_res + S > self._k_res.shape[2]:
+            lo, n = self._res_lo, self._n_res
+            if n:
+                if lo >= n:   # disjoint rows: a plain copy, nothing allocated
+                    self._kv_res[:, :, :, :n] = self._kv_res[:, :, :, lo : lo + n]
+                else:
+                    self._kv_res[:, :, :, :n] = self._kv_res[:, :, :, lo : lo + n].clone()
+            self._res_lo = 0
+
+    def _store_block(self, keys, values, S) -> None:
+        at = self._res_lo + self._n_res
+        if not kernels.kivi_append(keys, values, self._k_res, self._v_res, at):
+            pair = _paired_view(keys, values)
+            if pair is not None:
+                self._kv_res[:, :, :, at : at + S] = pair
+            else:
+                self._k_res[:, :, at : at + S] = keys
+                self._v_res[:, :, at : at + S] = values
+        self._n_res += S
+
+    def _quantize_rows(self, src_k, src_v, n_flush) -> None:
+        g = self._group_size
+        kernels.kivi_quantize_into(src_k[:, :, :n_flush], -2, g, self._b, codes=self._k_codes,
+                                   scale=self._k_scale, zero=self._k_zero, tok_offset=self._n_quantized,
+                                   store_bits=self._sb, eps=self._eps)
+        kernels.kivi_quantize_into(src_v[:, :, :n_flush], -1, g, self._b, codes=self._v_codes,
+                                   scale=self._v_scale, zero=self._v_zero, tok_offset=self._n_quantized,
+                                   store_bits=self._sb, eps=self._eps)
 
     # -- protocol ----------------------------------------------------------------------
     def update_and_fetch(self, keys: torch.Tensor, values: torch.Tensor):
@@ -354,49 +392,58 @@ class KIVIKVCache:
             self._dtype = keys.dtype
         self._shape_bhd = (B, H, D)
         dev = keys.device
-        g = self._group_size
         self.offset += S
         new_boundary = self._quantization_boundary()
         n_flush = new_boundary - self._n_quantized
         if n_flush <= 0:
-            self._ensure_residual(B, H, D, self._n_res + S, dev, keys.dtype)
-            if not kernels.kivi_append(keys, values, self._k_res, self._v_res, self._n_res):
-                pair = _paired_view(keys, values)
-                if pair is not None:
-                    self._kv_res[:, :, :, self._n_res : self._n_res + S] = pair
-                else:
-                    self._k_res[:, :, self._n_res : self._n_res + S] = keys
-                    self._v_res[:, :, self._n_res : self._n_res + S] = values
-            self._n_res += S
-        else:
-            # Rows to flush are the oldest unquantized ones: the residual first, then the
-            # head of this block. A large prefill block is quantized straight from the
-            # caller's tensor; only its tail is copied into the residual buffer.
-            if self._n_res == 0:
-                src_k, src_v = keys, values
-            else:
-                src_k = torch.cat([self._k_res[:, :, : self._n_res], keys], dim=2)
-                src_v = torch.cat([self._v_res[:, :, : self._n_res], values], dim=2)
+            self._make_room(B, H, D, S, dev, keys.dtype)
+            self._store_block(keys, values, S)
+        elif self._n_res == 0:
+            # A (prefill) block onto an empty residual: its head is quantized straight from the
+            # caller's tensor, only its tail is copied into the residual buffer.
             self._ensure_capacity(B, H, D, new_boundary, dev, keys.dtype)
-            kernels.kivi_quantize_into(src_k[:, :, :n_flush], -2, g, self._b, codes=self._k_codes,
-                                       scale=self._k_scale, zero=self._k_zero, tok_offset=self._n_quantized,
-                                       store_bits=self._sb, eps=self._eps)
-            kernels.kivi_quantize_into(src_v[:, :, :n_flush], -1, g, self._b, codes=self._v_codes,
-                                       scale=self._v_scale, zero=self._v_zero, tok_offset=self._n_quantized,
-                                       store_bits=self._sb, eps=self._eps)
-            keep = src_k.shape[2] - n_flush
-            self._n_res = 0
+            self._quantize_rows(keys, values, n_flush)
+            self._n_quantized = new_boundary
+            keep = S - n_flush
+            self._res_lo = 0
             self._ensure_residual(B, H, D, keep, dev, keys.dtype)
             if keep > 0:
-                self._k_res[:, :, :keep] = src_k[:, :, n_flush:]
-                self._v_res[:, :, :keep] = src_v[:, :, n_flush:]
-            self._n_res = keep
+                self._store_block(keys[:, :, n_flush:], values[:, :, n_flush:], keep)
+        elif S <= self._residual_length + self._group_size:
+            # Decode: the rows to flush are the oldest unquantized rows. The block is stored behind
+            # the live rows, then the aged rows are quantized where they lie and the window's
+            # start moves on: no concatenation, no shifting, no allocation.
+            self._make_room(B, H, D, S, dev, keys.dtype)
+            self._store_block(keys, values, S)
+            self._ensure_capacity(B, H, D, new_boundary, dev, keys.dtype)
+            lo = self._res_lo
+            self._quantize_rows(self._k_res[:, :, lo : lo + n_flush], self._v_res[:, :, lo : lo + n_flush], n_flush)
+            self._res_lo += n_flush
+            self._n_res -= n_flush
+            self._n_quantized = new_boundary
+        else:
+            # A long block onto a non-empty residual: the rows to flush span both.
+            lo = self._res_lo
+            src_k = torch.cat([self._k_res[:, :, lo : lo + self._n_res], keys], dim=2)
+            src_v = torch.cat([self._v_res[:, :, lo : lo + self._n_res], values], dim=2)
+            self._ensure_capacity(B, H, D, new_boundary, dev, keys.dtype)
+            self._quantize_rows(src_k, src_v, n_flush)
+            keep = src_k.shape[2] - n_flush
+            self._n_res = 0
+            self._res_lo = 0
+            self._ensure_residual(B, H, D, keep, dev, keys.dtype)
+            if keep > 0:
+                self._store_block(src_k[:, :, n_flush:], src_v[:, :, n_flush:], keep)
             self._n_quantized = new_boundary
         self._account_bytes(B, H, S, D, max(n_flush, 0))
         if self._memory_bound:
             z = keys.new_zeros((B, H, 0, D))
             return z, z
         return self._materialize()
+
+    def _live_res(self):
+        lo = self._res_lo
+        return self._k_res[:, :, lo : lo + self._n_res], self._v_res[:, :, lo : lo + self._n_res]
 
     def _materialize(self):
         """The reference cache's view: round-tripped quantized rows, then the exact tail."""
@@ -413,32 +460,42 @@ class KIVIKVCache:
                                             out_dtype=self._dtype)
             parts_k.append(kq)
             parts_v.append(vq)
-        parts_k.append(self._k_res[:, :, : self._n_res])
-        parts_v.append(self._v_res[:, :, : self._n_res])
+        kr, vr = self._live_res()
+        parts_k.append(kr)
+        parts_v.append(vr)
         return torch.cat(parts_k, dim=2), torch.cat(parts_v, dim=2)
 
     def fused_sdpa(self, q: torch.Tensor, scale: float, *, causal: bool = True, sliding_window: int = 0,
-                   out: torch.Tensor | None = None) -> torch.Tensor:
+                   out: torch.Tensor | None = None, overlap_previous: bool = False, gather=None) -> torch.Tensor:
         """Attention of ``q [B,H_q,S_q,D]`` over the packed store + residual, no dequantized
-        copy of the history. One query row per call (decode); for several rows pass
-        ``causal=False`` (every row then sees every slot, as the reference's
-        ``scalar_fused_decode_attend`` does)."""
+        copy of the history. With ``causal=True`` query row ``r`` of ``S_q`` sits at position
+        ``offset - S_q + r`` and sees the slots up to its own (the tail-aligned mask of the
+        reference's ``metal_fused_sdpa``, ``metal/fused_sdpa.py:200-299``); ``causal=False``
+        lets every row see every slot, as the reference's ``scalar_fused_decode_attend`` does.
+
+        ``overlap_previous`` / ``gather``: see :func:`kernels.kivi_decode_attend`."""
         if q.ndim != 4:
             raise ValueError(f"KIVIKVCache.fused_sdpa: q must be 4D, got {tuple(q.shape)}")
         if sliding_window:
             raise ValueError("KIVIKVCache.fused_sdpa: sliding_window is not supported")
-        if q.shape[2] != 1 and causal:
-            raise ValueError("KIVIKVCache.fused_sdpa: causal masking needs S_q == 1 (decode); "
-                             "use dense attention over update_and_fetch's output for prefill")
         if self.offset == 0:
             raise RuntimeError("KIVIKVCache.fused_sdpa: the cache is empty")
+        if q.shape[2] > self.offset and causal:
+            raise ValueError(f"KIVIKVCache.fused_sdpa: {q.shape[2]} query rows but only {self.offset} cached tokens")
         has_q = self._n_quantized > 0
         return kernels.kivi_decode_attend(
             q, self._k_codes if has_q else None, self._k_scale, self._k_zero,
             self._v_codes if has_q else None, self._v_scale, self._v_zero, self._group_size, scale,
             store_bits=self._sb, n_quant=self._n_quantized,
             k_res=self._k_res if self._n_res else None, v_res=self._v_res if self._n_res else None,
-            n_res=self._n_res, out=out, _fn="KIVIKVCache.fused_sdpa")
+            n_res=self._n_res, res_offset=self._res_lo, out=out, causal=bool(causal) and q.shape[2] > 1,
+            overlap_previous=overlap_previous, gather=gather, _fn="KIVIKVCache.fused_sdpa")
+
+    def check_status(self) -> None:
+        """Raise if a device-side bounded wait of an earlier attention call ran out (its output
+        was then invalid). Synchronises the device; call it where a silent wrong result is not
+        acceptable, e.g. once per decode step."""
+        kernels.attend_status()
 
     # -- trim / state ------------------------------------------------------------------
     def trim(self, n: int) -> int:
@@ -470,9 +527,11 @@ class KIVIKVCache:
                                                 self._v_scale[:, :, new_nq : hi_g * g].contiguous(),
                                                 self._v_zero[:, :, new_nq : hi_g * g].contiguous(), g, "V",
                                                 store_bits=self._sb, out_dtype=self._dtype)
+                self._n_res = 0
                 self._ensure_residual(B, H, D, keep, kq.device, self._dtype)
                 self._k_res[:, :, :keep] = kq[:, :, :keep]
                 self._v_res[:, :, :keep] = vq[:, :, :keep]
+            self._res_lo = 0
             self._n_res = keep
             self._n_quantized = new_nq
         self.offset = new_offset
@@ -500,7 +559,7 @@ class KIVIKVCache:
         pk = lambda t, n: None if t is None else t[:, :, :n].contiguous()  # noqa: E731
         return (pk(self._k_codes, nq), pk(self._k_scale, nq // g), pk(self._k_zero, nq // g),
                 pk(self._v_codes, nq), pk(self._v_scale, nq), pk(self._v_zero, nq),
-                self._k_res[:, :, : self._n_res].contiguous(), self._v_res[:, :, : self._n_res].contiguous(),
+                *(t.contiguous() for t in self._live_res()),
                 torch.tensor([self.offset, nq, self._n_res]))
 
     @state.setter
@@ -512,6 +571,7 @@ class KIVIKVCache:
         B, H, _, D = kr.shape
         self._shape_bhd, self._dtype = (B, H, D), kr.dtype
         self._k_codes = self._v_codes = None
+        self._k_scale = self._k_zero = self._v_scale = self._v_zero = None
         self._cap = 0
         if nq:
             self._ensure_capacity(B, H, D, nq, kr.device, kr.dtype)
@@ -522,6 +582,7 @@ class KIVIKVCache:
         self._n_quantized = nq
         self._kv_res = self._k_res = self._v_res = None
         self._n_res = 0
+        self._res_lo = 0
         self._ensure_residual(B, H, D, n_res, kr.device, kr.dtype)
         self._k_res[:, :, :n_res], self._v_res[:, :, :n_res] = kr, vr
         self._n_res = n_res

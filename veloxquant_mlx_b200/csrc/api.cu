@@ -1,4 +1,6 @@
 // Library-wide plumbing: version, thread-local error text, cached device facts.
+#include <atomic>
+#include <climits>
 #include <mutex>
 
 #include "common.cuh"
@@ -17,6 +19,17 @@ int32_t fail(int32_t code, const char *fmt, ...) {
     va_end(ap);
     return code;
 }
+
+// Process-wide knobs behind vq_tune(): defaults, and the accepted range of each.
+namespace {
+struct KnobSpec { int def, lo, hi; };
+constexpr KnobSpec kKnobSpec[] = {{2, 2, 4}, {2, 1, 32}, {0, 0, 3}, {0, 0, 1}, {0, 0, 1}};
+constexpr int kNumKnobs = sizeof(kKnobSpec) / sizeof(kKnobSpec[0]);
+std::atomic<int> g_knobs[kNumKnobs] = {{2}, {2}, {0}, {0}, {0}};
+}  // namespace
+
+int knob_get(int knob) { return g_knobs[knob].load(std::memory_order_relaxed); }
+int knob_take(int knob) { return g_knobs[knob].exchange(kKnobSpec[knob].def, std::memory_order_relaxed); }
 
 int32_t device_info(DeviceInfo *out) {
     // One entry per device ordinal; filled on first use and read-only afterwards.
@@ -44,5 +57,10 @@ int32_t device_info(DeviceInfo *out) {
 
 }  // namespace vq
 
-extern "C" int32_t vq_version(void) { return 100; }
+extern "C" int32_t vq_version(void) { return 200; }
+extern "C" int32_t vq_tune(int32_t knob, int32_t value) {
+    using namespace vq;
+    if (knob < 0 || knob >= kNumKnobs || value < kKnobSpec[knob].lo || value > kKnobSpec[knob].hi) return INT_MIN;
+    return g_knobs[knob].exchange(value, std::memory_order_relaxed);
+}
 extern "C" const char *vq_last_error(void) { return vq::last_error_buf(); }

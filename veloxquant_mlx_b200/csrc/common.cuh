@@ -49,6 +49,10 @@ struct DeviceInfo {
 };
 int32_t device_info(DeviceInfo *out);
 
+// Current value of a vq_knob (see vq_tune); knob_take also puts the default back (one-shot knobs).
+int knob_get(int knob);
+int knob_take(int knob);
+
 // ---- typed element access --------------------------------------------------------------
 template <typename T>
 __device__ __forceinline__ float to_f32(T v);

@@ -44,7 +44,8 @@ kivi_attend_general_kernel(const vq_kivi_attend_args a, int n_splits, int n_head
     }
     __syncthreads();
 
-    const int total = a.n_quant + a.n_res;
+    // slots this query row sees: all of them, or (tail-aligned causal mask) those up to its own
+    const int total = (a.flags & VQ_ATTEND_CAUSAL) ? a.n_quant + a.n_res - a.S_q + sq + 1 : a.n_quant + a.n_res;
     const int chunk = (total + n_splits - 1) / n_splits;
     const int t_begin = split * chunk;
     const int t_end = min(total, t_begin + chunk);
@@ -278,11 +279,14 @@ extern "C" int64_t vq_kivi_attend_workspace_bytes(const vq_kivi_attend_args *arg
 
 extern "C" int32_t vq_kivi_attend_status(void) {
     using namespace vq;
-    int flag = 0, flag2 = 0;
+    int flag = 0, flag2 = 0, flag3 = 0;
     int32_t rc = kivi_attend_mma_take_timeout(&flag);
     if (rc != VQ_OK) return rc;
     rc = coded_attend_take_timeout(&flag2);
     if (rc != VQ_OK) return rc;
+    rc = peer_gather_take_timeout(&flag3);
+    if (rc != VQ_OK) return rc;
+    if (flag3) return fail(VQ_ERR_TIMEOUT, "vq_peer_gather_wait: a peer's output rows did not arrive within the poll limit");
     if (flag) return fail(VQ_ERR_TIMEOUT, "vq_kivi_decode_attend: a bounded wait on a bulk-copy barrier gave up");
     if (flag2) return fail(VQ_ERR_TIMEOUT, "vq_rabitq_decode_attend: a bounded wait on a bulk-copy barrier gave up");
     return VQ_OK;
@@ -299,12 +303,19 @@ extern "C" int32_t vq_kivi_decode_attend(const vq_kivi_attend_args *args, void *
     if (rc != VQ_OK) return rc;
     cudaStream_t st = (cudaStream_t)stream;
 
+    VQ_REQUIRE(a.reserved == 0 && (a.flags & ~(VQ_ATTEND_OVERLAP_PREVIOUS | VQ_ATTEND_CAUSAL)) == 0, VQ_ERR_SHAPE,
+               "vq_kivi_decode_attend: unknown bits in flags (%d) or reserved (%d)", a.flags, a.reserved);
+    VQ_REQUIRE(!(a.flags & VQ_ATTEND_CAUSAL) || a.S_q <= a.n_quant + a.n_res, VQ_ERR_SHAPE,
+               "vq_kivi_decode_attend: causal mask with S_q=%d query rows over %d slots", a.S_q, a.n_quant + a.n_res);
     if (a.variant != 1) {
         const char *why = kivi_attend_mma_supported(a);
         if (why == nullptr) return kivi_attend_mma_launch(a, di, st);
         VQ_REQUIRE(a.variant != 2, VQ_ERR_SHAPE, "vq_kivi_decode_attend: tensor-core kernel unavailable: %s", why);
     }
 
+    VQ_REQUIRE(a.gather == nullptr, VQ_ERR_SHAPE,
+               "vq_kivi_decode_attend: publishing to peers (gather) needs the tensor-core kernel: %s",
+               a.variant == 1 ? "variant 1 was forced" : kivi_attend_mma_supported(a));
     const int n_splits = general_splits(a, di.sm_count);
     const int64_t rows = (int64_t)a.B * a.H_q * a.S_q;
     float *part_o = nullptr, *part_ml = nullptr;

@@ -13,6 +13,8 @@ int kivi_attend_mma_tail_parts(const vq_kivi_attend_args &a);
 int32_t kivi_attend_mma_take_timeout(int *flag);
 // The same flag of the staged RaBitQ attend kernel (coded_attend.cu).
 int32_t coded_attend_take_timeout(int *flag);
+// The same flag of the peer-arrival wait kernel (peer_gather.cu).
+int32_t peer_gather_take_timeout(int *flag);
 int32_t kivi_attend_mma_launch(const vq_kivi_attend_args &a, const DeviceInfo &di, cudaStream_t st);
 // Combine per-split partial softmaxes written as part_o[(row*n_splits+s)*D + d] (natural-exp
 // domain, unnormalised) and part_ml[(row*n_splits+s)*2 + {0: max, 1: sum}] into out[row*D + d].

@@ -50,6 +50,7 @@ constexpr int kMaxStages = 4;
 constexpr int kMaxHeads = 8;   // query heads per kv head
 constexpr int kChunkHeads = 4; // query heads per CTA (hi/lo halves fill the 8 MMA columns)
 constexpr uint32_t kSpinLimit = 1u << 18;
+constexpr uint32_t kSelfTestSpinLimit = 1u << 10;
 
 __device__ int g_attend_timeout = 0;
 
@@ -71,7 +72,7 @@ struct Cfg {
     static constexpr int STAGE_BYTES = VZ_OFF + 512;  // one warp, one stage: 6144 / 4096
     static constexpr int VROWS = kGroup * RB / 128;   // 128-byte lines of one group's V codes: 16 / 8
     // stages first (1024-byte aligned, as the swizzle pattern repeats every 1024 bytes), barriers after
-    static constexpr int smem_bytes(int stages) { return kWarps * stages * STAGE_BYTES + 128; }
+    static constexpr int smem_bytes(int stages) { return kWarps * stages * STAGE_BYTES + 256; }
 };
 
 // ---- PTX helpers ------------------------------------------------------------------------
@@ -85,8 +86,8 @@ __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
 }
 // Bounded wait: returns false (and the caller records a timeout) instead of spinning forever.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
-    for (uint32_t i = 0; i < kSpinLimit; ++i) {
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, uint32_t limit = kSpinLimit) {
+    for (uint32_t i = 0; i < limit; ++i) {
         uint32_t ok;
         asm volatile(
             "{\n\t.reg .pred p;\n\t"
@@ -209,14 +210,16 @@ struct Params {
     int groups_per_warp;  // consecutive groups owned by one warp
     float *part_o;      // [B*H_kv][n_parts][hpk][128]
     float *part_ml;     // [B*H_kv][n_parts][hpk][2]
+    int wait_test;      // self-test: every warp also waits (briefly) on a barrier that nothing arms
+    vq_peer_gather gather;  // world == 0: the output rows are not published to peers
 };
 
 // ---- tail (unquantized tokens): CUDA cores, n_tail CTAs per (batch, kv head) ---------------
 // A kernel of its own, launched after the main kernel as its programmatic dependent: its CTAs
 // become resident once every main CTA has started, i.e. they run on the SMs that the draining
-// main grid leaves idle, and they need nothing the main grid writes. Before it exits, each CTA
-// waits for the main grid (griddepcontrol.wait), so that the merge kernel, which waits for THIS
-// grid, also sees the main grid's partials complete. Tail CTA `ti` takes an equal slice of the
+// main grid leaves idle, and they need nothing the main grid writes. Before it writes its
+// partials, each CTA waits for the main grid (griddepcontrol.wait), so that the merge kernel,
+// which waits for THIS grid, also sees the main grid's partials complete. Tail CTA `ti` takes an equal slice of the
 // tail tokens; inside it each warp takes every fourth token, four tokens' rows in flight.
 template <typename T>
 __device__ __forceinline__ void load_row4(const T *p, float (&d)[4]) {
@@ -295,6 +298,10 @@ __global__ void __launch_bounds__(kWarps * 32) kivi_attend_tail_kernel(const __g
         }
     }
     __syncthreads();
+    // The partials may share their buffer with the previous call on the stream, and the merge
+    // kernel, which waits for THIS grid only, must find the main grid's partials complete too:
+    // wait for the main grid (and, through its own wait, for everything before it) here.
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     const int part = p.n_splits + ti;
     for (int i = threadIdx.x; i < hpk * kD; i += blockDim.x) {
         const int hp = i / kD, d = i % kD;
@@ -311,8 +318,6 @@ __global__ void __launch_bounds__(kWarps * 32) kivi_attend_tail_kernel(const __g
         p.part_o[rec * kD + d] = acc;
         if (d == 0) { p.part_ml[rec * 2] = gm; p.part_ml[rec * 2 + 1] = gl; }
     }
-    // this grid completes only after the main grid has (see the note above the kernel)
-    asm volatile("griddepcontrol.wait;" ::: "memory");
 }
 
 // ---- main kernel ----------------------------------------------------------------------------
@@ -378,7 +383,7 @@ kivi_attend_mma_kernel(const __grid_constant__ Params p) {
     };
 
     if (tid == 0) {
-        for (int s = 0; s < kWarps * STAGES; ++s) mbar_init(bar0 + 8u * s, 1);
+        for (int s = 0; s < kWarps * STAGES + 1; ++s) mbar_init(bar0 + 8u * s, 1);  // the last one is never armed
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
@@ -604,7 +609,15 @@ kivi_attend_mma_kernel(const __grid_constant__ Params p) {
         }
     }
 
-    if (timed_out && lane == 0) atomicExch(&g_attend_timeout, 1);
+    // Self-test of the bounded wait: a barrier that nothing arms never completes its phase.
+    if (p.wait_test && !mbar_wait(bar0 + 8u * (kWarps * STAGES), 0u, kSelfTestSpinLimit)) timed_out = true;
+    if (timed_out) {
+        if (lane == 0) atomicExch(&g_attend_timeout, 1);
+        // copies announced to a barrier that gave up may still be landing: give them time before
+        // the stages are reused below and the CTA leaves
+        if (!p.wait_test)
+            for (int i = 0; i < 64; ++i) __nanosleep(1000);
+    }
 
     // ---- merge the four warps, write this split's partial -----------------------------------
     l_run += __shfl_xor_sync(0xffffffffu, l_run, 4);
@@ -649,6 +662,11 @@ kivi_attend_mma_kernel(const __grid_constant__ Params p) {
         }
     }
     __syncthreads();
+    // Launched as a programmatic dependent (VQ_ATTEND_OVERLAP_PREVIOUS), this grid runs beside
+    // the end of the previous call, which may still be reading partials from the same buffer:
+    // everything above touched only this call's inputs; the writes below wait for the work
+    // before this grid to finish. (Returns at once after a plain launch.)
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     const int n_heads = min(kChunkHeads, hpk - h0);
     for (int i = tid; i < n_heads * kD; i += blockDim.x) {
         const int hp = i / kD, d = i % kD;
@@ -676,7 +694,10 @@ constexpr int kMergeMaxParts = 520;
 __global__ void __launch_bounds__(kD) kivi_attend_mma_merge_kernel(const __grid_constant__ Params p) {
     __shared__ float sh_w[kMergeMaxParts];
     __shared__ float sh_red[kD / 32];
+    __shared__ __align__(16) uint8_t sh_row[kD * 4];
     const vq_kivi_attend_args &a = p.a;
+    // the next call's kernel, if it asked to overlap, may become resident from here on
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const int hp = blockIdx.x % p.hpk;
     const int64_t bh = blockIdx.x / p.hpk;
     const int b = (int)(bh / a.H_kv), hkv = (int)(bh % a.H_kv);
@@ -737,27 +758,44 @@ __global__ void __launch_bounds__(kD) kivi_attend_mma_merge_kernel(const __grid_
     }
     for (; s < p.n_parts; ++s) acc = fmaf(p.part_o[(rec0 + (int64_t)s * p.hpk) * kD + d], sh_w[s], acc);
     const int64_t row = (int64_t)b * a.H_q + hkv * p.hpk + hp;
-    store_from_f32(a.out, a.out_dtype, row * kD + d, acc / gl);
+    const float res = acc / gl;
+    store_from_f32(a.out, a.out_dtype, row * kD + d, res);
+    if (p.gather.world > 0) {
+        // Publish the row to every rank's gathered tensor: the row is staged in shared memory in
+        // the output dtype and leaves as 16-byte stores (one per 16 threads and rank).
+        const vq_peer_gather &pg = p.gather;
+        store_from_f32(sh_row, a.out_dtype, d, res);
+        __syncthreads();
+        const int row_bytes = kD * (a.out_dtype == VQ_F32 ? 4 : 2);
+        const int segs = row_bytes / 16;
+        const int64_t grow = pg.row_offset + row;
+        for (int i = d; i < pg.world * segs; i += kD) {
+            const int pr = i / segs, sg = i % segs;
+            uint4 *dst = reinterpret_cast<uint4 *>(static_cast<uint8_t *>(pg.out[pr]) + grow * row_bytes) + sg;
+            *dst = reinterpret_cast<const uint4 *>(sh_row)[sg];
+        }
+        // Arrival: each storing thread fences system-wide, the CTA counts itself in; the CTA that
+        // completes the count opens the next round and raises this rank's word on every rank.
+        __threadfence_system();
+        __syncthreads();
+        if (d == 0) {
+            const unsigned prev = atomicAdd(&pg.state[0], 1u);
+            if (prev == gridDim.x - 1) {
+                pg.state[0] = 0u;
+                const unsigned round = pg.state[1] + 1u;
+                pg.state[1] = round;
+                __threadfence_system();
+                for (int pr = 0; pr < pg.world; ++pr)
+                    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(pg.flags[pr] + pg.rank), "r"(round) : "memory");
+            }
+        }
+    }
 }
 
-// Pipeline depth and waves-per-launch are tunables; the environment overrides exist for
-// measurement sweeps (VQ_ATTEND_STAGES = 2..4, VQ_ATTEND_WAVES = 1..32).
-int tuned_stages() {
-    static int v = [] {
-        const char *e = getenv("VQ_ATTEND_STAGES");
-        const int s = e ? atoi(e) : 2;
-        return (s >= 2 && s <= kMaxStages) ? s : 2;
-    }();
-    return v;
-}
-int tuned_waves() {
-    static int v = [] {
-        const char *e = getenv("VQ_ATTEND_WAVES");
-        const int s = e ? atoi(e) : 2;
-        return (s >= 1 && s <= 32) ? s : 2;
-    }();
-    return v;
-}
+// Pipeline depth and waves-per-launch are tunables (vq_tune: VQ_KNOB_ATTEND_STAGES = 2..4,
+// VQ_KNOB_ATTEND_WAVES = 1..32).
+int tuned_stages() { return knob_get(VQ_KNOB_ATTEND_STAGES); }
+int tuned_waves() { return knob_get(VQ_KNOB_ATTEND_WAVES); }
 
 int smem_for(int bits, int stages) {
     return bits == 4 ? Cfg<4>::smem_bytes(stages) : Cfg<2>::smem_bytes(stages);
@@ -801,13 +839,20 @@ int32_t launch_one(const Params &p, dim3 grid, cudaStream_t st) {
     const int smem = smem_for(BITS, STAGES);
     VQ_CHECK_CUDA(cudaFuncSetAttribute(kivi_attend_mma_kernel<BITS, STAGES>,
                                        cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-    // A plain (fully serialised) launch: only the kernels that follow it inside this call are
-    // programmatic dependents. (Launching this kernel as a dependent of the previous call's merge
-    // kernel, with the merge kernel triggering early, measured 2.4 % faster, but the same
-    // arrangement on the coded-cache kernels produced a wrong result in one test and the cause
-    // was not found, so it is not used.)
-    kivi_attend_mma_kernel<BITS, STAGES><<<grid, kWarps * 32, smem, st>>>(p);
-    VQ_CHECK_LAUNCH("kivi_attend_mma_kernel");
+    // A plain (fully serialised) launch unless the caller set VQ_ATTEND_OVERLAP_PREVIOUS: then the
+    // grid is a programmatic dependent of whatever precedes it on the stream (the previous call's
+    // merge kernel triggers early) and only its epilogue waits for that work.
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(kWarps * 32);
+    cfg.dynamicSmemBytes = (size_t)smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = (p.a.flags & VQ_ATTEND_OVERLAP_PREVIOUS) ? 1 : 0;
+    VQ_CHECK_CUDA(cudaLaunchKernelEx(&cfg, kivi_attend_mma_kernel<BITS, STAGES>, p));
     return VQ_OK;
 }
 
@@ -878,17 +923,22 @@ static EncodeTiledFn encode_tiled_fn() {
 // A per-(batch, kv head) array of 128-byte lines as a rank-3 byte tensor [n_bh][lines][128] whose
 // boxes (`box_lines` lines) are stored with the 128-byte swizzle. Used for the V codes (a unit's
 // rows are contiguous, so a line holds 2 (4-bit) or 4 (2-bit) token rows; one box = one 32-token
-// group) and for the K scales / zeros (4 lines of 32 floats per group). The last encoding of
-// each of the three uses is kept per thread: a decode loop calls with the same buffers again.
+// group) and for the K scales / zeros (4 lines of 32 floats per group).
 static int32_t make_line_map(int slot, const void *base, int64_t lines, int64_t stride_bh_bytes, int32_t n_bh,
                              int32_t box_lines, CUtensorMap *map) {
+    // An encoding depends on nothing but these five values, so entries never go stale. A decode
+    // step calls with one set of buffers per layer: 64 direct-mapped entries per use and thread
+    // keep all of them (the driver call costs more than the rest of this function's caller).
     struct Key { const void *ptr; int64_t lines, stride; int32_t n_bh, box; };
-    thread_local Key last_key[3] = {};
-    thread_local CUtensorMap last_map[3];
+    constexpr int kEntries = 64;
+    struct Entry { Key key; CUtensorMap map; };
+    thread_local Entry cache[3][kEntries] = {};
     const Key key = {base, lines, stride_bh_bytes, n_bh, box_lines};
-    Key &lk = last_key[slot];
+    const uintptr_t h = reinterpret_cast<uintptr_t>(base) >> 8;
+    Entry &e = cache[slot][(h ^ (h >> 6) ^ (h >> 12) ^ (h >> 18)) % kEntries];
+    const Key &lk = e.key;
     if (key.ptr == lk.ptr && key.lines == lk.lines && key.stride == lk.stride && key.n_bh == lk.n_bh && key.box == lk.box) {
-        *map = last_map[slot];
+        *map = e.map;
         return VQ_OK;
     }
     EncodeTiledFn enc = encode_tiled_fn();
@@ -902,8 +952,8 @@ static int32_t make_line_map(int slot, const void *base, int64_t lines, int64_t 
                            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     VQ_REQUIRE(r == CUDA_SUCCESS, VQ_ERR_CUDA, "vq_kivi_decode_attend: cuTensorMapEncodeTiled failed (%d)", (int)r);
-    lk = key;
-    last_map[slot] = *map;
+    e.key = key;
+    e.map = *map;
     return VQ_OK;
 }
 
@@ -919,6 +969,21 @@ int32_t kivi_attend_mma_launch(const vq_kivi_attend_args &a, const DeviceInfo &d
         if (rc != VQ_OK) return rc;
     }
     p.a = a;
+    p.a.gather = nullptr;  // (a host pointer: the kernels get a copy of the struct instead)
+    p.wait_test = knob_take(VQ_KNOB_ATTEND_WAIT_TEST);
+    p.gather = vq_peer_gather{};
+    if (a.gather != nullptr) {
+        const vq_peer_gather &pg = *a.gather;
+        VQ_REQUIRE(pg.world >= 1 && pg.world <= VQ_MAX_PEERS && pg.rank >= 0 && pg.rank < pg.world, VQ_ERR_SHAPE,
+                   "vq_kivi_decode_attend: gather rank %d of %d is out of range", pg.rank, pg.world);
+        VQ_REQUIRE(pg.rank < pg.n_sources && pg.n_sources <= pg.world, VQ_ERR_SHAPE,
+                   "vq_kivi_decode_attend: gather rank %d is not one of the %d publishing ranks", pg.rank, pg.n_sources);
+        VQ_REQUIRE(pg.state != nullptr && pg.row_offset >= 0, VQ_ERR_SHAPE, "vq_kivi_decode_attend: gather state is NULL");
+        for (int r = 0; r < pg.world; ++r)
+            VQ_REQUIRE(pg.out[r] != nullptr && pg.flags[r] != nullptr && is_aligned(pg.out[r], 16), VQ_ERR_ALIGN,
+                       "vq_kivi_decode_attend: gather buffers of rank %d must be non-NULL and 16-byte aligned", r);
+        p.gather = pg;
+    }
     p.hpk = a.H_q / a.H_kv;
     p.n_chunks = (int)ceil_div(p.hpk, kChunkHeads);
     p.n_splits = choose_splits(a, di);

@@ -9,10 +9,15 @@
 // caller; this one needs no workspace argument at all. The partial (max, sum, output)
 // records of the context splits go into a fixed array that is part of the library image.
 //
-// The array below lives in every CUDA context that loads this library, from load until
-// process exit (kStaticScratchBytes per GPU). In host code its name is only a handle for
-// the runtime, not an address a kernel could use, so the device address is looked up with
-// cudaGetSymbolAddress, once per device, and that pointer is what the kernels receive.
+// The array below is part of this library's device image: kStaticScratchBytes per GPU, held
+// until process exit once its module is loaded on that GPU. In host code its name is only a
+// handle for the runtime, not an address a kernel could use, so the device address is looked
+// up with cudaGetSymbolAddress, once per device, and that pointer is what the kernels receive.
+// This translation unit holds nothing but the array, so under CUDA's default lazy module
+// loading the look-up is what loads its module on a device: the driver sets the 8 MiB aside
+// at that moment, and the look-up can fail when the device is out of memory. That is why the
+// first call per device belongs before the caller freezes its memory; it is the only call
+// that can take device memory.
 #include <mutex>
 
 #include "common.cuh"

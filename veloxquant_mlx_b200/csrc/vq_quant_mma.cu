@@ -368,13 +368,13 @@ int32_t launch_sub(const void *x, int64_t n, int sub_dim, const float *cb, int n
 }  // namespace
 
 bool vq_quantize_mma_supported(const void *x, int32_t x_dtype, int64_t n, int32_t sub_dim, int32_t n_c, int32_t n_sub) {
-    static const char *mode = std::getenv("VQ_VQ_SEARCH");  // "exact" pins the CUDA-core search
-    if (mode && (std::strcmp(mode, "exact") == 0 || std::strcmp(mode, "tc5") == 0)) return false;
+    const int mode = knob_get(VQ_KNOB_VQ_SEARCH);  // 0 choose; 1 tcgen05 / 2 mma.sync / 3 exact pin one search
+    if (mode == 1 || mode == 3) return false;
     if (n_sub < 0 || n_sub > 65535 || (sub_dim != 4 && sub_dim != 8)) return false;
     if (n_c < 2 || n_c > 2048) return false;
     if (x_dtype != VQ_F16 && x_dtype != VQ_BF16 && x_dtype != VQ_F32) return false;
     if (!is_aligned(x, x_dtype == VQ_F32 ? 8 : 4)) return false;
-    const bool forced = mode && std::strcmp(mode, "mma") == 0;
+    const bool forced = mode == 2;
     return forced || n >= 1024;  // tiny inputs: the prologue would dominate
 }
 

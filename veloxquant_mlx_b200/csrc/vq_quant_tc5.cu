@@ -66,8 +66,8 @@ __device__ __forceinline__ void mma_f16_ss(uint32_t d_tmem, uint64_t a_desc, uin
         : "memory");
 }
 
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
-    for (uint32_t i = 0; i < kSpin; ++i) {
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, uint32_t limit = kSpin) {
+    for (uint32_t i = 0; i < limit; ++i) {
         uint32_t ok;
         asm volatile(
             "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
@@ -150,6 +150,7 @@ struct Tc5Smem {
     float xch_acc[kRows];          // pass-2 results of the upper column half
     float xch_base[kRows];
     uint64_t bar;
+    uint64_t idle_bar;             // never armed (self-test of the bounded wait)
     uint32_t tmem_base;
     float cmax2;
     int cb_bad;
@@ -225,7 +226,7 @@ __device__ __forceinline__ void pass_count(uint32_t taddr, int c_lo, int c_hi, f
 template <typename T>
 __global__ void __launch_bounds__(kThreads, 2)
 vq_quantize_tc5_kernel(const T *__restrict__ x, int64_t n_vec, const float *__restrict__ cb_all, int n_c, int n_sub,
-                       void *__restrict__ indices, int index_bytes) {
+                       void *__restrict__ indices, int index_bytes, int wait_test) {
     // With one codebook per sub-space (n_sub > 0) a CTA works on sub-space blockIdx.y only: its
     // rows are the sub-vectors sub, sub + n_sub, ... (row i is sub-vector i * vstride + sub).
     const int sub = n_sub > 0 ? blockIdx.y : 0;
@@ -286,6 +287,7 @@ vq_quantize_tc5_kernel(const T *__restrict__ x, int64_t n_vec, const float *__re
     if (tid == 0) {
         const uint32_t bar = smem_u32(&sm.bar);
         asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(bar));
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_u32(&sm.idle_bar)));
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 0) {
@@ -426,6 +428,9 @@ vq_quantize_tc5_kernel(const T *__restrict__ x, int64_t n_vec, const float *__re
     __syncthreads();
     finish_prev();
     if (timed_out && lane == 0) atomicExch(&g_tc5_timeout, 1);
+    // Self-test of the bounded wait, after all the work: a barrier that nothing arms never
+    // completes its phase, so this wait runs out and the flag is raised (indices stay valid).
+    if (wait_test && tid == 0 && !mbar_wait(smem_u32(&sm.idle_bar), 0u, 1u << 10)) atomicExch(&g_tc5_timeout, 1);
     // ---- release tensor memory on every path ---------------------------------------------------
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
@@ -438,12 +443,12 @@ vq_quantize_tc5_kernel(const T *__restrict__ x, int64_t n_vec, const float *__re
 }  // namespace
 
 bool vq_quantize_tc5_supported(const void *x, int32_t x_dtype, int64_t n, int32_t sub_dim, int32_t n_c, int32_t n_sub) {
-    static const char *mode = std::getenv("VQ_VQ_SEARCH");  // "exact" / "mma" / "tc5" pin one search
-    if (mode && (std::strcmp(mode, "exact") == 0 || std::strcmp(mode, "mma") == 0)) return false;
+    const int mode = knob_get(VQ_KNOB_VQ_SEARCH);  // 0 choose; 1 tcgen05 / 2 mma.sync / 3 exact pin one search
+    if (mode == 2 || mode == 3) return false;
     if ((x_dtype != VQ_F16 && x_dtype != VQ_BF16) || sub_dim != kSub || n_sub < 0 || n_sub > 65535) return false;
     if (n_c < 16 || n_c > 256 || n_c % 16) return false;
     if (!is_aligned(x, 16)) return false;
-    const bool forced = mode && std::strcmp(mode, "tc5") == 0;
+    const bool forced = mode == 1;
     return forced ? n >= 1 : n >= 4096;  // small inputs: the CUDA-core search has no set-up cost
 }
 
@@ -461,10 +466,11 @@ int32_t vq_quantize_tc5_launch(const void *x, int32_t x_dtype, int64_t n, const 
     const int64_t n_tiles = ceil_div(ceil_div(n, ny), kRows);
     const int64_t fill = std::max<int64_t>(1, ceil_div((int64_t)di.sm_count * 2, ny));  // CTAs per sub-space for two per SM
     const unsigned blocks = (unsigned)std::max<int64_t>(1, std::min<int64_t>(n_tiles, fill));
+    const int wait_test = knob_take(VQ_KNOB_VQ_WAIT_TEST);
     if (x_dtype == VQ_BF16)
-        vq_quantize_tc5_kernel<__nv_bfloat16><<<dim3(blocks, ny), kThreads, smem, st>>>((const __nv_bfloat16 *)x, n, cb, n_c, n_sub, indices, index_bytes);
+        vq_quantize_tc5_kernel<__nv_bfloat16><<<dim3(blocks, ny), kThreads, smem, st>>>((const __nv_bfloat16 *)x, n, cb, n_c, n_sub, indices, index_bytes, wait_test);
     else
-        vq_quantize_tc5_kernel<__half><<<dim3(blocks, ny), kThreads, smem, st>>>((const __half *)x, n, cb, n_c, n_sub, indices, index_bytes);
+        vq_quantize_tc5_kernel<__half><<<dim3(blocks, ny), kThreads, smem, st>>>((const __half *)x, n, cb, n_c, n_sub, indices, index_bytes, wait_test);
     VQ_CHECK_LAUNCH("vq_quantize_tc5_kernel");
     return VQ_OK;
 }

@@ -27,6 +27,37 @@ def kivi_available() -> bool:
     return os.path.exists(_lib.LIB_PATH) and torch.cuda.is_available()
 
 
+_KNOBS = {"attend_stages": _lib.VQ_KNOB_ATTEND_STAGES, "attend_waves": _lib.VQ_KNOB_ATTEND_WAVES,
+          "vq_search": _lib.VQ_KNOB_VQ_SEARCH, "attend_wait_test": _lib.VQ_KNOB_ATTEND_WAIT_TEST,
+          "vq_wait_test": _lib.VQ_KNOB_VQ_WAIT_TEST}
+
+
+def tune(knob: str, value: int) -> int:
+    """Set a process-wide tuning / self-test knob of the native library (``vq_tune``) and return
+    its previous value. Knobs: ``attend_stages`` (2..4), ``attend_waves`` (1..32), ``vq_search``
+    (0 choose, 1 tcgen05, 2 mma.sync, 3 exact), and the one-shot self-tests ``attend_wait_test``
+    / ``vq_wait_test`` that make the next launch's bounded device wait run out."""
+    if knob not in _KNOBS:
+        raise ValueError(f"tune: unknown knob {knob!r}; choices: {sorted(_KNOBS)}")
+    prev = lib().vq_tune(_KNOBS[knob], int(value))
+    if prev == -(1 << 31):
+        raise ValueError(f"tune: value {value} is out of range for {knob!r}")
+    return prev
+
+
+def attend_status() -> None:
+    """Synchronise the device and raise :class:`VQLibraryError` (``VQ_ERR_TIMEOUT``) if a decode
+    attention or peer-arrival kernel launched since the last check gave up a bounded device-side
+    wait; its output is then invalid. The flag is cleared by the check. Poll this where a wrong
+    result must not go unnoticed, e.g. once per decode step or per request."""
+    check(lib().vq_kivi_attend_status(), "attend_status")
+
+
+def quantize_status() -> None:
+    """The same check for the tensor-memory nearest-centroid search (``vq_vq_quantize_status``)."""
+    check(lib().vq_vq_quantize_status(), "quantize_status")
+
+
 def storage_bits(b: int) -> int:
     """Container width (1, 2, 4 or 8) used to store ``b``-bit codes."""
     if b < 1 or b > 8:
@@ -169,7 +200,6 @@ def kivi_quantize_into(x: torch.Tensor, axis: int, group_size: int, bits: int, *
     B, H, S, D = x.shape
     if S == 0:
         return
-    require_cuda(x, "kivi_quantize: x")
     row_bytes = D * sb // 8
     if codes.dtype != torch.uint8 or codes.shape[-1] != row_bytes or not codes.is_contiguous():
         raise ValueError(f"kivi_quantize: codes must be contiguous uint8 [B,H,cap,{row_bytes}]")
@@ -177,9 +207,15 @@ def kivi_quantize_into(x: torch.Tensor, axis: int, group_size: int, bits: int, *
         raise ValueError("kivi_quantize: scale/zero must be float32 tensors of equal shape")
     if not (scale.is_contiguous() and zero.is_contiguous()):
         raise ValueError("kivi_quantize: scale/zero must be contiguous")
+    if codes.ndim != 4 or scale.ndim != 4 or tuple(codes.shape[:2]) != (B, H) or tuple(scale.shape[:2]) != (B, H):
+        raise ValueError(f"kivi_quantize: codes and scale/zero must be 4D with leading [B={B}, H={H}] like x, got "
+                         f"codes {tuple(codes.shape)}, scale {tuple(scale.shape)}")
+    if codes.device != x.device or scale.device != x.device or zero.device != x.device:
+        raise ValueError("kivi_quantize: codes, scale and zero must live on x's device")
     cap = codes.shape[2]
     if tok_offset < 0 or tok_offset + S > cap:
         raise RuntimeError(f"kivi_quantize: rows [{tok_offset}, {tok_offset + S}) exceed capacity {cap}")
+    require_cuda(x, "kivi_quantize: x")
     xs, n_bh, stride = _slab_view(x, "x")
     if axis == -2:
         if tok_offset % group_size:
@@ -283,6 +319,7 @@ def _workspace(device: torch.device, nbytes: int) -> torch.Tensor:
 def kivi_decode_attend(q, k_codes, k_scale, k_zero, v_codes, v_scale, v_zero, group_size, scale, *,
                        store_bits=8, n_quant=None, k_res=None, v_res=None, n_res=None,
                        out=None, out_dtype=None, n_splits=0, variant=0, static_scratch=False,
+                       overlap_previous=False, gather=None, res_offset=0, causal=False,
                        _fn="kivi_decode_attend"):
     """Fused dequant + attention over packed codes and an optional unquantized tail.
 
@@ -295,11 +332,19 @@ def kivi_decode_attend(q, k_codes, k_scale, k_zero, v_codes, v_scale, v_zero, gr
     taken from torch's allocator, the split partials live in an 8 MiB array inside the
     library. For callers that must not allocate (pass ``out=`` too, so that nothing is
     allocated here either); such calls must not overlap on the GPU.
+
+    ``overlap_previous=True`` (``VQ_ATTEND_OVERLAP_PREVIOUS``) lets the kernel start while the
+    preceding work on the stream is still running; only pass it when every input of this call
+    was complete before that preceding work was launched (true for a decode loop over per-layer
+    caches whose queries do not come from the kernel right before). ``gather`` is a
+    ``_lib.PeerGather`` (see ``sharding.PeerExchange``): the output rows are also stored into
+    every rank's gathered tensor. ``causal=True`` (several query rows) applies the tail-aligned
+    causal mask: row ``r`` sees slots ``<= n_quant + n_res - S_q + r``. ``res_offset`` is the
+    first live row of ``k_res/v_res``.
     """
     fn = _fn
     if q.ndim != 4:
         raise ValueError(f"{fn}: q must be 4D, got {tuple(q.shape)}")
-    require_cuda(q, f"{fn}: q")
     B, H, S_q, D = q.shape
     if D > 256:
         raise ValueError(f"{fn}: D={D} must be <= 256")
@@ -322,6 +367,29 @@ def kivi_decode_attend(q, k_codes, k_scale, k_zero, v_codes, v_scale, v_zero, gr
             n_quant = cap
         if n_quant > cap or n_quant > v_codes.shape[2]:
             raise ValueError(f"{fn}: n_quant={n_quant} exceeds the code buffers")
+        if v_codes.shape[0] != B or v_codes.shape[3] != rb:
+            raise ValueError(f"{fn}: v_codes shape={tuple(v_codes.shape)} must have batch {B} and rows of {rb} bytes "
+                             "like k_codes")
+        g = int(group_size)
+        if g < 1:
+            raise ValueError(f"{fn}: group_size={group_size} must be >= 1")
+        gv = (D + g - 1) // g
+        for nm, t in (("k_scale", k_scale), ("k_zero", k_zero), ("v_scale", v_scale), ("v_zero", v_zero)):
+            if t is None or t.ndim != 4 or t.dtype != torch.float32 or tuple(t.shape[:2]) != (B, H_kv):
+                raise ValueError(f"{fn}: {nm} must be a float32 tensor [B={B}, H_kv={H_kv}, ...], got "
+                                 f"{None if t is None else (tuple(t.shape), t.dtype)}")
+        if k_scale.shape != k_zero.shape or k_scale.shape[3] != D or k_scale.shape[2] * g < n_quant:
+            raise ValueError(f"{fn}: k_scale/k_zero must be equal shapes [B,H_kv,>={-(-n_quant // g)},{D}], got "
+                             f"{tuple(k_scale.shape)} / {tuple(k_zero.shape)}")
+        if v_scale.shape != v_zero.shape or v_scale.shape[3] != gv or v_scale.shape[2] < n_quant:
+            raise ValueError(f"{fn}: v_scale/v_zero must be equal shapes [B,H_kv,>={n_quant},{gv}], got "
+                             f"{tuple(v_scale.shape)} / {tuple(v_zero.shape)}")
+        for nm, t in (("k_codes", k_codes), ("v_codes", v_codes), ("k_scale", k_scale), ("k_zero", k_zero),
+                      ("v_scale", v_scale), ("v_zero", v_zero)):
+            if t.device != q.device:
+                raise ValueError(f"{fn}: {nm} is on {t.device}, q on {q.device}")
+        if k_codes.dtype != torch.uint8 or v_codes.dtype != torch.uint8:
+            raise ValueError(f"{fn}: k_codes / v_codes must be uint8")
     else:
         if k_res is None:
             raise ValueError(f"{fn}: no keys given")
@@ -342,8 +410,14 @@ def kivi_decode_attend(q, k_codes, k_scale, k_zero, v_codes, v_scale, v_zero, gr
             raise ValueError(f"{fn}: k_res and v_res must match in shape and dtype")
         if not (k_res.is_contiguous() and v_res.is_contiguous()):
             raise ValueError(f"{fn}: k_res / v_res must be contiguous")
-        if n_res > k_res.shape[2]:
-            raise ValueError(f"{fn}: n_res={n_res} exceeds the residual buffers")
+        if res_offset < 0 or res_offset + n_res > k_res.shape[2]:
+            raise ValueError(f"{fn}: rows [{res_offset}, {res_offset + n_res}) exceed the residual buffers "
+                             f"({k_res.shape[2]} rows)")
+        if k_res.ndim != 4 or tuple(k_res.shape[:2]) != (B, H_kv) or k_res.shape[3] != D or k_res.device != q.device:
+            raise ValueError(f"{fn}: k_res / v_res must be [B={B}, H_kv={H_kv}, rows, D={D}] on q's device, got "
+                             f"{tuple(k_res.shape)} on {k_res.device}")
+        if k_res.dtype not in _FLOAT_DTYPES:
+            raise ValueError(f"{fn}: unsupported residual dtype {k_res.dtype}")
     else:
         n_res = 0
     if q.dtype not in _FLOAT_DTYPES:
@@ -352,11 +426,24 @@ def kivi_decode_attend(q, k_codes, k_scale, k_zero, v_codes, v_scale, v_zero, gr
     out_dtype = out_dtype or q.dtype
     if out is None:
         out = torch.empty((B, H, S_q, D), dtype=out_dtype, device=q.device)
+    else:
+        # a caller-owned output is written through its raw pointer: a wrong shape would be an
+        # out-of-bounds device write
+        if tuple(out.shape) != (B, H, S_q, D) or not out.is_contiguous() or out.device != q.device:
+            raise ValueError(f"{fn}: out must be a contiguous [{B}, {H}, {S_q}, {D}] tensor on {q.device}, got "
+                             f"{tuple(out.shape)} (contiguous={out.is_contiguous()}) on {out.device}")
+        if out.dtype not in _FLOAT_DTYPES:
+            raise ValueError(f"{fn}: unsupported out dtype {out.dtype}")
+    if gather is not None and not isinstance(gather, _lib.PeerGather):
+        raise ValueError(f"{fn}: gather must be a PeerGather structure (sharding.PeerExchange.layer)")
+    require_cuda(q, f"{fn}: q")  # (after the shape checks, so that those can be exercised without a GPU)
     a = KiviAttendArgs(
         q=q.data_ptr(), out=out.data_ptr(), q_dtype=dtype_code(q.dtype), out_dtype=dtype_code(out.dtype),
         B=B, H_q=H, H_kv=H_kv, S_q=S_q, D=D, store_bits=int(store_bits), group=int(group_size),
         n_quant=int(n_quant), n_res=int(n_res), scale=float(scale),
         n_splits=int(n_splits), variant=int(variant),
+        flags=(_lib.VQ_ATTEND_OVERLAP_PREVIOUS if overlap_previous else 0) | (_lib.VQ_ATTEND_CAUSAL if causal else 0),
+        gather=C.addressof(gather) if gather is not None else None,
     )
     if has_q:
         for t, nm in ((k_codes, "k_codes"), (v_codes, "v_codes"), (k_scale, "k_scale"), (k_zero, "k_zero"),
@@ -370,7 +457,8 @@ def kivi_decode_attend(q, k_codes, k_scale, k_zero, v_codes, v_scale, v_zero, gr
         a.v_scale, a.v_zero = v_scale.data_ptr(), v_zero.data_ptr()
         a.v_param_stride_bh = v_scale.shape[2] * v_scale.shape[3]
     if n_res:
-        a.k_res, a.v_res = k_res.data_ptr(), v_res.data_ptr()
+        row_bytes = D * k_res.element_size()
+        a.k_res, a.v_res = k_res.data_ptr() + res_offset * row_bytes, v_res.data_ptr() + res_offset * row_bytes
         a.res_dtype = dtype_code(k_res.dtype)
         a.res_stride_bh = k_res.shape[2] * k_res.shape[3]
     with torch.cuda.device(q.device):
@@ -544,7 +632,7 @@ def turboquant_bit_unpack(packed: torch.Tensor, N: int, b: int) -> torch.Tensor:
 
 
 __all__ = [
-    "kivi_available", "storage_bits", "kivi_group_quant_dequant", "kivi_quantize", "kivi_quantize_into",
+    "kivi_available", "tune", "attend_status", "quantize_status", "storage_bits", "kivi_group_quant_dequant", "kivi_quantize", "kivi_quantize_into",
     "scalar_decode_once", "kivi_decode_attend", "scalar_fused_decode_attend", "scalar_predecoded_attend",
     "scalar_fused_decode_attend_batched", "lse_merge",
     "turboquant_bit_pack", "turboquant_bit_unpack",
