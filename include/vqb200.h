@@ -199,6 +199,12 @@ typedef struct vq_kivi_attend_args {
  * fused_sdpa.py:200-299, applied to the KIVI store; S_q <= n_quant + n_res). General kernel. */
 #define VQ_ATTEND_CAUSAL 2
 int64_t vq_kivi_attend_workspace_bytes(const vq_kivi_attend_args *args);
+/* Context splits vq_kivi_decode_attend would use for `args` (its n_splits honoured when > 0). A
+ * caller that folds several layers into the batch axis passes the count of ONE layer as
+ * n_splits, so that every layer is summed in exactly the order of a per-layer call (the
+ * reference pins its batched kernel to its per-layer kernel bit for bit:
+ * tests/metal/test_scalar_attend.py:660-707). 0 for unusable sizes. */
+int32_t vq_kivi_attend_splits(const vq_kivi_attend_args *args);
 int32_t vq_kivi_decode_attend(const vq_kivi_attend_args *args, void *stream);
 /* Synchronises the device, then reports (and clears) whether any earlier
  * vq_kivi_decode_attend, vq_rabitq_decode_attend or vq_peer_gather_wait kernel abandoned a

@@ -137,6 +137,7 @@ SIGNATURES = {
     "vq_vq_encode_decode_keys": (C.c_int32, [C.POINTER(VqEncodeArgs), C.c_void_p]),
     "vq_vq_encode_decode_values": (C.c_int32, [C.POINTER(VqEncodeArgs), C.c_void_p]),
     "vq_kivi_attend_workspace_bytes": (C.c_int64, [C.POINTER(KiviAttendArgs)]),
+    "vq_kivi_attend_splits": (C.c_int32, [C.POINTER(KiviAttendArgs)]),
     "vq_kivi_decode_attend": (C.c_int32, [C.POINTER(KiviAttendArgs), C.c_void_p]),
     "vq_kivi_attend_status": (C.c_int32, []),
     "vq_kivi_decode_attend_static": (C.c_int32, [C.POINTER(KiviAttendArgs), C.c_void_p]),

@@ -271,10 +271,21 @@ extern "C" int64_t vq_kivi_attend_workspace_bytes(const vq_kivi_attend_args *arg
     DeviceInfo di;
     if (device_info(&di) != VQ_OK) { di.sm_count = 148; di.smem_optin = 227 * 1024; }
     const int64_t rows = (int64_t)a.B * a.H_q * a.S_q;
-    int64_t splits = general_splits(a, di.sm_count);
+    int64_t need = rows * general_splits(a, di.sm_count) * ((int64_t)a.D + 2) * (int64_t)sizeof(float);
     if (a.variant != 1 && a.H_kv >= 1 && a.H_q % a.H_kv == 0 && kivi_attend_mma_supported(a) == nullptr)
-        splits = std::max<int64_t>(splits, kivi_attend_mma_splits(a, di) + kivi_attend_mma_tail_parts(a));
-    return rows * splits * ((int64_t)a.D + 2) * (int64_t)sizeof(float) + 256;
+        need = std::max<int64_t>(need, kivi_attend_mma_workspace(a, kivi_attend_mma_splits(a, di)));
+    return need + 256;
+}
+
+extern "C" int32_t vq_kivi_attend_splits(const vq_kivi_attend_args *args) {
+    using namespace vq;
+    if (!args) return 0;
+    const vq_kivi_attend_args &a = *args;
+    if (a.B < 1 || a.H_q < 1 || a.H_kv < 1 || a.S_q < 1 || a.D < 1 || a.H_q % a.H_kv) return 0;
+    DeviceInfo di;
+    if (device_info(&di) != VQ_OK) { di.sm_count = 148; di.smem_optin = 227 * 1024; }
+    if (a.variant != 1 && kivi_attend_mma_supported(a) == nullptr) return kivi_attend_mma_splits(a, di);
+    return general_splits(a, di.sm_count);
 }
 
 extern "C" int32_t vq_kivi_attend_status(void) {

@@ -7,8 +7,8 @@ namespace vq {
 const char *kivi_attend_mma_supported(const vq_kivi_attend_args &a);
 // Context splits the tensor-core kernel will use for `a` (for workspace sizing).
 int kivi_attend_mma_splits(const vq_kivi_attend_args &a, const DeviceInfo &di);
-// Extra partials the tensor-core kernel writes for the unquantized tail of `a`.
-int kivi_attend_mma_tail_parts(const vq_kivi_attend_args &a);
+// Workspace bytes of the tensor-core kernel for `a` with `n_splits` context splits.
+int64_t kivi_attend_mma_workspace(const vq_kivi_attend_args &a, int n_splits);
 // Reads and clears the device-side "a bounded wait gave up" flag (synchronises the device).
 int32_t kivi_attend_mma_take_timeout(int *flag);
 // The same flag of the staged RaBitQ attend kernel (coded_attend.cu).

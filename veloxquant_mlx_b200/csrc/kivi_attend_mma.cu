@@ -27,12 +27,17 @@
 // transposing ldmatrix reads of V (8 token rows, one 16-byte segment each) then fall on 8
 // different bank groups instead of 2 (rows are only 64 or 32 bytes apart), which took a
 // quarter of the kernel's shared-memory wavefronts away.
-// The context is split across CTAs; each writes an unnormalised partial (m, l, o) and a
-// small kernel merges them. The unquantized tail adds a few more partials from a CUDA-core
-// kernel that runs while the main grid drains (programmatic dependent launch).
+// The context is split across CTAs; each writes an unnormalised partial (m, l, o) and takes a
+// ticket; the CTA that takes a unit's last ticket merges the unit's partials and writes the
+// output rows (and, in a sharded run, publishes them to the peers). The unquantized tail
+// (residual window) is spread over all warps of all of a unit's CTAs, a few rows each, after
+// their packed groups. One launch per call: nothing of a call sits resident and blocked, so a
+// call launched with VQ_ATTEND_OVERLAP_PREVIOUS streams in behind the previous one without
+// displacing its CTAs (this kernel takes the whole register file at 4 CTAs per SM).
 #include <cuda.h>
 
 #include <algorithm>
+#include <atomic>
 #include <cmath>
 #include <cstdlib>
 #include <cstring>
@@ -46,7 +51,6 @@ namespace {
 constexpr int kD = 128;
 constexpr int kGroup = 32;     // tokens per pipeline stage of one warp = one K scale group
 constexpr int kWarps = 4;
-constexpr int kMaxStages = 4;
 constexpr int kMaxHeads = 8;   // query heads per kv head
 constexpr int kChunkHeads = 4; // query heads per CTA (hi/lo halves fill the 8 MMA columns)
 constexpr uint32_t kSpinLimit = 1u << 18;
@@ -203,120 +207,50 @@ struct Params {
     vq_kivi_attend_args a;
     int hpk;
     int n_chunks;       // ceil(hpk / 4)
-    int n_splits;       // quantized-context splits
-    int n_tail;         // CTAs that attend the unquantized tail (0 if there is none)
-    int n_parts;        // n_splits + n_tail
+    int n_splits;       // context splits = partial records per (batch, kv head, query head)
     int groups_total;     // n_quant / 32
     int groups_per_warp;  // consecutive groups owned by one warp
-    float *part_o;      // [B*H_kv][n_parts][hpk][128]
-    float *part_ml;     // [B*H_kv][n_parts][hpk][2]
+    float *part_o;      // [B*H_kv][n_splits][hpk][128]
+    float *part_ml;     // [B*H_kv][n_splits][hpk][2]
+    unsigned long long *tickets;  // [B*H_kv][n_chunks]: (epoch << 32) | arrivals of the current call
+    uint32_t epoch;     // distinguishes this call's tickets from whatever the workspace held before
     int wait_test;      // self-test: every warp also waits (briefly) on a barrier that nothing arms
     vq_peer_gather gather;  // world == 0: the output rows are not published to peers
 };
 
-// ---- tail (unquantized tokens): CUDA cores, n_tail CTAs per (batch, kv head) ---------------
-// A kernel of its own, launched after the main kernel as its programmatic dependent: its CTAs
-// become resident once every main CTA has started, i.e. they run on the SMs that the draining
-// main grid leaves idle, and they need nothing the main grid writes. Before it writes its
-// partials, each CTA waits for the main grid (griddepcontrol.wait), so that the merge kernel,
-// which waits for THIS grid, also sees the main grid's partials complete. Tail CTA `ti` takes an equal slice of the
-// tail tokens; inside it each warp takes every fourth token, four tokens' rows in flight.
-template <typename T>
-__device__ __forceinline__ void load_row4(const T *p, float (&d)[4]) {
-    if constexpr (sizeof(T) == 2) {
-        const uint2 raw = *reinterpret_cast<const uint2 *>(p);
-        const T *h = reinterpret_cast<const T *>(&raw);
-#pragma unroll
-        for (int i = 0; i < 4; ++i) d[i] = to_f32<T>(h[i]);
-    } else {
-        const float4 v = *reinterpret_cast<const float4 *>(p);
+// ---- helpers for the unquantized tail ----------------------------------------------------------
+// Four consecutive elements of a residual row (dtype known at run time) as float32.
+__device__ __forceinline__ void load_res4(const void *base, int32_t dt, int64_t elem, float (&d)[4]) {
+    if (dt == VQ_F32) {
+        const float4 v = *reinterpret_cast<const float4 *>(reinterpret_cast<const float *>(base) + elem);
         d[0] = v.x; d[1] = v.y; d[2] = v.z; d[3] = v.w;
+    } else {
+        const uint2 raw = *reinterpret_cast<const uint2 *>(reinterpret_cast<const uint16_t *>(base) + elem);
+        if (dt == VQ_F16) {
+            const float2 lo = __half22float2(*reinterpret_cast<const __half2 *>(&raw.x));
+            const float2 hi = __half22float2(*reinterpret_cast<const __half2 *>(&raw.y));
+            d[0] = lo.x; d[1] = lo.y; d[2] = hi.x; d[3] = hi.y;
+        } else {
+            d[0] = __uint_as_float(raw.x << 16); d[1] = __uint_as_float(raw.x & 0xffff0000u);
+            d[2] = __uint_as_float(raw.y << 16); d[3] = __uint_as_float(raw.y & 0xffff0000u);
+        }
     }
 }
-
-template <typename T>
-__global__ void __launch_bounds__(kWarps * 32) kivi_attend_tail_kernel(const __grid_constant__ Params p) {
-    constexpr int kAheadTok = 4;
-    __shared__ __align__(16) float sh_q[kMaxHeads * kD];
-    __shared__ __align__(16) float sh_o[kWarps * kMaxHeads * kD];
-    __shared__ float sh_m[kWarps * kMaxHeads], sh_l[kWarps * kMaxHeads];
-    const vq_kivi_attend_args &a = p.a;
-    const int ti = blockIdx.x, hkv = blockIdx.y, b = blockIdx.z;
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int hpk = p.hpk;
-    const int64_t bh = (int64_t)b * a.H_kv + hkv;
-    const float sc = a.scale * 1.4426950408889634f;
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");  // the merge kernel may become resident
-    for (int i = threadIdx.x; i < hpk * kD; i += blockDim.x) {
-        const int hp = i / kD, d = i % kD;
-        sh_q[i] = load_as_f32(a.q, a.q_dtype, ((int64_t)b * a.H_q + hkv * hpk + hp) * kD + d) * sc;
-    }
-    __syncthreads();
-    float m[kMaxHeads], l[kMaxHeads], o[kMaxHeads][4];
-#pragma unroll
-    for (int hp = 0; hp < kMaxHeads; ++hp) {
-        m[hp] = -INFINITY;
-        l[hp] = 0.f;
-        o[hp][0] = o[hp][1] = o[hp][2] = o[hp][3] = 0.f;
-    }
-    const int per_cta = (a.n_res + p.n_tail - 1) / p.n_tail;
-    const int t_begin = ti * per_cta, t_end = min(a.n_res, t_begin + per_cta);
-    const T *kr = reinterpret_cast<const T *>(a.k_res) + bh * a.res_stride_bh + lane * 4;
-    const T *vr = reinterpret_cast<const T *>(a.v_res) + bh * a.res_stride_bh + lane * 4;
-    for (int t0 = t_begin + warp; t0 < t_end; t0 += kWarps * kAheadTok) {
-        float kd[kAheadTok][4], vd[kAheadTok][4];
-#pragma unroll
-        for (int j = 0; j < kAheadTok; ++j) {
-            const int t = min(t0 + j * kWarps, t_end - 1);  // (a repeated row past the end is skipped below)
-            load_row4<T>(kr + (int64_t)t * kD, kd[j]);
-            load_row4<T>(vr + (int64_t)t * kD, vd[j]);
+// Four consecutive output elements of a row, in the output dtype.
+__device__ __forceinline__ void store_out4(void *base, int32_t dt, int64_t elem, const float (&v)[4]) {
+    if (dt == VQ_F32) {
+        *reinterpret_cast<float4 *>(reinterpret_cast<float *>(base) + elem) = make_float4(v[0], v[1], v[2], v[3]);
+    } else {
+        uint2 raw;
+        if (dt == VQ_F16) {
+            raw.x = pack_h2(v[0], v[1]);
+            raw.y = pack_h2(v[2], v[3]);
+        } else {
+            const __nv_bfloat162 lo = __floats2bfloat162_rn(v[0], v[1]), hi = __floats2bfloat162_rn(v[2], v[3]);
+            raw.x = *reinterpret_cast<const uint32_t *>(&lo);
+            raw.y = *reinterpret_cast<const uint32_t *>(&hi);
         }
-#pragma unroll
-        for (int j = 0; j < kAheadTok; ++j) {
-            if (t0 + j * kWarps >= t_end) break;
-#pragma unroll
-            for (int hp = 0; hp < kMaxHeads; ++hp) {
-                if (hp < hpk) {
-                    const float4 qv = *reinterpret_cast<const float4 *>(sh_q + hp * kD + lane * 4);
-                    const float sv = warp_sum(qv.x * kd[j][0] + qv.y * kd[j][1] + qv.z * kd[j][2] + qv.w * kd[j][3]);
-                    const float mn = fmaxf(m[hp], sv);
-                    const float f = exp2f(m[hp] - mn), w = exp2f(sv - mn);
-                    l[hp] = l[hp] * f + w;
-                    m[hp] = mn;
-#pragma unroll
-                    for (int i = 0; i < 4; ++i) o[hp][i] = o[hp][i] * f + w * vd[j][i];
-                }
-            }
-        }
-    }
-#pragma unroll
-    for (int hp = 0; hp < kMaxHeads; ++hp) {
-        if (hp < hpk) {
-            if (lane == 0) { sh_m[warp * kMaxHeads + hp] = m[hp]; sh_l[warp * kMaxHeads + hp] = l[hp]; }
-#pragma unroll
-            for (int i = 0; i < 4; ++i) sh_o[(warp * kMaxHeads + hp) * kD + lane * 4 + i] = o[hp][i];
-        }
-    }
-    __syncthreads();
-    // The partials may share their buffer with the previous call on the stream, and the merge
-    // kernel, which waits for THIS grid only, must find the main grid's partials complete too:
-    // wait for the main grid (and, through its own wait, for everything before it) here.
-    asm volatile("griddepcontrol.wait;" ::: "memory");
-    const int part = p.n_splits + ti;
-    for (int i = threadIdx.x; i < hpk * kD; i += blockDim.x) {
-        const int hp = i / kD, d = i % kD;
-        float gm = -INFINITY;
-        for (int w = 0; w < kWarps; ++w) gm = fmaxf(gm, sh_m[w * kMaxHeads + hp]);
-        float gl = 0.f, acc = 0.f;
-        for (int w = 0; w < kWarps; ++w) {
-            const float mw = sh_m[w * kMaxHeads + hp];
-            const float f = (mw == -INFINITY) ? 0.f : exp2f(mw - gm);
-            gl += sh_l[w * kMaxHeads + hp] * f;
-            acc += sh_o[(w * kMaxHeads + hp) * kD + d] * f;
-        }
-        const int64_t rec = (bh * p.n_parts + part) * hpk + hp;
-        p.part_o[rec * kD + d] = acc;
-        if (d == 0) { p.part_ml[rec * 2] = gm; p.part_ml[rec * 2 + 1] = gl; }
+        *reinterpret_cast<uint2 *>(reinterpret_cast<uint16_t *>(base) + elem) = raw;
     }
 }
 
@@ -389,6 +323,14 @@ kivi_attend_mma_kernel(const __grid_constant__ Params p) {
     __syncthreads();
     if (lane == 0) {
         for (int i = 0; i < STAGES - 1 && i < n_local; ++i) issue_group(i);
+    }
+    // This warp's first residual row is read only after its packed groups: ask for its lines now
+    // (4 lanes: the two 128-byte halves of the K row and of the V row at 16-bit width).
+    if (lane < 4 && split * kWarps + warp < a.n_res) {
+        const size_t es = a.res_dtype == VQ_F32 ? 4 : 2;
+        const uint8_t *base = static_cast<const uint8_t *>((lane & 2) ? a.v_res : a.k_res) +
+                              ((size_t)bh * a.res_stride_bh + (size_t)(split * kWarps + warp) * kD) * es;
+        asm volatile("prefetch.global.L2 [%0];" ::"l"(base + (lane & 1) * (kD * es / 2)));
     }
 
     // This lane's 16 query channels (head hd) are channels 32c + 16*half_id + [0, 16), handled
@@ -619,7 +561,47 @@ kivi_attend_mma_kernel(const __grid_constant__ Params p) {
             for (int i = 0; i < 64; ++i) __nanosleep(1000);
     }
 
-    // ---- merge the four warps, write this split's partial -----------------------------------
+    // ---- the unquantized tail: residual row r belongs to warp r mod (splits * 4) of the unit ----
+    // CUDA cores, a lane holds 4 consecutive channels of the row; heads of this CTA's chunk only.
+    float tm[kChunkHeads], tl[kChunkHeads], to[kChunkHeads][4];
+#pragma unroll
+    for (int hp = 0; hp < kChunkHeads; ++hp) {
+        tm[hp] = -INFINITY;
+        tl[hp] = 0.f;
+        to[hp][0] = to[hp][1] = to[hp][2] = to[hp][3] = 0.f;
+    }
+    {
+        int r = split * kWarps + warp;
+        if (r < a.n_res) {
+            const int r_stride = p.n_splits * kWarps;
+            float qt[kChunkHeads][4];
+#pragma unroll
+            for (int hp = 0; hp < kChunkHeads; ++hp) {
+                const bool live = h0 + hp < hpk;
+                const int64_t qb = ((int64_t)b * a.H_q + hkv * hpk + h0 + hp) * kD + 4 * lane;
+#pragma unroll
+                for (int i = 0; i < 4; ++i) qt[hp][i] = live ? load_as_f32(a.q, a.q_dtype, qb + i) * sc : 0.f;
+            }
+            const int64_t rbase = bh * a.res_stride_bh + 4 * lane;
+            for (; r < a.n_res; r += r_stride) {
+                float kd[4], vd[4];
+                load_res4(a.k_res, a.res_dtype, rbase + (int64_t)r * kD, kd);
+                load_res4(a.v_res, a.res_dtype, rbase + (int64_t)r * kD, vd);
+#pragma unroll
+                for (int hp = 0; hp < kChunkHeads; ++hp) {
+                    const float sv = warp_sum(qt[hp][0] * kd[0] + qt[hp][1] * kd[1] + qt[hp][2] * kd[2] + qt[hp][3] * kd[3]);
+                    const float mn = fmaxf(tm[hp], sv);
+                    const float f = fast_exp2(tm[hp] - mn), wgt = fast_exp2(sv - mn);
+                    tl[hp] = tl[hp] * f + wgt;
+                    tm[hp] = mn;
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) to[hp][i] = to[hp][i] * f + wgt * vd[i];
+                }
+            }
+        }
+    }
+
+    // ---- merge the four warps (packed part and tail part of each), write this split's partial ----
     l_run += __shfl_xor_sync(0xffffffffu, l_run, 4);
     l_run += __shfl_xor_sync(0xffffffffu, l_run, 8);
     l_run += __shfl_xor_sync(0xffffffffu, l_run, 16);
@@ -632,10 +614,11 @@ kivi_attend_mma_kernel(const __grid_constant__ Params p) {
         oz[j] = z;
     }
     __syncthreads();  // all stages are drained: reuse them for the reduction
-    float *red_o = reinterpret_cast<float *>(stages);               // [4 warps][4 heads][128]
-    float *red_z = red_o + kWarps * kChunkHeads * kD;               // [4][4][4 groups]
-    float *red_m = red_z + kWarps * kChunkHeads * 4;                // [4][4]
-    float *red_l = red_m + kWarps * kChunkHeads;                    // [4][4]
+    constexpr int kSlots = 2 * kWarps;  // per warp: its packed groups, its tail rows
+    float *red_o = reinterpret_cast<float *>(stages);               // [8 slots][4 heads][128]
+    float *red_z = red_o + kSlots * kChunkHeads * kD;               // [8][4][4 groups]
+    float *red_m = red_z + kSlots * kChunkHeads * 4;                // [8][4]
+    float *red_l = red_m + kSlots * kChunkHeads;                    // [8][4]
     // channel of accumulator rows g / g+8 of MMA i
     auto chan = [&](int i) {
         const int seg = i / (C::CU / 2), u = i % (C::CU / 2);
@@ -660,127 +643,109 @@ kivi_attend_mma_kernel(const __grid_constant__ Params p) {
 #pragma unroll
             for (int j = 0; j < 4; ++j) red_z[(warp * kChunkHeads + c) * 4 + j] = oz[j];
         }
+        // the tail slot of this warp
+#pragma unroll
+        for (int hp = 0; hp < kChunkHeads; ++hp) {
+            const int slot = (kWarps + warp) * kChunkHeads + hp;
+            *reinterpret_cast<float4 *>(red_o + slot * kD + 4 * lane) = make_float4(to[hp][0], to[hp][1], to[hp][2], to[hp][3]);
+            if (lane == 0) { red_m[slot] = tm[hp]; red_l[slot] = tl[hp]; }
+            if (lane < 4) red_z[slot * 4 + lane] = 0.f;
+        }
     }
     __syncthreads();
     // Launched as a programmatic dependent (VQ_ATTEND_OVERLAP_PREVIOUS), this grid runs beside
-    // the end of the previous call, which may still be reading partials from the same buffer:
-    // everything above touched only this call's inputs; the writes below wait for the work
-    // before this grid to finish. (Returns at once after a plain launch.)
+    // the end of the previous call, whose last CTAs may still be reading partials and tickets in
+    // the same buffer: everything above touched only this call's inputs; the writes below wait
+    // for the work before this grid to finish. (Returns at once after a plain launch.)
     asm volatile("griddepcontrol.wait;" ::: "memory");
     const int n_heads = min(kChunkHeads, hpk - h0);
     for (int i = tid; i < n_heads * kD; i += blockDim.x) {
         const int hp = i / kD, d = i % kD;
         float gm = -INFINITY;
 #pragma unroll
-        for (int w = 0; w < kWarps; ++w) gm = fmaxf(gm, red_m[w * kChunkHeads + hp]);
+        for (int w = 0; w < kSlots; ++w) gm = fmaxf(gm, red_m[w * kChunkHeads + hp]);
         float gl = 0.f, acc = 0.f;
 #pragma unroll
-        for (int w = 0; w < kWarps; ++w) {
+        for (int w = 0; w < kSlots; ++w) {
             const float mw = red_m[w * kChunkHeads + hp];
             const float f = (mw == -INFINITY) ? 0.f : exp2f(mw - gm);
             gl += red_l[w * kChunkHeads + hp] * f;
             acc += (red_o[(w * kChunkHeads + hp) * kD + d] + red_z[(w * kChunkHeads + hp) * 4 + (d >> 5)]) * f;
         }
-        const int64_t rec = (bh * p.n_parts + split) * hpk + h0 + hp;
+        const int64_t rec = (bh * p.n_splits + split) * hpk + h0 + hp;
         p.part_o[rec * kD + d] = acc;
         if (d == 0) { p.part_ml[rec * 2] = gm; p.part_ml[rec * 2 + 1] = gl; }
     }
-}
 
-// One CTA per (batch, query head): combine the partials (log2-domain maxima). The split
-// weights are computed once into shared memory; the kernel is latency-bound, so the loads of
-// the (max, sum) pairs and of the first output partials are all issued up front.
-constexpr int kMergeMaxParts = 520;
-__global__ void __launch_bounds__(kD) kivi_attend_mma_merge_kernel(const __grid_constant__ Params p) {
-    __shared__ float sh_w[kMergeMaxParts];
-    __shared__ float sh_red[kD / 32];
-    __shared__ __align__(16) uint8_t sh_row[kD * 4];
-    const vq_kivi_attend_args &a = p.a;
-    // the next call's kernel, if it asked to overlap, may become resident from here on
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-    const int hp = blockIdx.x % p.hpk;
-    const int64_t bh = blockIdx.x / p.hpk;
-    const int b = (int)(bh / a.H_kv), hkv = (int)(bh % a.H_kv);
-    const int d = threadIdx.x, lane = d & 31, warp = d >> 5;
-    const int64_t rec0 = bh * p.n_parts * p.hpk + hp;  // record of part s: rec0 + s * hpk
-    // launched as a programmatic dependent of the tail (or main) kernel: the partials are complete
-    // and visible only after this wait
-    asm volatile("griddepcontrol.wait;" ::: "memory");
-    // One round trip to memory instead of three: every thread reads the (max, sum) pairs of its
-    // parts once, and the first 16 output partials are requested before the weights are known.
-    constexpr int kMl = (kMergeMaxParts + kD - 1) / kD;
-    constexpr int kAheadParts = 16;
-    float2 ml[kMl];
-#pragma unroll
-    for (int i = 0; i < kMl; ++i) {
-        const int s = d + i * kD;
-        ml[i] = s < p.n_parts ? *reinterpret_cast<const float2 *>(p.part_ml + (rec0 + (int64_t)s * p.hpk) * 2)
-                              : make_float2(-INFINITY, 0.f);
+    // ---- ticket: the CTA that arrives last for this (batch, kv head, head chunk) merges ----------
+    // The ticket word is (epoch << 32) | arrivals. Whatever the workspace held before this call has
+    // another epoch in its high half and counts as zero arrivals; the merging CTA leaves 0 behind
+    // (epoch 0 is never issued), so a captured launch can be replayed with the same epoch.
+    int *sh_last = reinterpret_cast<int *>(bars) + 48;  // (behind the barriers, inside their 256 bytes)
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) {
+        unsigned long long *t = p.tickets + bh * p.n_chunks + (h0 / kChunkHeads);
+        unsigned long long cur = *reinterpret_cast<volatile unsigned long long *>(t), want;
+        for (;;) {
+            want = ((uint32_t)(cur >> 32) == p.epoch) ? cur + 1ull : (((unsigned long long)p.epoch << 32) | 1ull);
+            const unsigned long long seen = atomicCAS(t, cur, want);
+            if (seen == cur) break;
+            cur = seen;  // (another CTA of this unit got in between: at most n_splits - 1 retries)
+        }
+        *sh_last = ((uint32_t)want == (uint32_t)p.n_splits);
     }
-    float v[kAheadParts];
-#pragma unroll
-    for (int j = 0; j < kAheadParts; ++j) v[j] = j < p.n_parts ? p.part_o[(rec0 + (int64_t)j * p.hpk) * kD + d] : 0.f;
-    // global maximum over parts
-    float m = -INFINITY;
-#pragma unroll
-    for (int i = 0; i < kMl; ++i) m = fmaxf(m, ml[i].x);
-    m = warp_max(m);
-    if (lane == 0) sh_red[warp] = m;
     __syncthreads();
-    const float gm = fmaxf(fmaxf(sh_red[0], sh_red[1]), fmaxf(sh_red[2], sh_red[3]));
-    __syncthreads();
-    // per-part weight, and the denominator
-    float l = 0.f;
+    if (!*sh_last) return;
+    __threadfence();
+    // Warp w merges query head h0 + w: lane holds channels 4*lane .. 4*lane+3; the (max, sum) pair
+    // of a part is one broadcast load. Loads bypass L1 (the partials were written by other SMs).
+    if (warp < n_heads) {
+        const int64_t rec0 = bh * p.n_splits * hpk + h0 + warp;  // record of part s: rec0 + s * hpk
+        float m = -INFINITY, l = 0.f, acc[4] = {0.f, 0.f, 0.f, 0.f};
+        constexpr int kBatch = 8;
+        for (int s0 = 0; s0 < p.n_splits; s0 += kBatch) {
+            float2 ml[kBatch];
+            float4 po[kBatch];
 #pragma unroll
-    for (int i = 0; i < kMl; ++i) {
-        const int s = d + i * kD;
-        if (s < p.n_parts) {
-            const float w = (ml[i].x == -INFINITY) ? 0.f : exp2f(ml[i].x - gm);
-            sh_w[s] = w;
-            l += w * ml[i].y;
+            for (int j = 0; j < kBatch; ++j) {
+                const int s = min(s0 + j, p.n_splits - 1);
+                const int64_t rec = rec0 + (int64_t)s * hpk;
+                ml[j] = __ldcg(reinterpret_cast<const float2 *>(p.part_ml + rec * 2));
+                po[j] = __ldcg(reinterpret_cast<const float4 *>(p.part_o + rec * kD + 4 * lane));
+            }
+#pragma unroll
+            for (int j = 0; j < kBatch; ++j) {
+                if (s0 + j < p.n_splits && ml[j].x != -INFINITY) {
+                    const float mn = fmaxf(m, ml[j].x);
+                    const float f = exp2f(m - mn), wgt = exp2f(ml[j].x - mn);
+                    l = l * f + ml[j].y * wgt;
+                    acc[0] = acc[0] * f + po[j].x * wgt; acc[1] = acc[1] * f + po[j].y * wgt;
+                    acc[2] = acc[2] * f + po[j].z * wgt; acc[3] = acc[3] * f + po[j].w * wgt;
+                    m = mn;
+                }
+            }
+        }
+        const float inv = 1.f / l;
+        const float res[4] = {acc[0] * inv, acc[1] * inv, acc[2] * inv, acc[3] * inv};
+        const int64_t row = (int64_t)b * a.H_q + hkv * hpk + h0 + warp;
+        store_out4(a.out, a.out_dtype, row * kD + 4 * lane, res);
+        if (p.gather.world > 0) {
+            // publish the row to every rank's gathered tensor (plain stores to peer-mapped memory)
+            const int64_t grow = p.gather.row_offset + row;
+            for (int pr = 0; pr < p.gather.world; ++pr) store_out4(p.gather.out[pr], a.out_dtype, grow * kD + 4 * lane, res);
         }
     }
-    l = warp_sum(l);
-    if (lane == 0) sh_red[warp] = l;
-    __syncthreads();
-    const float gl = sh_red[0] + sh_red[1] + sh_red[2] + sh_red[3];
-    float acc = 0.f;
-#pragma unroll
-    for (int j = 0; j < kAheadParts; ++j)
-        if (j < p.n_parts) acc = fmaf(v[j], sh_w[j], acc);
-    int s = kAheadParts;
-    for (; s + 8 <= p.n_parts; s += 8) {
-        float u[8];
-#pragma unroll
-        for (int j = 0; j < 8; ++j) u[j] = p.part_o[(rec0 + (int64_t)(s + j) * p.hpk) * kD + d];
-#pragma unroll
-        for (int j = 0; j < 8; ++j) acc = fmaf(u[j], sh_w[s + j], acc);
-    }
-    for (; s < p.n_parts; ++s) acc = fmaf(p.part_o[(rec0 + (int64_t)s * p.hpk) * kD + d], sh_w[s], acc);
-    const int64_t row = (int64_t)b * a.H_q + hkv * p.hpk + hp;
-    const float res = acc / gl;
-    store_from_f32(a.out, a.out_dtype, row * kD + d, res);
     if (p.gather.world > 0) {
-        // Publish the row to every rank's gathered tensor: the row is staged in shared memory in
-        // the output dtype and leaves as 16-byte stores (one per 16 threads and rank).
-        const vq_peer_gather &pg = p.gather;
-        store_from_f32(sh_row, a.out_dtype, d, res);
-        __syncthreads();
-        const int row_bytes = kD * (a.out_dtype == VQ_F32 ? 4 : 2);
-        const int segs = row_bytes / 16;
-        const int64_t grow = pg.row_offset + row;
-        for (int i = d; i < pg.world * segs; i += kD) {
-            const int pr = i / segs, sg = i % segs;
-            uint4 *dst = reinterpret_cast<uint4 *>(static_cast<uint8_t *>(pg.out[pr]) + grow * row_bytes) + sg;
-            *dst = reinterpret_cast<const uint4 *>(sh_row)[sg];
-        }
-        // Arrival: each storing thread fences system-wide, the CTA counts itself in; the CTA that
+        // Arrival: every storing thread fences system-wide, the CTA counts itself in; the CTA that
         // completes the count opens the next round and raises this rank's word on every rank.
+        const vq_peer_gather &pg = p.gather;
         __threadfence_system();
         __syncthreads();
-        if (d == 0) {
+        if (tid == 0) {
+            const unsigned total = gridDim.y * gridDim.z * (unsigned)p.n_chunks;
             const unsigned prev = atomicAdd(&pg.state[0], 1u);
-            if (prev == gridDim.x - 1) {
+            if (prev == total - 1) {
                 pg.state[0] = 0u;
                 const unsigned round = pg.state[1] + 1u;
                 pg.state[1] = round;
@@ -790,7 +755,10 @@ __global__ void __launch_bounds__(kD) kivi_attend_mma_merge_kernel(const __grid_
             }
         }
     }
+    if (tid == 0) p.tickets[bh * p.n_chunks + (h0 / kChunkHeads)] = 0ull;
 }
+
+constexpr int kMaxSplits = 512;
 
 // Pipeline depth and waves-per-launch are tunables (vq_tune: VQ_KNOB_ATTEND_STAGES = 2..4,
 // VQ_KNOB_ATTEND_WAVES = 1..32).
@@ -801,37 +769,33 @@ int smem_for(int bits, int stages) {
     return bits == 4 ? Cfg<4>::smem_bytes(stages) : Cfg<2>::smem_bytes(stages);
 }
 
+// Context splits per (batch, kv head, head chunk). A CTA has fixed costs (pipeline fill, its few
+// residual rows, the partial write and the ticket), so it wants a long run of groups; the GPU
+// wants enough CTAs. Measured on B200 (32K context, 8 kv heads, 4 query heads each):
+//   plain launches (a call runs alone): about 32 groups per warp, and at least ~256 CTAs per
+//     launch -- batch 16: 8 splits, batch 8 and 4: 9, batch 2: 16, batch 1: 20;
+//   calls that overlap their predecessor: CTAs of two or three calls are resident together, so a
+//     launch need not fill the GPU by itself and longer CTAs win -- about 64 groups per warp
+//     (32 when there are only a few units): batch 16: 3-4 splits, batch 8: 2-4, batch 4: 2-5,
+//     batch 2: 5-9, batch 1: 5-8.
 int choose_splits(const vq_kivi_attend_args &a, const DeviceInfo &di) {
+    (void)di;
     const int tiles = (int)ceil_div(a.n_quant, kGroup * kWarps);  // CTA-sized pieces of the context
     if (tiles <= 1) return std::max(tiles, 0);
-    if (a.n_splits > 0) return std::min(std::min(a.n_splits, tiles), kMergeMaxParts - 8);
-    const int smem = smem_for(a.store_bits, tuned_stages());
-    // resident CTAs per SM: shared memory, and 4 by registers (128 threads x <= 128 regs)
-    const int occ = std::max(1, std::min(4, (int)(di.smem_optin / (smem + 1024))));
+    if (a.n_splits > 0) return std::min(std::min(a.n_splits, tiles), kMaxSplits);
     const int n_chunks = (int)ceil_div(a.H_q / a.H_kv, kChunkHeads);
     const int64_t units = (int64_t)a.B * a.H_kv * n_chunks;
-    const int64_t slots = (int64_t)di.sm_count * occ;
-    // Aim for several waves of CTAs so the last, partly filled wave costs little, but keep
-    // at least 4 tiles per CTA so pipeline fill and the partial write stay amortised.
-    int64_t want = std::max<int64_t>(1, (slots * tuned_waves()) / units);
-    const int64_t cap = std::min<int64_t>(std::max(1, tiles / 4), kMergeMaxParts - 8);
-    want = std::min<int64_t>(want, cap);
-    // With more than a wave of CTAs, what is lost is the partly filled last wave: among the
-    // counts near `want` take the one that fills its last wave best (a tail CTA runs about half
-    // as long as a main one; a slight preference for fewer, longer CTAs). Measured at batch 16,
-    // 8 kv heads, 32K context: 9 splits (2.05 waves) 194 us, 8 or 12..13 splits 188 us.
-    if (units * want >= slots) {
-        const double tails = 0.0;  // the tail runs as a kernel of its own
-        double best_score = -1.0;
-        int64_t best = want;
-        for (int64_t s = std::max<int64_t>(2, want - 2); s <= std::min<int64_t>(want + 4, cap); ++s) {
-            const double waves = ((double)units * s + tails) / (double)slots;
-            const double score = waves / std::ceil(waves) - 0.01 * (double)std::llabs(s - want);
-            if (score > best_score) { best_score = score; best = s; }
-        }
-        want = best;
+    const int64_t groups = a.n_quant / kGroup;
+    const int64_t cap = std::min<int64_t>(std::max(1, tiles / 4), kMaxSplits);  // >= 4 groups per warp
+    int64_t want;
+    if (a.flags & VQ_ATTEND_OVERLAP_PREVIOUS) {
+        const int64_t per_warp = std::min<int64_t>(64, std::max<int64_t>(32, 2 * units));
+        want = (groups + 2 * per_warp) / (4 * per_warp);  // rounded to nearest
+    } else {
+        const int64_t fill = ceil_div((int64_t)64 * tuned_waves() * 2, units);  // 256 CTAs at the default setting
+        want = std::max<int64_t>(ceil_div(groups, 4 * 32), fill);
     }
-    return (int)want;
+    return (int)std::max<int64_t>(1, std::min(want, cap));
 }
 
 template <int BITS, int STAGES>
@@ -892,9 +856,13 @@ const char *kivi_attend_mma_supported(const vq_kivi_attend_args &a) {
 
 int kivi_attend_mma_splits(const vq_kivi_attend_args &a, const DeviceInfo &di) { return choose_splits(a, di); }
 
-// At most one tail CTA per 32 unquantized tokens and 8 in all (an upper bound: the launch may use one).
-int kivi_attend_mma_tail_parts(const vq_kivi_attend_args &a) {
-    return a.n_res > 0 ? (int)std::min<int64_t>(8, ceil_div(a.n_res, 32)) : 0;
+// Workspace of a launch with `n_splits` context splits: the partial records, then one 64-bit
+// ticket per (batch, kv head, head chunk).
+int64_t kivi_attend_mma_workspace(const vq_kivi_attend_args &a, int n_splits) {
+    const int hpk = a.H_q / a.H_kv;
+    const int64_t recs = (int64_t)a.B * a.H_kv * n_splits * hpk;
+    const int64_t part_bytes = recs * (kD + 2) * (int64_t)sizeof(float);
+    return ((part_bytes + 15) & ~(int64_t)15) + (int64_t)a.B * a.H_kv * ceil_div(hpk, kChunkHeads) * 8;
 }
 
 int32_t kivi_attend_mma_take_timeout(int *flag) {
@@ -991,41 +959,22 @@ int32_t kivi_attend_mma_launch(const vq_kivi_attend_args &a, const DeviceInfo &d
     p.groups_per_warp = (int)ceil_div(p.groups_total, (int64_t)p.n_splits * kWarps);
     // a split count that leaves trailing splits empty is trimmed
     p.n_splits = (int)ceil_div(p.groups_total, (int64_t)p.groups_per_warp * kWarps);
-    p.n_tail = kivi_attend_mma_tail_parts(a);
-    p.n_parts = p.n_splits + p.n_tail;
-    const int64_t recs = (int64_t)a.B * a.H_kv * p.n_parts * p.hpk;
-    const int64_t need = recs * (kD + 2) * (int64_t)sizeof(float);
+    const int64_t recs = (int64_t)a.B * a.H_kv * p.n_splits * p.hpk;
+    const int64_t part_bytes = recs * (kD + 2) * (int64_t)sizeof(float);
+    const int64_t need = kivi_attend_mma_workspace(a, p.n_splits);
     VQ_REQUIRE(a.workspace != nullptr && a.workspace_bytes >= need, VQ_ERR_CAPACITY,
                "vq_kivi_decode_attend: workspace of %lld bytes needed, %lld given", (long long)need,
                (long long)a.workspace_bytes);
     VQ_REQUIRE(is_aligned(a.workspace, 16), VQ_ERR_ALIGN, "vq_kivi_decode_attend: workspace must be 16-byte aligned");
     p.part_o = (float *)a.workspace;
     p.part_ml = p.part_o + recs * kD;
+    p.tickets = reinterpret_cast<unsigned long long *>(static_cast<uint8_t *>(a.workspace) + ((part_bytes + 15) & ~(int64_t)15));
+    // a fresh non-zero epoch per call (process-wide counter; 0 is what a merged ticket is reset to)
+    static std::atomic<uint32_t> next_epoch{1};
+    do { p.epoch = next_epoch.fetch_add(1, std::memory_order_relaxed); } while (p.epoch == 0);
 
     dim3 grid(p.n_splits * p.n_chunks, a.H_kv, a.B);
-    const int32_t rc = a.store_bits == 4 ? launch_bits<4>(p, grid, st) : launch_bits<2>(p, grid, st);
-    if (rc != VQ_OK) return rc;
-    // Programmatic dependent launches: the tail CTAs, then the merge CTAs, become resident while
-    // the last main CTAs drain. The tail grid ends with griddepcontrol.wait (on the main grid),
-    // the merge grid starts with it (on the tail grid, or on the main grid if there is no tail).
-    cudaLaunchConfig_t cfg = {};
-    cfg.blockDim = dim3(kD);
-    cfg.dynamicSmemBytes = 0;
-    cfg.stream = st;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
-    if (p.n_tail > 0) {
-        cfg.gridDim = dim3(p.n_tail, a.H_kv, a.B);
-        if (a.res_dtype == VQ_F16) VQ_CHECK_CUDA(cudaLaunchKernelEx(&cfg, kivi_attend_tail_kernel<__half>, p));
-        else if (a.res_dtype == VQ_BF16) VQ_CHECK_CUDA(cudaLaunchKernelEx(&cfg, kivi_attend_tail_kernel<__nv_bfloat16>, p));
-        else VQ_CHECK_CUDA(cudaLaunchKernelEx(&cfg, kivi_attend_tail_kernel<float>, p));
-    }
-    cfg.gridDim = dim3((unsigned)((int64_t)a.B * a.H_q));
-    VQ_CHECK_CUDA(cudaLaunchKernelEx(&cfg, kivi_attend_mma_merge_kernel, p));
-    return VQ_OK;
+    return a.store_bits == 4 ? launch_bits<4>(p, grid, st) : launch_bits<2>(p, grid, st);
 }
 
 }  // namespace vq

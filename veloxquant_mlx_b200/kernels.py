@@ -320,7 +320,7 @@ def kivi_decode_attend(q, k_codes, k_scale, k_zero, v_codes, v_scale, v_zero, gr
                        store_bits=8, n_quant=None, k_res=None, v_res=None, n_res=None,
                        out=None, out_dtype=None, n_splits=0, variant=0, static_scratch=False,
                        overlap_previous=False, gather=None, res_offset=0, causal=False,
-                       _fn="kivi_decode_attend"):
+                       _plan_batch=None, _fn="kivi_decode_attend"):
     """Fused dequant + attention over packed codes and an optional unquantized tail.
 
     ``k_codes/v_codes [B,H_kv,cap,D*store_bits/8]`` (first ``n_quant`` rows used),
@@ -462,6 +462,11 @@ def kivi_decode_attend(q, k_codes, k_scale, k_zero, v_codes, v_scale, v_zero, gr
         a.res_dtype = dtype_code(k_res.dtype)
         a.res_stride_bh = k_res.shape[2] * k_res.shape[3]
     with torch.cuda.device(q.device):
+        if _plan_batch is not None and not n_splits:
+            # layers folded into the batch axis: take the split count of one layer's shape
+            a.B = int(_plan_batch)
+            a.n_splits = int(lib().vq_kivi_attend_splits(C.byref(a)))
+            a.B = B
         if static_scratch:
             check(lib().vq_kivi_decode_attend_static(C.byref(a), stream_ptr(q.device)), fn)
             return out
@@ -501,7 +506,9 @@ def scalar_fused_decode_attend_batched(q, k_codes, k_scale, k_zero, v_codes, v_s
 
     Mirrors ``scalar_fused_decode_attend_batched`` (``metal/_scalar_attend.py:496-647``). The
     layer axis is folded into the batch axis of the same kernel (layers are just more
-    independent (batch, kv head) units), so stacked contiguous inputs cost no copy.
+    independent (batch, kv head) units), so stacked contiguous inputs cost no copy. The context
+    split count is the one a single layer's call would use, so each layer's result is bit-identical
+    to the per-layer call, as the reference pins it (``tests/metal/test_scalar_attend.py:660-707``).
     """
     fn = "scalar_fused_decode_attend_batched"
     if q.ndim != 5:
@@ -537,7 +544,7 @@ def scalar_fused_decode_attend_batched(q, k_codes, k_scale, k_zero, v_codes, v_s
         fold(q), fold(k_codes.to(torch.uint8)), fold(k_scale.to(torch.float32)), fold(k_zero.to(torch.float32)),
         fold(v_codes.to(torch.uint8)), fold(v_scale.to(torch.float32)), fold(v_zero.to(torch.float32)),
         group_size, scale, store_bits=store_bits, out_dtype=torch.float16,
-        n_splits=0 if nsg is None else nsg, _fn=fn,
+        n_splits=0 if nsg is None else nsg, _plan_batch=B, _fn=fn,
     )
     return out.reshape(NL, B, H, S_q, D)
 
