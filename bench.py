@@ -430,12 +430,12 @@ def run_ours(args):
     gathered = [torch.empty((B, H_q, 1, D), device=device, dtype=dtype) for _ in range(L)] if gather_mode == "nccl" else None
     torch.cuda.synchronize()
 
-    def nccl_gather(l):
+    def nccl_gather(l, src=None):
         ev = torch.cuda.Event()
         ev.record()
         with torch.cuda.stream(comm_stream):
             comm_stream.wait_event(ev)
-            sharding.gather_layer_output(outs[l], plan, out=gathered[l])
+            sharding.gather_layer_output(outs[l] if src is None else src, plan, out=gathered[l])
 
     def make_step(with_gather=True):
         def step():
@@ -565,54 +565,63 @@ def run_e2e(torch, dist, timer, w, plan, world, device, dtype, caches, outs, px,
     new token's K/V come from pinned host memory, the token is appended (and, every `group`
     steps, the group that aged out of the residual window is quantized into the packed store),
     attention runs over the packed cache, and the layer's output goes back to pinned host memory.
-    The copies run on their own streams: per layer ONE pinned staging buffer (query, key, value
-    back to back) with its device twin and an event; uploads are issued two layers ahead of the
-    compute launches; the compute stream waits for the event of the layer it is about to run,
-    the download stream for the layer's attention."""
+    The copies run on their own streams in chunks of four layers: one pinned staging buffer per
+    chunk (query, key, value of its layers back to back) with its device twin and an event;
+    uploads are issued one chunk ahead of the compute launches; the compute stream waits for the
+    event of the chunk it is about to run, the download stream for the chunk's last attention."""
     L, D = w["layers"], w["D"]
     scale = 1.0 / math.sqrt(D)
     kv_shape = (*shape_bh, 1, D)
     n_q = int(np.prod(q_shape))
     n_kv = int(np.prod(kv_shape))
-    host_o = [torch.empty(q_shape, dtype=dtype).pin_memory() for _ in range(L)]
-    host_in = [torch.empty(n_q + 2 * n_kv, dtype=dtype).pin_memory() for _ in range(L)]
-    dev_in = [torch.empty(n_q + 2 * n_kv, device=device, dtype=dtype) for _ in range(L)]
-    for l in range(L):
-        host_in[l].copy_(torch.randn(n_q + 2 * n_kv, dtype=torch.float32).to(dtype))
-    dq = [t[:n_q].view(q_shape) for t in dev_in]
-    dk = [t[n_q:n_q + n_kv].view(kv_shape) for t in dev_in]
-    dv = [t[n_q + n_kv:].view(kv_shape) for t in dev_in]
-    h2d_bytes = L * dev_in[0].numel() * dev_in[0].element_size()
-    d2h_bytes = L * n_q * dev_in[0].element_size()
+    per_layer = n_q + 2 * n_kv
+    CH = 4
+    chunks = [list(range(c, min(c + CH, L))) for c in range(0, L, CH)]
+    host_in = [torch.empty(len(ch) * per_layer, dtype=dtype).pin_memory() for ch in chunks]
+    dev_in = [torch.empty(len(ch) * per_layer, device=device, dtype=dtype) for ch in chunks]
+    for t in host_in:
+        t.copy_(torch.randn(t.numel(), dtype=torch.float32).to(dtype))
+    dq, dk, dv = [], [], []
+    for ci, ch in enumerate(chunks):
+        for j in range(len(ch)):
+            base = j * per_layer
+            dq.append(dev_in[ci][base:base + n_q].view(q_shape))
+            dk.append(dev_in[ci][base + n_q:base + n_q + n_kv].view(kv_shape))
+            dv.append(dev_in[ci][base + n_q + n_kv:base + per_layer].view(kv_shape))
+    # the layers of a chunk write their outputs into one device buffer, downloaded as a whole
+    dev_out = [torch.empty((len(ch), *q_shape), device=device, dtype=dtype) for ch in chunks]
+    host_out = [torch.empty((len(ch), *q_shape), dtype=dtype).pin_memory() for ch in chunks]
+    e2e_outs = [dev_out[ci][j] for ci, ch in enumerate(chunks) for j in range(len(ch))]
+    h2d_bytes = sum(t.numel() * t.element_size() for t in dev_in)
+    d2h_bytes = sum(t.numel() * t.element_size() for t in dev_out)
     up_stream, down_stream = torch.cuda.Stream(device), torch.cuda.Stream(device)
-    ev_in = [torch.cuda.Event() for _ in range(L)]
-    ev_done = [torch.cuda.Event() for _ in range(L)]
-    ahead = 2
+    ev_in = [torch.cuda.Event() for _ in chunks]
+    ev_done = [torch.cuda.Event() for _ in chunks]
 
-    def upload(l):
+    def upload(ci):
         with torch.cuda.stream(up_stream):
-            dev_in[l].copy_(host_in[l], non_blocking=True)
-            ev_in[l].record(up_stream)
+            dev_in[ci].copy_(host_in[ci], non_blocking=True)
+            ev_in[ci].record(up_stream)
 
     def e2e_step():
         main = torch.cuda.current_stream()
         up_stream.wait_stream(main)  # the previous step is done with the staging buffers
-        for l in range(min(ahead, L)):
-            upload(l)
-        for l in range(L):
-            if l + ahead < L:
-                upload(l + ahead)
-            main.wait_event(ev_in[l])
-            caches[l].update_and_fetch(dk[l], dv[l])
-            caches[l].fused_sdpa(dq[l], scale, out=outs[l], gather=px.layer(l) if px is not None else None)
-            if px is not None:
-                px.wait(l)
-            ev_done[l].record(main)
+        upload(0)
+        for ci, ch in enumerate(chunks):
+            if ci + 1 < len(chunks):
+                upload(ci + 1)
+            main.wait_event(ev_in[ci])
+            for l in ch:
+                caches[l].update_and_fetch(dk[l], dv[l])
+                caches[l].fused_sdpa(dq[l], scale, out=e2e_outs[l], gather=px.layer(l) if px is not None else None)
+                if px is not None:
+                    px.wait(l)
+                if gather_mode == "nccl":
+                    nccl_gather(l, e2e_outs[l])
+            ev_done[ci].record(main)
             with torch.cuda.stream(down_stream):
-                down_stream.wait_event(ev_done[l])
-                host_o[l].copy_(outs[l], non_blocking=True)
-            if gather_mode == "nccl":
-                nccl_gather(l)
+                down_stream.wait_event(ev_done[ci])
+                host_out[ci].copy_(dev_out[ci], non_blocking=True)
         if gather_mode == "nccl":
             main.wait_stream(comm_stream)
         main.wait_stream(down_stream)
@@ -661,8 +670,8 @@ def run_e2e(torch, dist, timer, w, plan, world, device, dtype, caches, outs, px,
         "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": d2h_bytes,
         "torch_allocations_in_timed_region": int(alloc1 - alloc0),
         "path": "KIVIKVCache.update_and_fetch(new token; quantize-on-append flush every group) + "
-                "KIVIKVCache.fused_sdpa per layer; pinned host buffers, uploads and downloads on their own "
-                "streams; value = mean over all timed steps, flush steps included",
+                "KIVIKVCache.fused_sdpa per layer; pinned host buffers, uploads and downloads in chunks of 4 "
+                "layers on their own streams; value = mean over all timed steps, flush steps included",
     }
 
 
@@ -789,9 +798,14 @@ def run_c5(torch, dist, timer, world, rank, device, dtype, args):
     scale = 1.0 / math.sqrt(D)
     S = 16384
     k, v = synth_kv(torch, (*shape_bh, S, D), device, 77 + rank, dtype)
+    # a first, untimed pass over all layers: it pays the kernels' first launches and leaves the
+    # device memory of 64 packed caches in torch's caching allocator, as a warmed-up server has it
     caches = [new_cache(w) for _ in range(L)]
-    # warm the quantize kernels on a scratch cache (first-launch cost is not the prompt's)
-    new_cache(w).update_and_fetch(k, v)
+    for l in range(L):
+        caches[l].update_and_fetch(k, v)
+    torch.cuda.synchronize()
+    del caches
+    caches = [new_cache(w) for _ in range(L)]
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     timer.barrier()
     e0.record()

@@ -61,8 +61,12 @@ typedef enum vq_knob {
                                     bounded wait runs out, the kernel finishes normally and
                                     vq_kivi_attend_status reports VQ_ERR_TIMEOUT once (one-shot
                                     self-test of that path; nothing faults or hangs) */
-    VQ_KNOB_VQ_WAIT_TEST = 4     /* 1: the same for the NEXT tcgen05 vq_vq_quantize launch and
+    VQ_KNOB_VQ_WAIT_TEST = 4,    /* 1: the same for the NEXT tcgen05 vq_vq_quantize launch and
                                     vq_vq_quantize_status */
+    VQ_KNOB_ATTEND_EXACT_PV = 5  /* decode attend, P.V products: 0 (default) one half-precision
+                                    operand per softmax weight x value scale (relative rounding 2^-11,
+                                    float32 accumulation); 1 a (high, low) pair of halves, exact
+                                    products, about 5 % more instructions. Q.K is always exact. */
 } vq_knob;
 int32_t vq_tune(int32_t knob, int32_t value);
 

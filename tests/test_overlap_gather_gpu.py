@@ -31,10 +31,10 @@ DEV = "cuda:0"
 SCALE = 1.0 / math.sqrt(128)
 
 
-def _cache(bits=4, residual=128):
+def _cache(bits=4, residual=128, capacity=None):
     from veloxquant_mlx_b200.cache import KVCacheConfig, KVCacheFactory
 
-    return KVCacheFactory.create(KVCacheConfig(method="kivi", head_dim=128, bit_width_inlier=bits,
+    return KVCacheFactory.create(KVCacheConfig(method="kivi", head_dim=128, bit_width_inlier=bits, capacity=capacity,
                                                residual_length=residual, fused_sdpa_memory_bound=True))
 
 
@@ -262,7 +262,7 @@ def test_steady_state_decode_allocates_nothing_and_matches_a_prefill():
     k = torch.randn((B, H_kv, S0 + n_dec, 128), generator=g, device=DEV, dtype=torch.float16)
     v = torch.randn((B, H_kv, S0 + n_dec, 128), generator=g, device=DEV, dtype=torch.float16)
     q = torch.randn((B, H_q, 1, 128), generator=g, device=DEV, dtype=torch.float16)
-    c = _cache()
+    c = _cache(capacity=1024)  # (the packed store doubles when full: pre-sized here, as a serving loop would)
     c.update_and_fetch(k[:, :, :S0], v[:, :, :S0])
     out = torch.empty_like(q)
     kt = torch.empty((B, H_kv, 1, 128), device=DEV, dtype=torch.float16)

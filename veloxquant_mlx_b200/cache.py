@@ -18,6 +18,7 @@ reference's VecInfer memory-bound mode (``cache/vecinfer_cache.py:491-532``).
 
 from __future__ import annotations
 
+import ctypes as C
 import dataclasses
 import functools
 import math
@@ -27,7 +28,7 @@ from typing import Any
 
 import torch
 
-from . import kernels
+from . import _lib, kernels
 
 
 class QuantizerConfigError(ValueError):
@@ -283,6 +284,10 @@ class KIVIKVCache:
             raise QuantizerConfigError("KIVIKVCache: head_dim * storage bits must be a multiple of 8")
         self._eps = 1e-8
         self._memory_bound = bool(getattr(config, "fused_sdpa_memory_bound", False))
+        # `capacity` (tokens) pre-sizes the packed store at its first allocation, so that a serving
+        # loop of known maximum length never reallocates; the store still doubles beyond it
+        cap_hint = getattr(config, "capacity", None)
+        self._capacity_hint = int(cap_hint) if cap_hint else 0
         self.offset = 0
         self._n_quantized = 0
         self._n_res = 0
@@ -293,6 +298,13 @@ class KIVIKVCache:
         self._kv_res = self._k_res = self._v_res = None
         self._shape_bhd = (1, 1, self._head_dim)
         self._dtype = None
+        # Host fast paths of the decode loop: the argument structure of the last attention call
+        # and the layout of the last single-token append, reused while nothing they describe has
+        # changed (`_version` moves whenever a buffer is replaced).
+        self._version = 0
+        self._attend_plan = None
+        self._append_plan = None
+        self._sentinel = None
         # byte accounting (same definitions as the reference's properties)
         self._key_bytes_compressed = 0
         self._value_bytes_compressed = 0
@@ -311,7 +323,7 @@ class KIVIKVCache:
         g = self._group_size
         if self._k_codes is not None and n_tokens <= self._cap:
             return
-        new_cap = max(256, self._cap)
+        new_cap = max(256, self._cap, self._capacity_hint)
         while new_cap < n_tokens:
             new_cap *= 2
         new_cap = ((new_cap + g - 1) // g) * g
@@ -331,6 +343,7 @@ class KIVIKVCache:
         self._v_scale = grow(self._v_scale, (B, H, new_cap, gv), torch.float32)
         self._v_zero = grow(self._v_zero, (B, H, new_cap, gv), torch.float32)
         self._cap = new_cap
+        self._version += 1
 
     def _ensure_residual(self, B, H, D, n, device, dtype) -> None:
         """Room for ``n`` live rows starting at row 0 (a larger buffer is allocated, and the
@@ -345,6 +358,7 @@ class KIVIKVCache:
             kv[:, :, :, : self._n_res] = self._kv_res[:, :, :, self._res_lo : self._res_lo + self._n_res]
         self._kv_res, self._k_res, self._v_res = kv, kv[0], kv[1]
         self._res_lo = 0
+        self._version += 1
 
     def _make_room(self, B, H, D, S, device, dtype) -> None:
         """Make rows ``[_res_lo + _n_res, +S)`` of the residual buffer exist."""
@@ -382,6 +396,23 @@ class KIVIKVCache:
     # -- protocol ----------------------------------------------------------------------
     def update_and_fetch(self, keys: torch.Tensor, values: torch.Tensor):
         """Append ``keys/values [B,H,S,D]``; flush aged whole groups into the packed store."""
+        ap = self._append_plan
+        if (ap is not None and ap[0] == self._version and keys.shape == ap[1] and values.shape == ap[1]
+                and keys.dtype is ap[2] and values.dtype is ap[2] and (self.offset + 1 - self._residual_length) % self._group_size
+                and self._res_lo + self._n_res < ap[3] and keys.is_contiguous() and values.is_contiguous()
+                and not (keys.data_ptr() | values.data_ptr()) & 15 and torch.cuda.current_device() == ap[9].index):
+            # One token, no group ages out, room behind the live rows, same layout as last time:
+            # straight to the copy kernel (the checks of the general path below were made then).
+            _, shape, _, _, n_bh, res_stride, dt, k_ptr, v_ptr, dev = ap
+            _lib.check(_lib.lib().vq_kivi_append(keys.data_ptr(), values.data_ptr(), shape[3], k_ptr, v_ptr, res_stride, n_bh, 1,
+                                                 self._res_lo + self._n_res, shape[3], dt, _lib.stream_ptr(dev)),
+                       "KIVIKVCache.update_and_fetch")
+            self.offset += 1
+            self._n_res += 1
+            self._account_bytes(shape[0], shape[1], 1, shape[3], 0)
+            if self._memory_bound:
+                return self._sentinel, self._sentinel
+            return self._materialize()
         if keys.ndim != 4 or keys.shape != values.shape:
             raise ValueError(f"KIVIKVCache.update_and_fetch: keys/values must be equal 4D shapes, got "
                              f"{tuple(keys.shape)} / {tuple(values.shape)}")
@@ -436,9 +467,17 @@ class KIVIKVCache:
                 self._store_block(src_k[:, :, n_flush:], src_v[:, :, n_flush:], keep)
             self._n_quantized = new_boundary
         self._account_bytes(B, H, S, D, max(n_flush, 0))
+        if (S == 1 and keys.dtype is self._k_res.dtype and keys.is_cuda and (D * keys.element_size()) % 16 == 0
+                and torch.cuda.current_device() == keys.device.index):
+            es = keys.element_size()
+            self._append_plan = (self._version, keys.shape, keys.dtype, self._k_res.shape[2], B * H,
+                                 self._k_res.shape[2] * D, _lib.dtype_code(keys.dtype), self._k_res.data_ptr(),
+                                 self._v_res.data_ptr(), keys.device)
+            assert (self._k_res.shape[2] * D * es) % 16 == 0
         if self._memory_bound:
-            z = keys.new_zeros((B, H, 0, D))
-            return z, z
+            if self._sentinel is None or self._sentinel.shape != (B, H, 0, D) or self._sentinel.dtype != keys.dtype:
+                self._sentinel = keys.new_zeros((B, H, 0, D))
+            return self._sentinel, self._sentinel
         return self._materialize()
 
     def _live_res(self):
@@ -474,6 +513,26 @@ class KIVIKVCache:
         lets every row see every slot, as the reference's ``scalar_fused_decode_attend`` does.
 
         ``overlap_previous`` / ``gather``: see :func:`kernels.kivi_decode_attend`."""
+        plan = self._attend_plan
+        if (plan is not None and out is not None and plan[0] == self._version and q.data_ptr() == plan[1]
+                and out.data_ptr() == plan[2] and q.shape == plan[3] and q.dtype is plan[4] and out.dtype is plan[5]
+                and out.shape == plan[3] and gather is plan[6] and not sliding_window and self._n_quantized > 0
+                and torch.cuda.current_device() == plan[7]):
+            # Same query / output buffers and cache buffers as the last call: only the counters,
+            # the residual window's start and the flags are new.
+            a, row_bytes, k_res_ptr, v_res_ptr, need = plan[8], plan[9], plan[10], plan[11], plan[12]
+            lib = _lib.lib()
+            a.n_quant, a.n_res, a.scale = self._n_quantized, self._n_res, scale
+            a.flags = _lib.VQ_ATTEND_OVERLAP_PREVIOUS if overlap_previous else 0
+            a.k_res = k_res_ptr + self._res_lo * row_bytes
+            a.v_res = v_res_ptr + self._res_lo * row_bytes
+            key = (self._n_quantized, a.flags)
+            if need[0] != key:
+                need[0], need[1] = key, lib.vq_kivi_attend_workspace_bytes(C.byref(a))
+            ws = kernels._workspace(q.device, need[1])
+            a.workspace, a.workspace_bytes = ws.data_ptr(), ws.numel()
+            _lib.check(lib.vq_kivi_decode_attend(C.byref(a), _lib.stream_ptr(q.device)), "KIVIKVCache.fused_sdpa")
+            return out
         if q.ndim != 4:
             raise ValueError(f"KIVIKVCache.fused_sdpa: q must be 4D, got {tuple(q.shape)}")
         if sliding_window:
@@ -483,13 +542,22 @@ class KIVIKVCache:
         if q.shape[2] > self.offset and causal:
             raise ValueError(f"KIVIKVCache.fused_sdpa: {q.shape[2]} query rows but only {self.offset} cached tokens")
         has_q = self._n_quantized > 0
-        return kernels.kivi_decode_attend(
+        want_plan = (out is not None and has_q and self._n_res > 0 and q.shape[2] == 1 and q.is_contiguous()
+                     and torch.cuda.current_device() == q.device.index)
+        keep = [] if want_plan else None
+        res = kernels.kivi_decode_attend(
             q, self._k_codes if has_q else None, self._k_scale, self._k_zero,
             self._v_codes if has_q else None, self._v_scale, self._v_zero, self._group_size, scale,
             store_bits=self._sb, n_quant=self._n_quantized,
             k_res=self._k_res if self._n_res else None, v_res=self._v_res if self._n_res else None,
             n_res=self._n_res, res_offset=self._res_lo, out=out, causal=bool(causal) and q.shape[2] > 1,
-            overlap_previous=overlap_previous, gather=gather, _fn="KIVIKVCache.fused_sdpa")
+            overlap_previous=overlap_previous, gather=gather, _keep_args=keep, _fn="KIVIKVCache.fused_sdpa")
+        if want_plan and keep:
+            # the validated argument structure, for the next call with the same buffers
+            self._attend_plan = (self._version, q.data_ptr(), out.data_ptr(), q.shape, q.dtype, out.dtype, gather,
+                                 q.device.index, keep[0], self._head_dim * self._k_res.element_size(),
+                                 self._k_res.data_ptr(), self._v_res.data_ptr(), [None, 0])
+        return res
 
     def check_status(self) -> None:
         """Raise if a device-side bounded wait of an earlier attention call ran out (its output

@@ -41,6 +41,7 @@
 #include <cmath>
 #include <cstdlib>
 #include <cstring>
+#include <random>
 
 #include "kivi_attend.h"
 
@@ -212,9 +213,10 @@ struct Params {
     int groups_per_warp;  // consecutive groups owned by one warp
     float *part_o;      // [B*H_kv][n_splits][hpk][128]
     float *part_ml;     // [B*H_kv][n_splits][hpk][2]
-    unsigned long long *tickets;  // [B*H_kv][n_chunks]: (epoch << 32) | arrivals of the current call
-    uint32_t epoch;     // distinguishes this call's tickets from whatever the workspace held before
+    unsigned long long *tickets;  // [B*H_kv][n_chunks]: (epoch << 16) | arrivals of the current call
+    unsigned long long epoch;     // 48 bits that tell this call's tickets from whatever the workspace held before
     int wait_test;      // self-test: every warp also waits (briefly) on a barrier that nothing arms
+    int split_pv;       // P * v_scale as hi + lo halves (exact products) instead of one rounded half
     vq_peer_gather gather;  // world == 0: the output rows are not published to peers
 };
 
@@ -514,8 +516,12 @@ kivi_attend_mma_kernel(const __grid_constant__ Params p) {
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
                     oz[j] = fmaf(pa, za4[j], fmaf(pb, zb4[j], oz[j]));
-                    pbw[j][0] = movmatrix_trans(split_pack(pa * sa4[j]));
-                    pbw[j][1] = movmatrix_trans(split_pack(pb * sb4[j]));
+                    // One half per product by default: its 2^-11 relative rounding is averaged over the
+                    // softmax weights and stays far inside the output tolerance; the (hi, lo) pair makes
+                    // the products exact at three more instructions each.
+                    const float xa = pa * sa4[j], xb = pb * sb4[j];
+                    pbw[j][0] = movmatrix_trans(p.split_pv ? split_pack(xa) : pack_h2(xa, 0.f));
+                    pbw[j][1] = movmatrix_trans(p.split_pv ? split_pack(xb) : pack_h2(xb, 0.f));
                 }
             }
 #pragma unroll
@@ -678,9 +684,11 @@ kivi_attend_mma_kernel(const __grid_constant__ Params p) {
     }
 
     // ---- ticket: the CTA that arrives last for this (batch, kv head, head chunk) merges ----------
-    // The ticket word is (epoch << 32) | arrivals. Whatever the workspace held before this call has
-    // another epoch in its high half and counts as zero arrivals; the merging CTA leaves 0 behind
-    // (epoch 0 is never issued), so a captured launch can be replayed with the same epoch.
+    // The ticket word is (epoch << 16) | arrivals. Whatever the workspace held before this call
+    // (another call's partials, a fresh allocation's old contents) has other upper 48 bits and
+    // counts as zero arrivals: the epoch is a per-call 48-bit hash, so stray data matches it with
+    // probability 2^-48. The merging CTA leaves 0 behind (epoch 0 is never issued), so in a steady
+    // decode loop every ticket is found at 0, and a captured launch can be replayed with its epoch.
     int *sh_last = reinterpret_cast<int *>(bars) + 48;  // (behind the barriers, inside their 256 bytes)
     __threadfence();
     __syncthreads();
@@ -688,12 +696,12 @@ kivi_attend_mma_kernel(const __grid_constant__ Params p) {
         unsigned long long *t = p.tickets + bh * p.n_chunks + (h0 / kChunkHeads);
         unsigned long long cur = *reinterpret_cast<volatile unsigned long long *>(t), want;
         for (;;) {
-            want = ((uint32_t)(cur >> 32) == p.epoch) ? cur + 1ull : (((unsigned long long)p.epoch << 32) | 1ull);
+            want = ((cur >> 16) == p.epoch) ? cur + 1ull : ((p.epoch << 16) | 1ull);
             const unsigned long long seen = atomicCAS(t, cur, want);
             if (seen == cur) break;
             cur = seen;  // (another CTA of this unit got in between: at most n_splits - 1 retries)
         }
-        *sh_last = ((uint32_t)want == (uint32_t)p.n_splits);
+        *sh_last = ((uint32_t)(want & 0xffffull) == (uint32_t)p.n_splits);
     }
     __syncthreads();
     if (!*sh_last) return;
@@ -758,7 +766,7 @@ kivi_attend_mma_kernel(const __grid_constant__ Params p) {
     if (tid == 0) p.tickets[bh * p.n_chunks + (h0 / kChunkHeads)] = 0ull;
 }
 
-constexpr int kMaxSplits = 512;
+constexpr int kMaxSplits = 512;  // (a ticket counts arrivals in 16 bits)
 
 // Pipeline depth and waves-per-launch are tunables (vq_tune: VQ_KNOB_ATTEND_STAGES = 2..4,
 // VQ_KNOB_ATTEND_WAVES = 1..32).
@@ -939,6 +947,7 @@ int32_t kivi_attend_mma_launch(const vq_kivi_attend_args &a, const DeviceInfo &d
     p.a = a;
     p.a.gather = nullptr;  // (a host pointer: the kernels get a copy of the struct instead)
     p.wait_test = knob_take(VQ_KNOB_ATTEND_WAIT_TEST);
+    p.split_pv = knob_get(VQ_KNOB_ATTEND_EXACT_PV);
     p.gather = vq_peer_gather{};
     if (a.gather != nullptr) {
         const vq_peer_gather &pg = *a.gather;
@@ -969,9 +978,16 @@ int32_t kivi_attend_mma_launch(const vq_kivi_attend_args &a, const DeviceInfo &d
     p.part_o = (float *)a.workspace;
     p.part_ml = p.part_o + recs * kD;
     p.tickets = reinterpret_cast<unsigned long long *>(static_cast<uint8_t *>(a.workspace) + ((part_bytes + 15) & ~(int64_t)15));
-    // a fresh non-zero epoch per call (process-wide counter; 0 is what a merged ticket is reset to)
-    static std::atomic<uint32_t> next_epoch{1};
-    do { p.epoch = next_epoch.fetch_add(1, std::memory_order_relaxed); } while (p.epoch == 0);
+    // a fresh non-zero 48-bit epoch per call: a process-wide counter, salted once per process and
+    // mixed (splitmix64), so that small integers or floats left in the workspace cannot equal it
+    static const uint64_t salt = [] { std::random_device rd; return ((uint64_t)rd() << 32) ^ rd(); }();
+    static std::atomic<uint64_t> next_epoch{1};
+    do {
+        uint64_t z = (next_epoch.fetch_add(1, std::memory_order_relaxed) ^ salt) + 0x9e3779b97f4a7c15ull;
+        z = (z ^ (z >> 30)) * 0xbf58476d1ce4e5b9ull;
+        z = (z ^ (z >> 27)) * 0x94d049bb133111ebull;
+        p.epoch = (z ^ (z >> 31)) >> 16;
+    } while (p.epoch == 0);
 
     dim3 grid(p.n_splits * p.n_chunks, a.H_kv, a.B);
     return a.store_bits == 4 ? launch_bits<4>(p, grid, st) : launch_bits<2>(p, grid, st);

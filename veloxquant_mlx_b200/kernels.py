@@ -29,14 +29,15 @@ def kivi_available() -> bool:
 
 _KNOBS = {"attend_stages": _lib.VQ_KNOB_ATTEND_STAGES, "attend_waves": _lib.VQ_KNOB_ATTEND_WAVES,
           "vq_search": _lib.VQ_KNOB_VQ_SEARCH, "attend_wait_test": _lib.VQ_KNOB_ATTEND_WAIT_TEST,
-          "vq_wait_test": _lib.VQ_KNOB_VQ_WAIT_TEST}
+          "vq_wait_test": _lib.VQ_KNOB_VQ_WAIT_TEST, "attend_exact_pv": _lib.VQ_KNOB_ATTEND_EXACT_PV}
 
 
 def tune(knob: str, value: int) -> int:
     """Set a process-wide tuning / self-test knob of the native library (``vq_tune``) and return
     its previous value. Knobs: ``attend_stages`` (2..4), ``attend_waves`` (1..32), ``vq_search``
-    (0 choose, 1 tcgen05, 2 mma.sync, 3 exact), and the one-shot self-tests ``attend_wait_test``
-    / ``vq_wait_test`` that make the next launch's bounded device wait run out."""
+    (0 choose, 1 tcgen05, 2 mma.sync, 3 exact), ``attend_exact_pv`` (1: exact P.V products in the
+    decode attention), and the one-shot self-tests ``attend_wait_test`` / ``vq_wait_test`` that
+    make the next launch's bounded device wait run out."""
     if knob not in _KNOBS:
         raise ValueError(f"tune: unknown knob {knob!r}; choices: {sorted(_KNOBS)}")
     prev = lib().vq_tune(_KNOBS[knob], int(value))
@@ -320,7 +321,7 @@ def kivi_decode_attend(q, k_codes, k_scale, k_zero, v_codes, v_scale, v_zero, gr
                        store_bits=8, n_quant=None, k_res=None, v_res=None, n_res=None,
                        out=None, out_dtype=None, n_splits=0, variant=0, static_scratch=False,
                        overlap_previous=False, gather=None, res_offset=0, causal=False,
-                       _plan_batch=None, _fn="kivi_decode_attend"):
+                       _plan_batch=None, _keep_args=None, _fn="kivi_decode_attend"):
     """Fused dequant + attention over packed codes and an optional unquantized tail.
 
     ``k_codes/v_codes [B,H_kv,cap,D*store_bits/8]`` (first ``n_quant`` rows used),
@@ -475,6 +476,8 @@ def kivi_decode_attend(q, k_codes, k_scale, k_zero, v_codes, v_scale, v_zero, gr
         a.workspace, a.workspace_bytes = ws.data_ptr(), ws.numel()
         entry = lib().vq_kivi_decode_attend if has_q else lib().vq_predecoded_attend
         check(entry(C.byref(a), stream_ptr(q.device)), fn)
+    if _keep_args is not None and has_q:
+        _keep_args.append(a)  # (for a caller that repeats the call with the same buffers)
     return out
 
 
