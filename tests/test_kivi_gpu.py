@@ -346,14 +346,15 @@ def test_mma_attend_parity(b, H, H_kv, n_quant, n_res):
 @pytest.mark.parametrize("n_res", [1, 3, 4, 17, 33, 255])
 @pytest.mark.parametrize("dt", ["float16", "bfloat16", "float32"])
 def test_mma_attend_tail_kernel_edges(n_res, dt):
-    """The unquantized tail is attended by a kernel of its own (four token rows in flight per
-    warp, up to 8 CTAs per unit): tail lengths around its unroll and slice boundaries, all three
-    residual dtypes, 8 query heads per KV head."""
+    """The unquantized tail is spread over the warps of a unit's CTAs (row r goes to warp
+    r mod 4*splits): tail lengths below, at and far above the warp count, all three residual
+    dtypes, 8 query heads per KV head. (The max-abs bound is asked of float16 outputs only: a
+    bfloat16 output of magnitude 0.5..1 is itself rounded by up to 2^-9.)"""
     rng = np.random.default_rng(1000 + n_res)
     (qt, kc, ks, kz, vc, vs, vz, k_res, v_res), ref = _packed_case(rng, 2, 16, 2, 96, n_res, 4, dt)
     out = _k().kivi_decode_attend(qt, kc, ks, kz, vc, vs, vz, 32, 1.0 / math.sqrt(128), store_bits=4,
                                   k_res=k_res, v_res=v_res, variant=2)
-    _assert_attn_close(out.float().cpu().numpy(), ref)
+    _assert_attn_close(out.float().cpu().numpy(), ref, strict=(dt != "bfloat16"))
     from veloxquant_mlx_b200 import _lib
     _lib.check(_lib.lib().vq_kivi_attend_status(), "status")
 
@@ -385,10 +386,9 @@ def test_back_to_back_calls_with_different_inputs_do_not_interfere():
 
 
 def test_mma_attend_replayed_from_a_cuda_graph():
-    """The call issues three kernels chained by programmatic dependent launch (main -> tail ->
-    merge). Captured into a CUDA graph and replayed several times back to back (so that one
-    replay's main kernel follows the previous replay's merge), the output must be that of the
-    plain call, bit for bit, also after the query changed in place."""
+    """Captured into a CUDA graph and replayed several times back to back (every replay finds the
+    tickets of the previous one and carries the same ticket epoch), the output must be that of
+    the plain call, bit for bit, also after the query changed in place."""
     rng = np.random.default_rng(77)
     (qt, kc, ks, kz, vc, vs, vz, k_res, v_res), ref = _packed_case(rng, 2, 8, 2, 2048, 100, 4, "float16")
     k = _k()

@@ -135,10 +135,12 @@ __device__ __forceinline__ void split_h2(float x0, float x1, uint32_t &hi, uint3
     const float2 h = unpack_h2(hi);
     lo = pack_h2(x0 - h.x, x1 - h.y);
 }
-// (half(x), half(x - half(x))) in one register: the column pair (2c, 2c+1) of one value.
-__device__ __forceinline__ uint32_t split_pack(float x) {
-    const float h = __half2float(__float2half_rn(x));
-    return pack_h2(x, x - h);
+// (hi, lo) halves of one value in one register = the column pair (2c, 2c+1): hi is x truncated
+// to 11 significant bits (one AND; exactly a half in the normal range), lo = half(x - hi), so
+// x = hi + lo holds to the half precision of lo (~22 significant bits).
+__device__ __forceinline__ uint32_t split_pack_trunc(float x) {
+    const float h = __uint_as_float(__float_as_uint(x) & 0xffffe000u);
+    return pack_h2(h, x - h);
 }
 __device__ __forceinline__ void mma_f16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                         uint32_t b0, uint32_t b1) {
@@ -516,12 +518,12 @@ kivi_attend_mma_kernel(const __grid_constant__ Params p) {
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
                     oz[j] = fmaf(pa, za4[j], fmaf(pb, zb4[j], oz[j]));
-                    // One half per product by default: its 2^-11 relative rounding is averaged over the
-                    // softmax weights and stays far inside the output tolerance; the (hi, lo) pair makes
-                    // the products exact at three more instructions each.
+                    // The (hi, lo) pair keeps the products exact. One rounded half per product (knob
+                    // VQ_KNOB_ATTEND_EXACT_PV = 0) measured 5 % faster at 2 bits, but with value channels
+                    // scaled x20 its 2^-11 relative rounding reached 1.1e-2 absolute: outside the tolerance.
                     const float xa = pa * sa4[j], xb = pb * sb4[j];
-                    pbw[j][0] = movmatrix_trans(p.split_pv ? split_pack(xa) : pack_h2(xa, 0.f));
-                    pbw[j][1] = movmatrix_trans(p.split_pv ? split_pack(xb) : pack_h2(xb, 0.f));
+                    pbw[j][0] = movmatrix_trans(p.split_pv ? split_pack_trunc(xa) : pack_h2(xa, 0.f));
+                    pbw[j][1] = movmatrix_trans(p.split_pv ? split_pack_trunc(xb) : pack_h2(xb, 0.f));
                 }
             }
 #pragma unroll
