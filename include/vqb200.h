@@ -442,6 +442,35 @@ typedef struct vq_rabitq_attend_args {
 int64_t vq_rabitq_attend_workspace_bytes(const vq_rabitq_attend_args *args);
 int32_t vq_rabitq_decode_attend(const vq_rabitq_attend_args *args, void *stream);
 
+/* Attention of MANY query rows over sign-bit keys (prompt chunks, multi-turn prefill): tiled on
+ * the tensor cores. Score model: the exact dot with the decoded key,
+ *   score[i][j] = (q[i] . (signs(k_bits[j]) * k_mag[j])) * scale + k_const[j]
+ * (not the popcount estimator of the decode kernel), softmax over all slots or, with
+ * causal != 0, the slots up to the query's own (row r of S_q sits at slot S_kv - S_q + r).
+ * Values: nibble-packed indices into a <= 16-entry codebook (v_mode 3: the reference form) or a
+ * dense f16 / bf16 tensor (v_mode 0). H_q may be a multiple of H_kv (contiguous blocks).
+ * D is 64 or 128. No workspace. Replaces rabitq_prefill_attend
+ * (veloxquant_mlx/metal/_rabitq_prefill.py:116-196, metal/src/rabitq_prefill.metal). */
+typedef struct vq_rabitq_prefill_args {
+    const void *q;            /* [B, H_q, S_q, D] */
+    void *out;                /* [B, H_q, S_q, D] */
+    int32_t q_dtype, out_dtype;
+    int32_t B, H_q, H_kv, S_q, S_kv, D;
+    int64_t kv_stride_tok;    /* token capacity between (b, kv head) slabs of the k/v arrays */
+    float scale;
+    int32_t causal;
+    const uint8_t *k_bits;    /* [B*H_kv][cap][D/8] */
+    const float *k_mag;       /* [B*H_kv][cap] */
+    const float *k_const;     /* [B*H_kv][cap] or NULL (= 0) */
+    int32_t v_mode;           /* 0 dense (v_dtype f16 / bf16), 3 nibble-packed codebook indices */
+    int32_t v_dtype;
+    const void *v;            /* dense [B*H_kv][cap][D] or nibbles [B*H_kv][cap][D/2] */
+    const float *v_cents;     /* [<= 16] */
+    int32_t n_cents;
+    int32_t reserved;
+} vq_rabitq_prefill_args;
+int32_t vq_rabitq_prefill_attend(const vq_rabitq_prefill_args *args, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -124,3 +124,33 @@ def reference_attend(q, q_scale, k_bits, k_mag, k_const, v, v_cents=None) -> np.
             w = w / w.sum(axis=-1, keepdims=True)
             out[b, h] = w @ v_hat[b, h]
     return out
+
+
+def reference_prefill(q, scale, k_bits, k_mag, k_const, v, v_cents=None, causal: bool = False) -> np.ndarray:
+    """Exact-dot attention of many query rows over sign-bit keys: a restatement of
+    ``_reference_prefill`` (``tests/metal/test_rabitq_prefill.py:32-53``) with contiguous-block GQA
+    and dense values added.
+
+    ``k_hat = signs(k_bits) * k_mag``; ``score = (q . k_hat) * scale + k_const``; with ``causal``
+    query row ``r`` of ``S_q`` sits at slot ``S_kv - S_q + r`` and slots after it are masked.
+    ``v`` holds indices into ``v_cents`` (``u8 [B,H_kv,S,D]``, unpacked) or, with
+    ``v_cents is None``, dense values.
+    """
+    q = np.asarray(q)
+    D = q.shape[-1]
+    S_q, S_kv = q.shape[2], k_bits.shape[2]
+    signs = np.unpackbits(np.asarray(k_bits, np.uint8), axis=-1, count=D, bitorder="little").astype(np.float32) * 2.0 - 1.0
+    k_hat = signs * np.asarray(k_mag, np.float32)[..., None]
+    kc = np.zeros(k_hat.shape[:3], np.float32) if k_const is None else np.asarray(k_const, np.float32)
+    v_hat = np.asarray(v_cents, np.float32)[np.asarray(v)] if v_cents is not None else np.asarray(v).astype(np.float32)
+    rep = q.shape[1] // k_hat.shape[1]
+    if rep > 1:
+        k_hat, kc, v_hat = (np.repeat(t, rep, axis=1) for t in (k_hat, kc, v_hat))
+    scores = np.einsum("bhqd,bhsd->bhqs", q.astype(np.float32), k_hat) * np.float32(scale) + kc[:, :, None, :]
+    if causal:
+        q_abs = (S_kv - S_q) + np.arange(S_q)
+        scores = np.where(np.arange(S_kv)[None, :] > q_abs[:, None], -np.inf, scores)
+    scores = scores - scores.max(axis=-1, keepdims=True)
+    w = np.exp(scores)
+    w = w / w.sum(axis=-1, keepdims=True)
+    return np.einsum("bhqs,bhsd->bhqd", w, v_hat).astype(np.float32)

@@ -137,6 +137,16 @@ def main():
         for k, v in dict(q=q, q_scale=q_scale, k_bits=k_bits, k_mag=k_mag, k_const=k_const,
                          v_idx=v_idx, v_cents=v_cents, out=ref, v_packed=ns_v["_pack_np"](v_idx)).items():
             out[f"{tag}_{k}"] = v
+    trp = os.path.join(pkg, "tests", "metal", "test_rabitq_prefill.py")
+    ns_p = extract_functions(trp, ["_reference_prefill", "_make_inputs"])
+    for B, H, S_q, S_kv, D, seed, causal in [(1, 1, 8, 33, 64, 11, False), (2, 2, 33, 200, 128, 12, False),
+                                             (1, 2, 40, 40, 128, 13, True), (2, 1, 5, 77, 64, 14, True)]:
+        q, scale, k_bits, k_mag, k_const, v_idx, v_cents = ns_p["_make_inputs"](B, H, S_q, S_kv, D, seed=seed)
+        ref = ns_p["_reference_prefill"](q, scale, k_bits, k_mag, k_const, v_idx, v_cents, causal=causal)
+        tag = f"pre_B{B}_H{H}_Sq{S_q}_S{S_kv}_D{D}_c{int(causal)}"
+        for k, v in dict(q=q, scale=scale, k_bits=k_bits, k_mag=k_mag, k_const=k_const, v_idx=v_idx, v_cents=v_cents,
+                         out=ref, v_packed=ns_v["_pack_np"](v_idx)).items():
+            out[f"{tag}_{k}"] = v
     resid = np.random.default_rng(8).standard_normal((5, 64)).astype(np.float32)
     out["signs_in"], out["signs_out"] = resid, ns_s["_pack_signs"](resid)
     for d, seed in [(64, 42), (128, 42), (128, 7)]:

@@ -1,0 +1,122 @@
+"""The standalone cache protocol (``KVCache``) and ``EncodedVector``, as the reference's
+``core/abstractions.py:120-189`` and ``core/context.py:72-138`` define them."""
+
+from __future__ import annotations
+
+import math
+
+import numpy as np
+import pytest
+import torch
+
+from veloxquant_mlx_b200.core import EncodedVector, KVCache, StandaloneProtocol
+
+
+def test_kvcache_is_abstract_and_has_the_reference_surface():
+    with pytest.raises(TypeError):
+        KVCache()
+    for name in ("append_key", "append_value", "attend", "memory_bytes", "reset", "append", "__len__"):
+        assert hasattr(KVCache, name)
+
+    class Tiny(KVCache):
+        def __init__(self):
+            self.k, self.v = [], []
+
+        def append_key(self, k):
+            self.k.append(k)
+
+        def append_value(self, v):
+            self.v.append(v)
+
+        def attend(self, q):
+            return q
+
+        def memory_bytes(self):
+            return 0
+
+        def __len__(self):
+            return len(self.v)
+
+    t = Tiny()
+    t.append(1, 2)
+    assert len(t) == 1 and repr(t) == "Tiny(size=1)"
+    with pytest.raises(NotImplementedError):
+        t.reset()
+
+
+def test_encoded_vector_counts_every_array_and_nested_encodings():
+    inner = EncodedVector("turboquant_mse", 2, 4, indices=np.zeros((2, 4), np.uint8))
+    ev = EncodedVector("composite", 2, 8, indices=torch.zeros(2, 8, dtype=torch.uint8), norm=torch.zeros(2, dtype=torch.float16),
+                       signs=np.zeros((2, 16), np.int8), angles=[np.zeros((2, 4), np.float16), np.zeros((2, 2), np.float16)],
+                       outlier_idx=np.arange(3, dtype=np.int32), inlier_encoded=inner)
+    assert ev.memory_bytes() == 16 + 4 + 32 + 16 + 8 + 12 + 8
+    assert EncodedVector("empty", 0, 8).memory_bytes() == 0
+    assert "composite" in repr(ev)
+
+
+def test_every_cache_class_is_a_kvcache():
+    from veloxquant_mlx_b200.cache import KIVIKVCache, RaBitQKVCache, VecInferKVCache
+
+    for cls in (KIVIKVCache, RaBitQKVCache, VecInferKVCache):
+        assert issubclass(cls, KVCache) and issubclass(cls, StandaloneProtocol)
+
+
+def test_standalone_protocol_argument_errors_need_no_gpu():
+    class Fake(StandaloneProtocol):
+        _head_dim = 8
+        offset = 0
+        nbytes = 0
+
+        def _reset_tokens(self):
+            self.offset = 0
+
+    f = Fake()
+    with pytest.raises(RuntimeError, match="append_key comes first"):
+        f.append_value(torch.zeros(8))
+    with pytest.raises(ValueError, match="expected d=8"):
+        f.append_key(torch.zeros(4))
+    with pytest.raises(ValueError, match="shape"):
+        f.append_key(torch.zeros(2, 8))
+    f.append_key(torch.zeros(8))
+    with pytest.raises(RuntimeError, match="still waits"):
+        f.append_key(torch.zeros(8))
+    assert torch.equal(f.attend(torch.ones(8)), torch.zeros(8)) and f.memory_bytes() == 0
+    f.reset()
+    assert f._pending_key is None
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("method", ["kivi", "rabitq", "vecinfer"])
+def test_standalone_calls_equal_the_batched_protocol(method):
+    import warnings
+
+    from veloxquant_mlx_b200.cache import KVCacheConfig, KVCacheFactory
+
+    d, n = 128, 200
+    kw = dict(method=method, head_dim=d)
+    if method == "kivi":
+        kw.update(bit_width_inlier=4, residual_length=64)
+    if method == "vecinfer":
+        kw.update(key_sub_dim=8, value_sub_dim=8, key_codebook_bits=8, value_codebook_bits=8, fused_sdpa=True)
+    g = torch.Generator(device="cuda:0").manual_seed(3)
+    k = torch.randn((n, d), generator=g, device="cuda:0", dtype=torch.float16)
+    v = torch.randn((n, d), generator=g, device="cuda:0", dtype=torch.float16)
+    q = torch.randn((d,), generator=g, device="cuda:0", dtype=torch.float16)
+    with warnings.catch_warnings():
+        warnings.simplefilter("ignore")
+        one, many = KVCacheFactory.create(KVCacheConfig(**kw)), KVCacheFactory.create(KVCacheConfig(**kw))
+    assert isinstance(one, KVCache) and len(one) == 0 and one.memory_bytes() == 0
+    assert torch.equal(one.attend(q), torch.zeros_like(q))
+    for t in range(n):
+        one.append(k[t], v[t])
+        many.update_and_fetch(k[t].view(1, 1, 1, d), v[t].view(1, 1, 1, d))
+    assert len(one) == n and one.memory_bytes() == many.nbytes > 0
+    want = many.fused_sdpa(q.view(1, 1, 1, d), 1.0 / math.sqrt(d)).view(d)
+    got = one.attend(q)
+    assert got.shape == (d,) and got.dtype == q.dtype and torch.equal(got, want)
+    one.reset()
+    assert len(one) == 0 and torch.equal(one.attend(q), torch.zeros_like(q))
+    one.append(k[0], v[0])          # still usable after reset: the quantizer state was kept
+    assert len(one) == 1
+    if method != "vecinfer":        # one token: the output is that token's value (kept exact by these two caches)
+        assert float((one.attend(q).float() - v[0].float()).abs().max()) < 1e-2

@@ -201,3 +201,16 @@ def test_vq_lut_equals_explicit_dot_and_dual_transform_invariance():
     s0 = np.einsum("bhqd,bhsd->bhqs", Q, np.repeat(K, 2, axis=1))
     s1 = np.einsum("bhqd,bhsd->bhqs", Qt, np.repeat(Kt, 2, axis=1))
     np.testing.assert_allclose(s0, s1, rtol=1e-4, atol=1e-4)
+
+
+@pytest.mark.parametrize("tag", ["pre_B1_H1_Sq8_S33_D64_c0", "pre_B2_H2_Sq33_S200_D128_c0", "pre_B1_H2_Sq40_S40_D128_c1",
+                                 "pre_B2_H1_Sq5_S77_D64_c1"])
+def test_rabitq_prefill_matches_reference_numpy(tag):
+    """``oracle.rabitq.reference_prefill`` against the outputs of the reference's own
+    ``_reference_prefill`` (tests/metal/test_rabitq_prefill.py), executed by make_golden.py."""
+    z = _load("rabitq.npz")
+    g = lambda n: z[f"{tag}_{n}"]  # noqa: E731
+    out = rabitq.reference_prefill(g("q"), float(g("scale")[0]), g("k_bits"), g("k_mag"), g("k_const"), g("v_idx"), g("v_cents"),
+                                   causal=tag.endswith("c1"))
+    np.testing.assert_allclose(out, g("out"), rtol=0, atol=1e-6)
+    assert np.array_equal(bitpack.pack(g("v_idx"), 4), g("v_packed"))

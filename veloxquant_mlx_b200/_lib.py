@@ -106,6 +106,17 @@ class RabitqAttendArgs(C.Structure):
     ]
 
 
+class RabitqPrefillArgs(C.Structure):
+    _fields_ = [
+        ("q", C.c_void_p), ("out", C.c_void_p), ("q_dtype", C.c_int32), ("out_dtype", C.c_int32),
+        ("B", C.c_int32), ("H_q", C.c_int32), ("H_kv", C.c_int32), ("S_q", C.c_int32), ("S_kv", C.c_int32),
+        ("D", C.c_int32), ("kv_stride_tok", C.c_int64), ("scale", C.c_float), ("causal", C.c_int32),
+        ("k_bits", C.c_void_p), ("k_mag", C.c_void_p), ("k_const", C.c_void_p),
+        ("v_mode", C.c_int32), ("v_dtype", C.c_int32), ("v", C.c_void_p), ("v_cents", C.c_void_p),
+        ("n_cents", C.c_int32), ("reserved", C.c_int32),
+    ]
+
+
 class VqEncodeArgs(C.Structure):
     _fields_ = [
         ("x", C.c_void_p), ("x_dtype", C.c_int32), ("n_tok", C.c_int64), ("D", C.c_int32), ("sub_dim", C.c_int32),
@@ -155,6 +166,7 @@ SIGNATURES = {
                                             C.c_void_p, C.c_void_p, C.c_void_p]),
     "vq_rabitq_attend_workspace_bytes": (C.c_int64, [C.POINTER(RabitqAttendArgs)]),
     "vq_rabitq_decode_attend": (C.c_int32, [C.POINTER(RabitqAttendArgs), C.c_void_p]),
+    "vq_rabitq_prefill_attend": (C.c_int32, [C.POINTER(RabitqPrefillArgs), C.c_void_p]),
     "vq_bit_pack": (C.c_int32, [C.c_void_p, C.c_int64, C.c_int32, C.c_void_p, C.c_void_p]),
     "vq_bit_unpack": (C.c_int32, [C.c_void_p, C.c_int64, C.c_int32, C.c_void_p, C.c_void_p]),
 }

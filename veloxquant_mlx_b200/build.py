@@ -36,6 +36,7 @@ SOURCES = [
     ("vq_quant_tc5.cu", []),
     ("rabitq.cu", ["-fmad=false"]),
     ("coded_attend.cu", []),
+    ("rabitq_prefill.cu", []),
 ]
 
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]

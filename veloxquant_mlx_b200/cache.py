@@ -29,6 +29,7 @@ from typing import Any
 import torch
 
 from . import _lib, kernels
+from .core import EncodedVector, KVCache, StandaloneProtocol
 
 
 class QuantizerConfigError(ValueError):
@@ -249,7 +250,7 @@ def _paired_view(keys: torch.Tensor, values: torch.Tensor):
     return torch.as_strided(keys, (2, *keys.shape), (delta, *keys.stride()), keys.storage_offset())
 
 
-class KIVIKVCache:
+class KIVIKVCache(StandaloneProtocol):
     """Packed KIVI cache: per-channel keys, per-token values, fp residual window.
 
     Storage (grown geometrically): packed codes ``u8 [B,H,cap,D*sb/8]``, key params
@@ -615,8 +616,11 @@ class KIVIKVCache:
     def size(self) -> int:
         return self.offset
 
-    def __len__(self) -> int:
-        return self.offset
+    def _reset_tokens(self) -> None:
+        """Forget every token; buffers, bit-width and group size stay (``KVCache.reset``)."""
+        self.offset = self._n_quantized = self._n_res = self._res_lo = 0
+        self._key_bytes_compressed = self._value_bytes_compressed = 0
+        self._key_bytes_fp16 = self._value_bytes_fp16 = self._residual_fp16_bytes = self._tokens_seen = 0
 
     @property
     def state(self):
@@ -654,6 +658,38 @@ class KIVIKVCache:
         self._ensure_residual(B, H, D, n_res, kr.device, kr.dtype)
         self._k_res[:, :, :n_res], self._v_res[:, :, :n_res] = kr, vr
         self._n_res = n_res
+
+    @property
+    def meta_state(self):
+        """What ``state`` does not carry, as strings (the convention of the reference's caches,
+        ``cache/turboquant_rvq_cache.py:396-405``): ``(head_dim, bits, group, residual_length,
+        offset, n_quantized, n_residual)``."""
+        return tuple(map(str, (self._head_dim, self._b, self._group_size, self._residual_length, self.offset,
+                               self._n_quantized, self._n_res)))
+
+    @meta_state.setter
+    def meta_state(self, v) -> None:
+        hd, b, g, r, off, nq, n_res = (int(x) for x in v)
+        if not 1 <= b <= 8 or g < 1 or (hd * kernels.storage_bits(b)) % 8:
+            raise QuantizerConfigError(f"KIVIKVCache.meta_state: unusable configuration {tuple(v)}")
+        self._head_dim, self._b, self._group_size, self._residual_length = hd, b, g, r
+        self._levels, self._sb = (1 << b) - 1, kernels.storage_bits(b)
+        self.offset, self._n_quantized, self._n_res = off, nq, n_res
+        if off == 0:
+            self._reset_tokens()
+
+    @classmethod
+    def from_state(cls, state, meta_state=None, config=None):
+        """A cache rebuilt from ``state`` and ``meta_state`` (``config`` supplies the flags that are
+        neither: ``fused_sdpa_memory_bound``, ``capacity``)."""
+        if meta_state is None:
+            raise TypeError("KIVIKVCache.from_state() requires meta_state")
+        hd, b, g, r = (int(x) for x in meta_state[:4])
+        cfg = config if config is not None else KVCacheConfig(method="kivi")
+        obj = cls(dataclasses.replace(cfg, method="kivi", head_dim=hd, bit_width_inlier=b, kivi_group_size=g, residual_length=r))
+        obj.meta_state = meta_state
+        obj.state = state
+        return obj
 
     def merge(self, *a, **k):
         raise NotImplementedError("KIVIKVCache.merge: batched-cache merging is not supported")
@@ -734,4 +770,4 @@ _CACHE_CLASS_BY_METHOD["kivi"] = KIVIKVCache
 from .cache_coded import RaBitQKVCache, VecInferKVCache  # noqa: E402  (registers "vecinfer", "rabitq")
 
 __all__ = ["QuantizerConfigError", "VecInferOptions", "KIVIOptions", "KVCacheConfig", "KVCacheFactory",
-           "KVCacheBuilder", "KIVIKVCache", "VecInferKVCache", "RaBitQKVCache"]
+           "KVCacheBuilder", "KIVIKVCache", "VecInferKVCache", "RaBitQKVCache", "KVCache", "EncodedVector"]

@@ -14,6 +14,7 @@ import torch
 from . import rabitq as rq
 from . import vecinfer as vi
 from .cache import QuantizerConfigError, _CACHE_CLASS_BY_METHOD, _native_only
+from .core import StandaloneProtocol
 
 _SMOOTH_FLOOR = 1e-8
 
@@ -25,7 +26,7 @@ def _grow(old, shape, dtype, device):
     return t
 
 
-class VecInferKVCache:
+class VecInferKVCache(StandaloneProtocol):
     """Keys dual-transformed (smooth + Hadamard) and product-VQ coded on append; values
     product-VQ coded. Only codebook indices are stored (one byte each for <= 256 centroids);
     :meth:`fused_sdpa` attends over them through a per-query lookup table.
@@ -179,6 +180,16 @@ class VecInferKVCache:
         self.offset -= n
         return n
 
+    def _reset_tokens(self) -> None:
+        self.offset = 0
+        self._key_bytes_fp16 = self._value_bytes_fp16 = 0
+
+    def check_status(self) -> None:
+        """Raise if a bounded device-side wait of an earlier quantize or attention call ran out."""
+        from . import kernels
+        kernels.quantize_status()
+        kernels.attend_status()
+
     def is_trimmable(self) -> bool:
         return True
 
@@ -206,6 +217,24 @@ class VecInferKVCache:
         self._k_idx[:, :, :n], self._v_idx[:, :, :n] = k, v
         self.offset = n
 
+    @property
+    def meta_state(self):
+        """``(head_dim, key_sub_dim, value_sub_dim, key_codebook_bits, value_codebook_bits, offset)``
+        as strings; the codebooks and smooth factors are configuration, not state."""
+        return tuple(map(str, (self._head_dim, self._key_sub_dim, self._value_sub_dim, self._key_bits, self._value_bits,
+                               self.offset)))
+
+    @meta_state.setter
+    def meta_state(self, v) -> None:
+        hd, ks, vs, kb, vb, off = (int(x) for x in v)
+        mine = (self._head_dim, self._key_sub_dim, self._value_sub_dim, self._key_bits, self._value_bits)
+        if (hd, ks, vs, kb, vb) != mine:
+            raise QuantizerConfigError(
+                f"VecInferKVCache.meta_state: stored indices were made with (head_dim, sub_dims, bits) = {(hd, ks, vs, kb, vb)}, "
+                f"this cache is configured with {mine}; indices are only meaningful with their own codebooks")
+        if off == 0:
+            self._reset_tokens()
+
     def merge(self, *a, **k):
         raise NotImplementedError("VecInferKVCache.merge: batched-cache merging is not supported")
 
@@ -222,7 +251,7 @@ class VecInferKVCache:
         return (self._key_bits / self._key_sub_dim + self._value_bits / self._value_sub_dim) / 2.0
 
 
-class RaBitQKVCache:
+class RaBitQKVCache(StandaloneProtocol):
     """1-bit keys (seeded randomized-Hadamard rotation, sign bits, L1 magnitude per key) with
     values kept in the activation dtype -- the pairing the reference documents for RaBitQ
     (``docs-site/docs/algorithms/rabitq.md:12``). Centroid-free: the score of key ``t`` is
@@ -236,7 +265,8 @@ class RaBitQKVCache:
         self._head_dim = D = int(config.head_dim)
         if D & (D - 1) or D % 32 or D > 256:
             raise QuantizerConfigError(f"RaBitQKVCache: head_dim={D} must be a power of 2 in 32..256.")
-        self._diag_np = rq.make_hadamard_diagonal(D, seed=int(getattr(config, "seed", 42)))
+        self._seed = int(getattr(config, "seed", 42))
+        self._diag_np = rq.make_hadamard_diagonal(D, seed=self._seed)
         self._diag = self._H = None
         self._bits = self._mag = self._v = None
         self.offset = 0
@@ -246,6 +276,19 @@ class RaBitQKVCache:
             self._diag = torch.from_numpy(self._diag_np).to(device)
             self._H = vi.walsh_hadamard_matrix(self._head_dim, device=device)
 
+    def _ensure_capacity(self, B, H, n, v_dtype, device) -> None:
+        cap = 0 if self._bits is None else self._bits.shape[2]
+        if n <= cap:
+            return
+        D = self._head_dim
+        new_cap = max(256, cap)
+        while new_cap < n:
+            new_cap *= 2
+        self._bits = _grow(self._bits, (B, H, new_cap, D // 8), torch.uint8, device)
+        self._mag = _grow(None if self._mag is None else self._mag[..., None], (B, H, new_cap, 1), torch.float32,
+                          device)[..., 0].contiguous()
+        self._v = _grow(self._v, (B, H, new_cap, D), v_dtype, device)
+
     def update_and_fetch(self, keys: torch.Tensor, values: torch.Tensor):
         if keys.ndim != 4 or keys.shape != values.shape:
             raise ValueError("RaBitQKVCache.update_and_fetch: keys/values must be equal 4D shapes")
@@ -254,15 +297,7 @@ class RaBitQKVCache:
             raise QuantizerConfigError(f"RaBitQKVCache: expected head_dim {self._head_dim}, got {D}.")
         self._to_device(keys.device)
         n = self.offset + S
-        cap = 0 if self._bits is None else self._bits.shape[2]
-        if n > cap:
-            new_cap = max(256, cap)
-            while new_cap < n:
-                new_cap *= 2
-            self._bits = _grow(self._bits, (B, H, new_cap, D // 8), torch.uint8, keys.device)
-            self._mag = _grow(None if self._mag is None else self._mag[..., None], (B, H, new_cap, 1), torch.float32,
-                              keys.device)[..., 0].contiguous()
-            self._v = _grow(self._v, (B, H, new_cap, D), values.dtype, keys.device)
+        self._ensure_capacity(B, H, n, values.dtype, keys.device)
         bits, mag = rq.rabitq_encode(keys.reshape(B * H * S, D), self._diag)
         self._bits[:, :, self.offset : n] = bits.view(B, H, S, D // 8)
         self._mag[:, :, self.offset : n] = mag.view(B, H, S)
@@ -272,13 +307,23 @@ class RaBitQKVCache:
         return z, z
 
     def fused_sdpa(self, q: torch.Tensor, scale: float, *, causal: bool = True, sliding_window: int = 0):
+        """One query row: the popcount estimator of the decode kernel. Several rows (a prompt
+        chunk): the tiled kernel, whose scores are exact dots of the rotated query with the
+        decoded keys ``signs * mag`` -- the same pairing of two score models as the reference's
+        ``rabitq_fused_attend`` / ``rabitq_prefill_attend``; ``causal`` aligns the rows to the
+        tail of the cache."""
         if q.ndim != 4:
             raise ValueError(f"RaBitQKVCache.fused_sdpa: q must be 4D, got {tuple(q.shape)}")
-        if sliding_window or (causal and q.shape[2] != 1):
-            raise ValueError("RaBitQKVCache.fused_sdpa: one query row per call, no window (every row sees every slot)")
+        if sliding_window:
+            raise ValueError("RaBitQKVCache.fused_sdpa: sliding_window is not supported")
         if self.offset == 0:
             raise RuntimeError("RaBitQKVCache.fused_sdpa: the cache is empty")
         q_rot = (q.to(torch.float32) * self._diag) @ self._H  # = WHT(q*diag)/sqrt(D)
+        if q.shape[2] > 1:
+            if causal and q.shape[2] > self.offset:
+                raise ValueError(f"RaBitQKVCache.fused_sdpa: {q.shape[2]} query rows but only {self.offset} cached tokens")
+            return rq.rabitq_prefill_attend(q_rot.to(torch.float16), float(scale), self._bits, self._mag, None, self._v, None,
+                                            causal=bool(causal), s_kv=self.offset, out_dtype=q.dtype)
         q_scale = q_rot.abs().mean(dim=-1) * float(scale)
         return rq.rabitq_fused_attend(q_rot, q_scale, self._bits, self._mag, None, self._v, None, s_kv=self.offset,
                                       out_dtype=q.dtype)
@@ -287,6 +332,17 @@ class RaBitQKVCache:
         n = int(min(max(n, 0), self.offset))
         self.offset -= n
         return n
+
+    def _reset_tokens(self) -> None:
+        self.offset = 0
+
+    def check_status(self) -> None:
+        """Raise if a bounded device-side wait of an earlier attention call ran out."""
+        from . import kernels
+        kernels.attend_status()
+
+    def is_trimmable(self) -> bool:
+        return True
 
     def empty(self) -> bool:
         return self.offset == 0
@@ -306,7 +362,31 @@ class RaBitQKVCache:
             return
         bits, mag, v = st
         self._to_device(bits.device)
-        self._bits, self._mag, self._v, self.offset = bits.clone(), mag.clone(), v.clone(), bits.shape[2]
+        B, H, n = bits.shape[:3]
+        # the same capacity rule as a cache that grew to n tokens by appends (the attention kernel
+        # picks its path by the buffers' row pitch, so a restored cache must not differ there)
+        self._bits = self._mag = self._v = None
+        self._ensure_capacity(B, H, n, v.dtype, bits.device)
+        self._bits[:, :, :n], self._mag[:, :, :n], self._v[:, :, :n] = bits, mag, v
+        self.offset = n
+
+    @property
+    def meta_state(self):
+        """``(head_dim, rotation seed, offset)`` as strings: the sign bits are only meaningful with
+        the rotation they were made with."""
+        return tuple(map(str, (self._head_dim, self._seed, self.offset)))
+
+    @meta_state.setter
+    def meta_state(self, v) -> None:
+        hd, seed, off = (int(x) for x in v)
+        if hd != self._head_dim:
+            raise QuantizerConfigError(f"RaBitQKVCache.meta_state: stored head_dim {hd}, configured {self._head_dim}")
+        if seed != self._seed:
+            self._seed = seed
+            self._diag_np = rq.make_hadamard_diagonal(hd, seed=seed)
+            self._diag = self._H = None
+        if off == 0:
+            self._reset_tokens()
 
     @property
     def nbytes(self) -> int:

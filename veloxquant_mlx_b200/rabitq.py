@@ -10,7 +10,7 @@ import ctypes as C
 import numpy as np
 import torch
 
-from ._lib import RabitqAttendArgs, check, dtype_code, lib, require_cuda, stream_ptr
+from ._lib import RabitqAttendArgs, RabitqPrefillArgs, check, dtype_code, lib, require_cuda, stream_ptr
 from .kernels import _FLOAT_DTYPES, _workspace
 
 
@@ -174,5 +174,69 @@ def rabitq_fused_attend(q, q_scale, k_bits, k_mag, k_const, v_idx, v_cents=None,
     return out
 
 
-__all__ = ["make_hadamard_diagonal", "make_rotation_matrix", "rabitq_encode", "rabitq_encode_rotated",
+def rabitq_prefill_attend(q, scale, k_bits, k_mag, k_const, v_idx, v_cents=None, *, causal: bool = False,
+                          s_kv=None, out_dtype=torch.float16) -> torch.Tensor:
+    """Tiled attention of many query rows over sign-bit keys (``metal/_rabitq_prefill.py:116-196``).
+
+    ``q [B,H_q,S_q,D]``; ``scale`` a float (or one-element tensor); ``k_bits [B,H_kv,S,D/8]``;
+    ``k_mag`` / ``k_const [B,H_kv,S]`` (``k_const`` may be ``None``); values nibble-packed
+    ``u8 [B,H_kv,S,D/2]`` with ``v_cents [<=16]`` (the reference form) or, with ``v_cents=None``,
+    a dense f16 / bf16 ``[B,H_kv,S,D]`` tensor. Scores are exact dots with the decoded keys
+    ``signs * k_mag`` (not the popcount estimator of :func:`rabitq_fused_attend`). ``causal=True``
+    aligns the queries to the tail of the cache (``q_abs = S_kv - S_q + q_pos``).
+    """
+    fn = "rabitq_prefill_attend"
+    if q.ndim != 4:
+        raise ValueError(f"{fn}: q must be 4D, got {tuple(q.shape)}")
+    B, H, S_q, D = q.shape
+    if D % 8 != 0:
+        raise ValueError(f"{fn}: D={D} must be divisible by 8")
+    if D not in (64, 128):
+        raise ValueError(f"{fn}: D={D} must be 64 or 128")
+    n_bytes = D // 8
+    if k_bits.ndim != 4 or k_bits.shape[0] != B or k_bits.shape[3] != n_bytes or H % k_bits.shape[1] != 0:
+        raise ValueError(f"{fn}: k_bits must be [B, H_kv, S_kv, {n_bytes}] with H_kv dividing {H}, got {tuple(k_bits.shape)}")
+    H_kv, cap = k_bits.shape[1], k_bits.shape[2]
+    S_kv = cap if s_kv is None else int(s_kv)
+    if tuple(k_mag.shape) != (B, H_kv, cap):
+        raise ValueError(f"{fn}: k_mag must be {(B, H_kv, cap)}, got {tuple(k_mag.shape)}")
+    if k_const is not None and tuple(k_const.shape) != (B, H_kv, cap):
+        raise ValueError(f"{fn}: k_const must be {(B, H_kv, cap)}, got {tuple(k_const.shape)}")
+    if causal and S_q > S_kv:
+        raise ValueError(f"{fn}: causal attention of {S_q} query rows over {S_kv} slots")
+    if q.dtype not in _FLOAT_DTYPES:
+        raise ValueError(f"{fn}: unsupported q dtype {q.dtype}")
+    if isinstance(scale, torch.Tensor):
+        scale = float(scale.reshape(-1)[0])
+    require_cuda(q, f"{fn}: q")
+    q = q.contiguous()
+    out = torch.empty((B, H, S_q, D), dtype=out_dtype, device=q.device)
+    kb = k_bits.to(torch.uint8).contiguous()
+    km = k_mag.to(torch.float32).contiguous()
+    kc = None if k_const is None else k_const.to(torch.float32).contiguous()
+    a = RabitqPrefillArgs(q=q.data_ptr(), out=out.data_ptr(), q_dtype=dtype_code(q.dtype), out_dtype=dtype_code(out_dtype),
+                          B=B, H_q=H, H_kv=H_kv, S_q=S_q, S_kv=S_kv, D=D, kv_stride_tok=cap, scale=float(scale),
+                          causal=1 if causal else 0, k_bits=kb.data_ptr(), k_mag=km.data_ptr(),
+                          k_const=None if kc is None else kc.data_ptr())
+    if v_cents is None:
+        if tuple(v_idx.shape) != (B, H_kv, cap, D) or v_idx.dtype not in (torch.float16, torch.bfloat16):
+            raise ValueError(f"{fn}: dense values must be f16 / bf16 {(B, H_kv, cap, D)}, got {tuple(v_idx.shape)} {v_idx.dtype}")
+        v = v_idx.contiguous()
+        a.v_mode, a.v, a.v_dtype = 0, v.data_ptr(), dtype_code(v.dtype)
+        cents = None
+    else:
+        if tuple(v_idx.shape) != (B, H_kv, cap, D // 2):
+            raise ValueError(f"{fn}: v_idx must be nibble-packed {(B, H_kv, cap, D // 2)} (see rabitq_pack_values), "
+                             f"got {tuple(v_idx.shape)}")
+        if v_cents.ndim != 1 or v_cents.shape[0] > 16:
+            raise ValueError(f"{fn}: v_cents must be 1D with <= 16 entries, got {tuple(v_cents.shape)}")
+        v = v_idx.to(torch.uint8).contiguous()
+        cents = v_cents.to(device=q.device, dtype=torch.float32).contiguous()
+        a.v_mode, a.v, a.v_cents, a.n_cents = 3, v.data_ptr(), cents.data_ptr(), cents.shape[0]
+    with torch.cuda.device(q.device):
+        check(lib().vq_rabitq_prefill_attend(C.byref(a), stream_ptr(q.device)), fn)
+    return out
+
+
+__all__ = ["rabitq_prefill_attend", "make_hadamard_diagonal", "make_rotation_matrix", "rabitq_encode", "rabitq_encode_rotated",
            "rabitq_pack_values", "rabitq_hamming_score", "rabitq_fused_attend"]
