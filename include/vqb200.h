@@ -364,6 +364,18 @@ typedef struct vq_vq_encode_args {
 int32_t vq_vq_encode_decode_keys(const vq_vq_encode_args *args, void *stream);
 int32_t vq_vq_encode_decode_values(const vq_vq_encode_args *args, void *stream);
 
+/* The dual transform with a defined float32 order: y = WHT(x / smooth) * c for keys
+ * (divide != 0), y = WHT(x * smooth) * c for queries, where WHT is the unnormalised Sylvester
+ * butterfly (pairs (lower + upper, lower - upper), strides 1, 2, 4, ...) and c the common entry
+ * magnitude of the orthonormal Walsh-Hadamard matrix. x is [n_rows, D] (dtype x_dtype), out
+ * float32 [n_rows, D]; row r belongs to head (r / tok_per_head) % n_heads and uses smooth row
+ * head % smooth_rows; smooth may be NULL. D is 32, 64, 128 or 256. Replaces
+ * apply_dual_transform_keys / _queries (veloxquant_mlx/allocators/vecinfer.py:93-184), which
+ * multiply by the dense matrix in an unspecified summation order. */
+int32_t vq_vq_dual_transform(const void *x, int32_t x_dtype, int64_t n_rows, int32_t D, int64_t tok_per_head,
+                             int32_t n_heads, const float *smooth, int32_t smooth_rows, int32_t divide, float c,
+                             float *out, void *stream);
+
 /* Attention over VQ-coded keys scored through a per-query lookup table
  * lut[s][c] = q_sub[s] . codebook[c], score = scale * sum_s lut[s][idx[s]]; values are either
  * VQ-coded (indices + codebook: the reference form) or a dense tensor. Tail-aligned causal

@@ -129,6 +129,39 @@ def apply_dual_transform_queries(q, smooth, H):
     return (q * _smooth_for(q, smooth, True)) @ np.asarray(H).astype(q.dtype)
 
 
+def _wht_fixed_order(x: np.ndarray, D: int) -> np.ndarray:
+    """Unnormalised Sylvester butterfly over the last axis in float32 (pairs (lower + upper,
+    lower - upper), strides 1, 2, 4, ...), then one multiplication by the common entry
+    magnitude of ``walsh_hadamard_matrix(D)``."""
+    y = np.ascontiguousarray(x, dtype=np.float32).reshape(-1, D).copy()
+    h = 1
+    while h < D:
+        y = y.reshape(-1, D // (2 * h), 2, h)
+        lo, up = y[:, :, 0, :].copy(), y[:, :, 1, :].copy()
+        y[:, :, 0, :] = lo + up
+        y[:, :, 1, :] = lo - up
+        y = y.reshape(-1, D)
+        h *= 2
+    c = walsh_hadamard_matrix(D)[0, 0]
+    return (y * c).astype(np.float32).reshape(x.shape)
+
+
+def dual_transform_keys_wht(K, smooth=None):
+    """``WHT(K / lambda)`` with the fixed summation order the native butterfly uses: the same
+    mathematics as :func:`apply_dual_transform_keys` with the Walsh-Hadamard matrix, whose
+    matrix-product order the reference leaves to its framework."""
+    K = np.asarray(K).astype(np.float32)
+    x = K if smooth is None else (K / _smooth_for(K, np.asarray(smooth, np.float32), False)).astype(np.float32)
+    return _wht_fixed_order(x, K.shape[-1])
+
+
+def dual_transform_queries_wht(q, smooth=None):
+    """``WHT(q * lambda)``, the query side of :func:`dual_transform_keys_wht`."""
+    q = np.asarray(q).astype(np.float32)
+    x = q if smooth is None else (q * _smooth_for(q, np.asarray(smooth, np.float32), True)).astype(np.float32)
+    return _wht_fixed_order(x, q.shape[-1])
+
+
 def reference_sdpa(q_tilde, k_indices, k_codebook, v, scale, *, v_codebook=None,
                    causal=True, sliding_window=0) -> np.ndarray:
     """Dense fp32 attention over VQ keys in the transformed space.

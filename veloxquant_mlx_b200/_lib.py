@@ -157,6 +157,8 @@ SIGNATURES = {
     "vq_vq_quantize_status": (C.c_int32, []),
     "vq_vq_dequant": (C.c_int32, [C.c_void_p, C.c_int32, C.c_int64, C.c_void_p, C.c_int32, C.c_int32, C.c_int32,
                                   C.c_void_p, C.c_int32, C.c_void_p]),
+    "vq_vq_dual_transform": (C.c_int32, [C.c_void_p, C.c_int32, C.c_int64, C.c_int32, C.c_int64, C.c_int32, C.c_void_p,
+                                         C.c_int32, C.c_int32, C.c_float, C.c_void_p, C.c_void_p]),
     "vq_vq_attend_workspace_bytes": (C.c_int64, [C.POINTER(VqAttendArgs)]),
     "vq_vq_decode_attend": (C.c_int32, [C.POINTER(VqAttendArgs), C.c_void_p]),
     "vq_rabitq_encode": (C.c_int32, [C.c_void_p, C.c_int32, C.c_int64, C.c_int32, C.c_void_p, C.c_int32,

@@ -32,6 +32,7 @@ SOURCES = [
     ("peer_gather.cu", []),
     ("vq_quant.cu", ["-fmad=false"]),
     ("vq_encode.cu", ["-fmad=false"]),
+    ("vq_transform.cu", ["-fmad=false"]),
     ("vq_quant_mma.cu", []),
     ("vq_quant_tc5.cu", []),
     ("rabitq.cu", ["-fmad=false"]),

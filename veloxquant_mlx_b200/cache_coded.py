@@ -145,7 +145,8 @@ class VecInferKVCache(StandaloneProtocol):
         self._to_device(keys.device)
         self._resolve_smooth_heads(H)
         self._ensure_index_capacity(B, H, self.offset + S, keys.device)
-        k_tilde = vi.apply_dual_transform_keys(keys.to(torch.float32), self._smooth_or_ones(keys.device), self._H)
+        # smooth divide + Walsh-Hadamard butterfly in one native launch, fixed summation order
+        k_tilde = vi.dual_transform_keys_wht(keys, self._smooth)
         lo, hi = self.offset, self.offset + S
         self._k_idx[:, :, lo:hi] = vi.quantize_vq(k_tilde, self._key_codebook, self._key_sub_dim, index_dtype=self._k_idx.dtype)
         self._v_idx[:, :, lo:hi] = vi.quantize_vq(values, self._value_codebook, self._value_sub_dim, index_dtype=self._v_idx.dtype)
@@ -171,7 +172,7 @@ class VecInferKVCache(StandaloneProtocol):
         scored by table lookup, values are gathered from their codebook."""
         if self.offset == 0:
             raise RuntimeError("VecInferKVCache.fused_sdpa: the cache is empty")
-        q_tilde = vi.apply_dual_transform_queries(q.to(torch.float32), self._smooth_or_ones(q.device), self._H)
+        q_tilde = vi.dual_transform_queries_wht(q, self._smooth)
         return vi.fused_sdpa_vq(q_tilde, self._k_idx, self._key_codebook, self._v_idx, self._value_codebook, scale,
                                 causal=causal, sliding_window=sliding_window, out_dtype=q.dtype, s_kv=self.offset)
 
@@ -318,7 +319,7 @@ class RaBitQKVCache(StandaloneProtocol):
             raise ValueError("RaBitQKVCache.fused_sdpa: sliding_window is not supported")
         if self.offset == 0:
             raise RuntimeError("RaBitQKVCache.fused_sdpa: the cache is empty")
-        q_rot = (q.to(torch.float32) * self._diag) @ self._H  # = WHT(q*diag)/sqrt(D)
+        q_rot = vi.dual_transform_queries_wht(q, self._diag)  # = WHT(q*diag)/sqrt(D), native butterfly
         if q.shape[2] > 1:
             if causal and q.shape[2] > self.offset:
                 raise ValueError(f"RaBitQKVCache.fused_sdpa: {q.shape[2]} query rows but only {self.offset} cached tokens")

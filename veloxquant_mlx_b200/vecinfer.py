@@ -1,12 +1,15 @@
 """VecInfer product-VQ wrappers on ``torch.Tensor`` (reference: ``allocators/vecinfer.py``,
 ``metal/_vecinfer.py``, ``metal/fused_sdpa.py``). The nearest-centroid search, the gather and
-the LUT attention run in ``libvqb200.so``; the dual transform is an elementwise scale and a
-D x D matmul (a plain library GEMM) as in the reference.
+the LUT attention run in ``libvqb200.so``. The dual transform exists twice: as the reference
+writes it (an elementwise scale and a D x D matrix product with any matrix ``H``), and, for the
+Walsh-Hadamard matrix itself, as a native butterfly with a fixed summation order
+(``dual_transform_*_wht``), which is what the caches use.
 """
 
 from __future__ import annotations
 
 import ctypes as C
+import functools
 import math
 
 import numpy as np
@@ -57,6 +60,60 @@ def apply_dual_transform_queries(q: torch.Tensor, smooth: torch.Tensor, H: torch
     """``q_tilde = (q * lambda) @ H``; per-KV-head factors repeat over their query group
     (``allocators/vecinfer.py:137-184``)."""
     return (q * _smooth_for(q, smooth, True, "apply_dual_transform_queries")) @ H.to(q.dtype)
+
+
+@functools.lru_cache(maxsize=None)
+def wht_entry(d: int) -> float:
+    """The common entry magnitude of :func:`walsh_hadamard_matrix` ``(d)``, computed by the same
+    float32 recurrence (one multiplication by ``1/sqrt(2)`` per doubling)."""
+    if d < 1 or (d & (d - 1)) != 0:
+        raise ValueError(f"wht_entry: d={d} must be a power of 2.")
+    c = np.array([[1.0]], dtype=np.float32)
+    inv_sqrt2 = 1.0 / math.sqrt(2.0)
+    size = 1
+    while size < d:
+        c = c * inv_sqrt2
+        size *= 2
+    return float(c[0, 0])
+
+
+def _dual_transform_wht(x: torch.Tensor, smooth, for_query: bool, who: str) -> torch.Tensor:
+    if x.ndim < 1 or x.shape[-1] not in (32, 64, 128, 256):
+        raise ValueError(f"{who}: head_dim={x.shape[-1] if x.ndim else None} must be 32, 64, 128 or 256")
+    if x.dtype not in _FLOAT_DTYPES:
+        raise ValueError(f"{who}: unsupported dtype {x.dtype}")
+    require_cuda(x, f"{who}: x")
+    D = x.shape[-1]
+    x = x.contiguous()
+    n_rows = x.numel() // D
+    sm_ptr, rows, n_heads, tph = None, 0, 1, max(n_rows, 1)
+    if smooth is not None:
+        # (the broadcasting rule only looks at the shape: a storage-less stand-in of x's shape)
+        sm = _smooth_for(torch.empty(x.shape, dtype=torch.float32, device="meta"), smooth.to(torch.float32), for_query, who)
+        sm = sm.to(device=x.device, dtype=torch.float32)
+        if sm.ndim == 1:
+            sm2, n_heads, tph = sm.reshape(1, D).contiguous(), 1, max(n_rows, 1)
+        else:  # [heads, 1, D]: one row per head of x's axis -3
+            sm2, n_heads, tph = sm.reshape(-1, D).contiguous(), x.shape[-3], x.shape[-2]
+        sm_ptr, rows = sm2.data_ptr(), sm2.shape[0]
+    out = torch.empty(x.shape, dtype=torch.float32, device=x.device)
+    with torch.cuda.device(x.device):
+        check(lib().vq_vq_dual_transform(x.data_ptr(), dtype_code(x.dtype), n_rows, D, tph, n_heads, sm_ptr, rows,
+                                         0 if for_query else 1, wht_entry(D), out.data_ptr(), stream_ptr(x.device)), who)
+    return out
+
+
+def dual_transform_keys_wht(K: torch.Tensor, smooth=None) -> torch.Tensor:
+    """``K_tilde = WHT(K / lambda)``: :func:`apply_dual_transform_keys` for the Walsh-Hadamard
+    matrix itself, as a butterfly with a fixed float32 summation order (so that the VQ indices
+    of the transformed keys are reproducible bit for bit) instead of a matrix product. float32
+    result; ``smooth`` as in :func:`apply_dual_transform_keys` or ``None``."""
+    return _dual_transform_wht(K, smooth, False, "dual_transform_keys_wht")
+
+
+def dual_transform_queries_wht(q: torch.Tensor, smooth=None) -> torch.Tensor:
+    """``q_tilde = WHT(q * lambda)``, the query side of :func:`dual_transform_keys_wht`."""
+    return _dual_transform_wht(q, smooth, True, "dual_transform_queries_wht")
 
 
 def _codebook_f32(codebook: torch.Tensor, who: str):
