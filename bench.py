@@ -612,8 +612,11 @@ def run_e2e(torch, dist, timer, w, plan, world, device, dtype, caches, outs, px,
                 upload(ci + 1)
             main.wait_event(ev_in[ci])
             for l in ch:
-                caches[l].update_and_fetch(dk[l], dv[l])
-                caches[l].fused_sdpa(dq[l], scale, out=e2e_outs[l], gather=px.layer(l) if px is not None else None)
+                # (the new token and the query come from the upload stream, never from the kernels
+                # right before these calls: both may start under the previous layer's attention)
+                caches[l].update_and_fetch(dk[l], dv[l], overlap_previous=True)
+                caches[l].fused_sdpa(dq[l], scale, out=e2e_outs[l], overlap_previous=True,
+                                     gather=px.layer(l) if px is not None else None)
                 if px is not None:
                     px.wait(l)
                 if gather_mode == "nccl":
@@ -637,11 +640,11 @@ def run_e2e(torch, dist, timer, w, plan, world, device, dtype, caches, outs, px,
         e2e_step()
     timer.barrier()
     n_steps = max(args.steps, g) * 2  # two flush periods at least
-    alloc0 = torch.cuda.memory_stats(device).get("allocation.all.allocated", 0)
     per_step = []
     flush_steps = []
-    t_all0 = time.perf_counter()
     timer.barrier()
+    alloc0 = torch.cuda.memory_stats(device).get("allocation.all.allocated", 0)
+    t_all0 = time.perf_counter()
     for i in range(n_steps):
         nq_before = caches[0]._n_quantized
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -652,9 +655,9 @@ def run_e2e(torch, dist, timer, w, plan, world, device, dtype, caches, outs, px,
         per_step.append(e0.elapsed_time(e1))
         if caches[0]._n_quantized != nq_before:
             flush_steps.append(i)
-    timer.barrier()
     alloc1 = torch.cuda.memory_stats(device).get("allocation.all.allocated", 0)
     wall_ms = (time.perf_counter() - t_all0) * 1e3 / n_steps
+    timer.barrier()
     t = torch.tensor([float(np.mean(per_step)), float(np.median(per_step)),
                       float(np.mean([per_step[i] for i in flush_steps])) if flush_steps else 0.0],
                      device=device, dtype=torch.float64)
@@ -838,8 +841,8 @@ def run_c5(torch, dist, timer, world, rank, device, dtype, args):
 
     def dec_step():
         for l in range(L):
-            caches[l].update_and_fetch(kn, vn)
-            caches[l].fused_sdpa(qs[l], scale, out=outs[l], gather=px.layer(l) if px is not None else None)
+            caches[l].update_and_fetch(kn, vn, overlap_previous=True)
+            caches[l].fused_sdpa(qs[l], scale, out=outs[l], overlap_previous=True, gather=px.layer(l) if px is not None else None)
             if px is not None:
                 px.wait(l)
 

@@ -126,10 +126,14 @@ int32_t vq_kivi_quant_dequant(const vq_kivi_quant_args *args, void *stream);
  * k_new + (s*new_stride_bh + r*head_dim) elements and written to
  * k_res + (s*res_stride_bh + (tok_offset + r)*head_dim) elements; likewise for the values.
  * dtype: VQ_F16, VQ_BF16 or VQ_F32. Rows must be multiples of 16 bytes, the four pointers
- * 16-byte aligned and both strides multiples of 16 bytes (VQ_ERR_ALIGN otherwise). */
+ * 16-byte aligned and both strides multiples of 16 bytes (VQ_ERR_ALIGN otherwise).
+ * flags: 0, or VQ_ATTEND_OVERLAP_PREVIOUS: the copy may start while the preceding work on the
+ * stream still runs (its loads of k_new / v_new then must not depend on that work); its stores
+ * wait for that work to finish, and a vq_kivi_decode_attend with the same flag that follows
+ * may start at once (it reads the residual rows only after this copy has completed). */
 int32_t vq_kivi_append(const void *k_new, const void *v_new, int64_t new_stride_bh, void *k_res, void *v_res,
                        int64_t res_stride_bh, int64_t n_bh, int64_t n_new, int64_t tok_offset, int32_t head_dim,
-                       int32_t dtype, void *stream);
+                       int32_t dtype, int32_t flags, void *stream);
 
 /* Flat dequantization code*scale+zero of one K (axis 0) or V (axis 1) tensor to
  * f16/bf16/f32. Replaces scalar_decode_once (veloxquant_mlx/metal/_scalar_attend.py:650-699,
@@ -193,12 +197,13 @@ typedef struct vq_kivi_attend_args {
                                  to the other ranks of a sharded run (see vq_peer_gather) */
 } vq_kivi_attend_args;
 /* The attention kernel may begin while the work that precedes this call on the stream is still
- * running (programmatic dependent launch): its prologue and its reads of the packed cache then
+ * running (programmatic dependent launch): its prologue and its pass over the packed cache then
  * hide the previous kernels' drain, e.g. the previous layer's vq_kivi_decode_attend. The caller
- * promises that every INPUT of this call (q, codes, scales, zeros, residual rows) was complete
- * before that preceding work was launched. `workspace` and `out` are exempt: the library orders
- * its own accesses to them, so back-to-back calls may share one workspace. Tensor-core kernel
- * only; ignored by the general kernel. */
+ * promises that q, the codes, the scales and the zero-points of this call were complete before
+ * that preceding work was launched. The residual rows, `workspace` and `out` are exempt: the
+ * kernel touches them only after the preceding work has finished, so the residual rows may come
+ * from a vq_kivi_append issued right before, and back-to-back calls may share one workspace.
+ * Tensor-core kernel only; ignored by the general kernel. */
 #define VQ_ATTEND_OVERLAP_PREVIOUS 1
 /* Tail-aligned causal mask for S_q > 1: query row r sits at slot n_quant + n_res - S_q + r and
  * sees the slots up to its own (the mask of metal_fused_sdpa, veloxquant_mlx/metal/

@@ -368,3 +368,48 @@ def test_two_gpus_sharded_attention_gathers_the_unsharded_output():
     ret = mgr.dict()
     mp.spawn(_two_gpu_worker, args=(2, _free_port(), ret), nprocs=2, join=True)
     assert dict(ret) == {0: True, 1: True}
+
+
+def test_overlapped_decode_loop_equals_the_plain_loop():
+    """update_and_fetch + fused_sdpa per layer, every call allowed to start under the previous
+    one (the append copies its rows after a wait, the attention reads them after its own): the
+    same outputs as the plain loop (up to the split plan's summation order) and bit-identical
+    stores, across two quantize-on-append flushes; flush steps fall back to plain launches."""
+    L, B, H_kv, H_q, S0, n_dec = 4, 2, 2, 8, 1000, 70
+    g = torch.Generator(device=DEV)
+    g.manual_seed(21)
+    kv = torch.randn((2, L, B, H_kv, S0 + n_dec, 128), generator=g, device=DEV, dtype=torch.float16)
+    qs = torch.randn((n_dec, L, B, H_q, 1, 128), generator=g, device=DEV, dtype=torch.float16)
+    plain = [_cache(capacity=2048) for _ in range(L)]
+    fast = [_cache(capacity=2048) for _ in range(L)]
+    for l in range(L):
+        for c in (plain[l], fast[l]):
+            c.update_and_fetch(kv[0, l, :, :, :S0], kv[1, l, :, :, :S0])
+    out_p = torch.empty((L, B, H_q, 1, 128), device=DEV, dtype=torch.float16)
+    out_f = torch.empty_like(out_p)
+    flushes = 0
+    for t in range(n_dec):
+        nq = fast[0]._n_quantized
+        for l in range(L):
+            k1, v1 = kv[0, l, :, :, S0 + t : S0 + t + 1].contiguous(), kv[1, l, :, :, S0 + t : S0 + t + 1].contiguous()
+            plain[l].update_and_fetch(k1, v1)
+            plain[l].fused_sdpa(qs[t, l], SCALE, out=out_p[l])
+        torch.cuda.synchronize()
+        # (inputs of the overlapped calls are complete here: nothing they read is produced by the
+        # kernels right before them)
+        for l in range(L):
+            k1, v1 = kv[0, l, :, :, S0 + t : S0 + t + 1].contiguous(), kv[1, l, :, :, S0 + t : S0 + t + 1].contiguous()
+            torch.cuda.synchronize()
+            fast[l].update_and_fetch(k1, v1, overlap_previous=True)
+            fast[l].fused_sdpa(qs[t, l], SCALE, out=out_f[l], overlap_previous=True)
+        torch.cuda.synchronize()
+        flushes += int(fast[0]._n_quantized != nq)
+        assert float((out_p.float() - out_f.float()).abs().max()) < 1e-3, f"step {t}"
+    assert flushes == 2
+    for a, b in zip(plain, fast):
+        nq = a._n_quantized
+        assert nq == b._n_quantized and a._n_res == b._n_res
+        assert torch.equal(a._k_codes[:, :, :nq], b._k_codes[:, :, :nq]) and torch.equal(a._v_scale[:, :, :nq], b._v_scale[:, :, :nq])
+        for x, y in zip(a.state, b.state):
+            assert torch.equal(x, y)
+    fast[0].check_status()

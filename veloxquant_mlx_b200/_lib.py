@@ -140,7 +140,7 @@ SIGNATURES = {
     "vq_kivi_quantize_pack": (C.c_int32, [C.POINTER(KiviQuantArgs), C.c_void_p]),
     "vq_kivi_quant_dequant": (C.c_int32, [C.POINTER(KiviQuantArgs), C.c_void_p]),
     "vq_kivi_append": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64,
-                                   C.c_int64, C.c_int64, C.c_int32, C.c_int32, C.c_void_p]),
+                                   C.c_int64, C.c_int64, C.c_int32, C.c_int32, C.c_int32, C.c_void_p]),
     "vq_kivi_dequant": (C.c_int32, [C.POINTER(KiviDequantArgs), C.c_void_p]),
     "vq_predecoded_attend": (C.c_int32, [C.POINTER(KiviAttendArgs), C.c_void_p]),
     "vq_lse_merge": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_int64, C.c_int32, C.c_int32, C.c_void_p, C.c_int32,

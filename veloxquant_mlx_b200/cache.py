@@ -303,6 +303,7 @@ class KIVIKVCache(StandaloneProtocol):
         # and the layout of the last single-token append, reused while nothing they describe has
         # changed (`_version` moves whenever a buffer is replaced).
         self._version = 0
+        self._just_flushed = False
         self._attend_plan = None
         self._append_plan = None
         self._sentinel = None
@@ -374,9 +375,9 @@ class KIVIKVCache(StandaloneProtocol):
                     self._kv_res[:, :, :, :n] = self._kv_res[:, :, :, lo : lo + n].clone()
             self._res_lo = 0
 
-    def _store_block(self, keys, values, S) -> None:
+    def _store_block(self, keys, values, S, overlap=False) -> None:
         at = self._res_lo + self._n_res
-        if not kernels.kivi_append(keys, values, self._k_res, self._v_res, at):
+        if not kernels.kivi_append(keys, values, self._k_res, self._v_res, at, overlap):
             pair = _paired_view(keys, values)
             if pair is not None:
                 self._kv_res[:, :, :, at : at + S] = pair
@@ -395,8 +396,15 @@ class KIVIKVCache(StandaloneProtocol):
                                    store_bits=self._sb, eps=self._eps)
 
     # -- protocol ----------------------------------------------------------------------
-    def update_and_fetch(self, keys: torch.Tensor, values: torch.Tensor):
-        """Append ``keys/values [B,H,S,D]``; flush aged whole groups into the packed store."""
+    def update_and_fetch(self, keys: torch.Tensor, values: torch.Tensor, *, overlap_previous: bool = False):
+        """Append ``keys/values [B,H,S,D]``; flush aged whole groups into the packed store.
+
+        ``overlap_previous=True`` (an addition to the reference's protocol): the copy of a block
+        that flushes nothing may start under the preceding work on the stream, so that a decode
+        loop ``update_and_fetch -> fused_sdpa(overlap_previous=True)`` per layer streams from one
+        layer into the next. Only pass it when ``keys`` / ``values`` are not produced by the kernels
+        right before this call. A call that flushes a group ignores it, and so does the attention
+        call that follows the flush."""
         ap = self._append_plan
         if (ap is not None and ap[0] == self._version and keys.shape == ap[1] and values.shape == ap[1]
                 and keys.dtype is ap[2] and values.dtype is ap[2] and (self.offset + 1 - self._residual_length) % self._group_size
@@ -406,7 +414,8 @@ class KIVIKVCache(StandaloneProtocol):
             # straight to the copy kernel (the checks of the general path below were made then).
             _, shape, _, _, n_bh, res_stride, dt, k_ptr, v_ptr, dev = ap
             _lib.check(_lib.lib().vq_kivi_append(keys.data_ptr(), values.data_ptr(), shape[3], k_ptr, v_ptr, res_stride, n_bh, 1,
-                                                 self._res_lo + self._n_res, shape[3], dt, _lib.stream_ptr(dev)),
+                                                 self._res_lo + self._n_res, shape[3], dt,
+                                                 _lib.VQ_ATTEND_OVERLAP_PREVIOUS if overlap_previous else 0, _lib.stream_ptr(dev)),
                        "KIVIKVCache.update_and_fetch")
             self.offset += 1
             self._n_res += 1
@@ -427,9 +436,10 @@ class KIVIKVCache(StandaloneProtocol):
         self.offset += S
         new_boundary = self._quantization_boundary()
         n_flush = new_boundary - self._n_quantized
+        self._just_flushed = n_flush > 0
         if n_flush <= 0:
             self._make_room(B, H, D, S, dev, keys.dtype)
-            self._store_block(keys, values, S)
+            self._store_block(keys, values, S, overlap_previous)
         elif self._n_res == 0:
             # A (prefill) block onto an empty residual: its head is quantized straight from the
             # caller's tensor, only its tail is copied into the residual buffer.
@@ -527,9 +537,16 @@ class KIVIKVCache(StandaloneProtocol):
             a.flags = _lib.VQ_ATTEND_OVERLAP_PREVIOUS if overlap_previous else 0
             a.k_res = k_res_ptr + self._res_lo * row_bytes
             a.v_res = v_res_ptr + self._res_lo * row_bytes
+            a.n_splits = 0
             key = (self._n_quantized, a.flags)
             if need[0] != key:
                 need[0], need[1] = key, lib.vq_kivi_attend_workspace_bytes(C.byref(a))
+            if self._just_flushed:
+                # right after a flush the packed store was written by the kernels just before this
+                # call: a plain launch, with the split plan (= summation order) the caller asked for
+                if a.flags:
+                    a.n_splits, a.flags = lib.vq_kivi_attend_splits(C.byref(a)), 0
+                self._just_flushed = False
             ws = kernels._workspace(q.device, need[1])
             a.workspace, a.workspace_bytes = ws.data_ptr(), ws.numel()
             _lib.check(lib.vq_kivi_decode_attend(C.byref(a), _lib.stream_ptr(q.device)), "KIVIKVCache.fused_sdpa")
@@ -543,6 +560,8 @@ class KIVIKVCache(StandaloneProtocol):
         if q.shape[2] > self.offset and causal:
             raise ValueError(f"KIVIKVCache.fused_sdpa: {q.shape[2]} query rows but only {self.offset} cached tokens")
         has_q = self._n_quantized > 0
+        plain_after_flush = bool(overlap_previous) and self._just_flushed
+        self._just_flushed = False
         want_plan = (out is not None and has_q and self._n_res > 0 and q.shape[2] == 1 and q.is_contiguous()
                      and torch.cuda.current_device() == q.device.index)
         keep = [] if want_plan else None
@@ -552,7 +571,8 @@ class KIVIKVCache(StandaloneProtocol):
             store_bits=self._sb, n_quant=self._n_quantized,
             k_res=self._k_res if self._n_res else None, v_res=self._v_res if self._n_res else None,
             n_res=self._n_res, res_offset=self._res_lo, out=out, causal=bool(causal) and q.shape[2] > 1,
-            overlap_previous=overlap_previous, gather=gather, _keep_args=keep, _fn="KIVIKVCache.fused_sdpa")
+            overlap_previous=overlap_previous, gather=gather, _keep_args=keep, _plain_launch=plain_after_flush,
+            _fn="KIVIKVCache.fused_sdpa")
         if want_plan and keep:
             # the validated argument structure, for the next call with the same buffers
             self._attend_plan = (self._version, q.data_ptr(), out.data_ptr(), q.shape, q.dtype, out.dtype, gather,

@@ -569,6 +569,14 @@ kivi_attend_mma_kernel(const __grid_constant__ Params p) {
             for (int i = 0; i < 64; ++i) __nanosleep(1000);
     }
 
+    // Launched as a programmatic dependent (VQ_ATTEND_OVERLAP_PREVIOUS), this grid runs beside
+    // the end of the previous work on the stream. Everything above touched only q and the packed
+    // store; what follows reads the residual rows (which a vq_kivi_append right before this call
+    // may just have written) and writes partials and tickets into a buffer that the previous
+    // call's last CTAs may still be reading: it waits for the work before this grid to finish.
+    // (Returns at once after a plain launch.)
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+
     // ---- the unquantized tail: residual row r belongs to warp r mod (splits * 4) of the unit ----
     // CUDA cores, a lane holds 4 consecutive channels of the row; heads of this CTA's chunk only.
     float tm[kChunkHeads], tl[kChunkHeads], to[kChunkHeads][4];
@@ -661,11 +669,6 @@ kivi_attend_mma_kernel(const __grid_constant__ Params p) {
         }
     }
     __syncthreads();
-    // Launched as a programmatic dependent (VQ_ATTEND_OVERLAP_PREVIOUS), this grid runs beside
-    // the end of the previous call, whose last CTAs may still be reading partials and tickets in
-    // the same buffer: everything above touched only this call's inputs; the writes below wait
-    // for the work before this grid to finish. (Returns at once after a plain launch.)
-    asm volatile("griddepcontrol.wait;" ::: "memory");
     const int n_heads = min(kChunkHeads, hpk - h0);
     for (int i = tid; i < n_heads * kD; i += blockDim.x) {
         const int hp = i / kD, d = i % kD;

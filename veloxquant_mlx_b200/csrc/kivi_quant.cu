@@ -271,20 +271,30 @@ __global__ void __launch_bounds__(256)
 kivi_append_kernel(const uint4 *__restrict__ k_new, const uint4 *__restrict__ v_new, int64_t new_stride_bh,
                    uint4 *__restrict__ k_res, uint4 *__restrict__ v_res, int64_t res_stride_bh, int64_t n_bh,
                    int64_t n_new, int64_t tok_offset, int row_chunks) {
+    // Launched as a programmatic dependent (flags & VQ_ATTEND_OVERLAP_PREVIOUS) this grid may
+    // start while the work before it still runs. What follows it may start as well (the
+    // trigger), e.g. the attention over the same cache, which reads these rows only after its
+    // own wait. The rows are loaded at once and written after the wait, i.e. after everything
+    // before this grid has finished. (Both instructions do nothing after a plain launch.)
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const int64_t per_slab = n_new * row_chunks;
     const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= n_bh * per_slab) return;
-    const int64_t s = i / per_slab, off = i % per_slab;  // strides are in 16-byte chunks here
+    const bool live = i < n_bh * per_slab;
+    const int64_t s = live ? i / per_slab : 0, off = live ? i % per_slab : 0;  // strides are in 16-byte chunks here
     const int64_t src = s * new_stride_bh + off, dst = s * res_stride_bh + tok_offset * row_chunks + off;
-    const uint4 kv = k_new[src], vv = v_new[src];
-    k_res[dst] = kv;
-    v_res[dst] = vv;
+    uint4 kv = make_uint4(0, 0, 0, 0), vv = kv;
+    if (live) { kv = k_new[src]; vv = v_new[src]; }
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    if (live) {
+        k_res[dst] = kv;
+        v_res[dst] = vv;
+    }
 }
 }  // namespace vq
 
 extern "C" int32_t vq_kivi_append(const void *k_new, const void *v_new, int64_t new_stride_bh, void *k_res, void *v_res,
                                   int64_t res_stride_bh, int64_t n_bh, int64_t n_new, int64_t tok_offset,
-                                  int32_t head_dim, int32_t dtype, void *stream) {
+                                  int32_t head_dim, int32_t dtype, int32_t flags, void *stream) {
     using namespace vq;
     VQ_REQUIRE(k_new && v_new && k_res && v_res, VQ_ERR_SHAPE, "vq_kivi_append: a buffer is NULL");
     VQ_REQUIRE(dtype == VQ_F16 || dtype == VQ_BF16 || dtype == VQ_F32, VQ_ERR_DTYPE, "vq_kivi_append: bad dtype %d", dtype);
@@ -297,10 +307,18 @@ extern "C" int32_t vq_kivi_append(const void *k_new, const void *v_new, int64_t 
     const int64_t total = n_bh * n_new * row_chunks;
     if (total == 0) return VQ_OK;
     VQ_REQUIRE(ceil_div(total, 256) < (1ll << 31), VQ_ERR_SHAPE, "vq_kivi_append: block too large for one launch");
-    kivi_append_kernel<<<(unsigned)ceil_div(total, 256), 256, 0, (cudaStream_t)stream>>>(
-        (const uint4 *)k_new, (const uint4 *)v_new, new_stride_bh * es / 16, (uint4 *)k_res, (uint4 *)v_res,
-        res_stride_bh * es / 16, n_bh, n_new, tok_offset, row_chunks);
-    VQ_CHECK_LAUNCH("kivi_append_kernel");
+    VQ_REQUIRE((flags & ~VQ_ATTEND_OVERLAP_PREVIOUS) == 0, VQ_ERR_SHAPE, "vq_kivi_append: unknown bits in flags (%d)", flags);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)ceil_div(total, 256));
+    cfg.blockDim = dim3(256);
+    cfg.stream = (cudaStream_t)stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = (flags & VQ_ATTEND_OVERLAP_PREVIOUS) ? 1 : 0;
+    VQ_CHECK_CUDA(cudaLaunchKernelEx(&cfg, kivi_append_kernel, (const uint4 *)k_new, (const uint4 *)v_new, new_stride_bh * es / 16,
+                                     (uint4 *)k_res, (uint4 *)v_res, res_stride_bh * es / 16, n_bh, n_new, tok_offset, row_chunks));
     return VQ_OK;
 }
 

@@ -101,13 +101,14 @@ def _slab_view(x: torch.Tensor, name: str):
 # ----------------------------------------------------------------------------------------
 
 def kivi_append(keys: torch.Tensor, values: torch.Tensor, k_res: torch.Tensor, v_res: torch.Tensor,
-                tok_offset: int) -> bool:
+                tok_offset: int, overlap_previous: bool = False) -> bool:
     """Copy the block ``keys/values [B,H,S,D]`` behind row ``tok_offset`` of the residual buffers
     ``k_res/v_res [B,H,cap,D]``, both in one launch (the store of the incoming block in the
     reference's ``KIVIKVCache.update_and_fetch``, ``cache/kivi_cache.py:250``). Returns ``False``
     without doing anything when the layout is not one the kernel takes (rows, strides and
     pointers must be multiples of 16 bytes, slabs evenly spaced); the caller then copies with
-    torch."""
+    torch. ``overlap_previous``: see ``vq_kivi_append`` (the copy may start under the preceding
+    work; ``keys`` / ``values`` must not be produced by that work)."""
     B, H, S, D = keys.shape
     es = keys.element_size()
     if keys.dtype not in _FLOAT_DTYPES or not (keys.dtype == values.dtype == k_res.dtype == v_res.dtype):
@@ -132,7 +133,8 @@ def kivi_append(keys: torch.Tensor, values: torch.Tensor, k_res: torch.Tensor, v
     if any(t.data_ptr() % 16 for t in (keys, values, k_res, v_res)):
         return False
     check(lib().vq_kivi_append(keys.data_ptr(), values.data_ptr(), sn, k_res.data_ptr(), v_res.data_ptr(), rk, B * H, S,
-                               int(tok_offset), D, dtype_code(keys.dtype), stream_ptr(keys.device)), "kivi_append")
+                               int(tok_offset), D, dtype_code(keys.dtype),
+                               _lib.VQ_ATTEND_OVERLAP_PREVIOUS if overlap_previous else 0, stream_ptr(keys.device)), "kivi_append")
     return True
 
 
@@ -321,7 +323,7 @@ def kivi_decode_attend(q, k_codes, k_scale, k_zero, v_codes, v_scale, v_zero, gr
                        store_bits=8, n_quant=None, k_res=None, v_res=None, n_res=None,
                        out=None, out_dtype=None, n_splits=0, variant=0, static_scratch=False,
                        overlap_previous=False, gather=None, res_offset=0, causal=False,
-                       _plan_batch=None, _keep_args=None, _fn="kivi_decode_attend"):
+                       _plan_batch=None, _keep_args=None, _plain_launch=False, _fn="kivi_decode_attend"):
     """Fused dequant + attention over packed codes and an optional unquantized tail.
 
     ``k_codes/v_codes [B,H_kv,cap,D*store_bits/8]`` (first ``n_quant`` rows used),
@@ -335,9 +337,10 @@ def kivi_decode_attend(q, k_codes, k_scale, k_zero, v_codes, v_scale, v_zero, gr
     allocated here either); such calls must not overlap on the GPU.
 
     ``overlap_previous=True`` (``VQ_ATTEND_OVERLAP_PREVIOUS``) lets the kernel start while the
-    preceding work on the stream is still running; only pass it when every input of this call
-    was complete before that preceding work was launched (true for a decode loop over per-layer
-    caches whose queries do not come from the kernel right before). ``gather`` is a
+    preceding work on the stream is still running; only pass it when ``q`` and the packed store
+    were complete before that preceding work was launched (true for a decode loop over per-layer
+    caches whose queries do not come from the kernel right before; the residual rows may come
+    from a ``kivi_append`` issued right before). ``gather`` is a
     ``_lib.PeerGather`` (see ``sharding.PeerExchange``): the output rows are also stored into
     every rank's gathered tensor. ``causal=True`` (several query rows) applies the tail-aligned
     causal mask: row ``r`` sees slots ``<= n_quant + n_res - S_q + r``. ``res_offset`` is the
@@ -463,6 +466,11 @@ def kivi_decode_attend(q, k_codes, k_scale, k_zero, v_codes, v_scale, v_zero, gr
         a.res_dtype = dtype_code(k_res.dtype)
         a.res_stride_bh = k_res.shape[2] * k_res.shape[3]
     with torch.cuda.device(q.device):
+        if _plain_launch and a.flags & _lib.VQ_ATTEND_OVERLAP_PREVIOUS and not n_splits:
+            # the split plan (= summation order) of an overlapped call, launched plainly: for a call
+            # whose packed store was written by the kernels right before it
+            a.n_splits = int(lib().vq_kivi_attend_splits(C.byref(a)))
+            a.flags &= ~_lib.VQ_ATTEND_OVERLAP_PREVIOUS
         if _plan_batch is not None and not n_splits:
             # layers folded into the batch axis: take the split count of one layer's shape
             a.B = int(_plan_batch)
