@@ -735,9 +735,18 @@ def run_extras(torch, dist, timer, w, plan, world, rank, device, dtype, px, args
             keys = torch.randn(8, S, 128, device=device).to(torch.float16)
             cb = torch.randn(256, 8, device=device)
             ms = graph_time(lambda: vi.quantize_vq(keys, cb, 8, index_dtype=torch.uint8), 5)
+            # the other searches on the same input: tcgen05 with the two-pass epilogue, warp-level MMAs
+            other = {}
+            for name, mode in (("tcgen05_two_pass", 4), ("mma_sync", 2)):
+                vk.tune("vq_search", mode)
+                other[name + "_us"] = graph_time(lambda: vi.quantize_vq(keys, cb, 8, index_dtype=torch.uint8), 5) * 1e3
+            vk.tune("vq_search", 0)
             fl = 2 * 8 * S * 16 * 256 * 8
+            # tensor-pipe time of the two 128 x 256 x 16 MMAs per 128 rows at the measured dense peak
+            mma_fl = 2 * 8 * S * 16 * 256 * 32
             extra[f"quantize_vq_S{S}"] = {"shape": [8, S, 128], "us": ms * 1e3, "useful_TFLOPs": fl / (ms * 1e-3) / 1e12,
-                                          "frac_of_bf16_peak": fl / (ms * 1e-3) / 1e12 / tpeak, "peak_kind": tkind}
+                                          "frac_of_bf16_peak": fl / (ms * 1e-3) / 1e12 / tpeak, "peak_kind": tkind,
+                                          "issued_mma_frac_of_peak": mma_fl / (ms * 1e-3) / 1e12 / tpeak, **other}
         vk.quantize_status()
 
         # -- RaBitQ config 4: encode and attend

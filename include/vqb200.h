@@ -55,7 +55,7 @@ const char *vq_last_error(void);
 typedef enum vq_knob {
     VQ_KNOB_ATTEND_STAGES = 0,   /* bulk-copy pipeline depth of the decode attend: 2..4 (2) */
     VQ_KNOB_ATTEND_WAVES = 1,    /* waves of CTAs the split count aims at: 1..32 (2) */
-    VQ_KNOB_VQ_SEARCH = 2,       /* vq_vq_quantize search: 0 choose, 1 tcgen05, 2 mma.sync, 3 exact */
+    VQ_KNOB_VQ_SEARCH = 2,       /* vq_vq_quantize search: 0 choose, 1 tcgen05, 2 mma.sync, 3 exact, 4 tcgen05 with the two-pass epilogue */
     VQ_KNOB_ATTEND_WAIT_TEST = 3,/* 1: in the NEXT vq_kivi_decode_attend (tensor-core kernel) every warp
                                     also waits, with 1024 polls, on a barrier that nothing arms: the
                                     bounded wait runs out, the kernel finishes normally and

@@ -126,6 +126,13 @@ def test_dispatch_rule_memory_bound_never_falls_back_to_the_sentinels():
     assert seen["cache"] is d and seen["mask"] == "causal" and seen["scale"] == 0.3 and d.calls == []
 
 
+def test_attention_function_refuses_orphaned_sentinels():
+    q = torch.randn(1, 4, 1, 8)
+    z = torch.zeros(1, 2, 0, 8)
+    with pytest.raises(RuntimeError, match="zero-length keys"):
+        I.veloxquant_attention(None, q, z, z, None, scaling=0.3)
+
+
 def _tiny_llama():
     from transformers import LlamaConfig, LlamaForCausalLM
 

@@ -10,7 +10,7 @@ import torch
 
 pytestmark = pytest.mark.gpu
 
-_MODES = {"tc5": 1, "mma": 2, "exact": 3}
+_MODES = {"tc5": 1, "mma": 2, "exact": 3, "tc5_two_pass": 4}
 
 
 @pytest.fixture
@@ -39,7 +39,7 @@ def _check(x32, cb, tag, dt):
     assert bad == 0, f"{tag}: {bad} of {want.size} indices differ"
 
 
-@pytest.mark.parametrize("mode", ["tc5", "mma", "exact"])
+@pytest.mark.parametrize("mode", ["tc5", "mma", "exact", "tc5_two_pass"])
 def test_pinned_search_matches_the_reference_order(mode, pinned_search):
     pinned_search(mode)
     rng = np.random.default_rng(0)
@@ -59,6 +59,23 @@ def test_pinned_search_matches_the_reference_order(mode, pinned_search):
         cb2[64:, 0] = np.nextafter(cb2[:64, 0], np.float32(np.inf))
         x2 = (cb2[rng.integers(0, 128, 4096)] + 1e-3 * rng.standard_normal((4096, 8))).astype(np.float32)
         _check(x2, cb2, "near-ties", dt)
+        # 256 centroids (the single-pass epilogue's 8 x 16 grid per half row): duplicates that share a
+        # grid column, a grid row, or sit in the two halves; then 1-ulp near-ties of every centroid
+        cb3 = rng.integers(-3, 4, (256, 8)).astype(np.float32)
+        cb3[23] = cb3[7]          # same grid column (7 and 7 + 16)
+        cb3[41] = cb3[40]         # same grid row
+        cb3[130] = cb3[2]         # lower and upper half
+        cb3[255] = cb3[128]
+        x3 = rng.integers(-3, 4, (8192, 8)).astype(np.float32)
+        x3[:256] = cb3            # every centroid is hit exactly
+        _check(x3, cb3, "lattice 256", dt)
+        cb4 = rng.standard_normal((256, 8)).astype(np.float32)
+        cb4[128:] = cb4[:128]
+        cb4[128:, 0] = np.nextafter(cb4[:128, 0], np.float32(np.inf))
+        cb4[64:128] = cb4[:64]
+        cb4[64:128, 1] = np.nextafter(cb4[:64, 1], np.float32(-np.inf))
+        x4 = (cb4[rng.integers(0, 256, 8192)] + 1e-3 * rng.standard_normal((8192, 8))).astype(np.float32)
+        _check(x4, cb4, "near-ties 256", dt)
         # rows and codebooks outside the half-precision window fall back to the reference order
         xb = rng.standard_normal((2048, 8)).astype(np.float32)
         xb[5] *= 3e4

@@ -369,7 +369,7 @@ int32_t launch_sub(const void *x, int64_t n, int sub_dim, const float *cb, int n
 
 bool vq_quantize_mma_supported(const void *x, int32_t x_dtype, int64_t n, int32_t sub_dim, int32_t n_c, int32_t n_sub) {
     const int mode = knob_get(VQ_KNOB_VQ_SEARCH);  // 0 choose; 1 tcgen05 / 2 mma.sync / 3 exact pin one search
-    if (mode == 1 || mode == 3) return false;
+    if (mode == 1 || mode == 3 || mode == 4) return false;
     if (n_sub < 0 || n_sub > 65535 || (sub_dim != 4 && sub_dim != 8)) return false;
     if (n_c < 2 || n_c > 2048) return false;
     if (x_dtype != VQ_F16 && x_dtype != VQ_BF16 && x_dtype != VQ_F32) return false;

@@ -10,14 +10,27 @@
 // memory in the canonical K-major layout (8-row x 16-byte core matrices, no swizzle); a row of
 // x is 16 bytes, so a tile of x is already a stack of core matrices and is brought in with
 // one 16-byte cp.async per row. Two threads (one per warpgroup) then own each row and half of its
-// columns each: they read their scores from tensor memory twice, 32 columns per load with the
-// next load in flight -- pass 1 takes the maximum, pass 2 counts and names the scores within
+// columns each. What they must learn from their 128 scores: the column of the best one, and
+// whether any other score lies within
 //     delta = 2^-16 * (|x|^2 + max|c|^2)
 // of it (twice the worst-case difference between this evaluation and the reference's
 // sequential float32 one: see vq_quant_mma.cu). One candidate: the answer. Otherwise (near-ties,
 // duplicates, a row or a codebook outside the half-precision window) the warp runs the
-// reference evaluation order for that row. Two CTAs share an SM (256 accumulator columns each),
-// so one CTA's MMAs run under the other's epilogue.
+// reference evaluation order for that row.
+//
+// With 256 centroids the scores leave tensor memory once (pass_grid): the thread views its 128
+// columns as an 8 x 16 grid and keeps the 16 column maxima and the 8 row maxima, one max3 per
+// two scores each, i.e. one instruction per score. Two different columns differ in their grid row
+// or their grid column, so "exactly one row maximum and exactly one column maximum reach
+// best - delta" holds exactly when one score does, and then the two name its place. The 24 maxima
+// are counted against the threshold afterwards (48 instructions per thread instead of 256). The
+// two halves of a row never wait for each other: each reports (its maximum, its verdict against
+// its own maximum) and the half with the larger maximum is believed unless the two maxima are
+// within delta of each other.
+// Other centroid counts read the accumulator twice, 32 columns per load with the next load in
+// flight: pass 1 takes the maximum, pass 2 counts and names the scores within delta of it.
+// Two CTAs share an SM (256 accumulator columns each), so one CTA's MMAs run under the other's
+// epilogue.
 //
 // Every wait on the MMA-completion barrier is bounded; on a timeout the CTA raises a device
 // flag, skips the tile and still frees its tensor memory before it exits.
@@ -147,8 +160,8 @@ struct Tc5Smem {
     uint8_t b1[2][256 * 16];       // [K chunk]: centroid piece 0 | piece 1
     uint8_t b2[2][256 * 16];       // [K chunk]: (h0 h1 h2 0 ...) | 0; bf16: centroid piece 2 | (h0 h1 h2 h3 0 ...)
     float xch_m[2][kRows];         // row maxima of the two column halves
-    float xch_acc[kRows];          // pass-2 results of the upper column half
-    float xch_base[kRows];
+    float xch_acc[kRows];          // pass-2 results of the upper column half (single pass: its column-maxima verdict)
+    float xch_base[kRows];         // (single pass: its row-maxima verdict)
     uint64_t bar;
     uint64_t idle_bar;             // never armed (self-test of the bounded wait)
     uint32_t tmem_base;
@@ -220,10 +233,75 @@ __device__ __forceinline__ void pass_count(uint32_t taddr, int c_lo, int c_hi, f
     }
 }
 
+// Keeps the values of an array that an earlier tmem_ld32 filled from being read before the
+// tcgen05.wait::ld that precedes this statement (both are volatile: they keep their order).
+__device__ __forceinline__ void tmem_pin(float (&v)[32]) {
+    asm volatile(""
+                 : "+f"(v[0]), "+f"(v[1]), "+f"(v[2]), "+f"(v[3]), "+f"(v[4]), "+f"(v[5]), "+f"(v[6]), "+f"(v[7]), "+f"(v[8]),
+                   "+f"(v[9]), "+f"(v[10]), "+f"(v[11]), "+f"(v[12]), "+f"(v[13]), "+f"(v[14]), "+f"(v[15]), "+f"(v[16]),
+                   "+f"(v[17]), "+f"(v[18]), "+f"(v[19]), "+f"(v[20]), "+f"(v[21]), "+f"(v[22]), "+f"(v[23]), "+f"(v[24]),
+                   "+f"(v[25]), "+f"(v[26]), "+f"(v[27]), "+f"(v[28]), "+f"(v[29]), "+f"(v[30]), "+f"(v[31])
+                 :
+                 : "memory");
+}
+
+// Maximum of 16 values in 8 instructions.
+__device__ __forceinline__ float max16(const float *c) {
+    float m = max3(c[0], c[1], c[2]);
+#pragma unroll
+    for (int i = 3; i < 15; i += 2) m = max3(m, c[i], c[i + 1]);
+    return fmaxf(m, c[15]);
+}
+
+// One 32-column chunk = grid rows b0 and b0 + 1: their maxima, and the running column maxima.
+template <bool FIRST>
+__device__ __forceinline__ void grid_chunk(const float (&cur)[32], float (&P)[16], float &q0, float &q1) {
+    q0 = max16(cur);
+    q1 = max16(cur + 16);
+#pragma unroll
+    for (int j = 0; j < 16; ++j) P[j] = FIRST ? fmaxf(cur[j], cur[16 + j]) : max3(P[j], cur[j], cur[16 + j]);
+}
+
+// The single pass over this thread's 128 columns [c_lo, c_lo + 128), seen as 8 rows of 16:
+// P[j] = maximum of grid column j, Q[k] = maximum of grid row k. Two loads are in flight at a time.
+__device__ __forceinline__ void pass_grid(uint32_t taddr, int c_lo, float (&P)[16], float (&Q)[8]) {
+    float va[32], vb[32];
+    tmem_ld32(taddr + c_lo, va);
+    tmem_ld32(taddr + c_lo + 32, vb);
+    tmem_ld_wait(va);
+    tmem_pin(vb);
+    grid_chunk<true>(va, P, Q[0], Q[1]);
+    tmem_ld32(taddr + c_lo + 64, va);
+    grid_chunk<false>(vb, P, Q[2], Q[3]);
+    tmem_ld32(taddr + c_lo + 96, vb);
+    tmem_ld_wait(va);
+    tmem_pin(vb);
+    grid_chunk<false>(va, P, Q[4], Q[5]);
+    grid_chunk<false>(vb, P, Q[6], Q[7]);
+}
+
+// Verdict of one half against its own maximum m: ap = 65536 * (column maxima >= m - d) + their
+// grid columns, aq = 65536 * (row maxima >= m - d) + 16 * their grid rows. One score within d of
+// the best: both counts are 1 and the score's column is (ap - 65536) + (aq - 65536).
+__device__ __forceinline__ void grid_verdict(const float (&P)[16], const float (&Q)[8], float d, float &m, float &ap, float &aq) {
+    m = fmaxf(max3(Q[0], Q[1], Q[2]), max3(Q[3], Q[4], Q[5]));
+    m = max3(m, Q[6], Q[7]);
+    const float thr = m - d;
+    float a4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int j = 0; j < 16; ++j) add_if_ge(a4[j & 3], P[j], thr, 65536.f + (float)j);
+    ap = (a4[0] + a4[1]) + (a4[2] + a4[3]);
+    float b4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int k = 0; k < 8; ++k) add_if_ge(b4[k & 3], Q[k], thr, 65536.f + 16.f * (float)k);
+    aq = (b4[0] + b4[1]) + (b4[2] + b4[3]);
+}
+
 // T = __half: operands in f16, centroid = 2 pieces (K slots: x|x against c0|c1, then 1 1 1 against
 // the three pieces of h). T = __nv_bfloat16: operands in bf16, whose 8-bit mantissa needs 3
 // pieces per centroid and 4 for h: x|x against c0|c1, then x|1 1 1 1 against c2|h0 h1 h2 h3.
-template <typename T>
+// ONEPASS: 256 centroids, the single-pass epilogue (pass_grid); otherwise the two-pass one.
+template <typename T, bool ONEPASS>
 __global__ void __launch_bounds__(kThreads, 2)
 vq_quantize_tc5_kernel(const T *__restrict__ x, int64_t n_vec, const float *__restrict__ cb_all, int n_c, int n_sub,
                        void *__restrict__ indices, int index_bytes, int wait_test) {
@@ -307,10 +385,6 @@ vq_quantize_tc5_kernel(const T *__restrict__ x, int64_t n_vec, const float *__re
     // 128-byte core matrix (8 rows of 16 bytes)
     const uint32_t lbo_a = (uint32_t)(kRows * 16), sbo_a = 128u;
     const uint32_t lbo_b = (uint32_t)(256 * 16), sbo_b = 128u;
-    const uint64_t desc_a2 = make_desc(smem_u32(sm.a2[0]), lbo_a, sbo_a);
-    const uint64_t desc_b1 = make_desc(smem_u32(sm.b1[0]), lbo_b, sbo_b);
-    const uint64_t desc_b2 = make_desc(smem_u32(sm.b2[0]), lbo_b, sbo_b);
-    const uint32_t idesc = make_idesc(kRows, N, BF);
     const uint32_t bar = smem_u32(&sm.bar);
 
     // columns of this thread: the lower or the upper half (in whole 32-column chunks)
@@ -339,15 +413,29 @@ vq_quantize_tc5_kernel(const T *__restrict__ x, int64_t n_vec, const float *__re
     uint32_t phase = 0;
     bool timed_out = false;
     // results of the previous tile, finished after barrier A of the next one
-    float prev_acc = 0.f, prev_base = 0.f;
+    float prev_acc = 0.f, prev_base = 0.f, prev_m = 0.f, prev_d = 0.f;
     bool prev_bad = false, have_prev = false;
     int64_t prev_tile = 0;
     auto finish_prev = [&]() {
         if (!have_prev || half != 0) return;
         const int64_t row = prev_tile * kRows + r;
-        const float acc = prev_acc + sm.xch_acc[r], base = prev_base + sm.xch_base[r];
-        const bool slow = prev_bad || !(acc >= 65536.f && acc < 131072.f);
-        uint32_t idx = (uint32_t)((int)acc - 65536 + (int)base) & 0xffffu;
+        bool slow;
+        uint32_t idx;
+        if constexpr (ONEPASS) {
+            // the half with the larger maximum holds the best score; the other half holds a
+            // candidate too when the maxima are within delta (also true when either is NaN)
+            const float m1 = sm.xch_m[1][r];
+            const bool upper = m1 > prev_m;
+            const float ap = upper ? sm.xch_acc[r] : prev_acc, aq = upper ? sm.xch_base[r] : prev_base;
+            const bool both = !(fabsf(prev_m - m1) > prev_d);
+            const bool one = ap >= 65536.f && ap < 131072.f && aq >= 65536.f && aq < 131072.f;
+            slow = prev_bad || both || !one;
+            idx = (uint32_t)((int)ap + (int)aq - 131072 + (upper ? 128 : 0)) & 0xffffu;
+        } else {
+            const float acc = prev_acc + sm.xch_acc[r], base = prev_base + sm.xch_base[r];
+            slow = prev_bad || !(acc >= 65536.f && acc < 131072.f);
+            idx = (uint32_t)((int)acc - 65536 + (int)base) & 0xffffu;
+        }
         // rows that need the reference order: the whole warp works on each in turn
         uint32_t slow_mask = __ballot_sync(0xffffffffu, slow && row < n && !timed_out);
         while (slow_mask) {
@@ -372,6 +460,12 @@ vq_quantize_tc5_kernel(const T *__restrict__ x, int64_t n_vec, const float *__re
         __syncthreads();  // A: this tile of x is in place; pass 2 of the previous tile has released tensor memory
         if (tid == 0) {
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            // (descriptors are rebuilt here, by the one thread that uses them, rather than kept in
+            // every thread's registers across the epilogue)
+            const uint64_t desc_a2 = make_desc(smem_u32(sm.a2[0]), lbo_a, sbo_a);
+            const uint64_t desc_b1 = make_desc(smem_u32(sm.b1[0]), lbo_b, sbo_b);
+            const uint64_t desc_b2 = make_desc(smem_u32(sm.b2[0]), lbo_b, sbo_b);
+            const uint32_t idesc = make_idesc(kRows, N, BF);
             const uint64_t desc_a = make_desc(smem_u32(sm.a[stage][0]), lbo_a, sbo_a);
             mma_f16_ss(tmem, desc_a, desc_b1, idesc, 0u);
             if (BF) {
@@ -412,16 +506,29 @@ vq_quantize_tc5_kernel(const T *__restrict__ x, int64_t n_vec, const float *__re
         timed_out = sm.timeout != 0;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 
-        // ---- pass 1: the row's best score (each half of the columns, then exchanged) ----------
-        sm.xch_m[half][r] = timed_out ? 0.f : pass_max(taddr, c_lo, c_hi);
-        __syncthreads();  // C
-        const float m = fmaxf(sm.xch_m[0][r], sm.xch_m[1][r]);
         // bf16: ~30 float32 roundings per score instead of ~20: the margin is doubled
-        const float thr = m - (BF ? 3.0517578125e-05f : 1.52587890625e-05f) * (xn + cmax2);
-        // ---- pass 2: count and name the scores within delta of it ----------------------------
+        const float delta = (BF ? 3.0517578125e-05f : 1.52587890625e-05f) * (xn + cmax2);
         float acc = 0.f, base = 0.f;
-        if (!timed_out) pass_count(taddr, c_lo, c_hi, thr, acc, base);
-        if (half) { sm.xch_acc[r] = acc; sm.xch_base[r] = base; }
+        if constexpr (ONEPASS) {
+            // ---- the single pass: 24 maxima of this half, then its verdict ----------------------
+            float m = 0.f;
+            if (!timed_out) {
+                float P[16], Q[8];
+                pass_grid(taddr, c_lo, P, Q);
+                grid_verdict(P, Q, delta, m, acc, base);
+            }
+            if (half) { sm.xch_m[1][r] = m; sm.xch_acc[r] = acc; sm.xch_base[r] = base; }
+            prev_m = m; prev_d = delta;
+        } else {
+            // ---- pass 1: the row's best score (each half of the columns, then exchanged) --------
+            sm.xch_m[half][r] = timed_out ? 0.f : pass_max(taddr, c_lo, c_hi);
+            __syncthreads();  // C
+            const float m = fmaxf(sm.xch_m[0][r], sm.xch_m[1][r]);
+            const float thr = m - delta;
+            // ---- pass 2: count and name the scores within delta of it --------------------------
+            if (!timed_out) pass_count(taddr, c_lo, c_hi, thr, acc, base);
+            if (half) { sm.xch_acc[r] = acc; sm.xch_base[r] = base; }
+        }
         prev_acc = acc; prev_base = base; prev_bad = bad; prev_tile = tile; have_prev = true;
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -443,12 +550,13 @@ vq_quantize_tc5_kernel(const T *__restrict__ x, int64_t n_vec, const float *__re
 }  // namespace
 
 bool vq_quantize_tc5_supported(const void *x, int32_t x_dtype, int64_t n, int32_t sub_dim, int32_t n_c, int32_t n_sub) {
-    const int mode = knob_get(VQ_KNOB_VQ_SEARCH);  // 0 choose; 1 tcgen05 / 2 mma.sync / 3 exact pin one search
+    // 0 choose; 1 tcgen05 / 2 mma.sync / 3 exact pin one search; 4 = tcgen05 with the two-pass epilogue
+    const int mode = knob_get(VQ_KNOB_VQ_SEARCH);
     if (mode == 2 || mode == 3) return false;
     if ((x_dtype != VQ_F16 && x_dtype != VQ_BF16) || sub_dim != kSub || n_sub < 0 || n_sub > 65535) return false;
     if (n_c < 16 || n_c > 256 || n_c % 16) return false;
     if (!is_aligned(x, 16)) return false;
-    const bool forced = mode == 1;
+    const bool forced = mode == 1 || mode == 4;
     return forced ? n >= 1 : n >= 4096;  // small inputs: the CUDA-core search has no set-up cost
 }
 
@@ -460,17 +568,27 @@ int32_t vq_quantize_tc5_launch(const void *x, int32_t x_dtype, int64_t n, const 
     // Two CTAs per SM: each holds 256 of the SM's 512 accumulator columns. The shared-memory
     // request is padded so that a third CTA (which would wait for columns) cannot be resident.
     const size_t smem = std::max(sizeof(Tc5Smem) + 128, (size_t)80 * 1024);
-    VQ_CHECK_CUDA(cudaFuncSetAttribute(vq_quantize_tc5_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    VQ_CHECK_CUDA(cudaFuncSetAttribute(vq_quantize_tc5_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    // 256 centroids take the single-pass epilogue (knob value 4 pins the two-pass one, to measure it)
+    const bool onepass = n_c == 256 && knob_get(VQ_KNOB_VQ_SEARCH) != 4;
+    VQ_CHECK_CUDA(cudaFuncSetAttribute(vq_quantize_tc5_kernel<__half, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    VQ_CHECK_CUDA(cudaFuncSetAttribute(vq_quantize_tc5_kernel<__nv_bfloat16, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    VQ_CHECK_CUDA(cudaFuncSetAttribute(vq_quantize_tc5_kernel<__half, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    VQ_CHECK_CUDA(cudaFuncSetAttribute(vq_quantize_tc5_kernel<__nv_bfloat16, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     const int ny = n_sub > 0 ? n_sub : 1;
     const int64_t n_tiles = ceil_div(ceil_div(n, ny), kRows);
     const int64_t fill = std::max<int64_t>(1, ceil_div((int64_t)di.sm_count * 2, ny));  // CTAs per sub-space for two per SM
     const unsigned blocks = (unsigned)std::max<int64_t>(1, std::min<int64_t>(n_tiles, fill));
     const int wait_test = knob_take(VQ_KNOB_VQ_WAIT_TEST);
-    if (x_dtype == VQ_BF16)
-        vq_quantize_tc5_kernel<__nv_bfloat16><<<dim3(blocks, ny), kThreads, smem, st>>>((const __nv_bfloat16 *)x, n, cb, n_c, n_sub, indices, index_bytes, wait_test);
-    else
-        vq_quantize_tc5_kernel<__half><<<dim3(blocks, ny), kThreads, smem, st>>>((const __half *)x, n, cb, n_c, n_sub, indices, index_bytes, wait_test);
+    const dim3 grid(blocks, ny);
+    if (x_dtype == VQ_BF16) {
+        const auto *xp = (const __nv_bfloat16 *)x;
+        if (onepass) vq_quantize_tc5_kernel<__nv_bfloat16, true><<<grid, kThreads, smem, st>>>(xp, n, cb, n_c, n_sub, indices, index_bytes, wait_test);
+        else vq_quantize_tc5_kernel<__nv_bfloat16, false><<<grid, kThreads, smem, st>>>(xp, n, cb, n_c, n_sub, indices, index_bytes, wait_test);
+    } else {
+        const auto *xp = (const __half *)x;
+        if (onepass) vq_quantize_tc5_kernel<__half, true><<<grid, kThreads, smem, st>>>(xp, n, cb, n_c, n_sub, indices, index_bytes, wait_test);
+        else vq_quantize_tc5_kernel<__half, false><<<grid, kThreads, smem, st>>>(xp, n, cb, n_c, n_sub, indices, index_bytes, wait_test);
+    }
     VQ_CHECK_LAUNCH("vq_quantize_tc5_kernel");
     return VQ_OK;
 }

@@ -248,6 +248,11 @@ def veloxquant_attention(module: Any, query: torch.Tensor, key: torch.Tensor, va
     if cache is not None:
         out = fused_sdpa_dispatch(query, key, value, cache, scale, mask, sinks=kwargs.get("s_aux"))
     else:
+        if key.shape[-2] == 0:
+            # a memory-bound cache's sentinel that lost its reference to the cache (something copied
+            # or reshaped the key tensor on the way here): there is nothing to attend over
+            raise RuntimeError("veloxquant_attention: received zero-length keys without a cache reference; a "
+                               "memory-bound cache must reach this function through VeloxQuantCacheLayer.update unchanged")
         out = _dense_sdpa(query, key, value, scale, mask)
     return out.transpose(1, 2).contiguous(), None
 

@@ -80,13 +80,15 @@ def op_kivi_quantize(a):
 
 def op_vq_quantize(a):
     dt = _DT[a.dtype]
+    k.tune("vq_search", a.search)
     for S in (4096, 65536):
         keys = torch.randn(8, S, 128, device="cuda").to(dt)
         cb = torch.randn(256, 8, device="cuda")
         us = _time_us(lambda: vi.quantize_vq(keys, cb, 8, index_dtype=torch.uint8), a.iters)
         n = 8 * S * 16
-        _line("vq_quantize", f"[8,{S},128] {a.dtype} sub_dim=8 n_c=256", us, flops=2 * n * 256 * 8,
+        _line("vq_quantize", f"[8,{S},128] {a.dtype} sub_dim=8 n_c=256 search={a.search}", us, flops=2 * n * 256 * 8,
               nbytes=keys.numel() * keys.element_size() + n)
+    k.tune("vq_search", 0)
 
 
 def op_vq_encode(a):
@@ -154,6 +156,8 @@ def main(argv=None):
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--batch", type=int, default=4, help="batch of the kivi_quantize shape")
     ap.add_argument("--ctx", type=int, default=32768, help="context of the kivi_quantize shape")
+    ap.add_argument("--search", type=int, default=0, choices=range(5),
+                    help="vq_quantize: 0 choose, 1 tcgen05, 2 mma.sync, 3 exact, 4 tcgen05 with the two-pass epilogue")
     ap.add_argument("--graph", action="store_true", help="time CUDA-graph replays (GPU time without launch overhead)")
     a = ap.parse_args(argv)
     global _USE_GRAPH

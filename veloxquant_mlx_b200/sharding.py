@@ -244,6 +244,12 @@ class PeerExchange:
         flat = raw.view(self.dtype).view(self.plan.units, self.hpk, self.s_q, self.D)
         return unshard_output(flat, self.plan)
 
+    def __enter__(self) -> "PeerExchange":
+        return self
+
+    def __exit__(self, *exc) -> None:
+        self.close()
+
     def close(self) -> None:
         """Unmap the peers' buffers (after a barrier: nobody may still be writing into ours)."""
         if self.plan.world > 1:
