@@ -162,6 +162,25 @@ int32_t vq_kivi_dequant(const vq_kivi_dequant_args *args, void *stream);
  * Replaces scalar_fused_decode_attend (veloxquant_mlx/metal/_scalar_attend.py:370-493,
  * metal/src/scalar_affine_attend.metal:8-175) and scalar_predecoded_attend
  * (_scalar_attend.py:702-779) when n_quant == 0. */
+/* Protected ("sink") tokens of a sink-protected KIVI store (the reference's SinkProtectedKVCache,
+ * veloxquant_mlx/cache/sink_cache.py:117-190, keeps the highest-key-norm tokens in fp16 inside its
+ * dequantized buffer). Here such a token keeps a slot in the packed store, quantized from a copy
+ * of a neighbouring row (as the reference does before it computes the group parameters) with its
+ * value scale and zero-point set to 0, so the slot adds nothing to P.V; what its key still adds
+ * to the softmax sum is taken out again through k_dead, and the token's exact rows come in as
+ * extra tail rows. Batch element b has count[b] <= max_rows protected rows; per (b, kv head) a
+ * slab of rows [max_rows..][D], stride_bh elements apart: k and v in the residual's dtype
+ * (res_dtype must be set even when n_res is 0), k_dead in float32. */
+typedef struct vq_kivi_sinks {
+    const void *k;            /* exact key rows */
+    const void *v;            /* exact value rows */
+    const float *k_dead;      /* dequantized key of the slot each row left behind in the packed store */
+    const int32_t *count;     /* [B], device memory */
+    int64_t stride_bh;        /* elements */
+    int32_t max_rows;
+    int32_t reserved;         /* must be 0 */
+} vq_kivi_sinks;
+
 typedef struct vq_kivi_attend_args {
     const void *q;            /* [B, H_q, S_q, D] contiguous */
     void *out;                /* [B, H_q, S_q, D] contiguous */
@@ -195,6 +214,7 @@ typedef struct vq_kivi_attend_args {
     int32_t reserved;         /* must be 0 */
     const struct vq_peer_gather *gather; /* NULL, or where the output rows are also published
                                  to the other ranks of a sharded run (see vq_peer_gather) */
+    const struct vq_kivi_sinks *sinks;   /* NULL, or the protected tokens (tensor-core kernel only) */
 } vq_kivi_attend_args;
 /* The attention kernel may begin while the work that precedes this call on the stream is still
  * running (programmatic dependent launch): its prologue and its pass over the packed cache then

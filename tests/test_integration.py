@@ -188,13 +188,27 @@ def test_transformers_model_decodes_over_the_compressed_caches(method, memory_bo
         I.patch_hf_for_fused_sdpa(model)
         assert model.make_cache() is not first and len(first.layers) == 2
         cache = model.make_cache()
+        fused_calls = []
+        if memory_bound:   # the packed store must be what is attended over, in every layer
+            for layer in cache.layers:
+                inner = layer.cache.fused_sdpa
+                layer.cache.fused_sdpa = (lambda f: lambda q, *a, **k: (fused_calls.append(q.shape[2]), f(q, *a, **k))[1])(inner)
         out = model(ids, past_key_values=cache, use_cache=True)
         assert cache.get_seq_length() == 200
+        assert fused_calls == ([200, 200] if memory_bound else [])
         if method == "kivi":
             assert float((out.logits.float() - ref.logits.float()).abs().max()) < 0.08
             assert cache.layers[0].cache._n_quantized == 160
         step = model(ids[:, -1:], past_key_values=cache, use_cache=True)
         assert step.logits.shape == (2, 1, 100) and cache.get_seq_length() == 201 and torch.isfinite(step.logits).all()
+        assert fused_calls == ([200, 200, 1, 1] if memory_bound else [])
+        if method == "rabitq":
+            # sign-bit keys are a coarse estimate, but the attention must see the values: the
+            # logits follow the uncompressed run far more closely than a run without attention would
+            ref_step = ref.logits[:, -1].float()
+            got = out.logits[:, -1].float()
+            cos = torch.nn.functional.cosine_similarity(got, ref_step, dim=-1)
+            assert float(cos.min()) > 0.5, cos
         gen = model.generate(ids[:, :50], attention_mask=torch.ones_like(ids[:, :50]), max_new_tokens=8, do_sample=False,
                              past_key_values=model.make_cache())
         assert gen.shape == (2, 58)

@@ -61,7 +61,7 @@ class KiviAttendArgs(C.Structure):
         ("k_res", C.c_void_p), ("v_res", C.c_void_p), ("res_dtype", C.c_int32), ("res_stride_bh", C.c_int64),
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_int64),
         ("n_splits", C.c_int32), ("variant", C.c_int32),
-        ("flags", C.c_int32), ("reserved", C.c_int32), ("gather", C.c_void_p),
+        ("flags", C.c_int32), ("reserved", C.c_int32), ("gather", C.c_void_p), ("sinks", C.c_void_p),
     ]
 
 
@@ -70,6 +70,13 @@ VQ_ATTEND_CAUSAL = 2
 VQ_MAX_PEERS = 16
 (VQ_KNOB_ATTEND_STAGES, VQ_KNOB_ATTEND_WAVES, VQ_KNOB_VQ_SEARCH, VQ_KNOB_ATTEND_WAIT_TEST,
  VQ_KNOB_VQ_WAIT_TEST, VQ_KNOB_ATTEND_EXACT_PV) = range(6)
+
+
+class KiviSinks(C.Structure):
+    _fields_ = [
+        ("k", C.c_void_p), ("v", C.c_void_p), ("k_dead", C.c_void_p), ("count", C.c_void_p),
+        ("stride_bh", C.c_int64), ("max_rows", C.c_int32), ("reserved", C.c_int32),
+    ]
 
 
 class PeerGather(C.Structure):

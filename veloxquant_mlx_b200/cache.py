@@ -94,6 +94,7 @@ class KVCacheConfig:
     fused_sdpa: Any = False
     fused_sdpa_max_ctx: Any = None
     fused_sdpa_memory_bound: bool = False
+    n_sink_tokens: int = 5
 
     def __repr__(self) -> str:
         return (f"KVCacheConfig(method={self.method!r}, d={self.head_dim}, "
@@ -571,14 +572,18 @@ class KIVIKVCache(StandaloneProtocol):
             store_bits=self._sb, n_quant=self._n_quantized,
             k_res=self._k_res if self._n_res else None, v_res=self._v_res if self._n_res else None,
             n_res=self._n_res, res_offset=self._res_lo, out=out, causal=bool(causal) and q.shape[2] > 1,
-            overlap_previous=overlap_previous, gather=gather, _keep_args=keep, _plain_launch=plain_after_flush,
-            _fn="KIVIKVCache.fused_sdpa")
+            overlap_previous=overlap_previous, gather=gather, sinks=self._attend_sinks() if has_q and q.shape[2] == 1 else None,
+            _keep_args=keep, _plain_launch=plain_after_flush, _fn="KIVIKVCache.fused_sdpa")
         if want_plan and keep:
             # the validated argument structure, for the next call with the same buffers
             self._attend_plan = (self._version, q.data_ptr(), out.data_ptr(), q.shape, q.dtype, out.dtype, gather,
                                  q.device.index, keep[0], self._head_dim * self._k_res.element_size(),
                                  self._k_res.data_ptr(), self._v_res.data_ptr(), [None, 0])
         return res
+
+    def _attend_sinks(self):
+        """Protected tokens for the attention call (none in plain KIVI; see ``cache_sink``)."""
+        return None
 
     def check_status(self) -> None:
         """Raise if a device-side bounded wait of an earlier attention call ran out (its output
@@ -788,6 +793,8 @@ class KIVIKVCache(StandaloneProtocol):
 _CACHE_CLASS_BY_METHOD["kivi"] = KIVIKVCache
 
 from .cache_coded import RaBitQKVCache, VecInferKVCache  # noqa: E402  (registers "vecinfer", "rabitq")
+from .cache_sink import SinkProtectedKVCache  # noqa: E402  (registers "kivi_sink")
 
 __all__ = ["QuantizerConfigError", "VecInferOptions", "KIVIOptions", "KVCacheConfig", "KVCacheFactory",
-           "KVCacheBuilder", "KIVIKVCache", "VecInferKVCache", "RaBitQKVCache", "KVCache", "EncodedVector"]
+           "KVCacheBuilder", "KIVIKVCache", "SinkProtectedKVCache", "VecInferKVCache", "RaBitQKVCache", "KVCache",
+           "EncodedVector"]

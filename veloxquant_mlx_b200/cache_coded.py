@@ -267,6 +267,9 @@ class RaBitQKVCache(StandaloneProtocol):
         if D & (D - 1) or D % 32 or D > 256:
             raise QuantizerConfigError(f"RaBitQKVCache: head_dim={D} must be a power of 2 in 32..256.")
         self._seed = int(getattr(config, "seed", 42))
+        # the keys exist as sign bits only: update_and_fetch always returns sentinels and attention
+        # always goes through fused_sdpa, whatever the configuration's flag says
+        self._memory_bound = True
         self._diag_np = rq.make_hadamard_diagonal(D, seed=self._seed)
         self._diag = self._H = None
         self._bits = self._mag = self._v = None

@@ -324,6 +324,9 @@ extern "C" int32_t vq_kivi_decode_attend(const vq_kivi_attend_args *args, void *
         VQ_REQUIRE(a.variant != 2, VQ_ERR_SHAPE, "vq_kivi_decode_attend: tensor-core kernel unavailable: %s", why);
     }
 
+    VQ_REQUIRE(a.sinks == nullptr, VQ_ERR_SHAPE,
+               "vq_kivi_decode_attend: protected tokens (sinks) need the tensor-core kernel: %s",
+               a.variant == 1 ? "variant 1 was forced" : kivi_attend_mma_supported(a));
     VQ_REQUIRE(a.gather == nullptr, VQ_ERR_SHAPE,
                "vq_kivi_decode_attend: publishing to peers (gather) needs the tensor-core kernel: %s",
                a.variant == 1 ? "variant 1 was forced" : kivi_attend_mma_supported(a));

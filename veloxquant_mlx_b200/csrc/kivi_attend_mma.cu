@@ -220,6 +220,7 @@ struct Params {
     int wait_test;      // self-test: every warp also waits (briefly) on a barrier that nothing arms
     int split_pv;       // P * v_scale as hi + lo halves (exact products) instead of one rounded half
     vq_peer_gather gather;  // world == 0: the output rows are not published to peers
+    vq_kivi_sinks sinks;    // count == nullptr: no protected tokens
 };
 
 // ---- helpers for the unquantized tail ----------------------------------------------------------
@@ -264,7 +265,9 @@ __device__ __forceinline__ void store_out4(void *base, int32_t dt, int64_t elem,
 //   as an accumulator column pair (cols 2c, 2c+1): the high and the low half of head c, so
 //   a lane adds its two columns and owns ONE head for its rows: no exchange between lanes for
 //   the hi + lo sums, and the softmax of a head is computed once (by the 8 lanes g of column c).
-template <int BITS, int STAGES>
+// SINKS: the call carries protected tokens (extra tail rows); a separate instantiation so that
+// the plain kernel's register allocation (at the limit of four CTAs per SM) is not touched.
+template <int BITS, int STAGES, bool SINKS>
 __global__ void __launch_bounds__(kWarps * 32, 4)
 kivi_attend_mma_kernel(const __grid_constant__ Params p) {
     using C = Cfg<BITS>;
@@ -587,8 +590,15 @@ kivi_attend_mma_kernel(const __grid_constant__ Params p) {
         to[hp][0] = to[hp][1] = to[hp][2] = to[hp][3] = 0.f;
     }
     {
+        // With protected tokens (SINKS), this batch element's side rows follow the residual rows,
+        // twice: their exact rows (weight +1), then the dequantized keys of the slots they left
+        // in the packed store (weight -1, no value: those slots' value scales are 0, so all they
+        // added above is their share of the softmax sum, and this takes it out again).
+        int n_sink = 0;
+        if constexpr (SINKS) n_sink = min(p.sinks.count[b], p.sinks.max_rows);
+        const int n_tail = a.n_res + 2 * n_sink;
         int r = split * kWarps + warp;
-        if (r < a.n_res) {
+        if (r < n_tail) {
             const int r_stride = p.n_splits * kWarps;
             float qt[kChunkHeads][4];
 #pragma unroll
@@ -599,16 +609,26 @@ kivi_attend_mma_kernel(const __grid_constant__ Params p) {
                 for (int i = 0; i < 4; ++i) qt[hp][i] = live ? load_as_f32(a.q, a.q_dtype, qb + i) * sc : 0.f;
             }
             const int64_t rbase = bh * a.res_stride_bh + 4 * lane;
-            for (; r < a.n_res; r += r_stride) {
+            for (; r < n_tail; r += r_stride) {
                 float kd[4], vd[4];
-                load_res4(a.k_res, a.res_dtype, rbase + (int64_t)r * kD, kd);
-                load_res4(a.v_res, a.res_dtype, rbase + (int64_t)r * kD, vd);
+                bool dead = false;
+                if (!SINKS || r < a.n_res) {
+                    load_res4(a.k_res, a.res_dtype, rbase + (int64_t)r * kD, kd);
+                    load_res4(a.v_res, a.res_dtype, rbase + (int64_t)r * kD, vd);
+                } else {
+                    const int rs = r - a.n_res;  // a protected token's row: exact first, then dead
+                    dead = rs >= n_sink;
+                    const int64_t e = bh * p.sinks.stride_bh + (int64_t)(dead ? rs - n_sink : rs) * kD + 4 * lane;
+                    load_res4(dead ? p.sinks.k_dead : p.sinks.k, dead ? VQ_F32 : a.res_dtype, e, kd);
+                    if (dead) vd[0] = vd[1] = vd[2] = vd[3] = 0.f;
+                    else load_res4(p.sinks.v, a.res_dtype, e, vd);
+                }
 #pragma unroll
                 for (int hp = 0; hp < kChunkHeads; ++hp) {
                     const float sv = warp_sum(qt[hp][0] * kd[0] + qt[hp][1] * kd[1] + qt[hp][2] * kd[2] + qt[hp][3] * kd[3]);
                     const float mn = fmaxf(tm[hp], sv);
                     const float f = fast_exp2(tm[hp] - mn), wgt = fast_exp2(sv - mn);
-                    tl[hp] = tl[hp] * f + wgt;
+                    tl[hp] = tl[hp] * f + ((SINKS && dead) ? -wgt : wgt);
                     tm[hp] = mn;
 #pragma unroll
                     for (int i = 0; i < 4; ++i) to[hp][i] = to[hp][i] * f + wgt * vd[i];
@@ -811,10 +831,10 @@ int choose_splits(const vq_kivi_attend_args &a, const DeviceInfo &di) {
     return (int)std::max<int64_t>(1, std::min(want, cap));
 }
 
-template <int BITS, int STAGES>
+template <int BITS, int STAGES, bool SINKS>
 int32_t launch_one(const Params &p, dim3 grid, cudaStream_t st) {
     const int smem = smem_for(BITS, STAGES);
-    VQ_CHECK_CUDA(cudaFuncSetAttribute(kivi_attend_mma_kernel<BITS, STAGES>,
+    VQ_CHECK_CUDA(cudaFuncSetAttribute(kivi_attend_mma_kernel<BITS, STAGES, SINKS>,
                                        cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     // A plain (fully serialised) launch unless the caller set VQ_ATTEND_OVERLAP_PREVIOUS: then the
     // grid is a programmatic dependent of whatever precedes it on the stream (the previous call's
@@ -829,16 +849,17 @@ int32_t launch_one(const Params &p, dim3 grid, cudaStream_t st) {
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = (p.a.flags & VQ_ATTEND_OVERLAP_PREVIOUS) ? 1 : 0;
-    VQ_CHECK_CUDA(cudaLaunchKernelEx(&cfg, kivi_attend_mma_kernel<BITS, STAGES>, p));
+    VQ_CHECK_CUDA(cudaLaunchKernelEx(&cfg, kivi_attend_mma_kernel<BITS, STAGES, SINKS>, p));
     return VQ_OK;
 }
 
 template <int BITS>
 int32_t launch_bits(const Params &p, dim3 grid, cudaStream_t st) {
+    if (p.sinks.count != nullptr) return launch_one<BITS, 2, true>(p, grid, st);  // (the stage knob applies to the plain kernel)
     switch (tuned_stages()) {
-        case 3: return launch_one<BITS, 3>(p, grid, st);
-        case 4: return launch_one<BITS, 4>(p, grid, st);
-        default: return launch_one<BITS, 2>(p, grid, st);
+        case 3: return launch_one<BITS, 3, false>(p, grid, st);
+        case 4: return launch_one<BITS, 4, false>(p, grid, st);
+        default: return launch_one<BITS, 2, false>(p, grid, st);
     }
 }
 
@@ -860,7 +881,7 @@ const char *kivi_attend_mma_supported(const vq_kivi_attend_args &a) {
     if (!is_aligned(a.k_scale, 16) || !is_aligned(a.k_zero, 16) || !is_aligned(a.v_scale, 16) ||
         !is_aligned(a.v_zero, 16) || a.k_param_stride_bh % 4 || a.v_param_stride_bh % 4)
         return "scale/zero buffers must be 16-byte aligned";
-    if (a.n_res > 0 && a.res_dtype != VQ_F16 && a.res_dtype != VQ_BF16 && a.res_dtype != VQ_F32)
+    if ((a.n_res > 0 || a.sinks != nullptr) && a.res_dtype != VQ_F16 && a.res_dtype != VQ_BF16 && a.res_dtype != VQ_F32)
         return "bad residual dtype";
     if (a.n_res > 0 && (!is_aligned(a.k_res, 16) || !is_aligned(a.v_res, 16) || a.res_stride_bh % 8))
         return "residual buffers must be 16-byte aligned";
@@ -950,7 +971,21 @@ int32_t kivi_attend_mma_launch(const vq_kivi_attend_args &a, const DeviceInfo &d
         if (rc != VQ_OK) return rc;
     }
     p.a = a;
-    p.a.gather = nullptr;  // (a host pointer: the kernels get a copy of the struct instead)
+    p.a.gather = nullptr;  // (host pointers: the kernel gets copies of the structs instead)
+    p.a.sinks = nullptr;
+    p.sinks = vq_kivi_sinks{};
+    if (a.sinks != nullptr) {
+        const vq_kivi_sinks &sk = *a.sinks;
+        VQ_REQUIRE(sk.reserved == 0 && sk.max_rows >= 0 && sk.max_rows <= 4096, VQ_ERR_SHAPE,
+                   "vq_kivi_decode_attend: sinks.max_rows=%d must be in 0..4096 (reserved must be 0)", sk.max_rows);
+        if (sk.max_rows > 0) {
+            VQ_REQUIRE(sk.k && sk.v && sk.k_dead && sk.count, VQ_ERR_SHAPE, "vq_kivi_decode_attend: a sinks pointer is NULL");
+            VQ_REQUIRE(is_aligned(sk.k, 16) && is_aligned(sk.v, 16) && is_aligned(sk.k_dead, 16) && sk.stride_bh % 8 == 0 &&
+                           sk.stride_bh >= (int64_t)sk.max_rows * kD,
+                       VQ_ERR_ALIGN, "vq_kivi_decode_attend: sinks rows must be 16-byte aligned, slabs >= max_rows rows apart");
+            p.sinks = sk;
+        }
+    }
     p.wait_test = knob_take(VQ_KNOB_ATTEND_WAIT_TEST);
     p.split_pv = knob_get(VQ_KNOB_ATTEND_EXACT_PV);
     p.gather = vq_peer_gather{};

@@ -322,7 +322,7 @@ def _workspace(device: torch.device, nbytes: int) -> torch.Tensor:
 def kivi_decode_attend(q, k_codes, k_scale, k_zero, v_codes, v_scale, v_zero, group_size, scale, *,
                        store_bits=8, n_quant=None, k_res=None, v_res=None, n_res=None,
                        out=None, out_dtype=None, n_splits=0, variant=0, static_scratch=False,
-                       overlap_previous=False, gather=None, res_offset=0, causal=False,
+                       overlap_previous=False, gather=None, res_offset=0, causal=False, sinks=None,
                        _plan_batch=None, _keep_args=None, _plain_launch=False, _fn="kivi_decode_attend"):
     """Fused dequant + attention over packed codes and an optional unquantized tail.
 
@@ -440,6 +440,28 @@ def kivi_decode_attend(q, k_codes, k_scale, k_zero, v_codes, v_scale, v_zero, gr
             raise ValueError(f"{fn}: unsupported out dtype {out.dtype}")
     if gather is not None and not isinstance(gather, _lib.PeerGather):
         raise ValueError(f"{fn}: gather must be a PeerGather structure (sharding.PeerExchange.layer)")
+    sink_struct = None
+    if sinks is not None:
+        # (exact keys, exact values, dequantized keys of the slots left behind, rows in use per batch element)
+        sk, sv, sd, cnt = sinks
+        for t, nm in ((sk, "sinks[0]"), (sv, "sinks[1]"), (sd, "sinks[2]")):
+            if t.ndim != 4 or t.shape[0] != B or t.shape[1] != H_kv or t.shape[3] != D or not t.is_contiguous() or t.shape != sk.shape:
+                raise ValueError(f"{fn}: {nm} must be a contiguous [{B}, {H_kv}, rows, {D}] tensor, got {tuple(t.shape)}")
+            if t.device != q.device:
+                raise ValueError(f"{fn}: {nm} must be on {q.device}")
+        if sv.dtype != sk.dtype or sd.dtype != torch.float32:
+            raise ValueError(f"{fn}: sinks[0] and sinks[1] must share one dtype and sinks[2] must be float32, got "
+                             f"{sk.dtype}, {sv.dtype}, {sd.dtype}")
+        if k_res is not None and sk.dtype != k_res.dtype:
+            raise ValueError(f"{fn}: sink rows must have the residual's dtype {k_res.dtype}, got {sk.dtype}")
+        if sk.dtype not in _FLOAT_DTYPES:
+            raise ValueError(f"{fn}: unsupported sink row dtype {sk.dtype}")
+        if cnt.dtype != torch.int32 or tuple(cnt.shape) != (B,) or cnt.device != q.device or not cnt.is_contiguous():
+            raise ValueError(f"{fn}: sinks[3] must be an int32 [{B}] tensor on {q.device}, got {cnt.dtype} {tuple(cnt.shape)}")
+        if not has_q or S_q != 1:
+            raise ValueError(f"{fn}: protected tokens need a packed store and one query row")
+        sink_struct = _lib.KiviSinks(k=sk.data_ptr(), v=sv.data_ptr(), k_dead=sd.data_ptr(), count=cnt.data_ptr(),
+                                     stride_bh=sk.shape[2] * D, max_rows=sk.shape[2])
     require_cuda(q, f"{fn}: q")  # (after the shape checks, so that those can be exercised without a GPU)
     a = KiviAttendArgs(
         q=q.data_ptr(), out=out.data_ptr(), q_dtype=dtype_code(q.dtype), out_dtype=dtype_code(out.dtype),
@@ -448,7 +470,11 @@ def kivi_decode_attend(q, k_codes, k_scale, k_zero, v_codes, v_scale, v_zero, gr
         n_splits=int(n_splits), variant=int(variant),
         flags=(_lib.VQ_ATTEND_OVERLAP_PREVIOUS if overlap_previous else 0) | (_lib.VQ_ATTEND_CAUSAL if causal else 0),
         gather=C.addressof(gather) if gather is not None else None,
+        sinks=C.addressof(sink_struct) if sink_struct is not None else None,
     )
+    if sink_struct is not None:
+        a.res_dtype = dtype_code(sinks[0].dtype)
+        a._sink_struct = sink_struct  # (keeps the structure alive as long as the arguments)
     if has_q:
         for t, nm in ((k_codes, "k_codes"), (v_codes, "v_codes"), (k_scale, "k_scale"), (k_zero, "k_zero"),
                       (v_scale, "v_scale"), (v_zero, "v_zero")):
