@@ -11,6 +11,8 @@
 #include <algorithm>
 
 #include "common.cuh"
+#include <cuda.h>
+
 #include "kivi_attend.h"
 
 namespace vq {
@@ -237,13 +239,15 @@ coded_attend_kernel(const CodedParams p, int key_floats, int vlut_floats) {
     const int q_abs = p.S_kv - p.S_q + sq;
     const int n_words = D / 32;
 
-    float m_run[NH], l_run[NH], acc[NH][DPL];
+    // acc[mt]: channels 16*mt + g (regs 0, 1) and + 8 (regs 2, 3); columns 2c, 2c+1 = the (high, low)
+    // weight columns of head c (NH = 4) or heads 2c, 2c+1 (NH = 8)
+    float m_run[NH], l_run[NH], acc[8][4];
 #pragma unroll
-    for (int h = 0; h < NH; ++h) {
-        m_run[h] = -INFINITY; l_run[h] = 0.f;
+    for (int h = 0; h < NH; ++h) { m_run[h] = -INFINITY; l_run[h] = 0.f; }
 #pragma unroll
-        for (int i = 0; i < DPL; ++i) acc[h][i] = 0.f;
-    }
+    for (int mt = 0; mt < 8; ++mt) acc[mt][0] = acc[mt][1] = acc[mt][2] = acc[mt][3] = 0.f;
+    // this lane's rows of the transposing loads: matrix lane / 8 = (keys 0-7 | 8-15) x (channel chunk even | odd)
+    const uint32_t lm_tok = (uint32_t)(8 * (lane >> 4) + (lane & 7)), lm_chunk = (uint32_t)((lane >> 3) & 1);
 
     for (int tile = t_begin + 32 * warp; tile < t_end; tile += 32 * kWarpsC) {
         const int t = tile + lane;
@@ -423,11 +427,22 @@ coded_attend_kernel(const CodedParams p, int key_floats, int vlut_floats) {
 // The same attention as coded_attend_kernel for the serving shape, with the key bits, key
 // magnitudes (and constants) and the value rows of each 32-key tile brought in by the bulk
 // async-copy engine: every warp runs its own two-stage cp.async.bulk + mbarrier pipeline
-// (4 contiguous pieces per tile, 8.7-8.9 KB), so HBM reads stay in flight while the warp
+// (3 linear pieces and two tensor boxes per tile, 8.7-8.9 KB), so HBM reads stay in flight while the warp
 // scores and accumulates. Waits are bounded; a timeout raises a device flag that
 // vq_kivi_attend_status() reports.
-constexpr int kStWarps = 4, kStStages = 2;
-constexpr int kStMag = 512, kStConst = 640, kStV = 768, kStBytes = 768 + 32 * 256;  // one warp, one stage
+//
+// The weighted value sum runs on the tensor cores: O^T[channel, head] += V^T[channel, key] . P[key, head]
+// as m16n8k16 MMAs with the value rows as the A operand (read from shared memory by transposing
+// ldmatrix loads; the rows arrive through a tensor map with the 128-byte swizzle, which spreads
+// the eight rows of a load over all banks) and the softmax weights as the small B operand. With
+// up to four heads per CTA each weight occupies two of the eight columns as a (high, low) pair of
+// halves, so the products carry ~22 bits of the weight; with eight heads it is one rounded
+// half / bfloat16 per weight.
+// three warps per CTA: four CTAs (57 KB of stages each) share an SM, and the 592 CTA slots divide typical
+// (batch x kv head x split) grids better than 444 slots of four warps did (measured 51 vs 53 us at B=8, 8 kv heads, 16K keys)
+constexpr int kStWarps = 3, kStStages = 2;
+// one warp, one stage: key bits | magnitudes | constants | value rows (two swizzled halves of 32 x 128 bytes)
+constexpr int kStMag = 512, kStConst = 640, kStV = 1024, kStBytes = 1024 + 32 * 256;
 constexpr uint32_t kStSpin = 1u << 18;
 __device__ int g_coded_timeout = 0;
 
@@ -447,11 +462,55 @@ __device__ __forceinline__ void st_bulk_g2s(uint32_t dst, const void *src, uint3
                  "r"(bytes), "r"(bar) : "memory");
 }
 
+__device__ __forceinline__ void st_tensor_g2s(uint32_t dst, const CUtensorMap *map, int x, int y, int z, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];" ::"r"(dst),
+        "l"(map), "r"(x), "r"(y), "r"(z), "r"(bar)
+        : "memory");
+}
+__device__ __forceinline__ void st_ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+template <bool BF16>
+__device__ __forceinline__ void st_mma(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    if constexpr (BF16)
+        asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                     : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+    else
+        asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                     : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+// Two weights as one B-operand register in the value dtype: the high halves (rounded weights) or,
+// for the low column of a head, what the rounding left over.
+template <bool BF16>
+__device__ __forceinline__ uint32_t st_pack_weights(float x0, float x1, bool low) {
+    if constexpr (BF16) {
+        __nv_bfloat162 h = __floats2bfloat162_rn(x0, x1);
+        if (low) h = __floats2bfloat162_rn(x0 - __low2float(h), x1 - __high2float(h));
+        return *reinterpret_cast<uint32_t *>(&h);
+    } else {
+        __half2 h = __floats2half2_rn(x0, x1);
+        if (low) h = __floats2half2_rn(x0 - __low2float(h), x1 - __high2float(h));
+        return *reinterpret_cast<uint32_t *>(&h);
+    }
+}
+
+// Warp maximum of finite-or-minus-infinity floats in one reduction instruction: floats order like
+// their bit patterns read as sign-magnitude integers, which one XOR turns into two's complement.
+__device__ __forceinline__ float st_warp_max(float x) {
+    int i = __float_as_int(x);
+    i ^= (i >> 31) & 0x7fffffff;
+    i = __reduce_max_sync(0xffffffffu, i);
+    i ^= (i >> 31) & 0x7fffffff;
+    return __int_as_float(i);
+}
+
 template <bool VBF16, int NH>
-__global__ void __launch_bounds__(kStWarps * 32, 3)
-rabitq_attend_staged_kernel(const CodedParams p) {
-    extern __shared__ __align__(128) uint8_t st_raw[];
-    constexpr int D = 128, DPL = 4;
+__global__ void __launch_bounds__(kStWarps * 32, 4)
+rabitq_attend_staged_kernel(const CodedParams p, const __grid_constant__ CUtensorMap v_map) {
+    extern __shared__ __align__(1024) uint8_t st_raw[];
+    constexpr int D = 128;
     const int lane = threadIdx.x & 31, warp = __shfl_sync(0xffffffffu, threadIdx.x >> 5, 0);  // (known warp-uniform)
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");  // the merge kernel may become resident
     const int split = blockIdx.x;
@@ -465,13 +524,20 @@ rabitq_attend_staged_kernel(const CodedParams p) {
     const int nh = min(NH, hpk - h0);
     const int64_t bh = (int64_t)b * p.H_kv + hkv;
 
-    // shared: barriers | query sign words [NH][4] | query scales [NH] | weights [warp][32][NH] | stages
-    uint64_t *bars = reinterpret_cast<uint64_t *>(st_raw);
-    uint32_t *sh_qbits = reinterpret_cast<uint32_t *>(st_raw + 64);
-    float *sh_qs = reinterpret_cast<float *>(st_raw + 64 + NH * 16);
-    float *sh_w = reinterpret_cast<float *>(st_raw + 256) + warp * (32 * NH);
-    uint8_t *stages = st_raw + 256 + kStWarps * 32 * NH * 4 + (size_t)warp * kStStages * kStBytes;
+    // shared: stages (1024-byte aligned: the swizzle pattern repeats every 1024 bytes) | barriers |
+    // query sign words [NH][4] | query scales [NH] | weights [warp][32][NH]
+    constexpr int kStagesAll = kStWarps * kStStages * kStBytes;
+    uint8_t *stages = st_raw + (size_t)warp * kStStages * kStBytes;
+    uint64_t *bars = reinterpret_cast<uint64_t *>(st_raw + kStagesAll);
+    uint32_t *sh_qbits = reinterpret_cast<uint32_t *>(st_raw + kStagesAll + 64);
+    float *sh_qs = reinterpret_cast<float *>(st_raw + kStagesAll + 64 + NH * 16);
+    float *sh_w = reinterpret_cast<float *>(st_raw + kStagesAll + 256) + warp * (32 * NH);
     const uint32_t wbar0 = st_smem_u32(bars) + 8u * (warp * kStStages);
+    const int g = lane >> 2, c = lane & 3;
+    if (st_smem_u32(st_raw) & 1023u) {  // the swizzled addressing below assumes this; never seen
+        if (threadIdx.x == 0) atomicExch(&g_coded_timeout, 2);
+        return;
+    }
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < kStWarps * kStStages; ++i)
@@ -499,7 +565,6 @@ rabitq_attend_staged_kernel(const CodedParams p) {
     const uint8_t *kb_g = reinterpret_cast<const uint8_t *>(p.k_codes) + bh * p.stride_tok * 16;
     const float *km_g = p.k_mag + bh * p.stride_tok;
     const float *kc_g = p.k_const ? p.k_const + bh * p.stride_tok : nullptr;
-    const uint8_t *v_g = reinterpret_cast<const uint8_t *>(p.v) + bh * p.stride_tok * 256;
 
     auto issue = [&](int j) {  // lane 0 only
         const int64_t tile = t_begin + 32 * (warp + kStWarps * j);
@@ -511,18 +576,22 @@ rabitq_attend_staged_kernel(const CodedParams p) {
         st_bulk_g2s(dst, kb_g + tile * 16, 512, bar);
         st_bulk_g2s(dst + kStMag, km_g + tile, 128, bar);
         if (kc_g) st_bulk_g2s(dst + kStConst, kc_g + tile, 128, bar);
-        st_bulk_g2s(dst + kStV, v_g + tile * 256, 32 * 256, bar);
+        // the value rows: channels 0-63 and 64-127 as two swizzled boxes; rows past the context read as zeros
+        st_tensor_g2s(dst + kStV, &v_map, 0, (int)tile, (int)bh, bar);
+        st_tensor_g2s(dst + kStV + 4096, &v_map, 128, (int)tile, (int)bh, bar);
     };
     if (lane == 0)
         for (int j = 0; j < kStStages - 1 && j < n_local; ++j) issue(j);
 
-    float m_run[NH], l_run[NH], acc[NH][DPL];
+    // acc[mt]: channels 16*mt + g (regs 0, 1) and + 8 (regs 2, 3); columns 2c, 2c+1 = the (high, low)
+    // weight columns of head c (NH = 4) or heads 2c, 2c+1 (NH = 8)
+    float m_run[NH], l_run[NH], acc[8][4];
 #pragma unroll
-    for (int h = 0; h < NH; ++h) {
-        m_run[h] = -INFINITY; l_run[h] = 0.f;
+    for (int h = 0; h < NH; ++h) { m_run[h] = -INFINITY; l_run[h] = 0.f; }
 #pragma unroll
-        for (int i = 0; i < DPL; ++i) acc[h][i] = 0.f;
-    }
+    for (int mt = 0; mt < 8; ++mt) acc[mt][0] = acc[mt][1] = acc[mt][2] = acc[mt][3] = 0.f;
+    // this lane's rows of the transposing loads: matrix lane / 8 = (keys 0-7 | 8-15) x (channel chunk even | odd)
+    const uint32_t lm_tok = (uint32_t)(8 * (lane >> 4) + (lane & 7)), lm_chunk = (uint32_t)((lane >> 3) & 1);
     bool timed_out = false;
     for (int j = 0; j < n_local; ++j) {
         __syncwarp();  // every lane is done with the stage that is refilled next
@@ -548,68 +617,94 @@ rabitq_attend_staged_kernel(const CodedParams p) {
             w[h] = valid ? s : -INFINITY;
         }
         // ---- online softmax per head ------------------------------------------------------
+        float factor[NH];
 #pragma unroll
         for (int h = 0; h < NH; ++h) {
             if (h < nh) {
-                const float tile_max = warp_max(w[h]);  // at least lane 0 of a tile is valid
+                const float tile_max = st_warp_max(w[h]);  // at least lane 0 of a tile is valid
                 const float m_new = fmaxf(m_run[h], tile_max);
-                const float factor = (m_run[h] == -INFINITY) ? 0.f : __expf(m_run[h] - m_new);
+                factor[h] = (m_run[h] == -INFINITY) ? 0.f : __expf(m_run[h] - m_new);
                 m_run[h] = m_new;
                 w[h] = valid ? __expf(w[h] - m_new) : 0.f;
-                l_run[h] = l_run[h] * factor + warp_sum(w[h]);
-#pragma unroll
-                for (int i = 0; i < DPL; ++i) acc[h][i] *= factor;
+                l_run[h] = l_run[h] * factor[h] + w[h];  // (this lane's share: summed over the warp after the loop)
             } else {
                 w[h] = 0.f;
+                factor[h] = 1.f;
             }
         }
-        // ---- values from shared memory: one 8-byte read per row and lane --------------------
+        {
+            // rescale this lane's columns (the maxima settle after a few tiles: skipped when nothing moved)
+            bool moved = false;
+#pragma unroll
+            for (int h = 0; h < NH; ++h) moved |= factor[h] != 1.f;
+            if (moved) {  // (factor is the same in every lane)
+                float f0, f1;
+                if constexpr (NH == 4) {
+                    f0 = f1 = c == 0 ? factor[0] : c == 1 ? factor[1] : c == 2 ? factor[2] : factor[3];
+                } else {
+                    f0 = c == 0 ? factor[0] : c == 1 ? factor[2] : c == 2 ? factor[4] : factor[6];
+                    f1 = c == 0 ? factor[1] : c == 1 ? factor[3] : c == 2 ? factor[5] : factor[7];
+                }
+#pragma unroll
+                for (int mt = 0; mt < 8; ++mt) { acc[mt][0] *= f0; acc[mt][1] *= f1; acc[mt][2] *= f0; acc[mt][3] *= f1; }
+            }
+        }
+        // ---- the weights as the B operand: column g = head g / 2, high or low half (NH = 4); head g (NH = 8)
         __syncwarp();
         *reinterpret_cast<float4 *>(sh_w + lane * NH) = make_float4(w[0], w[1], w[2], w[3]);
         if constexpr (NH == 8) *reinterpret_cast<float4 *>(sh_w + lane * NH + 4) = make_float4(w[4], w[5], w[6], w[7]);
         __syncwarp();
-#pragma unroll 8
-        for (int r = 0; r < 32; ++r) {
-            const uint2 raw = *reinterpret_cast<const uint2 *>(st + kStV + r * 256 + lane * 8);
-            float v[4];
-            if constexpr (VBF16) {
-                v[0] = __uint_as_float(raw.x << 16); v[1] = __uint_as_float(raw.x & 0xffff0000u);
-                v[2] = __uint_as_float(raw.y << 16); v[3] = __uint_as_float(raw.y & 0xffff0000u);
-            } else {
-                const float2 f0 = __half22float2(*reinterpret_cast<const __half2 *>(&raw.x));
-                const float2 f1 = __half22float2(*reinterpret_cast<const __half2 *>(&raw.y));
-                v[0] = f0.x; v[1] = f0.y; v[2] = f1.x; v[3] = f1.y;
+        uint32_t pb[2][2];
+        {
+            const int hh = NH == 4 ? (g >> 1) : g;
+            const bool low = NH == 4 && (g & 1);
+#pragma unroll
+            for (int ks = 0; ks < 2; ++ks) {
+                const float *wp = sh_w + (16 * ks + 2 * c) * NH + hh;
+                pb[ks][0] = st_pack_weights<VBF16>(wp[0], wp[NH], low);
+                pb[ks][1] = st_pack_weights<VBF16>(wp[8 * NH], wp[9 * NH], low);
             }
-            const float4 wa = *reinterpret_cast<const float4 *>(sh_w + r * NH);
-            const float wl4[4] = {wa.x, wa.y, wa.z, wa.w};
+        }
+        // ---- O^T += V^T . P on the tensor cores ---------------------------------------------
+        const uint32_t v_base = st_smem_u32(st + kStV);
 #pragma unroll
-            for (int h = 0; h < 4; ++h)
+        for (int mt = 0; mt < 8; ++mt) {
+            // 16-byte chunk (8 channels) 2*mt + lm_chunk of the 256-byte row: half (mt / 4), chunk within it
+            const uint32_t chunk = (uint32_t)(2 * (mt & 3)) + lm_chunk;
 #pragma unroll
-                for (int i = 0; i < DPL; ++i) acc[h][i] = fmaf(wl4[h], v[i], acc[h][i]);
-            if constexpr (NH == 8) {
-                const float4 wb = *reinterpret_cast<const float4 *>(sh_w + r * NH + 4);
-                const float wh4[4] = {wb.x, wb.y, wb.z, wb.w};
-#pragma unroll
-                for (int h = 0; h < 4; ++h)
-#pragma unroll
-                    for (int i = 0; i < DPL; ++i) acc[4 + h][i] = fmaf(wh4[h], v[i], acc[4 + h][i]);
+            for (int ks = 0; ks < 2; ++ks) {
+                const uint32_t tok = 16u * ks + lm_tok;
+                uint32_t a[4];
+                st_ldmatrix_x4_trans(a, v_base + (uint32_t)(mt >> 2) * 4096u + tok * 128u + ((chunk ^ (tok & 7u)) << 4));
+                st_mma<VBF16>(acc[mt], a, pb[ks][0], pb[ks][1]);
             }
         }
     }
     if (timed_out && lane == 0) atomicExch(&g_coded_timeout, 1);
+#pragma unroll
+    for (int h = 0; h < NH; ++h) l_run[h] = warp_sum(l_run[h]);
 
     // ---- merge the warps of this CTA (the stages are drained: reuse them) ----------------------
     __syncthreads();
-    float *red_o = reinterpret_cast<float *>(st_raw + 256 + kStWarps * 32 * NH * 4);  // [warps][heads][D]
+    float *red_o = reinterpret_cast<float *>(st_raw);  // [warps][heads][D]
     float *red_m = red_o + kStWarps * NH * D;
     float *red_l = red_m + kStWarps * NH;
 #pragma unroll
-    for (int h = 0; h < NH; ++h) {
-        if (h < nh) {
-#pragma unroll
-            for (int i = 0; i < DPL; ++i) red_o[(warp * NH + h) * D + lane * DPL + i] = acc[h][i];
-            if (lane == 0) { red_m[warp * NH + h] = m_run[h]; red_l[warp * NH + h] = l_run[h]; }
+    for (int mt = 0; mt < 8; ++mt) {
+        const int d0 = 16 * mt + g;
+        if constexpr (NH == 4) {  // the high and the low weight column of head c
+            red_o[(warp * NH + c) * D + d0] = acc[mt][0] + acc[mt][1];
+            red_o[(warp * NH + c) * D + d0 + 8] = acc[mt][2] + acc[mt][3];
+        } else {
+            red_o[(warp * NH + 2 * c) * D + d0] = acc[mt][0];
+            red_o[(warp * NH + 2 * c + 1) * D + d0] = acc[mt][1];
+            red_o[(warp * NH + 2 * c) * D + d0 + 8] = acc[mt][2];
+            red_o[(warp * NH + 2 * c + 1) * D + d0 + 8] = acc[mt][3];
         }
+    }
+    if (lane == 0) {
+#pragma unroll
+        for (int h = 0; h < NH; ++h) { red_m[warp * NH + h] = m_run[h]; red_l[warp * NH + h] = l_run[h]; }
     }
     __syncthreads();
     for (int i = threadIdx.x; i < nh * D; i += blockDim.x) {
@@ -690,7 +785,7 @@ int32_t launch_coded(CodedParams &p, void *workspace, int64_t workspace_bytes, i
     p.n_head_chunks = (int)ceil_div(hpk, kHeadsC);
     const int64_t gy = (int64_t)p.H_kv * p.S_q * p.n_head_chunks;
     VQ_REQUIRE(gy <= 65535 && p.B <= 65535, VQ_ERR_SHAPE, "%s: grid too large", who);
-    p.n_splits = staged_ok(p) ? pick_splits_waves(requested_splits, p.S_kv, gy * p.B, di.sm_count, 3, 32)
+    p.n_splits = staged_ok(p) ? pick_splits_waves(requested_splits, p.S_kv, gy * p.B, di.sm_count, 4, 32)
                               : pick_splits(requested_splits, p.S_kv, gy * p.B, di.sm_count);
     const int64_t rows = (int64_t)p.B * p.H_q * p.S_q;
     if (p.n_splits > 1) {
@@ -702,14 +797,19 @@ int32_t launch_coded(CodedParams &p, void *workspace, int64_t workspace_bytes, i
     }
     if (staged_ok(p)) {
         const int nh_s = hpk <= 4 ? 4 : kHeadsC;
-        const size_t st_red = ((size_t)kStWarps * nh_s * p.D + 2 * kStWarps * nh_s) * sizeof(float);
-        const size_t st_smem = 256 + (size_t)kStWarps * 32 * nh_s * 4 + std::max((size_t)kStWarps * kStStages * kStBytes, st_red);
+        static_assert((size_t)kStWarps * kStStages * kStBytes >= ((size_t)kStWarps * 8 * 128 + 2 * kStWarps * 8) * sizeof(float),
+                      "the warp merge reuses the stages");
+        const size_t st_smem = (size_t)kStWarps * kStStages * kStBytes + 256 + (size_t)kStWarps * 32 * nh_s * 4;
         dim3 sgrid(p.n_splits, (unsigned)gy, p.B);
+        // the value rows as [batch * kv head][key][256 bytes], boxes of 32 keys x 128 bytes
+        CUtensorMap v_map;
+        rc = make_rows_map(3, p.v, 256, p.S_kv, p.stride_tok * 256, p.B * p.H_kv, 128, 32, &v_map);
+        if (rc != VQ_OK) return rc;
 #define VQ_STAGED(BF, NHT)                                                                                      \
     do {                                                                                                        \
         VQ_CHECK_CUDA(cudaFuncSetAttribute(rabitq_attend_staged_kernel<BF, NHT>,                                 \
                                            cudaFuncAttributeMaxDynamicSharedMemorySize, (int)st_smem));         \
-        rabitq_attend_staged_kernel<BF, NHT><<<sgrid, kStWarps * 32, st_smem, st>>>(p);                         \
+        rabitq_attend_staged_kernel<BF, NHT><<<sgrid, kStWarps * 32, st_smem, st>>>(p, v_map);                  \
     } while (0)
         if (p.v_dtype == VQ_BF16) { if (nh_s == 4) VQ_STAGED(true, 4); else VQ_STAGED(true, 8); }
         else { if (nh_s == 4) VQ_STAGED(false, 4); else VQ_STAGED(false, 8); }

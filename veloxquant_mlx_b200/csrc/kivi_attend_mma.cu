@@ -922,41 +922,45 @@ static EncodeTiledFn encode_tiled_fn() {
     return fn;
 }
 
-// A per-(batch, kv head) array of 128-byte lines as a rank-3 byte tensor [n_bh][lines][128] whose
-// boxes (`box_lines` lines) are stored with the 128-byte swizzle. Used for the V codes (a unit's
-// rows are contiguous, so a line holds 2 (4-bit) or 4 (2-bit) token rows; one box = one 32-token
-// group) and for the K scales / zeros (4 lines of 32 floats per group).
-static int32_t make_line_map(int slot, const void *base, int64_t lines, int64_t stride_bh_bytes, int32_t n_bh,
-                             int32_t box_lines, CUtensorMap *map) {
-    // An encoding depends on nothing but these five values, so entries never go stale. A decode
+int32_t make_rows_map(int slot, const void *base, int64_t row_bytes, int64_t rows, int64_t stride_bh_bytes, int32_t n_bh,
+                      int32_t box_bytes, int32_t box_rows, CUtensorMap *map) {
+    // An encoding depends on nothing but these values, so entries never go stale. A decode
     // step calls with one set of buffers per layer: 64 direct-mapped entries per use and thread
     // keep all of them (the driver call costs more than the rest of this function's caller).
-    struct Key { const void *ptr; int64_t lines, stride; int32_t n_bh, box; };
+    struct Key { const void *ptr; int64_t row_bytes, rows, stride; int32_t n_bh, box_bytes, box_rows; };
     constexpr int kEntries = 64;
     struct Entry { Key key; CUtensorMap map; };
-    thread_local Entry cache[3][kEntries] = {};
-    const Key key = {base, lines, stride_bh_bytes, n_bh, box_lines};
+    thread_local Entry cache[4][kEntries] = {};
+    const Key key = {base, row_bytes, rows, stride_bh_bytes, n_bh, box_bytes, box_rows};
     const uintptr_t h = reinterpret_cast<uintptr_t>(base) >> 8;
     Entry &e = cache[slot][(h ^ (h >> 6) ^ (h >> 12) ^ (h >> 18)) % kEntries];
     const Key &lk = e.key;
-    if (key.ptr == lk.ptr && key.lines == lk.lines && key.stride == lk.stride && key.n_bh == lk.n_bh && key.box == lk.box) {
+    if (key.ptr == lk.ptr && key.row_bytes == lk.row_bytes && key.rows == lk.rows && key.stride == lk.stride &&
+        key.n_bh == lk.n_bh && key.box_bytes == lk.box_bytes && key.box_rows == lk.box_rows) {
         *map = e.map;
         return VQ_OK;
     }
     EncodeTiledFn enc = encode_tiled_fn();
-    VQ_REQUIRE(enc != nullptr, VQ_ERR_CUDA, "vq_kivi_decode_attend: the driver does not export cuTensorMapEncodeTiled");
-    const cuuint64_t dims[3] = {128, (cuuint64_t)lines, (cuuint64_t)n_bh};
+    VQ_REQUIRE(enc != nullptr, VQ_ERR_CUDA, "the driver does not export cuTensorMapEncodeTiled");
+    const cuuint64_t dims[3] = {(cuuint64_t)row_bytes, (cuuint64_t)rows, (cuuint64_t)n_bh};
     // (the stride of a dimension of extent 1 is not used for addressing but is still checked)
-    const cuuint64_t strides[2] = {128, (cuuint64_t)std::max<int64_t>(stride_bh_bytes, 128)};
-    const cuuint32_t box[3] = {128, (cuuint32_t)box_lines, 1};
+    const cuuint64_t strides[2] = {(cuuint64_t)row_bytes, (cuuint64_t)std::max<int64_t>(stride_bh_bytes, row_bytes)};
+    const cuuint32_t box[3] = {(cuuint32_t)box_bytes, (cuuint32_t)box_rows, 1};
     const cuuint32_t estr[3] = {1, 1, 1};
     const CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void *>(base), dims, strides, box, estr,
                            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    VQ_REQUIRE(r == CUDA_SUCCESS, VQ_ERR_CUDA, "vq_kivi_decode_attend: cuTensorMapEncodeTiled failed (%d)", (int)r);
+    VQ_REQUIRE(r == CUDA_SUCCESS, VQ_ERR_CUDA, "cuTensorMapEncodeTiled failed (%d)", (int)r);
     e.key = key;
     e.map = *map;
     return VQ_OK;
+}
+
+// 128-byte lines: the V codes (a unit's rows are contiguous, so a line holds 2 (4-bit) or 4 (2-bit)
+// token rows; one box = one 32-token group) and the K scales / zeros (4 lines of 32 floats per group).
+static int32_t make_line_map(int slot, const void *base, int64_t lines, int64_t stride_bh_bytes, int32_t n_bh,
+                             int32_t box_lines, CUtensorMap *map) {
+    return make_rows_map(slot, base, 128, lines, stride_bh_bytes, n_bh, 128, box_lines, map);
 }
 
 int32_t kivi_attend_mma_launch(const vq_kivi_attend_args &a, const DeviceInfo &di, cudaStream_t st) {
