@@ -749,6 +749,23 @@ def run_extras(torch, dist, timer, w, plan, world, rank, device, dtype, px, args
                                           "issued_mma_frac_of_peak": mma_fl / (ms * 1e-3) / 1e12 / tpeak, **other}
         vk.quantize_status()
 
+        # -- TurboQuant-RVQ: quantize+pack and unpack+decode of 1 Mi rotated keys
+        from veloxquant_mlx_b200 import rvq
+        Nr = 8 * 8 * 16384
+        tq = rvq.TurboQuantRVQ(D, 2, use_hadamard=True)
+        yr = (torch.randn(Nr, D, device=device) / D ** 0.5).to(torch.float16)
+        cb1, cb2 = tq._codebook1, tq._codebook2
+        ms = graph_time(lambda: rvq.rvq_quant_pack(yr, cb1.centroids, cb1.boundaries, cb2.boundaries, 2), 5)
+        nb = Nr * D * 2 + 2 * Nr * rvq.n_words_for(D, 2) * 4
+        extra["rvq_quant_pack_2bit"] = {"rows": Nr, "us": ms * 1e3, "GBps": nb / (ms * 1e-3) / 1e9, "frac": nb / (ms * 1e-3) / 1e9 / peak}
+        pk1, pk2 = rvq.rvq_quant_pack(yr, cb1.centroids, cb1.boundaries, cb2.boundaries, 2)
+        nrm = torch.ones(Nr, device=device, dtype=torch.bfloat16)
+        dg = tq._rot(device)
+        ms = graph_time(lambda: rvq.rvq_unpack_decode(pk1, pk2, nrm, cb1.centroids, cb2.centroids, dg, 2, D), 5)
+        nb += Nr * 2
+        extra["rvq_unpack_decode_2bit"] = {"rows": Nr, "us": ms * 1e3, "GBps": nb / (ms * 1e-3) / 1e9, "frac": nb / (ms * 1e-3) / 1e9 / peak}
+        del yr, pk1, pk2, nrm
+
         # -- RaBitQ config 4: encode and attend
         from veloxquant_mlx_b200 import rabitq as rq
         Br, Hr, Sr = 8, 8, 16384

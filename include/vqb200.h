@@ -508,6 +508,34 @@ typedef struct vq_rabitq_prefill_args {
 } vq_rabitq_prefill_args;
 int32_t vq_rabitq_prefill_attend(const vq_rabitq_prefill_args *args, void *stream);
 
+/* ------------------------------------------------------------------------------------
+ * TurboQuant-RVQ: two-stage scalar residual quantization of rotated key vectors, packed.
+ * ------------------------------------------------------------------------------------ */
+/* rvq_quant_pack (veloxquant_mlx/metal/_rvq_quant_pack.py:83-149, src/rvq_quant_pack.metal):
+ * rotated [n_rows, D] float16 (device); centroids1 [2^bits], boundaries1 / boundaries2
+ * [2^bits - 1] are HOST arrays (sorted, float16-representable values, as ScalarCodebook holds
+ * them); packed1 / packed2 [n_rows, ceil(D / (32 / bits))] uint32 (device): code i of a word in
+ * bits [i*bits, (i+1)*bits), last word zero-padded. bits 1..4, D <= 1024. Bit-identical to
+ * ScalarCodebook.quantize + _pack_indices of both stages. */
+int32_t vq_rvq_quant_pack(const void *rotated, int64_t n_rows, int32_t D, const float *centroids1,
+                          const float *boundaries1, const float *boundaries2, const uint8_t *table, int32_t bits,
+                          uint32_t *packed1, uint32_t *packed2, void *stream);
+/* Both codes depend on nothing but the coordinate's 16 bits, so the whole two-stage quantizer is a
+ * 65 536-entry table: table[bits of y] = idx1 | idx2 << 4 (device memory, 16-byte aligned, 64 KiB).
+ * Built once per pair of codebooks and passed to vq_rvq_quant_pack as `table` (may be NULL there:
+ * the kernel then compares against the boundaries; with a table the codebook pointers may be NULL
+ * for inputs of at least 65 536 words). No counterpart in the reference. */
+int32_t vq_rvq_build_table(const float *centroids1, const float *boundaries1, const float *boundaries2, int32_t bits,
+                           uint8_t *table, void *stream);
+/* rvq_unpack_decode (veloxquant_mlx/metal/_rvq_unpack_decode.py:78-183, src/rvq_unpack_decode.metal):
+ * the packed streams are read in place from buffers of `cap` rows per (batch, head) of which the
+ * first `seq` are live; norms [n_bh * cap] in norms_dtype; centroids1 / centroids2 [2^bits] are
+ * HOST arrays, diag [D] (+-1) is a device array; out [n_bh * seq, D] float16, rows ordered
+ * (batch-head, token). D a power of two <= 1024. */
+int32_t vq_rvq_unpack_decode(const uint32_t *packed1, const uint32_t *packed2, const void *norms, int32_t norms_dtype,
+                             const float *centroids1, const float *centroids2, const float *diag, int32_t bits,
+                             int32_t D, int64_t n_bh, int64_t seq, int64_t cap, void *out, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -18,6 +18,12 @@ What is executed from the reference, unmodified:
 * ``walsh_hadamard_matrix`` and ``_pack_signs`` are pulled the same way from
   ``allocators/vecinfer.py`` / ``quantizers/rabitq.py`` (both NumPy-only
   bodies inside MLX-importing modules).
+* ``veloxquant_mlx/math/lloyd_max.py`` and ``math/distributions.py`` are MLX-free
+  and loaded whole (``core/constants.py``, which ``lloyd_max`` imports by its package
+  path, is loaded the same way and registered under that path first); the
+  Lloyd-Max codebooks of TurboQuant-RVQ are computed with them, using the
+  supports of ``codebooks/strategies.py:38-94`` and the ``_laplacian_pdf`` of
+  ``quantizers/turboquant_rvq.py``.
 
 Nothing here imports the oracle: the fixtures are the reference's outputs and
 the oracle is checked against them by ``tests/test_oracle_golden.py``.
@@ -162,6 +168,33 @@ def main():
     for d in (1, 2, 8, 128):
         out[f"wht_{d}"] = np.asarray(ns_w["walsh_hadamard_matrix"](d))
     np.savez_compressed(os.path.join(HERE, "vq.npz"), **out)
+    # ---------------- TurboQuant-RVQ codebooks (whole modules) ----------------
+    import sys
+    import types
+
+    consts = load_module(os.path.join(pkg, "core", "constants.py"), "veloxquant_mlx.core.constants")
+    for name in ("veloxquant_mlx", "veloxquant_mlx.core"):
+        sys.modules.setdefault(name, types.ModuleType(name))
+    sys.modules["veloxquant_mlx.core.constants"] = consts
+    lm = load_module(os.path.join(pkg, "math", "lloyd_max.py"), "ref_lloyd_max")
+    dist = load_module(os.path.join(pkg, "math", "distributions.py"), "ref_distributions")
+    ns_l = extract_functions(os.path.join(pkg, "quantizers", "turboquant_rvq.py"), ["_laplacian_pdf"])
+    out = {}
+    for b in (1, 2, 3, 4):
+        for d in (64, 128, 256):
+            sigma = 1.0 / math.sqrt(d)
+            c, _ = lm.lloyd_max(lambda x, s=sigma: dist.gaussian_pdf(x, sigma=s), (-6.0 * sigma, 6.0 * sigma), n_levels=2 ** b)
+            out[f"gauss_b{b}_d{d}"] = c
+            # the default residual scale of TurboQuantRVQ.__init__ for (d, b)
+            sigma_q = math.sqrt((math.sqrt(3.0 * math.pi) / 2.0) * (4.0 ** -b) / d)
+            scale = max(sigma_q / math.sqrt(2.0), 1e-6)
+            c2, _ = lm.lloyd_max(ns_l["_laplacian_pdf"](scale), (-8.0 * scale, 8.0 * scale), n_levels=2 ** b)
+            out[f"laplace_b{b}_d{d}"] = c2
+            out[f"scale_b{b}_d{d}"] = np.float64(scale)
+        for d in (8, 16, 32):
+            c, _ = lm.lloyd_max(lambda x, dd=d: dist.beta_pdf(x, dd), (-1.0 + 1e-6, 1.0 - 1e-6), n_levels=2 ** b)
+            out[f"beta_b{b}_d{d}"] = c
+    np.savez_compressed(os.path.join(HERE, "rvq.npz"), **out)
     print("golden fixtures written to", HERE)
 
 

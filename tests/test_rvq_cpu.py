@@ -1,0 +1,99 @@
+"""TurboQuant-RVQ host pieces: the Lloyd-Max codebooks against fixtures computed by the
+reference's own ``math/lloyd_max.py`` (``tests/golden/rvq.npz``), the packing layout, and the
+oracle's quantize / decode round trip."""
+
+from __future__ import annotations
+
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import rvq as o_rvq
+
+GOLD = np.load(os.path.join(os.path.dirname(__file__), "golden", "rvq.npz"))
+
+
+@pytest.mark.parametrize("b", [1, 2, 3, 4])
+def test_codebooks_match_the_reference_lloyd_max(b):
+    from veloxquant_mlx_b200 import rvq
+
+    for d in (64, 128, 256):
+        cb = rvq.gaussian_codebook(b, d)
+        ref = GOLD[f"gauss_b{b}_d{d}"]
+        np.testing.assert_allclose(cb.centroids32, ref.astype(np.float32), rtol=0, atol=1e-9)
+        np.testing.assert_array_equal(cb.centroids, ref.astype(np.float32).astype(np.float16))
+        ref32 = np.sort(ref.astype(np.float32))
+        np.testing.assert_array_equal(cb.boundaries, ((ref32[:-1] + ref32[1:]) / np.float32(2)).astype(np.float16))
+        scale = float(GOLD[f"scale_b{b}_d{d}"])
+        q = rvq.TurboQuantRVQ(d, b, use_hadamard=True)
+        assert q._residual_scale == scale
+        np.testing.assert_array_equal(q._codebook2.centroids, GOLD[f"laplace_b{b}_d{d}"].astype(np.float32).astype(np.float16))
+    for d in (8, 16, 32):
+        np.testing.assert_array_equal(rvq.beta_codebook(b, d).centroids, GOLD[f"beta_b{b}_d{d}"].astype(np.float32).astype(np.float16))
+
+
+def test_lloyd_max_rejects_bad_arguments():
+    from veloxquant_mlx_b200 import rvq
+
+    with pytest.raises(ValueError):
+        rvq.lloyd_max(lambda x: np.ones_like(x), (1.0, 0.0), 4)
+    with pytest.raises(ValueError):
+        rvq.lloyd_max(lambda x: np.ones_like(x), (0.0, 1.0), 0)
+    c, b = rvq.lloyd_max(lambda x: np.ones_like(x), (0.0, 1.0), 4)   # uniform density: equal cells
+    np.testing.assert_allclose(c, [0.125, 0.375, 0.625, 0.875], atol=1e-6)
+    assert b[0] == -np.inf and b[-1] == np.inf
+
+
+@pytest.mark.parametrize("bits", [1, 2, 3, 4])
+@pytest.mark.parametrize("d", [8, 13, 32, 100, 128])
+def test_pack_layout_and_round_trip(bits, d):
+    from veloxquant_mlx_b200 import rvq
+
+    rng = np.random.default_rng(bits * 100 + d)
+    idx = rng.integers(0, 1 << bits, (5, d)).astype(np.uint8)
+    packed = o_rvq.pack_indices(idx, bits)
+    assert packed.dtype == np.uint32 and packed.shape == (5, rvq.n_words_for(d, bits))
+    np.testing.assert_array_equal(o_rvq.unpack_indices(packed, bits, d), idx)
+    t = rvq.pack_indices(torch.from_numpy(idx), bits)
+    np.testing.assert_array_equal(t.view(torch.int32).numpy().view(np.uint32), packed)
+    np.testing.assert_array_equal(rvq.unpack_indices(t, bits, d).numpy(), idx)
+    # element i of a word sits in bits [i*bits, (i+1)*bits)
+    epw = 32 // bits
+    for i in range(min(d, epw)):
+        assert (int(packed[0, 0]) >> (i * bits)) & ((1 << bits) - 1) == idx[0, i]
+
+
+def test_known_answer_two_bit_word():
+    idx = np.array([[0, 1, 2, 3] * 4], dtype=np.uint8)
+    assert o_rvq.pack_indices(idx, 2)[0, 0] == 0xE4E4E4E4
+
+
+def test_oracle_quantize_counts_boundaries_and_rounds_the_residual():
+    c1 = np.array([-1.0, -0.25, 0.25, 1.0], np.float16)
+    b1 = np.array([-0.625, 0.0, 0.625], np.float16)
+    b2 = np.array([-0.1, 0.0, 0.1], np.float16)
+    y = np.array([[-2.0, -0.625, 0.0, 1e-3, 0.7, np.nan, 0.3, 0.35]], np.float16)
+    idx1, idx2, p1, p2 = o_rvq.rvq_quant_pack(y, c1, b1, b2, 2)
+    # a value equal to a boundary does not exceed it; NaN exceeds nothing
+    assert idx1.tolist() == [[0, 0, 1, 2, 3, 0, 2, 2]]
+    assert idx2[0, 7] == 3 and idx2[0, 6] == 2      # residuals 0.1 (just above fp16(0.1)) and 0.05
+    np.testing.assert_array_equal(o_rvq.unpack_indices(p1, 2, 8), idx1)
+
+
+def test_oracle_decode_inverts_the_rotation():
+    from veloxquant_mlx_b200 import rvq
+    from veloxquant_mlx_b200.rabitq import make_hadamard_diagonal
+
+    d, bits = 128, 4
+    rng = np.random.default_rng(0)
+    x = rng.standard_normal((64, d)).astype(np.float32)
+    x /= np.linalg.norm(x, axis=1, keepdims=True)
+    diag = make_hadamard_diagonal(d, seed=3)
+    y = (o_rvq.wht_butterfly(x * diag) / np.sqrt(np.float32(d))).astype(np.float16)
+    c1, c2 = rvq.gaussian_codebook(bits, d), rvq.TurboQuantRVQ(d, bits, use_hadamard=True)._codebook2
+    _, _, p1, p2 = o_rvq.rvq_quant_pack(y, c1.centroids, c1.boundaries, c2.boundaries, bits)
+    rec = o_rvq.rvq_unpack_decode(p1, p2, np.ones(64, np.float32), c1.centroids, c2.centroids, diag, bits, d).astype(np.float32)
+    cos = (rec * x).sum(1) / np.linalg.norm(rec, axis=1)
+    assert cos.min() > 0.995

@@ -176,6 +176,11 @@ SIGNATURES = {
     "vq_rabitq_attend_workspace_bytes": (C.c_int64, [C.POINTER(RabitqAttendArgs)]),
     "vq_rabitq_decode_attend": (C.c_int32, [C.POINTER(RabitqAttendArgs), C.c_void_p]),
     "vq_rabitq_prefill_attend": (C.c_int32, [C.POINTER(RabitqPrefillArgs), C.c_void_p]),
+    "vq_rvq_quant_pack": (C.c_int32, [C.c_void_p, C.c_int64, C.c_int32, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32,
+                                      C.c_void_p, C.c_void_p, C.c_void_p]),
+    "vq_rvq_build_table": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p, C.c_void_p]),
+    "vq_rvq_unpack_decode": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p, C.c_void_p, C.c_void_p,
+                                         C.c_int32, C.c_int32, C.c_int64, C.c_int64, C.c_int64, C.c_void_p, C.c_void_p]),
     "vq_bit_pack": (C.c_int32, [C.c_void_p, C.c_int64, C.c_int32, C.c_void_p, C.c_void_p]),
     "vq_bit_unpack": (C.c_int32, [C.c_void_p, C.c_int64, C.c_int32, C.c_void_p, C.c_void_p]),
 }

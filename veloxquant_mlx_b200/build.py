@@ -38,6 +38,7 @@ SOURCES = [
     ("rabitq.cu", ["-fmad=false"]),
     ("coded_attend.cu", []),
     ("rabitq_prefill.cu", []),
+    ("rvq.cu", []),
 ]
 
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]

@@ -794,7 +794,8 @@ _CACHE_CLASS_BY_METHOD["kivi"] = KIVIKVCache
 
 from .cache_coded import RaBitQKVCache, VecInferKVCache  # noqa: E402  (registers "vecinfer", "rabitq")
 from .cache_sink import SinkProtectedKVCache  # noqa: E402  (registers "kivi_sink")
+from .cache_rvq import TurboQuantRVQKVCache  # noqa: E402  (registers "turboquant_rvq")
 
 __all__ = ["QuantizerConfigError", "VecInferOptions", "KIVIOptions", "KVCacheConfig", "KVCacheFactory",
-           "KVCacheBuilder", "KIVIKVCache", "SinkProtectedKVCache", "VecInferKVCache", "RaBitQKVCache", "KVCache",
+           "KVCacheBuilder", "KIVIKVCache", "SinkProtectedKVCache", "TurboQuantRVQKVCache", "VecInferKVCache", "RaBitQKVCache", "KVCache",
            "EncodedVector"]

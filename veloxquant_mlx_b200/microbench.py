@@ -127,6 +127,25 @@ def op_rabitq(a):
     _line("rabitq_attend", f"B={B} H_q=32 H_kv={H} S={S} dense f16 values", us, nbytes=B * H * S * (D // 8 + 4 + 2 * D))
 
 
+def op_rvq(a):
+    """TurboQuant-RVQ quantize+pack and unpack+decode of 1 Mi rotated key vectors (head_dim 128)."""
+    from . import rvq
+
+    N, D = 8 * 8 * 16384, 128
+    for bits in (2, 4):
+        q = rvq.TurboQuantRVQ(D, bits, use_hadamard=True)
+        y = (torch.randn(N, D, device="cuda") / D ** 0.5).to(torch.float16)
+        c1, c2 = q._codebook1, q._codebook2
+        us = _time_us(lambda: rvq.rvq_quant_pack(y, c1.centroids, c1.boundaries, c2.boundaries, bits), a.iters)
+        nw = rvq.n_words_for(D, bits)
+        _line("rvq_quant_pack", f"[{N},{D}] f16 b={bits}", us, nbytes=N * D * 2 + 2 * N * nw * 4)
+        p1, p2 = rvq.rvq_quant_pack(y, c1.centroids, c1.boundaries, c2.boundaries, bits)
+        norms = torch.ones(N, device="cuda", dtype=torch.bfloat16)
+        diag = q._rot("cuda")
+        us = _time_us(lambda: rvq.rvq_unpack_decode(p1, p2, norms, c1.centroids, c2.centroids, diag, bits, D), a.iters)
+        _line("rvq_unpack_decode", f"[{N},{D}] b={bits} -> f16", us, nbytes=N * D * 2 + 2 * N * nw * 4 + N * 2)
+
+
 def op_kivi_attend(a):
     """Decode attention over a KIVI cache at the small benchmark shapes (config 1 and config 5, one layer)."""
     from .cache import KVCacheConfig, KVCacheFactory
@@ -146,7 +165,7 @@ def op_kivi_attend(a):
 
 
 OPS = {"kivi_attend": op_kivi_attend, "kivi_quantize": op_kivi_quantize, "vq_quantize": op_vq_quantize, "vq_encode": op_vq_encode,
-       "vq_attend": op_vq_attend, "rabitq": op_rabitq}
+       "vq_attend": op_vq_attend, "rabitq": op_rabitq, "rvq": op_rvq}
 
 
 def main(argv=None):
