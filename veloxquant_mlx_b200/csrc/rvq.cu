@@ -435,9 +435,10 @@ extern "C" int32_t vq_rvq_quant_pack(const void *rotated, int64_t n_rows, int32_
     cudaStream_t st = (cudaStream_t)stream;
     const __half *y = (const __half *)rotated;
     if (table != nullptr && total >= 65536) {
-        // one CTA per SM keeps the 64 KB table in shared memory (smaller inputs: filling it would cost more than it saves)
+        // every CTA keeps the 64 KB table in shared memory, three CTAs per SM (smaller inputs: filling
+        // the table would cost more than it saves)
         const size_t smem = 65536;
-        const unsigned blocks = (unsigned)std::min<int64_t>(ceil_div(total, 512), (int64_t)di.sm_count * 2);
+        const unsigned blocks = (unsigned)std::min<int64_t>(ceil_div(total, 512), (int64_t)di.sm_count * 3);
 #define VQ_RVQ_LUT(B)                                                                                                       \
     do {                                                                                                                    \
         VQ_CHECK_CUDA(cudaFuncSetAttribute(rvq_quant_pack_lut_kernel<B>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
