@@ -267,12 +267,13 @@ int32_t vq_lse_merge(const float *part_o, const float *part_ml, int64_t rows, in
  * node needs no collective inside attention; each rank only has to deliver its rows of the
  * layer's output [B*H_q*S_q, D] to every rank. With `gather` set, the merge step of
  * vq_kivi_decode_attend stores its rows straight into every rank's copy of the gathered tensor
- * (plain stores to peer-mapped addresses over NVLink; no multicast, no bulk-copy engine) and
- * then raises an arrival word on every rank. vq_peer_gather_wait is the consumer side: a
- * one-CTA kernel that returns once all ranks' rows of the current round have arrived, or
- * gives up after a bounded number of polls (vq_kivi_attend_status then reports VQ_ERR_TIMEOUT).
- * Rounds are counted on the device (`state`), so a captured CUDA graph can be replayed.
- * The reference has no multi-device code; there is no counterpart.
+ * (plain stores to peer-mapped addresses over NVLink; no multicast, no bulk-copy engine); each of
+ * its CTAs that wrote rows then fences once and adds 1 to this rank's arrival word on every rank.
+ * vq_peer_gather_wait is the consumer side: a one-CTA kernel that returns once every publishing
+ * rank's word has reached (rounds so far) x (that rank's arrivals per round), or gives up after a
+ * bounded number of polls (vq_kivi_attend_status then reports VQ_ERR_TIMEOUT). Rounds are counted
+ * on the device (`state`), so a captured CUDA graph can be replayed; the words only ever grow
+ * (compared modulo 2^32). The reference has no multi-device code; there is no counterpart.
  * ---------------------------------------------------------------------------------- */
 #define VQ_MAX_PEERS 16
 typedef struct vq_peer_gather {
@@ -283,10 +284,13 @@ typedef struct vq_peer_gather {
     int64_t row_offset;           /* first row of this call's rows inside the gathered tensor */
     void *out[VQ_MAX_PEERS];      /* base of the gathered tensor on each rank (own entry included),
                                      out_dtype, rows of D elements, 16-byte aligned */
-    uint32_t *flags[VQ_MAX_PEERS];/* arrival words on each rank: uint32[world]; this rank
-                                     writes entry `rank` of every array */
-    uint32_t *state;              /* this rank's round counters: uint32[4], zeroed once by the
-                                     caller together with its `flags` array */
+    uint32_t *flags[VQ_MAX_PEERS];/* arrival words on each rank: uint32[world]; this rank adds
+                                     to entry `rank` of every array */
+    uint32_t *state;              /* this rank's round counter (word 2 of uint32[4]), zeroed once by
+                                     the caller together with its `flags` array */
+    int32_t arrivals[VQ_MAX_PEERS]; /* what each publishing rank adds to its word per round: its
+                                     (batch, kv head) units x ceil(query heads per kv head / 4),
+                                     i.e. the CTAs of its call that write rows; read by the wait */
 } vq_peer_gather;
 /* Waits on `stream` until the rows of the next round have arrived from every publishing rank
  * in this rank's gathered tensor. Call it once per vq_kivi_decode_attend that was given the same `gather`. */

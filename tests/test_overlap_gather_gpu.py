@@ -128,6 +128,8 @@ def _emulated_gathers(world, B, H_kv, hpk, dtype):
             pg.out[p] = outs[p].data_ptr()
             pg.flags[p] = flags[p].data_ptr()
         pg.state = states[r].data_ptr()
+        for p in range(world):
+            pg.arrivals[p] = plans[p].owned * -(-hpk // 4)
         structs.append(pg)
     return plans, structs, outs, flags, states
 
@@ -169,8 +171,9 @@ def test_peer_exchange_emulated_ranks_gather_the_unsharded_output(world, B, H_kv
             err = (got.float() - want.float()).abs()
             assert bool((err <= 2e-3 + 1e-2 * want.float().abs()).all()), f"rank {r} round {rnd}: {err.max().item():.3e}"
             assert torch.equal(outs[r], outs[0])
-        assert [int(s[1]) for s in states] == [rnd + 1] * world and [int(s[2]) for s in states] == [rnd + 1] * world
-        assert all(int(f[r]) == rnd + 1 for f in flags for r in range(world))
+        assert [int(s[2]) for s in states] == [rnd + 1] * world
+        # every rank's word r holds (rounds so far) x (rank r's CTAs that write rows)
+        assert all(int(f[r]) == (rnd + 1) * plans[r].owned * -(-hpk // 4) for f in flags for r in range(world))
 
 
 def test_peer_wait_that_nothing_satisfies_times_out_and_is_reported_once():

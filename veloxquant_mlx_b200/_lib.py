@@ -84,6 +84,7 @@ class PeerGather(C.Structure):
         ("world", C.c_int32), ("rank", C.c_int32), ("n_sources", C.c_int32), ("reserved", C.c_int32),
         ("row_offset", C.c_int64),
         ("out", C.c_void_p * VQ_MAX_PEERS), ("flags", C.c_void_p * VQ_MAX_PEERS), ("state", C.c_void_p),
+        ("arrivals", C.c_int32 * VQ_MAX_PEERS),
     ]
 
 

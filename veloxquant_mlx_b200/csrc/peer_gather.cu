@@ -3,9 +3,9 @@
 //
 // The producer side is the merge kernel of the decode attend (kivi_attend_mma.cu): it stores
 // its output rows into every rank's gathered tensor through peer-mapped pointers and then
-// writes its round number into word `rank` of every rank's arrival array. Here:
+// each of its CTAs adds 1 to word `rank` of every rank's arrival array. Here:
 //   - peer_gather_wait_kernel: one CTA, thread r polls arrival word r of THIS rank until it
-//     reaches the round this rank is waiting for. The poll count is bounded; a wait that runs
+//     reaches (the round this rank is waiting for) x (rank r's arrivals per round). The poll count is bounded; a wait that runs
 //     out raises a device flag (reported by vq_kivi_attend_status) and the kernel returns, so
 //     a missing peer can never hang the GPU.
 //   - vq_peer_export / vq_peer_open / vq_peer_close: CUDA IPC handles, so that one process per
@@ -23,7 +23,10 @@ constexpr uint32_t kPeerSpinLimit = 1u << 20;  // x ~0.5-1 us of sleep per poll:
 
 __device__ int g_peer_timeout = 0;
 
-__global__ void __launch_bounds__(32) peer_gather_wait_kernel(const uint32_t *flags, uint32_t *state, int n_sources) {
+struct Arrivals { int32_t n[VQ_MAX_PEERS]; };
+
+__global__ void __launch_bounds__(32) peer_gather_wait_kernel(const uint32_t *flags, uint32_t *state, int n_sources,
+                                                               const __grid_constant__ Arrivals per_round) {
     // whatever follows on the stream may become resident; it must not read the gathered rows
     // before this grid has completed
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
@@ -37,10 +40,11 @@ __global__ void __launch_bounds__(32) peer_gather_wait_kernel(const uint32_t *fl
     if ((int)threadIdx.x < n_sources) {
         ok = false;
         const uint32_t *f = flags + threadIdx.x;
+        const uint32_t need = want * (uint32_t)per_round.n[threadIdx.x];  // (modulo 2^32, like the word itself)
         for (uint32_t i = 0; i < kPeerSpinLimit; ++i) {
             uint32_t v;
             asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(f) : "memory");
-            if ((int32_t)(v - want) >= 0) { ok = true; break; }
+            if ((int32_t)(v - need) >= 0) { ok = true; break; }
             __nanosleep(400);
         }
     }
@@ -77,7 +81,12 @@ extern "C" int32_t vq_peer_gather_wait(const vq_peer_gather *g, void *stream) {
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    VQ_CHECK_CUDA(cudaLaunchKernelEx(&cfg, peer_gather_wait_kernel, (const uint32_t *)g->flags[g->rank], g->state, (int)g->n_sources));
+    Arrivals per_round;
+    for (int r = 0; r < VQ_MAX_PEERS; ++r) {
+        VQ_REQUIRE(r >= g->n_sources || g->arrivals[r] >= 1, VQ_ERR_SHAPE, "vq_peer_gather_wait: arrivals[%d]=%d must be >= 1", r, g->arrivals[r]);
+        per_round.n[r] = g->arrivals[r];
+    }
+    VQ_CHECK_CUDA(cudaLaunchKernelEx(&cfg, peer_gather_wait_kernel, (const uint32_t *)g->flags[g->rank], g->state, (int)g->n_sources, per_round));
     return VQ_OK;
 }
 

@@ -225,6 +225,10 @@ class PeerExchange:
             pg.out[r] = base + l * self._layer_bytes
             pg.flags[r] = base + self._flags_off + l * self._FLAG_STRIDE
         pg.state = self.state[l].data_ptr()
+        n_chunks = -(-self.hpk // 4)   # CTAs per unit that write rows (four query heads each)
+        for r in range(self.plan.world):
+            lo, hi = self.plan.block(r)
+            pg.arrivals[r] = (hi - lo) * n_chunks * self.s_q
         return pg
 
     def layer(self, l: int) -> _lib.PeerGather:
