@@ -42,6 +42,7 @@
 #include <cstdlib>
 #include <cstring>
 #include <random>
+#include <type_traits>
 
 #include "kivi_attend.h"
 
@@ -303,14 +304,14 @@ kivi_attend_mma_kernel(const __grid_constant__ Params p) {
     const uint32_t wbar0 = bar0 + 8u * (warp * STAGES);
     uint8_t *wstages = stages + (size_t)warp * STAGES * C::STAGE_BYTES;
 
-    auto issue_group = [&](int local_idx) {  // called by lane 0 only
+    auto issue_group = [&](auto stage_c, int local_idx) {  // called by lane 0 only; stage_c = local_idx % STAGES
+        constexpr int stage = decltype(stage_c)::value;
         const int64_t bhv = bh;
         const uint8_t *kc_g = a.k_codes + bhv * a.k_codes_stride_bh;
         const float *vs_g = a.v_scale + bhv * a.v_param_stride_bh;
         const float *vz_g = a.v_zero + bhv * a.v_param_stride_bh;
         const int64_t grp = grp_begin + local_idx;
         const int64_t tok0 = grp * kGroup;
-        const int stage = local_idx % STAGES;
         const uint32_t bar = wbar0 + 8u * stage;
         const uint32_t dst = smem_u32(wstages + (size_t)stage * C::STAGE_BYTES);
         constexpr uint32_t code_bytes = kGroup * C::RB;
@@ -329,7 +330,9 @@ kivi_attend_mma_kernel(const __grid_constant__ Params p) {
     }
     __syncthreads();
     if (lane == 0) {
-        for (int i = 0; i < STAGES - 1 && i < n_local; ++i) issue_group(i);
+        if (0 < STAGES - 1 && 0 < n_local) issue_group(std::integral_constant<int, 0>{}, 0);
+        if (1 < STAGES - 1 && 1 < n_local) issue_group(std::integral_constant<int, 1 % STAGES>{}, 1);
+        if (2 < STAGES - 1 && 2 < n_local) issue_group(std::integral_constant<int, 2 % STAGES>{}, 2);
     }
     // This warp's first residual row is read only after its packed groups: ask for its lines now
     // (4 lanes: the two 128-byte halves of the K row and of the V row at 16-bit width).
@@ -379,14 +382,16 @@ kivi_attend_mma_kernel(const __grid_constant__ Params p) {
     const float sc = a.scale * 1.4426950408889634f;  // scores kept in the log2 domain
     bool timed_out = false;
 
-    for (int it = 0; it < n_local; ++it) {
+    // One group of 32 tokens from pipeline stage `stage` (a compile-time value, so that every
+    // shared-memory address of the body is this lane's fixed offset plus a constant).
+    auto body = [&](auto stage_c, const int it) {
+        constexpr int stage = decltype(stage_c)::value;
         __syncwarp();  // every lane is done reading the stage that is refilled next
         if (lane == 0 && it + STAGES - 1 < n_local) {
             // order the lanes' generic-proxy reads before the async-proxy overwrite
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-            issue_group(it + STAGES - 1);
+            issue_group(std::integral_constant<int, (stage + STAGES - 1) % STAGES>{}, it + STAGES - 1);
         }
-        const int stage = it % STAGES;
         // After a timeout the warp stops waiting (later waits would only repeat it); its
         // result is garbage and the host learns of it through vq_kivi_attend_status().
         if (!timed_out && !mbar_wait(wbar0 + 8u * stage, (uint32_t)((it / STAGES) & 1))) timed_out = true;
@@ -560,6 +565,18 @@ kivi_attend_mma_kernel(const __grid_constant__ Params p) {
                 }
             }
         }
+    };
+    {
+        int it = 0;
+        for (; it + STAGES <= n_local; it += STAGES) {
+            body(std::integral_constant<int, 0>{}, it);
+            body(std::integral_constant<int, 1>{}, it + 1);
+            if constexpr (STAGES > 2) body(std::integral_constant<int, 2>{}, it + 2);
+            if constexpr (STAGES > 3) body(std::integral_constant<int, 3>{}, it + 3);
+        }
+        if (it < n_local) body(std::integral_constant<int, 0>{}, it++);
+        if constexpr (STAGES > 2) { if (it < n_local) body(std::integral_constant<int, 1>{}, it++); }
+        if constexpr (STAGES > 3) { if (it < n_local) body(std::integral_constant<int, 2>{}, it++); }
     }
 
     // Self-test of the bounded wait: a barrier that nothing arms never completes its phase.
