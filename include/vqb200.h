@@ -61,14 +61,8 @@ typedef enum vq_knob {
                                     bounded wait runs out, the kernel finishes normally and
                                     vq_kivi_attend_status reports VQ_ERR_TIMEOUT once (one-shot
                                     self-test of that path; nothing faults or hangs) */
-    VQ_KNOB_VQ_WAIT_TEST = 4,    /* 1: the same for the NEXT tcgen05 vq_vq_quantize launch and
+    VQ_KNOB_VQ_WAIT_TEST = 4     /* 1: the same for the NEXT tcgen05 vq_vq_quantize launch and
                                     vq_vq_quantize_status */
-    VQ_KNOB_ATTEND_EXACT_PV = 5  /* decode attend, P.V products: 1 (default) each softmax weight x
-                                    value scale enters the tensor cores as a (high, low) pair of
-                                    halves, exact products; 0 one rounded half (relative rounding
-                                    2^-11, ~5 % fewer instructions; NOT within the attention
-                                    tolerance when value channels carry x20 outliers). Q.K is
-                                    always exact. */
 } vq_knob;
 int32_t vq_tune(int32_t knob, int32_t value);
 

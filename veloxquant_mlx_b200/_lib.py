@@ -69,7 +69,7 @@ VQ_ATTEND_OVERLAP_PREVIOUS = 1
 VQ_ATTEND_CAUSAL = 2
 VQ_MAX_PEERS = 16
 (VQ_KNOB_ATTEND_STAGES, VQ_KNOB_ATTEND_WAVES, VQ_KNOB_VQ_SEARCH, VQ_KNOB_ATTEND_WAIT_TEST,
- VQ_KNOB_VQ_WAIT_TEST, VQ_KNOB_ATTEND_EXACT_PV) = range(6)
+ VQ_KNOB_VQ_WAIT_TEST) = range(5)
 
 
 class KiviSinks(C.Structure):

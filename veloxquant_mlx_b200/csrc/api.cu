@@ -23,9 +23,9 @@ int32_t fail(int32_t code, const char *fmt, ...) {
 // Process-wide knobs behind vq_tune(): defaults, and the accepted range of each.
 namespace {
 struct KnobSpec { int def, lo, hi; };
-constexpr KnobSpec kKnobSpec[] = {{2, 2, 4}, {2, 1, 32}, {0, 0, 4}, {0, 0, 1}, {0, 0, 1}, {1, 0, 1}};
+constexpr KnobSpec kKnobSpec[] = {{2, 2, 4}, {2, 1, 32}, {0, 0, 4}, {0, 0, 1}, {0, 0, 1}};
 constexpr int kNumKnobs = sizeof(kKnobSpec) / sizeof(kKnobSpec[0]);
-std::atomic<int> g_knobs[kNumKnobs] = {{2}, {2}, {0}, {0}, {0}, {1}};
+std::atomic<int> g_knobs[kNumKnobs] = {{2}, {2}, {0}, {0}, {0}};
 }  // namespace
 
 int knob_get(int knob) { return g_knobs[knob].load(std::memory_order_relaxed); }

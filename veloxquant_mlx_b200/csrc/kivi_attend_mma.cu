@@ -219,7 +219,6 @@ struct Params {
     unsigned long long *tickets;  // [B*H_kv][n_chunks]: (epoch << 16) | arrivals of the current call
     unsigned long long epoch;     // 48 bits that tell this call's tickets from whatever the workspace held before
     int wait_test;      // self-test: every warp also waits (briefly) on a barrier that nothing arms
-    int split_pv;       // P * v_scale as hi + lo halves (exact products) instead of one rounded half
     vq_peer_gather gather;  // world == 0: the output rows are not published to peers
     vq_kivi_sinks sinks;    // count == nullptr: no protected tokens
 };
@@ -304,24 +303,24 @@ kivi_attend_mma_kernel(const __grid_constant__ Params p) {
     const uint32_t wbar0 = bar0 + 8u * (warp * STAGES);
     uint8_t *wstages = stages + (size_t)warp * STAGES * C::STAGE_BYTES;
 
+    // Where this warp's first group starts in each of the three linearly copied arrays (the other
+    // three pieces go through tensor maps and are addressed by group number).
+    constexpr uint32_t code_bytes = kGroup * C::RB;
+    const uint8_t *kc_w = a.k_codes + bh * a.k_codes_stride_bh + (int64_t)grp_begin * code_bytes;
+    const float *vs_w = a.v_scale + bh * a.v_param_stride_bh + (int64_t)grp_begin * (kGroup * 4);
+    const float *vz_w = a.v_zero + bh * a.v_param_stride_bh + (int64_t)grp_begin * (kGroup * 4);
     auto issue_group = [&](auto stage_c, int local_idx) {  // called by lane 0 only; stage_c = local_idx % STAGES
         constexpr int stage = decltype(stage_c)::value;
-        const int64_t bhv = bh;
-        const uint8_t *kc_g = a.k_codes + bhv * a.k_codes_stride_bh;
-        const float *vs_g = a.v_scale + bhv * a.v_param_stride_bh;
-        const float *vz_g = a.v_zero + bhv * a.v_param_stride_bh;
-        const int64_t grp = grp_begin + local_idx;
-        const int64_t tok0 = grp * kGroup;
+        const int grp = grp_begin + local_idx;
         const uint32_t bar = wbar0 + 8u * stage;
         const uint32_t dst = smem_u32(wstages + (size_t)stage * C::STAGE_BYTES);
-        constexpr uint32_t code_bytes = kGroup * C::RB;
         mbar_expect_tx(bar, 2 * code_bytes + 4 * 512);
-        bulk_g2s(dst + C::KC_OFF, kc_g + tok0 * C::RB, code_bytes, bar);
-        tensor_g2s(dst + C::VC_OFF, &p.v_map, 0, (int)grp * C::VROWS, (int)bhv, bar);
-        tensor_g2s(dst + C::KS_OFF, &p.ks_map, 0, (int)grp * 4, (int)bhv, bar);
-        tensor_g2s(dst + C::KZ_OFF, &p.kz_map, 0, (int)grp * 4, (int)bhv, bar);
-        bulk_g2s(dst + C::VS_OFF, vs_g + tok0 * 4, 512, bar);
-        bulk_g2s(dst + C::VZ_OFF, vz_g + tok0 * 4, 512, bar);
+        bulk_g2s(dst + C::KC_OFF, kc_w + (uint32_t)local_idx * code_bytes, code_bytes, bar);
+        tensor_g2s(dst + C::VC_OFF, &p.v_map, 0, grp * C::VROWS, (int)bh, bar);
+        tensor_g2s(dst + C::KS_OFF, &p.ks_map, 0, grp * 4, (int)bh, bar);
+        tensor_g2s(dst + C::KZ_OFF, &p.kz_map, 0, grp * 4, (int)bh, bar);
+        bulk_g2s(dst + C::VS_OFF, vs_w + (uint32_t)local_idx * (kGroup * 4), 512, bar);
+        bulk_g2s(dst + C::VZ_OFF, vz_w + (uint32_t)local_idx * (kGroup * 4), 512, bar);
     };
 
     if (tid == 0) {
@@ -526,12 +525,12 @@ kivi_attend_mma_kernel(const __grid_constant__ Params p) {
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
                     oz[j] = fmaf(pa, za4[j], fmaf(pb, zb4[j], oz[j]));
-                    // The (hi, lo) pair keeps the products exact. One rounded half per product (knob
-                    // VQ_KNOB_ATTEND_EXACT_PV = 0) measured 5 % faster at 2 bits, but with value channels
-                    // scaled x20 its 2^-11 relative rounding reached 1.1e-2 absolute: outside the tolerance.
+                    // The (hi, lo) pair keeps the products exact. One rounded half per product measured
+                    // 5 % faster at 2 bits, but with value channels scaled x20 its 2^-11 relative
+                    // rounding reached 1.1e-2 absolute: outside the tolerance, so it is not offered.
                     const float xa = pa * sa4[j], xb = pb * sb4[j];
-                    pbw[j][0] = movmatrix_trans(p.split_pv ? split_pack_trunc(xa) : pack_h2(xa, 0.f));
-                    pbw[j][1] = movmatrix_trans(p.split_pv ? split_pack_trunc(xb) : pack_h2(xb, 0.f));
+                    pbw[j][0] = movmatrix_trans(split_pack_trunc(xa));
+                    pbw[j][1] = movmatrix_trans(split_pack_trunc(xb));
                 }
             }
 #pragma unroll
@@ -1002,7 +1001,6 @@ int32_t kivi_attend_mma_launch(const vq_kivi_attend_args &a, const DeviceInfo &d
         }
     }
     p.wait_test = knob_take(VQ_KNOB_ATTEND_WAIT_TEST);
-    p.split_pv = knob_get(VQ_KNOB_ATTEND_EXACT_PV);
     p.gather = vq_peer_gather{};
     if (a.gather != nullptr) {
         const vq_peer_gather &pg = *a.gather;

@@ -29,14 +29,13 @@ def kivi_available() -> bool:
 
 _KNOBS = {"attend_stages": _lib.VQ_KNOB_ATTEND_STAGES, "attend_waves": _lib.VQ_KNOB_ATTEND_WAVES,
           "vq_search": _lib.VQ_KNOB_VQ_SEARCH, "attend_wait_test": _lib.VQ_KNOB_ATTEND_WAIT_TEST,
-          "vq_wait_test": _lib.VQ_KNOB_VQ_WAIT_TEST, "attend_exact_pv": _lib.VQ_KNOB_ATTEND_EXACT_PV}
+          "vq_wait_test": _lib.VQ_KNOB_VQ_WAIT_TEST}
 
 
 def tune(knob: str, value: int) -> int:
     """Set a process-wide tuning / self-test knob of the native library (``vq_tune``) and return
     its previous value. Knobs: ``attend_stages`` (2..4), ``attend_waves`` (1..32), ``vq_search``
-    (0 choose, 1 tcgen05, 2 mma.sync, 3 exact, 4 tcgen05 with the two-pass epilogue), ``attend_exact_pv`` (default 1: exact P.V products in the
-    decode attention; 0 trades them for ~5 % at 2 bits), and the one-shot self-tests ``attend_wait_test`` / ``vq_wait_test`` that
+    (0 choose, 1 tcgen05, 2 mma.sync, 3 exact, 4 tcgen05 with the two-pass epilogue), and the one-shot self-tests ``attend_wait_test`` / ``vq_wait_test`` that
     make the next launch's bounded device wait run out."""
     if knob not in _KNOBS:
         raise ValueError(f"tune: unknown knob {knob!r}; choices: {sorted(_KNOBS)}")
