@@ -233,8 +233,37 @@ def dtype_code(dt: torch.dtype) -> int:
         raise ValueError(f"unsupported dtype {dt}; expected float16, bfloat16 or float32") from None
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
 def stream_ptr(device: torch.device) -> int:
+    """The current stream of ``device`` as a raw ``cudaStream_t`` value. (Through the raw accessor
+    where PyTorch has it: building a ``torch.cuda.Stream`` object per kernel launch costs several
+    microseconds, more than the launch itself.)"""
+    if _raw_stream is not None:
+        idx = device.index
+        return _raw_stream(torch.cuda.current_device() if idx is None else idx)
     return torch.cuda.current_stream(device).cuda_stream
+
+
+class _NoGuard:
+    def __enter__(self):
+        return None
+
+    def __exit__(self, *exc):
+        return False
+
+
+_NO_GUARD = _NoGuard()
+
+
+def on_device(device: torch.device):
+    """Context that makes ``device`` current for a library call; free when it already is (the
+    device guard object costs more than a kernel launch)."""
+    idx = device.index
+    if idx is None or idx == torch.cuda.current_device():
+        return _NO_GUARD
+    return torch.cuda.device(idx)
 
 
 def require_cuda(t: torch.Tensor, name: str) -> None:

@@ -307,6 +307,7 @@ class KIVIKVCache(StandaloneProtocol):
         self._just_flushed = False
         self._attend_plan = None
         self._append_plan = None
+        self._quant_args = None
         self._sentinel = None
         # byte accounting (same definitions as the reference's properties)
         self._key_bytes_compressed = 0
@@ -389,6 +390,38 @@ class KIVIKVCache(StandaloneProtocol):
 
     def _quantize_rows(self, src_k, src_v, n_flush) -> None:
         g = self._group_size
+        B, H, _, D = src_k.shape
+        s0, s1, s2, s3 = src_k.stride()
+        if (src_k.is_cuda and src_k.dtype is src_v.dtype and src_k.shape == src_v.shape and src_v.stride() == (s0, s1, s2, s3)
+                and s3 == 1 and s2 == D and (B == 1 or s0 == H * s1) and n_flush > 0
+                and self._n_quantized + n_flush <= self._cap and self._n_quantized % g == 0):
+            # Evenly spaced (batch, head) slabs of whole rows, into this cache's own buffers: the two
+            # launches go straight to the library with argument blocks kept from the last flush
+            # (what kernels.kivi_quantize_into would check about the destination holds by construction).
+            qa = self._quant_args
+            if qa is None or qa[0] != self._version:
+                rb, gv = D * self._sb // 8, (D + g - 1) // g
+                common = dict(n_bh=B * H, head_dim=D, levels=self._levels, store_bits=self._sb, group=g, eps=self._eps,
+                              codes_stride_bh=self._cap * rb, recon=None, recon_stride_bh=0)
+                qa = self._quant_args = (self._version, _lib.KiviQuantArgs(axis=0, param_stride_bh=(self._cap // g) * D, **common),
+                                         _lib.KiviQuantArgs(axis=1, param_stride_bh=self._cap * gv, **common), rb, gv)
+            _, ak, av, rb, gv = qa
+            nq = self._n_quantized
+            stride_bh = s1 if H > 1 else (s0 if B > 1 else src_k.shape[2] * D)
+            dt = _lib.dtype_code(src_k.dtype)
+            ak.x, ak.dtype, ak.n_tok, ak.x_stride_bh = src_k.data_ptr(), dt, n_flush, stride_bh
+            ak.codes = self._k_codes.data_ptr() + nq * rb
+            ak.scale = self._k_scale.data_ptr() + 4 * (nq // g) * D
+            ak.zero = self._k_zero.data_ptr() + 4 * (nq // g) * D
+            av.x, av.dtype, av.n_tok, av.x_stride_bh = src_v.data_ptr(), dt, n_flush, stride_bh
+            av.codes = self._v_codes.data_ptr() + nq * rb
+            av.scale = self._v_scale.data_ptr() + 4 * nq * gv
+            av.zero = self._v_zero.data_ptr() + 4 * nq * gv
+            lib, st = _lib.lib(), _lib.stream_ptr(src_k.device)
+            with _lib.on_device(src_k.device):
+                _lib.check(lib.vq_kivi_quantize_pack(C.byref(ak), st), "KIVIKVCache: quantize keys")
+                _lib.check(lib.vq_kivi_quantize_pack(C.byref(av), st), "KIVIKVCache: quantize values")
+            return
         kernels.kivi_quantize_into(src_k[:, :, :n_flush], -2, g, self._b, codes=self._k_codes,
                                    scale=self._k_scale, zero=self._k_zero, tok_offset=self._n_quantized,
                                    store_bits=self._sb, eps=self._eps)

@@ -274,7 +274,8 @@ kivi_attend_mma_kernel(const __grid_constant__ Params p) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     const vq_kivi_attend_args &a = p.a;
     const int b = blockIdx.z, hkv = blockIdx.y;
-    // the tail and merge kernels may be made resident as soon as every CTA of this grid has started
+    // whatever follows on the stream (the next call, launched as a programmatic dependent) may be
+    // made resident as soon as every CTA of this grid has started
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const int split = blockIdx.x / p.n_chunks;
     const int h0 = (blockIdx.x % p.n_chunks) * kChunkHeads;  // first head of this CTA's chunk
@@ -848,7 +849,7 @@ int32_t launch_one(const Params &p, dim3 grid, cudaStream_t st) {
                                        cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     // A plain (fully serialised) launch unless the caller set VQ_ATTEND_OVERLAP_PREVIOUS: then the
     // grid is a programmatic dependent of whatever precedes it on the stream (the previous call's
-    // merge kernel triggers early) and only its epilogue waits for that work.
+    // kernel triggers at its start) and only its residual rows and merge wait for that work.
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid;
     cfg.blockDim = dim3(kWarps * 32);

@@ -1,9 +1,9 @@
 // Sharded decode across the GPUs of one node: the consumer side of the per-layer output
 // exchange, and the inter-process mapping of the exchange buffers.
 //
-// The producer side is the merge kernel of the decode attend (kivi_attend_mma.cu): it stores
-// its output rows into every rank's gathered tensor through peer-mapped pointers and then
-// each of its CTAs adds 1 to word `rank` of every rank's arrival array. Here:
+// The producer side is the merging CTAs of the decode attend kernel (kivi_attend_mma.cu): they store
+// their output rows into every rank's gathered tensor through peer-mapped pointers and then
+// each of those CTAs adds 1 to word `rank` of every rank's arrival array. Here:
 //   - peer_gather_wait_kernel: one CTA, thread r polls arrival word r of THIS rank until it
 //     reaches (the round this rank is waiting for) x (rank r's arrivals per round). The poll count is bounded; a wait that runs
 //     out raises a device flag (reported by vq_kivi_attend_status) and the kernel returns, so

@@ -172,7 +172,7 @@ def kivi_group_quant_dequant(x: torch.Tensor, axis: int, group_size: int, levels
         codes=None, codes_stride_bh=0, scale=None, zero=None, param_stride_bh=0,
         recon=out.data_ptr(), recon_stride_bh=S * D,
     )
-    with torch.cuda.device(x.device):
+    with _lib.on_device(x.device):
         check(lib().vq_kivi_quant_dequant(C.byref(a), stream_ptr(x.device)), "kivi_group_quant_dequant")
     return out
 
@@ -242,7 +242,7 @@ def kivi_quantize_into(x: torch.Tensor, axis: int, group_size: int, bits: int, *
         scale=scale.data_ptr() + 4 * p_off, zero=zero.data_ptr() + 4 * p_off, param_stride_bh=p_stride,
         recon=None, recon_stride_bh=0,
     )
-    with torch.cuda.device(x.device):
+    with _lib.on_device(x.device):
         check(lib().vq_kivi_quantize_pack(C.byref(a), stream_ptr(x.device)), "kivi_quantize")
 
 
@@ -296,7 +296,7 @@ def scalar_decode_once(codes: torch.Tensor, scale: torch.Tensor, zero: torch.Ten
         store_bits=store_bits, group=int(group_size), n_bh=B * H, n_tok=S, head_dim=D,
         out=out.data_ptr(), out_dtype=dtype_code(out_dtype), out_stride_bh=S * D,
     )
-    with torch.cuda.device(codes.device):
+    with _lib.on_device(codes.device):
         check(lib().vq_kivi_dequant(C.byref(a), stream_ptr(codes.device)), "scalar_decode_once")
     return out
 
@@ -310,7 +310,7 @@ _workspaces: dict = {}
 
 def _workspace(device: torch.device, nbytes: int) -> torch.Tensor:
     """Per-(device, stream) scratch buffer, grown geometrically and reused."""
-    key = (device.index, torch.cuda.current_stream(device).cuda_stream)
+    key = (device.index, stream_ptr(device))
     buf = _workspaces.get(key)
     if buf is None or buf.numel() < nbytes:
         buf = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
@@ -490,7 +490,7 @@ def kivi_decode_attend(q, k_codes, k_scale, k_zero, v_codes, v_scale, v_zero, gr
         a.k_res, a.v_res = k_res.data_ptr() + res_offset * row_bytes, v_res.data_ptr() + res_offset * row_bytes
         a.res_dtype = dtype_code(k_res.dtype)
         a.res_stride_bh = k_res.shape[2] * k_res.shape[3]
-    with torch.cuda.device(q.device):
+    with _lib.on_device(q.device):
         if _plain_launch and a.flags & _lib.VQ_ATTEND_OVERLAP_PREVIOUS and not n_splits:
             # the split plan (= summation order) of an overlapped call, launched plainly: for a call
             # whose packed store was written by the kernels right before it
@@ -599,7 +599,7 @@ def lse_merge(part_o: torch.Tensor, part_ml: torch.Tensor, out_dtype=torch.float
     rows, n_splits, D = part_o.shape
     po, pm = part_o.contiguous(), part_ml.contiguous()
     out = torch.empty((rows, D), dtype=out_dtype, device=part_o.device)
-    with torch.cuda.device(part_o.device):
+    with _lib.on_device(part_o.device):
         check(lib().vq_lse_merge(po.data_ptr(), pm.data_ptr(), rows, n_splits, D, out.data_ptr(),
                                  dtype_code(out_dtype), stream_ptr(part_o.device)), fn)
     return out
@@ -648,7 +648,7 @@ def turboquant_bit_pack(indices: torch.Tensor, b: int) -> torch.Tensor:
     require_cuda(indices, "turboquant_bit_pack: indices")
     flat = indices.reshape(-1).to(torch.uint8).contiguous()
     out = torch.empty(N * b // 8, dtype=torch.uint8, device=indices.device)
-    with torch.cuda.device(indices.device):
+    with _lib.on_device(indices.device):
         check(lib().vq_bit_pack(flat.data_ptr(), N, b, out.data_ptr(), stream_ptr(indices.device)),
               "turboquant_bit_pack")
     return out
@@ -668,7 +668,7 @@ def turboquant_bit_unpack(packed: torch.Tensor, N: int, b: int) -> torch.Tensor:
     require_cuda(packed, "turboquant_bit_unpack: packed")
     flat = packed.reshape(-1).to(torch.uint8).contiguous()
     out = torch.empty(N, dtype=torch.uint8, device=packed.device)
-    with torch.cuda.device(packed.device):
+    with _lib.on_device(packed.device):
         check(lib().vq_bit_unpack(flat.data_ptr(), N, b, out.data_ptr(), stream_ptr(packed.device)),
               "turboquant_bit_unpack")
     return out

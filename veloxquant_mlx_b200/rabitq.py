@@ -10,6 +10,7 @@ import ctypes as C
 import numpy as np
 import torch
 
+from . import _lib
 from ._lib import RabitqAttendArgs, RabitqPrefillArgs, check, dtype_code, lib, require_cuda, stream_ptr
 from .kernels import _FLOAT_DTYPES, _workspace
 
@@ -55,7 +56,7 @@ def _encode(keys: torch.Tensor, diag, rotate: int, who: str):
     keys = keys.contiguous()
     bits = torch.empty((N, D // 8), dtype=torch.uint8, device=keys.device)
     mag = torch.empty((N,), dtype=torch.float32, device=keys.device)
-    with torch.cuda.device(keys.device):
+    with _lib.on_device(keys.device):
         check(lib().vq_rabitq_encode(keys.data_ptr(), dtype_code(keys.dtype), N, D, dptr, rotate,
                                      bits.data_ptr(), mag.data_ptr(), stream_ptr(keys.device)), who)
     return bits, mag
@@ -80,7 +81,7 @@ def rabitq_pack_values(v_idx: torch.Tensor) -> torch.Tensor:
     require_cuda(v_idx, "rabitq_pack_values: v_idx")
     v = v_idx.to(torch.uint8).contiguous()
     out = torch.empty((*v.shape[:-1], v.shape[-1] // 2), dtype=torch.uint8, device=v.device)
-    with torch.cuda.device(v.device):
+    with _lib.on_device(v.device):
         check(lib().vq_rabitq_pack_values(v.data_ptr(), out.numel(), out.data_ptr(), stream_ptr(v.device)),
               "rabitq_pack_values")
     return out
@@ -100,7 +101,7 @@ def rabitq_hamming_score(qbits: torch.Tensor, bits: torch.Tensor, scale: float, 
     bb = bits.to(torch.uint8).contiguous()
     cxf = cx.to(device=bits.device, dtype=torch.float32).contiguous()
     out = torch.empty((N,), dtype=torch.float32, device=bits.device)
-    with torch.cuda.device(bits.device):
+    with _lib.on_device(bits.device):
         check(lib().vq_rabitq_hamming_score(qb.data_ptr(), bb.data_ptr(), N, n_bytes, float(scale), cxf.data_ptr(),
                                             out.data_ptr(), stream_ptr(bits.device)), "rabitq_hamming_score")
     return out
@@ -167,7 +168,7 @@ def rabitq_fused_attend(q, q_scale, k_bits, k_mag, k_const, v_idx, v_cents=None,
         v = v_idx.to(torch.uint8).contiguous()
         cents = v_cents.to(device=q.device, dtype=torch.float32).contiguous()
         a.v, a.v_cents, a.n_cents = v.data_ptr(), cents.data_ptr(), cents.shape[0]
-    with torch.cuda.device(q.device):
+    with _lib.on_device(q.device):
         ws = _workspace(q.device, lib().vq_rabitq_attend_workspace_bytes(C.byref(a)))
         a.workspace, a.workspace_bytes = ws.data_ptr(), ws.numel()
         check(lib().vq_rabitq_decode_attend(C.byref(a), stream_ptr(q.device)), fn)
@@ -233,7 +234,7 @@ def rabitq_prefill_attend(q, scale, k_bits, k_mag, k_const, v_idx, v_cents=None,
         v = v_idx.to(torch.uint8).contiguous()
         cents = v_cents.to(device=q.device, dtype=torch.float32).contiguous()
         a.v_mode, a.v, a.v_cents, a.n_cents = 3, v.data_ptr(), cents.data_ptr(), cents.shape[0]
-    with torch.cuda.device(q.device):
+    with _lib.on_device(q.device):
         check(lib().vq_rabitq_prefill_attend(C.byref(a), stream_ptr(q.device)), fn)
     return out
 

@@ -20,6 +20,7 @@ from functools import lru_cache
 import numpy as np
 import torch
 
+from . import _lib
 from ._lib import check, dtype_code, lib, require_cuda, stream_ptr
 from .rabitq import make_hadamard_diagonal, make_rotation_matrix
 
@@ -211,7 +212,7 @@ def rvq_code_table(centroids1, boundaries1, boundaries2, bits: int, device) -> t
     if t is None:
         t = torch.empty(65536, dtype=torch.uint8, device=device)
         require_cuda(t, f"{who}: device")
-        with torch.cuda.device(device):
+        with _lib.on_device(device):
             check(lib().vq_rvq_build_table(c1.ctypes.data_as(C.c_void_p), b1.ctypes.data_as(C.c_void_p),
                                            b2.ctypes.data_as(C.c_void_p), bits, t.data_ptr(), stream_ptr(device)), who)
         if len(_TABLES) > 64:
@@ -248,7 +249,7 @@ def rvq_quant_pack(rotated: torch.Tensor, centroids1, boundaries1, boundaries2, 
     table = rvq_code_table(c1, b1, b2, bits, y.device) if use_table else None
     p1 = torch.empty((N, nw), dtype=torch.uint32, device=y.device)
     p2 = torch.empty((N, nw), dtype=torch.uint32, device=y.device)
-    with torch.cuda.device(y.device):
+    with _lib.on_device(y.device):
         check(lib().vq_rvq_quant_pack(y.data_ptr(), N, D, c1.ctypes.data_as(C.c_void_p), b1.ctypes.data_as(C.c_void_p),
                                       b2.ctypes.data_as(C.c_void_p), table.data_ptr() if table is not None else None, bits,
                                       p1.data_ptr(), p2.data_ptr(), stream_ptr(y.device)), who)
@@ -305,7 +306,7 @@ def rvq_unpack_decode(packed1: torch.Tensor, packed2: torch.Tensor, norms: torch
         nr = nr.float()
     p1, p2 = packed1.contiguous(), packed2.contiguous()
     out = torch.empty((N, d), dtype=torch.float16, device=dev)
-    with torch.cuda.device(dev):
+    with _lib.on_device(dev):
         check(lib().vq_rvq_unpack_decode(p1.data_ptr(), p2.data_ptr(), nr.data_ptr(), dtype_code(nr.dtype),
                                          c1.ctypes.data_as(C.c_void_p), c2.ctypes.data_as(C.c_void_p), dg.data_ptr(), bits, d,
                                          bh, seq, cap, out.data_ptr(), stream_ptr(dev)), who)

@@ -190,7 +190,7 @@ class PeerExchange:
         else:
             handle = (C.c_ubyte * 64)()
             off = C.c_int64(0)
-            with torch.cuda.device(device):
+            with _lib.on_device(device):
                 _lib.check(lib.vq_peer_export(self.buffer.data_ptr(), handle, C.byref(off)), "PeerExchange")
             mine = (bytes(handle), int(off.value))
             everyone = [None] * plan.world
@@ -205,7 +205,7 @@ class PeerExchange:
                 if entry is None:
                     base = C.c_void_p()
                     hb = (C.c_ubyte * 64).from_buffer_copy(h)
-                    with torch.cuda.device(device):
+                    with _lib.on_device(device):
                         _lib.check(lib.vq_peer_open(hb, C.byref(base)), "PeerExchange")
                     entry = self._MAPPED[key] = [base.value, 0]
                 entry[1] += 1
@@ -238,7 +238,7 @@ class PeerExchange:
 
     def wait(self, l: int) -> None:
         """Enqueue, on the current stream, the bounded wait for all ranks' rows of layer ``l``."""
-        with torch.cuda.device(self.device):
+        with _lib.on_device(self.device):
             _lib.check(_lib.lib().vq_peer_gather_wait(C.byref(self._structs[l]), _lib.stream_ptr(self.device)),
                        "PeerExchange.wait")
 
@@ -264,7 +264,7 @@ class PeerExchange:
             entry = self._MAPPED[key]
             entry[1] -= 1
             if entry[1] == 0:
-                with torch.cuda.device(self.device):
+                with _lib.on_device(self.device):
                     lib.vq_peer_close(entry[0])
                 del self._MAPPED[key]
         self._opened = []

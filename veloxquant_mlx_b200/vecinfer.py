@@ -15,6 +15,7 @@ import math
 import numpy as np
 import torch
 
+from . import _lib
 from ._lib import VqAttendArgs, VqEncodeArgs, check, dtype_code, lib, require_cuda, stream_ptr
 from .kernels import _FLOAT_DTYPES, _workspace
 
@@ -97,7 +98,7 @@ def _dual_transform_wht(x: torch.Tensor, smooth, for_query: bool, who: str) -> t
             sm2, n_heads, tph = sm.reshape(-1, D).contiguous(), x.shape[-3], x.shape[-2]
         sm_ptr, rows = sm2.data_ptr(), sm2.shape[0]
     out = torch.empty(x.shape, dtype=torch.float32, device=x.device)
-    with torch.cuda.device(x.device):
+    with _lib.on_device(x.device):
         check(lib().vq_vq_dual_transform(x.data_ptr(), dtype_code(x.dtype), n_rows, D, tph, n_heads, sm_ptr, rows,
                                          0 if for_query else 1, wht_entry(D), out.data_ptr(), stream_ptr(x.device)), who)
     return out
@@ -148,7 +149,7 @@ def quantize_vq(x: torch.Tensor, codebook: torch.Tensor, sub_dim: int, *,
     xs = x.contiguous()
     out = torch.empty((*lead, n_sub), dtype=index_dtype, device=x.device)
     n = xs.numel() // sub_dim
-    with torch.cuda.device(x.device):
+    with _lib.on_device(x.device):
         check(lib().vq_vq_quantize(xs.data_ptr(), dtype_code(x.dtype), n, sub_dim, cb.data_ptr(), n_c, stacked,
                                    out.data_ptr(), _INDEX_DTYPES[index_dtype], stream_ptr(x.device)), "quantize_vq")
     return out
@@ -173,7 +174,7 @@ def dequantize_vq(indices: torch.Tensor, codebook: torch.Tensor, *, out_dtype=No
     out_dtype = out_dtype or (codebook.dtype if codebook.dtype in _FLOAT_DTYPES else torch.float32)
     idx = indices.contiguous()
     out = torch.empty((*lead, n_sub * sd), dtype=out_dtype, device=indices.device)
-    with torch.cuda.device(indices.device):
+    with _lib.on_device(indices.device):
         check(lib().vq_vq_dequant(idx.data_ptr(), _INDEX_DTYPES[idx.dtype], idx.numel(), cb.data_ptr(), n_c, sd,
                                   stacked, out.data_ptr(), dtype_code(out_dtype), stream_ptr(indices.device)),
               "dequantize_vq")
@@ -237,7 +238,7 @@ def _encode_decode(who: str, x: torch.Tensor, codebook: torch.Tensor, sub_dim: i
         x_hat=hat.data_ptr() if hat is not None else None, hat_dtype=dtype_code(hat_dtype),
         indices=idx.data_ptr(), index_bytes=_INDEX_DTYPES[index_dtype])
     fn = lib().vq_vq_encode_decode_keys if keys else lib().vq_vq_encode_decode_values
-    with torch.cuda.device(x.device):
+    with _lib.on_device(x.device):
         check(fn(C.byref(a), stream_ptr(x.device)), who)
     return hat, idx
 
@@ -332,7 +333,7 @@ def fused_sdpa_vq(q_tilde: torch.Tensor, k_indices: torch.Tensor, k_codebook: to
             raise ValueError(f"fused_sdpa: dense values must be float [B,H_kv,{cap},{D}], got {tuple(v.shape)}")
         v = v.contiguous()
         a.v_mode, a.v, a.v_dtype = 0, v.data_ptr(), dtype_code(v.dtype)
-    with torch.cuda.device(q.device):
+    with _lib.on_device(q.device):
         ws = _workspace(q.device, lib().vq_vq_attend_workspace_bytes(C.byref(a)))
         a.workspace, a.workspace_bytes = ws.data_ptr(), ws.numel()
         check(lib().vq_vq_decode_attend(C.byref(a), stream_ptr(q.device)), "fused_sdpa")
