@@ -880,6 +880,23 @@ def run_c5(torch, dist, timer, world, rank, device, dtype, args):
     wq = dict(w, ctx=ctx_end)
     wq["n_quant"], wq["n_res"] = caches[0]._n_quantized, caches[0]._n_res
     bl = algorithmic_bytes_per_layer(wq)
+
+    # The attention of the same step as the device sees it: the 64 launches (and, sharded, the
+    # exchange) captured once and replayed, as in the default workload's timed region.
+    def attend_step():
+        for l in range(L):
+            caches[l].fused_sdpa(qs[l], scale, out=outs[l], overlap_previous=True, gather=px.layer(l) if px is not None else None)
+            if px is not None:
+                px.wait(l)
+
+    try:
+        replay = capture(torch, attend_step).replay
+        for _ in range(3):
+            replay()
+        graph_ms = float(np.median(timer.blocks(replay, 10, 5)))
+    except Exception:
+        graph_ms = None
+    vk.attend_status()
     if px is not None:
         px.close()
     return {"workload": w["name"], "layers": L, "batch": B, "prompt": S, "decode_steps": n_dec, "bits": w["bits"],
@@ -887,8 +904,11 @@ def run_c5(torch, dist, timer, world, rank, device, dtype, args):
             "prefill_tokens_per_s": B * S / (prefill_ms * 1e-3),
             "decode_ms_per_step": ms, "decode_tokens_per_s": B / (ms * 1e-3),
             "decode_value": bl * L / (ms * 1e-3) / 1e9, "unit": UNIT,
+            "attend_graph_ms_per_step": graph_ms,
+            "attend_graph_value": None if not graph_ms else bl * L / (graph_ms * 1e-3) / 1e9,
             "units_per_rank": plan.size, "gather": "peer" if px is not None else ("none" if world == 1 else "not gathered"),
-            "note": "decode steps are eager launches through update_and_fetch + fused_sdpa (host-bound at this size)"}
+            "note": "decode steps are eager launches through update_and_fetch + fused_sdpa (host-bound at this size); "
+                    "attend_graph_*: the step's 64 attention launches (+ exchange) captured into a CUDA graph"}
 
 
 def main():

@@ -821,7 +821,7 @@ int smem_for(int bits, int stages) {
 //   calls that overlap their predecessor: CTAs of two or three calls are resident together, so a
 //     launch need not fill the GPU by itself and longer CTAs win -- about 64 groups per warp
 //     (32 when there are only a few units): batch 16: 3-4 splits, batch 8: 2-4, batch 4: 2-5,
-//     batch 2: 5-9, batch 1: 5-8.
+//     batch 2: 5-9, batch 1: 5-8. Shorter contexts take proportionally shorter runs (16 at least).
 int choose_splits(const vq_kivi_attend_args &a, const DeviceInfo &di) {
     (void)di;
     const int tiles = (int)ceil_div(a.n_quant, kGroup * kWarps);  // CTA-sized pieces of the context
@@ -833,7 +833,12 @@ int choose_splits(const vq_kivi_attend_args &a, const DeviceInfo &di) {
     const int64_t cap = std::min<int64_t>(std::max(1, tiles / 4), kMaxSplits);  // >= 4 groups per warp
     int64_t want;
     if (a.flags & VQ_ATTEND_OVERLAP_PREVIOUS) {
-        const int64_t per_warp = std::min<int64_t>(64, std::max<int64_t>(32, 2 * units));
+        // (the run of groups a warp takes grows with the launch's total work, units x groups,
+        // normalised to the 32K context the figures above were measured at: a launch of half the
+        // context and half the units -- one rank's share of a sharded 16K-token batch -- at 64 groups
+        // per warp was 64 CTAs that took as long as the unsharded launch)
+        const int64_t scaled = (2 * units * groups + 512) / 1024;
+        const int64_t per_warp = std::min<int64_t>(64, std::max<int64_t>(groups >= 768 ? 32 : 16, scaled));
         want = (groups + 2 * per_warp) / (4 * per_warp);  // rounded to nearest
     } else {
         const int64_t fill = ceil_div((int64_t)64 * tuned_waves() * 2, units);  // 256 CTAs at the default setting
