@@ -343,6 +343,23 @@ def test_mma_attend_parity(b, H, H_kv, n_quant, n_res):
     _assert_attn_close(out3.float().cpu().numpy(), ref)
 
 
+@pytest.mark.parametrize("b", [2, 4])
+@pytest.mark.parametrize("B,H,H_kv", [(3, 40, 8), (4, 48, 6), (12, 14, 2)])
+def test_mma_attend_parity_more_than_four_heads_long_context(b, B, H, H_kv):
+    """5, 8 and 7 query heads per kv head over a context long and wide enough (512 groups or more,
+    12288 unit-groups or more) that the launch takes the eight-head kernel; plain and overlapped
+    launches, automatic and explicit splits."""
+    rng = np.random.default_rng(b + H)
+    (qt, kc, ks, kz, vc, vs, vz, k_res, v_res), ref = _packed_case(rng, B, H, H_kv, 16384 + 32, 37, b, "bfloat16")
+    k = _k()
+    for kw in ({}, {"n_splits": 3}, {"overlap_previous": True}):
+        out = k.kivi_decode_attend(qt, kc, ks, kz, vc, vs, vz, 32, 1.0 / math.sqrt(128), store_bits=b,
+                                   k_res=k_res, v_res=v_res, variant=2, **kw)
+        _assert_attn_close(out.float().cpu().numpy(), ref, strict=False)
+    from veloxquant_mlx_b200 import _lib
+    _lib.check(_lib.lib().vq_kivi_attend_status(), "status")
+
+
 @pytest.mark.parametrize("n_res", [1, 3, 4, 17, 33, 255])
 @pytest.mark.parametrize("dt", ["float16", "bfloat16", "float32"])
 def test_mma_attend_tail_kernel_edges(n_res, dt):

@@ -134,14 +134,17 @@ def _emulated_gathers(world, B, H_kv, hpk, dtype):
     return plans, structs, outs, flags, states
 
 
-@pytest.mark.parametrize("world,B,H_kv,H_q,dtype", [(2, 2, 2, 8, torch.float16), (4, 3, 2, 16, torch.bfloat16),
-                                                     (3, 1, 4, 8, torch.float32)])
-def test_peer_exchange_emulated_ranks_gather_the_unsharded_output(world, B, H_kv, H_q, dtype):
+@pytest.mark.parametrize("world,B,H_kv,H_q,dtype,S", [
+    (2, 2, 2, 8, torch.float16, 1500), (4, 3, 2, 16, torch.bfloat16, 1500), (3, 1, 4, 8, torch.float32, 1500),
+    # long and large enough that every rank's launch takes the eight-head kernel, whose CTAs arrive
+    # with the weight of the four-head chunks they stand for (5 heads per kv head: weight 2)
+    (2, 6, 8, 40, torch.float16, 16384 + 200)])
+def test_peer_exchange_emulated_ranks_gather_the_unsharded_output(world, B, H_kv, H_q, dtype, S):
     from veloxquant_mlx_b200 import _lib
     from veloxquant_mlx_b200 import kernels as vk
     from veloxquant_mlx_b200.sharding import shard_kv, shard_queries, unshard_output
 
-    S, hpk = 1500, H_q // H_kv
+    hpk = H_q // H_kv
     act = torch.float16 if dtype == torch.float32 else dtype
     full, k, v = _filled(5, B, H_kv, S, dtype=act)
     units = B * H_kv
@@ -172,7 +175,7 @@ def test_peer_exchange_emulated_ranks_gather_the_unsharded_output(world, B, H_kv
             assert bool((err <= 2e-3 + 1e-2 * want.float().abs()).all()), f"rank {r} round {rnd}: {err.max().item():.3e}"
             assert torch.equal(outs[r], outs[0])
         assert [int(s[2]) for s in states] == [rnd + 1] * world
-        # every rank's word r holds (rounds so far) x (rank r's CTAs that write rows)
+        # every rank's word r holds (rounds so far) x (rank r's four-head chunks that write rows)
         assert all(int(f[r]) == (rnd + 1) * plans[r].owned * -(-hpk // 4) for f in flags for r in range(world))
 
 

@@ -246,8 +246,6 @@ coded_attend_kernel(const CodedParams p, int key_floats, int vlut_floats) {
     for (int h = 0; h < NH; ++h) { m_run[h] = -INFINITY; l_run[h] = 0.f; }
 #pragma unroll
     for (int mt = 0; mt < 8; ++mt) acc[mt][0] = acc[mt][1] = acc[mt][2] = acc[mt][3] = 0.f;
-    // this lane's rows of the transposing loads: matrix lane / 8 = (keys 0-7 | 8-15) x (channel chunk even | odd)
-    const uint32_t lm_tok = (uint32_t)(8 * (lane >> 4) + (lane & 7)), lm_chunk = (uint32_t)((lane >> 3) & 1);
 
     for (int tile = t_begin + 32 * warp; tile < t_end; tile += 32 * kWarpsC) {
         const int t = tile + lane;

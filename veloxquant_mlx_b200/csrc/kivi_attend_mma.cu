@@ -221,6 +221,7 @@ struct Params {
     int wait_test;      // self-test: every warp also waits (briefly) on a barrier that nothing arms
     vq_peer_gather gather;  // world == 0: the output rows are not published to peers
     vq_kivi_sinks sinks;    // count == nullptr: no protected tokens
+    int wide;               // eight query heads per CTA (kivi_attend_mma8_kernel) instead of four
 };
 
 // ---- helpers for the unquantized tail ----------------------------------------------------------
@@ -257,6 +258,93 @@ __device__ __forceinline__ void store_out4(void *base, int32_t dt, int64_t elem,
         }
         *reinterpret_cast<uint2 *>(reinterpret_cast<uint16_t *>(base) + elem) = raw;
     }
+}
+
+// The end of a CTA's work, after its partial record is written: take a ticket for the (batch, kv
+// head, head chunk); the CTA that takes the last one merges the unit's partials, writes the
+// output rows and, in a sharded run, publishes them. CH = query heads per CTA.
+template <int CH>
+__device__ __forceinline__ void ticket_merge_publish(const Params &p, uint64_t *bars, int64_t bh, int b, int hkv, int h0,
+                                                     int hpk, int n_heads, int tid, int lane, int warp) {
+    const vq_kivi_attend_args &a = p.a;
+    // ---- ticket: the CTA that arrives last for this (batch, kv head, head chunk) merges ----------
+    // The ticket word is (epoch << 16) | arrivals. Whatever the workspace held before this call
+    // (another call's partials, a fresh allocation's old contents) has other upper 48 bits and
+    // counts as zero arrivals: the epoch is a per-call 48-bit hash, so stray data matches it with
+    // probability 2^-48. The merging CTA leaves 0 behind (epoch 0 is never issued), so in a steady
+    // decode loop every ticket is found at 0, and a captured launch can be replayed with its epoch.
+    int *sh_last = reinterpret_cast<int *>(bars) + 48;  // (behind the barriers, inside their 256 bytes)
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) {
+        unsigned long long *t = p.tickets + bh * p.n_chunks + (h0 / CH);
+        unsigned long long cur = *reinterpret_cast<volatile unsigned long long *>(t), want;
+        for (;;) {
+            want = ((cur >> 16) == p.epoch) ? cur + 1ull : ((p.epoch << 16) | 1ull);
+            const unsigned long long seen = atomicCAS(t, cur, want);
+            if (seen == cur) break;
+            cur = seen;  // (another CTA of this unit got in between: at most n_splits - 1 retries)
+        }
+        *sh_last = ((uint32_t)(want & 0xffffull) == (uint32_t)p.n_splits);
+    }
+    __syncthreads();
+    if (!*sh_last) return;
+    __threadfence();
+    // Warp w merges query heads h0 + w, h0 + w + 4, ...: lane holds channels 4*lane .. 4*lane+3; the (max, sum) pair
+    // of a part is one broadcast load. Loads bypass L1 (the partials were written by other SMs).
+    for (int hw = warp; hw < n_heads; hw += kWarps) {
+        const int64_t rec0 = bh * p.n_splits * hpk + h0 + hw;  // record of part s: rec0 + s * hpk
+        float m = -INFINITY, l = 0.f, acc[4] = {0.f, 0.f, 0.f, 0.f};
+        constexpr int kBatch = 8;
+        for (int s0 = 0; s0 < p.n_splits; s0 += kBatch) {
+            float2 ml[kBatch];
+            float4 po[kBatch];
+#pragma unroll
+            for (int j = 0; j < kBatch; ++j) {
+                const int s = min(s0 + j, p.n_splits - 1);
+                const int64_t rec = rec0 + (int64_t)s * hpk;
+                ml[j] = __ldcg(reinterpret_cast<const float2 *>(p.part_ml + rec * 2));
+                po[j] = __ldcg(reinterpret_cast<const float4 *>(p.part_o + rec * kD + 4 * lane));
+            }
+#pragma unroll
+            for (int j = 0; j < kBatch; ++j) {
+                if (s0 + j < p.n_splits && ml[j].x != -INFINITY) {
+                    const float mn = fmaxf(m, ml[j].x);
+                    const float f = exp2f(m - mn), wgt = exp2f(ml[j].x - mn);
+                    l = l * f + ml[j].y * wgt;
+                    acc[0] = acc[0] * f + po[j].x * wgt; acc[1] = acc[1] * f + po[j].y * wgt;
+                    acc[2] = acc[2] * f + po[j].z * wgt; acc[3] = acc[3] * f + po[j].w * wgt;
+                    m = mn;
+                }
+            }
+        }
+        const float inv = 1.f / l;
+        const float res[4] = {acc[0] * inv, acc[1] * inv, acc[2] * inv, acc[3] * inv};
+        const int64_t row = (int64_t)b * a.H_q + hkv * hpk + h0 + hw;
+        store_out4(a.out, a.out_dtype, row * kD + 4 * lane, res);
+        if (p.gather.world > 0) {
+            // publish the row to every rank's gathered tensor (plain stores to peer-mapped memory)
+            const int64_t grow = p.gather.row_offset + row;
+            for (int pr = 0; pr < p.gather.world; ++pr) store_out4(p.gather.out[pr], a.out_dtype, grow * kD + 4 * lane, res);
+        }
+    }
+    if (p.gather.world > 0) {
+        // Arrival: once the CTA's rows are stored, thread r fences system-wide (the barrier puts
+        // every thread's stores before that fence) and adds 1 to this rank's word on rank r. One
+        // fence latency per layer; the waiting side knows how many four-head chunks each rank sends per round.
+        // (Counting the CTAs locally first and raising a flag from the last one cost a second fence;
+        // a release store per rank cost one fence each: 22 us per layer at 8 ranks.)
+        const vq_peer_gather &pg = p.gather;
+        __syncthreads();
+        if (tid < pg.world) {
+            __threadfence_system();
+            // (a CTA of the eight-head kernel counts as the four-head CTAs it stands for, so the count a
+            // waiting rank expects does not depend on which kernel the sender's launch picked)
+            asm volatile("red.relaxed.sys.global.add.u32 [%0], %1;" ::"l"(pg.flags[tid] + pg.rank),
+                         "r"((uint32_t)(n_heads + kChunkHeads - 1) / kChunkHeads) : "memory");
+        }
+    }
+    if (tid == 0) p.tickets[bh * p.n_chunks + (h0 / CH)] = 0ull;
 }
 
 // ---- main kernel ----------------------------------------------------------------------------
@@ -725,81 +813,416 @@ kivi_attend_mma_kernel(const __grid_constant__ Params p) {
         if (d == 0) { p.part_ml[rec * 2] = gm; p.part_ml[rec * 2 + 1] = gl; }
     }
 
-    // ---- ticket: the CTA that arrives last for this (batch, kv head, head chunk) merges ----------
-    // The ticket word is (epoch << 16) | arrivals. Whatever the workspace held before this call
-    // (another call's partials, a fresh allocation's old contents) has other upper 48 bits and
-    // counts as zero arrivals: the epoch is a per-call 48-bit hash, so stray data matches it with
-    // probability 2^-48. The merging CTA leaves 0 behind (epoch 0 is never issued), so in a steady
-    // decode loop every ticket is found at 0, and a captured launch can be replayed with its epoch.
-    int *sh_last = reinterpret_cast<int *>(bars) + 48;  // (behind the barriers, inside their 256 bytes)
-    __threadfence();
-    __syncthreads();
+    ticket_merge_publish<kChunkHeads>(p, bars, bh, b, hkv, h0, hpk, n_heads, tid, lane, warp);
+}
+
+// ---- the same kernel for 5..8 query heads per kv head --------------------------------------------
+// With four heads a CTA spends the eight MMA columns on (high, low) halves of each head's B
+// operand; a kv head with more query heads then needs two CTAs, i.e. the unpack of every code
+// twice. Here the eight columns are eight heads, and every A fragment (unpacked once) feeds two
+// MMAs into the same accumulators: one with the high halves of the B operand, one with the low
+// halves (hi + lo contributions simply add). Per 32-token group that is the unpack once, 64 MMAs
+// instead of 2 x 32, and the per-head B-operand and softmax work of eight heads instead of
+// 2 x 4: about half the instructions of two four-head CTAs. It costs registers (the B operands of
+// eight heads in both halves): three CTAs per SM instead of four.
+// Lane roles (g = lane / 4, c = lane % 4): as a B-operand column, head g for the 32 channels of
+// chunk c; as an accumulator column pair (cols 2c, 2c+1), heads 2c and 2c+1 for its rows.
+constexpr int kWideHeads = 8;
+
+template <int BITS>
+__global__ void __launch_bounds__(kWarps * 32, 3)
+kivi_attend_mma8_kernel(const __grid_constant__ Params p) {
+    using C = Cfg<BITS>;
+    constexpr int STAGES = 2;
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    const vq_kivi_attend_args &a = p.a;
+    const int b = blockIdx.z, hkv = blockIdx.y;
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    const int split = blockIdx.x / p.n_chunks;
+    const int h0 = (blockIdx.x % p.n_chunks) * kWideHeads;
+    const int tid = threadIdx.x, lane = tid & 31;
+    const int warp = __shfl_sync(0xffffffffu, tid >> 5, 0);
+    const int g = lane >> 2, c = lane & 3;
+    const int hpk = p.hpk;
+    const int64_t bh = (int64_t)b * a.H_kv + hkv;
+
+    uint8_t *stages = smem_raw;
+    constexpr int kStageArea = kWarps * STAGES * C::STAGE_BYTES;
+    constexpr int kRedArea = (2 * kWarps * kWideHeads * (kD + 4 + 2)) * 4;
+    constexpr int kArea = kStageArea > kRedArea ? kStageArea : kRedArea;
+    uint64_t *bars = reinterpret_cast<uint64_t *>(smem_raw + kArea);
+    const uint32_t bar0 = smem_u32(bars);
+    if (smem_u32(stages) & 1023u) {
+        if (tid == 0) atomicExch(&g_attend_timeout, 2);
+        return;
+    }
+    const int grp_begin = min(p.groups_total, (split * kWarps + warp) * p.groups_per_warp);
+    const int grp_end = min(p.groups_total, grp_begin + p.groups_per_warp);
+    const int n_local = grp_end - grp_begin;
+    const uint32_t wbar0 = bar0 + 8u * (warp * STAGES);
+    uint8_t *wstages = stages + (size_t)warp * STAGES * C::STAGE_BYTES;
+
+    constexpr uint32_t code_bytes = kGroup * C::RB;
+    const uint8_t *kc_w = a.k_codes + bh * a.k_codes_stride_bh + (int64_t)grp_begin * code_bytes;
+    const float *vs_w = a.v_scale + bh * a.v_param_stride_bh + (int64_t)grp_begin * (kGroup * 4);
+    const float *vz_w = a.v_zero + bh * a.v_param_stride_bh + (int64_t)grp_begin * (kGroup * 4);
+    auto issue_group = [&](auto stage_c, int local_idx) {  // lane 0 only; stage_c = local_idx % STAGES
+        constexpr int stage = decltype(stage_c)::value;
+        const int grp = grp_begin + local_idx;
+        const uint32_t bar = wbar0 + 8u * stage;
+        const uint32_t dst = smem_u32(wstages + (size_t)stage * C::STAGE_BYTES);
+        mbar_expect_tx(bar, 2 * code_bytes + 4 * 512);
+        bulk_g2s(dst + C::KC_OFF, kc_w + (uint32_t)local_idx * code_bytes, code_bytes, bar);
+        tensor_g2s(dst + C::VC_OFF, &p.v_map, 0, grp * C::VROWS, (int)bh, bar);
+        tensor_g2s(dst + C::KS_OFF, &p.ks_map, 0, grp * 4, (int)bh, bar);
+        tensor_g2s(dst + C::KZ_OFF, &p.kz_map, 0, grp * 4, (int)bh, bar);
+        bulk_g2s(dst + C::VS_OFF, vs_w + (uint32_t)local_idx * (kGroup * 4), 512, bar);
+        bulk_g2s(dst + C::VZ_OFF, vz_w + (uint32_t)local_idx * (kGroup * 4), 512, bar);
+    };
     if (tid == 0) {
-        unsigned long long *t = p.tickets + bh * p.n_chunks + (h0 / kChunkHeads);
-        unsigned long long cur = *reinterpret_cast<volatile unsigned long long *>(t), want;
-        for (;;) {
-            want = ((cur >> 16) == p.epoch) ? cur + 1ull : ((p.epoch << 16) | 1ull);
-            const unsigned long long seen = atomicCAS(t, cur, want);
-            if (seen == cur) break;
-            cur = seen;  // (another CTA of this unit got in between: at most n_splits - 1 retries)
-        }
-        *sh_last = ((uint32_t)(want & 0xffffull) == (uint32_t)p.n_splits);
+        for (int s = 0; s < kWarps * STAGES + 1; ++s) mbar_init(bar0 + 8u * s, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
-    if (!*sh_last) return;
-    __threadfence();
-    // Warp w merges query head h0 + w: lane holds channels 4*lane .. 4*lane+3; the (max, sum) pair
-    // of a part is one broadcast load. Loads bypass L1 (the partials were written by other SMs).
-    if (warp < n_heads) {
-        const int64_t rec0 = bh * p.n_splits * hpk + h0 + warp;  // record of part s: rec0 + s * hpk
-        float m = -INFINITY, l = 0.f, acc[4] = {0.f, 0.f, 0.f, 0.f};
-        constexpr int kBatch = 8;
-        for (int s0 = 0; s0 < p.n_splits; s0 += kBatch) {
-            float2 ml[kBatch];
-            float4 po[kBatch];
+    if (lane == 0 && n_local > 0) issue_group(std::integral_constant<int, 0>{}, 0);
+    if (lane < 4 && split * kWarps + warp < a.n_res) {
+        const size_t es = a.res_dtype == VQ_F32 ? 4 : 2;
+        const uint8_t *base = static_cast<const uint8_t *>((lane & 2) ? a.v_res : a.k_res) +
+                              ((size_t)bh * a.res_stride_bh + (size_t)(split * kWarps + warp) * kD) * es;
+        asm volatile("prefetch.global.L2 [%0];" ::"l"(base + (lane & 1) * (kD * es / 2)));
+    }
+
+    // B-operand register r = w * NH + i of this lane (word w of its 32-channel chunk, unpacked
+    // register i) pairs the chunk's channels CPW*w + i and CPW*w + CPW/2 + i (the i-th code of the
+    // word's low and of its high 16 bits); both are pre-divided by the register's code weight.
+    constexpr int NR = C::KW * C::NH;  // 16
+    float qa[NR], qb[NR];
+    {
+        const bool live = h0 + g < hpk;
+        const int64_t qbase = ((int64_t)b * a.H_q + hkv * hpk + h0 + g) * kD + 32 * c;
 #pragma unroll
-            for (int j = 0; j < kBatch; ++j) {
-                const int s = min(s0 + j, p.n_splits - 1);
-                const int64_t rec = rec0 + (int64_t)s * hpk;
-                ml[j] = __ldcg(reinterpret_cast<const float2 *>(p.part_ml + rec * 2));
-                po[j] = __ldcg(reinterpret_cast<const float4 *>(p.part_o + rec * kD + 4 * lane));
+        for (int r = 0; r < NR; ++r) {
+            const int w = r / C::NH, i = r % C::NH;
+            const float inv = 1.f / code_weight<BITS>(i);
+            qa[r] = live ? load_as_f32(a.q, a.q_dtype, qbase + C::CPW * w + i) * inv : 0.f;
+            qb[r] = live ? load_as_f32(a.q, a.q_dtype, qbase + C::CPW * w + C::CPW / 2 + i) * inv : 0.f;
+        }
+    }
+    const uint32_t v_sel = (g & 1) ? 0x7351u : 0x6240u;
+    const int v_src = ((g >> 1) << 2) | c;
+    const uint32_t v_lin = (uint32_t)((8 * ((lane >> 3) & 1) + (lane & 7)) * C::RB + 16 * (lane >> 4));
+    const uint32_t v_off0 = swz128(v_lin);
+    const uint32_t v_off1 = (BITS == 4) ? v_off0 + 16 * C::RB : swz128(v_lin + 16 * C::RB);
+    float o[8][4];  // [MMA][row g: heads 2c, 2c+1 | row g+8: heads 2c, 2c+1]
+#pragma unroll
+    for (int i = 0; i < 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+    float oz[4][2];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) oz[j][0] = oz[j][1] = 0.f;
+    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+    const float sc = a.scale * 1.4426950408889634f;
+    bool timed_out = false;
+
+    auto body = [&](auto stage_c, const int it) {
+        constexpr int stage = decltype(stage_c)::value;
+        __syncwarp();
+        if (lane == 0 && it + 1 < n_local) {
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            issue_group(std::integral_constant<int, (stage + 1) % STAGES>{}, it + 1);
+        }
+        if (!timed_out && !mbar_wait(wbar0 + 8u * stage, (uint32_t)((it / STAGES) & 1))) timed_out = true;
+        const uint8_t *st = wstages + (size_t)stage * C::STAGE_BYTES;
+
+        // ---- B operand of QK^T: q * k_scale of head g over chunk c, as high and low halves ----
+        uint32_t qh[NR], ql[NR];
+        float ck0, ck1;
+        {
+            // (the tiles arrive 128-byte swizzled: 16-byte block j of line c sits at j ^ c)
+            float ks[32], kz[32];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const float4 s4 = *reinterpret_cast<const float4 *>(st + C::KS_OFF + 128 * c + 16 * (j ^ c));
+                const float4 z4 = *reinterpret_cast<const float4 *>(st + C::KZ_OFF + 128 * c + 16 * (j ^ c));
+                ks[4 * j] = s4.x; ks[4 * j + 1] = s4.y; ks[4 * j + 2] = s4.z; ks[4 * j + 3] = s4.w;
+                kz[4 * j] = z4.x; kz[4 * j + 1] = z4.y; kz[4 * j + 2] = z4.z; kz[4 * j + 3] = z4.w;
+            }
+            float cp[4] = {0.f, 0.f, 0.f, 0.f};  // per code weight: sum q / weight * k_zero
+#pragma unroll
+            for (int r = 0; r < NR; ++r) {
+                const int w = r / C::NH, i = r % C::NH;
+                const int fa = C::CPW * w + i, fb = fa + C::CPW / 2;
+                const float xa = qa[r] * ks[fa], xb = qb[r] * ks[fb];
+                cp[i & 3] = fmaf(qa[r], kz[fa], fmaf(qb[r], kz[fb], cp[i & 3]));
+                split_h2(xa, xb, qh[r], ql[r]);
+            }
+            float cpart = cp[0] * code_weight<BITS>(0) + cp[1] * code_weight<BITS>(1) +
+                          cp[2] * code_weight<BITS>(2) + cp[3] * code_weight<BITS>(3);
+            cpart += __shfl_xor_sync(0xffffffffu, cpart, 1);
+            cpart += __shfl_xor_sync(0xffffffffu, cpart, 2);
+            // this lane's accumulator columns are heads 2c and 2c+1: their zero-point terms sit in quads 2c, 2c+1
+            ck0 = __shfl_sync(0xffffffffu, cpart, 8 * c);
+            ck1 = __shfl_sync(0xffffffffu, cpart, 8 * c + 4);
+        }
+
+        // ---- S = codes . (q*k_scale): every unpacked fragment feeds a high-half and a low-half MMA ----
+        float s_acc[2][4];
+#pragma unroll
+        for (int mt = 0; mt < 2; ++mt) {
+            s_acc[mt][0] = s_acc[mt][1] = s_acc[mt][2] = s_acc[mt][3] = 0.f;
+            uint32_t kw[2][C::KW];
+#pragma unroll
+            for (int r = 0; r < 2; ++r) {
+                const int tok = 16 * mt + g + 8 * r;
+                const uint8_t *src = st + C::KC_OFF + tok * C::RB + c * (C::KW * 4);
+                if constexpr (C::KW == 4) {
+                    const uint4 v = *reinterpret_cast<const uint4 *>(src);
+                    kw[r][0] = v.x; kw[r][1] = v.y; kw[r][2] = v.z; kw[r][3] = v.w;
+                } else {
+                    const uint2 v = *reinterpret_cast<const uint2 *>(src);
+                    kw[r][0] = v.x; kw[r][1] = v.y;
+                }
             }
 #pragma unroll
-            for (int j = 0; j < kBatch; ++j) {
-                if (s0 + j < p.n_splits && ml[j].x != -INFINITY) {
-                    const float mn = fmaxf(m, ml[j].x);
-                    const float f = exp2f(m - mn), wgt = exp2f(ml[j].x - mn);
-                    l = l * f + ml[j].y * wgt;
-                    acc[0] = acc[0] * f + po[j].x * wgt; acc[1] = acc[1] * f + po[j].y * wgt;
-                    acc[2] = acc[2] * f + po[j].z * wgt; acc[3] = acc[3] * f + po[j].w * wgt;
-                    m = mn;
+            for (int w = 0; w < C::KW; ++w) {
+                uint32_t x0[C::NH], x1[C::NH];
+                unpack_word<BITS>(kw[0][w], x0);
+                unpack_word<BITS>(kw[1][w], x1);
+#pragma unroll
+                for (int jj = 0; jj < C::NH / 2; ++jj) {
+                    mma_f16(s_acc[mt], x0[2 * jj], x1[2 * jj], x0[2 * jj + 1], x1[2 * jj + 1],
+                            qh[w * C::NH + 2 * jj], qh[w * C::NH + 2 * jj + 1]);
+                    mma_f16(s_acc[mt], x0[2 * jj], x1[2 * jj], x0[2 * jj + 1], x1[2 * jj + 1],
+                            ql[w * C::NH + 2 * jj], ql[w * C::NH + 2 * jj + 1]);
                 }
             }
         }
-        const float inv = 1.f / l;
-        const float res[4] = {acc[0] * inv, acc[1] * inv, acc[2] * inv, acc[3] * inv};
-        const int64_t row = (int64_t)b * a.H_q + hkv * hpk + h0 + warp;
-        store_out4(a.out, a.out_dtype, row * kD + 4 * lane, res);
-        if (p.gather.world > 0) {
-            // publish the row to every rank's gathered tensor (plain stores to peer-mapped memory)
-            const int64_t grow = p.gather.row_offset + row;
-            for (int pr = 0; pr < p.gather.world; ++pr) store_out4(p.gather.out[pr], a.out_dtype, grow * kD + 4 * lane, res);
+
+        // ---- online softmax of heads 2c, 2c+1 over this lane's four tokens and the 8 lanes g ----
+        float pr[2][2][2];  // [m-tile][token g / g + 8][head 2c / 2c + 1]
+        {
+            const float k0 = ck0 * sc, k1 = ck1 * sc, f = sc * kTwo24;
+#pragma unroll
+            for (int mt = 0; mt < 2; ++mt) {
+                pr[mt][0][0] = fmaf(s_acc[mt][0], f, k0); pr[mt][0][1] = fmaf(s_acc[mt][1], f, k1);
+                pr[mt][1][0] = fmaf(s_acc[mt][2], f, k0); pr[mt][1][1] = fmaf(s_acc[mt][3], f, k1);
+            }
+            float corr[2];
+#pragma unroll
+            for (int hh = 0; hh < 2; ++hh) {
+                float v = fmaxf(fmaxf(pr[0][0][hh], pr[0][1][hh]), fmaxf(pr[1][0][hh], pr[1][1][hh]));
+                v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 4));
+                v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 8));
+                v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 16));
+                const float mn = fmaxf(m_run[hh], v);
+                corr[hh] = fast_exp2(m_run[hh] - mn);
+                m_run[hh] = mn;
+#pragma unroll
+                for (int mt = 0; mt < 2; ++mt) {
+                    pr[mt][0][hh] = fast_exp2(pr[mt][0][hh] - mn);
+                    pr[mt][1][hh] = fast_exp2(pr[mt][1][hh] - mn);
+                }
+                l_run[hh] = l_run[hh] * corr[hh] + ((pr[0][0][hh] + pr[0][1][hh]) + (pr[1][0][hh] + pr[1][1][hh]));
+            }
+            if (__any_sync(0xffffffffu, corr[0] != 1.f || corr[1] != 1.f)) {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    o[i][0] *= corr[0]; o[i][1] *= corr[1]; o[i][2] *= corr[0]; o[i][3] *= corr[1];
+                }
+#pragma unroll
+                for (int j = 0; j < 4; ++j) { oz[j][0] *= corr[0]; oz[j][1] *= corr[1]; }
+            }
+        }
+
+        // ---- O^T += codes^T . (P*v_scale) (high and low halves), zero-point term in float32 ----
+#pragma unroll
+        for (int mt = 0; mt < 2; ++mt) {
+            const int t0 = 16 * mt;
+            const uint32_t v_off = mt ? v_off1 : v_off0;
+            uint32_t pbh[4][2], pbl[4][2];  // [channel group][tokens 0-7 / 8-15 of the m-tile]
+            {
+                const float4 sa = *reinterpret_cast<const float4 *>(st + C::VS_OFF + (t0 + g) * 16);
+                const float4 sbv = *reinterpret_cast<const float4 *>(st + C::VS_OFF + (t0 + g + 8) * 16);
+                const float4 za = *reinterpret_cast<const float4 *>(st + C::VZ_OFF + (t0 + g) * 16);
+                const float4 zb = *reinterpret_cast<const float4 *>(st + C::VZ_OFF + (t0 + g + 8) * 16);
+                const float sa4[4] = {sa.x, sa.y, sa.z, sa.w}, sb4[4] = {sbv.x, sbv.y, sbv.z, sbv.w};
+                const float za4[4] = {za.x, za.y, za.z, za.w}, zb4[4] = {zb.x, zb.y, zb.z, zb.w};
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+#pragma unroll
+                    for (int hh = 0; hh < 2; ++hh)
+                        oz[j][hh] = fmaf(pr[mt][0][hh], za4[j], fmaf(pr[mt][1][hh], zb4[j], oz[j][hh]));
+                    // element pair (row = token, columns 2c, 2c+1 = heads 2c, 2c+1); the 8x8 transpose makes it
+                    // the B operand (tokens on K, heads on N). High halves are truncations (one AND each).
+#pragma unroll
+                    for (int r = 0; r < 2; ++r) {
+                        const float x0 = pr[mt][r][0] * (r ? sb4[j] : sa4[j]), x1 = pr[mt][r][1] * (r ? sb4[j] : sa4[j]);
+                        const float h0f = __uint_as_float(__float_as_uint(x0) & 0xffffe000u);
+                        const float h1f = __uint_as_float(__float_as_uint(x1) & 0xffffe000u);
+                        pbh[j][r] = movmatrix_trans(pack_h2(h0f, h1f));
+                        pbl[j][r] = movmatrix_trans(pack_h2(x0 - h0f, x1 - h1f));
+                    }
+                }
+            }
+#pragma unroll
+            for (int sb = 0; sb < C::NSEG; sb += 2) {
+                uint32_t R[4];
+                ldmatrix_x4_trans(R, smem_u32(st + C::VC_OFF) + (v_off ^ (16 * sb)));
+                if constexpr (BITS == 2) {
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const uint32_t lo = __shfl_sync(0xffffffffu, R[i], v_src);
+                        const uint32_t hi = __shfl_sync(0xffffffffu, R[i], v_src + 16);
+                        R[i] = __byte_perm(lo, hi, v_sel);
+                    }
+                }
+#pragma unroll
+                for (int si = 0; si < 2; ++si) {
+                    const int seg = sb + si;
+                    uint32_t e0[C::CU], e1[C::CU];
+                    unpack_word<BITS>(R[2 * si + 0], e0);
+                    unpack_word<BITS>(R[2 * si + 1], e1);
+#pragma unroll
+                    for (int u = 0; u < C::CU / 2; ++u) {
+                        const int gd = (BITS == 4) ? seg : 2 * seg + (u >> 1);
+                        mma_f16(o[seg * (C::CU / 2) + u], e0[2 * u], e0[2 * u + 1], e1[2 * u], e1[2 * u + 1], pbh[gd][0], pbh[gd][1]);
+                        mma_f16(o[seg * (C::CU / 2) + u], e0[2 * u], e0[2 * u + 1], e1[2 * u], e1[2 * u + 1], pbl[gd][0], pbl[gd][1]);
+                    }
+                }
+            }
+        }
+    };
+    {
+        int it = 0;
+        for (; it + STAGES <= n_local; it += STAGES) {
+            body(std::integral_constant<int, 0>{}, it);
+            body(std::integral_constant<int, 1>{}, it + 1);
+        }
+        if (it < n_local) body(std::integral_constant<int, 0>{}, it);
+    }
+    if (p.wait_test && !mbar_wait(bar0 + 8u * (kWarps * STAGES), 0u, kSelfTestSpinLimit)) timed_out = true;
+    if (timed_out) {
+        if (lane == 0) atomicExch(&g_attend_timeout, 1);
+        if (!p.wait_test)
+            for (int i = 0; i < 64; ++i) __nanosleep(1000);
+    }
+
+    // ---- this warp's packed part into its slot of the reduction area (frees the accumulators) ----
+#pragma unroll
+    for (int hh = 0; hh < 2; ++hh) {
+        l_run[hh] += __shfl_xor_sync(0xffffffffu, l_run[hh], 4);
+        l_run[hh] += __shfl_xor_sync(0xffffffffu, l_run[hh], 8);
+        l_run[hh] += __shfl_xor_sync(0xffffffffu, l_run[hh], 16);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            float z = oz[j][hh];
+            z += __shfl_xor_sync(0xffffffffu, z, 4);
+            z += __shfl_xor_sync(0xffffffffu, z, 8);
+            z += __shfl_xor_sync(0xffffffffu, z, 16);
+            oz[j][hh] = z;
         }
     }
-    if (p.gather.world > 0) {
-        // Arrival: once the CTA's rows are stored, thread r fences system-wide (the barrier puts
-        // every thread's stores before that fence) and adds 1 to this rank's word on rank r. One
-        // fence latency per layer; the waiting side knows how many CTAs each rank sends per round.
-        // (Counting the CTAs locally first and raising a flag from the last one cost a second fence;
-        // a release store per rank cost one fence each: 22 us per layer at 8 ranks.)
-        const vq_peer_gather &pg = p.gather;
-        __syncthreads();
-        if (tid < pg.world) {
-            __threadfence_system();
-            asm volatile("red.relaxed.sys.global.add.u32 [%0], 1;" ::"l"(pg.flags[tid] + pg.rank) : "memory");
+    __syncthreads();  // all stages are drained: reuse them for the reduction
+    constexpr int kSlots = 2 * kWarps;
+    float *red_o = reinterpret_cast<float *>(stages);              // [8 slots][8 heads][128]
+    float *red_z = red_o + kSlots * kWideHeads * kD;               // [8][8][4 groups]
+    float *red_m = red_z + kSlots * kWideHeads * 4;                // [8][8]
+    float *red_l = red_m + kSlots * kWideHeads;                    // [8][8]
+    auto chan = [&](int i) {
+        const int seg = i / (C::CU / 2), u = i % (C::CU / 2);
+        if constexpr (BITS == 4) return 32 * seg + 4 * g + 2 * u;
+        else return 64 * seg + 32 * (u >> 1) + 4 * g + 2 * (u & 1);
+    };
+    {
+        float *base0 = red_o + (warp * kWideHeads + 2 * c) * kD, *base1 = base0 + kD;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const int u = i % (C::CU / 2);
+            const float f0 = kTwo24 / code_weight<BITS>(2 * u), f1 = kTwo24 / code_weight<BITS>(2 * u + 1);
+            const int d0 = chan(i);
+            base0[d0] = o[i][0] * f0; base1[d0] = o[i][1] * f0;
+            base0[d0 + 1] = o[i][2] * f1; base1[d0 + 1] = o[i][3] * f1;
+        }
+        if (g == 0) {
+#pragma unroll
+            for (int hh = 0; hh < 2; ++hh) {
+                const int slot = warp * kWideHeads + 2 * c + hh;
+                red_m[slot] = m_run[hh];
+                red_l[slot] = l_run[hh];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) red_z[slot * 4 + j] = oz[j][hh];
+            }
         }
     }
-    if (tid == 0) p.tickets[bh * p.n_chunks + (h0 / kChunkHeads)] = 0ull;
+
+    // (see the four-head kernel: everything above touched only q and the packed store)
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+
+    // ---- the unquantized tail, two passes of four heads (the registers of one pass are reused) ----
+    const int n_heads = min(kWideHeads, hpk - h0);
+#pragma unroll 1
+    for (int hq = 0; hq < kWideHeads; hq += 4) {
+        float tm[4], tl[4], to[4][4];
+#pragma unroll
+        for (int hp = 0; hp < 4; ++hp) {
+            tm[hp] = -INFINITY;
+            tl[hp] = 0.f;
+            to[hp][0] = to[hp][1] = to[hp][2] = to[hp][3] = 0.f;
+        }
+        int r = split * kWarps + warp;
+        if (r < a.n_res && hq < n_heads) {
+            const int r_stride = p.n_splits * kWarps;
+            float qt[4][4];
+#pragma unroll
+            for (int hp = 0; hp < 4; ++hp) {
+                const bool live = h0 + hq + hp < hpk;
+                const int64_t qb = ((int64_t)b * a.H_q + hkv * hpk + h0 + hq + hp) * kD + 4 * lane;
+#pragma unroll
+                for (int i = 0; i < 4; ++i) qt[hp][i] = live ? load_as_f32(a.q, a.q_dtype, qb + i) * sc : 0.f;
+            }
+            const int64_t rbase = bh * a.res_stride_bh + 4 * lane;
+            for (; r < a.n_res; r += r_stride) {
+                float kd[4], vd[4];
+                load_res4(a.k_res, a.res_dtype, rbase + (int64_t)r * kD, kd);
+                load_res4(a.v_res, a.res_dtype, rbase + (int64_t)r * kD, vd);
+#pragma unroll
+                for (int hp = 0; hp < 4; ++hp) {
+                    const float sv = warp_sum(qt[hp][0] * kd[0] + qt[hp][1] * kd[1] + qt[hp][2] * kd[2] + qt[hp][3] * kd[3]);
+                    const float mn = fmaxf(tm[hp], sv);
+                    const float f = fast_exp2(tm[hp] - mn), wgt = fast_exp2(sv - mn);
+                    tl[hp] = tl[hp] * f + wgt;
+                    tm[hp] = mn;
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) to[hp][i] = to[hp][i] * f + wgt * vd[i];
+                }
+            }
+        }
+#pragma unroll
+        for (int hp = 0; hp < 4; ++hp) {
+            const int slot = (kWarps + warp) * kWideHeads + hq + hp;
+            *reinterpret_cast<float4 *>(red_o + slot * kD + 4 * lane) = make_float4(to[hp][0], to[hp][1], to[hp][2], to[hp][3]);
+            if (lane == 0) { red_m[slot] = tm[hp]; red_l[slot] = tl[hp]; }
+            if (lane < 4) red_z[slot * 4 + lane] = 0.f;
+        }
+    }
+    __syncthreads();
+    for (int i = tid; i < n_heads * kD; i += blockDim.x) {
+        const int hp = i / kD, d = i % kD;
+        float gm = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < kSlots; ++w) gm = fmaxf(gm, red_m[w * kWideHeads + hp]);
+        float gl = 0.f, acc = 0.f;
+#pragma unroll
+        for (int w = 0; w < kSlots; ++w) {
+            const float mw = red_m[w * kWideHeads + hp];
+            const float f = (mw == -INFINITY) ? 0.f : exp2f(mw - gm);
+            gl += red_l[w * kWideHeads + hp] * f;
+            acc += (red_o[(w * kWideHeads + hp) * kD + d] + red_z[(w * kWideHeads + hp) * 4 + (d >> 5)]) * f;
+        }
+        const int64_t rec = (bh * p.n_splits + split) * hpk + h0 + hp;
+        p.part_o[rec * kD + d] = acc;
+        if (d == 0) { p.part_ml[rec * 2] = gm; p.part_ml[rec * 2 + 1] = gl; }
+    }
+    ticket_merge_publish<kWideHeads>(p, bars, bh, b, hkv, h0, hpk, n_heads, tid, lane, warp);
 }
 
 constexpr int kMaxSplits = 512;  // (a ticket counts arrivals in 16 bits)
@@ -822,12 +1245,28 @@ int smem_for(int bits, int stages) {
 //     launch need not fill the GPU by itself and longer CTAs win -- about 64 groups per warp
 //     (32 when there are only a few units): batch 16: 3-4 splits, batch 8: 2-4, batch 4: 2-5,
 //     batch 2: 5-9, batch 1: 5-8. Shorter contexts take proportionally shorter runs (16 at least).
+// More than four query heads per kv head go to the eight-head kernel when the context is long and
+// the launch is large (not with protected tokens: those rows exist in the four-head kernel only).
+// Measured per layer, eight-head against two four-head chunks: 200 / 231 us (8 heads per kv head,
+// batch 16, 32K context), 114 / 125 us (5 heads, batch 16, 16K), 35 / 40 us (5 heads, batch 4,
+// 16K); but 289 / 266 us at batch 64 with an 8K context (one short CTA per unit and its larger
+// fixed cost), and 21.5 / 20.3 us and 17.9 / 13.7 us on a half and an eighth of the batch-4 launch
+// (too few CTAs: the four-head kernel's twice as many fill the GPU better).
+bool wide_heads(const vq_kivi_attend_args &a) {
+    const int64_t groups = a.n_quant / kGroup;
+    return a.H_q / a.H_kv > kChunkHeads && a.sinks == nullptr && groups >= 512 &&
+           (int64_t)a.B * a.H_kv * groups >= 12288;
+}
+int head_chunks(const vq_kivi_attend_args &a) {
+    return (int)ceil_div(a.H_q / a.H_kv, wide_heads(a) ? kWideHeads : kChunkHeads);
+}
+
 int choose_splits(const vq_kivi_attend_args &a, const DeviceInfo &di) {
     (void)di;
     const int tiles = (int)ceil_div(a.n_quant, kGroup * kWarps);  // CTA-sized pieces of the context
     if (tiles <= 1) return std::max(tiles, 0);
     if (a.n_splits > 0) return std::min(std::min(a.n_splits, tiles), kMaxSplits);
-    const int n_chunks = (int)ceil_div(a.H_q / a.H_kv, kChunkHeads);
+    const int n_chunks = head_chunks(a);
     const int64_t units = (int64_t)a.B * a.H_kv * n_chunks;
     const int64_t groups = a.n_quant / kGroup;
     const int64_t cap = std::min<int64_t>(std::max(1, tiles / 4), kMaxSplits);  // >= 4 groups per warp
@@ -870,7 +1309,28 @@ int32_t launch_one(const Params &p, dim3 grid, cudaStream_t st) {
 }
 
 template <int BITS>
+int32_t launch_wide(const Params &p, dim3 grid, cudaStream_t st) {
+    using C = Cfg<BITS>;
+    constexpr int stage_area = kWarps * 2 * C::STAGE_BYTES, red_area = (2 * kWarps * kWideHeads * (kD + 4 + 2)) * 4;
+    const int smem = (stage_area > red_area ? stage_area : red_area) + 256;
+    VQ_CHECK_CUDA(cudaFuncSetAttribute(kivi_attend_mma8_kernel<BITS>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(kWarps * 32);
+    cfg.dynamicSmemBytes = (size_t)smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = (p.a.flags & VQ_ATTEND_OVERLAP_PREVIOUS) ? 1 : 0;
+    VQ_CHECK_CUDA(cudaLaunchKernelEx(&cfg, kivi_attend_mma8_kernel<BITS>, p));
+    return VQ_OK;
+}
+
+template <int BITS>
 int32_t launch_bits(const Params &p, dim3 grid, cudaStream_t st) {
+    if (p.wide) return launch_wide<BITS>(p, grid, st);
     if (p.sinks.count != nullptr) return launch_one<BITS, 2, true>(p, grid, st);  // (the stage knob applies to the plain kernel)
     switch (tuned_stages()) {
         case 3: return launch_one<BITS, 3, false>(p, grid, st);
@@ -1021,7 +1481,8 @@ int32_t kivi_attend_mma_launch(const vq_kivi_attend_args &a, const DeviceInfo &d
         p.gather = pg;
     }
     p.hpk = a.H_q / a.H_kv;
-    p.n_chunks = (int)ceil_div(p.hpk, kChunkHeads);
+    p.wide = wide_heads(a);
+    p.n_chunks = head_chunks(a);
     p.n_splits = choose_splits(a, di);
     p.groups_total = a.n_quant / kGroup;
     p.groups_per_warp = (int)ceil_div(p.groups_total, (int64_t)p.n_splits * kWarps);
