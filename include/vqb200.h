@@ -534,6 +534,42 @@ int32_t vq_rvq_unpack_decode(const uint32_t *packed1, const uint32_t *packed2, c
                              const float *centroids1, const float *centroids2, const float *diag, int32_t bits,
                              int32_t D, int64_t n_bh, int64_t seq, int64_t cap, void *out, void *stream);
 
+/* ---- SKVQ: clipped group quantization along the channel axis (per-token groups) -------------- */
+/* clipped_group_quant (veloxquant_mlx/quantizers/skvq.py:103-165) with the channel gather of
+ * apply_permutation (:98-100) folded in, codes bit-packed LSB-first along the row (the layout of
+ * vq_bit_pack). For every group of `group_size` channels of a token and every clip factor alpha:
+ * lo = mid - alpha*range/2, scale = max(alpha*range/(2^bits-1), 1e-8),
+ * code = clip(rint((x - lo)/scale), 0, 2^bits-1); the alpha with the smallest squared
+ * reconstruction error wins (first on ties; error sums in a fixed order: eight partial sums over
+ * the elements 8 apart, then a tree) and is folded into the stored (lo, scale). float32 arithmetic,
+ * every product and sum rounded separately. group_size 8, 16, 32 or 64 dividing D (the
+ * reference pads a ragged last group; not offered here). */
+typedef struct vq_skvq_quant_args {
+    const void *x;        /* [n_bh][n_tok][D] in x_dtype; (batch, head) blocks x_stride_bh ELEMENTS apart */
+    int64_t x_stride_bh;
+    const int32_t *perm;  /* device [n_heads][D] or NULL: stored channel j = x[..., perm[bh % n_heads][j]] */
+    uint8_t *codes;       /* [n_bh][>= n_tok][D*bits/8]; blocks q_stride_bh ROWS apart (also lo, scale) */
+    float *lo;            /* [n_bh][>= n_tok][D/group_size] */
+    float *scale;
+    int64_t q_stride_bh;
+    float alphas[8];      /* clip factors, each in (0, 1]; one value = no search */
+    int32_t n_alphas, x_dtype, n_bh, n_heads, n_tok, D, bits, group_size;
+} vq_skvq_quant_args;
+int32_t vq_skvq_quantize_pack(const vq_skvq_quant_args *args, void *stream);
+/* clipped_group_dequant (skvq.py:168-182) + the inverse gather: out[..., c] = code*scale + lo of
+ * stored channel inv_perm[bh % n_heads][c] (c itself when inv_perm is NULL), rounded to out_dtype. */
+typedef struct vq_skvq_dequant_args {
+    const uint8_t *codes;
+    const float *lo;
+    const float *scale;
+    int64_t q_stride_bh;
+    const int32_t *inv_perm;
+    void *out;            /* [n_bh][n_tok][D]; blocks out_stride_bh ELEMENTS apart */
+    int64_t out_stride_bh;
+    int32_t out_dtype, n_bh, n_heads, n_tok, D, bits, group_size, reserved;
+} vq_skvq_dequant_args;
+int32_t vq_skvq_unpack_dequant(const vq_skvq_dequant_args *args, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -25,6 +25,11 @@ What is executed from the reference, unmodified:
   supports of ``codebooks/strategies.py:38-94`` and the ``_laplacian_pdf`` of
   ``quantizers/turboquant_rvq.py``.
 
+* ``veloxquant_mlx/quantizers/skvq.py`` is loaded whole with a NumPy stand-in registered as
+  ``mlx.core`` (the functions it calls -- min, max, mean, round, clip, argmin, argsort, take ...
+  -- answered by NumPy in float32): the file's own arithmetic runs unmodified; what the stand-in
+  decides is the order of the error mean and ``round``'s tie rule (NumPy's).
+
 Nothing here imports the oracle: the fixtures are the reference's outputs and
 the oracle is checked against them by ``tests/test_oracle_golden.py``.
 """
@@ -195,7 +200,63 @@ def main():
             c, _ = lm.lloyd_max(lambda x, dd=d: dist.beta_pdf(x, dd), (-1.0 + 1e-6, 1.0 - 1e-6), n_levels=2 ** b)
             out[f"beta_b{b}_d{d}"] = c
     np.savez_compressed(os.path.join(HERE, "rvq.npz"), **out)
+
+    # ---------------- SKVQ quantizer (whole module, NumPy standing in for mlx.core) ----------------
+    mlx_pkg = types.ModuleType("mlx")
+    mlx_pkg.core = _mx_numpy_module()
+    saved = {k: sys.modules.get(k) for k in ("mlx", "mlx.core")}
+    sys.modules["mlx"], sys.modules["mlx.core"] = mlx_pkg, mlx_pkg.core
+    try:
+        skvq = load_module(os.path.join(pkg, "quantizers", "skvq.py"), "ref_skvq")
+    finally:
+        for k, v in saved.items():
+            if v is None:
+                sys.modules.pop(k, None)
+            else:
+                sys.modules[k] = v
+    out = {"alpha_grid": np.asarray(skvq.DEFAULT_ALPHA_GRID, np.float64)}
+    rng = np.random.default_rng(2405)
+    for tag, n, d, bits, gs, dt in [("a", 64, 32, 2, 8, np.float32), ("b", 48, 128, 4, 32, np.float16),
+                                    ("c", 40, 64, 3, 16, np.float16), ("d", 33, 128, 1, 64, np.float32),
+                                    ("e", 24, 128, 8, 32, np.float16)]:
+        scales = np.logspace(-2, 1, d)
+        rng.shuffle(scales)
+        x = (rng.standard_normal((n, d)) * scales[None, :]).astype(np.float32)
+        x[rng.random((n, d)) < 0.03] *= 20.0                       # sparse outliers: where clipping wins
+        x[0, :gs] = 0.75                                           # a constant group (range 0 -> scale = eps)
+        x = x.astype(dt)
+        codes, lo, scale = skvq.clipped_group_quant(x, bits, gs)
+        perm = skvq.channel_permutation(x)
+        out[f"{tag}_x"], out[f"{tag}_meta"] = x, np.asarray([bits, gs])
+        out[f"{tag}_codes"], out[f"{tag}_lo"], out[f"{tag}_scale"] = np.asarray(codes), np.asarray(lo), np.asarray(scale)
+        out[f"{tag}_perm"] = np.asarray(perm)
+        out[f"{tag}_inv"] = np.asarray(skvq.invert_permutation(perm))
+        out[f"{tag}_rt"] = np.asarray(skvq.skvq_round_trip(x, perm, bits, gs))
+        c1, lo1, s1 = skvq.clipped_group_quant(x, bits, gs, alphas=(0.9,))
+        out[f"{tag}_codes_a90"], out[f"{tag}_lo_a90"], out[f"{tag}_scale_a90"] = np.asarray(c1), np.asarray(lo1), np.asarray(s1)
+    out["bytes"] = np.asarray([skvq.skvq_compressed_bytes(123, 128, 4, 32), skvq.skvq_compressed_bytes(11, 64, 3, 16),
+                               skvq.skvq_fp16_bytes(77, 128)])
+    np.savez_compressed(os.path.join(HERE, "skvq.npz"), **out)
     print("golden fixtures written to", HERE)
+
+
+def _mx_numpy_module():
+    """A module object that answers the ``mlx.core`` names ``quantizers/skvq.py`` uses with NumPy
+    (float32 arrays stay float32: Python scalars are weak). ``argsort`` is stable, as MLX's is said
+    to be (skvq.py:88-89)."""
+    import types
+
+    m = types.ModuleType("mlx.core")
+    m.float32, m.uint8, m.int32, m.float16 = np.float32, np.uint8, np.int32, np.float16
+    m.array = lambda a, dtype=None: np.asarray(a, dtype=dtype)
+    m.min = lambda a, axis=None, keepdims=False: np.min(a, axis=axis, keepdims=keepdims)
+    m.max = lambda a, axis=None, keepdims=False: np.max(a, axis=axis, keepdims=keepdims)
+    m.mean = lambda a, axis=None, keepdims=False: np.mean(a, axis=axis, keepdims=keepdims)
+    m.maximum, m.clip, m.round, m.square = np.maximum, np.clip, np.round, np.square
+    m.argmin = lambda a, axis=None: np.argmin(a, axis=axis)
+    m.argsort = lambda a, axis=-1: np.argsort(a, axis=axis, kind="stable")
+    m.broadcast_to, m.take_along_axis, m.concatenate, m.take = np.broadcast_to, np.take_along_axis, np.concatenate, np.take
+    return m
 
 
 class _NdView(np.ndarray):

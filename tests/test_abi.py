@@ -53,17 +53,18 @@ def test_struct_sizes_match_header(built_lib, tmp_path):
 
     src = tmp_path / "sz.c"
     src.write_text(
-        '#include <stdio.h>\n#include "vqb200.h"\nint main(){printf("%zu %zu %zu %zu %zu %zu %zu %zu %zu\\n",'
+        '#include <stdio.h>\n#include "vqb200.h"\nint main(){printf("%zu %zu %zu %zu %zu %zu %zu %zu %zu %zu %zu\\n",'
         "sizeof(vq_kivi_quant_args),sizeof(vq_kivi_dequant_args),sizeof(vq_kivi_attend_args),"
         "sizeof(vq_vq_attend_args),sizeof(vq_rabitq_attend_args),sizeof(vq_vq_encode_args),"
-        "sizeof(vq_peer_gather),sizeof(vq_rabitq_prefill_args),sizeof(vq_kivi_sinks));return 0;}\n"
+        "sizeof(vq_peer_gather),sizeof(vq_rabitq_prefill_args),sizeof(vq_kivi_sinks),"
+        "sizeof(vq_skvq_quant_args),sizeof(vq_skvq_dequant_args));return 0;}\n"
     )
     exe = tmp_path / "sz"
     subprocess.run(["gcc", "-I", os.path.join(ROOT, "include"), str(src), "-o", str(exe)], check=True)
     out = subprocess.run([str(exe)], capture_output=True, text=True, check=True).stdout.split()
     got = [ctypes.sizeof(t) for t in (_lib.KiviQuantArgs, _lib.KiviDequantArgs, _lib.KiviAttendArgs,
                                       _lib.VqAttendArgs, _lib.RabitqAttendArgs, _lib.VqEncodeArgs, _lib.PeerGather,
-                                      _lib.RabitqPrefillArgs, _lib.KiviSinks)]
+                                      _lib.RabitqPrefillArgs, _lib.KiviSinks, _lib.SkvqQuantArgs, _lib.SkvqDequantArgs)]
     assert [int(v) for v in out] == got
 
 

@@ -214,3 +214,50 @@ def test_rabitq_prefill_matches_reference_numpy(tag):
                                    causal=tag.endswith("c1"))
     np.testing.assert_allclose(out, g("out"), rtol=0, atol=1e-6)
     assert np.array_equal(bitpack.pack(g("v_idx"), 4), g("v_packed"))
+
+
+@pytest.mark.parametrize("tag", list("abcde"))
+def test_skvq_oracle_matches_the_reference_module_run_over_numpy(tag):
+    """``oracle.skvq`` against ``quantizers/skvq.py`` executed whole with NumPy standing in for
+    ``mlx.core`` (make_golden.py): codes, lo, scale with and without the clip search, the channel
+    permutation and the permuted round trip, bit for bit."""
+    from oracle import skvq
+
+    z = _load("skvq.npz")
+    x = z[f"{tag}_x"]
+    bits, gs = (int(v) for v in z[f"{tag}_meta"])
+    assert tuple(z["alpha_grid"]) == skvq.DEFAULT_ALPHA_GRID
+    for suffix, alphas in (("", skvq.DEFAULT_ALPHA_GRID), ("_a90", (0.9,))):
+        codes, lo, scale = skvq.clipped_group_quant(x, bits, gs, alphas)
+        assert np.array_equal(codes, z[f"{tag}_codes{suffix}"])
+        assert np.array_equal(lo, z[f"{tag}_lo{suffix}"]) and np.array_equal(scale, z[f"{tag}_scale{suffix}"])
+    perm = skvq.channel_permutation(x)
+    assert np.array_equal(perm, z[f"{tag}_perm"]) and np.array_equal(skvq.invert_permutation(perm), z[f"{tag}_inv"])
+    rt = skvq.skvq_round_trip(x, perm, bits, gs)
+    assert rt.dtype == x.dtype and np.array_equal(rt, z[f"{tag}_rt"])
+    assert [skvq.skvq_compressed_bytes(123, 128, 4, 32), skvq.skvq_compressed_bytes(11, 64, 3, 16),
+            skvq.skvq_fp16_bytes(77, 128)] == [int(v) for v in z["bytes"]]
+
+
+def test_skvq_oracle_properties_of_the_reference_tests():
+    """alpha = 1 is plain min/max quantization up to one step on isolated boundary elements; the
+    searched clip factor is never worse per group (quantizers test_skvq.py:100-138)."""
+    from oracle import skvq
+
+    rng = np.random.default_rng(6)
+    x = rng.standard_normal((128, 32)).astype(np.float32)
+    x[rng.random((128, 32)) < 0.03] *= 20.0
+    codes, lo, scale = skvq.clipped_group_quant(x, 2, 8, (1.0,))
+    xg = x.reshape(128, 4, 8)
+    gmin, gmax = xg.min(-1, keepdims=True), xg.max(-1, keepdims=True)
+    ref_scale = np.maximum((gmax - gmin) / 3.0, 1e-8)
+    ref_codes = np.clip(np.round((xg - gmin) / ref_scale), 0, 3)
+    got = codes.astype(np.float64).reshape(128, 4, 8)
+    assert np.mean(got == ref_codes) > 0.999 and np.max(np.abs(got - ref_codes)) <= 1.0
+
+    def per_group_mse(alphas):
+        c, lo, sc = skvq.clipped_group_quant(x, 2, 8, alphas)
+        r = skvq.clipped_group_dequant(c, lo, sc, 8, 32)
+        return ((r - x) ** 2).reshape(128, 4, 8).mean(-1)
+
+    assert np.all(per_group_mse(skvq.DEFAULT_ALPHA_GRID) <= per_group_mse((1.0,)) + 1e-9)

@@ -127,6 +127,23 @@ def test_attend_parity_and_packed_equals_unpacked(D, S_kv, S_q, BH):
     assert torch.equal(out, packed)  # bit-identical, as the reference requires
 
 
+@pytest.mark.parametrize("D", [64, 256])
+@pytest.mark.parametrize("H,H_kv", [(6, 2), (12, 2)])
+def test_attend_parity_grouped_heads_every_head_dim(D, H, H_kv):
+    """3 and 6 query heads per kv head (the 4- and 8-head instantiations) at the narrowest and the
+    widest head_dim: every head keeps its own accumulators, nibble-coded and dense values."""
+    B, S = 2, 700
+    ins = _attend_inputs(B, H, 1, S, D, seed=D + H, H_kv=H_kv)
+    ref = o_rq.reference_attend(*ins)
+    r = _r()
+    got = r.rabitq_fused_attend(*[_t(a) for a in ins]).float().cpu().numpy()
+    assert np.all(np.abs(got - ref) <= 2e-3 + 1e-2 * np.abs(ref)), np.abs(got - ref).max()
+    v = np.random.default_rng(D).standard_normal((B, H_kv, S, D)).astype(np.float16)
+    ref = o_rq.reference_attend(*ins[:5], v)
+    got = r.rabitq_fused_attend(*[_t(a) for a in ins[:5]], _t(v), None).float().cpu().numpy()
+    assert np.all(np.abs(got - ref) <= 2e-3 + 1e-2 * np.abs(ref)), np.abs(got - ref).max()
+
+
 def test_attend_golden_fixture_gqa_dense_values_and_errors():
     z = np.load(os.path.join(GOLDEN, "rabitq.npz"))
     r = _r()

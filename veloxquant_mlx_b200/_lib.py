@@ -135,6 +135,24 @@ class VqEncodeArgs(C.Structure):
     ]
 
 
+class SkvqQuantArgs(C.Structure):
+    _fields_ = [
+        ("x", C.c_void_p), ("x_stride_bh", C.c_int64), ("perm", C.c_void_p), ("codes", C.c_void_p), ("lo", C.c_void_p),
+        ("scale", C.c_void_p), ("q_stride_bh", C.c_int64), ("alphas", C.c_float * 8), ("n_alphas", C.c_int32),
+        ("x_dtype", C.c_int32), ("n_bh", C.c_int32), ("n_heads", C.c_int32), ("n_tok", C.c_int32), ("D", C.c_int32),
+        ("bits", C.c_int32), ("group_size", C.c_int32),
+    ]
+
+
+class SkvqDequantArgs(C.Structure):
+    _fields_ = [
+        ("codes", C.c_void_p), ("lo", C.c_void_p), ("scale", C.c_void_p), ("q_stride_bh", C.c_int64),
+        ("inv_perm", C.c_void_p), ("out", C.c_void_p), ("out_stride_bh", C.c_int64), ("out_dtype", C.c_int32),
+        ("n_bh", C.c_int32), ("n_heads", C.c_int32), ("n_tok", C.c_int32), ("D", C.c_int32), ("bits", C.c_int32),
+        ("group_size", C.c_int32), ("reserved", C.c_int32),
+    ]
+
+
 # name -> (restype, argtypes); every symbol include/vqb200.h declares.
 SIGNATURES = {
     "vq_version": (C.c_int32, []),
@@ -182,6 +200,8 @@ SIGNATURES = {
     "vq_rvq_build_table": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p, C.c_void_p]),
     "vq_rvq_unpack_decode": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p, C.c_void_p, C.c_void_p,
                                          C.c_int32, C.c_int32, C.c_int64, C.c_int64, C.c_int64, C.c_void_p, C.c_void_p]),
+    "vq_skvq_quantize_pack": (C.c_int32, [C.POINTER(SkvqQuantArgs), C.c_void_p]),
+    "vq_skvq_unpack_dequant": (C.c_int32, [C.POINTER(SkvqDequantArgs), C.c_void_p]),
     "vq_bit_pack": (C.c_int32, [C.c_void_p, C.c_int64, C.c_int32, C.c_void_p, C.c_void_p]),
     "vq_bit_unpack": (C.c_int32, [C.c_void_p, C.c_int64, C.c_int32, C.c_void_p, C.c_void_p]),
 }

@@ -39,6 +39,7 @@ SOURCES = [
     ("coded_attend.cu", []),
     ("rabitq_prefill.cu", []),
     ("rvq.cu", []),
+    ("skvq.cu", ["-fmad=false"]),
 ]
 
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]

@@ -53,10 +53,27 @@ class KIVIOptions:
     kivi_group_size: int = 32
 
 
+@dataclass
+class SKVQOptions:
+    """SKVQ configuration (reference: ``cache/options.py:314-325``)."""
+
+    skvq_bits_key: int = 4
+    skvq_bits_value: int = 4
+    skvq_group_size: int = 32
+    skvq_window: int = 128
+    skvq_n_sink: int = 5
+    skvq_reorder: bool = True
+    skvq_clip_search: bool = True
+    skvq_clip_alpha: float = 1.0
+    skvq_max_ctx: Any = None
+
+
 _FIELD_TO_OPTIONS_CLASS = {
     "key_sub_dim": "VecInferOptions", "value_sub_dim": "VecInferOptions",
     "key_codebook_bits": "VecInferOptions", "value_codebook_bits": "VecInferOptions",
     "residual_length": "VecInferOptions", "kivi_group_size": "KIVIOptions",
+    **{name: "SKVQOptions" for name in ("skvq_bits_key", "skvq_bits_value", "skvq_group_size", "skvq_window", "skvq_n_sink",
+                                        "skvq_reorder", "skvq_clip_search", "skvq_clip_alpha", "skvq_max_ctx")},
 }
 
 _CACHE_CLASS_BY_METHOD: dict = {}  # filled at the bottom of the module
@@ -95,6 +112,15 @@ class KVCacheConfig:
     fused_sdpa_max_ctx: Any = None
     fused_sdpa_memory_bound: bool = False
     n_sink_tokens: int = 5
+    skvq_bits_key: int = 4
+    skvq_bits_value: int = 4
+    skvq_group_size: int = 32
+    skvq_window: int = 128
+    skvq_n_sink: int = 5
+    skvq_reorder: bool = True
+    skvq_clip_search: bool = True
+    skvq_clip_alpha: float = 1.0
+    skvq_max_ctx: Any = None
 
     def __repr__(self) -> str:
         return (f"KVCacheConfig(method={self.method!r}, d={self.head_dim}, "
@@ -828,7 +854,8 @@ _CACHE_CLASS_BY_METHOD["kivi"] = KIVIKVCache
 from .cache_coded import RaBitQKVCache, VecInferKVCache  # noqa: E402  (registers "vecinfer", "rabitq")
 from .cache_sink import SinkProtectedKVCache  # noqa: E402  (registers "kivi_sink")
 from .cache_rvq import TurboQuantRVQKVCache  # noqa: E402  (registers "turboquant_rvq")
+from .cache_skvq import SKVQKVCache  # noqa: E402  (registers "skvq")
 
-__all__ = ["QuantizerConfigError", "VecInferOptions", "KIVIOptions", "KVCacheConfig", "KVCacheFactory",
-           "KVCacheBuilder", "KIVIKVCache", "SinkProtectedKVCache", "TurboQuantRVQKVCache", "VecInferKVCache", "RaBitQKVCache", "KVCache",
-           "EncodedVector"]
+__all__ = ["QuantizerConfigError", "VecInferOptions", "KIVIOptions", "SKVQOptions", "KVCacheConfig", "KVCacheFactory",
+           "KVCacheBuilder", "KIVIKVCache", "SinkProtectedKVCache", "TurboQuantRVQKVCache", "SKVQKVCache", "VecInferKVCache",
+           "RaBitQKVCache", "KVCache", "EncodedVector"]

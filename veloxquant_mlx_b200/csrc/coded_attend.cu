@@ -239,13 +239,13 @@ coded_attend_kernel(const CodedParams p, int key_floats, int vlut_floats) {
     const int q_abs = p.S_kv - p.S_q + sq;
     const int n_words = D / 32;
 
-    // acc[mt]: channels 16*mt + g (regs 0, 1) and + 8 (regs 2, 3); columns 2c, 2c+1 = the (high, low)
-    // weight columns of head c (NH = 4) or heads 2c, 2c+1 (NH = 8)
-    float m_run[NH], l_run[NH], acc[8][4];
+    float m_run[NH], l_run[NH], acc[NH][DPL];  // acc[head][this lane's DPL channels]
 #pragma unroll
-    for (int h = 0; h < NH; ++h) { m_run[h] = -INFINITY; l_run[h] = 0.f; }
+    for (int h = 0; h < NH; ++h) {
+        m_run[h] = -INFINITY; l_run[h] = 0.f;
 #pragma unroll
-    for (int mt = 0; mt < 8; ++mt) acc[mt][0] = acc[mt][1] = acc[mt][2] = acc[mt][3] = 0.f;
+        for (int i = 0; i < DPL; ++i) acc[h][i] = 0.f;
+    }
 
     for (int tile = t_begin + 32 * warp; tile < t_end; tile += 32 * kWarpsC) {
         const int t = tile + lane;

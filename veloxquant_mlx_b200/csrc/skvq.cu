@@ -1,0 +1,222 @@
+// SKVQ: clipped group quantization with a per-group clip-factor search, packed, and its inverse
+// (reference: veloxquant_mlx/quantizers/skvq.py:103-182; the channel gathers of :98-100 folded in).
+//
+// One thread owns one (token, channel group): the group's GS values live in registers, so the
+// min / max, the five candidate windows and their reconstruction errors need no shuffles. The
+// error sums follow a fixed order (eight partial sums over the elements 8 apart, then a tree),
+// every product and sum is rounded separately (this file is compiled with -fmad=false; the fused
+// operations of the quotient below are explicit), the first minimum wins. HBM traffic is small
+// next to the arithmetic: ~13 instructions per element and candidate, so the search runs at the
+// instruction rate, the single-candidate form near the copy rate.
+#include "common.cuh"
+
+namespace vq {
+namespace {
+
+constexpr float kMagic = 12582912.0f;  // 1.5 * 2^23: x + kMagic - kMagic rounds x to the nearest-even integer
+constexpr float kEps = 1e-8f;
+
+struct QuantParams {
+    const void *x; int64_t x_stride_bh;
+    const int32_t *perm;
+    uint8_t *codes; float *lo; float *scale; int64_t q_stride_bh;
+    float alphas[8]; int n_alphas;
+    int n_bh, n_heads, n_tok, D, bits;
+};
+
+// code = clip(rint((v - lo) / scale), 0, levels) with the IEEE quotient from rc = RN(1/scale):
+// t0 = RN(d*rc), r = d - scale*t0 (exact in one fma), RN(t0 + r*rc) (Markstein); a quotient that
+// is not finite falls back to the divide.
+__device__ __forceinline__ float code_of(float v, float lo, float scale, float rc, float levels) {
+    const float d = __fsub_rn(v, lo);
+    const float t0 = __fmul_rn(d, rc);
+    float q = __fmaf_rn(__fmaf_rn(-scale, t0, d), rc, t0);
+    if (!(fabsf(q) < 1e30f)) q = __fdiv_rn(d, scale);
+    q = __fsub_rn(__fadd_rn(fminf(fmaxf(q, -1.0f), levels + 1.0f), kMagic), kMagic);  // rint of the clamped quotient
+    return fminf(fmaxf(q, 0.0f), levels);
+}
+
+template <typename T, int GS>
+__global__ void __launch_bounds__(128) skvq_quant_kernel(const QuantParams p) {
+    const int G = p.D / GS;
+    const int64_t n_groups = (int64_t)p.n_bh * p.n_tok * G;
+    const int64_t gi = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (gi >= n_groups) return;
+    const int g = (int)(gi % G);
+    const int64_t row = gi / G;
+    const int tok = (int)(row % p.n_tok);
+    const int bh = (int)(row / p.n_tok);
+    const T *src = reinterpret_cast<const T *>(p.x) + (int64_t)bh * p.x_stride_bh + (int64_t)tok * p.D;
+
+    float v[GS];
+    if (p.perm) {
+        const int32_t *pm = p.perm + (int64_t)(bh % p.n_heads) * p.D + g * GS;
+#pragma unroll
+        for (int j = 0; j < GS; ++j) v[j] = to_f32<T>(src[__ldg(pm + j)]);
+    } else {
+        // 16-byte vector loads of the group's contiguous channels
+        constexpr int PER = 16 / (int)sizeof(T);
+        const uint4 *s4 = reinterpret_cast<const uint4 *>(src + g * GS);
+#pragma unroll
+        for (int j = 0; j < GS / PER; ++j) {
+            const uint4 w = __ldg(s4 + j);
+            const T *e = reinterpret_cast<const T *>(&w);
+#pragma unroll
+            for (int i = 0; i < PER; ++i) v[j * PER + i] = to_f32<T>(e[i]);
+        }
+    }
+    float gmin = v[0], gmax = v[0];
+#pragma unroll
+    for (int j = 1; j < GS; ++j) { gmin = fminf(gmin, v[j]); gmax = fmaxf(gmax, v[j]); }
+    const float mid = __fmul_rn(__fadd_rn(gmax, gmin), 0.5f);
+    const float rng = __fsub_rn(gmax, gmin);
+    const float levels = (float)((1 << p.bits) - 1);
+
+    float best_err = 0.f, best_lo = 0.f, best_scale = 0.f;
+    for (int a = 0; a < p.n_alphas; ++a) {
+        const float ar = __fmul_rn(p.alphas[a], rng);
+        const float lo = __fsub_rn(mid, __fmul_rn(ar, 0.5f));
+        const float scale = fmaxf(__fdiv_rn(ar, levels), kEps);
+        if (p.n_alphas == 1) { best_lo = lo; best_scale = scale; break; }
+        const float rc = __frcp_rn(scale);
+        float r[8];
+#pragma unroll
+        for (int j = 0; j < GS; ++j) {
+            const float c = code_of(v[j], lo, scale, rc, levels);
+            const float e = __fsub_rn(__fadd_rn(__fmul_rn(c, scale), lo), v[j]);
+            const float sq = __fmul_rn(e, e);
+            if (j < 8) r[j] = sq;
+            else r[j & 7] = __fadd_rn(r[j & 7], sq);
+        }
+        const float err = __fadd_rn(__fadd_rn(__fadd_rn(r[0], r[1]), __fadd_rn(r[2], r[3])),
+                                    __fadd_rn(__fadd_rn(r[4], r[5]), __fadd_rn(r[6], r[7])));
+        if (a == 0 || err < best_err) { best_err = err; best_lo = lo; best_scale = scale; }
+    }
+
+    // codes of the chosen window, appended LSB-first; a group is GS*bits/8 whole bytes
+    const int64_t qrow = (int64_t)bh * p.q_stride_bh + tok;
+    p.lo[qrow * G + g] = best_lo;
+    p.scale[qrow * G + g] = best_scale;
+    const float rc = __frcp_rn(best_scale);
+    const int group_bytes = GS * p.bits / 8;
+    uint8_t *dst = p.codes + qrow * ((int64_t)p.D * p.bits / 8) + (int64_t)g * group_bytes;
+    uint64_t acc = 0;
+    int nb = 0;
+    if ((group_bytes & 3) == 0) {
+        uint32_t *d32 = reinterpret_cast<uint32_t *>(dst);
+#pragma unroll
+        for (int j = 0; j < GS; ++j) {
+            acc |= (uint64_t)(uint32_t)code_of(v[j], best_lo, best_scale, rc, levels) << nb;
+            nb += p.bits;
+            if (nb >= 32) { *d32++ = (uint32_t)acc; acc >>= 32; nb -= 32; }
+        }
+    } else {
+#pragma unroll
+        for (int j = 0; j < GS; ++j) {
+            acc |= (uint64_t)(uint32_t)code_of(v[j], best_lo, best_scale, rc, levels) << nb;
+            nb += p.bits;
+            while (nb >= 8) { *dst++ = (uint8_t)acc; acc >>= 8; nb -= 8; }
+        }
+    }
+}
+
+struct DequantParams {
+    const uint8_t *codes; const float *lo; const float *scale; int64_t q_stride_bh;
+    const int32_t *inv_perm;
+    void *out; int64_t out_stride_bh; int out_dtype;
+    int n_bh, n_heads, n_tok, D, bits, gs;
+};
+
+// One thread per output element: channel c of the output is stored channel inv_perm[c] (so the
+// stores are coalesced and the gather hits the row's few cache lines).
+__global__ void __launch_bounds__(256) skvq_dequant_kernel(const DequantParams p) {
+    const int64_t total = (int64_t)p.n_bh * p.n_tok * p.D;
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= total) return;
+    const int c = (int)(i % p.D);
+    const int64_t row = i / p.D;
+    const int tok = (int)(row % p.n_tok);
+    const int bh = (int)(row / p.n_tok);
+    const int j = p.inv_perm ? __ldg(p.inv_perm + (int64_t)(bh % p.n_heads) * p.D + c) : c;
+    const int64_t qrow = (int64_t)bh * p.q_stride_bh + tok;
+    const uint8_t *src = p.codes + qrow * ((int64_t)p.D * p.bits / 8);
+    const int bit = j * p.bits;
+    uint32_t w = src[bit >> 3];
+    if ((bit & 7) + p.bits > 8) w |= (uint32_t)src[(bit >> 3) + 1] << 8;
+    const float code = (float)((w >> (bit & 7)) & ((1u << p.bits) - 1u));
+    const int G = p.D / p.gs;
+    const float val = __fadd_rn(__fmul_rn(code, p.scale[qrow * G + j / p.gs]), p.lo[qrow * G + j / p.gs]);
+    store_from_f32(p.out, p.out_dtype, (int64_t)bh * p.out_stride_bh + (int64_t)tok * p.D + c, val);
+}
+
+template <typename T>
+int32_t launch_quant(const QuantParams &p, int gs, cudaStream_t st) {
+    const int64_t n_groups = (int64_t)p.n_bh * p.n_tok * (p.D / gs);
+    const unsigned blocks = (unsigned)ceil_div(n_groups, 128);
+    switch (gs) {
+        case 8: skvq_quant_kernel<T, 8><<<blocks, 128, 0, st>>>(p); break;
+        case 16: skvq_quant_kernel<T, 16><<<blocks, 128, 0, st>>>(p); break;
+        case 32: skvq_quant_kernel<T, 32><<<blocks, 128, 0, st>>>(p); break;
+        default: skvq_quant_kernel<T, 64><<<blocks, 128, 0, st>>>(p); break;
+    }
+    VQ_CHECK_LAUNCH("skvq_quant_kernel");
+    return VQ_OK;
+}
+
+}  // namespace
+}  // namespace vq
+
+extern "C" int32_t vq_skvq_quantize_pack(const vq_skvq_quant_args *args, void *stream) {
+    using namespace vq;
+    VQ_REQUIRE(args != nullptr, VQ_ERR_SHAPE, "vq_skvq_quantize_pack: args is NULL");
+    const vq_skvq_quant_args &a = *args;
+    VQ_REQUIRE(a.bits >= 1 && a.bits <= 8, VQ_ERR_SHAPE, "skvq: bits=%d must be in [1, 8] (uint8 codes)", a.bits);
+    VQ_REQUIRE(a.group_size == 8 || a.group_size == 16 || a.group_size == 32 || a.group_size == 64, VQ_ERR_SHAPE,
+               "skvq: group_size=%d must be 8, 16, 32 or 64 here", a.group_size);
+    VQ_REQUIRE(a.D >= a.group_size && a.D % a.group_size == 0 && a.D <= 1024, VQ_ERR_SHAPE,
+               "skvq: D=%d must be a multiple of group_size=%d (at most 1024)", a.D, a.group_size);
+    VQ_REQUIRE(a.n_alphas >= 1 && a.n_alphas <= 8, VQ_ERR_SHAPE, "skvq: alphas must hold 1 to 8 values");
+    for (int i = 0; i < a.n_alphas; ++i)
+        VQ_REQUIRE(a.alphas[i] > 0.f && a.alphas[i] <= 1.f, VQ_ERR_SHAPE, "skvq: alpha=%g must be in (0, 1]", (double)a.alphas[i]);
+    VQ_REQUIRE(a.n_bh >= 0 && a.n_tok >= 0 && a.n_heads >= 1, VQ_ERR_SHAPE, "skvq: bad sizes");
+    if (a.n_bh == 0 || a.n_tok == 0) return VQ_OK;
+    VQ_REQUIRE(a.x && a.codes && a.lo && a.scale, VQ_ERR_SHAPE, "skvq: NULL argument");
+    VQ_REQUIRE(a.x_dtype == VQ_F16 || a.x_dtype == VQ_BF16 || a.x_dtype == VQ_F32, VQ_ERR_DTYPE, "skvq: unsupported dtype %d", a.x_dtype);
+    const size_t es = dtype_size(a.x_dtype);
+    VQ_REQUIRE(a.perm || (is_aligned(a.x, 16) && (a.x_stride_bh * es) % 16 == 0 && ((size_t)a.D * es) % 16 == 0 &&
+                          ((size_t)a.group_size * es) % 16 == 0),
+               VQ_ERR_ALIGN, "skvq: rows must be 16-byte aligned");
+    const int group_bytes = a.group_size * a.bits / 8;
+    VQ_REQUIRE((group_bytes & 3) != 0 || (is_aligned(a.codes, 4) && ((int64_t)a.D * a.bits / 8) % 4 == 0), VQ_ERR_ALIGN,
+               "skvq: packed rows must be 4-byte aligned");
+    QuantParams p{};
+    p.x = a.x; p.x_stride_bh = a.x_stride_bh; p.perm = a.perm;
+    p.codes = a.codes; p.lo = a.lo; p.scale = a.scale; p.q_stride_bh = a.q_stride_bh;
+    for (int i = 0; i < a.n_alphas; ++i) p.alphas[i] = a.alphas[i];
+    p.n_alphas = a.n_alphas; p.n_bh = a.n_bh; p.n_heads = a.n_heads; p.n_tok = a.n_tok; p.D = a.D; p.bits = a.bits;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (a.x_dtype == VQ_F16) return launch_quant<__half>(p, a.group_size, st);
+    if (a.x_dtype == VQ_BF16) return launch_quant<__nv_bfloat16>(p, a.group_size, st);
+    return launch_quant<float>(p, a.group_size, st);
+}
+
+extern "C" int32_t vq_skvq_unpack_dequant(const vq_skvq_dequant_args *args, void *stream) {
+    using namespace vq;
+    VQ_REQUIRE(args != nullptr, VQ_ERR_SHAPE, "vq_skvq_unpack_dequant: args is NULL");
+    const vq_skvq_dequant_args &a = *args;
+    VQ_REQUIRE(a.bits >= 1 && a.bits <= 8, VQ_ERR_SHAPE, "skvq: bits=%d must be in [1, 8] (uint8 codes)", a.bits);
+    VQ_REQUIRE(a.group_size >= 1 && a.D >= 1 && a.D % a.group_size == 0 && ((int64_t)a.D * a.bits) % 8 == 0, VQ_ERR_SHAPE,
+               "skvq: D=%d must be a multiple of group_size=%d and D*bits of 8", a.D, a.group_size);
+    VQ_REQUIRE(a.n_bh >= 0 && a.n_tok >= 0 && a.n_heads >= 1, VQ_ERR_SHAPE, "skvq: bad sizes");
+    if (a.n_bh == 0 || a.n_tok == 0) return VQ_OK;
+    VQ_REQUIRE(a.codes && a.lo && a.scale && a.out, VQ_ERR_SHAPE, "skvq: NULL argument");
+    VQ_REQUIRE(a.out_dtype == VQ_F16 || a.out_dtype == VQ_BF16 || a.out_dtype == VQ_F32, VQ_ERR_DTYPE, "skvq: unsupported dtype %d", a.out_dtype);
+    DequantParams p{};
+    p.codes = a.codes; p.lo = a.lo; p.scale = a.scale; p.q_stride_bh = a.q_stride_bh; p.inv_perm = a.inv_perm;
+    p.out = a.out; p.out_stride_bh = a.out_stride_bh; p.out_dtype = a.out_dtype;
+    p.n_bh = a.n_bh; p.n_heads = a.n_heads; p.n_tok = a.n_tok; p.D = a.D; p.bits = a.bits; p.gs = a.group_size;
+    const int64_t total = (int64_t)a.n_bh * a.n_tok * a.D;
+    skvq_dequant_kernel<<<(unsigned)ceil_div(total, 256), 256, 0, (cudaStream_t)stream>>>(p);
+    VQ_CHECK_LAUNCH("skvq_dequant_kernel");
+    return VQ_OK;
+}
