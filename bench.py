@@ -766,6 +766,18 @@ def run_extras(torch, dist, timer, w, plan, world, rank, device, dtype, px, args
         extra["rvq_unpack_decode_2bit"] = {"rows": Nr, "us": ms * 1e3, "GBps": nb / (ms * 1e-3) / 1e9, "frac": nb / (ms * 1e-3) / 1e9 / peak}
         del yr, pk1, pk2, nrm
 
+        # -- SKVQ: clipped group quantize + pack (five clip factors searched / one) and unpack + dequantize, 1 Mi rows
+        from veloxquant_mlx_b200 import skvq
+        xs = torch.randn(64, 16384, D, device=device, dtype=torch.float16)
+        nb = xs.numel() * 2 + xs.numel() // 2 + 2 * (xs.numel() // 32) * 4
+        sk_out = skvq.quantize_pack(xs, 4, 32)
+        for name, alphas in (("skvq_quant_pack_4bit_search5", skvq.DEFAULT_ALPHA_GRID), ("skvq_quant_pack_4bit_fixed", (0.94,))):
+            ms = graph_time(lambda: skvq.quantize_pack(xs, 4, 32, alphas, out=sk_out), 5)
+            extra[name] = {"rows": 64 * 16384, "us": ms * 1e3, "GBps": nb / (ms * 1e-3) / 1e9, "frac": nb / (ms * 1e-3) / 1e9 / peak}
+        ms = graph_time(lambda: skvq.unpack_dequant(*sk_out, 4, 32, 16384, torch.float16, out=xs), 5)
+        extra["skvq_unpack_dequant_4bit"] = {"rows": 64 * 16384, "us": ms * 1e3, "GBps": nb / (ms * 1e-3) / 1e9, "frac": nb / (ms * 1e-3) / 1e9 / peak}
+        del xs, sk_out
+
         # -- RaBitQ config 4: encode and attend
         from veloxquant_mlx_b200 import rabitq as rq
         Br, Hr, Sr = 8, 8, 16384

@@ -127,8 +127,8 @@ struct DequantParams {
     int n_bh, n_heads, n_tok, D, bits, gs;
 };
 
-// One thread per output element: channel c of the output is stored channel inv_perm[c] (so the
-// stores are coalesced and the gather hits the row's few cache lines).
+// General form, one thread per output element: channel c of the output is stored channel
+// inv_perm[c] (any D, any group size). The serving shapes take the row kernel below.
 __global__ void __launch_bounds__(256) skvq_dequant_kernel(const DequantParams p) {
     const int64_t total = (int64_t)p.n_bh * p.n_tok * p.D;
     const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -147,6 +147,121 @@ __global__ void __launch_bounds__(256) skvq_dequant_kernel(const DequantParams p
     const int G = p.D / p.gs;
     const float val = __fadd_rn(__fmul_rn(code, p.scale[qrow * G + j / p.gs]), p.lo[qrow * G + j / p.gs]);
     store_from_f32(p.out, p.out_dtype, (int64_t)bh * p.out_stride_bh + (int64_t)tok * p.D + c, val);
+}
+
+// Row form (D = 32 * CPL, CPL = 2, 4 or 8; packed rows and parameter rows 4-byte aligned): a warp
+// owns a token row. Its lanes load the row's packed words (at most 64) and its (lo, scale) pairs
+// once, coalesced; every lane then picks the codes of its CPL consecutive OUTPUT channels out of
+// the other lanes' registers by shuffle -- which is also the inverse channel gather -- and stores
+// them as one vector. Eight rows per warp are in flight. blockIdx.y = (batch, head) block, so the
+// head's permutation entries are loaded once per thread.
+// float(c) for 0 <= c < 2^23 without the conversion unit: c in the mantissa of 2^23, minus 2^23 (exact)
+__device__ __forceinline__ float small_uint_as_float(uint32_t c) { return __fsub_rn(__uint_as_float(0x4B000000u | c), 8388608.0f); }
+
+constexpr int kDqWarps = 4, kDqRowsPerWarp = 16;
+
+template <typename T, int CPL>
+__global__ void __launch_bounds__(kDqWarps * 32) skvq_dequant_rows_kernel(const DequantParams p) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int bh = blockIdx.y;
+    const int D = 32 * CPL;
+    const int G = D / p.gs;
+    const int n_words = D * p.bits / 32;   // <= 64
+    const uint32_t mask = (1u << p.bits) - 1u;
+    const bool wide = n_words > 32, straddle = (p.bits & (p.bits - 1)) != 0;  // a code crosses words only at 3, 5, 6, 7 bits
+    // without a permutation and at 1, 2, 4 bits (8 too while a lane's codes fit one word) a lane's CPL
+    // codes share one packed word and one group: three shuffles per row instead of three per code
+    const bool same = p.inv_perm == nullptr && !straddle && CPL * p.bits <= 32;
+    int bit[CPL], grp[CPL];
+#pragma unroll
+    for (int i = 0; i < CPL; ++i) {
+        const int c = lane * CPL + i;
+        const int j = p.inv_perm ? __ldg(p.inv_perm + (int64_t)(bh % p.n_heads) * D + c) : c;
+        bit[i] = j * p.bits;
+        grp[i] = j / p.gs;
+    }
+    const int tok0 = (blockIdx.x * kDqWarps + warp) * kDqRowsPerWarp;
+    T *out = reinterpret_cast<T *>(p.out) + (int64_t)bh * p.out_stride_bh;
+    constexpr int R = 8;  // rows in flight
+    for (int t0 = tok0; t0 < min(tok0 + kDqRowsPerWarp, p.n_tok); t0 += R) {
+        uint32_t w0[R], w1[R];
+        float lo[R], sc[R];
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+            const int tok = min(t0 + r, p.n_tok - 1);
+            const int64_t qrow = (int64_t)bh * p.q_stride_bh + tok;
+            const uint32_t *src = reinterpret_cast<const uint32_t *>(p.codes + qrow * ((int64_t)n_words * 4));
+            w0[r] = lane < n_words ? __ldg(src + lane) : 0u;
+            w1[r] = lane + 32 < n_words ? __ldg(src + lane + 32) : 0u;
+            lo[r] = lane < G ? __ldg(p.lo + qrow * G + lane) : 0.f;
+            sc[r] = lane < G ? __ldg(p.scale + qrow * G + lane) : 0.f;
+        }
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+            float v[CPL];
+            uint32_t w_same = 0u;
+            float l_same = 0.f, s_same = 0.f;
+            if (same) {
+                w_same = __shfl_sync(0xffffffffu, w0[r], bit[0] >> 5);
+                l_same = __shfl_sync(0xffffffffu, lo[r], grp[0]);
+                s_same = __shfl_sync(0xffffffffu, sc[r], grp[0]);
+            }
+#pragma unroll
+            for (int i = 0; i < CPL; ++i) {
+                if (same) {
+                    v[i] = __fadd_rn(__fmul_rn(small_uint_as_float((w_same >> (bit[i] & 31)) & mask), s_same), l_same);
+                    continue;
+                }
+                const int wi = bit[i] >> 5, sh = bit[i] & 31;
+                // (64-bit window over words wi and wi + 1: a code may straddle two words)
+                // (the second register and the next word only where the shape needs them: warp-uniform)
+                uint32_t wlo = __shfl_sync(0xffffffffu, w0[r], wi & 31), whi = 0u;
+                if (wide) {
+                    const uint32_t a1 = __shfl_sync(0xffffffffu, w1[r], wi & 31);
+                    wlo = wi < 32 ? wlo : a1;
+                }
+                if (straddle) {
+                    whi = __shfl_sync(0xffffffffu, w0[r], (wi + 1) & 31);
+                    if (wide) {
+                        const uint32_t b1 = __shfl_sync(0xffffffffu, w1[r], (wi + 1) & 31);
+                        whi = wi + 1 < 32 ? whi : b1;
+                    }
+                }
+                const uint32_t code = (uint32_t)((((uint64_t)whi << 32) | wlo) >> sh) & mask;
+                const float l = __shfl_sync(0xffffffffu, lo[r], grp[i]), s = __shfl_sync(0xffffffffu, sc[r], grp[i]);
+                v[i] = __fadd_rn(__fmul_rn(small_uint_as_float(code), s), l);
+            }
+            if (t0 + r < p.n_tok) {
+                T *dst = out + (int64_t)(t0 + r) * D + lane * CPL;
+                if constexpr (sizeof(T) == 4) {
+#pragma unroll
+                    for (int i = 0; i < CPL; i += 4) *reinterpret_cast<float4 *>(dst + i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+                } else {
+                    uint32_t pk[CPL / 2];
+#pragma unroll
+                    for (int i = 0; i < CPL / 2; ++i) {
+                        const T a = from_f32<T>(v[2 * i]), b = from_f32<T>(v[2 * i + 1]);
+                        pk[i] = (uint32_t)*reinterpret_cast<const uint16_t *>(&a) | ((uint32_t)*reinterpret_cast<const uint16_t *>(&b) << 16);
+                    }
+                    if constexpr (CPL == 2) *reinterpret_cast<uint32_t *>(dst) = pk[0];
+                    else if constexpr (CPL == 4) *reinterpret_cast<uint2 *>(dst) = make_uint2(pk[0], pk[1]);
+                    else *reinterpret_cast<uint4 *>(dst) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+                }
+            }
+        }
+    }
+}
+
+template <typename T>
+int32_t launch_dequant_rows(const DequantParams &p, cudaStream_t st) {
+    dim3 grid((unsigned)ceil_div(p.n_tok, kDqWarps * kDqRowsPerWarp), (unsigned)p.n_bh);
+    switch (p.D / 32) {
+        case 2: skvq_dequant_rows_kernel<T, 2><<<grid, kDqWarps * 32, 0, st>>>(p); break;
+        case 4: skvq_dequant_rows_kernel<T, 4><<<grid, kDqWarps * 32, 0, st>>>(p); break;
+        default: skvq_dequant_rows_kernel<T, 8><<<grid, kDqWarps * 32, 0, st>>>(p); break;
+    }
+    VQ_CHECK_LAUNCH("skvq_dequant_rows_kernel");
+    return VQ_OK;
 }
 
 template <typename T>
@@ -215,8 +330,17 @@ extern "C" int32_t vq_skvq_unpack_dequant(const vq_skvq_dequant_args *args, void
     p.codes = a.codes; p.lo = a.lo; p.scale = a.scale; p.q_stride_bh = a.q_stride_bh; p.inv_perm = a.inv_perm;
     p.out = a.out; p.out_stride_bh = a.out_stride_bh; p.out_dtype = a.out_dtype;
     p.n_bh = a.n_bh; p.n_heads = a.n_heads; p.n_tok = a.n_tok; p.D = a.D; p.bits = a.bits; p.gs = a.group_size;
+    cudaStream_t st = (cudaStream_t)stream;
+    const size_t es = dtype_size(a.out_dtype);
+    const bool rows_ok = (a.D == 64 || a.D == 128 || a.D == 256) && a.n_bh <= 65535 && ((int64_t)a.D * a.bits / 8) % 4 == 0 &&
+                         is_aligned(a.codes, 4) && is_aligned(a.out, 16) && ((size_t)a.out_stride_bh * es) % 16 == 0;
+    if (rows_ok) {
+        if (a.out_dtype == VQ_F16) return launch_dequant_rows<__half>(p, st);
+        if (a.out_dtype == VQ_BF16) return launch_dequant_rows<__nv_bfloat16>(p, st);
+        return launch_dequant_rows<float>(p, st);
+    }
     const int64_t total = (int64_t)a.n_bh * a.n_tok * a.D;
-    skvq_dequant_kernel<<<(unsigned)ceil_div(total, 256), 256, 0, (cudaStream_t)stream>>>(p);
+    skvq_dequant_kernel<<<(unsigned)ceil_div(total, 256), 256, 0, st>>>(p);
     VQ_CHECK_LAUNCH("skvq_dequant_kernel");
     return VQ_OK;
 }

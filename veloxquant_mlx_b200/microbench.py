@@ -146,6 +146,28 @@ def op_rvq(a):
         _line("rvq_unpack_decode", f"[{N},{D}] b={bits} -> f16", us, nbytes=N * D * 2 + 2 * N * nw * 4 + N * 2)
 
 
+def op_skvq(a):
+    """SKVQ clipped group quantize+pack (clip-factor search / one factor, with and without a channel
+    permutation) and unpack+dequantize of 1 Mi rows (head_dim 128, groups of 32)."""
+    from . import skvq
+
+    n_bh, n_tok, D = 64, 16384, 128
+    x = torch.randn(n_bh, n_tok, D, device="cuda", dtype=_DT[a.dtype])
+    perm = torch.stack([torch.randperm(D, device="cuda") for _ in range(8)]).to(torch.int32)
+    for bits in (2, 4):
+        out = skvq.quantize_pack(x, bits, 32)
+        nb = x.numel() * x.element_size() + x.numel() * bits // 8 + 2 * (x.numel() // 32) * 4
+        for label, alphas, p in (("search5", skvq.DEFAULT_ALPHA_GRID, None), ("search5+perm", skvq.DEFAULT_ALPHA_GRID, perm),
+                                 ("fixed", (0.94,), None)):
+            us = _time_us(lambda: skvq.quantize_pack(x, bits, 32, alphas, perm=p, out=out), a.iters)
+            _line("skvq_quant_pack", f"[{n_bh * n_tok},{D}] {a.dtype} b={bits} {label}", us, nbytes=nb)
+        y = torch.empty_like(x)
+        inv = torch.argsort(perm.long(), dim=-1).to(torch.int32)
+        for label, ip in (("", None), ("+perm", inv)):
+            us = _time_us(lambda: skvq.unpack_dequant(*out, bits, 32, n_tok, x.dtype, inv_perm=ip, out=y), a.iters)
+            _line("skvq_unpack_dequant", f"[{n_bh * n_tok},{D}] b={bits} -> {a.dtype} {label}", us, nbytes=nb)
+
+
 def op_kivi_attend(a):
     """Decode attention over a KIVI cache at the small benchmark shapes (config 1 and config 5, one layer)."""
     from .cache import KVCacheConfig, KVCacheFactory
@@ -165,7 +187,7 @@ def op_kivi_attend(a):
 
 
 OPS = {"kivi_attend": op_kivi_attend, "kivi_quantize": op_kivi_quantize, "vq_quantize": op_vq_quantize, "vq_encode": op_vq_encode,
-       "vq_attend": op_vq_attend, "rabitq": op_rabitq, "rvq": op_rvq}
+       "vq_attend": op_vq_attend, "rabitq": op_rabitq, "rvq": op_rvq, "skvq": op_skvq}
 
 
 def main(argv=None):
