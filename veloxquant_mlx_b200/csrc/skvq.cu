@@ -8,6 +8,8 @@
 // operations of the quotient below are explicit), the first minimum wins. HBM traffic is small
 // next to the arithmetic: ~13 instructions per element and candidate, so the search runs at the
 // instruction rate, the single-candidate form near the copy rate.
+#include <type_traits>
+
 #include "common.cuh"
 
 namespace vq {
@@ -24,16 +26,79 @@ struct QuantParams {
     int n_bh, n_heads, n_tok, D, bits;
 };
 
-// code = clip(rint((v - lo) / scale), 0, levels) with the IEEE quotient from rc = RN(1/scale):
-// t0 = RN(d*rc), r = d - scale*t0 (exact in one fma), RN(t0 + r*rc) (Markstein); a quotient that
-// is not finite falls back to the divide.
-__device__ __forceinline__ float code_of(float v, float lo, float scale, float rc, float levels) {
+// clip((v - lo) / scale, 0, levels) + kMagic: the IEEE quotient from rc = RN(1/scale) as t0 = RN(d*rc),
+// r = d - scale*t0 (exact in one fma), RN(t0 + r*rc) (Markstein), clamped BEFORE the rounding (the
+// bounds are integers, so clamp and round-to-nearest-even commute), then rounded by the magic-number
+// add: the sum's low mantissa bits hold the code. For finite input of sane magnitude (range below
+// 1e30) the quotient is finite; `exact_div` selects the divide for the rest.
+template <bool EXACT_DIV>
+__device__ __forceinline__ float code_plus_magic(float v, float lo, float scale, float rc, float levels) {
     const float d = __fsub_rn(v, lo);
-    const float t0 = __fmul_rn(d, rc);
-    float q = __fmaf_rn(__fmaf_rn(-scale, t0, d), rc, t0);
-    if (!(fabsf(q) < 1e30f)) q = __fdiv_rn(d, scale);
-    q = __fsub_rn(__fadd_rn(fminf(fmaxf(q, -1.0f), levels + 1.0f), kMagic), kMagic);  // rint of the clamped quotient
-    return fminf(fmaxf(q, 0.0f), levels);
+    float q;
+    if (EXACT_DIV) {
+        q = __fdiv_rn(d, scale);
+    } else {
+        const float t0 = __fmul_rn(d, rc);
+        q = __fmaf_rn(__fmaf_rn(-scale, t0, d), rc, t0);
+    }
+    return __fadd_rn(fminf(fmaxf(q, 0.0f), levels), kMagic);
+}
+
+// The search and the packing of one group whose values, minimum, maximum and range are known.
+template <int GS, bool EXACT_DIV>
+__device__ __forceinline__ void quantize_group(const QuantParams &p, const float (&v)[GS], float gmin, float gmax, float rng,
+                                               int bh, int tok, int g, int G) {
+    const float mid = __fmul_rn(__fadd_rn(gmax, gmin), 0.5f);
+    const float levels = (float)((1 << p.bits) - 1);
+
+    float best_err = 0.f, best_lo = 0.f, best_scale = 0.f;
+    for (int a = 0; a < p.n_alphas; ++a) {
+        const float ar = __fmul_rn(p.alphas[a], rng);
+        const float lo = __fsub_rn(mid, __fmul_rn(ar, 0.5f));
+        const float scale = fmaxf(__fdiv_rn(ar, levels), kEps);
+        if (p.n_alphas == 1) { best_lo = lo; best_scale = scale; break; }
+        const float rc = __frcp_rn(scale);
+        float r[8];
+#pragma unroll
+        for (int j = 0; j < GS; ++j) {
+            const float c = __fsub_rn(code_plus_magic<EXACT_DIV>(v[j], lo, scale, rc, levels), kMagic);
+            const float e = __fsub_rn(__fadd_rn(__fmul_rn(c, scale), lo), v[j]);
+            const float sq = __fmul_rn(e, e);
+            if (j < 8) r[j] = sq;
+            else r[j & 7] = __fadd_rn(r[j & 7], sq);
+        }
+        const float err = __fadd_rn(__fadd_rn(__fadd_rn(r[0], r[1]), __fadd_rn(r[2], r[3])),
+                                    __fadd_rn(__fadd_rn(r[4], r[5]), __fadd_rn(r[6], r[7])));
+        if (a == 0 || err < best_err) { best_err = err; best_lo = lo; best_scale = scale; }
+    }
+
+    // codes of the chosen window, appended LSB-first; a group is GS*bits/8 whole bytes
+    const int64_t qrow = (int64_t)bh * p.q_stride_bh + tok;
+    p.lo[qrow * G + g] = best_lo;
+    p.scale[qrow * G + g] = best_scale;
+    const float rc = __frcp_rn(best_scale);
+    const int group_bytes = GS * p.bits / 8;
+    uint8_t *dst = p.codes + qrow * ((int64_t)p.D * p.bits / 8) + (int64_t)g * group_bytes;
+    uint64_t acc = 0;
+    int nb = 0;
+    if ((group_bytes & 3) == 0) {
+        uint32_t *d32 = reinterpret_cast<uint32_t *>(dst);
+#pragma unroll
+        for (int j = 0; j < GS; ++j) {
+            const float cm = code_plus_magic<EXACT_DIV>(v[j], best_lo, best_scale, rc, levels);
+            acc |= (uint64_t)(__float_as_uint(cm) & 0xFFu) << nb;   // (the code: low mantissa bits of code + 1.5 * 2^23)
+            nb += p.bits;
+            if (nb >= 32) { *d32++ = (uint32_t)acc; acc >>= 32; nb -= 32; }
+        }
+    } else {
+#pragma unroll
+        for (int j = 0; j < GS; ++j) {
+            const float cm = code_plus_magic<EXACT_DIV>(v[j], best_lo, best_scale, rc, levels);
+            acc |= (uint64_t)(__float_as_uint(cm) & 0xFFu) << nb;   // (the code: low mantissa bits of code + 1.5 * 2^23)
+            nb += p.bits;
+            while (nb >= 8) { *dst++ = (uint8_t)acc; acc >>= 8; nb -= 8; }
+        }
+    }
 }
 
 template <typename T, int GS>
@@ -68,56 +133,10 @@ __global__ void __launch_bounds__(128) skvq_quant_kernel(const QuantParams p) {
     float gmin = v[0], gmax = v[0];
 #pragma unroll
     for (int j = 1; j < GS; ++j) { gmin = fminf(gmin, v[j]); gmax = fmaxf(gmax, v[j]); }
-    const float mid = __fmul_rn(__fadd_rn(gmax, gmin), 0.5f);
     const float rng = __fsub_rn(gmax, gmin);
-    const float levels = (float)((1 << p.bits) - 1);
-
-    float best_err = 0.f, best_lo = 0.f, best_scale = 0.f;
-    for (int a = 0; a < p.n_alphas; ++a) {
-        const float ar = __fmul_rn(p.alphas[a], rng);
-        const float lo = __fsub_rn(mid, __fmul_rn(ar, 0.5f));
-        const float scale = fmaxf(__fdiv_rn(ar, levels), kEps);
-        if (p.n_alphas == 1) { best_lo = lo; best_scale = scale; break; }
-        const float rc = __frcp_rn(scale);
-        float r[8];
-#pragma unroll
-        for (int j = 0; j < GS; ++j) {
-            const float c = code_of(v[j], lo, scale, rc, levels);
-            const float e = __fsub_rn(__fadd_rn(__fmul_rn(c, scale), lo), v[j]);
-            const float sq = __fmul_rn(e, e);
-            if (j < 8) r[j] = sq;
-            else r[j & 7] = __fadd_rn(r[j & 7], sq);
-        }
-        const float err = __fadd_rn(__fadd_rn(__fadd_rn(r[0], r[1]), __fadd_rn(r[2], r[3])),
-                                    __fadd_rn(__fadd_rn(r[4], r[5]), __fadd_rn(r[6], r[7])));
-        if (a == 0 || err < best_err) { best_err = err; best_lo = lo; best_scale = scale; }
-    }
-
-    // codes of the chosen window, appended LSB-first; a group is GS*bits/8 whole bytes
-    const int64_t qrow = (int64_t)bh * p.q_stride_bh + tok;
-    p.lo[qrow * G + g] = best_lo;
-    p.scale[qrow * G + g] = best_scale;
-    const float rc = __frcp_rn(best_scale);
-    const int group_bytes = GS * p.bits / 8;
-    uint8_t *dst = p.codes + qrow * ((int64_t)p.D * p.bits / 8) + (int64_t)g * group_bytes;
-    uint64_t acc = 0;
-    int nb = 0;
-    if ((group_bytes & 3) == 0) {
-        uint32_t *d32 = reinterpret_cast<uint32_t *>(dst);
-#pragma unroll
-        for (int j = 0; j < GS; ++j) {
-            acc |= (uint64_t)(uint32_t)code_of(v[j], best_lo, best_scale, rc, levels) << nb;
-            nb += p.bits;
-            if (nb >= 32) { *d32++ = (uint32_t)acc; acc >>= 32; nb -= 32; }
-        }
-    } else {
-#pragma unroll
-        for (int j = 0; j < GS; ++j) {
-            acc |= (uint64_t)(uint32_t)code_of(v[j], best_lo, best_scale, rc, levels) << nb;
-            nb += p.bits;
-            while (nb >= 8) { *dst++ = (uint8_t)acc; acc >>= 8; nb -= 8; }
-        }
-    }
+    // (a range of 1e30 or more, or NaN: the quotients may leave the finite range; plain divides)
+    if (rng < 1e30f) quantize_group<GS, false>(p, v, gmin, gmax, rng, bh, tok, g, G);
+    else quantize_group<GS, true>(p, v, gmin, gmax, rng, bh, tok, g, G);
 }
 
 struct DequantParams {
@@ -153,112 +172,159 @@ __global__ void __launch_bounds__(256) skvq_dequant_kernel(const DequantParams p
 // owns a token row. Its lanes load the row's packed words (at most 64) and its (lo, scale) pairs
 // once, coalesced; every lane then picks the codes of its CPL consecutive OUTPUT channels out of
 // the other lanes' registers by shuffle -- which is also the inverse channel gather -- and stores
-// them as one vector. Eight rows per warp are in flight. blockIdx.y = (batch, head) block, so the
+// them as one vector. Four rows per warp are in flight (eight measured slower: fewer resident warps). blockIdx.y = (batch, head) block, so the
 // head's permutation entries are loaded once per thread.
 // float(c) for 0 <= c < 2^23 without the conversion unit: c in the mantissa of 2^23, minus 2^23 (exact)
 __device__ __forceinline__ float small_uint_as_float(uint32_t c) { return __fsub_rn(__uint_as_float(0x4B000000u | c), 8388608.0f); }
 
-constexpr int kDqWarps = 4, kDqRowsPerWarp = 16;
+constexpr int kDqWarps = 4, kDqRowsPerWarp = 8;
+
+__device__ __forceinline__ uint32_t bit_field(uint32_t w, int pos, int len) {
+    uint32_t r;
+    asm("bfe.u32 %0, %1, %2, %3;" : "=r"(r) : "r"(w), "r"(pos), "r"(len));
+    return r;
+}
 
 template <typename T, int CPL>
+__device__ __forceinline__ void store_row_piece(T *dst, const float (&v)[CPL]) {
+    if constexpr (sizeof(T) == 4) {
+#pragma unroll
+        for (int i = 0; i < CPL; i += 4) *reinterpret_cast<float4 *>(dst + i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+    } else {
+        uint32_t pk[CPL / 2];
+#pragma unroll
+        for (int i = 0; i < CPL / 2; ++i) {
+            if constexpr (sizeof(T) == 2 && std::is_same<T, __half>::value) {
+                const __half2 h = __floats2half2_rn(v[2 * i], v[2 * i + 1]);
+                pk[i] = *reinterpret_cast<const uint32_t *>(&h);
+            } else {
+                const __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+                pk[i] = *reinterpret_cast<const uint32_t *>(&h);
+            }
+        }
+        if constexpr (CPL == 2) *reinterpret_cast<uint32_t *>(dst) = pk[0];
+        else if constexpr (CPL == 4) *reinterpret_cast<uint2 *>(dst) = make_uint2(pk[0], pk[1]);
+        else *reinterpret_cast<uint4 *>(dst) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+    }
+}
+
+// ONE_WORD: no permutation and a lane's CPL codes inside one packed word (1, 2, 4 bits; 8 while
+// CPL <= 4): one word shuffle and one (lo, scale) shuffle pair per row. Otherwise every code is
+// fetched by its own shuffles (two words where a code may straddle: 3, 5, 6, 7 bits; a second
+// register where the row has more than 32 words).
+// GATHER (with ONE_WORD): a permutation is undone through shared memory -- the row is decoded in
+// stored order, rounded to the output type, parked in the warp's slice, and every lane picks its
+// output channels from there (four 2- or 4-byte reads instead of three shuffles per code).
+template <typename T, int CPL, bool ONE_WORD, bool GATHER>
 __global__ void __launch_bounds__(kDqWarps * 32) skvq_dequant_rows_kernel(const DequantParams p) {
+    __shared__ __align__(16) T park[GATHER ? kDqWarps * 32 * CPL : 1];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int bh = blockIdx.y;
-    const int D = 32 * CPL;
+    constexpr int D = 32 * CPL;
     const int G = D / p.gs;
     const int n_words = D * p.bits / 32;   // <= 64
-    const uint32_t mask = (1u << p.bits) - 1u;
-    const bool wide = n_words > 32, straddle = (p.bits & (p.bits - 1)) != 0;  // a code crosses words only at 3, 5, 6, 7 bits
-    // without a permutation and at 1, 2, 4 bits (8 too while a lane's codes fit one word) a lane's CPL
-    // codes share one packed word and one group: three shuffles per row instead of three per code
-    const bool same = p.inv_perm == nullptr && !straddle && CPL * p.bits <= 32;
+    const bool wide = n_words > 32, straddle = (p.bits & (p.bits - 1)) != 0;
     int bit[CPL], grp[CPL];
 #pragma unroll
     for (int i = 0; i < CPL; ++i) {
         const int c = lane * CPL + i;
-        const int j = p.inv_perm ? __ldg(p.inv_perm + (int64_t)(bh % p.n_heads) * D + c) : c;
+        const int j = (!ONE_WORD && p.inv_perm) ? __ldg(p.inv_perm + (int64_t)(bh % p.n_heads) * D + c) : c;
         bit[i] = j * p.bits;
         grp[i] = j / p.gs;
     }
+    int from[CPL];  // GATHER: stored channel of each of this lane's output channels
+#pragma unroll
+    for (int i = 0; i < CPL; ++i) from[i] = GATHER ? __ldg(p.inv_perm + (int64_t)(bh % p.n_heads) * D + lane * CPL + i) : 0;
+    T *mine = park + (GATHER ? warp * 32 * CPL : 0);
     const int tok0 = (blockIdx.x * kDqWarps + warp) * kDqRowsPerWarp;
-    T *out = reinterpret_cast<T *>(p.out) + (int64_t)bh * p.out_stride_bh;
-    constexpr int R = 8;  // rows in flight
-    for (int t0 = tok0; t0 < min(tok0 + kDqRowsPerWarp, p.n_tok); t0 += R) {
+    const int64_t q0 = (int64_t)bh * p.q_stride_bh;
+    const uint32_t *codes = reinterpret_cast<const uint32_t *>(p.codes) + q0 * n_words + lane;
+    const float *lo_p = p.lo + q0 * G + lane, *sc_p = p.scale + q0 * G + lane;
+    T *out = reinterpret_cast<T *>(p.out) + (int64_t)bh * p.out_stride_bh + lane * CPL;
+    const bool has_w0 = lane < n_words, has_w1 = lane + 32 < n_words, has_g = lane < G;
+    constexpr int R = 4;  // rows in flight
+    const int t_end = min(tok0 + kDqRowsPerWarp, p.n_tok);
+    for (int t0 = tok0; t0 < t_end; t0 += R) {
         uint32_t w0[R], w1[R];
         float lo[R], sc[R];
 #pragma unroll
         for (int r = 0; r < R; ++r) {
             const int tok = min(t0 + r, p.n_tok - 1);
-            const int64_t qrow = (int64_t)bh * p.q_stride_bh + tok;
-            const uint32_t *src = reinterpret_cast<const uint32_t *>(p.codes + qrow * ((int64_t)n_words * 4));
-            w0[r] = lane < n_words ? __ldg(src + lane) : 0u;
-            w1[r] = lane + 32 < n_words ? __ldg(src + lane + 32) : 0u;
-            lo[r] = lane < G ? __ldg(p.lo + qrow * G + lane) : 0.f;
-            sc[r] = lane < G ? __ldg(p.scale + qrow * G + lane) : 0.f;
+            w0[r] = has_w0 ? __ldg(codes + tok * n_words) : 0u;
+            w1[r] = (!ONE_WORD && has_w1) ? __ldg(codes + tok * n_words + 32) : 0u;
+            lo[r] = has_g ? __ldg(lo_p + tok * G) : 0.f;
+            sc[r] = has_g ? __ldg(sc_p + tok * G) : 0.f;
         }
 #pragma unroll
         for (int r = 0; r < R; ++r) {
             float v[CPL];
-            uint32_t w_same = 0u;
-            float l_same = 0.f, s_same = 0.f;
-            if (same) {
-                w_same = __shfl_sync(0xffffffffu, w0[r], bit[0] >> 5);
-                l_same = __shfl_sync(0xffffffffu, lo[r], grp[0]);
-                s_same = __shfl_sync(0xffffffffu, sc[r], grp[0]);
-            }
+            if constexpr (ONE_WORD) {
+                const uint32_t w = __shfl_sync(0xffffffffu, w0[r], bit[0] >> 5);
+                const float l = __shfl_sync(0xffffffffu, lo[r], grp[0]), sc1 = __shfl_sync(0xffffffffu, sc[r], grp[0]);
 #pragma unroll
-            for (int i = 0; i < CPL; ++i) {
-                if (same) {
-                    v[i] = __fadd_rn(__fmul_rn(small_uint_as_float((w_same >> (bit[i] & 31)) & mask), s_same), l_same);
-                    continue;
-                }
-                const int wi = bit[i] >> 5, sh = bit[i] & 31;
-                // (64-bit window over words wi and wi + 1: a code may straddle two words)
-                // (the second register and the next word only where the shape needs them: warp-uniform)
-                uint32_t wlo = __shfl_sync(0xffffffffu, w0[r], wi & 31), whi = 0u;
-                if (wide) {
-                    const uint32_t a1 = __shfl_sync(0xffffffffu, w1[r], wi & 31);
-                    wlo = wi < 32 ? wlo : a1;
-                }
-                if (straddle) {
-                    whi = __shfl_sync(0xffffffffu, w0[r], (wi + 1) & 31);
+                for (int i = 0; i < CPL; ++i)
+                    v[i] = __fadd_rn(__fmul_rn(small_uint_as_float(bit_field(w, (bit[0] & 31) + i * p.bits, p.bits)), sc1), l);
+            } else {
+#pragma unroll
+                for (int i = 0; i < CPL; ++i) {
+                    const int wi = bit[i] >> 5, sh = bit[i] & 31;
+                    uint32_t wlo = __shfl_sync(0xffffffffu, w0[r], wi & 31), whi = 0u;
                     if (wide) {
-                        const uint32_t b1 = __shfl_sync(0xffffffffu, w1[r], (wi + 1) & 31);
-                        whi = wi + 1 < 32 ? whi : b1;
+                        const uint32_t a1 = __shfl_sync(0xffffffffu, w1[r], wi & 31);
+                        wlo = wi < 32 ? wlo : a1;
                     }
+                    if (straddle) {
+                        whi = __shfl_sync(0xffffffffu, w0[r], (wi + 1) & 31);
+                        if (wide) {
+                            const uint32_t b1 = __shfl_sync(0xffffffffu, w1[r], (wi + 1) & 31);
+                            whi = wi + 1 < 32 ? whi : b1;
+                        }
+                    }
+                    const uint32_t code = bit_field(__funnelshift_r(wlo, whi, sh), 0, p.bits);
+                    const float l = __shfl_sync(0xffffffffu, lo[r], grp[i]), sc1 = __shfl_sync(0xffffffffu, sc[r], grp[i]);
+                    v[i] = __fadd_rn(__fmul_rn(small_uint_as_float(code), sc1), l);
                 }
-                const uint32_t code = (uint32_t)((((uint64_t)whi << 32) | wlo) >> sh) & mask;
-                const float l = __shfl_sync(0xffffffffu, lo[r], grp[i]), s = __shfl_sync(0xffffffffu, sc[r], grp[i]);
-                v[i] = __fadd_rn(__fmul_rn(small_uint_as_float(code), s), l);
             }
-            if (t0 + r < p.n_tok) {
-                T *dst = out + (int64_t)(t0 + r) * D + lane * CPL;
-                if constexpr (sizeof(T) == 4) {
+            if constexpr (GATHER) {
+                __syncwarp();  // the previous row's reads are done
+                store_row_piece<T, CPL>(mine + lane * CPL, v);
+                __syncwarp();
+                __align__(16) T g[CPL];
 #pragma unroll
-                    for (int i = 0; i < CPL; i += 4) *reinterpret_cast<float4 *>(dst + i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
-                } else {
-                    uint32_t pk[CPL / 2];
+                for (int i = 0; i < CPL; ++i) g[i] = mine[from[i]];
+                if (t0 + r < p.n_tok) {
+                    T *dst = out + (int64_t)(t0 + r) * D;
+                    if constexpr (sizeof(T) * CPL == 4) *reinterpret_cast<uint32_t *>(dst) = *reinterpret_cast<const uint32_t *>(g);
+                    else if constexpr (sizeof(T) * CPL == 8) *reinterpret_cast<uint2 *>(dst) = *reinterpret_cast<const uint2 *>(g);
+                    else {
 #pragma unroll
-                    for (int i = 0; i < CPL / 2; ++i) {
-                        const T a = from_f32<T>(v[2 * i]), b = from_f32<T>(v[2 * i + 1]);
-                        pk[i] = (uint32_t)*reinterpret_cast<const uint16_t *>(&a) | ((uint32_t)*reinterpret_cast<const uint16_t *>(&b) << 16);
+                        for (int i = 0; i < (int)(sizeof(T) * CPL / 16); ++i)
+                            reinterpret_cast<uint4 *>(dst)[i] = reinterpret_cast<const uint4 *>(g)[i];
                     }
-                    if constexpr (CPL == 2) *reinterpret_cast<uint32_t *>(dst) = pk[0];
-                    else if constexpr (CPL == 4) *reinterpret_cast<uint2 *>(dst) = make_uint2(pk[0], pk[1]);
-                    else *reinterpret_cast<uint4 *>(dst) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
                 }
+            } else {
+                if (t0 + r < p.n_tok) store_row_piece<T, CPL>(out + (int64_t)(t0 + r) * D, v);
             }
         }
     }
+}
+
+template <typename T, int CPL>
+void launch_dequant_rows_cpl(const DequantParams &p, dim3 grid, cudaStream_t st) {
+    const bool pow2 = (p.bits & (p.bits - 1)) == 0;
+    const bool one_word = pow2 && CPL * p.bits <= 32;
+    if (one_word && p.inv_perm == nullptr) skvq_dequant_rows_kernel<T, CPL, true, false><<<grid, kDqWarps * 32, 0, st>>>(p);
+    else if (one_word) skvq_dequant_rows_kernel<T, CPL, true, true><<<grid, kDqWarps * 32, 0, st>>>(p);
+    else skvq_dequant_rows_kernel<T, CPL, false, false><<<grid, kDqWarps * 32, 0, st>>>(p);
 }
 
 template <typename T>
 int32_t launch_dequant_rows(const DequantParams &p, cudaStream_t st) {
     dim3 grid((unsigned)ceil_div(p.n_tok, kDqWarps * kDqRowsPerWarp), (unsigned)p.n_bh);
     switch (p.D / 32) {
-        case 2: skvq_dequant_rows_kernel<T, 2><<<grid, kDqWarps * 32, 0, st>>>(p); break;
-        case 4: skvq_dequant_rows_kernel<T, 4><<<grid, kDqWarps * 32, 0, st>>>(p); break;
-        default: skvq_dequant_rows_kernel<T, 8><<<grid, kDqWarps * 32, 0, st>>>(p); break;
+        case 2: launch_dequant_rows_cpl<T, 2>(p, grid, st); break;
+        case 4: launch_dequant_rows_cpl<T, 4>(p, grid, st); break;
+        default: launch_dequant_rows_cpl<T, 8>(p, grid, st); break;
     }
     VQ_CHECK_LAUNCH("skvq_dequant_rows_kernel");
     return VQ_OK;
