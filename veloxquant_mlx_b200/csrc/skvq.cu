@@ -44,6 +44,27 @@ __device__ __forceinline__ float code_plus_magic(float v, float lo, float scale,
     return __fadd_rn(fminf(fmaxf(q, 0.0f), levels), kMagic);
 }
 
+// 1, 2, 4, 8 bits with whole words per group: 32/BITS codes fill a word exactly. The float bits
+// (0x4B400000 + code) are shift-added as they are (compile-time shifts); the exponent bits that
+// rode along sum to a constant that is taken off once per word (all modulo 2^32).
+template <int GS, int BITS, bool EXACT_DIV>
+__device__ __forceinline__ void pack_pow2(const float (&v)[GS], float lo, float scale, float rc, float levels, uint32_t *d32) {
+    constexpr int PER = 32 / BITS;
+    if constexpr (GS % PER == 0) {
+        uint32_t ride = 0;
+#pragma unroll
+        for (int k = 0; k < PER; ++k) ride += 0x4B400000u << (k * BITS);
+#pragma unroll
+        for (int j0 = 0; j0 < GS; j0 += PER) {
+            uint32_t w = 0;
+#pragma unroll
+            for (int k = 0; k < PER; ++k)
+                w += __float_as_uint(code_plus_magic<EXACT_DIV>(v[j0 + k], lo, scale, rc, levels)) << (k * BITS);
+            *d32++ = w - ride;
+        }
+    }
+}
+
 // The search and the packing of one group whose values, minimum, maximum and range are known.
 template <int GS, bool EXACT_DIV>
 __device__ __forceinline__ void quantize_group(const QuantParams &p, const float (&v)[GS], float gmin, float gmax, float rng,
@@ -81,7 +102,15 @@ __device__ __forceinline__ void quantize_group(const QuantParams &p, const float
     uint8_t *dst = p.codes + qrow * ((int64_t)p.D * p.bits / 8) + (int64_t)g * group_bytes;
     uint64_t acc = 0;
     int nb = 0;
-    if ((group_bytes & 3) == 0) {
+    if ((group_bytes & 3) == 0 && (p.bits & (p.bits - 1)) == 0) {
+        uint32_t *d32 = reinterpret_cast<uint32_t *>(dst);
+        switch (p.bits) {
+            case 1: pack_pow2<GS, 1, EXACT_DIV>(v, best_lo, best_scale, rc, levels, d32); break;
+            case 2: pack_pow2<GS, 2, EXACT_DIV>(v, best_lo, best_scale, rc, levels, d32); break;
+            case 4: pack_pow2<GS, 4, EXACT_DIV>(v, best_lo, best_scale, rc, levels, d32); break;
+            default: pack_pow2<GS, 8, EXACT_DIV>(v, best_lo, best_scale, rc, levels, d32); break;
+        }
+    } else if ((group_bytes & 3) == 0) {
         uint32_t *d32 = reinterpret_cast<uint32_t *>(dst);
 #pragma unroll
         for (int j = 0; j < GS; ++j) {
