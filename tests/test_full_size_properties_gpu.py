@@ -154,3 +154,47 @@ def test_full_size_rabitq_config4_properties():
     assert torch.equal(out2[0], out2[B - 1])
     from veloxquant_mlx_b200._lib import lib
     assert lib().vq_kivi_attend_status() == 0
+
+
+def test_full_size_skvq_properties():
+    """1 Mi rows of 128 channels (a 16K-token prefill of 64 (batch, head) blocks) through the SKVQ
+    kernels: with one clip factor of 1 every element is reconstructed to within half a step and every
+    group uses both end codes; the searched factor is never worse per group; a permuted round trip
+    equals the plain round trip of the pre-permuted rows; a sample of rows equals the oracle."""
+    from oracle import skvq as o_skvq
+    from veloxquant_mlx_b200 import skvq
+
+    n_bh, n_tok, D, gs, bits = 64, 16384, 128, 32, 4
+    g = torch.Generator(device=DEV).manual_seed(11)
+    x = torch.randn(n_bh, n_tok, D, device=DEV, dtype=torch.float32, generator=g)
+    x[..., [3, 40, 77, 120]] *= 20.0
+    x = x.to(torch.float16)
+    x32 = x.float()
+    packed, lo, scale = skvq.quantize_pack(x, bits, gs, (1.0,))
+    rt1 = skvq.unpack_dequant(packed, lo, scale, bits, gs, n_tok, torch.float32)
+    step = scale.repeat_interleave(gs, dim=-1)
+    assert bool(((rt1 - x32).abs() <= 0.5 * step * (1 + 1e-5) + 1e-6).all())
+    codes = skvq.unpack_dequant(packed, torch.zeros_like(lo), torch.ones_like(scale), bits, gs, n_tok, torch.float32)
+    cg = codes.reshape(n_bh, n_tok, D // gs, gs)
+    assert bool((cg.amin(-1) == 0).all()) and bool((cg.amax(-1) == 15).all())
+    e1 = ((rt1 - x32) ** 2).reshape(n_bh, n_tok, D // gs, gs).sum(-1)
+    del rt1, codes, cg, step
+    packed5 = skvq.quantize_pack(x, bits, gs)
+    rt5 = skvq.unpack_dequant(*packed5, bits, gs, n_tok, torch.float32)
+    e5 = ((rt5 - x32) ** 2).reshape(n_bh, n_tok, D // gs, gs).sum(-1)
+    assert bool((e5 <= e1 * (1 + 1e-5) + 1e-9).all()) and float(e5.sum()) < float(e1.sum())
+    del e1, e5, rt5
+    perm = torch.stack([torch.randperm(D, generator=torch.Generator().manual_seed(h)) for h in range(8)]).to(torch.int32).to(DEV)
+    inv = torch.argsort(perm.long(), dim=-1).to(torch.int32)
+    pp = skvq.quantize_pack(x, bits, gs, perm=perm)
+    a = skvq.unpack_dequant(*pp, bits, gs, n_tok, torch.float16, inv_perm=inv)
+    xp = torch.gather(x, 2, perm.long()[torch.arange(n_bh, device=DEV) % 8][:, None, :].expand(n_bh, n_tok, D))
+    b = skvq.unpack_dequant(*skvq.quantize_pack(xp, bits, gs), bits, gs, n_tok, torch.float16)
+    b = torch.gather(b, 2, inv.long()[torch.arange(n_bh, device=DEV) % 8][:, None, :].expand(n_bh, n_tok, D))
+    assert torch.equal(a, b)
+    rows = x[5::16, 100::4000].reshape(-1, D).cpu().numpy()
+    oc, olo, osc = o_skvq.clipped_group_quant(rows, bits, gs)
+    got = tuple(t[5::16, 100::4000] for t in packed5)
+    np.testing.assert_array_equal(got[0].reshape(-1, D * bits // 8).cpu().numpy(), o_bp.pack(oc, bits))
+    np.testing.assert_array_equal(got[1].reshape(-1, D // gs).cpu().numpy(), olo)
+    np.testing.assert_array_equal(got[2].reshape(-1, D // gs).cpu().numpy(), osc)
