@@ -30,6 +30,9 @@ What is executed from the reference, unmodified:
   -- answered by NumPy in float32): the file's own arithmetic runs unmodified; what the stand-in
   decides is the order of the error mean and ``round``'s tie rule (NumPy's).
 
+* ``quantizers/_quant_utils.py``, ``quantizers/kitty.py`` and ``quantizers/age_tiered.py`` are loaded
+  whole over the same stand-in (``_quant_utils`` registered under its package path first).
+
 Nothing here imports the oracle: the fixtures are the reference's outputs and
 the oracle is checked against them by ``tests/test_oracle_golden.py``.
 """
@@ -50,6 +53,8 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 def load_module(path: str, name: str):
     spec = importlib.util.spec_from_file_location(name, path)
     mod = importlib.util.module_from_spec(spec)
+    import sys
+    sys.modules[name] = mod   # (dataclasses look their module up while the body runs)
     spec.loader.exec_module(mod)
     return mod
 
@@ -237,6 +242,48 @@ def main():
     out["bytes"] = np.asarray([skvq.skvq_compressed_bytes(123, 128, 4, 32), skvq.skvq_compressed_bytes(11, 64, 3, 16),
                                skvq.skvq_fp16_bytes(77, 128)])
     np.savez_compressed(os.path.join(HERE, "skvq.npz"), **out)
+
+    # ------- shared group-quant core, Kitty and AgeTiered quantizers (whole modules over the same stand-in) -------
+    saved = {k: sys.modules.get(k) for k in ("mlx", "mlx.core", "veloxquant_mlx.quantizers", "veloxquant_mlx.quantizers._quant_utils")}
+    sys.modules["mlx"], sys.modules["mlx.core"] = mlx_pkg, mlx_pkg.core
+    try:
+        qu = load_module(os.path.join(pkg, "quantizers", "_quant_utils.py"), "veloxquant_mlx.quantizers._quant_utils")
+        sys.modules.setdefault("veloxquant_mlx.quantizers", types.ModuleType("veloxquant_mlx.quantizers"))
+        sys.modules["veloxquant_mlx.quantizers._quant_utils"] = qu
+        kitty = load_module(os.path.join(pkg, "quantizers", "kitty.py"), "ref_kitty")
+        age = load_module(os.path.join(pkg, "quantizers", "age_tiered.py"), "ref_age_tiered")
+    finally:
+        for k, v in saved.items():
+            if v is None:
+                sys.modules.pop(k, None)
+            else:
+                sys.modules[k] = v
+    out = {}
+    rng = np.random.default_rng(256)
+    for tag, n, s_len, d, b, gs, dt in [("a", 3, 70, 32, 2, 32, np.float16), ("b", 2, 64, 128, 4, 32, np.float16),
+                                        ("c", 4, 5, 16, 8, 8, np.float32), ("d", 1, 33, 64, 3, 16, np.float16)]:
+        x = (rng.standard_normal((n, s_len, d)) * np.logspace(-1, 1, d)[None, None, :]).astype(dt)
+        codes, scale, zero = qu._group_quant_codes_batched(x, b, gs)
+        out[f"gq_{tag}_x"], out[f"gq_{tag}_meta"] = x, np.asarray([b, gs])
+        out[f"gq_{tag}_codes"], out[f"gq_{tag}_scale"], out[f"gq_{tag}_zero"] = np.asarray(codes), np.asarray(scale), np.asarray(zero)
+        out[f"gq_{tag}_rt"] = np.asarray(qu._group_quant_dequant_batched(x, b, gs))
+    # Kitty: channel ranking and the mixed-precision round trip (per-row masks)
+    kx = (rng.standard_normal((6, 96, 64)) * rng.permutation(np.logspace(-1, 1, 64))[None, None, :]).astype(np.float16)
+    var = np.var(kx.astype(np.float32), axis=1)
+    mask = kitty.hi_mask_from_variance_batched(var, 0.25)
+    out["kitty_x"], out["kitty_var"], out["kitty_mask"] = kx, var, np.asarray(mask)
+    out["kitty_out"] = np.asarray(kitty.quantize_mixed_channels_batched(kx, mask, hi_bit=4, lo_bit=2, group_size=32))
+    out["kitty_running_var"] = np.asarray(kitty.compute_running_variance(kx.astype(np.float32).sum(1)[0], (kx.astype(np.float32) ** 2).sum(1)[0], 96))
+    # AgeTiered: three tiers over position-aligned groups, last group ragged
+    ax = rng.standard_normal((4, 200, 32)).astype(np.float16)
+    tiers = age.default_age_tiers(8, 4, 2)
+    ages = [200 - (i + 1) for i in range(200)]
+    tok_tier = age.assign_age_tiers(ages, 40, 120)
+    group_tier = [tok_tier[g * 32] for g in range(7)]
+    out["age_x"], out["age_tok_tier"], out["age_group_tier"] = ax, np.asarray(tok_tier), np.asarray(group_tier)
+    out["age_out"] = np.asarray(age.age_tier_quantize_batched(ax, group_tier, tiers, 32))
+    out["age_bytes"] = np.asarray([age.age_tiered_bytes({age.RECENT: 40, age.MID: 80, age.OLD: 80}, tiers, 32), age.full_fp16_bytes(200, 32)])
+    np.savez_compressed(os.path.join(HERE, "group_quant.npz"), **out)
     print("golden fixtures written to", HERE)
 
 
@@ -256,6 +303,10 @@ def _mx_numpy_module():
     m.argmin = lambda a, axis=None: np.argmin(a, axis=axis)
     m.argsort = lambda a, axis=-1: np.argsort(a, axis=axis, kind="stable")
     m.broadcast_to, m.take_along_axis, m.concatenate, m.take = np.broadcast_to, np.take_along_axis, np.concatenate, np.take
+    m.var = lambda a, axis=None, keepdims=False: np.var(a, axis=axis, keepdims=keepdims)
+    m.sum = lambda a, axis=None, keepdims=False: np.sum(a, axis=axis, keepdims=keepdims)
+    m.where, m.stack, m.zeros_like, m.arange = np.where, np.stack, np.zeros_like, np.arange
+    m.eval = lambda *a: None
     return m
 
 

@@ -261,3 +261,30 @@ def test_skvq_oracle_properties_of_the_reference_tests():
         return ((r - x) ** 2).reshape(128, 4, 8).mean(-1)
 
     assert np.all(per_group_mse(skvq.DEFAULT_ALPHA_GRID) <= per_group_mse((1.0,)) + 1e-9)
+
+
+def test_group_quant_core_kitty_and_age_tiered_oracles_match_the_reference_modules_run_over_numpy():
+    """``oracle.kivi.quant_keys`` / ``dequant_keys`` against ``quantizers/_quant_utils.py``, and
+    ``oracle.kitty`` / ``oracle.age_tiered`` against ``quantizers/kitty.py`` / ``age_tiered.py``, all
+    executed whole with NumPy standing in for ``mlx.core`` (make_golden.py), bit for bit."""
+    from oracle import age_tiered, kitty
+
+    z = _load("group_quant.npz")
+    for tag in "abcd":
+        x = z[f"gq_{tag}_x"]
+        b, gs = (int(v) for v in z[f"gq_{tag}_meta"])
+        N, S, D = x.shape
+        ng = -(-S // gs)
+        c, s, zz = kivi.quant_keys(x.astype(np.float32)[None], gs, (1 << b) - 1)
+        assert np.array_equal(c[0].astype(np.float32), z[f"gq_{tag}_codes"].reshape(N, ng * gs, D)[:, :S])
+        assert np.array_equal(s[0].reshape(N, ng, 1, D), z[f"gq_{tag}_scale"])
+        assert np.array_equal(zz[0].reshape(N, ng, 1, D), z[f"gq_{tag}_zero"])
+        assert np.array_equal(kitty.group_quant_dequant_batched(x, b, gs), z[f"gq_{tag}_rt"])
+    mask = kitty.hi_mask_from_variance_batched(z["kitty_var"], 0.25)
+    assert np.array_equal(mask, z["kitty_mask"]) and int(mask.sum(1)[0]) == 16
+    assert np.array_equal(kitty.quantize_mixed_channels_batched(z["kitty_x"], mask), z["kitty_out"])
+    kx = z["kitty_x"].astype(np.float32)
+    assert np.array_equal(kitty.compute_running_variance(kx.sum(1)[0], (kx ** 2).sum(1)[0], 96), z["kitty_running_var"])
+    assert np.array_equal(age_tiered.assign_age_tiers([200 - (i + 1) for i in range(200)], 40, 120), z["age_tok_tier"])
+    assert np.array_equal(age_tiered.age_tier_quantize_batched(z["age_x"], list(z["age_group_tier"]), (8, 4, 2), 32), z["age_out"])
+    assert [age_tiered.age_tiered_bytes({0: 40, 1: 80, 2: 80}, (8, 4, 2), 32), age_tiered.full_fp16_bytes(200, 32)] == list(z["age_bytes"])

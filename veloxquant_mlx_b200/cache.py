@@ -68,12 +68,37 @@ class SKVQOptions:
     skvq_max_ctx: Any = None
 
 
+@dataclass
+class KittyOptions:
+    """Kitty configuration (reference: ``cache/options.py:67-73``)."""
+
+    kitty_hi_fraction: float = 0.25
+    kitty_hi_bit: int = 4
+    kitty_lo_bit: int = 2
+    kitty_group_size: int = 32
+
+
+@dataclass
+class AgeTieredKVOptions:
+    """AgeTieredKV configuration (reference: ``cache/options.py:496-505``)."""
+
+    age_recent_boundary: int = 128
+    age_mid_boundary: int = 1024
+    age_bits_recent: int = 8
+    age_bits_mid: int = 4
+    age_bits_old: int = 2
+    age_group_size: int = 32
+
+
 _FIELD_TO_OPTIONS_CLASS = {
     "key_sub_dim": "VecInferOptions", "value_sub_dim": "VecInferOptions",
     "key_codebook_bits": "VecInferOptions", "value_codebook_bits": "VecInferOptions",
     "residual_length": "VecInferOptions", "kivi_group_size": "KIVIOptions",
     **{name: "SKVQOptions" for name in ("skvq_bits_key", "skvq_bits_value", "skvq_group_size", "skvq_window", "skvq_n_sink",
                                         "skvq_reorder", "skvq_clip_search", "skvq_clip_alpha", "skvq_max_ctx")},
+    **{name: "KittyOptions" for name in ("kitty_hi_fraction", "kitty_hi_bit", "kitty_lo_bit", "kitty_group_size")},
+    **{name: "AgeTieredKVOptions" for name in ("age_recent_boundary", "age_mid_boundary", "age_bits_recent", "age_bits_mid",
+                                             "age_bits_old", "age_group_size")},
 }
 
 _CACHE_CLASS_BY_METHOD: dict = {}  # filled at the bottom of the module
@@ -121,6 +146,16 @@ class KVCacheConfig:
     skvq_clip_search: bool = True
     skvq_clip_alpha: float = 1.0
     skvq_max_ctx: Any = None
+    kitty_hi_fraction: float = 0.25
+    kitty_hi_bit: int = 4
+    kitty_lo_bit: int = 2
+    kitty_group_size: int = 32
+    age_recent_boundary: int = 128
+    age_mid_boundary: int = 1024
+    age_bits_recent: int = 8
+    age_bits_mid: int = 4
+    age_bits_old: int = 2
+    age_group_size: int = 32
 
     def __repr__(self) -> str:
         return (f"KVCacheConfig(method={self.method!r}, d={self.head_dim}, "
@@ -855,7 +890,9 @@ from .cache_coded import RaBitQKVCache, VecInferKVCache  # noqa: E402  (register
 from .cache_sink import SinkProtectedKVCache  # noqa: E402  (registers "kivi_sink")
 from .cache_rvq import TurboQuantRVQKVCache  # noqa: E402  (registers "turboquant_rvq")
 from .cache_skvq import SKVQKVCache  # noqa: E402  (registers "skvq")
+from .cache_kitty import AgeTieredKVCache, KittyKVCache  # noqa: E402  (registers "kitty", "age_tiered")
 
 __all__ = ["QuantizerConfigError", "VecInferOptions", "KIVIOptions", "SKVQOptions", "KVCacheConfig", "KVCacheFactory",
-           "KVCacheBuilder", "KIVIKVCache", "SinkProtectedKVCache", "TurboQuantRVQKVCache", "SKVQKVCache", "VecInferKVCache",
+           "KVCacheBuilder", "KIVIKVCache", "SinkProtectedKVCache", "TurboQuantRVQKVCache", "SKVQKVCache", "KittyKVCache",
+           "AgeTieredKVCache", "KittyOptions", "AgeTieredKVOptions", "VecInferKVCache",
            "RaBitQKVCache", "KVCache", "EncodedVector"]
