@@ -9,7 +9,9 @@ last row). The reference's splice of unchanged groups (:248-333) returns the sam
 recomputing every group from raw, which is what this model does.
 
 Pinning: ``tests/golden/group_quant.npz`` (the reference's modules executed with a NumPy stand-in
-for ``mlx.core``) pins the quantizer functions; the cache model is a restatement by reading.
+for ``mlx.core``) pins the quantizer functions; the cache model reproduces what the reference's
+``AgeTieredKVCache`` class returns over a call script, executed over the same stand-in and a minimal
+container for its ``mlx_lm`` base class (``tests/golden/cache_traces.npz``).
 """
 
 from __future__ import annotations

@@ -7,9 +7,11 @@ statistics afterwards :86-114, accumulators fed with the stored keys :116-137, b
 :153-167, trim :180-210).
 
 Pinning: ``tests/golden/group_quant.npz`` holds outputs of the reference's modules executed with a
-NumPy stand-in for ``mlx.core``; the quantizer functions here reproduce them bit for bit. The
-cache model is a restatement by reading (the reference's cache needs ``mlx_lm``); its variance
-and accumulator sums are float32 NumPy reductions, whose order MLX need not share.
+NumPy stand-in for ``mlx.core``; the quantizer functions here reproduce them bit for bit, and the
+cache model reproduces what the reference's ``KittyKVCache`` class returns over a call script with a
+trim, executed over the same stand-in and a minimal container for its ``mlx_lm`` base class
+(``tests/golden/cache_traces.npz``). Its variance and accumulator sums are float32 NumPy
+reductions, whose order MLX need not share.
 """
 
 from __future__ import annotations
@@ -89,3 +91,29 @@ class KittyCacheModel:
         self.keys = k_store if self.keys is None else np.concatenate([self.keys, k_store], axis=2)
         self.values = values.copy() if self.values is None else np.concatenate([self.values, values], axis=2)
         return self.keys, self.values
+
+    def trim(self, n: int) -> int:
+        """``kitty_cache.py:180-210``: the trimmed rows leave the running statistics and the accounting."""
+        old = self.keys.shape[2] if self.keys is not None else 0
+        trimmed = min(old, max(int(n), 0))
+        if trimmed:
+            gone = self.keys[:, :, old - trimmed:old]
+            B, H = gone.shape[:2]
+            if self.n_keys - trimmed <= 0:
+                self.key_sum = self.key_sq_sum = None
+                self.n_keys = 0
+            else:
+                g32 = np.mean(gone.astype(f32), axis=0)
+                self.key_sum = self.key_sum - np.sum(g32, axis=1)
+                self.key_sq_sum = self.key_sq_sum - np.sum(g32 * g32, axis=1)
+                self.n_keys -= trimmed
+            n_hi = max(1, int(self.D * self.hi_fraction))
+
+            def channel_bytes(n_ch, b):
+                return (math.ceil(trimmed * n_ch * b / 8) + math.ceil(trimmed / self.gs) * n_ch * 2 * 2) * H * B
+
+            self.compressed_key_bytes = max(0, self.compressed_key_bytes - channel_bytes(n_hi, self.hi_bit) - channel_bytes(self.D - n_hi, self.lo_bit))
+            self.fp16_key_bytes = max(0, self.fp16_key_bytes - B * H * trimmed * self.D * 2)
+            self.value_fp16_bytes = max(0, self.value_fp16_bytes - B * H * trimmed * self.D * 2)
+            self.keys, self.values = self.keys[:, :, : old - trimmed], self.values[:, :, : old - trimmed]
+        return trimmed

@@ -13,10 +13,13 @@ A NumPy restatement of ``SinkProtectedKVCache`` (``veloxquant_mlx/cache/sink_cac
 * ``trim`` (``sink_cache.py:192-218``, buffer semantics of ``cache/kivi_cache.py:264-299``): the
   frontier snaps down to a group multiple; candidates at discarded positions are dropped.
 
-Parity unpinned: the reference class runs on MLX only and holds no golden vectors; what pins this
-file is (a) the group quantizer it calls (``oracle.kivi``, pinned), (b) ``n_sink = 0`` being plain
-KIVI, and (c) the properties the reference's own tests assert
-(``veloxquant_mlx/tests/cache/test_sink_cache.py``), restated in ``tests/test_sink_cache_cpu.py``.
+Pinning: ``tests/golden/cache_traces.npz`` holds what the reference's own ``SinkProtectedKVCache``
+and (with ``n_sink = 0``) ``KIVIKVCache`` classes return over a call script with a trim, executed
+unmodified over NumPy stand-ins for ``mlx.core`` and their ``mlx_lm`` base class
+(``tests/golden/make_golden.py``); this model reproduces every recorded tensor, the frontier and the
+sink positions bit for bit (``tests/test_oracle_golden.py``). Also anchored by the properties the
+reference's own tests assert (``veloxquant_mlx/tests/cache/test_sink_cache.py``), restated in
+``tests/test_sink_cache_cpu.py``.
 """
 
 from __future__ import annotations

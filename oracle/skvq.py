@@ -10,8 +10,9 @@ Pinning: ``tests/golden/skvq.npz`` holds outputs of the reference's ``quantizers
 unmodified with a NumPy stand-in for ``mlx.core`` (``tests/golden/make_golden.py``); this file
 reproduces them bit for bit (``tests/test_oracle_golden.py``). What that cannot pin is MLX's own
 order of the 1/group_size error mean and its rounding mode for ``round`` (taken as NumPy's: eight
-strided partial sums and a tree; half to even). The cache model is a restatement by reading (the
-reference's cache needs ``mlx_lm``).
+strided partial sums and a tree; half to even). The cache model reproduces, bit for bit, what the
+reference's ``SKVQKVCache`` class returns when it is executed over the same stand-in and a minimal
+container for its ``mlx_lm`` base class (``tests/golden/cache_traces.npz``).
 
 All arithmetic is float32 with every product and sum rounded separately.
 """

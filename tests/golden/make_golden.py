@@ -284,7 +284,113 @@ def main():
     out["age_out"] = np.asarray(age.age_tier_quantize_batched(ax, group_tier, tiers, 32))
     out["age_bytes"] = np.asarray([age.age_tiered_bytes({age.RECENT: 40, age.MID: 80, age.OLD: 80}, tiers, 32), age.full_fp16_bytes(200, 32)])
     np.savez_compressed(os.path.join(HERE, "group_quant.npz"), **out)
+
+    # ------- the cache classes themselves, over the same stand-in plus a minimal container base class -------
+    names = ["mlx", "mlx.core", "mlx_lm", "mlx_lm.models", "mlx_lm.models.cache", "veloxquant_mlx.core.exceptions",
+             "veloxquant_mlx.metal", "veloxquant_mlx.metal.kernels", "veloxquant_mlx.cache", "veloxquant_mlx.cache.kivi_cache",
+             "veloxquant_mlx.quantizers", "veloxquant_mlx.quantizers._quant_utils", "veloxquant_mlx.quantizers.skvq",
+             "veloxquant_mlx.quantizers.kitty", "veloxquant_mlx.quantizers.age_tiered"]
+    saved = {k: sys.modules.get(k) for k in names}
+    try:
+        sys.modules["mlx"], sys.modules["mlx.core"] = mlx_pkg, mlx_pkg.core
+        for name in ("mlx_lm", "mlx_lm.models", "veloxquant_mlx.cache", "veloxquant_mlx.quantizers"):
+            sys.modules[name] = types.ModuleType(name)
+        base = types.ModuleType("mlx_lm.models.cache")
+        base.KVCache = _GrowingKV
+        sys.modules["mlx_lm.models.cache"] = base
+        load_module(os.path.join(pkg, "core", "exceptions.py"), "veloxquant_mlx.core.exceptions")
+        metal = types.ModuleType("veloxquant_mlx.metal")
+        metal.metal_available = lambda: False               # the classes then take their own array path
+        metal_k = types.ModuleType("veloxquant_mlx.metal.kernels")
+        metal_k.kivi_group_quant_dequant = None
+        sys.modules["veloxquant_mlx.metal"], sys.modules["veloxquant_mlx.metal.kernels"] = metal, metal_k
+        for mod in ("_quant_utils", "skvq", "kitty", "age_tiered"):
+            load_module(os.path.join(pkg, "quantizers", mod + ".py"), "veloxquant_mlx.quantizers." + mod)
+        kivi_c = load_module(os.path.join(pkg, "cache", "kivi_cache.py"), "veloxquant_mlx.cache.kivi_cache")
+        sink_c = load_module(os.path.join(pkg, "cache", "sink_cache.py"), "ref_sink_cache")
+        skvq_c = load_module(os.path.join(pkg, "cache", "skvq_cache.py"), "ref_skvq_cache")
+        kitty_c = load_module(os.path.join(pkg, "cache", "kitty_cache.py"), "ref_kitty_cache")
+        age_c = load_module(os.path.join(pkg, "cache", "age_tiered_cache.py"), "ref_age_tiered_cache")
+        out = {}
+        rng = np.random.default_rng(77)
+        B, H, D, T = 2, 2, 32, 120
+        scales = rng.permutation(np.logspace(-1, 1, D))
+        k = (rng.standard_normal((B, H, T, D)) * scales[None, None, None, :]).astype(np.float16)
+        v = rng.standard_normal((B, H, T, D)).astype(np.float16)
+        k[0, :, 3] *= 6.0
+        k[1, :, 17] *= 6.0                                   # one outstanding key norm per sequence (a sink)
+        out["k"], out["v"] = k, v
+        # calls: a prefill, single tokens, a block, a trim (where the class allows it), more tokens
+        script = [("put", 0, 45)] + [("put", t, t + 1) for t in range(45, 75)] + [("put", 75, 90), ("trim", 11, 0)] + \
+                 [("put", t, t + 1) for t in range(79, 100)] + [("put", 100, 120)]
+        out["script"] = np.asarray([[{"put": 0, "trim": 1}[op], a, b] for op, a, b in script])
+
+        def run(tag, cache, counters, trimmable):
+            for i, (op, a, b) in enumerate(script):
+                if op == "trim":
+                    if not trimmable:
+                        continue
+                    assert cache.trim(a) == a
+                    continue
+                ko, vo = cache.update_and_fetch(k[:, :, a:b], v[:, :, a:b])
+                if b - a > 1 or b % 8 == 0 or b == 120:
+                    out[f"{tag}_k_{i}"], out[f"{tag}_v_{i}"] = np.array(ko), np.array(vo)
+                    out[f"{tag}_c_{i}"] = np.asarray([int(getattr(cache, c)) for c in counters], dtype=np.int64)
+
+        cfg = types.SimpleNamespace(head_dim=D, bit_width_inlier=2, kivi_group_size=8, residual_length=16, use_metal_kernels=None,
+                                    n_sink_tokens=2, skvq_bits_key=2, skvq_bits_value=3, skvq_group_size=8, skvq_window=16,
+                                    skvq_n_sink=3, skvq_reorder=True, skvq_clip_search=True, skvq_clip_alpha=1.0, skvq_max_ctx=None,
+                                    kitty_hi_fraction=0.25, kitty_hi_bit=4, kitty_lo_bit=2, kitty_group_size=8,
+                                    age_recent_boundary=20, age_mid_boundary=50, age_bits_recent=8, age_bits_mid=4, age_bits_old=2,
+                                    age_group_size=8)
+        run("kivi", kivi_c.KIVIKVCache(cfg), ["offset", "_n_quantized", "_key_bytes_compressed", "_value_bytes_compressed",
+                                              "_key_bytes_fp16", "_residual_fp16_bytes", "_tokens_seen"], True)
+        sink = sink_c.SinkProtectedKVCache(cfg)
+        run("sink", sink, ["offset", "_n_quantized", "_key_bytes_compressed", "_value_bytes_compressed", "_sink_fp16_bytes",
+                           "_residual_fp16_bytes", "_tokens_seen"], True)
+        out["sink_positions"] = np.asarray([sink.sink_positions_for(0), sink.sink_positions_for(1)])
+        skc = skvq_c.SKVQKVCache(cfg)
+        run("skvq", skc, ["offset", "_q_end", "_compressed_key_bytes", "_compressed_value_bytes", "_fp16_key_bytes",
+                          "residual_fp16_bytes", "perm_bytes"], False)
+        out["skvq_perm_k"], out["skvq_perm_v"] = np.asarray(skc.key_perms), np.asarray(skc.value_perms)
+        run("kitty", kitty_c.KittyKVCache(cfg), ["offset", "_n_keys", "_compressed_key_bytes", "_fp16_key_bytes", "_value_fp16_bytes"], True)
+        run("age", age_c.AgeTieredKVCache(cfg), ["offset", "age_tiered_bytes", "full_seq_bytes", "tokens_recent", "tokens_mid", "tokens_old"], False)
+        np.savez_compressed(os.path.join(HERE, "cache_traces.npz"), **out)
+    finally:
+        for key, val in saved.items():
+            if val is None:
+                sys.modules.pop(key, None)
+            else:
+                sys.modules[key] = val
     print("golden fixtures written to", HERE)
+
+
+class _GrowingKV:
+    """Minimal stand-in for the container class the reference's caches derive from (``mlx_lm``'s
+    ``KVCache``, a dependency that is not part of the reference checkout): rows are appended along
+    axis 2, ``keys`` / ``values`` hold at least ``offset`` rows, ``trim`` lowers ``offset``. Written
+    for this script; it allocates exactly, where the original grows in steps."""
+
+    def __init__(self):
+        self.keys = self.values = None
+        self.offset = 0
+
+    def update_and_fetch(self, keys, values):
+        if self.keys is None:
+            self.keys, self.values = np.array(keys), np.array(values)
+        else:
+            self.keys = np.concatenate([self.keys[..., : self.offset, :], keys], axis=2)
+            self.values = np.concatenate([self.values[..., : self.offset, :], values], axis=2)
+        self.offset += keys.shape[2]
+        return self.keys[..., : self.offset, :], self.values[..., : self.offset, :]
+
+    def trim(self, n):
+        n = min(self.offset, n)
+        self.offset -= n
+        return n
+
+    def is_trimmable(self):
+        return True
 
 
 def _mx_numpy_module():
@@ -295,7 +401,7 @@ def _mx_numpy_module():
 
     m = types.ModuleType("mlx.core")
     m.float32, m.uint8, m.int32, m.float16 = np.float32, np.uint8, np.int32, np.float16
-    m.array = lambda a, dtype=None: np.asarray(a, dtype=dtype)
+    m.array = lambda a, dtype=None: np.array(a, dtype=dtype)    # (a copy, as an MLX array of an array is)
     m.min = lambda a, axis=None, keepdims=False: np.min(a, axis=axis, keepdims=keepdims)
     m.max = lambda a, axis=None, keepdims=False: np.max(a, axis=axis, keepdims=keepdims)
     m.mean = lambda a, axis=None, keepdims=False: np.mean(a, axis=axis, keepdims=keepdims)
@@ -307,6 +413,9 @@ def _mx_numpy_module():
     m.sum = lambda a, axis=None, keepdims=False: np.sum(a, axis=axis, keepdims=keepdims)
     m.where, m.stack, m.zeros_like, m.arange = np.where, np.stack, np.zeros_like, np.arange
     m.eval = lambda *a: None
+    m.moveaxis = np.moveaxis
+    m.linalg = types.SimpleNamespace(norm=np.linalg.norm)
+    m.bfloat16 = object()        # (NumPy has no bfloat16: compares unequal to every dtype)
     return m
 
 

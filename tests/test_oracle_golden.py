@@ -288,3 +288,49 @@ def test_group_quant_core_kitty_and_age_tiered_oracles_match_the_reference_modul
     assert np.array_equal(age_tiered.assign_age_tiers([200 - (i + 1) for i in range(200)], 40, 120), z["age_tok_tier"])
     assert np.array_equal(age_tiered.age_tier_quantize_batched(z["age_x"], list(z["age_group_tier"]), (8, 4, 2), 32), z["age_out"])
     assert [age_tiered.age_tiered_bytes({0: 40, 1: 80, 2: 80}, (8, 4, 2), 32), age_tiered.full_fp16_bytes(200, 32)] == list(z["age_bytes"])
+
+
+def _replay(tag, model, z, trimmable, counters):
+    """Feed the recorded call script to an oracle cache model and compare what it returns, and its
+    counters, with what the reference's cache CLASS returned when make_golden.py executed it over the
+    NumPy stand-ins (``mlx.core`` answered by NumPy, a minimal container for its ``mlx_lm`` base class)."""
+    k, v = z["k"], z["v"]
+    checked = 0
+    for i, (op, a, b) in enumerate(z["script"].tolist()):
+        if op == 1:
+            if trimmable:
+                assert model.trim(a) == a
+            continue
+        ko, vo = model.update_and_fetch(k[:, :, a:b], v[:, :, a:b])
+        if f"{tag}_k_{i}" in z:
+            assert np.array_equal(ko, z[f"{tag}_k_{i}"]), (tag, i)
+            assert np.array_equal(vo, z[f"{tag}_v_{i}"]), (tag, i)
+            got = [int(c(model)) for c in counters]
+            assert got == z[f"{tag}_c_{i}"].tolist()[: len(got)], (tag, i, got, z[f"{tag}_c_{i}"].tolist())
+            checked += 1
+    assert checked >= 10
+    return model
+
+
+def test_cache_policies_match_the_reference_classes_run_over_numpy():
+    """KIVI (residual window, group-aligned frontier, trim), sink-protected KIVI, SKVQ, Kitty and
+    AgeTieredKV: the oracle's cache models against traces of the reference's own classes
+    (``cache/kivi_cache.py``, ``sink_cache.py``, ``skvq_cache.py``, ``kitty_cache.py``,
+    ``age_tiered_cache.py``) executed unmodified: returned keys / values bit for bit at every
+    recorded call (a prefill, single tokens, a block, a trim, more tokens), frontier and byte counters."""
+    from oracle import age_tiered, kitty, kivi_sink, skvq
+
+    z = _load("cache_traces.npz")
+    _replay("kivi", kivi_sink.SinkProtectedOracle(32, 2, group=8, residual_length=16, n_sink=0), z, True,
+            [lambda m: m.offset, lambda m: m.n_quantized])
+    s = _replay("sink", kivi_sink.SinkProtectedOracle(32, 2, group=8, residual_length=16, n_sink=2), z, True,
+                [lambda m: m.offset, lambda m: m.n_quantized])
+    assert [s.sink_positions_for(0), s.sink_positions_for(1)] == z["sink_positions"].tolist()
+    m = _replay("skvq", skvq.SKVQCacheModel(32, bits_k=2, bits_v=3, group_size=8, window=16, n_sink=3), z, False,
+                [lambda m: m.offset, lambda m: m.q_end, lambda m: m.compressed_key_bytes, lambda m: m.compressed_value_bytes])
+    assert np.array_equal(m.perm_k, z["skvq_perm_k"]) and np.array_equal(m.perm_v, z["skvq_perm_v"])
+    _replay("kitty", kitty.KittyCacheModel(32, 0.25, 4, 2, 8), z, True,
+            [lambda m: m.keys.shape[2], lambda m: m.n_keys, lambda m: m.compressed_key_bytes, lambda m: m.fp16_key_bytes,
+             lambda m: m.value_fp16_bytes])
+    _replay("age", age_tiered.AgeTieredCacheModel(32, 20, 50, (8, 4, 2), 8), z, False,
+            [lambda m: m.raw_k.shape[1], lambda m: m.age_tiered_bytes, lambda m: m.full_seq_bytes])
