@@ -10,12 +10,16 @@ Follows:
 * ``veloxquant_mlx/allocators/vecinfer.py:93-184`` (dual transform)
 * ``veloxquant_mlx/tests/cache/test_vecinfer_fused_sdpa.py:69-115`` (``_reference_sdpa``)
 
-PARITY UNPINNED for ``quantize_vq`` indices at the bit level: the reference
-computes ``mx.sum(diff*diff, -1)`` / ``mx.argmin`` inside MLX, which cannot be
-installed here, and its tests only check statistical agreement. The canonical
-order fixed here: float32; ``d = x_i - c_i``; ``dist = dist + d*d`` with the
-product and the sum rounded separately, for ``i = 0..sub_dim-1`` in order,
-starting from ``0.0``; the first (lowest-index) minimum wins.
+``quantize_vq``: the reference computes ``mx.sum(diff*diff, -1)`` / ``mx.argmin`` inside MLX, which
+cannot be installed here, and its tests only check statistical agreement. The canonical order fixed
+here: float32; ``d = x_i - c_i``; ``dist = dist + d*d`` with the product and the sum rounded
+separately, for ``i = 0..sub_dim-1`` in order, starting from ``0.0``; the first (lowest-index)
+minimum wins. Pinning: ``tests/golden/vq.npz`` holds the indices of the reference's own function
+executed with NumPy answering ``mx`` (``tests/golden/make_golden.py``); NumPy sums a row of fewer than
+8 float32 in exactly this order, so at sub-vector sizes 2 and 4 the pin is bit for bit by
+construction; at size 8 NumPy adds as a tree and the recorded indices still all agree (a difference
+could only be a near-tie). What stays open is MLX's own reduction order. ``reference_sdpa`` and the
+encode / decode kernels' arithmetic remain unpinned.
 """
 
 from __future__ import annotations

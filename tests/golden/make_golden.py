@@ -177,10 +177,26 @@ def main():
     out = {}
     for d in (1, 2, 8, 128):
         out[f"wht_{d}"] = np.asarray(ns_w["walsh_hadamard_matrix"](d))
-    np.savez_compressed(os.path.join(HERE, "vq.npz"), **out)
-    # ---------------- TurboQuant-RVQ codebooks (whole modules) ----------------
+    # quantize_vq / dequantize_vq (allocators/vecinfer.py:281-335): the module's own array-API path,
+    # executed with NumPy answering ``mx``. NumPy sums a contiguous row of fewer than 8 float32 in
+    # order, which is also the order of the reference's Metal kernel; at sub_dim 8 it sums as a tree.
     import sys
     import types
+
+    ns_q = extract_functions(os.path.join(pkg, "allocators", "vecinfer.py"), ["quantize_vq", "dequantize_vq"],
+                             extra_ns={"mx": _mx_numpy_module()})
+    rng = np.random.default_rng(281)
+    for tag, sub, n_c, shape in [("s2", 2, 16, (3, 50, 16)), ("s4", 4, 256, (2, 4, 64, 64)), ("s4big", 4, 4096, (1, 2, 40, 128)),
+                                 ("s8", 8, 256, (2, 300, 128))]:
+        x = rng.standard_normal(shape).astype(np.float16)
+        cb = rng.standard_normal((n_c, sub)).astype(np.float16)
+        cb[7] = cb[3]                                        # a duplicated centroid: the lower index must win
+        x.reshape(-1, sub)[5] = cb[3]                        # an exact hit on it
+        idx = np.asarray(ns_q["quantize_vq"](x, cb, sub))
+        out[f"q_{tag}_x"], out[f"q_{tag}_cb"], out[f"q_{tag}_idx"] = x, cb, idx
+        out[f"q_{tag}_deq"] = np.asarray(ns_q["dequantize_vq"](idx, cb))
+    np.savez_compressed(os.path.join(HERE, "vq.npz"), **out)
+    # ---------------- TurboQuant-RVQ codebooks (whole modules) ----------------
 
     consts = load_module(os.path.join(pkg, "core", "constants.py"), "veloxquant_mlx.core.constants")
     for name in ("veloxquant_mlx", "veloxquant_mlx.core"):

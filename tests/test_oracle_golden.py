@@ -334,3 +334,17 @@ def test_cache_policies_match_the_reference_classes_run_over_numpy():
              lambda m: m.value_fp16_bytes])
     _replay("age", age_tiered.AgeTieredCacheModel(32, 20, 50, (8, 4, 2), 8), z, False,
             [lambda m: m.raw_k.shape[1], lambda m: m.age_tiered_bytes, lambda m: m.full_seq_bytes])
+
+
+@pytest.mark.parametrize("tag,sub", [("s2", 2), ("s4", 4), ("s4big", 4), ("s8", 8)])
+def test_quantize_vq_oracle_matches_the_reference_function_run_over_numpy(tag, sub):
+    """``oracle.vq.quantize_vq`` / ``dequantize_vq`` against ``allocators/vecinfer.py:281-335`` executed
+    with NumPy answering ``mx`` (make_golden.py). Below 8 elements NumPy sums a row in order, the
+    order of the reference's Metal kernel and of the oracle: bit for bit. At sub_dim 8 NumPy sums as
+    a tree; the indices still agree on these vectors (a difference could only be a near-tie)."""
+    z = _load("vq.npz")
+    x, cb, idx = z[f"q_{tag}_x"], z[f"q_{tag}_cb"], z[f"q_{tag}_idx"]
+    got = vq.quantize_vq(x, cb, sub)
+    assert got.dtype == idx.dtype == np.int32 and np.array_equal(got, idx)
+    assert int(idx.reshape(-1)[5]) == 3                      # the duplicated centroid: lower index wins
+    assert np.array_equal(vq.dequantize_vq(idx, cb), z[f"q_{tag}_deq"])
