@@ -18,8 +18,10 @@ minimum wins. Pinning: ``tests/golden/vq.npz`` holds the indices of the referenc
 executed with NumPy answering ``mx`` (``tests/golden/make_golden.py``); NumPy sums a row of fewer than
 8 float32 in exactly this order, so at sub-vector sizes 2 and 4 the pin is bit for bit by
 construction; at size 8 NumPy adds as a tree and the recorded indices still all agree (a difference
-could only be a near-tie). What stays open is MLX's own reduction order. ``reference_sdpa`` and the
-encode / decode kernels' arithmetic remain unpinned.
+could only be a near-tie). What stays open is MLX's own reduction order. ``reference_sdpa`` (with the
+dual transform of the queries) equals the reference's ``_reference_sdpa``, executed the same way, to
+2e-6 on causal / windowed / grouped-head / smoothed cases (same file). The fused encode / decode
+kernels' arithmetic remains unpinned.
 """
 
 from __future__ import annotations

@@ -195,6 +195,29 @@ def main():
         idx = np.asarray(ns_q["quantize_vq"](x, cb, sub))
         out[f"q_{tag}_x"], out[f"q_{tag}_cb"], out[f"q_{tag}_idx"] = x, cb, idx
         out[f"q_{tag}_deq"] = np.asarray(ns_q["dequantize_vq"](idx, cb))
+    # _reference_sdpa (tests/cache/test_vecinfer_fused_sdpa.py:69-115): the reference's dense statement of
+    # attention over VQ keys and values (dequantize, rotate back, smooth, masked softmax), same stand-in
+    shim = _mx_numpy_module()
+    ns_s = extract_functions(os.path.join(pkg, "tests", "cache", "test_vecinfer_fused_sdpa.py"), ["_reference_sdpa"],
+                             extra_ns={"mx": shim, "dequantize_vq": ns_q["dequantize_vq"]})
+    Hm = np.asarray(ns_w["walsh_hadamard_matrix"](64), np.float32)
+    for tag, B, H_q, H_kv, S_q, S_kv, causal, window, smooth_kind in [
+            ("a", 1, 4, 4, 1, 200, True, 0, "none"), ("b", 2, 8, 2, 1, 333, True, 0, "per_head"),
+            ("c", 1, 4, 2, 8, 64, True, 0, "shared"), ("d", 2, 4, 4, 3, 150, True, 40, "per_head"),
+            ("e", 1, 2, 2, 5, 90, False, 0, "none")]:
+        q = rng.standard_normal((B, H_q, S_q, 64)).astype(np.float16)
+        cb_k = rng.standard_normal((256, 8)).astype(np.float16)
+        cb_v = rng.standard_normal((256, 8)).astype(np.float16)
+        k_idx = rng.integers(0, 256, (B, H_kv, S_kv, 8)).astype(np.int32)
+        v_idx = rng.integers(0, 256, (B, H_kv, S_kv, 8)).astype(np.int32)
+        smooth = {"none": None, "per_head": rng.uniform(0.5, 2.0, (H_kv, 64)).astype(np.float32),
+                  "shared": rng.uniform(0.5, 2.0, (64,)).astype(np.float32)}[smooth_kind]
+        o = ns_s["_reference_sdpa"](q, k_idx, cb_k, v_idx, cb_v, smooth, Hm, 0.125, causal=causal, sliding_window=window)
+        for name, arr in (("q", q), ("cb_k", cb_k), ("cb_v", cb_v), ("k_idx", k_idx), ("v_idx", v_idx), ("out", np.asarray(o)),
+                          ("flags", np.asarray([int(causal), window]))):
+            out[f"sdpa_{tag}_{name}"] = arr
+        if smooth is not None:
+            out[f"sdpa_{tag}_smooth"] = smooth
     np.savez_compressed(os.path.join(HERE, "vq.npz"), **out)
     # ---------------- TurboQuant-RVQ codebooks (whole modules) ----------------
 
@@ -429,7 +452,14 @@ def _mx_numpy_module():
     m.sum = lambda a, axis=None, keepdims=False: np.sum(a, axis=axis, keepdims=keepdims)
     m.where, m.stack, m.zeros_like, m.arange = np.where, np.stack, np.zeros_like, np.arange
     m.eval = lambda *a: None
-    m.moveaxis = np.moveaxis
+    m.moveaxis, m.swapaxes = np.moveaxis, np.swapaxes
+    m.repeat = lambda a, repeats, axis=None: np.repeat(a, repeats, axis=axis)
+
+    def softmax(a, axis=-1):
+        e = np.exp(a - np.max(a, axis=axis, keepdims=True))
+        return e / np.sum(e, axis=axis, keepdims=True)
+
+    m.softmax = softmax
     m.linalg = types.SimpleNamespace(norm=np.linalg.norm)
     m.bfloat16 = object()        # (NumPy has no bfloat16: compares unequal to every dtype)
     return m

@@ -348,3 +348,20 @@ def test_quantize_vq_oracle_matches_the_reference_function_run_over_numpy(tag, s
     assert got.dtype == idx.dtype == np.int32 and np.array_equal(got, idx)
     assert int(idx.reshape(-1)[5]) == 3                      # the duplicated centroid: lower index wins
     assert np.array_equal(vq.dequantize_vq(idx, cb), z[f"q_{tag}_deq"])
+
+
+@pytest.mark.parametrize("tag", list("abcde"))
+def test_vq_reference_sdpa_matches_the_reference_function_run_over_numpy(tag):
+    """``oracle.vq.reference_sdpa`` (attention in the transformed space: dual-transformed queries
+    against dequantized key codes) against the reference's ``_reference_sdpa``
+    (tests/cache/test_vecinfer_fused_sdpa.py:69-115: dequantize, rotate back, smooth, masked softmax in
+    the original space), executed with NumPy answering ``mx``: causal, tail-aligned multi-row,
+    trailing window, grouped heads, per-head / shared / no smooth factors. Equal to 2e-6."""
+    z = _load("vq.npz")
+    g = lambda n: z[f"sdpa_{tag}_{n}"]  # noqa: E731
+    smooth = z[f"sdpa_{tag}_smooth"] if f"sdpa_{tag}_smooth" in z else np.ones(64, np.float32)
+    causal, window = (int(x) for x in g("flags"))
+    q_t = vq.apply_dual_transform_queries(g("q").astype(np.float32), smooth, vq.walsh_hadamard_matrix(64))
+    out = vq.reference_sdpa(q_t, g("k_idx"), g("cb_k"), g("v_idx"), 0.125, v_codebook=g("cb_v"), causal=bool(causal),
+                            sliding_window=window)
+    np.testing.assert_allclose(out, g("out"), rtol=0, atol=2e-6)
