@@ -328,7 +328,8 @@ def main():
     names = ["mlx", "mlx.core", "mlx_lm", "mlx_lm.models", "mlx_lm.models.cache", "veloxquant_mlx.core.exceptions",
              "veloxquant_mlx.metal", "veloxquant_mlx.metal.kernels", "veloxquant_mlx.cache", "veloxquant_mlx.cache.kivi_cache",
              "veloxquant_mlx.quantizers", "veloxquant_mlx.quantizers._quant_utils", "veloxquant_mlx.quantizers.skvq",
-             "veloxquant_mlx.quantizers.kitty", "veloxquant_mlx.quantizers.age_tiered"]
+             "veloxquant_mlx.quantizers.kitty", "veloxquant_mlx.quantizers.age_tiered", "veloxquant_mlx.metal.fused_sdpa",
+             "veloxquant_mlx.allocators", "veloxquant_mlx.allocators.vecinfer"]
     saved = {k: sys.modules.get(k) for k in names}
     try:
         sys.modules["mlx"], sys.modules["mlx.core"] = mlx_pkg, mlx_pkg.core
@@ -394,6 +395,23 @@ def main():
         out["skvq_perm_k"], out["skvq_perm_v"] = np.asarray(skc.key_perms), np.asarray(skc.value_perms)
         run("kitty", kitty_c.KittyKVCache(cfg), ["offset", "_n_keys", "_compressed_key_bytes", "_fp16_key_bytes", "_value_fp16_bytes"], True)
         run("age", age_c.AgeTieredKVCache(cfg), ["offset", "age_tiered_bytes", "full_seq_bytes", "tokens_recent", "tokens_mid", "tokens_old"], False)
+        # VecInfer (standard path: every block smoothed, rotated, VQ-coded and reconstructed on its own)
+        fs = types.ModuleType("veloxquant_mlx.metal.fused_sdpa")
+        fs.supports_shape = lambda **kw: False
+        fs.is_patched = lambda: False
+        sys.modules["veloxquant_mlx.metal.fused_sdpa"] = fs
+        sys.modules["veloxquant_mlx.allocators"] = types.ModuleType("veloxquant_mlx.allocators")
+        load_module(os.path.join(pkg, "allocators", "vecinfer.py"), "veloxquant_mlx.allocators.vecinfer")
+        vi_c = load_module(os.path.join(pkg, "cache", "vecinfer_cache.py"), "ref_vecinfer_cache")
+        vcfg = types.SimpleNamespace(head_dim=D, key_sub_dim=4, value_sub_dim=8, key_codebook_bits=8, value_codebook_bits=8,
+                                     residual_length=128, seed=42, use_metal_kernels=None, fused_sdpa=False,
+                                     fused_sdpa_memory_bound=False, fused_sdpa_max_ctx=None,
+                                     smooth_factors=rng.uniform(0.5, 2.0, (H, D)).astype(np.float32),
+                                     key_codebook=rng.standard_normal((256, 4)).astype(np.float32),
+                                     value_codebook=rng.standard_normal((256, 8)).astype(np.float32))
+        out["vecinfer_smooth"], out["vecinfer_cb_k"], out["vecinfer_cb_v"] = vcfg.smooth_factors, vcfg.key_codebook, vcfg.value_codebook
+        run("vecinfer", vi_c.VecInferKVCache(vcfg), ["offset", "_key_bytes_compressed", "_value_bytes_compressed", "_key_bytes_fp16",
+                                                     "_tokens_seen"], True)
         np.savez_compressed(os.path.join(HERE, "cache_traces.npz"), **out)
     finally:
         for key, val in saved.items():
@@ -440,7 +458,18 @@ def _mx_numpy_module():
 
     m = types.ModuleType("mlx.core")
     m.float32, m.uint8, m.int32, m.float16 = np.float32, np.uint8, np.int32, np.float16
-    m.array = lambda a, dtype=None: np.array(a, dtype=dtype)    # (a copy, as an MLX array of an array is)
+    class _IsNdarray(type):
+        def __instancecheck__(cls, obj):
+            return isinstance(obj, np.ndarray)
+
+    class array(metaclass=_IsNdarray):
+        """``mx.array`` is a constructor and a type: calls copy into a NumPy array (as an MLX array of an
+        array is a copy), ``isinstance(x, mx.array)`` holds for NumPy arrays."""
+
+        def __new__(cls, a, dtype=None):
+            return np.array(a, dtype=dtype)
+
+    m.array = array
     m.min = lambda a, axis=None, keepdims=False: np.min(a, axis=axis, keepdims=keepdims)
     m.max = lambda a, axis=None, keepdims=False: np.max(a, axis=axis, keepdims=keepdims)
     m.mean = lambda a, axis=None, keepdims=False: np.mean(a, axis=axis, keepdims=keepdims)
@@ -462,6 +491,10 @@ def _mx_numpy_module():
     m.softmax = softmax
     m.linalg = types.SimpleNamespace(norm=np.linalg.norm)
     m.bfloat16 = object()        # (NumPy has no bfloat16: compares unequal to every dtype)
+    m.uint32, m.int8, m.uint16 = np.uint32, np.int8, np.uint16
+    m.logical_not, m.logical_and, m.isfinite, m.abs, m.sqrt, m.matmul = np.logical_not, np.logical_and, np.isfinite, np.abs, np.sqrt, np.matmul
+    m.zeros = lambda shape, dtype=np.float32: np.zeros(shape, dtype=dtype)
+    m.ones = lambda shape, dtype=np.float32: np.ones(shape, dtype=dtype)
     return m
 
 

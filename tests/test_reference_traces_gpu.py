@@ -51,3 +51,31 @@ def test_native_caches_replay_the_reference_classes_traces(method, tag, trimmabl
             assert c.offset == int(z[f"{tag}_c_{i}"][0])
             checked += 1
     assert checked >= 10
+
+
+def test_native_vecinfer_cache_replays_the_reference_class_trace():
+    """VecInfer (standard path, per-head smooth factors, 256-entry codebooks): the value reconstructions
+    equal the reference class's bit for bit (no transform on that side); the key reconstructions agree to
+    one float16 step, and all but a sliver exactly -- the reference rotates with a dense ``@ H`` (whatever
+    order the matrix product takes), this package with the butterfly, so the float32 values behind the
+    float16 rounding differ in their last bits."""
+    z = np.load(os.path.join(GOLDEN, "cache_traces.npz"))
+    c = _make("vecinfer", head_dim=32, key_sub_dim=4, value_sub_dim=8, key_codebook_bits=8, value_codebook_bits=8,
+              smooth_factors=_t(z["vecinfer_smooth"]), key_codebook=_t(z["vecinfer_cb_k"]), value_codebook=_t(z["vecinfer_cb_v"]))
+    k, v = z["k"], z["v"]
+    checked, same, total = 0, 0, 0
+    for i, (op, a, b) in enumerate(z["script"].tolist()):
+        if op == 1:
+            assert c.trim(a) == a
+            continue
+        ko, vo = c.update_and_fetch(_t(k[:, :, a:b]), _t(v[:, :, a:b]))
+        if f"vecinfer_k_{i}" in z:
+            want_k, want_v = z[f"vecinfer_k_{i}"], z[f"vecinfer_v_{i}"]
+            np.testing.assert_array_equal(vo.cpu().numpy(), want_v)
+            got = ko.float().cpu().numpy()
+            np.testing.assert_allclose(got, want_k.astype(np.float32), rtol=2.0 ** -10, atol=2.0 ** -14)
+            same += int((got == want_k.astype(np.float32)).sum())
+            total += got.size
+            assert c.offset == int(z[f"vecinfer_c_{i}"][0])
+            checked += 1
+    assert checked >= 10 and same / total > 0.995
