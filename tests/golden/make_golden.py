@@ -243,6 +243,25 @@ def main():
         for d in (8, 16, 32):
             c, _ = lm.lloyd_max(lambda x, dd=d: dist.beta_pdf(x, dd), (-1.0 + 1e-6, 1.0 - 1e-6), n_levels=2 ** b)
             out[f"beta_b{b}_d{d}"] = c
+    # helper functions of cache/turboquant_rvq_cache.py (:65-126): unit direction + norm, rescale with
+    # float16 saturation, bit-packing of the code streams; executed with NumPy answering ``mx``
+    from functools import partial
+
+    shim = _mx_numpy_module()
+    ns_r = extract_functions(os.path.join(pkg, "cache", "turboquant_rvq_cache.py"),
+                             ["_unit_fp16_from_fp16", "_rescale_fp16", "_pack_indices", "_unpack_indices"],
+                             extra_ns={"mx": shim, "partial": partial, "Any": object, "_WORD_BITS": 32})
+    rng_r = np.random.default_rng(747)
+    kk = (rng_r.standard_normal((5, 7, 64)) * 10.0 ** rng_r.uniform(-3, 4.5, (5, 7, 1))).astype(np.float16)   # norms past 65504 too
+    unit, norms = ns_r["_unit_fp16_from_fp16"](kk)
+    out["cache_k"], out["cache_unit"], out["cache_norms"] = kk, np.asarray(unit), np.asarray(norms)
+    out["cache_rescaled"] = np.asarray(ns_r["_rescale_fp16"](np.asarray(unit), np.asarray(norms)))
+    for bits in (1, 2, 3, 4):
+        for d in (64, 128, 20):
+            idx = rng_r.integers(0, 1 << bits, (3, 4, d)).astype(np.uint8)
+            packed = np.asarray(ns_r["_pack_indices"](idx, bits))
+            out[f"pack_b{bits}_d{d}_idx"], out[f"pack_b{bits}_d{d}_words"] = idx, packed.astype(np.uint32)
+            assert np.array_equal(np.asarray(ns_r["_unpack_indices"](packed.astype(np.uint32), bits, d)), idx)
     np.savez_compressed(os.path.join(HERE, "rvq.npz"), **out)
 
     # ---------------- SKVQ quantizer (whole module, NumPy standing in for mlx.core) ----------------
@@ -481,6 +500,7 @@ def _mx_numpy_module():
     m.sum = lambda a, axis=None, keepdims=False: np.sum(a, axis=axis, keepdims=keepdims)
     m.where, m.stack, m.zeros_like, m.arange = np.where, np.stack, np.zeros_like, np.arange
     m.eval = lambda *a: None
+    m.compile = lambda f=None, **kw: f
     m.moveaxis, m.swapaxes = np.moveaxis, np.swapaxes
     m.repeat = lambda a, repeats, axis=None: np.repeat(a, repeats, axis=axis)
 

@@ -97,3 +97,32 @@ def test_oracle_decode_inverts_the_rotation():
     rec = o_rvq.rvq_unpack_decode(p1, p2, np.ones(64, np.float32), c1.centroids, c2.centroids, diag, bits, d).astype(np.float32)
     cos = (rec * x).sum(1) / np.linalg.norm(rec, axis=1)
     assert cos.min() > 0.995
+
+
+def test_packing_and_norm_helpers_match_the_reference_cache_functions_run_over_numpy():
+    """``_pack_indices`` / ``_unpack_indices`` / ``_unit_fp16_from_fp16`` / ``_rescale_fp16`` of
+    ``cache/turboquant_rvq_cache.py:65-126``, extracted and executed with NumPy answering ``mx``
+    (tests/golden/rvq.npz): the oracle's and the package's packing reproduce the words bit for bit
+    (1-4 bits, a ragged last word); the unit direction / norm split and the saturating rescale of the
+    cache agree with theirs (norms to float32 rounding, unit vectors and rescaled rows to a float16 step)."""
+    from veloxquant_mlx_b200 import rvq
+
+    z = GOLD
+    for bits in (1, 2, 3, 4):
+        for d in (64, 128, 20):
+            idx, words = z[f"pack_b{bits}_d{d}_idx"], z[f"pack_b{bits}_d{d}_words"]
+            assert np.array_equal(o_rvq.pack_indices(idx, bits), words)
+            assert np.array_equal(o_rvq.unpack_indices(words, bits, d), idx)
+            got = rvq.pack_indices(torch.from_numpy(idx), bits)
+            assert got.dtype == torch.uint32 and np.array_equal(got.view(torch.int32).numpy().view(np.uint32), words)
+            assert np.array_equal(rvq.unpack_indices(got, bits, d).numpy(), idx)
+    k = torch.from_numpy(z["cache_k"])
+    k32 = k.float()
+    norms = torch.linalg.vector_norm(k32, dim=-1, keepdim=True)          # what TurboQuantRVQKVCache.update_and_fetch computes
+    unit = (k32 / norms.clamp_min(1e-4)).to(torch.float16)
+    np.testing.assert_allclose(norms.numpy(), z["cache_norms"], rtol=2e-7)
+    np.testing.assert_allclose(unit.float().numpy(), z["cache_unit"].astype(np.float32), rtol=2.0 ** -10, atol=2.0 ** -24)
+    assert float((unit.numpy() == z["cache_unit"]).mean()) > 0.99
+    assert float(z["cache_norms"].max()) > 65504.0                         # the case the float32 norm exists for
+    resc = (torch.from_numpy(z["cache_unit"]).float() * torch.from_numpy(z["cache_norms"])).clamp(-65504.0, 65504.0).to(torch.float16)
+    assert np.array_equal(resc.numpy(), z["cache_rescaled"])
