@@ -243,6 +243,51 @@ def main():
         for d in (8, 16, 32):
             c, _ = lm.lloyd_max(lambda x, dd=d: dist.beta_pdf(x, dd), (-1.0 + 1e-6, 1.0 - 1e-6), n_levels=2 ** b)
             out[f"beta_b{b}_d{d}"] = c
+    # the mask recogniser of the fused attention dispatch (metal/fused_sdpa.py:332-396), same stand-in
+    ns_m = extract_functions(os.path.join(pkg, "metal", "fused_sdpa.py"), ["_memory_bound_mask_parameters"],
+                             extra_ns={"mx": _mx_numpy_module()})
+    rng_m = np.random.default_rng(332)
+    cases = []
+
+    def tail_mask(n, kv, width=None):
+        qp = np.arange(kv - n, kv)[:, None]
+        kp = np.arange(kv)[None, :]
+        vis = kp <= qp
+        if width:
+            vis &= kp > qp - width
+        return vis
+
+    def additive(vis, neg=-np.inf, dt=np.float32):
+        return np.where(vis, 0.0, neg).astype(dt)
+
+    Bm, Hm_, Nm, KV = 2, 3, 4, 11
+    base = [tail_mask(Nm, KV), tail_mask(Nm, KV, 5), tail_mask(Nm, KV, 1), tail_mask(Nm, KV, KV), np.ones((Nm, KV), bool),
+            tail_mask(1, KV), tail_mask(1, KV, 3), np.ones((1, KV), bool), np.zeros((Nm, KV), bool)]
+    for vis in base:
+        n = vis.shape[0]
+        for form in (vis, additive(vis), additive(vis, dt=np.float16), additive(vis, neg=-1e9), vis.astype(np.int32)):
+            for shape in ((n, KV), (1, 1, n, KV), (Bm, 1, n, KV), (1, Hm_, n, KV), (Bm, Hm_, n, KV)):
+                cases.append((np.broadcast_to(form, shape).copy(), n))
+    hole = tail_mask(Nm, KV)
+    hole[2, 1] = False                                                 # a padding hole
+    per_head = np.broadcast_to(tail_mask(Nm, KV), (Bm, Hm_, Nm, KV)).copy()
+    per_head[1, 2] = tail_mask(Nm, KV, 5)                              # one head with its own window
+    shifted = np.roll(tail_mask(Nm, KV), 1, axis=1)                    # causal, but not tail-aligned
+    cases += [(hole, Nm), (additive(hole), Nm), (per_head, Nm), (shifted, Nm), (tail_mask(Nm, KV)[:, :KV - 1], Nm),
+              (tail_mask(Nm, KV)[None, None, None], Nm), (np.ones((KV,), bool), Nm), (tail_mask(Nm, KV)[-1], Nm),
+              (np.ones((Nm, 1), bool), Nm), (additive(tail_mask(Nm, KV)) + np.float32(0.5), Nm),
+              (rng_m.random((Nm, KV)) < 0.5, Nm), (np.ones((3, Hm_, Nm, KV), bool), Nm)]
+    out_m = {"n_cases": np.asarray([len(cases)]), "dims": np.asarray([Bm, Hm_, KV])}
+    for i, (mask, n) in enumerate(cases):
+        q = np.zeros((Bm, Hm_, n, 8), np.float16)
+        try:
+            causal, window = ns_m["_memory_bound_mask_parameters"](mask, q, KV)
+            res = [1, int(bool(causal)), int(window)]
+        except ValueError:
+            res = [0, 0, 0]
+        out_m[f"m{i}"], out_m[f"r{i}"] = mask, np.asarray(res + [n])
+    np.savez_compressed(os.path.join(HERE, "masks.npz"), **out_m)
+
     # helper functions of cache/turboquant_rvq_cache.py (:65-126): unit direction + norm, rescale with
     # float16 saturation, bit-packing of the code streams; executed with NumPy answering ``mx``
     from functools import partial
@@ -501,6 +546,7 @@ def _mx_numpy_module():
     m.where, m.stack, m.zeros_like, m.arange = np.where, np.stack, np.zeros_like, np.arange
     m.eval = lambda *a: None
     m.compile = lambda f=None, **kw: f
+    m.bool_, m.floating, m.issubdtype, m.all = np.bool_, np.floating, np.issubdtype, np.all
     m.moveaxis, m.swapaxes = np.moveaxis, np.swapaxes
     m.repeat = lambda a, repeats, axis=None: np.repeat(a, repeats, axis=axis)
 

@@ -212,3 +212,31 @@ def test_transformers_model_decodes_over_the_compressed_caches(method, memory_bo
         gen = model.generate(ids[:, :50], attention_mask=torch.ones_like(ids[:, :50]), max_new_tokens=8, do_sample=False,
                              past_key_values=model.make_cache())
         assert gen.shape == (2, 58)
+
+
+def test_mask_recogniser_agrees_with_the_reference_function_on_every_recorded_mask():
+    """237 masks -- all-visible, tail-aligned causal, trailing windows of several widths, boolean /
+    additive float32 / float16 / -1e9 / integer forms, every broadcastable shape, and masks with holes,
+    per-head differences, shifts, wrong shapes, biases, random patterns -- through the reference's
+    ``_memory_bound_mask_parameters`` (``metal/fused_sdpa.py:332-396``, executed over NumPy by
+    tests/golden/make_golden.py): the same ``(causal, window)`` or the same refusal for every one."""
+    import os
+
+    import numpy as np
+
+    from veloxquant_mlx_b200.integration import _memory_bound_mask_parameters
+
+    z = np.load(os.path.join(os.path.dirname(__file__), "golden", "masks.npz"))
+    B, H, KV = (int(x) for x in z["dims"])
+    accepted = 0
+    for i in range(int(z["n_cases"][0])):
+        ok, causal, window, N = (int(x) for x in z[f"r{i}"])
+        q = torch.zeros(B, H, N, 8)
+        try:
+            got = _memory_bound_mask_parameters(torch.from_numpy(z[f"m{i}"]), q, KV)
+            res = (1, int(got[0]), int(got[1]))
+        except ValueError:
+            res = (0, 0, 0)
+        assert res == (ok, causal, window), (i, z[f"m{i}"].shape, z[f"m{i}"].dtype)
+        accepted += ok
+    assert 100 < accepted < 200
