@@ -251,18 +251,28 @@ class AgeTieredKVCache(StandaloneProtocol):
     def _pack_final(self, rows_k: torch.Tensor, rows_v: torch.Tensor) -> None:
         """Append whole groups that reached the last tier to the packed store (quantized from raw)."""
         bits, gs = self._tiers[at.OLD].bits, self._group_size
-        new = {}
+        n_new = rows_k.shape[1]
+        if self._final is None:
+            self._final = {}
         for name, rows in (("k", rows_k), ("v", rows_v)):
-            q = kernels.kivi_quantize(rows[None].contiguous(), -2, gs, bits, eps=1e-8)
-            if self._final is None:
-                new[name] = q
-            else:
-                new[name] = tuple(torch.cat([a, b], dim=2) for a, b in zip(self._final[name], q))
-        self._final = new
-        self._n_final += rows_k.shape[1]
+            q = kernels.kivi_quantize(rows[None].contiguous(), -2, gs, bits, eps=1e-8)   # codes per token, (scale, zero) per group
+            have = self._final.get(name)
+            per = (1, gs, gs)                                   # tokens per row of (codes, scale, zero)
+            if have is None or any((self._n_final + n_new) // p > t.shape[2] for t, p in zip(have, per)):
+                # grow geometrically: the store is appended to every group_size tokens
+                cap = max(2 * (self._n_final + n_new), 64 * gs)
+                grown = tuple(torch.empty((*t.shape[:2], cap // p, t.shape[3]), dtype=t.dtype, device=t.device) for t, p in zip(q, per))
+                if have is not None:
+                    for g, t, p in zip(grown, have, per):
+                        g[:, :, : self._n_final // p] = t[:, :, : self._n_final // p]
+                have = self._final[name] = grown
+            for t, new, p in zip(have, q, per):
+                t[:, :, self._n_final // p:(self._n_final + n_new) // p] = new
+        self._n_final += n_new
 
     def _dense_final(self, which: str) -> torch.Tensor:
-        codes, scale, zero = self._final[which]
+        gs, n = self._group_size, self._n_final
+        codes, scale, zero = (t[:, :, : n // p].contiguous() for t, p in zip(self._final[which], (1, gs, gs)))
         bits = self._tiers[at.OLD].bits
         # float32 reconstruction rounded to float16, then to the storage dtype: the reference's two casts
         out = kernels.scalar_decode_once(codes, scale, zero, self._group_size, "K", store_bits=kernels.storage_bits(bits),
@@ -338,7 +348,9 @@ class AgeTieredKVCache(StandaloneProtocol):
         """Resident bytes: packed final groups with float32 parameters, raw rows of the younger groups."""
         total = 0
         if self._final is not None:
-            total += sum(t.numel() * t.element_size() for bufs in self._final.values() for t in bufs)
+            gs, n = self._group_size, self._n_final
+            total += sum(t.shape[0] * t.shape[1] * (n // p) * t.shape[3] * t.element_size()
+                         for bufs in self._final.values() for t, p in zip(bufs, (1, gs, gs)))
         for t in (self._raw_k, self._raw_v):
             if t is not None:
                 total += t.numel() * t.element_size()
