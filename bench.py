@@ -919,7 +919,8 @@ def run_c5(torch, dist, timer, world, rank, device, dtype, args):
             "attend_graph_ms_per_step": graph_ms,
             "attend_graph_value": None if not graph_ms else bl * L / (graph_ms * 1e-3) / 1e9,
             "units_per_rank": plan.size, "gather": "peer" if px is not None else ("none" if world == 1 else "not gathered"),
-            "note": "decode steps are eager launches through update_and_fetch + fused_sdpa (host-bound at this size); "
+            "note": "decode steps are eager launches through update_and_fetch + fused_sdpa (about 1.3 ms of host time per step on "
+                    "an idle host, close to the device time: a busy host makes the loop host-bound); "
                     "attend_graph_*: the step's 64 attention launches (+ exchange) captured into a CUDA graph"}
 
 
