@@ -706,12 +706,21 @@ def run_extras(torch, dist, timer, w, plan, world, rank, device, dtype, px, args
             for l in range(L):
                 c2[l].fused_sdpa(q2[l], scale, out=o2[l], overlap_previous=True)
 
-        ms = graph_time(step2, args.steps, 10)
+        try:
+            run2 = capture(torch, step2).replay
+        except Exception:
+            run2 = step2
+        for _ in range(3):
+            run2()
+        blocks2 = timer.blocks(run2, args.steps, 10)
+        ms, ms_best = float(np.median(blocks2)), float(min(blocks2))
         bl = algorithmic_bytes_per_layer(w, bits=2)
         extra["kivi2"] = {"workload": "the default shape with 2-bit codes", "ms_per_step": ms,
                           "value": bl * L / (ms * 1e-3) / 1e9, "unit": UNIT,
                           "frac": bl * L / (ms * 1e-3) / 1e9 / peak, "tokens_per_s": B / (ms * 1e-3),
-                          "algorithmic_bytes_per_launch": bl}
+                          "algorithmic_bytes_per_launch": bl,
+                          # (the fastest of the ten blocks: the first ones run before the power cap pulls the clock down)
+                          "best_block_ms_per_step": ms_best, "best_block_frac": bl * L / (ms_best * 1e-3) / 1e9 / peak}
         del c2, q2, o2
         torch.cuda.empty_cache()
 
@@ -748,6 +757,18 @@ def run_extras(torch, dist, timer, w, plan, world, rank, device, dtype, px, args
                                           "frac_of_bf16_peak": fl / (ms * 1e-3) / 1e12 / tpeak, "peak_kind": tkind,
                                           "issued_mma_frac_of_peak": mma_fl / (ms * 1e-3) / 1e12 / tpeak, **other}
         vk.quantize_status()
+
+        # -- VecInfer config 2: decode attention over the VQ key codes (dense fp16 values, 32 query heads)
+        from veloxquant_mlx_b200 import vecinfer as vi
+        kx = torch.randn(1, 8, 4096, D, device=device, dtype=torch.float16)
+        cbk = torch.randn(256, 8, device=device)
+        kix = vi.quantize_vq(kx, cbk, 8, index_dtype=torch.uint8)
+        qx = torch.randn(1, 32, 1, D, device=device, dtype=torch.float16)
+        ms = graph_time(lambda: vi.fused_sdpa_vq(qx, kix, cbk, kx, None, D ** -0.5), 20)
+        nb = kix.numel() + kx.numel() * 2
+        extra["vq_attend_config2"] = {"shape": [1, 8, 4096, D], "us": ms * 1e3, "GBps": nb / (ms * 1e-3) / 1e9,
+                                      "note": "8.9 MB: bound by per-CTA set-up (lookup tables) and load latency, not by HBM"}
+        del kx, kix, qx
 
         # -- TurboQuant-RVQ: quantize+pack and unpack+decode of 1 Mi rotated keys
         from veloxquant_mlx_b200 import rvq

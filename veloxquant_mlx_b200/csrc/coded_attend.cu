@@ -147,13 +147,63 @@ __device__ __forceinline__ void decode_v(const CodedParams &p, const VRaw<DPL, V
     }
 }
 
+// Warp maximum of finite-or-minus-infinity floats in one reduction instruction: floats order like
+// their bit patterns read as sign-magnitude integers, which one XOR turns into two's complement.
+__device__ __forceinline__ float st_warp_max(float x) {
+    int i = __float_as_int(x);
+    i ^= (i >> 31) & 0x7fffffff;
+    i = __reduce_max_sync(0xffffffffu, i);
+    i ^= (i >> 31) & 0x7fffffff;
+    return __int_as_float(i);
+}
+
+__device__ __forceinline__ bool is_aligned_dev(const void *ptr, unsigned a) { return (reinterpret_cast<uintptr_t>(ptr) & (a - 1)) == 0; }
+
+// lut[head][sub][c] = q_sub[head][sub] . codebook[c] for sub-vectors of KS = 4 or 8 floats.
+template <int KS, int NH>
+__device__ __forceinline__ void build_lut_vec(const CodedParams &p, float *lut, const float *sh_q, int nh, int n_sub, int lut_stride, int D) {
+    for (int c = threadIdx.x; c < p.k_nc; c += blockDim.x) {
+        float cbr[KS];
+        for (int s = 0; s < n_sub; ++s) {
+            if (s == 0 || p.k_stacked) {
+                const float4 *cb = reinterpret_cast<const float4 *>(p.k_codebook + ((int64_t)(p.k_stacked ? s : 0) * p.k_nc + c) * KS);
+#pragma unroll
+                for (int e = 0; e < KS / 4; ++e) {
+                    const float4 t = __ldg(cb + e);
+                    cbr[4 * e] = t.x; cbr[4 * e + 1] = t.y; cbr[4 * e + 2] = t.z; cbr[4 * e + 3] = t.w;
+                }
+            }
+            float dot[NH];
+#pragma unroll
+            for (int hp = 0; hp < NH; ++hp) {
+                // (rows past nh hold whatever the buffer held: computed, never stored)
+                const float4 *qv = reinterpret_cast<const float4 *>(sh_q + (hp < nh ? hp : 0) * D + s * KS);
+                float acc = 0.f;
+#pragma unroll
+                for (int e = 0; e < KS / 4; ++e) {
+                    const float4 t = qv[e];
+                    acc = fmaf(t.x, cbr[4 * e], acc); acc = fmaf(t.y, cbr[4 * e + 1], acc);
+                    acc = fmaf(t.z, cbr[4 * e + 2], acc); acc = fmaf(t.w, cbr[4 * e + 3], acc);
+                }
+                dot[hp] = acc;
+            }
+#pragma unroll
+            for (int hp = 0; hp < NH; ++hp)
+                if (hp < nh) lut[hp * lut_stride + s * p.k_nc + c] = dot[hp];
+        }
+    }
+}
+
 // One CTA: (context split, kv head x query row x head chunk, batch). All (<= 8) query heads of
 // the kv head are handled together: a key's code is loaded once and scored against every
 // head, a value row is loaded once and accumulated into every head. Warps take alternate
 // 32-key tiles of the split; value rows are fetched eight at a time so that eight
 // independent loads are in flight per lane.
-template <int DPL, int VM, int NH>
-__global__ void __launch_bounds__(kWarpsC * 32, (NH <= 4 && DPL <= 4 && VM != VM_GENERIC) ? 3 : 2)
+// EAGER (small grids: about one CTA per SM, every load's latency exposed): a warp requests all 32
+// value rows of its tile before it scores the keys, so the rows arrive under the score / softmax work
+// instead of in four batches after it (64 more registers; two CTAs per SM).
+template <int DPL, int VM, int NH, bool EAGER = false>
+__global__ void __launch_bounds__(kWarpsC * 32, (NH <= 4 && DPL <= 4 && VM != VM_GENERIC && !EAGER) ? 3 : 2)
 coded_attend_kernel(const CodedParams p, int key_floats, int vlut_floats) {
     extern __shared__ __align__(16) float smem[];
     const int lane = threadIdx.x & 31, warp = __shfl_sync(0xffffffffu, threadIdx.x >> 5, 0);  // (known warp-uniform)
@@ -203,7 +253,12 @@ coded_attend_kernel(const CodedParams p, int key_floats, int vlut_floats) {
                 }
             }
         }
-        for (int c = threadIdx.x; c < p.k_nc && p.k_sub <= 16; c += blockDim.x) {
+        // sub-vectors of 4 or 8 (16-byte aligned codebook rows): the centroid as vector loads, the query
+        // sub-vector as broadcast vector reads, all heads' dot products as independent chains
+        const bool vec_cb = (p.k_sub == 8 || p.k_sub == 4) && is_aligned_dev(p.k_codebook, 16) && lut_stride % 4 == 0;
+        if (vec_cb && p.k_sub == 8) build_lut_vec<8, NH>(p, lut, sh_q, nh, n_sub, lut_stride, D);
+        if (vec_cb && p.k_sub == 4) build_lut_vec<4, NH>(p, lut, sh_q, nh, n_sub, lut_stride, D);
+        for (int c = threadIdx.x; c < p.k_nc && p.k_sub <= 16 && !vec_cb; c += blockDim.x) {
             float cbr[16];
             for (int s = 0; s < n_sub; ++s) {
                 if (s == 0 || p.k_stacked) {
@@ -238,6 +293,7 @@ coded_attend_kernel(const CodedParams p, int key_floats, int vlut_floats) {
     const int t_end = min(p.S_kv, t_begin + chunk);
     const int q_abs = p.S_kv - p.S_q + sq;
     const int n_words = D / 32;
+    const bool idx16 = p.key_mode == KEY_VQ && n_sub == 16 && p.k_index_bytes == 1 && is_aligned_dev(p.k_codes, 16);
 
     float m_run[NH], l_run[NH], acc[NH][DPL];  // acc[head][this lane's DPL channels]
 #pragma unroll
@@ -254,17 +310,37 @@ coded_attend_kernel(const CodedParams p, int key_floats, int vlut_floats) {
         if (valid && p.window > 0 && q_abs + 1 > p.window && t + p.window < q_abs + 1) valid = false;
         const int64_t tok = bh * p.stride_tok + (valid ? t : t_begin);
         float w[NH];
+        VRaw<DPL, VM> early[EAGER ? 32 : 1];
+        if constexpr (EAGER) {
+            const int n_in = min(32, t_end - tile);
+#pragma unroll
+            for (int j = 0; j < 32; ++j) early[j] = load_v_raw<DPL, VM>(p, bh * p.stride_tok + tile + min(j, n_in - 1), lane);
+        }
         // ---- scores of this lane's key against every head ---------------------------------
         if (p.key_mode == KEY_VQ) {
 #pragma unroll
             for (int h = 0; h < NH; ++h) w[h] = 0.f;
-            for (int sub = 0; sub < n_sub; ++sub) {
-                uint32_t c = load_index(p.k_codes, p.k_index_bytes, tok * n_sub + sub);
-                c = min(c, (uint32_t)(p.k_nc - 1));
-                const float *row = lut + sub * p.k_nc + c;
+            if (idx16) {
+                // sixteen one-byte indices per key: the whole row in one 16-byte load
+                const uint4 iv = __ldg(reinterpret_cast<const uint4 *>(static_cast<const uint8_t *>(p.k_codes) + tok * 16));
+                const uint32_t wd[4] = {iv.x, iv.y, iv.z, iv.w};
 #pragma unroll
-                for (int h = 0; h < NH; ++h)
-                    if (h < nh) w[h] += row[h * lut_stride];
+                for (int sub = 0; sub < 16; ++sub) {
+                    const uint32_t c = min((wd[sub >> 2] >> (8 * (sub & 3))) & 0xFFu, (uint32_t)(p.k_nc - 1));
+                    const float *row = lut + sub * p.k_nc + c;
+#pragma unroll
+                    for (int h = 0; h < NH; ++h)
+                        if (h < nh) w[h] += row[h * lut_stride];
+                }
+            } else {
+                for (int sub = 0; sub < n_sub; ++sub) {
+                    uint32_t c = load_index(p.k_codes, p.k_index_bytes, tok * n_sub + sub);
+                    c = min(c, (uint32_t)(p.k_nc - 1));
+                    const float *row = lut + sub * p.k_nc + c;
+#pragma unroll
+                    for (int h = 0; h < NH; ++h)
+                        if (h < nh) w[h] += row[h * lut_stride];
+                }
             }
 #pragma unroll
             for (int h = 0; h < NH; ++h) w[h] = valid ? w[h] * p.scale : -INFINITY;
@@ -290,14 +366,14 @@ coded_attend_kernel(const CodedParams p, int key_floats, int vlut_floats) {
 #pragma unroll
         for (int h = 0; h < NH; ++h) {
             if (h < nh) {
-                const float tile_max = warp_max(w[h]);
+                const float tile_max = st_warp_max(w[h]);      // (one reduction instruction)
                 if (tile_max == -INFINITY) { w[h] = 0.f; continue; }
                 any_live = true;
                 const float m_new = fmaxf(m_run[h], tile_max);
                 const float factor = (m_run[h] == -INFINITY) ? 0.f : __expf(m_run[h] - m_new);
                 m_run[h] = m_new;
                 w[h] = valid ? __expf(w[h] - m_new) : 0.f;
-                l_run[h] = l_run[h] * factor + warp_sum(w[h]);
+                l_run[h] = l_run[h] * factor + w[h];           // (this lane's share: summed over the warp after the loop)
 #pragma unroll
                 for (int i = 0; i < DPL; ++i) acc[h][i] *= factor;
             } else {
@@ -334,6 +410,21 @@ coded_attend_kernel(const CodedParams p, int key_floats, int vlut_floats) {
             *reinterpret_cast<float4 *>(sh_w + lane * NH) = make_float4(w[0], w[1], w[2], w[3]);
             if constexpr (NH == 8) *reinterpret_cast<float4 *>(sh_w + lane * NH + 4) = make_float4(w[4], w[5], w[6], w[7]);
             __syncwarp();
+            if constexpr (EAGER) {
+                static_assert(NH == 4, "the eager form is instantiated for four heads");
+#pragma unroll
+                for (int j = 0; j < 32; ++j) {
+                    float v[DPL];
+                    decode_v<DPL, VM>(p, early[j], sh_vlut, lane, v);
+                    const float4 wa = *reinterpret_cast<const float4 *>(sh_w + j * NH);   // (0 for rows past the tile's end)
+                    const float wl4[4] = {wa.x, wa.y, wa.z, wa.w};
+#pragma unroll
+                    for (int h = 0; h < 4; ++h)
+#pragma unroll
+                        for (int i = 0; i < DPL; ++i) acc[h][i] = fmaf(wl4[h], v[i], acc[h][i]);
+                }
+                continue;
+            }
             // Two batches of R rows are in flight: the next batch is requested before the
             // current one is consumed.
             constexpr int R = 8;
@@ -384,6 +475,8 @@ coded_attend_kernel(const CodedParams p, int key_floats, int vlut_floats) {
     }
 
     // ---- merge the warps of this CTA -------------------------------------------------------
+#pragma unroll
+    for (int h = 0; h < NH; ++h) l_run[h] = warp_sum(l_run[h]);
     __syncthreads();  // the lookup tables are dead: reuse shared memory
     float *red_o = smem;                                   // [warps][heads][D]
     float *red_m = red_o + kWarpsC * NH * D;          // [warps][heads]
@@ -492,16 +585,6 @@ __device__ __forceinline__ uint32_t st_pack_weights(float x0, float x1, bool low
         if (low) h = __floats2half2_rn(x0 - __low2float(h), x1 - __high2float(h));
         return *reinterpret_cast<uint32_t *>(&h);
     }
-}
-
-// Warp maximum of finite-or-minus-infinity floats in one reduction instruction: floats order like
-// their bit patterns read as sign-magnitude integers, which one XOR turns into two's complement.
-__device__ __forceinline__ float st_warp_max(float x) {
-    int i = __float_as_int(x);
-    i ^= (i >> 31) & 0x7fffffff;
-    i = __reduce_max_sync(0xffffffffu, i);
-    i ^= (i >> 31) & 0x7fffffff;
-    return __int_as_float(i);
 }
 
 template <bool VBF16, int NH>
@@ -862,6 +945,18 @@ int32_t launch_coded(CodedParams &p, void *workspace, int64_t workspace_bytes, i
         }                                                                                                  \
         break;
 #define VQ_CODED_GEN(DPL) case DPL: VQ_CODED_VM(DPL, VM_GENERIC); break;
+    // small grids (at most two CTAs per SM), head_dim 128, dense 16-bit values, up to four heads per kv head: the eager form
+    if (gy * p.B * p.n_splits <= 2 * (int64_t)di.sm_count && dpl == 4 && hpk <= 4 && (vm == VM_F16 || vm == VM_BF16)) {
+        if (smem > 48 * 1024) {
+            VQ_CHECK_CUDA(cudaFuncSetAttribute(coded_attend_kernel<4, VM_F16, 4, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            VQ_CHECK_CUDA(cudaFuncSetAttribute(coded_attend_kernel<4, VM_BF16, 4, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        }
+        if (vm == VM_F16) coded_attend_kernel<4, VM_F16, 4, true><<<grid, kWarpsC * 32, smem, st>>>(p, key_floats, vlut_floats);
+        else coded_attend_kernel<4, VM_BF16, 4, true><<<grid, kWarpsC * 32, smem, st>>>(p, key_floats, vlut_floats);
+        VQ_CHECK_LAUNCH("coded_attend_kernel");
+        if (p.n_splits > 1) return launch_split_merge(p.part_o, p.part_ml, p.n_splits, p.D, p.out, p.out_dtype, rows, st);
+        return VQ_OK;
+    }
     switch (dpl) {
         VQ_CODED_GEN(1) VQ_CODED_FAST(2) VQ_CODED_GEN(3) VQ_CODED_FAST(4) VQ_CODED_GEN(5) VQ_CODED_GEN(6)
         VQ_CODED_GEN(7) VQ_CODED_FAST(8)
