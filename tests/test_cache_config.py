@@ -72,3 +72,27 @@ def test_no_cpu_path():
 def test_builder_layer_lists_validate():
     with pytest.raises(QuantizerConfigError, match="2 entries for 3 layers"):
         KVCacheBuilder.for_layers(3, KVCacheConfig(method="kivi", bit_width_inlier=[2, 4]))
+
+
+def test_named_bit_width_inlier_warns_for_methods_that_ignore_it():
+    """The reference warns when the caller names ``bit_width_inlier`` for a method that never reads
+    it, pointing at the method's own bit-width fields (``cache/base.py:930-955``); a copy made by
+    ``dataclasses.replace`` names every field and does not warn."""
+    import dataclasses
+    import warnings
+
+    from veloxquant_mlx_b200.cache import KVCacheConfig
+
+    with warnings.catch_warnings(record=True) as w:
+        warnings.simplefilter("always")
+        KVCacheConfig(method="kivi", bit_width_inlier=4)
+        KVCacheConfig(method="turboquant_rvq", bit_width_inlier=3)
+        KVCacheConfig(method="skvq")
+        assert not w
+        c = KVCacheConfig(method="skvq", bit_width_inlier=2)
+        assert len(w) == 1 and issubclass(w[0].category, UserWarning)
+        assert "ignores bit_width_inlier=2" in str(w[0].message) and "skvq_bits_key, skvq_bits_value" in str(w[0].message)
+        dataclasses.replace(c, head_dim=64)
+        assert len(w) == 1
+        KVCacheConfig(method="vecinfer", bit_width_inlier=3)
+        assert len(w) == 2 and "own bit-width field" not in str(w[1].message)

@@ -169,6 +169,7 @@ class KVCacheConfig:
             for f in dataclasses.fields(self.options):
                 if f.name in _FIELD_TO_OPTIONS_CLASS and f.name not in explicit:
                     object.__setattr__(self, f.name, getattr(self.options, f.name))
+        _warn_inlier_bits_ignored(self, getattr(self, "_explicit_fields", frozenset()))
         object.__setattr__(self, "_post_init_done", True)
 
     def __setattr__(self, name: str, value: Any) -> None:
@@ -179,6 +180,26 @@ class KVCacheConfig:
                 f"(pass it via KVCacheConfig(options={cls_name}({name}=...))).",
                 DeprecationWarning, stacklevel=2)
         object.__setattr__(self, name, value)
+
+
+# the methods (of this package) whose caches read ``bit_width_inlier``
+_INLIER_BITS_METHODS = frozenset({"kivi", "kivi_sink", "turboquant_rvq"})
+
+
+def _warn_inlier_bits_ignored(config, explicit) -> None:
+    """``UserWarning`` when the caller NAMED ``bit_width_inlier`` for a method that never reads it
+    (reference: ``cache/base.py:930-955``). A copy made by ``dataclasses.replace`` names every field
+    and is not the caller asking for a width: no warning then."""
+    if "bit_width_inlier" not in explicit or config.method in _INLIER_BITS_METHODS:
+        return
+    init_names = {f.name for f in dataclasses.fields(config) if f.init}
+    if explicit >= init_names:
+        return
+    own = sorted(f.name for f in dataclasses.fields(config)
+                 if f.init and "bit" in f.name and f.name.startswith(f"{config.method}_"))
+    hint = f"; this method's own bit-width field is {', '.join(own)}" if own else ""
+    warnings.warn(f"KVCacheConfig(method={config.method!r}) ignores bit_width_inlier={config.bit_width_inlier!r}: only "
+                  f"{', '.join(sorted(_INLIER_BITS_METHODS))} read it{hint}.", UserWarning, stacklevel=5)
 
 
 def _track_explicit_fields(cls):
