@@ -393,7 +393,10 @@ def main():
              "veloxquant_mlx.metal", "veloxquant_mlx.metal.kernels", "veloxquant_mlx.cache", "veloxquant_mlx.cache.kivi_cache",
              "veloxquant_mlx.quantizers", "veloxquant_mlx.quantizers._quant_utils", "veloxquant_mlx.quantizers.skvq",
              "veloxquant_mlx.quantizers.kitty", "veloxquant_mlx.quantizers.age_tiered", "veloxquant_mlx.metal.fused_sdpa",
-             "veloxquant_mlx.allocators", "veloxquant_mlx.allocators.vecinfer"]
+             "veloxquant_mlx.allocators", "veloxquant_mlx.allocators.vecinfer", "veloxquant_mlx.core.context",
+             "veloxquant_mlx.core.abstractions", "veloxquant_mlx.cache.options", "veloxquant_mlx.cache.sliding_window_cache",
+             "veloxquant_mlx.cache.sink_cache", "veloxquant_mlx.cache.skvq_cache", "veloxquant_mlx.cache.kitty_cache",
+             "veloxquant_mlx.cache.age_tiered_cache", "veloxquant_mlx.cache.base"]
     saved = {k: sys.modules.get(k) for k in names}
     try:
         sys.modules["mlx"], sys.modules["mlx.core"] = mlx_pkg, mlx_pkg.core
@@ -477,6 +480,28 @@ def main():
         run("vecinfer", vi_c.VecInferKVCache(vcfg), ["offset", "_key_bytes_compressed", "_value_bytes_compressed", "_key_bytes_fp16",
                                                      "_tokens_seen"], True)
         np.savez_compressed(os.path.join(HERE, "cache_traces.npz"), **out)
+
+        # ------- the configuration layer itself (cache/base.py, cache/options.py), same stand-ins -------
+        import json
+
+        import config_scenarios
+
+        for mod in ("context", "abstractions"):
+            load_module(os.path.join(pkg, "core", mod + ".py"), "veloxquant_mlx.core." + mod)
+        opts = load_module(os.path.join(pkg, "cache", "options.py"), "veloxquant_mlx.cache.options")
+        sw = types.ModuleType("veloxquant_mlx.cache.sliding_window_cache")
+        sw.SlidingWindowKVCache = type("SlidingWindowKVCache", (), {"__init__": lambda self, cache, window_size: None})
+        sys.modules["veloxquant_mlx.cache.sliding_window_cache"] = sw
+        for name, path in (("sink_cache", "sink_cache.py"), ("skvq_cache", "skvq_cache.py"), ("kitty_cache", "kitty_cache.py"),
+                           ("age_tiered_cache", "age_tiered_cache.py")):
+            load_module(os.path.join(pkg, "cache", path), "veloxquant_mlx.cache." + name)
+        base_m = load_module(os.path.join(pkg, "cache", "base.py"), "veloxquant_mlx.cache.base")
+        ns_cfg = types.SimpleNamespace(KVCacheConfig=base_m.KVCacheConfig, KVCacheFactory=base_m.KVCacheFactory,
+                                       VecInferOptions=opts.VecInferOptions, KIVIOptions=opts.KIVIOptions, SKVQOptions=opts.SKVQOptions,
+                                       KittyOptions=opts.KittyOptions, AgeTieredKVOptions=opts.AgeTieredKVOptions)
+        with open(os.path.join(HERE, "config_traces.json"), "w") as fh:
+            json.dump({"config": config_scenarios.scenarios(ns_cfg), "construction": config_scenarios.construction_scenarios(ns_cfg)},
+                      fh, indent=1, sort_keys=True, default=str)
     finally:
         for key, val in saved.items():
             if val is None:

@@ -96,3 +96,57 @@ def test_named_bit_width_inlier_warns_for_methods_that_ignore_it():
         assert len(w) == 1
         KVCacheConfig(method="vecinfer", bit_width_inlier=3)
         assert len(w) == 2 and "own bit-width field" not in str(w[1].message)
+
+
+def _config_namespace():
+    import types
+
+    from veloxquant_mlx_b200 import cache as c
+
+    return types.SimpleNamespace(KVCacheConfig=c.KVCacheConfig, KVCacheFactory=c.KVCacheFactory, VecInferOptions=c.VecInferOptions,
+                                 KIVIOptions=c.KIVIOptions, SKVQOptions=c.SKVQOptions, KittyOptions=c.KittyOptions,
+                                 AgeTieredKVOptions=c.AgeTieredKVOptions)
+
+
+def _load_config_scenarios():
+    import importlib.util
+    import json
+    import os
+
+    here = os.path.join(os.path.dirname(__file__), "golden")
+    spec = importlib.util.spec_from_file_location("config_scenarios", os.path.join(here, "config_scenarios.py"))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    with open(os.path.join(here, "config_traces.json")) as fh:
+        return mod, json.load(fh)
+
+
+def test_configuration_layer_matches_the_reference_config_layer_scenario_by_scenario():
+    """Defaults of every shared field (the default method included), options read-through, an
+    explicitly named flat field beating the options object, the deprecation warning on assigning an
+    options-owned flat field, the ignored-bit-width warning, ``repr``, positional construction and the
+    factory's refusals (unknown method, list-form width, observers, outlier width): the same scenarios
+    (tests/golden/config_scenarios.py) were run by make_golden.py against the reference's own
+    ``cache/base.py`` + ``cache/options.py``; every record (values, warnings, errors) must be equal."""
+    import json
+
+    mod, ref = _load_config_scenarios()
+    mine = json.loads(json.dumps(mod.scenarios(_config_namespace()), default=str))
+    assert set(mine) == set(ref["config"]) and len(mine) >= 19
+    for name, record in ref["config"].items():
+        assert mine[name] == record, name
+
+
+@pytest.mark.gpu
+def test_cache_construction_matches_the_reference_classes_scenario_by_scenario():
+    """Class created per method and every constructor refusal (negative sink count, window of 1, sinks
+    past the window, zero bits, clip factor above 1, hi fraction above 1, boundaries out of order, 17
+    bits, list-form width, a sliding window on a protocol cache): same class names, same error types
+    and messages as the reference's cache classes executed by make_golden.py."""
+    import json
+
+    mod, ref = _load_config_scenarios()
+    mine = json.loads(json.dumps(mod.construction_scenarios(_config_namespace()), default=str))
+    assert set(mine) == set(ref["construction"]) and len(mine) >= 15
+    for name, record in ref["construction"].items():
+        assert mine[name] == record, (name, mine[name], record)

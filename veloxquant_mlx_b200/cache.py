@@ -113,7 +113,7 @@ class KVCacheConfig:
     pure-MLX twin, which does not exist in this package, and is rejected.
     """
 
-    method: str = "kivi"
+    method: str = "turboquant_rvq"   # (the reference's default, cache/base.py)
     head_dim: int = 128
     bit_width_inlier: Any = 2
     bit_width_outlier: Any = None
