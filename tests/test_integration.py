@@ -166,7 +166,8 @@ def test_transformers_adapter_generates_like_the_dynamic_cache_cpu():
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("method,memory_bound", [("kivi", False), ("kivi", True), ("rabitq", True)])
+@pytest.mark.parametrize("method,memory_bound", [("kivi", False), ("kivi", True), ("rabitq", True), ("kivi_sink", False), ("skvq", False),
+                                                 ("kitty", False), ("age_tiered", False), ("turboquant_rvq", False)])
 def test_transformers_model_decodes_over_the_compressed_caches(method, memory_bound):
     """A randomly initialised Llama generates with this package's caches through
     ``patch_model_kv_cache`` + ``patch_hf_for_fused_sdpa``; with 8-bit KIVI the logits stay close
@@ -182,8 +183,14 @@ def test_transformers_model_decodes_over_the_compressed_caches(method, memory_bo
         warnings.simplefilter("ignore")
         ref = model(ids, past_key_values=DynamicCache(config=cfg), use_cache=True)
         kw = dict(method=method, head_dim=128, fused_sdpa_memory_bound=memory_bound)
-        if method == "kivi":
+        if method in ("kivi", "kivi_sink"):
             kw.update(bit_width_inlier=8, residual_length=32)
+        if method == "skvq":
+            kw.update(skvq_bits_key=8, skvq_bits_value=8, skvq_window=32)
+        if method == "turboquant_rvq":
+            kw.update(bit_width_inlier=4)
+        if method not in ("kivi", "kivi_sink", "rabitq"):
+            kw.pop("fused_sdpa_memory_bound")
         first = I.patch_model_kv_cache(model, KVCacheConfig(**kw))
         I.patch_hf_for_fused_sdpa(model)
         assert model.make_cache() is not first and len(first.layers) == 2
@@ -196,9 +203,14 @@ def test_transformers_model_decodes_over_the_compressed_caches(method, memory_bo
         out = model(ids, past_key_values=cache, use_cache=True)
         assert cache.get_seq_length() == 200
         assert fused_calls == ([200, 200] if memory_bound else [])
-        if method == "kivi":
+        if method in ("kivi", "kivi_sink", "skvq"):
             assert float((out.logits.float() - ref.logits.float()).abs().max()) < 0.08
+        if method == "kivi":
             assert cache.layers[0].cache._n_quantized == 160
+        if method == "skvq":
+            assert cache.layers[0].cache.quantized_tokens == 192
+        if method == "age_tiered":
+            assert cache.layers[0].cache.tokens_mid == 2 * 2 * (200 - 128)
         step = model(ids[:, -1:], past_key_values=cache, use_cache=True)
         assert step.logits.shape == (2, 1, 100) and cache.get_seq_length() == 201 and torch.isfinite(step.logits).all()
         assert fused_calls == ([200, 200, 1, 1] if memory_bound else [])
