@@ -131,3 +131,30 @@ def test_age_tiered_cache_equals_the_dense_model(dt):
         _make("age_tiered", head_dim=D, age_recent_boundary=64, age_mid_boundary=32)
     with pytest.raises(QuantizerConfigError, match="age_bits_old"):
         _make("age_tiered", head_dim=D, age_bits_old=0)
+
+
+@pytest.mark.parametrize("method,cfg", [("kitty", dict(kitty_group_size=8)),
+                                        ("age_tiered", dict(age_recent_boundary=20, age_mid_boundary=50, age_group_size=8))])
+def test_saved_and_restored_caches_continue_bit_identically(method, cfg, tmp_path):
+    """``save_prompt_cache`` / ``load_prompt_cache`` of a Kitty and an AgeTieredKV cache mid-sequence:
+    the restored cache returns exactly what the uninterrupted one returns for the tokens that follow."""
+    from veloxquant_mlx_b200.cache import KVCacheConfig
+    from veloxquant_mlx_b200.persistence import load_prompt_cache, save_prompt_cache
+
+    B, H, D = 2, 2, 32
+    rng = np.random.default_rng(9)
+    k = (rng.standard_normal((B, H, 130, D)) * _het(D, 2)[None, None, None, :]).astype(np.float16)
+    v = rng.standard_normal((B, H, 130, D)).astype(np.float16)
+    c = _make(method, head_dim=D, **cfg)
+    c.update_and_fetch(_t(k[:, :, :90]), _t(v[:, :, :90]))
+    c.update_and_fetch(_t(k[:, :, 90:91]), _t(v[:, :, 90:91]))
+    path = str(tmp_path / f"{method}.safetensors")
+    save_prompt_cache(path, [c])
+    (d,) = load_prompt_cache(path, KVCacheConfig(method=method, head_dim=D, **cfg), device=DEV)
+    assert d.offset == 91
+    q = torch.randn(B, 4, 1, D, device=DEV, dtype=torch.float16)
+    assert torch.equal(c.fused_sdpa(q, 0.2), d.fused_sdpa(q, 0.2))
+    for lo, hi in [(91, 92), (92, 120), (120, 121), (121, 130)]:
+        a = c.update_and_fetch(_t(k[:, :, lo:hi]), _t(v[:, :, lo:hi]))
+        b = d.update_and_fetch(_t(k[:, :, lo:hi]), _t(v[:, :, lo:hi]))
+        assert torch.equal(a[0], b[0]) and torch.equal(a[1], b[1])

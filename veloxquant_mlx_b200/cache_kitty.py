@@ -244,6 +244,7 @@ class AgeTieredKVCache(StandaloneProtocol):
         self._tokens_seen_total = self._current_position = 0
         self._age_tiered_bytes = self._full_seq_bytes = 0
         self._dtype = torch.float16
+        self._last = None       # what the last update_and_fetch returned (fused_sdpa attends over it)
 
     def _tier_list(self, n: int):
         return at.assign_age_tiers([self._current_position - (i + 1) for i in range(n)], self._age_recent_boundary, self._age_mid_boundary)
@@ -309,18 +310,25 @@ class AgeTieredKVCache(StandaloneProtocol):
             cut = (g1 - g0) * gs
             self._pack_final(self._raw_k[:, :cut], self._raw_v[:, :cut])
             self._raw_k, self._raw_v = self._raw_k[:, cut:].contiguous(), self._raw_v[:, cut:].contiguous()
+        counts = {t: tiers.count(t) * G for t in (at.RECENT, at.MID, at.OLD)}
+        self._age_tiered_bytes = at.age_tiered_bytes(counts, self._tiers, self._head_dim)
+        self._last = self._dense_view()
+        return self._last[0], self._last[1]
+
+    def _dense_view(self):
+        """``(keys, values)`` ``[B, H, offset, D]``: final groups dequantized, younger groups round-tripped at their tier."""
+        gs, n = self._group_size, self.offset
+        tiers = self._tier_list(n)
+        group_tier = [tiers[g * gs] for g in range(-(-n // gs))]
         outs = []
         for which, raw in (("k", self._raw_k), ("v", self._raw_v)):
             parts = []
             if self._n_final:
                 parts.append(self._dense_final(which))
-            if raw.shape[1]:
+            if raw is not None and raw.shape[1]:
                 parts.append(at.age_tier_quantize_batched(raw, group_tier[self._n_final // gs:], self._tiers, gs))
-            outs.append((parts[0] if len(parts) == 1 else torch.cat(parts, dim=1)).reshape(B, H, n, D))
-        counts = {t: tiers.count(t) * G for t in (at.RECENT, at.MID, at.OLD)}
-        self._age_tiered_bytes = at.age_tiered_bytes(counts, self._tiers, self._head_dim)
-        self._last = outs
-        return outs[0], outs[1]
+            outs.append((parts[0] if len(parts) == 1 else torch.cat(parts, dim=1)).reshape(self._B, self._H, n, self._head_dim))
+        return outs
 
     def fused_sdpa(self, q, scale, *, causal: bool = True, sliding_window: int = 0):
         """PyTorch's attention over what the last ``update_and_fetch`` returned."""
@@ -328,6 +336,8 @@ class AgeTieredKVCache(StandaloneProtocol):
             raise ValueError("AgeTieredKVCache.fused_sdpa: sliding_window is not supported")
         if self.offset == 0:
             raise RuntimeError("AgeTieredKVCache.fused_sdpa: the cache is empty")
+        if getattr(self, "_last", None) is None:      # (restored from state: rebuild what update_and_fetch would have returned)
+            self._last = self._dense_view()
         return _sdpa_dense(q, self._last[0], self._last[1], scale, causal)
 
     def check_status(self) -> None:
@@ -355,6 +365,43 @@ class AgeTieredKVCache(StandaloneProtocol):
             if t is not None:
                 total += t.numel() * t.element_size()
         return total
+
+    @property
+    def state(self):
+        """The stored tensors: packed codes, scale, zero of the final groups (keys, then values; live
+        rows), then the raw rows of the younger groups (keys, values)."""
+        if self.offset == 0:
+            return (None,) * 8
+        gs, n = self._group_size, self._n_final
+        packed = [None] * 6
+        if n:
+            packed = [t[:, :, : n // p].contiguous() for name in ("k", "v") for t, p in zip(self._final[name], (1, gs, gs))]
+        return (*packed, self._raw_k, self._raw_v)
+
+    @state.setter
+    def state(self, v) -> None:
+        kc, ks, kz, vc, vs, vz, rk, rv = v
+        self._final = None if kc is None else {"k": (kc, ks, kz), "v": (vc, vs, vz)}
+        self._n_final = 0 if kc is None else kc.shape[2]
+        self._raw_k, self._raw_v = rk, rv
+        self.offset = self._n_final + (0 if rk is None else rk.shape[1])
+        if rk is not None:
+            self._dtype = rk.dtype
+        self._last = None
+
+    @property
+    def meta_state(self):
+        """Configuration and counters as strings."""
+        return tuple(map(str, (self._head_dim, self._age_recent_boundary, self._age_mid_boundary, *(t.bits for t in self._tiers),
+                               self._group_size, self._B, self._H, self._tokens_seen_total, self._current_position,
+                               self._age_tiered_bytes, self._full_seq_bytes, "bfloat16" if self._dtype == torch.bfloat16 else "float16")))
+
+    @meta_state.setter
+    def meta_state(self, v) -> None:
+        (self._head_dim, self._age_recent_boundary, self._age_mid_boundary, b0, b1, b2, self._group_size, self._B, self._H,
+         self._tokens_seen_total, self._current_position, self._age_tiered_bytes, self._full_seq_bytes) = (int(x) for x in v[:13])
+        self._tiers = at.default_age_tiers(b0, b1, b2)
+        self._dtype = torch.bfloat16 if v[13] == "bfloat16" else torch.float16
 
     age_tiered_bytes = property(lambda self: self._age_tiered_bytes)
     full_seq_bytes = property(lambda self: self._full_seq_bytes)
