@@ -160,3 +160,35 @@ def test_fused_sdpa_vq_long_context_dense_values_and_capacity():
         v.fused_sdpa_vq(q[:, :3], kbuf, cb, vbuf, None, scale, s_kv=S)
     with pytest.raises(ValueError, match="must equal n_sub"):
         v.fused_sdpa_vq(q, kbuf, cb[:, :4], vbuf, None, scale, s_kv=S)
+
+
+@pytest.mark.parametrize("dt,H_q,S_q,stacked,n_c", [("float16", 32, 1, False, 256), ("bfloat16", 16, 1, True, 200), ("float16", 8, 2, False, 256)])
+def test_fused_sdpa_vq_serving_shape_takes_the_staged_kernel(dt, H_q, S_q, stacked, n_c):
+    """Long contexts with byte-wide indices, sub-vectors of 8 and dense 16-bit values (here 2 x 8 kv
+    heads x 16 400 keys in buffers of 16 512 rows) are attended by the staged kernel: indices and value
+    rows through the bulk-copy pipelines, scores from the shared-memory table, the value sum on the
+    tensor cores. Shared and per-sub-space codebooks, fewer than 256 centroids, 4 / 2 / 1 heads per
+    kv head, two unmasked query rows; an explicit split count agrees."""
+    rng = np.random.default_rng(H_q + n_c)
+    v = _v()
+    B, H_kv, S, cap, D = 2, 8, 16400, 16512, 128
+    q, q32 = _cast((rng.standard_normal((B, H_q, S_q, D)) * 0.3).astype(np.float32), dt)
+    vals, v32 = _cast(rng.standard_normal((B, H_kv, S, D)).astype(np.float32), dt)
+    cb32 = rng.standard_normal(((16, n_c, 8) if stacked else (n_c, 8))).astype(np.float32)
+    kidx = rng.integers(0, n_c, (B, H_kv, S, 16)).astype(np.uint8)
+    kbuf = torch.zeros((B, H_kv, cap, 16), dtype=torch.uint8, device=DEV)
+    vbuf = torch.zeros((B, H_kv, cap, D), dtype=_DT[dt], device=DEV)
+    kbuf[:, :, :S], vbuf[:, :, :S] = torch.from_numpy(kidx).to(DEV), vals
+    scale = 1.0 / math.sqrt(D)
+    k_hat = (np.stack([cb32[s][kidx[..., s]] for s in range(16)], axis=-2) if stacked else cb32[kidx]).reshape(B, H_kv, S, D)
+    scores = np.einsum("bhgqd,bhsd->bhgqs", q32.reshape(B, H_kv, H_q // H_kv, S_q, D), k_hat) * scale
+    wts = np.exp(scores - scores.max(-1, keepdims=True))
+    wts /= wts.sum(-1, keepdims=True)
+    ref = np.einsum("bhgqs,bhsd->bhgqd", wts, v32).reshape(B, H_q, S_q, D)
+    cb = torch.from_numpy(cb32).to(DEV)
+    for kw in ({}, {"n_splits": 5}):
+        out = v.fused_sdpa_vq(q, kbuf, cb, vbuf, None, scale, s_kv=S, causal=S_q == 1, out_dtype=torch.float32, **kw)
+        err = np.abs(out.cpu().numpy() - ref)
+        assert np.all(err <= 2e-3 + 1e-2 * np.abs(ref)), f"max err {err.max():.3e}"
+    from veloxquant_mlx_b200 import kernels as k
+    k.attend_status()

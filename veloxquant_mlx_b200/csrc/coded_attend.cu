@@ -587,8 +587,11 @@ __device__ __forceinline__ uint32_t st_pack_weights(float x0, float x1, bool low
     }
 }
 
-template <bool VBF16, int NH>
-__global__ void __launch_bounds__(kStWarps * 32, 4)
+// W = warps per CTA. VQ = the keys are sixteen one-byte codebook indices (the 512-byte "bits" piece of a
+// stage carries them) scored through a lookup table lut[sub][centroid][head] of 64 KB that the CTA builds
+// first: one CTA of eight warps per SM instead of four CTAs of three.
+template <bool VBF16, int NH, int W, bool VQ>
+__global__ void __launch_bounds__(W * 32, VQ ? 1 : 4)
 rabitq_attend_staged_kernel(const CodedParams p, const __grid_constant__ CUtensorMap v_map) {
     extern __shared__ __align__(1024) uint8_t st_raw[];
     constexpr int D = 128;
@@ -607,12 +610,15 @@ rabitq_attend_staged_kernel(const CodedParams p, const __grid_constant__ CUtenso
 
     // shared: stages (1024-byte aligned: the swizzle pattern repeats every 1024 bytes) | barriers |
     // query sign words [NH][4] | query scales [NH] | weights [warp][32][NH]
-    constexpr int kStagesAll = kStWarps * kStStages * kStBytes;
+    constexpr int kStagesAll = W * kStStages * kStBytes;
     uint8_t *stages = st_raw + (size_t)warp * kStStages * kStBytes;
     uint64_t *bars = reinterpret_cast<uint64_t *>(st_raw + kStagesAll);
     uint32_t *sh_qbits = reinterpret_cast<uint32_t *>(st_raw + kStagesAll + 64);
     float *sh_qs = reinterpret_cast<float *>(st_raw + kStagesAll + 64 + NH * 16);
     float *sh_w = reinterpret_cast<float *>(st_raw + kStagesAll + 256) + warp * (32 * NH);
+    // VQ: query rows [NH][128] and the table [16][256] x float4 (one entry = the four heads' partial scores)
+    float *sh_q = reinterpret_cast<float *>(st_raw + kStagesAll + 256) + W * (32 * NH);
+    float4 *lutv = reinterpret_cast<float4 *>(sh_q + NH * D);
     const uint32_t wbar0 = st_smem_u32(bars) + 8u * (warp * kStStages);
     const int g = lane >> 2, c = lane & 3;
     if (st_smem_u32(st_raw) & 1023u) {  // the swizzled addressing below assumes this; never seen
@@ -621,19 +627,51 @@ rabitq_attend_staged_kernel(const CodedParams p, const __grid_constant__ CUtenso
     }
 
     if (threadIdx.x == 0) {
-        for (int i = 0; i < kStWarps * kStStages; ++i)
+        for (int i = 0; i < W * kStStages; ++i)
             asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(st_smem_u32(bars) + 8u * i));
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    for (int h = warp; h < nh; h += kStWarps) {
-        const int64_t qrow = ((int64_t)b * p.H_q + hkv * hpk + h0 + h) * p.S_q + sq;
-#pragma unroll
-        for (int w = 0; w < 4; ++w) {
-            const float v = load_as_f32(p.q, p.q_dtype, qrow * D + 32 * w + lane);
-            const uint32_t bits = __ballot_sync(0xffffffffu, v >= 0.f);
-            if (lane == 0) sh_qbits[h * 4 + w] = bits;
+    if constexpr (VQ) {
+        static_assert(NH == 4, "the table entry holds four heads");
+        for (int i = threadIdx.x; i < NH * D; i += W * 32) {
+            const int h = i / D, d = i % D;
+            const int64_t qrow = ((int64_t)b * p.H_q + hkv * hpk + h0 + h) * p.S_q + sq;
+            sh_q[i] = h < nh ? load_as_f32(p.q, p.q_dtype, qrow * D + d) : 0.f;
         }
-        if (lane == 0) sh_qs[h] = p.q_scale[qrow];
+        __syncthreads();
+        for (int cc = threadIdx.x; cc < 256; cc += W * 32) {
+            const int cen = min(cc, p.k_nc - 1);
+            float cbr[8];
+            for (int sub = 0; sub < 16; ++sub) {
+                if (sub == 0 || p.k_stacked) {
+                    const float4 *cb = reinterpret_cast<const float4 *>(p.k_codebook + ((int64_t)(p.k_stacked ? sub : 0) * p.k_nc + cen) * 8);
+                    const float4 t0 = __ldg(cb), t1 = __ldg(cb + 1);
+                    cbr[0] = t0.x; cbr[1] = t0.y; cbr[2] = t0.z; cbr[3] = t0.w; cbr[4] = t1.x; cbr[5] = t1.y; cbr[6] = t1.z; cbr[7] = t1.w;
+                }
+                float dot[4];
+#pragma unroll
+                for (int h = 0; h < 4; ++h) {
+                    const float4 *qv = reinterpret_cast<const float4 *>(sh_q + h * D + sub * 8);
+                    const float4 u0 = qv[0], u1 = qv[1];
+                    float acc1 = u0.x * cbr[0];
+                    acc1 = fmaf(u0.y, cbr[1], acc1); acc1 = fmaf(u0.z, cbr[2], acc1); acc1 = fmaf(u0.w, cbr[3], acc1);
+                    acc1 = fmaf(u1.x, cbr[4], acc1); acc1 = fmaf(u1.y, cbr[5], acc1); acc1 = fmaf(u1.z, cbr[6], acc1); acc1 = fmaf(u1.w, cbr[7], acc1);
+                    dot[h] = acc1;
+                }
+                lutv[sub * 256 + cc] = make_float4(dot[0], dot[1], dot[2], dot[3]);
+            }
+        }
+    } else {
+        for (int h = warp; h < nh; h += W) {
+            const int64_t qrow = ((int64_t)b * p.H_q + hkv * hpk + h0 + h) * p.S_q + sq;
+#pragma unroll
+            for (int w = 0; w < 4; ++w) {
+                const float v = load_as_f32(p.q, p.q_dtype, qrow * D + 32 * w + lane);
+                const uint32_t bits = __ballot_sync(0xffffffffu, v >= 0.f);
+                if (lane == 0) sh_qbits[h * 4 + w] = bits;
+            }
+            if (lane == 0) sh_qs[h] = p.q_scale[qrow];
+        }
     }
     __syncthreads();
 
@@ -642,20 +680,20 @@ rabitq_attend_staged_kernel(const CodedParams p, const __grid_constant__ CUtenso
     const int t_begin = split * chunk;
     const int t_end = min(p.S_kv, t_begin + chunk);
     const int n_tiles = t_begin < t_end ? (t_end - t_begin + 31) / 32 : 0;
-    const int n_local = warp < n_tiles ? (n_tiles - warp + kStWarps - 1) / kStWarps : 0;
+    const int n_local = warp < n_tiles ? (n_tiles - warp + W - 1) / W : 0;
     const uint8_t *kb_g = reinterpret_cast<const uint8_t *>(p.k_codes) + bh * p.stride_tok * 16;
-    const float *km_g = p.k_mag + bh * p.stride_tok;
-    const float *kc_g = p.k_const ? p.k_const + bh * p.stride_tok : nullptr;
+    const float *km_g = VQ ? nullptr : p.k_mag + bh * p.stride_tok;
+    const float *kc_g = (!VQ && p.k_const) ? p.k_const + bh * p.stride_tok : nullptr;
 
     auto issue = [&](int j) {  // lane 0 only
-        const int64_t tile = t_begin + 32 * (warp + kStWarps * j);
+        const int64_t tile = t_begin + 32 * (warp + W * j);
         const int stage = j % kStStages;
         const uint32_t bar = wbar0 + 8u * stage;
         const uint32_t dst = st_smem_u32(stages + (size_t)stage * kStBytes);
-        const uint32_t bytes = 512 + 128 + (kc_g ? 128 : 0) + 32 * 256;
+        const uint32_t bytes = 512 + (VQ ? 0 : 128) + (kc_g ? 128 : 0) + 32 * 256;
         asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
         st_bulk_g2s(dst, kb_g + tile * 16, 512, bar);
-        st_bulk_g2s(dst + kStMag, km_g + tile, 128, bar);
+        if constexpr (!VQ) st_bulk_g2s(dst + kStMag, km_g + tile, 128, bar);
         if (kc_g) st_bulk_g2s(dst + kStConst, kc_g + tile, 128, bar);
         // the value rows: channels 0-63 and 64-127 as two swizzled boxes; rows past the context read as zeros
         st_tensor_g2s(dst + kStV, &v_map, 0, (int)tile, (int)bh, bar);
@@ -683,19 +721,33 @@ rabitq_attend_staged_kernel(const CodedParams p, const __grid_constant__ CUtenso
         const int stage = j % kStStages;
         if (!timed_out && !st_mbar_wait(wbar0 + 8u * stage, (uint32_t)((j / kStStages) & 1))) timed_out = true;
         const uint8_t *st = stages + (size_t)stage * kStBytes;
-        const int tile = t_begin + 32 * (warp + kStWarps * j);
+        const int tile = t_begin + 32 * (warp + W * j);
         const bool valid = tile + lane < t_end;
         // ---- scores of this lane's key against every head ---------------------------------
         const uint4 kw = *reinterpret_cast<const uint4 *>(st + lane * 16);
-        const float km = reinterpret_cast<const float *>(st + kStMag)[lane];
-        const float kc = kc_g ? reinterpret_cast<const float *>(st + kStConst)[lane] : 0.f;
         float w[NH];
+        if constexpr (VQ) {
+            // sixteen table reads of 16 bytes: one entry holds this centroid's partial score for all four heads
+            const uint32_t wd[4] = {kw.x, kw.y, kw.z, kw.w};
+            float4 sacc = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
-        for (int h = 0; h < NH; ++h) {
-            const uint32_t *qb = sh_qbits + (h < nh ? h : 0) * 4;
-            const int ham = __popc(qb[0] ^ kw.x) + __popc(qb[1] ^ kw.y) + __popc(qb[2] ^ kw.z) + __popc(qb[3] ^ kw.w);
-            const float s = ((float)D - 2.0f * (float)ham) * sh_qs[h < nh ? h : 0] * km + kc;
-            w[h] = valid ? s : -INFINITY;
+            for (int sub = 0; sub < 16; ++sub) {
+                const uint32_t cen = (wd[sub >> 2] >> (8 * (sub & 3))) & 0xFFu;
+                const float4 e = lutv[sub * 256 + cen];
+                sacc.x += e.x; sacc.y += e.y; sacc.z += e.z; sacc.w += e.w;
+            }
+            w[0] = valid ? sacc.x * p.scale : -INFINITY; w[1] = valid ? sacc.y * p.scale : -INFINITY;
+            w[2] = valid ? sacc.z * p.scale : -INFINITY; w[3] = valid ? sacc.w * p.scale : -INFINITY;
+        } else {
+            const float km = reinterpret_cast<const float *>(st + kStMag)[lane];
+            const float kc = kc_g ? reinterpret_cast<const float *>(st + kStConst)[lane] : 0.f;
+#pragma unroll
+            for (int h = 0; h < NH; ++h) {
+                const uint32_t *qb = sh_qbits + (h < nh ? h : 0) * 4;
+                const int ham = __popc(qb[0] ^ kw.x) + __popc(qb[1] ^ kw.y) + __popc(qb[2] ^ kw.z) + __popc(qb[3] ^ kw.w);
+                const float s = ((float)D - 2.0f * (float)ham) * sh_qs[h < nh ? h : 0] * km + kc;
+                w[h] = valid ? s : -INFINITY;
+            }
         }
         // ---- online softmax per head ------------------------------------------------------
         float factor[NH];
@@ -768,8 +820,8 @@ rabitq_attend_staged_kernel(const CodedParams p, const __grid_constant__ CUtenso
     // ---- merge the warps of this CTA (the stages are drained: reuse them) ----------------------
     __syncthreads();
     float *red_o = reinterpret_cast<float *>(st_raw);  // [warps][heads][D]
-    float *red_m = red_o + kStWarps * NH * D;
-    float *red_l = red_m + kStWarps * NH;
+    float *red_m = red_o + W * NH * D;
+    float *red_l = red_m + W * NH;
 #pragma unroll
     for (int mt = 0; mt < 8; ++mt) {
         const int d0 = 16 * mt + g;
@@ -791,9 +843,9 @@ rabitq_attend_staged_kernel(const CodedParams p, const __grid_constant__ CUtenso
     for (int i = threadIdx.x; i < nh * D; i += blockDim.x) {
         const int h = i / D, d = i % D;
         float gm = -INFINITY;
-        for (int wq = 0; wq < kStWarps; ++wq) gm = fmaxf(gm, red_m[wq * NH + h]);
+        for (int wq = 0; wq < W; ++wq) gm = fmaxf(gm, red_m[wq * NH + h]);
         float gl = 0.f, o = 0.f;
-        for (int wq = 0; wq < kStWarps; ++wq) {
+        for (int wq = 0; wq < W; ++wq) {
             const float mw = red_m[wq * NH + h];
             const float f = (mw == -INFINITY) ? 0.f : __expf(mw - gm);
             gl += red_l[wq * NH + h] * f;
@@ -815,13 +867,22 @@ rabitq_attend_staged_kernel(const CodedParams p, const __grid_constant__ CUtenso
 // Can `p` take the staged kernel? Whole tiles are copied, so the buffers must hold the context
 // rounded up to 32 keys, and every copied piece must start on a 16-byte boundary.
 bool staged_ok(const CodedParams &p) {
-    if (p.key_mode != KEY_RABITQ || p.D != 128 || p.v_mode != V_DENSE) return false;
+    if (p.D != 128 || p.v_mode != V_DENSE) return false;
     if (p.v_dtype != VQ_F16 && p.v_dtype != VQ_BF16) return false;
     if (p.stride_tok % 4 || p.stride_tok < (((int64_t)p.S_kv + 31) & ~(int64_t)31)) return false;
-    if (!is_aligned(p.k_codes, 16) || !is_aligned(p.k_mag, 16) || !is_aligned(p.v, 16)) return false;
+    if (!is_aligned(p.k_codes, 16) || !is_aligned(p.v, 16)) return false;
+    if (p.key_mode == KEY_VQ) {
+        // sixteen one-byte indices per key, up to 256 centroids of 8, at most four heads per kv head, and
+        // enough keys per CTA to pay for the table (a short context takes the plain kernel)
+        // (the staged kernel applies no mask: one query row, or several without a causal mask, and no window)
+        return p.k_sub == 8 && p.k_index_bytes == 1 && p.k_nc <= 256 && p.H_q / p.H_kv <= 4 && is_aligned(p.k_codebook, 16) &&
+               p.window == 0 && (!p.causal || p.S_q == 1) && (int64_t)p.S_kv * p.B * p.H_kv * p.S_q >= (int64_t)1 << 18;
+    }
+    if (!is_aligned(p.k_mag, 16)) return false;
     if (p.k_const && !is_aligned(p.k_const, 16)) return false;
     return true;
 }
+constexpr int kVqStWarps = 8;   // warps of the lookup-table form (one CTA per SM)
 
 // Split count for a kernel that keeps `per_sm` CTAs of this kind resident per SM: the count
 // that minimises (waves of CTAs) x (keys per CTA + a fixed set-up cost in keys), so that the
@@ -866,8 +927,9 @@ int32_t launch_coded(CodedParams &p, void *workspace, int64_t workspace_bytes, i
     p.n_head_chunks = (int)ceil_div(hpk, kHeadsC);
     const int64_t gy = (int64_t)p.H_kv * p.S_q * p.n_head_chunks;
     VQ_REQUIRE(gy <= 65535 && p.B <= 65535, VQ_ERR_SHAPE, "%s: grid too large", who);
-    p.n_splits = staged_ok(p) ? pick_splits_waves(requested_splits, p.S_kv, gy * p.B, di.sm_count, 4, 32)
-                              : pick_splits(requested_splits, p.S_kv, gy * p.B, di.sm_count);
+    p.n_splits = !staged_ok(p)           ? pick_splits(requested_splits, p.S_kv, gy * p.B, di.sm_count)
+                 : p.key_mode == KEY_VQ ? pick_splits_waves(requested_splits, p.S_kv, gy * p.B, di.sm_count, 1, 32 * kVqStWarps)
+                                        : pick_splits_waves(requested_splits, p.S_kv, gy * p.B, di.sm_count, 4, 32);
     const int64_t rows = (int64_t)p.B * p.H_q * p.S_q;
     if (p.n_splits > 1) {
         const int64_t need = rows * p.n_splits * ((int64_t)p.D + 2) * (int64_t)sizeof(float);
@@ -875,6 +937,26 @@ int32_t launch_coded(CodedParams &p, void *workspace, int64_t workspace_bytes, i
                    "%s: workspace of %lld bytes needed, %lld given", who, (long long)need, (long long)workspace_bytes);
         p.part_o = (float *)workspace;
         p.part_ml = p.part_o + rows * p.n_splits * p.D;
+    }
+    if (staged_ok(p) && p.key_mode == KEY_VQ) {
+        constexpr int Wv = kVqStWarps;
+        static_assert((size_t)Wv * kStStages * kStBytes >= ((size_t)Wv * 4 * 128 + 2 * Wv * 4) * sizeof(float), "the warp merge reuses the stages");
+        const size_t st_smem = (size_t)Wv * kStStages * kStBytes + 256 + (size_t)Wv * 32 * 4 * 4 + 4 * 128 * 4 + 16 * 256 * 16;
+        VQ_REQUIRE(st_smem <= di.smem_optin, VQ_ERR_CAPACITY, "%s: %zu bytes of shared memory needed", who, st_smem);
+        dim3 sgrid(p.n_splits, (unsigned)gy, p.B);
+        CUtensorMap v_map;
+        rc = make_rows_map(3, p.v, 256, p.S_kv, p.stride_tok * 256, p.B * p.H_kv, 128, 32, &v_map);
+        if (rc != VQ_OK) return rc;
+        if (p.v_dtype == VQ_BF16) {
+            VQ_CHECK_CUDA(cudaFuncSetAttribute(rabitq_attend_staged_kernel<true, 4, Wv, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)st_smem));
+            rabitq_attend_staged_kernel<true, 4, Wv, true><<<sgrid, Wv * 32, st_smem, st>>>(p, v_map);
+        } else {
+            VQ_CHECK_CUDA(cudaFuncSetAttribute(rabitq_attend_staged_kernel<false, 4, Wv, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)st_smem));
+            rabitq_attend_staged_kernel<false, 4, Wv, true><<<sgrid, Wv * 32, st_smem, st>>>(p, v_map);
+        }
+        VQ_CHECK_LAUNCH("staged lookup-table attention kernel");
+        if (p.n_splits > 1) return launch_split_merge(p.part_o, p.part_ml, p.n_splits, p.D, p.out, p.out_dtype, rows, st);
+        return VQ_OK;
     }
     if (staged_ok(p)) {
         const int nh_s = hpk <= 4 ? 4 : kHeadsC;
@@ -888,9 +970,9 @@ int32_t launch_coded(CodedParams &p, void *workspace, int64_t workspace_bytes, i
         if (rc != VQ_OK) return rc;
 #define VQ_STAGED(BF, NHT)                                                                                      \
     do {                                                                                                        \
-        VQ_CHECK_CUDA(cudaFuncSetAttribute(rabitq_attend_staged_kernel<BF, NHT>,                                 \
+        VQ_CHECK_CUDA(cudaFuncSetAttribute(rabitq_attend_staged_kernel<BF, NHT, kStWarps, false>,                \
                                            cudaFuncAttributeMaxDynamicSharedMemorySize, (int)st_smem));         \
-        rabitq_attend_staged_kernel<BF, NHT><<<sgrid, kStWarps * 32, st_smem, st>>>(p, v_map);                  \
+        rabitq_attend_staged_kernel<BF, NHT, kStWarps, false><<<sgrid, kStWarps * 32, st_smem, st>>>(p, v_map); \
     } while (0)
         if (p.v_dtype == VQ_BF16) { if (nh_s == 4) VQ_STAGED(true, 4); else VQ_STAGED(true, 8); }
         else { if (nh_s == 4) VQ_STAGED(false, 4); else VQ_STAGED(false, 8); }
