@@ -769,6 +769,14 @@ def run_extras(torch, dist, timer, w, plan, world, rank, device, dtype, px, args
         extra["vq_attend_config2"] = {"shape": [1, 8, 4096, D], "us": ms * 1e3, "GBps": nb / (ms * 1e-3) / 1e9,
                                       "note": "8.9 MB: bound by per-CTA set-up (lookup tables) and load latency, not by HBM"}
         del kx, kix, qx
+        # ... and at a serving shape (batch 8, 16 384 keys): the staged tensor-core kernel with the score table in shared memory
+        kx = torch.randn(8, 8, 16384, D, device=device, dtype=torch.float16)
+        kix = vi.quantize_vq(kx, cbk, 8, index_dtype=torch.uint8)
+        qx = torch.randn(8, 32, 1, D, device=device, dtype=torch.float16)
+        ms = graph_time(lambda: vi.fused_sdpa_vq(qx, kix, cbk, kx, None, D ** -0.5), 10)
+        nb = kix.numel() + kx.numel() * 2
+        extra["vq_attend_serving"] = {"shape": [8, 8, 16384, D], "us": ms * 1e3, "GBps": nb / (ms * 1e-3) / 1e9, "frac": nb / (ms * 1e-3) / 1e9 / peak}
+        del kx, kix, qx
 
         # -- TurboQuant-RVQ: quantize+pack and unpack+decode of 1 Mi rotated keys
         from veloxquant_mlx_b200 import rvq
