@@ -111,6 +111,13 @@ def op_vq_attend(a):
     q = torch.randn(1, 32, 1, 128, device="cuda", dtype=torch.float16)
     us = _time_us(lambda: vi.fused_sdpa_vq(q, kidx, cb, v, None, 0.088), a.iters)
     _line("vq_attend", f"H_q=32 H_kv=8 S={S} dense f16 values", us, nbytes=kidx.numel() + v.numel() * 2)
+    # a serving shape (batch 8, 16 384 keys): the staged tensor-core kernel with the score table in shared memory
+    B, S = 8, 16384
+    v = torch.randn(B, 8, S, 128, device="cuda", dtype=torch.float16)
+    kidx = vi.quantize_vq(v, cb, 8, index_dtype=torch.uint8)
+    q = torch.randn(B, 32, 1, 128, device="cuda", dtype=torch.float16)
+    us = _time_us(lambda: vi.fused_sdpa_vq(q, kidx, cb, v, None, 0.088), a.iters)
+    _line("vq_attend", f"B={B} H_q=32 H_kv=8 S={S} dense f16 values", us, nbytes=kidx.numel() + v.numel() * 2)
 
 
 def op_rabitq(a):
