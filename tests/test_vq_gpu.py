@@ -190,5 +190,17 @@ def test_fused_sdpa_vq_serving_shape_takes_the_staged_kernel(dt, H_q, S_q, stack
         out = v.fused_sdpa_vq(q, kbuf, cb, vbuf, None, scale, s_kv=S, causal=S_q == 1, out_dtype=torch.float32, **kw)
         err = np.abs(out.cpu().numpy() - ref)
         assert np.all(err <= 2e-3 + 1e-2 * np.abs(ref)), f"max err {err.max():.3e}"
+    # values as codebook indices too (what the VecInfer cache stores): the warp expands them into the value tile
+    n_cv = 256 if n_c == 256 else 77
+    vcb32 = rng.standard_normal((n_cv, 8)).astype(np.float32)
+    vidx = rng.integers(0, n_cv, (B, H_kv, S, 16)).astype(np.uint8)
+    vibuf = torch.zeros((B, H_kv, cap, 16), dtype=torch.uint8, device=DEV)
+    vibuf[:, :, :S] = torch.from_numpy(vidx).to(DEV)
+    ref_v = np.einsum("bhgqs,bhsd->bhgqd", wts, vcb32[vidx].reshape(B, H_kv, S, D)).reshape(B, H_q, S_q, D)
+    for kw in ({}, {"n_splits": 3}):
+        out = v.fused_sdpa_vq(q, kbuf, cb, vibuf, torch.from_numpy(vcb32).to(DEV), scale, s_kv=S, causal=S_q == 1,
+                              out_dtype=torch.float32, **kw)
+        err = np.abs(out.cpu().numpy() - ref_v)
+        assert np.all(err <= 2e-3 + 1e-2 * np.abs(ref_v)), f"coded values: max err {err.max():.3e}"
     from veloxquant_mlx_b200 import kernels as k
     k.attend_status()

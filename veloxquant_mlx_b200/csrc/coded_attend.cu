@@ -587,10 +587,12 @@ __device__ __forceinline__ uint32_t st_pack_weights(float x0, float x1, bool low
     }
 }
 
-// W = warps per CTA. VQ = the keys are sixteen one-byte codebook indices (the 512-byte "bits" piece of a
-// stage carries them) scored through a lookup table lut[sub][centroid][head] of 64 KB that the CTA builds
-// first: one CTA of eight warps per SM instead of four CTAs of three.
-template <bool VBF16, int NH, int W, bool VQ>
+// W = warps per CTA. VQ != 0: the keys are sixteen one-byte codebook indices (the 512-byte "bits" piece of
+// a stage carries them) scored through a lookup table lut[sub][centroid][head] of 64 KB that the CTA builds
+// first: one CTA of eight warps per SM instead of four CTAs of three. VQ == 2: the values are sixteen
+// one-byte indices as well (a second 512-byte piece); the warp expands them through a float16 copy of the
+// value codebook into the stage's value tile, in the layout the swizzled tensor copy would have left.
+template <bool VBF16, int NH, int W, int VQ>
 __global__ void __launch_bounds__(W * 32, VQ ? 1 : 4)
 rabitq_attend_staged_kernel(const CodedParams p, const __grid_constant__ CUtensorMap v_map) {
     extern __shared__ __align__(1024) uint8_t st_raw[];
@@ -619,6 +621,8 @@ rabitq_attend_staged_kernel(const CodedParams p, const __grid_constant__ CUtenso
     // VQ: query rows [NH][128] and the table [16][256] x float4 (one entry = the four heads' partial scores)
     float *sh_q = reinterpret_cast<float *>(st_raw + kStagesAll + 256) + W * (32 * NH);
     float4 *lutv = reinterpret_cast<float4 *>(sh_q + NH * D);
+    constexpr bool VV = VQ == 2;
+    __half *sh_vcb = reinterpret_cast<__half *>(lutv + 16 * 256);   // VV: value centroids [256][8] as halves
     const uint32_t wbar0 = st_smem_u32(bars) + 8u * (warp * kStStages);
     const int g = lane >> 2, c = lane & 3;
     if (st_smem_u32(st_raw) & 1023u) {  // the swizzled addressing below assumes this; never seen
@@ -637,6 +641,10 @@ rabitq_attend_staged_kernel(const CodedParams p, const __grid_constant__ CUtenso
             const int h = i / D, d = i % D;
             const int64_t qrow = ((int64_t)b * p.H_q + hkv * hpk + h0 + h) * p.S_q + sq;
             sh_q[i] = h < nh ? load_as_f32(p.q, p.q_dtype, qrow * D + d) : 0.f;
+        }
+        if constexpr (VV) {
+            for (int i = threadIdx.x; i < 256 * 8; i += W * 32)
+                sh_vcb[i] = __float2half_rn(p.v_codebook[(int64_t)min(i >> 3, p.v_nc - 1) * 8 + (i & 7)]);
         }
         __syncthreads();
         for (int cc = threadIdx.x; cc < 256; cc += W * 32) {
@@ -682,6 +690,7 @@ rabitq_attend_staged_kernel(const CodedParams p, const __grid_constant__ CUtenso
     const int n_tiles = t_begin < t_end ? (t_end - t_begin + 31) / 32 : 0;
     const int n_local = warp < n_tiles ? (n_tiles - warp + W - 1) / W : 0;
     const uint8_t *kb_g = reinterpret_cast<const uint8_t *>(p.k_codes) + bh * p.stride_tok * 16;
+    const uint8_t *vb_g = VV ? reinterpret_cast<const uint8_t *>(p.v) + bh * p.stride_tok * 16 : nullptr;
     const float *km_g = VQ ? nullptr : p.k_mag + bh * p.stride_tok;
     const float *kc_g = (!VQ && p.k_const) ? p.k_const + bh * p.stride_tok : nullptr;
 
@@ -690,9 +699,13 @@ rabitq_attend_staged_kernel(const CodedParams p, const __grid_constant__ CUtenso
         const int stage = j % kStStages;
         const uint32_t bar = wbar0 + 8u * stage;
         const uint32_t dst = st_smem_u32(stages + (size_t)stage * kStBytes);
-        const uint32_t bytes = 512 + (VQ ? 0 : 128) + (kc_g ? 128 : 0) + 32 * 256;
+        const uint32_t bytes = VV ? 1024u : 512 + (VQ ? 0 : 128) + (kc_g ? 128 : 0) + 32 * 256;
         asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
         st_bulk_g2s(dst, kb_g + tile * 16, 512, bar);
+        if constexpr (VV) {
+            st_bulk_g2s(dst + 512, vb_g + tile * 16, 512, bar);   // the value indices (the value tile is built by the warp)
+            return;
+        }
         if constexpr (!VQ) st_bulk_g2s(dst + kStMag, km_g + tile, 128, bar);
         if (kc_g) st_bulk_g2s(dst + kStConst, kc_g + tile, 128, bar);
         // the value rows: channels 0-63 and 64-127 as two swizzled boxes; rows past the context read as zeros
@@ -798,6 +811,20 @@ rabitq_attend_staged_kernel(const CodedParams p, const __grid_constant__ CUtenso
                 pb[ks][1] = st_pack_weights<VBF16>(wp[8 * NH], wp[9 * NH], low);
             }
         }
+        if constexpr (VV) {
+            // this lane's key: sixteen centroids of 8 channels = sixteen 16-byte chunks of its 256-byte value
+            // row, stored where the 128-byte-swizzled tensor copy would have put them
+            const uint4 vw = *reinterpret_cast<const uint4 *>(st + 512 + lane * 16);
+            const uint32_t vd[4] = {vw.x, vw.y, vw.z, vw.w};
+            uint8_t *vt = const_cast<uint8_t *>(st) + kStV + lane * 128;
+#pragma unroll
+            for (int sub = 0; sub < 16; ++sub) {
+                const uint32_t cen = min((vd[sub >> 2] >> (8 * (sub & 3))) & 0xFFu, (uint32_t)(p.v_nc - 1));
+                const uint4 val = *reinterpret_cast<const uint4 *>(sh_vcb + cen * 8);
+                *reinterpret_cast<uint4 *>(vt + (sub >> 3) * 4096 + (((sub & 7) ^ (lane & 7)) << 4)) = val;
+            }
+            __syncwarp();
+        }
         // ---- O^T += V^T . P on the tensor cores ---------------------------------------------
         const uint32_t v_base = st_smem_u32(st + kStV);
 #pragma unroll
@@ -867,8 +894,10 @@ rabitq_attend_staged_kernel(const CodedParams p, const __grid_constant__ CUtenso
 // Can `p` take the staged kernel? Whole tiles are copied, so the buffers must hold the context
 // rounded up to 32 keys, and every copied piece must start on a 16-byte boundary.
 bool staged_ok(const CodedParams &p) {
-    if (p.D != 128 || p.v_mode != V_DENSE) return false;
-    if (p.v_dtype != VQ_F16 && p.v_dtype != VQ_BF16) return false;
+    if (p.D != 128) return false;
+    // values: dense 16-bit rows, or (with VQ keys) sixteen one-byte indices into at most 256 centroids of 8
+    const bool vq_values = p.key_mode == KEY_VQ && p.v_mode == V_VQ && p.v_index_bytes == 1 && p.v_sub == 8 && p.v_nc <= 256;
+    if (!vq_values && (p.v_mode != V_DENSE || (p.v_dtype != VQ_F16 && p.v_dtype != VQ_BF16))) return false;
     if (p.stride_tok % 4 || p.stride_tok < (((int64_t)p.S_kv + 31) & ~(int64_t)31)) return false;
     if (!is_aligned(p.k_codes, 16) || !is_aligned(p.v, 16)) return false;
     if (p.key_mode == KEY_VQ) {
@@ -941,18 +970,26 @@ int32_t launch_coded(CodedParams &p, void *workspace, int64_t workspace_bytes, i
     if (staged_ok(p) && p.key_mode == KEY_VQ) {
         constexpr int Wv = kVqStWarps;
         static_assert((size_t)Wv * kStStages * kStBytes >= ((size_t)Wv * 4 * 128 + 2 * Wv * 4) * sizeof(float), "the warp merge reuses the stages");
-        const size_t st_smem = (size_t)Wv * kStStages * kStBytes + 256 + (size_t)Wv * 32 * 4 * 4 + 4 * 128 * 4 + 16 * 256 * 16;
+        const bool vv = p.v_mode == V_VQ;
+        const size_t st_smem = (size_t)Wv * kStStages * kStBytes + 256 + (size_t)Wv * 32 * 4 * 4 + 4 * 128 * 4 + 16 * 256 * 16 + (vv ? 256 * 8 * 2 : 0);
         VQ_REQUIRE(st_smem <= di.smem_optin, VQ_ERR_CAPACITY, "%s: %zu bytes of shared memory needed", who, st_smem);
         dim3 sgrid(p.n_splits, (unsigned)gy, p.B);
-        CUtensorMap v_map;
+        CUtensorMap v_map = {};
+        if (vv) {   // coded values: no tensor copies, the value tile is built in shared memory
+            VQ_CHECK_CUDA(cudaFuncSetAttribute(rabitq_attend_staged_kernel<false, 4, Wv, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)st_smem));
+            rabitq_attend_staged_kernel<false, 4, Wv, 2><<<sgrid, Wv * 32, st_smem, st>>>(p, v_map);
+            VQ_CHECK_LAUNCH("staged lookup-table attention kernel");
+            if (p.n_splits > 1) return launch_split_merge(p.part_o, p.part_ml, p.n_splits, p.D, p.out, p.out_dtype, rows, st);
+            return VQ_OK;
+        }
         rc = make_rows_map(3, p.v, 256, p.S_kv, p.stride_tok * 256, p.B * p.H_kv, 128, 32, &v_map);
         if (rc != VQ_OK) return rc;
         if (p.v_dtype == VQ_BF16) {
-            VQ_CHECK_CUDA(cudaFuncSetAttribute(rabitq_attend_staged_kernel<true, 4, Wv, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)st_smem));
-            rabitq_attend_staged_kernel<true, 4, Wv, true><<<sgrid, Wv * 32, st_smem, st>>>(p, v_map);
+            VQ_CHECK_CUDA(cudaFuncSetAttribute(rabitq_attend_staged_kernel<true, 4, Wv, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)st_smem));
+            rabitq_attend_staged_kernel<true, 4, Wv, 1><<<sgrid, Wv * 32, st_smem, st>>>(p, v_map);
         } else {
-            VQ_CHECK_CUDA(cudaFuncSetAttribute(rabitq_attend_staged_kernel<false, 4, Wv, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)st_smem));
-            rabitq_attend_staged_kernel<false, 4, Wv, true><<<sgrid, Wv * 32, st_smem, st>>>(p, v_map);
+            VQ_CHECK_CUDA(cudaFuncSetAttribute(rabitq_attend_staged_kernel<false, 4, Wv, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)st_smem));
+            rabitq_attend_staged_kernel<false, 4, Wv, 1><<<sgrid, Wv * 32, st_smem, st>>>(p, v_map);
         }
         VQ_CHECK_LAUNCH("staged lookup-table attention kernel");
         if (p.n_splits > 1) return launch_split_merge(p.part_o, p.part_ml, p.n_splits, p.D, p.out, p.out_dtype, rows, st);
@@ -970,9 +1007,9 @@ int32_t launch_coded(CodedParams &p, void *workspace, int64_t workspace_bytes, i
         if (rc != VQ_OK) return rc;
 #define VQ_STAGED(BF, NHT)                                                                                      \
     do {                                                                                                        \
-        VQ_CHECK_CUDA(cudaFuncSetAttribute(rabitq_attend_staged_kernel<BF, NHT, kStWarps, false>,                \
+        VQ_CHECK_CUDA(cudaFuncSetAttribute(rabitq_attend_staged_kernel<BF, NHT, kStWarps, 0>,                \
                                            cudaFuncAttributeMaxDynamicSharedMemorySize, (int)st_smem));         \
-        rabitq_attend_staged_kernel<BF, NHT, kStWarps, false><<<sgrid, kStWarps * 32, st_smem, st>>>(p, v_map); \
+        rabitq_attend_staged_kernel<BF, NHT, kStWarps, 0><<<sgrid, kStWarps * 32, st_smem, st>>>(p, v_map); \
     } while (0)
         if (p.v_dtype == VQ_BF16) { if (nh_s == 4) VQ_STAGED(true, 4); else VQ_STAGED(true, 8); }
         else { if (nh_s == 4) VQ_STAGED(false, 4); else VQ_STAGED(false, 8); }
