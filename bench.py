@@ -776,7 +776,12 @@ def run_extras(torch, dist, timer, w, plan, world, rank, device, dtype, px, args
         ms = graph_time(lambda: vi.fused_sdpa_vq(qx, kix, cbk, kx, None, D ** -0.5), 10)
         nb = kix.numel() + kx.numel() * 2
         extra["vq_attend_serving"] = {"shape": [8, 8, 16384, D], "us": ms * 1e3, "GBps": nb / (ms * 1e-3) / 1e9, "frac": nb / (ms * 1e-3) / 1e9 / peak}
-        del kx, kix, qx
+        # ... and with the values as codebook indices too (what VecInferKVCache stores: 32 bytes per key)
+        vix = torch.randint(0, 256, (8, 8, 16384, 16), device=device, dtype=torch.uint8)
+        ms = graph_time(lambda: vi.fused_sdpa_vq(qx, kix, cbk, vix, cbk, D ** -0.5), 10)
+        extra["vq_attend_serving_coded_values"] = {"shape": [8, 8, 16384, D], "us": ms * 1e3, "keys_per_us": 8 * 8 * 16384 / (ms * 1e3),
+                                                    "note": "33.5 MB: bound by the expansion of the value tile and the table gathers, not by HBM"}
+        del kx, kix, qx, vix
 
         # -- TurboQuant-RVQ: quantize+pack and unpack+decode of 1 Mi rotated keys
         from veloxquant_mlx_b200 import rvq
