@@ -32,6 +32,17 @@ What is executed from the reference, unmodified:
 
 * ``quantizers/_quant_utils.py``, ``quantizers/kitty.py`` and ``quantizers/age_tiered.py`` are loaded
   whole over the same stand-in (``_quant_utils`` registered under its package path first).
+* Extracted by name and executed over the same stand-in: ``quantize_vq`` / ``dequantize_vq``
+  (``allocators/vecinfer.py``), ``_reference_sdpa`` (``tests/cache/test_vecinfer_fused_sdpa.py``),
+  ``_memory_bound_mask_parameters`` (``metal/fused_sdpa.py``), and the helper functions of
+  ``cache/turboquant_rvq_cache.py`` (word packing, norm split, rescale).
+* The cache CLASSES ``cache/kivi_cache.py``, ``sink_cache.py``, ``skvq_cache.py``, ``kitty_cache.py``,
+  ``age_tiered_cache.py``, ``vecinfer_cache.py`` and the configuration layer ``cache/base.py`` +
+  ``cache/options.py`` are loaded whole over the stand-in with stubs for their other imports: a
+  minimal container (``_GrowingKV``, written here) for the ``mlx_lm`` class they derive from,
+  ``metal_available() = False``, the real ``core/exceptions.py``, ``core/context.py``,
+  ``core/abstractions.py``. Their traces over a call script go to ``cache_traces.npz``; the scenario
+  records of ``config_scenarios.py`` to ``config_traces.json``.
 
 Nothing here imports the oracle: the fixtures are the reference's outputs and
 the oracle is checked against them by ``tests/test_oracle_golden.py``.
