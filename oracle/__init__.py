@@ -22,12 +22,18 @@ Pinning status (what anchors these restatements to the reference itself):
 * ``rabitq``   -- pinned: fixtures from the reference's ``_wht_butterfly/
   _reference_encode/_reference_attend/_pack_np`` test functions and from
   ``math/rotation.py`` executed here.
-* ``vq``       -- ``quantize_vq`` index parity is UNPINNED at the bit level
-  ("parity unpinned"): the reference's arithmetic for it lives in MLX
-  (``mx.sum``/``mx.argmin``), which is not installable here, and the
-  reference's own tests only pin it statistically. The oracle fixes the
-  summation order of ``vecinfer_quantize.metal`` (sequential over the
-  sub-vector, unfused multiply/add, lowest index wins ties).
+* ``vq``       -- ``quantize_vq`` and the attention oracle are pinned by the
+  reference's own functions executed with NumPy answering ``mlx.core``
+  (``tests/golden/vq.npz``). What stays open ("parity unpinned" at the bit
+  level) is MLX's own reduction order, which is not installable here; the
+  oracle fixes the summation order of ``vecinfer_quantize.metal`` (sequential
+  over the sub-vector, unfused multiply/add, lowest index wins ties).
+* ``rvq``      -- pinned: codebooks from the reference's Lloyd-Max modules;
+  the quantizer's ``encode`` / ``decode`` and the cache class executed over
+  the same stand-in (``tests/golden/rvq_reference.npz``), bit for bit.
+* ``skvq``, ``kitty``, ``age_tiered``, ``kivi_sink`` -- pinned: the
+  reference's quantizer modules and cache classes executed over the stand-in
+  (``tests/golden/skvq.npz``, ``group_quant.npz``, ``cache_traces.npz``).
 """
 
 from . import bitpack, kivi, rabitq, vq  # noqa: F401

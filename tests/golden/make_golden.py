@@ -44,6 +44,14 @@ What is executed from the reference, unmodified:
   ``core/abstractions.py``. Their traces over a call script go to ``cache_traces.npz``; the scenario
   records of ``config_scenarios.py`` to ``config_traces.json``.
 
+* ``quantizers/turboquant_rvq.py`` and ``cache/turboquant_rvq_cache.py`` are loaded whole with the
+  package modules they import (``core/constants.py``, ``exceptions.py``, ``context.py``,
+  ``abstractions.py``, ``registry.py``, ``dsa/avl_tree.py``, ``math/distributions.py``,
+  ``lloyd_max.py``, ``rotation.py``, ``codebooks/scalar_codebook.py``, ``base.py``,
+  ``strategies.py``, ``preconditioners/rotation.py``) over the stand-in, extended with a float32
+  butterfly for ``hadamard_transform``, ``searchsorted`` and ``ml_dtypes``'s ``bfloat16``; the
+  quantizer's outputs and the cache class's trace go to ``rvq_reference.npz``.
+
 Nothing here imports the oracle: the fixtures are the reference's outputs and
 the oracle is checked against them by ``tests/test_oracle_golden.py``.
 """
@@ -519,7 +527,116 @@ def main():
                 sys.modules.pop(key, None)
             else:
                 sys.modules[key] = val
+    _rvq_reference_section(pkg)
     print("golden fixtures written to", HERE)
+
+
+def _rvq_reference_section(pkg: str) -> None:
+    """``quantizers/turboquant_rvq.py`` (``TurboQuantRVQ.encode`` / ``decode``) and the cache class of
+    ``cache/turboquant_rvq_cache.py``, loaded whole with everything they import from the package
+    (``codebooks/``, ``preconditioners/rotation.py``, ``math/``, ``dsa/avl_tree.py``, ``core/``) over
+    the NumPy stand-in. Two ``mlx.core`` functions have no NumPy namesake and are written here:
+    ``hadamard_transform`` (float32 butterfly, strides ascending, times ``1/sqrt(n)``) and
+    ``searchsorted``; ``bfloat16`` is ``ml_dtypes``'s. Writes ``rvq_reference.npz``."""
+    import sys
+    import types
+
+    import ml_dtypes
+
+    mx = _mx_numpy_module()
+    mx.bfloat16 = ml_dtypes.bfloat16
+
+    def hadamard_transform(a, scale=None):
+        x = np.asarray(a, dtype=np.float32).copy()
+        n = x.shape[-1]
+        h = 1
+        while h < n:
+            y = x.reshape(*x.shape[:-1], n // (2 * h), 2, h)
+            lo, hi = y[..., 0, :] + y[..., 1, :], y[..., 0, :] - y[..., 1, :]
+            x = np.stack([lo, hi], axis=-2).reshape(*x.shape[:-1], n).astype(np.float32)
+            h *= 2
+        return (x * np.float32(1.0 / np.sqrt(np.float32(n)) if scale is None else scale)).astype(np.float32)
+
+    mx.hadamard_transform = hadamard_transform
+    mx.searchsorted = lambda a, v, side="left": np.searchsorted(a, v, side=side)
+    mlx_pkg = types.ModuleType("mlx")
+    mlx_pkg.core = mx
+    packages = ["veloxquant_mlx", "veloxquant_mlx.core", "veloxquant_mlx.dsa", "veloxquant_mlx.codebooks", "veloxquant_mlx.math",
+                "veloxquant_mlx.preconditioners", "veloxquant_mlx.quantizers", "veloxquant_mlx.cache", "mlx_lm", "mlx_lm.models"]
+    files = [("core/constants.py", "core.constants"), ("core/exceptions.py", "core.exceptions"), ("core/context.py", "core.context"),
+             ("core/abstractions.py", "core.abstractions"), ("core/registry.py", "core.registry"), ("dsa/avl_tree.py", "dsa.avl_tree"),
+             ("math/distributions.py", "math.distributions"), ("math/lloyd_max.py", "math.lloyd_max"), ("math/rotation.py", "math.rotation"),
+             ("codebooks/scalar_codebook.py", "codebooks.scalar_codebook"), ("codebooks/base.py", "codebooks.base"),
+             ("codebooks/strategies.py", "codebooks.strategies"), ("preconditioners/rotation.py", "preconditioners.rotation"),
+             ("quantizers/turboquant_rvq.py", "quantizers.turboquant_rvq"), ("cache/turboquant_rvq_cache.py", "cache.turboquant_rvq_cache")]
+    names = ["mlx", "mlx.core", "mlx_lm.models.cache", "veloxquant_mlx.metal"] + packages + ["veloxquant_mlx." + n for _, n in files]
+    saved = {k: sys.modules.get(k) for k in names}
+    try:
+        sys.modules["mlx"], sys.modules["mlx.core"] = mlx_pkg, mx
+        for name in packages:
+            sys.modules[name] = types.ModuleType(name)
+
+        class _SteppedKV(_GrowingKV):
+            step = 256                                           # the growth step of the class the reference derives from
+
+        base = types.ModuleType("mlx_lm.models.cache")
+        base.KVCache, base.create_attention_mask = _SteppedKV, None
+        sys.modules["mlx_lm.models.cache"] = base
+        metal = types.ModuleType("veloxquant_mlx.metal")
+        metal.metal_available = lambda: False                    # the classes then take their own array path
+        sys.modules["veloxquant_mlx.metal"] = metal
+        mods = {n: load_module(os.path.join(pkg, *rel.split("/")), "veloxquant_mlx." + n) for rel, n in files}
+        rvq, cache_m = mods["quantizers.turboquant_rvq"], mods["cache.turboquant_rvq_cache"]
+
+        out = {}
+        cases = [(64, 1), (64, 4), (128, 2), (128, 3), (128, 4), (256, 2)]
+        out["quantizer_cases"] = np.asarray(cases)
+        for d, b in cases:
+            q = rvq.TurboQuantRVQ(d=d, b=b, seed=3, use_hadamard=True)
+            x = np.random.default_rng(1000 * d + b).standard_normal((96, d)).astype(np.float32)
+            x = (x / np.linalg.norm(x, axis=-1, keepdims=True)).astype(np.float16)
+            ev = q.encode(x)
+            t = f"q_d{d}_b{b}_"
+            out[t + "x"], out[t + "rotated"] = x, np.asarray(q._rotation.apply(x))
+            out[t + "idx1"], out[t + "idx2"] = np.asarray(ev.indices), np.asarray(ev.signs).astype(np.uint8)
+            out[t + "decoded"] = np.asarray(q.decode(ev))
+            out[t + "diag"] = np.asarray(q._rotation._D, dtype=np.float32)
+            out[t + "c1"], out[t + "b1"] = np.asarray(q._codebook1.centroids_mx()), np.asarray(q._codebook1.boundaries_mx())
+            out[t + "c2"], out[t + "b2"] = np.asarray(q._codebook2.centroids_mx()), np.asarray(q._codebook2.boundaries_mx())
+
+        # the cache class over a call script: a prefill, single tokens, a block, a trim, more tokens
+        rng = np.random.default_rng(251)
+        B, H, D, T, bits, seed = 2, 2, 64, 120, 2, 5
+        k = (rng.standard_normal((B, H, T, D)) * 10.0 ** rng.uniform(-2, 2, (B, H, T, 1))).astype(np.float16)
+        k[1, 0, 9] = (np.sign(k[1, 0, 9].astype(np.float32)) * 30000.0).astype(np.float16)     # a norm past 65504
+        k[0, 1, 50] = 0                                                                          # a zero key
+        v = rng.standard_normal((B, H, T, D)).astype(np.float16)
+        script = [("put", 0, 45)] + [("put", t, t + 1) for t in range(45, 75)] + [("put", 75, 90), ("trim", 11, 0)] + \
+                 [("put", t, t + 1) for t in range(79, 100)] + [("put", 100, 120)]
+        out["cache_dims"], out["cache_k"], out["cache_v"] = np.asarray([B, H, D, T, bits, seed]), k, v
+        out["cache_script"] = np.asarray([[{"put": 0, "trim": 1}[op], a, b] for op, a, b in script])
+        cfg = types.SimpleNamespace(head_dim=D, bit_width_inlier=bits, seed=seed, use_metal_kernels=None)
+        cache = cache_m.TurboQuantRVQKVCache(cfg)
+        for i, (op, a, b) in enumerate(script):
+            if op == "trim":
+                assert cache.trim(a) == a
+                continue
+            ko, vo = cache.update_and_fetch(k[:, :, a:b], v[:, :, a:b])
+            if b - a > 1 or b % 32 == 0:
+                out[f"cache_k_{i}"], out[f"cache_v_{i}"] = np.array(ko), np.array(vo)
+                out[f"cache_c_{i}"] = np.asarray([cache.offset, cache._packed1.shape[2], cache.compressed_key_bytes, cache.fp16_key_bytes,
+                                                  cache.nbytes], dtype=np.int64)
+        p1, p2, norms, vals = cache.state
+        out["cache_state_p1"], out["cache_state_p2"] = np.asarray(p1).astype(np.uint32), np.asarray(p2).astype(np.uint32)
+        out["cache_state_norms"] = np.asarray(norms).astype(np.float32)
+        out["cache_meta_state"] = np.asarray([int(s) for s in cache.meta_state])
+        np.savez_compressed(os.path.join(HERE, "rvq_reference.npz"), **out)
+    finally:
+        for key, val in saved.items():
+            if val is None:
+                sys.modules.pop(key, None)
+            else:
+                sys.modules[key] = val
 
 
 class _GrowingKV:

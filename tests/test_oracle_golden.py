@@ -365,3 +365,70 @@ def test_vq_reference_sdpa_matches_the_reference_function_run_over_numpy(tag):
     out = vq.reference_sdpa(q_t, g("k_idx"), g("cb_k"), g("v_idx"), 0.125, v_codebook=g("cb_v"), causal=bool(causal),
                             sliding_window=window)
     np.testing.assert_allclose(out, g("out"), rtol=0, atol=2e-6)
+
+
+def _rvq_midpoints(centroids64):
+    """Voronoi boundaries as the reference's ``ScalarCodebook`` holds them: midpoints of the float32
+    centroids, rounded to float16 (``codebooks/scalar_codebook.py:57-60``)."""
+    c = np.asarray(centroids64).astype(np.float32)
+    return ((c[:-1] + c[1:]) / np.float32(2.0)).astype(np.float16)
+
+
+def test_rvq_oracle_matches_the_reference_quantizer_run_over_numpy():
+    """``rvq_reference.npz``: ``TurboQuantRVQ.encode`` / ``decode`` executed unmodified over the NumPy
+    stand-in. From the reference's rotated input both index streams are reproduced bit for bit, and so
+    are the rotation and the decoded vectors (the stand-in's Hadamard butterfly is this oracle's)."""
+    from oracle import rvq
+
+    z = np.load(os.path.join(GOLDEN, "rvq_reference.npz"))
+    codebooks = np.load(os.path.join(GOLDEN, "rvq.npz"))
+    for d, b in z["quantizer_cases"]:
+        t = f"q_d{d}_b{b}_"
+        c1, b1, c2, b2, diag = (z[t + k] for k in ("c1", "b1", "c2", "b2", "diag"))
+        # the tables the quantizer built are the float16 roundings of the pinned Lloyd-Max codebooks
+        np.testing.assert_array_equal(c1, codebooks[f"gauss_b{b}_d{d}"].astype(np.float16))
+        np.testing.assert_array_equal(c2, codebooks[f"laplace_b{b}_d{d}"].astype(np.float16))
+        np.testing.assert_array_equal(b1, _rvq_midpoints(codebooks[f"gauss_b{b}_d{d}"]))
+        np.testing.assert_array_equal(b2, _rvq_midpoints(codebooks[f"laplace_b{b}_d{d}"]))
+        np.testing.assert_array_equal(diag, rabitq.make_hadamard_diagonal(int(d), 3))
+        i1, i2, w1, w2 = rvq.rvq_quant_pack(z[t + "rotated"], c1, b1, b2, int(b))
+        np.testing.assert_array_equal(i1, z[t + "idx1"])
+        np.testing.assert_array_equal(i2, z[t + "idx2"])
+        assert len(np.unique(i2)) == 2 ** b                    # the residual stage is exercised
+        np.testing.assert_array_equal(rvq.rotate(z[t + "x"], diag), z[t + "rotated"])
+        got = rvq.rvq_unpack_decode(w1, w2, np.ones(len(i1), np.float32), c1, c2, diag, int(b), int(d))
+        np.testing.assert_array_equal(got, z[t + "decoded"])
+
+
+def test_rvq_cache_model_matches_the_reference_class_run_over_numpy():
+    """The reference's ``TurboQuantRVQKVCache`` over a call script (prefill, single tokens, a block, a
+    trim, more tokens; one key with a norm past 65504 and one zero key): returned keys and values,
+    offsets, buffer growth and byte counters, then the stored state."""
+    from oracle import rvq
+
+    z = np.load(os.path.join(GOLDEN, "rvq_reference.npz"))
+    codebooks = np.load(os.path.join(GOLDEN, "rvq.npz"))
+    B, H, D, T, bits, seed = (int(x) for x in z["cache_dims"])
+    c1 = codebooks[f"gauss_b{bits}_d{D}"].astype(np.float16)
+    c2 = codebooks[f"laplace_b{bits}_d{D}"].astype(np.float16)
+    m = rvq.RVQCacheModel(D, bits, rabitq.make_hadamard_diagonal(D, seed), c1, _rvq_midpoints(codebooks[f"gauss_b{bits}_d{D}"]),
+                          c2, _rvq_midpoints(codebooks[f"laplace_b{bits}_d{D}"]))
+    k, v = z["cache_k"], z["cache_v"]
+    checked = 0
+    for i, (op, a, b) in enumerate(z["cache_script"]):
+        if op == 1:
+            assert m.trim(int(a)) == a
+            continue
+        ko, vo = m.update_and_fetch(k[:, :, a:b], v[:, :, a:b])
+        if f"cache_k_{i}" in z.files:
+            np.testing.assert_array_equal(ko, z[f"cache_k_{i}"])
+            np.testing.assert_array_equal(vo, z[f"cache_v_{i}"])
+            assert [m.offset, m.p1.shape[2], m.compressed_key_bytes, m.fp16_key_bytes, m.nbytes] == list(z[f"cache_c_{i}"])
+            checked += 1
+    assert checked >= 5 and np.isfinite(ko.astype(np.float32)).all()
+    n = m.offset
+    np.testing.assert_array_equal(m.p1[:, :, :n], z["cache_state_p1"])
+    np.testing.assert_array_equal(m.p2[:, :, :n], z["cache_state_p2"])
+    np.testing.assert_array_equal(m.norms[:, :, :n], z["cache_state_norms"])
+    assert float(z["cache_state_norms"].max()) > 65504.0 and float(z["cache_state_norms"].min()) == 0.0
+    assert list(z["cache_meta_state"]) == [D, bits, seed, n]

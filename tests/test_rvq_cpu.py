@@ -126,3 +126,28 @@ def test_packing_and_norm_helpers_match_the_reference_cache_functions_run_over_n
     assert float(z["cache_norms"].max()) > 65504.0                         # the case the float32 norm exists for
     resc = (torch.from_numpy(z["cache_unit"]).float() * torch.from_numpy(z["cache_norms"])).clamp(-65504.0, 65504.0).to(torch.float16)
     assert np.array_equal(resc.numpy(), z["cache_rescaled"])
+
+
+def test_quantizer_tables_and_host_encode_match_the_reference_quantizer_run_over_numpy():
+    """``rvq_reference.npz`` holds what the reference's ``TurboQuantRVQ`` built and returned when run
+    over a NumPy stand-in: this package's quantizer builds the same tables, and its host-side
+    two-stage encode maps the reference's rotated input to the reference's indices."""
+    from veloxquant_mlx_b200 import rvq
+
+    z = np.load(os.path.join(os.path.dirname(__file__), "golden", "rvq_reference.npz"))
+    for d, b in z["quantizer_cases"]:
+        t = f"q_d{d}_b{b}_"
+        q = rvq.TurboQuantRVQ(int(d), int(b), seed=3, use_hadamard=True)
+        np.testing.assert_array_equal(q._codebook1.centroids, z[t + "c1"])
+        np.testing.assert_array_equal(q._codebook1.boundaries, z[t + "b1"])
+        np.testing.assert_array_equal(q._codebook2.centroids, z[t + "c2"])
+        np.testing.assert_array_equal(q._codebook2.boundaries, z[t + "b2"])
+        np.testing.assert_array_equal(q._diag_np, z[t + "diag"])
+        y = torch.from_numpy(z[t + "rotated"])
+        idx1 = q._codebook1.quantize(y)
+        r1 = y - q._codebook1.dequantize(idx1).to(y.dtype)
+        np.testing.assert_array_equal(idx1.numpy(), z[t + "idx1"])
+        np.testing.assert_array_equal(q._codebook2.quantize(r1).numpy(), z[t + "idx2"])
+        # the rotation itself (matrix form on the host) agrees to float16 rounding
+        rot = q.rotate(torch.from_numpy(z[t + "x"])).float().numpy()
+        np.testing.assert_allclose(rot, z[t + "rotated"].astype(np.float32), atol=2.0 ** -10, rtol=0)
