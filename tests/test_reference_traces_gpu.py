@@ -1,7 +1,8 @@
 """The native caches against traces of the reference's own cache classes (``cache/kivi_cache.py``,
 ``sink_cache.py``, ``skvq_cache.py``, ``kitty_cache.py``, ``age_tiered_cache.py``), which
 ``tests/golden/make_golden.py`` executed unmodified over NumPy stand-ins for ``mlx.core`` and for the
-``mlx_lm`` container class they derive from (``tests/golden/cache_traces.npz``)."""
+``mlx_lm`` container class they derive from (``tests/golden/cache_traces.npz``; the TurboQuant-RVQ
+class's trace is in ``tests/golden/rvq_reference.npz``)."""
 
 import os
 
@@ -79,3 +80,40 @@ def test_native_vecinfer_cache_replays_the_reference_class_trace():
             assert c.offset == int(z[f"vecinfer_c_{i}"][0])
             checked += 1
     assert checked >= 10 and same / total > 0.995
+
+
+def test_native_rvq_cache_replays_the_reference_class_trace():
+    """TurboQuant-RVQ (``cache/turboquant_rvq_cache.py`` executed over the stand-ins,
+    ``tests/golden/rvq_reference.npz``; one key with a norm past 65504, one zero key, a trim): values,
+    offsets, buffer growth and byte counters equal the reference class's; the decoded keys and the stored
+    code words equal it row for row, where a row may differ only if the float32 norm's summation order
+    (a library reduction here, NumPy's there) moved a coordinate across a code boundary -- at most a
+    sliver of rows, each then within one code step."""
+    z = np.load(os.path.join(GOLDEN, "rvq_reference.npz"))
+    B, H, D, T, bits, seed = (int(x) for x in z["cache_dims"])
+    c = _make("turboquant_rvq", head_dim=D, bit_width_inlier=bits, seed=seed)
+    k, v = z["cache_k"], z["cache_v"]
+    checked, same, total = 0, 0, 0
+    for i, (op, a, b) in enumerate(z["cache_script"].tolist()):
+        if op == 1:
+            assert c.trim(a) == a
+            continue
+        ko, vo = c.update_and_fetch(_t(k[:, :, a:b]), _t(v[:, :, a:b]))
+        if f"cache_k_{i}" in z:
+            want = z[f"cache_k_{i}"].astype(np.float32)
+            got = ko.float().cpu().numpy()
+            assert ko.dtype == torch.float16 and got.shape == want.shape and np.isfinite(got).all()
+            np.testing.assert_array_equal(vo.cpu().numpy(), z[f"cache_v_{i}"])
+            rows_same = (got == want).all(-1)
+            err = np.linalg.norm(got - want, axis=-1) / np.maximum(np.linalg.norm(want, axis=-1), 1e-30)
+            assert float(err.max()) <= 0.25
+            same += int(rows_same.sum())
+            total += rows_same.size
+            assert [c.offset, c._packed1.shape[2], c.compressed_key_bytes, c.fp16_key_bytes, c.nbytes] == z[f"cache_c_{i}"].tolist()
+            checked += 1
+    assert checked >= 5 and same / total >= 0.98
+    p1, p2, norms, _ = c.state
+    words_same = (p1.cpu().numpy().view(np.uint32) == z["cache_state_p1"]).all(-1) & (p2.cpu().numpy().view(np.uint32) == z["cache_state_p2"]).all(-1)
+    assert float(words_same.mean()) >= 0.98
+    np.testing.assert_allclose(norms.float().cpu().numpy(), z["cache_state_norms"], rtol=2.0 ** -7, atol=0)
+    assert [int(s) for s in c.meta_state] == z["cache_meta_state"].tolist()
