@@ -9,6 +9,10 @@ Follows, line by line:
 * ``veloxquant_mlx/tests/metal/test_scalar_attend.py:85-115`` (``_reference_attend``)
 * ``veloxquant_mlx/cache/kivi_cache.py:206-225`` (``_quantization_boundary``)
 
+Pinning: ``tests/golden/kivi.npz`` (the test functions above, executed as they stand) and
+``tests/golden/kivi_quantizer.npz`` (the ``KIVIQuantizer`` class executed unmodified over a NumPy
+stand-in for ``mlx.core``), both reproduced bit for bit (``tests/test_oracle_golden.py``).
+
 All arithmetic is float32 in the reference's operation order: ``min``, ``max``,
 ``(max-min)/levels``, ``maximum(eps)``, ``(x-min)/scale``, round-half-even,
 ``clip``. Reconstruction is a separately rounded multiply then add.

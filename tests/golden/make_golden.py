@@ -52,6 +52,10 @@ What is executed from the reference, unmodified:
   butterfly for ``hadamard_transform``, ``searchsorted`` and ``ml_dtypes``'s ``bfloat16``; the
   quantizer's outputs and the cache class's trace go to ``rvq_reference.npz``.
 
+* ``quantizers/kivi.py`` (the ``KIVIQuantizer`` class) is loaded whole over the stand-in with the
+  ``core/`` modules it imports; its ``encode`` / ``decode`` / ``estimate_inner_product`` outputs on
+  both grouping axes go to ``kivi_quantizer.npz``.
+
 Nothing here imports the oracle: the fixtures are the reference's outputs and
 the oracle is checked against them by ``tests/test_oracle_golden.py``.
 """
@@ -528,6 +532,7 @@ def main():
             else:
                 sys.modules[key] = val
     _rvq_reference_section(pkg)
+    _kivi_quantizer_section(pkg)
     print("golden fixtures written to", HERE)
 
 
@@ -631,6 +636,61 @@ def _rvq_reference_section(pkg: str) -> None:
         out["cache_state_norms"] = np.asarray(norms).astype(np.float32)
         out["cache_meta_state"] = np.asarray([int(s) for s in cache.meta_state])
         np.savez_compressed(os.path.join(HERE, "rvq_reference.npz"), **out)
+    finally:
+        for key, val in saved.items():
+            if val is None:
+                sys.modules.pop(key, None)
+            else:
+                sys.modules[key] = val
+
+
+def _kivi_quantizer_section(pkg: str) -> None:
+    """``quantizers/kivi.py`` (``KIVIQuantizer.encode`` / ``decode``, both axes, ragged last groups),
+    loaded whole over the NumPy stand-in with the ``core/`` modules it imports. Writes
+    ``kivi_quantizer.npz``."""
+    import sys
+    import types
+
+    mx = _mx_numpy_module()
+    mlx_pkg = types.ModuleType("mlx")
+    mlx_pkg.core = mx
+    packages = ["veloxquant_mlx", "veloxquant_mlx.core", "veloxquant_mlx.quantizers"]
+    files = [("core/constants.py", "core.constants"), ("core/exceptions.py", "core.exceptions"), ("core/context.py", "core.context"),
+             ("core/abstractions.py", "core.abstractions"), ("core/registry.py", "core.registry"), ("quantizers/kivi.py", "quantizers.kivi")]
+    names = ["mlx", "mlx.core"] + packages + ["veloxquant_mlx." + n for _, n in files]
+    saved = {k: sys.modules.get(k) for k in names}
+    try:
+        sys.modules["mlx"], sys.modules["mlx.core"] = mlx_pkg, mx
+        for name in packages:
+            sys.modules[name] = types.ModuleType(name)
+        mods = {n: load_module(os.path.join(pkg, *rel.split("/")), "veloxquant_mlx." + n) for rel, n in files}
+        kivi = mods["quantizers.kivi"]
+        rng = np.random.default_rng(103)
+        out = {}
+        cases = []
+        for axis in ("channel", "token"):
+            for n, d, b, g in [(64, 32, 2, 32), (70, 40, 2, 32), (45, 24, 4, 8), (33, 16, 1, 16), (12, 8, 8, 5), (7, 64, 3, 1)]:
+                cases.append([0 if axis == "channel" else 1, n, d, b, g])
+                x = (rng.standard_normal((n, d)) * rng.uniform(0.2, 3.0, (1, d))).astype(np.float16)
+                x[n // 2, :] = x[n // 2, 0]                      # a constant row (one-value groups on the token axis)
+                x[:, d // 2] = 1.5                               # a constant channel (one-value groups on the channel axis)
+                q = kivi.KIVIQuantizer(d=d, b=b, group_size=g, axis=axis)
+                ev = q.encode(x)
+                t = f"{axis}_n{n}_d{d}_b{b}_g{g}_"
+                out[t + "x"], out[t + "codes"] = x, np.asarray(ev.indices)
+                out[t + "scale"], out[t + "zero"] = np.asarray(ev.norm), np.asarray(ev.residual_norm)
+                out[t + "decoded"] = np.asarray(q.decode(ev))
+                qv = rng.standard_normal(d).astype(np.float16)
+                out[t + "q"], out[t + "ip"] = qv, np.asarray(q.estimate_inner_product(qv, ev))
+        out["cases"] = np.asarray(cases)
+        bad = np.ones((4, 8), np.float16)
+        bad[1, 2] = np.inf
+        try:
+            kivi.KIVIQuantizer(d=8).encode(bad)
+            raise AssertionError("an infinite input was accepted")
+        except mods["core.exceptions"].QuantizerConfigError as e:
+            out["nonfinite_message"] = np.asarray(str(e))
+        np.savez_compressed(os.path.join(HERE, "kivi_quantizer.npz"), **out)
     finally:
         for key, val in saved.items():
             if val is None:

@@ -432,3 +432,32 @@ def test_rvq_cache_model_matches_the_reference_class_run_over_numpy():
     np.testing.assert_array_equal(m.norms[:, :, :n], z["cache_state_norms"])
     assert float(z["cache_state_norms"].max()) > 65504.0 and float(z["cache_state_norms"].min()) == 0.0
     assert list(z["cache_meta_state"]) == [D, bits, seed, n]
+
+
+def test_kivi_oracle_matches_the_reference_quantizer_class_run_over_numpy():
+    """``kivi_quantizer.npz``: the reference's ``KIVIQuantizer`` (``quantizers/kivi.py:103-196``) executed
+    unmodified over the NumPy stand-in, both grouping axes, ragged last groups, one-value groups: codes,
+    scales, zero points and the float16 reconstruction, bit for bit."""
+    z = np.load(os.path.join(GOLDEN, "kivi_quantizer.npz"))
+    assert len(z["cases"]) == 12
+    for axis, n, d, b, g in z["cases"].tolist():
+        t = f"{'token' if axis else 'channel'}_n{n}_d{d}_b{b}_g{g}_"
+        x = z[t + "x"][None, None]
+        levels = (1 << b) - 1
+        if axis == 0:
+            c, s, zp = kivi.quant_keys(x, g, levels)
+            rec = kivi.dequant_keys(c, s, zp, g)
+            assert s.shape == (1, 1, -(-n // g), d)
+        else:
+            c, s, zp = kivi.quant_values(x, g, levels)
+            rec = kivi.dequant_values(c, s, zp, g)
+            assert s.shape == (1, 1, n, -(-d // g))
+        np.testing.assert_array_equal(c[0, 0], z[t + "codes"])
+        np.testing.assert_array_equal(s[0, 0], z[t + "scale"])
+        np.testing.assert_array_equal(zp[0, 0], z[t + "zero"])
+        assert z[t + "scale"].dtype == np.float32 and z[t + "codes"].dtype == np.uint8
+        np.testing.assert_array_equal(rec[0, 0].astype(np.float16), z[t + "decoded"])
+        ip = (rec[0, 0].astype(np.float16).astype(np.float32) @ z[t + "q"].astype(np.float32)).astype(np.float16)
+        np.testing.assert_allclose(ip.astype(np.float32), z[t + "ip"].astype(np.float32), rtol=2e-3, atol=2e-3)
+        assert s.min() >= np.float32(1e-8) and (axis == 1 or s.min() == np.float32(1e-8))   # the constant channel: eps-floored scale
+    assert "NaN or Inf" in str(z["nonfinite_message"])
