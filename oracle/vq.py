@@ -84,6 +84,8 @@ def dequantize_vq(indices: np.ndarray, codebook: np.ndarray) -> np.ndarray:
 def compute_query_lut(q_tilde: np.ndarray, codebook: np.ndarray, sub_dim: int) -> np.ndarray:
     """``lut[..., s, c] = q_sub[..., s, :] . codebook[c, :]``."""
     *lead, D = q_tilde.shape
+    if D % sub_dim != 0:
+        raise ValueError(f"compute_query_lut: D={D} not divisible by sub_dim={sub_dim}")
     n_sub = D // sub_dim
     q_sub = q_tilde.reshape(*lead, n_sub, sub_dim).astype(np.float32)
     cb = np.asarray(codebook).astype(np.float32)

@@ -56,6 +56,11 @@ What is executed from the reference, unmodified:
   ``core/`` modules it imports; its ``encode`` / ``decode`` / ``estimate_inner_product`` outputs on
   both grouping axes go to ``kivi_quantizer.npz``.
 
+* ``apply_dual_transform_keys`` / ``apply_dual_transform_queries`` / ``compute_query_lut``
+  (``allocators/vecinfer.py``) are extracted by name and executed over the stand-in on every
+  smooth-factor broadcasting convention; outputs and the accept / reject table go to
+  ``vq_transform.npz``.
+
 Nothing here imports the oracle: the fixtures are the reference's outputs and
 the oracle is checked against them by ``tests/test_oracle_golden.py``.
 """
@@ -533,6 +538,7 @@ def main():
                 sys.modules[key] = val
     _rvq_reference_section(pkg)
     _kivi_quantizer_section(pkg)
+    _vq_transform_section(pkg)
     print("golden fixtures written to", HERE)
 
 
@@ -697,6 +703,58 @@ def _kivi_quantizer_section(pkg: str) -> None:
                 sys.modules.pop(key, None)
             else:
                 sys.modules[key] = val
+
+
+def _vq_transform_section(pkg: str) -> None:
+    """``apply_dual_transform_keys`` / ``apply_dual_transform_queries`` / ``compute_query_lut`` /
+    ``walsh_hadamard_matrix`` (``allocators/vecinfer.py:60-184``, ``:341-359``) extracted by name and
+    executed over the NumPy stand-in, over every broadcasting convention of the smooth factors (one
+    vector, one row per head, grouped query heads, mismatched head counts) and the shapes they
+    reject. Writes ``vq_transform.npz``."""
+    mx = _mx_numpy_module()
+    ns = extract_functions(os.path.join(pkg, "allocators", "vecinfer.py"),
+                           ["walsh_hadamard_matrix", "apply_dual_transform_keys", "apply_dual_transform_queries", "compute_query_lut"],
+                           extra_ns={"mx": mx})
+    rng = np.random.default_rng(616)
+    D, Hkv, Hq, B, S = 32, 2, 6, 2, 5
+    Hm = np.asarray(ns["walsh_hadamard_matrix"](D), dtype=np.float32)
+    out = {"H": Hm}
+    smooth = {"vec": rng.uniform(0.5, 2.0, D).astype(np.float32), "kv": rng.uniform(0.5, 2.0, (Hkv, D)).astype(np.float32),
+              "q": rng.uniform(0.5, 2.0, (Hq, D)).astype(np.float32), "five": rng.uniform(0.5, 2.0, (5, D)).astype(np.float32)}
+    xs = {"k4": rng.standard_normal((B, Hkv, S, D)).astype(np.float32), "k3": rng.standard_normal((Hkv, S, D)).astype(np.float32),
+          "k2": rng.standard_normal((S, D)).astype(np.float32), "q4": rng.standard_normal((B, Hq, S, D)).astype(np.float32),
+          "q3": rng.standard_normal((Hq, 1, D)).astype(np.float32), "k4h": rng.standard_normal((B, Hkv, S, D)).astype(np.float16)}
+    for name, arr in list(smooth.items()) + list(xs.items()):
+        out["in_" + name] = arr
+    table = []
+    for fn_name, short in (("apply_dual_transform_keys", "keys"), ("apply_dual_transform_queries", "queries")):
+        for xn, x in xs.items():
+            for sn, sm in smooth.items():
+                tag = f"{short}_{xn}_{sn}"
+                try:
+                    out[tag] = np.asarray(ns[fn_name](x, sm, Hm))
+                    table.append(tag + ":ok")
+                except ValueError:
+                    table.append(tag + ":ValueError")
+    for fn_name, short in (("apply_dual_transform_keys", "keys"), ("apply_dual_transform_queries", "queries")):
+        for tag, x, sm in ((f"{short}_k4_badwidth", xs["k4"], np.ones((Hkv, D + 1), np.float32)),
+                           (f"{short}_k4_smooth3d", xs["k4"], np.ones((1, Hkv, D), np.float32))):
+            try:
+                ns[fn_name](x, sm, Hm)
+                table.append(tag + ":ok")
+            except ValueError:
+                table.append(tag + ":ValueError")
+    out["table"] = np.asarray(table)
+    cb = rng.standard_normal((16, 4)).astype(np.float32)
+    out["lut_codebook"] = cb
+    out["lut_q4"] = np.asarray(ns["compute_query_lut"](xs["q4"], cb, 4))
+    out["lut_q3"] = np.asarray(ns["compute_query_lut"](xs["q3"], cb, 4))
+    try:
+        ns["compute_query_lut"](xs["q4"], rng.standard_normal((16, 5)).astype(np.float32), 5)
+        out["lut_bad"] = np.asarray("ok")
+    except ValueError as e:
+        out["lut_bad"] = np.asarray(str(e))
+    np.savez_compressed(os.path.join(HERE, "vq_transform.npz"), **out)
 
 
 class _GrowingKV:

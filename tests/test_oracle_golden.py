@@ -461,3 +461,48 @@ def test_kivi_oracle_matches_the_reference_quantizer_class_run_over_numpy():
         np.testing.assert_allclose(ip.astype(np.float32), z[t + "ip"].astype(np.float32), rtol=2e-3, atol=2e-3)
         assert s.min() >= np.float32(1e-8) and (axis == 1 or s.min() == np.float32(1e-8))   # the constant channel: eps-floored scale
     assert "NaN or Inf" in str(z["nonfinite_message"])
+
+
+def _vq_transform_cases(z):
+    """(tag, expected outcome, function kind, input, smooth) for every row of the fixture's table."""
+    for row in z["table"]:
+        tag, res = str(row).split(":")
+        short, xn, sn = tag.split("_")
+        if sn == "badwidth":
+            sm = np.ones((2, 33), np.float32)
+        elif sn == "smooth3d":
+            sm = np.ones((1, 2, 32), np.float32)
+        else:
+            sm = z["in_" + sn]
+        yield tag, res, short, z["in_" + xn], sm
+
+
+def test_vq_dual_transform_and_lut_match_the_reference_functions_run_over_numpy():
+    """``vq_transform.npz``: ``apply_dual_transform_keys`` / ``_queries`` / ``compute_query_lut``
+    (``allocators/vecinfer.py:93-184``, ``:341-359``) executed over the NumPy stand-in on every way the
+    smooth factors broadcast (one vector, a row per head, query groups of a KV head, the averaged
+    fallback for mismatched head counts, 2-D / 3-D / 4-D inputs, float16) and the shapes they reject."""
+    z = np.load(os.path.join(GOLDEN, "vq_transform.npz"))
+    H = z["H"]
+    np.testing.assert_array_equal(vq.walsh_hadamard_matrix(32).astype(np.float32), H)
+    fns = {"keys": vq.apply_dual_transform_keys, "queries": vq.apply_dual_transform_queries}
+    n_ok = n_rejected = 0
+    for tag, res, short, x, sm in _vq_transform_cases(z):
+        if res == "ValueError":
+            with pytest.raises(ValueError):
+                fns[short](x, sm, H)
+            n_rejected += 1
+            continue
+        got, want = fns[short](x, sm, H), z[tag]
+        assert got.dtype == want.dtype and got.shape == want.shape, tag
+        tol = 1e-5 if want.dtype == np.float32 else 2e-2
+        np.testing.assert_allclose(got.astype(np.float32), want.astype(np.float32), rtol=0, atol=tol, err_msg=tag)
+        n_ok += 1
+    assert n_ok == 48 and n_rejected == 4
+    for name in ("q4", "q3"):
+        got = vq.compute_query_lut(z["in_" + name], z["lut_codebook"], 4)
+        assert got.shape == z["lut_" + name].shape
+        np.testing.assert_allclose(got, z["lut_" + name], rtol=0, atol=1e-6)
+    with pytest.raises(ValueError, match="not divisible"):
+        vq.compute_query_lut(z["in_q4"], np.ones((16, 5), np.float32), 5)
+    assert "not divisible by sub_dim=5" in str(z["lut_bad"])

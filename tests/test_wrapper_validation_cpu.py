@@ -82,3 +82,44 @@ def test_quantize_into_rejects_buffers_of_another_batch_or_head_count():
         k.kivi_quantize_into(x, -2, g, bits, codes=codes, scale=scale[:, :1].contiguous(), zero=scale[:, :1].clone())
     with pytest.raises(ValueError, match="contiguous uint8"):
         k.kivi_quantize_into(x, -2, g, bits, codes=codes[..., :32], scale=scale, zero=scale.clone())
+
+
+def test_dual_transforms_and_lut_follow_the_reference_functions_on_every_smooth_convention():
+    """The host-side ``apply_dual_transform_keys`` / ``_queries`` / ``compute_query_lut`` on CPU tensors
+    against the reference's own functions executed over a NumPy stand-in
+    (``tests/golden/vq_transform.npz``): same outputs, dtypes and shapes on every way the smooth factors
+    broadcast, and a ``ValueError`` on every shape the reference rejects."""
+    import os
+
+    import numpy as np
+
+    from veloxquant_mlx_b200 import vecinfer as vi
+
+    z = np.load(os.path.join(os.path.dirname(__file__), "golden", "vq_transform.npz"))
+    H = torch.from_numpy(z["H"])
+    assert torch.equal(vi.walsh_hadamard_matrix(32), H)
+    fns = {"keys": vi.apply_dual_transform_keys, "queries": vi.apply_dual_transform_queries}
+    n_ok = n_rejected = 0
+    for row in z["table"]:
+        tag, res = str(row).split(":")
+        short, xn, sn = tag.split("_")
+        sm = {"badwidth": np.ones((2, 33), np.float32), "smooth3d": np.ones((1, 2, 32), np.float32)}.get(sn)
+        sm = torch.from_numpy(z["in_" + sn] if sm is None else sm)
+        x = torch.from_numpy(z["in_" + xn])
+        if res == "ValueError":
+            with pytest.raises(ValueError):
+                fns[short](x, sm, H)
+            n_rejected += 1
+            continue
+        got, want = fns[short](x, sm, H).numpy(), z[tag]
+        assert got.dtype == want.dtype and got.shape == want.shape, tag
+        np.testing.assert_allclose(got.astype(np.float32), want.astype(np.float32), rtol=0,
+                                   atol=1e-5 if want.dtype == np.float32 else 2e-2, err_msg=tag)
+        n_ok += 1
+    assert n_ok == 48 and n_rejected == 4
+    cb = torch.from_numpy(z["lut_codebook"])
+    for name in ("q4", "q3"):
+        np.testing.assert_allclose(vi.compute_query_lut(torch.from_numpy(z["in_" + name]), cb, 4).numpy(), z["lut_" + name], rtol=0, atol=1e-6)
+    with pytest.raises(ValueError) as e:
+        vi.compute_query_lut(torch.from_numpy(z["in_q4"]), torch.ones(16, 5), 5)
+    assert str(e.value) == str(z["lut_bad"])

@@ -38,6 +38,9 @@ def walsh_hadamard_matrix(d: int, dtype=torch.float32, device=None) -> torch.Ten
 
 
 def _smooth_for(x: torch.Tensor, smooth: torch.Tensor, for_query: bool, who: str) -> torch.Tensor:
+    if smooth.ndim in (1, 2) and smooth.shape[-1] not in (1, x.shape[-1]):
+        # (the reference's array library answers an impossible broadcast with a ValueError)
+        raise ValueError(f"{who}: cannot broadcast smooth {tuple(smooth.shape)} to {tuple(x.shape)}")
     if smooth.ndim == 1:
         return smooth.to(x.dtype)
     if smooth.ndim != 2:
