@@ -82,3 +82,111 @@ def construction_scenarios(ns):
                             ("age_tiered", {"age_bits_mid": 17}, "bits_17"), ("kivi", {"bit_width_inlier": [2]}, "kivi_list")):
         out[f"factory_{method}_{tag}"] = _record(lambda m=method, k=kw: type(F.create(C(method=m, head_dim=32, **k))).__name__)
     return out
+
+
+def _record_full(fn):
+    """As :func:`_record`, with whole messages."""
+    with warnings.catch_warnings(record=True) as w:
+        warnings.simplefilter("always")
+        try:
+            result, error = fn(), None
+        except Exception as e:  # noqa: BLE001
+            result, error = None, [type(e).__name__, str(e)]
+    return {"result": result, "warnings": sorted([x.category.__name__, str(x.message)] for x in w), "error": error}
+
+
+class _Attn:
+    def __init__(self, head_dim=None):
+        if head_dim is not None:
+            self.head_dim = head_dim
+
+
+class _Layer:
+    def __init__(self, kind="self_attn", head_dim=None):
+        if kind is not None:
+            setattr(self, kind, _Attn(head_dim))
+
+
+class _Args:
+    def __init__(self, **kw):
+        self.__dict__.update(kw)
+
+
+def builder_scenarios(ns):
+    """``KVCacheBuilder.for_model`` over stand-in models (``ns`` also carries ``KVCacheBuilder`` and
+    ``PlainCache``, the class handed to layers without attention). ``KVCacheFactory.create`` is replaced
+    for the duration of a scenario by a recorder, so a record is the per-layer plan: for an attention
+    layer ``[method, head_dim, bit width, seed]``, otherwise ``"plain"`` or the model's own slot."""
+    C, F, Bld = ns.KVCacheConfig, ns.KVCacheFactory, ns.KVCacheBuilder
+
+    def plan(model, cfg):
+        original = F.create
+        F.create = staticmethod(lambda c: ("cache", [c.method, c.head_dim, c.bit_width_inlier, c.seed]))
+        try:
+            caches = Bld.for_model(model, cfg)
+        finally:
+            F.create = staticmethod(original)
+        return [c[1] if isinstance(c, tuple) else "plain" if isinstance(c, ns.PlainCache) else str(c) for c in caches]
+
+    class Flat:                                    # layers on the model itself, per-layer head_dim
+        def __init__(self):
+            self.layers = [_Layer(head_dim=64), _Layer(head_dim=32), _Layer("attn", head_dim=16)]
+
+    class Nested:                                  # model.model.layers, head_dim from the arguments
+        def __init__(self, args, layers=None):
+            self.model = _Args(layers=layers or [_Layer(), _Layer()])
+            self.args = args
+
+    class Hybrid:                                  # attention, recurrent, attention; the model offers its own slots
+        def __init__(self):
+            self.layers = [_Layer(head_dim=64), _Layer(None), _Layer(head_dim=64)]
+
+        def make_cache(self):
+            return ["slot0", "slot1", "slot2"]
+
+    class HybridNoHook(Hybrid):
+        make_cache = None
+
+    class HybridShortHook(Hybrid):
+        def make_cache(self):
+            return ["slot0"]
+
+    class HybridFailingHook(Hybrid):
+        def make_cache(self):
+            raise RuntimeError("no cache today")
+
+    class Patched(Hybrid):                         # an instance attribute must not be called back
+        def __init__(self):
+            super().__init__()
+            self.make_cache = lambda: 1 / 0
+
+    class Wrapped:                                 # arguments without hidden_size: the language model's are used
+        def __init__(self):
+            self.layers = [_Layer(), _Layer()]
+            self.args = _Args(model_type="wrapper")
+            self.language_model = _Args(args=_Args(hidden_size=512, num_attention_heads=4))
+
+    class EmptyOuter:                              # an empty outer list falls through to model.model.layers
+        def __init__(self):
+            self.layers = []
+            self.model = _Args(layers=[_Layer(head_dim=8)])
+
+    out = {}
+    kivi = C(method="kivi", bit_width_inlier=4, seed=10)
+    out["flat_per_layer_head_dim"] = _record_full(lambda: plan(Flat(), kivi))
+    out["nested_hidden_over_heads"] = _record_full(lambda: plan(Nested(_Args(hidden_size=256, num_attention_heads=4)), kivi))
+    out["nested_args_head_dim_wins"] = _record_full(lambda: plan(Nested(_Args(head_dim=32, hidden_size=256, num_attention_heads=4)), kivi))
+    out["nested_layer_head_dim_wins"] = _record_full(
+        lambda: plan(Nested(_Args(head_dim=32), [_Layer(head_dim=128), _Layer()]), kivi))
+    out["hybrid_native_slot"] = _record_full(lambda: plan(Hybrid(), kivi))
+    out["hybrid_no_hook"] = _record_full(lambda: plan(HybridNoHook(), kivi))
+    out["hybrid_short_hook"] = _record_full(lambda: plan(HybridShortHook(), kivi))
+    out["hybrid_failing_hook"] = _record_full(lambda: plan(HybridFailingHook(), kivi))
+    out["hybrid_patched_instance"] = _record_full(lambda: plan(Patched(), kivi))
+    out["wrapped_language_model_args"] = _record_full(lambda: plan(Wrapped(), kivi))
+    out["empty_outer_layers"] = _record_full(lambda: plan(EmptyOuter(), kivi))
+    out["list_bits_over_attention_layers"] = _record_full(lambda: plan(Hybrid(), C(method="kivi", bit_width_inlier=[2, 4], seed=3)))
+    out["list_bits_wrong_length"] = _record_full(lambda: plan(Hybrid(), C(method="kivi", bit_width_inlier=[2, 4, 8])))
+    out["rvq_default_method"] = _record_full(lambda: plan(Flat(), C(head_dim=4)))
+    out["no_head_dim_anywhere"] = _record_full(lambda: plan(Nested(None), kivi))
+    return out

@@ -424,7 +424,7 @@ def main():
              "veloxquant_mlx.allocators", "veloxquant_mlx.allocators.vecinfer", "veloxquant_mlx.core.context",
              "veloxquant_mlx.core.abstractions", "veloxquant_mlx.cache.options", "veloxquant_mlx.cache.sliding_window_cache",
              "veloxquant_mlx.cache.sink_cache", "veloxquant_mlx.cache.skvq_cache", "veloxquant_mlx.cache.kitty_cache",
-             "veloxquant_mlx.cache.age_tiered_cache", "veloxquant_mlx.cache.base"]
+             "veloxquant_mlx.cache.age_tiered_cache", "veloxquant_mlx.cache.base", "veloxquant_mlx.metal._warmup"]
     saved = {k: sys.modules.get(k) for k in names}
     try:
         sys.modules["mlx"], sys.modules["mlx.core"] = mlx_pkg, mlx_pkg.core
@@ -526,9 +526,14 @@ def main():
         base_m = load_module(os.path.join(pkg, "cache", "base.py"), "veloxquant_mlx.cache.base")
         ns_cfg = types.SimpleNamespace(KVCacheConfig=base_m.KVCacheConfig, KVCacheFactory=base_m.KVCacheFactory,
                                        VecInferOptions=opts.VecInferOptions, KIVIOptions=opts.KIVIOptions, SKVQOptions=opts.SKVQOptions,
-                                       KittyOptions=opts.KittyOptions, AgeTieredKVOptions=opts.AgeTieredKVOptions)
+                                       KittyOptions=opts.KittyOptions, AgeTieredKVOptions=opts.AgeTieredKVOptions,
+                                       KVCacheBuilder=base_m.KVCacheBuilder, PlainCache=_GrowingKV)
+        warm = types.ModuleType("veloxquant_mlx.metal._warmup")          # (kernel pre-compilation: nothing to do here)
+        warm.warmup_for_config = lambda cfg: None
+        sys.modules["veloxquant_mlx.metal._warmup"] = warm
         with open(os.path.join(HERE, "config_traces.json"), "w") as fh:
-            json.dump({"config": config_scenarios.scenarios(ns_cfg), "construction": config_scenarios.construction_scenarios(ns_cfg)},
+            json.dump({"config": config_scenarios.scenarios(ns_cfg), "construction": config_scenarios.construction_scenarios(ns_cfg),
+                       "builder": config_scenarios.builder_scenarios(ns_cfg)},
                       fh, indent=1, sort_keys=True, default=str)
     finally:
         for key, val in saved.items():

@@ -105,7 +105,7 @@ def _config_namespace():
 
     return types.SimpleNamespace(KVCacheConfig=c.KVCacheConfig, KVCacheFactory=c.KVCacheFactory, VecInferOptions=c.VecInferOptions,
                                  KIVIOptions=c.KIVIOptions, SKVQOptions=c.SKVQOptions, KittyOptions=c.KittyOptions,
-                                 AgeTieredKVOptions=c.AgeTieredKVOptions)
+                                 AgeTieredKVOptions=c.AgeTieredKVOptions, KVCacheBuilder=c.KVCacheBuilder, PlainCache=c.DenseKVCache)
 
 
 def _load_config_scenarios():
@@ -150,3 +150,45 @@ def test_cache_construction_matches_the_reference_classes_scenario_by_scenario()
     assert set(mine) == set(ref["construction"]) and len(mine) >= 15
     for name, record in ref["construction"].items():
         assert mine[name] == record, (name, mine[name], record)
+
+
+def test_builder_plans_a_model_layer_by_layer_as_the_reference_builder_does():
+    """``KVCacheBuilder.for_model`` over stand-in models, against the reference's own builder run by
+    make_golden.py on the same models (``cache/base.py:1242-1433``): where the layers are found, the
+    per-layer head_dim and its three sources in their order of precedence, seeds by layer index, a
+    list-form width spread over the attention layers only, what a layer without attention receives (the
+    model's own slot, looked up on the class; a plain cache when the hook is missing, fails with a
+    warning, or returns the wrong length), and the error for a list of the wrong length."""
+    import json
+
+    mod, ref = _load_config_scenarios()
+    mine = json.loads(json.dumps(mod.builder_scenarios(_config_namespace()), default=str))
+    assert set(mine) == set(ref["builder"]) and len(mine) >= 15
+    for name, record in ref["builder"].items():
+        assert mine[name] == record, (name, mine[name], record)
+
+
+def test_dense_cache_for_unquantized_layers_grows_trims_and_restores():
+    import torch
+
+    from veloxquant_mlx_b200.cache import DenseKVCache
+
+    k, v = torch.randn(1, 2, 300, 8), torch.randn(1, 2, 300, 4)
+    d = DenseKVCache()
+    assert d.empty() and d.nbytes == 0 and d.state == (None, None)
+    a, b = d.update_and_fetch(k[:, :, :250], v[:, :, :250])
+    assert d.keys.shape[2] == 512 and a.shape[2] == 250
+    for t in range(250, 300):
+        a, b = d.update_and_fetch(k[:, :, t:t + 1], v[:, :, t:t + 1])
+    assert torch.equal(a, k) and torch.equal(b, v) and d.offset == d.size() == 300
+    assert d.nbytes == 300 * 2 * (8 + 4) * 4 and d.is_trimmable()
+    assert d.trim(5) == 5 and d.trim(1000) == 295 and d.offset == 0
+    a, b = d.update_and_fetch(k[:, :, :3], v[:, :, :3])
+    assert torch.equal(a, k[:, :, :3])
+    e = DenseKVCache()
+    e.state = d.state
+    assert e.offset == 3 and torch.equal(e.state[1], v[:, :, :3])
+    a, b = e.update_and_fetch(k[:, :, 3:4], v[:, :, 3:4])           # a restored cache grows from its live rows
+    assert torch.equal(a, k[:, :, :4]) and torch.equal(b, v[:, :, :4])
+    e.reset()
+    assert e.empty() and e.offset == 0

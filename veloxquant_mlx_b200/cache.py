@@ -294,18 +294,144 @@ class KVCacheBuilder:
 
     @staticmethod
     def for_model(model: Any, config: KVCacheConfig) -> list:
-        """Build per-layer caches for ``model`` (anything with ``.layers`` or a HF-style
-        ``.config.num_hidden_layers``)."""
-        layers = getattr(model, "layers", None)
-        if layers is None and hasattr(model, "model"):
-            layers = getattr(model.model, "layers", None)
-        if layers is not None:
-            n = len(layers)
-        elif hasattr(model, "config") and hasattr(model.config, "num_hidden_layers"):
-            n = int(model.config.num_hidden_layers)
-        else:
+        """One cache per layer of ``model`` (``cache/base.py:1242-1433``): ``model.layers`` or
+        ``model.model.layers``; a layer's head_dim comes from its ``self_attn`` / ``attn`` module, else
+        from ``model.args`` (``model.config`` for a Transformers model): ``head_dim`` or
+        ``hidden_size // num_attention_heads``; seeds are ``config.seed + layer index``; a list-form
+        ``bit_width_inlier`` is spread over the attention layers. A layer without attention gets the
+        slot of the model's own ``make_cache()`` (looked up on the class, so a patched instance hook is
+        not called back) or a :class:`DenseKVCache`. A model that only carries
+        ``config.num_hidden_layers`` gets that many caches of ``config`` as it stands."""
+        layers = getattr(model, "layers", None) or getattr(getattr(model, "model", None), "layers", None)
+        if layers is None:
+            if hasattr(model, "config") and hasattr(model.config, "num_hidden_layers"):
+                return KVCacheBuilder.for_layers(int(model.config.num_hidden_layers), config)
             raise QuantizerConfigError("KVCacheBuilder.for_model: cannot find the model's layers")
-        return KVCacheBuilder.for_layers(n, config)
+        native: list = []
+        native_fn = None
+        for klass in type(model).__mro__:
+            candidate = klass.__dict__.get("make_cache")
+            if candidate is not None:
+                native_fn = candidate.__get__(model, type(model))
+                break
+        if callable(native_fn):
+            try:
+                built = native_fn()
+                if isinstance(built, list) and len(built) == len(layers):
+                    native = built
+            except Exception as exc:
+                warnings.warn(
+                    f"KVCacheBuilder.for_model: {type(model).__name__}.make_cache() "
+                    f"raised {type(exc).__name__}: {exc}. Falling back to a plain "
+                    f"KVCache for any unquantized layer; recurrent/linear-attention "
+                    f"layers on this model may not behave correctly.",
+                    stacklevel=2,
+                )
+                native = []
+        args = getattr(model, "args", None)
+        if args is None:
+            args = getattr(model, "config", None)
+        if args is not None and not hasattr(args, "hidden_size"):
+            lm = getattr(model, "language_model", None)
+            if lm is not None:
+                args = getattr(lm, "args", args)
+        b_spec = config.bit_width_inlier
+        if isinstance(b_spec, list):
+            n_attn = sum(1 for layer in layers
+                         if (getattr(layer, "self_attn", None) or getattr(layer, "attn", None)) is not None)
+            if len(b_spec) != n_attn:
+                raise QuantizerConfigError(
+                    f"KVCacheBuilder.for_model: bit_width_inlier is a list of "
+                    f"length {len(b_spec)}, but model has {n_attn} attention "
+                    f"layers. The list must have one entry per attention layer.")
+        caches = []
+        attn_idx = 0
+        for i, layer in enumerate(layers):
+            hd = _resolve_head_dim(layer, args)
+            if hd is None:
+                caches.append(native[i] if i < len(native) else DenseKVCache())
+                continue
+            layer_b = b_spec[attn_idx] if isinstance(b_spec, list) else b_spec
+            caches.append(KVCacheFactory.create(dataclasses.replace(config, head_dim=hd, bit_width_inlier=layer_b,
+                                                                    seed=config.seed + i)))
+            attn_idx += 1
+        return caches
+
+
+def _resolve_head_dim(layer: Any, args: Any):
+    """A layer's attention head_dim, or ``None`` for a layer without attention
+    (``cache/base.py:455-470``)."""
+    attn = getattr(layer, "self_attn", None) or getattr(layer, "attn", None)
+    if attn is None:
+        return None
+    hd = getattr(attn, "head_dim", None)
+    if hd is None and args is not None:
+        hd = getattr(args, "head_dim", None) or (args.hidden_size // args.num_attention_heads)
+    return hd
+
+
+class DenseKVCache:
+    """Uncompressed keys and values for a layer this package does not quantize: the counterpart of
+    the plain container the reference hands such layers (``cache/base.py:1284-1330``). Buffers grow
+    in steps of 256 rows; ``update_and_fetch`` returns views of the live rows."""
+
+    step = 256
+
+    def __init__(self) -> None:
+        self.keys = self.values = None
+        self.offset = 0
+
+    def update_and_fetch(self, keys: torch.Tensor, values: torch.Tensor):
+        S = keys.shape[2]
+        prev = self.offset
+        if self.keys is None or prev + S > self.keys.shape[2]:
+            rows = -(-(self.step + S - 1) // self.step) * self.step
+
+            def grown(buf, new):
+                fresh = new.new_zeros((*new.shape[:2], rows, new.shape[3]))
+                return fresh if buf is None else torch.cat([buf[:, :, :prev], fresh], dim=2)
+
+            self.keys, self.values = grown(self.keys, keys), grown(self.values, values)
+        self.offset = prev + S
+        self.keys[:, :, prev:self.offset] = keys
+        self.values[:, :, prev:self.offset] = values
+        return self.keys[:, :, :self.offset], self.values[:, :, :self.offset]
+
+    def trim(self, n: int) -> int:
+        n = int(min(self.offset, max(n, 0)))
+        self.offset -= n
+        return n
+
+    def is_trimmable(self) -> bool:
+        return True
+
+    def empty(self) -> bool:
+        return self.keys is None
+
+    def size(self) -> int:
+        return self.offset
+
+    def reset(self) -> None:
+        self.keys = self.values = None
+        self.offset = 0
+
+    @property
+    def state(self):
+        if self.keys is None:
+            return (None, None)
+        return self.keys[:, :, :self.offset], self.values[:, :, :self.offset]
+
+    @state.setter
+    def state(self, v) -> None:
+        self.keys, self.values = v
+        self.offset = 0 if self.keys is None else self.keys.shape[2]
+
+    @property
+    def nbytes(self) -> int:
+        if self.keys is None:
+            return 0
+        k, v = self.state
+        return k.numel() * k.element_size() + v.numel() * v.element_size()
 
 
 def _native_only(config, who: str) -> None:
@@ -914,6 +1040,6 @@ from .cache_skvq import SKVQKVCache  # noqa: E402  (registers "skvq")
 from .cache_kitty import AgeTieredKVCache, KittyKVCache  # noqa: E402  (registers "kitty", "age_tiered")
 
 __all__ = ["QuantizerConfigError", "VecInferOptions", "KIVIOptions", "SKVQOptions", "KVCacheConfig", "KVCacheFactory",
-           "KVCacheBuilder", "KIVIKVCache", "SinkProtectedKVCache", "TurboQuantRVQKVCache", "SKVQKVCache", "KittyKVCache",
+           "KVCacheBuilder", "DenseKVCache", "KIVIKVCache", "SinkProtectedKVCache", "TurboQuantRVQKVCache", "SKVQKVCache", "KittyKVCache",
            "AgeTieredKVCache", "KittyOptions", "AgeTieredKVOptions", "VecInferKVCache",
            "RaBitQKVCache", "KVCache", "EncodedVector"]
