@@ -189,4 +189,27 @@ def builder_scenarios(ns):
     out["list_bits_wrong_length"] = _record_full(lambda: plan(Hybrid(), C(method="kivi", bit_width_inlier=[2, 4, 8])))
     out["rvq_default_method"] = _record_full(lambda: plan(Flat(), C(head_dim=4)))
     out["no_head_dim_anywhere"] = _record_full(lambda: plan(Nested(None), kivi))
+
+    # the fluent surface and build()'s own validation (the factory again replaced by the recorder)
+    def built(make):
+        original = F.create
+        F.create = staticmethod(lambda c: [c.method, c.head_dim, c.bit_width_inlier, c.bit_width_outlier, c.seed, c.capacity,
+                                           c.sliding_window, len(c.observers), str(c.dtype)])
+        try:
+            return make(Bld()).build()
+        finally:
+            F.create = staticmethod(original)
+
+    out["fluent_defaults"] = _record_full(lambda: built(lambda b: b))
+    out["fluent_every_setter"] = _record_full(lambda: built(
+        lambda b: b.with_method("kivi").with_head_dim(64).with_bit_width(4).with_seed(7).with_precision("f16").with_capacity(4096)
+        .with_sliding_window(512).with_observer("obs")))
+    out["fluent_bit_width_pair"] = _record_full(lambda: built(lambda b: b.with_method("kivi").with_bit_width(inlier=2, outlier=3)))
+    out["fluent_head_dim_96"] = _record_full(lambda: built(lambda b: b.with_head_dim(96)))
+    out["fluent_head_dim_0"] = _record_full(lambda: built(lambda b: b.with_head_dim(0)))
+    out["fluent_bits_0"] = _record_full(lambda: built(lambda b: b.with_method("kivi").with_bit_width(0)))
+    out["fluent_bits_empty_list"] = _record_full(lambda: built(lambda b: b.with_method("kivi").with_bit_width([])))
+    out["fluent_bits_list_with_zero"] = _record_full(lambda: built(lambda b: b.with_method("kivi").with_bit_width([2, 0])))
+    out["fluent_bits_list_with_float"] = _record_full(lambda: built(lambda b: b.with_method("kivi").with_bit_width([2, 2.0])))
+    out["fluent_bits_list_reaches_factory"] = _record_full(lambda: built(lambda b: b.with_method("kivi").with_bit_width([2, 4])))
     return out

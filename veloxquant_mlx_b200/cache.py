@@ -250,29 +250,61 @@ class KVCacheFactory:
 
 
 class KVCacheBuilder:
-    """Fluent builder (reference: ``cache/base.py:1195-1433``), hot-path subset."""
+    """Fluent builder (reference: ``cache/base.py:1050-1241``) for the fields the hot-path methods read;
+    ``build()`` validates as the reference's does (power-of-two head_dim, bit widths >= 1) before the
+    factory is called."""
 
     def __init__(self) -> None:
         self._config = KVCacheConfig()
 
-    def with_method(self, method: str) -> "KVCacheBuilder":
-        object.__setattr__(self._config, "method", method)
+    def _set(self, name: str, value) -> "KVCacheBuilder":
+        object.__setattr__(self._config, name, value)
         return self
+
+    def with_method(self, method: str) -> "KVCacheBuilder":
+        return self._set("method", method)
 
     def with_head_dim(self, d: int) -> "KVCacheBuilder":
-        object.__setattr__(self._config, "head_dim", int(d))
-        return self
+        return self._set("head_dim", d)
 
-    def with_bits(self, inlier: int) -> "KVCacheBuilder":
-        object.__setattr__(self._config, "bit_width_inlier", inlier)
-        return self
+    def with_bit_width(self, inlier, outlier=None) -> "KVCacheBuilder":
+        """``inlier``: an int, or a list with one entry per attention layer (then only
+        :meth:`for_model` can consume the configuration)."""
+        self._set("bit_width_inlier", inlier)
+        return self._set("bit_width_outlier", outlier)
+
+    def with_bits(self, inlier) -> "KVCacheBuilder":
+        return self._set("bit_width_inlier", inlier)
 
     def with_seed(self, seed: int) -> "KVCacheBuilder":
-        object.__setattr__(self._config, "seed", int(seed))
+        return self._set("seed", seed)
+
+    def with_precision(self, dtype) -> "KVCacheBuilder":
+        return self._set("dtype", dtype)
+
+    def with_capacity(self, max_tokens: int) -> "KVCacheBuilder":
+        return self._set("capacity", max_tokens)
+
+    def with_observer(self, observer) -> "KVCacheBuilder":
+        self._config.observers.append(observer)
         return self
 
+    def with_sliding_window(self, window_size: int) -> "KVCacheBuilder":
+        return self._set("sliding_window", window_size)
+
     def build(self):
-        return KVCacheFactory.create(self._config)
+        cfg = self._config
+        d = cfg.head_dim
+        if not (d >= 1 and (d & (d - 1)) == 0):
+            raise QuantizerConfigError(f"KVCacheBuilder: head_dim={d} must be a power of 2.")
+        if isinstance(cfg.bit_width_inlier, list):
+            if not cfg.bit_width_inlier:
+                raise QuantizerConfigError("KVCacheBuilder: bit_width_inlier list must not be empty.")
+            if not all(isinstance(b, int) and b >= 1 for b in cfg.bit_width_inlier):
+                raise QuantizerConfigError("KVCacheBuilder: every element of bit_width_inlier must be an int >= 1.")
+        elif cfg.bit_width_inlier < 1:
+            raise QuantizerConfigError(f"KVCacheBuilder: bit_width_inlier={cfg.bit_width_inlier} must be >= 1.")
+        return KVCacheFactory.create(cfg)
 
     @staticmethod
     def for_layers(n_layers: int, config: KVCacheConfig, head_dims=None) -> list:
