@@ -252,3 +252,41 @@ def test_mask_recogniser_agrees_with_the_reference_function_on_every_recorded_ma
         assert res == (ok, causal, window), (i, z[f"m{i}"].shape, z[f"m{i}"].dtype)
         accepted += ok
     assert 100 < accepted < 200
+
+
+def test_hf_cache_is_planned_from_the_model_layer_by_layer():
+    """``make_hf_cache(model, config)`` asks ``KVCacheBuilder.for_model``: the head_dim of every layer is
+    read from the model's attention modules (not from the configuration's default), seeds follow the layer
+    index, an instance-level ``make_cache`` hook installed by an earlier patch is not called back. The
+    factory is replaced by a recorder, so this needs no device."""
+    from transformers import LlamaConfig, LlamaForCausalLM
+
+    from veloxquant_mlx_b200 import cache as c
+
+    cfg = LlamaConfig(vocab_size=50, hidden_size=128, intermediate_size=64, num_hidden_layers=3, num_attention_heads=4,
+                      num_key_value_heads=2, head_dim=32, max_position_embeddings=64)
+    model = LlamaForCausalLM(cfg).eval()
+    model.make_cache = lambda: 1 / 0
+    seen = []
+
+    class Recorded(c.DenseKVCache):
+        def __init__(self, config):
+            super().__init__()
+            seen.append((config.method, config.head_dim, config.bit_width_inlier, config.seed))
+
+    original = c.KVCacheFactory.create
+    c.KVCacheFactory.create = staticmethod(Recorded)
+    try:
+        hf = I.make_hf_cache(model, c.KVCacheConfig(method="kivi", bit_width_inlier=[2, 4, 8], seed=5))
+        by_count = I.make_hf_cache(2, c.KVCacheConfig(method="kivi", head_dim=64, seed=1))
+    finally:
+        c.KVCacheFactory.create = staticmethod(original)
+    assert seen == [("kivi", 32, 2, 5), ("kivi", 32, 4, 6), ("kivi", 32, 8, 7), ("kivi", 64, 2, 1), ("kivi", 64, 2, 2)]
+    assert len(hf.layers) == 3 and len(by_count.layers) == 2 and hf.get_seq_length() == 0
+    # the adapter drives any cache of the list through the same calls: a prefill and a step on the stand-ins
+    ids = torch.randint(1, 50, (1, 9))
+    with torch.no_grad(), warnings.catch_warnings():
+        warnings.simplefilter("ignore")
+        out = model(ids, past_key_values=hf, use_cache=True)
+        model(ids[:, -1:], past_key_values=hf, use_cache=True)
+    assert hf.get_seq_length() == 10 and torch.isfinite(out.logits).all()

@@ -208,13 +208,18 @@ _LAYER_CLASS = None
 
 
 def make_hf_cache(model_or_n_layers: Any, config: KVCacheConfig):
-    """A fresh ``transformers.Cache`` whose layers are caches of this package (one per attention
-    layer, seeds ``config.seed + i``, list-form ``bit_width_inlier`` spread over the layers)."""
+    """A fresh ``transformers.Cache`` whose layers are caches of this package: for a model, what
+    :meth:`KVCacheBuilder.for_model` plans for it (``integration/mlx_lm_patch.py:25-80`` builds its
+    list the same way); for a layer count, that many caches of ``config`` with seeds ``config.seed + i``
+    and a list-form ``bit_width_inlier`` spread over them."""
     from transformers.cache_utils import Cache
 
-    n = model_or_n_layers if isinstance(model_or_n_layers, int) else _n_layers_of(model_or_n_layers)
     Layer = make_cache_layer_class()
-    return Cache(layers=[Layer(c) for c in KVCacheBuilder.for_layers(n, config)])
+    if isinstance(model_or_n_layers, int):
+        caches = KVCacheBuilder.for_layers(model_or_n_layers, config)
+    else:   # per-layer head_dim from the model itself, a plain cache for a layer without attention
+        caches = KVCacheBuilder.for_model(model_or_n_layers, config)
+    return Cache(layers=[Layer(c) for c in caches])
 
 
 def patch_model_kv_cache(model: Any, config: KVCacheConfig):
