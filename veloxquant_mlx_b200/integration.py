@@ -122,16 +122,6 @@ def _dense_sdpa(q, k, v, scale, mask):
 # ----------------------------------------------------------------------------------------------
 # Hugging Face Transformers
 # ----------------------------------------------------------------------------------------------
-def _n_layers_of(model: Any) -> int:
-    cfg = getattr(model, "config", None)
-    if cfg is not None and hasattr(cfg, "num_hidden_layers"):
-        return int(cfg.num_hidden_layers)
-    layers = getattr(model, "layers", None) or getattr(getattr(model, "model", None), "layers", None)
-    if layers is None:
-        raise ValueError("cannot find the model's layer count (no config.num_hidden_layers, no .layers)")
-    return len(layers)
-
-
 def _cache_layer_base():
     from transformers.cache_utils import CacheLayerMixin
 
