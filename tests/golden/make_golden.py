@@ -61,6 +61,10 @@ What is executed from the reference, unmodified:
   smooth-factor broadcasting convention; outputs and the accept / reject table go to
   ``vq_transform.npz``.
 
+* The parameter lists of the kernel wrappers (``metal/_*.py``, ``metal/fused_sdpa.py``) and of the
+  VecInfer functions are read from the parsed source, without executing them, into
+  ``wrapper_signatures.json``.
+
 Nothing here imports the oracle: the fixtures are the reference's outputs and
 the oracle is checked against them by ``tests/test_oracle_golden.py``.
 """
@@ -544,6 +548,7 @@ def main():
     _rvq_reference_section(pkg)
     _kivi_quantizer_section(pkg)
     _vq_transform_section(pkg)
+    _wrapper_signatures_section(pkg)
     print("golden fixtures written to", HERE)
 
 
@@ -760,6 +765,45 @@ def _vq_transform_section(pkg: str) -> None:
     except ValueError as e:
         out["lut_bad"] = np.asarray(str(e))
     np.savez_compressed(os.path.join(HERE, "vq_transform.npz"), **out)
+
+
+WRAPPER_FILES = {
+    "metal/_kivi_quant.py": ["kivi_group_quant_dequant"],
+    "metal/_scalar_attend.py": ["scalar_fused_decode_attend", "scalar_fused_decode_attend_batched", "scalar_decode_once",
+                                "scalar_predecoded_attend"],
+    "metal/_bit_packing.py": ["turboquant_bit_pack", "turboquant_bit_unpack"],
+    "metal/_rabitq.py": ["rabitq_hamming_score"], "metal/_rabitq_attend.py": ["rabitq_fused_attend"],
+    "metal/_rabitq_encode.py": ["rabitq_encode"], "metal/_rabitq_prefill.py": ["rabitq_prefill_attend"],
+    "metal/_rabitq_values.py": ["rabitq_pack_values"], "metal/_rvq_quant_pack.py": ["rvq_quant_pack"],
+    "metal/_rvq_unpack_decode.py": ["rvq_unpack_decode"],
+    "metal/_vecinfer.py": ["vecinfer_quantize_metal", "vecinfer_dequant_metal", "vecinfer_encode_decode_metal",
+                           "vecinfer_encode_decode_simple_metal"],
+    "metal/fused_sdpa.py": ["metal_fused_sdpa", "supports_shape"],
+    "allocators/vecinfer.py": ["quantize_vq", "dequantize_vq", "compute_query_lut", "apply_dual_transform_keys",
+                               "apply_dual_transform_queries", "walsh_hadamard_matrix"],
+}
+
+
+def _wrapper_signatures_section(pkg: str) -> None:
+    """The parameter lists of the reference's kernel wrappers and VecInfer functions on this path, read
+    from the parsed source (nothing is executed): positional names in order, keyword-only names, how
+    many positionals carry a default. Writes ``wrapper_signatures.json``."""
+    import json
+
+    out = {}
+    for rel, names in WRAPPER_FILES.items():
+        with open(os.path.join(pkg, *rel.split("/")), "r", encoding="utf-8") as fh:
+            tree = ast.parse(fh.read())
+        found = {n.name: n for n in tree.body if isinstance(n, ast.FunctionDef) and n.name in names}
+        missing = set(names) - set(found)
+        if missing:
+            raise RuntimeError(f"{rel}: functions not found: {sorted(missing)}")
+        for name, node in found.items():
+            a = node.args
+            out[name] = {"file": rel, "positional": [x.arg for x in a.posonlyargs + a.args], "keyword_only": [x.arg for x in a.kwonlyargs],
+                         "n_defaults": len(a.defaults)}
+    with open(os.path.join(HERE, "wrapper_signatures.json"), "w") as fh:
+        json.dump(out, fh, indent=1, sort_keys=True)
 
 
 class _GrowingKV:

@@ -91,7 +91,7 @@ def test_pack_values_and_hamming(shape):
     bits = rng.integers(0, 256, (97, 16), dtype=np.uint8)
     qb = rng.integers(0, 256, 16, dtype=np.uint8)
     cx = rng.standard_normal(97).astype(np.float32)
-    s = _r().rabitq_hamming_score(_t(qb), _t(bits), 0.25, _t(cx))
+    s = _r().rabitq_hamming_score(_t(qb), _t(bits), _t(cx), 0.25)      # (the reference's order: constants, then the scale)
     np.testing.assert_array_equal(s.cpu().numpy(), o_rq.hamming_score(qb, bits, 0.25, cx))
 
 

@@ -123,3 +123,44 @@ def test_dual_transforms_and_lut_follow_the_reference_functions_on_every_smooth_
     with pytest.raises(ValueError) as e:
         vi.compute_query_lut(torch.from_numpy(z["in_q4"]), torch.ones(16, 5), 5)
     assert str(e.value) == str(z["lut_bad"])
+
+
+def test_every_wrapper_takes_the_reference_wrappers_arguments_in_their_order():
+    """``tests/golden/wrapper_signatures.json`` holds the parameter lists of the reference's kernel
+    wrappers and VecInfer functions on this path, read from its source. Each one exists here under the
+    same name, is importable from the single ``kernels`` module as in the reference
+    (``metal/kernels.py``), takes the same positional parameters in the same order (extra parameters
+    may only follow, with defaults), knows every keyword-only name, and requires no argument the
+    reference gives a default."""
+    import inspect
+    import json
+    import os
+
+    from veloxquant_mlx_b200 import integration, vecinfer
+
+    with open(os.path.join(os.path.dirname(__file__), "golden", "wrapper_signatures.json")) as fh:
+        ref = json.load(fh)
+    assert len(ref) == 26
+    for name, spec in ref.items():
+        if spec["file"].startswith("metal/_") or name == "metal_fused_sdpa":
+            fn = getattr(k, name)                                   # the reference's one import point
+        else:
+            fn = getattr(vecinfer, name, None) or getattr(integration, name)
+        params = list(inspect.signature(fn).parameters.values())
+        positional = [p for p in params if p.kind in (p.POSITIONAL_ONLY, p.POSITIONAL_OR_KEYWORD)]
+        names = [p.name for p in positional]
+        n = len(spec["positional"])
+        assert names[:n] == spec["positional"], (name, names, spec["positional"])
+        required = n - spec["n_defaults"]
+        assert all(p.default is not p.empty for p in positional[required:]), (name, "a required argument the reference defaults")
+        accepted = {p.name for p in params}
+        assert set(spec["keyword_only"]) <= accepted, (name, spec["keyword_only"])
+        assert all(p.default is not p.empty for p in params if p.kind == p.KEYWORD_ONLY), name
+    assert k.rvq_quant_pack.__module__.endswith(".rvq") and k.rabitq_encode.__module__.endswith(".rabitq")
+    with pytest.raises(AttributeError):
+        k.no_such_wrapper
+    assert vecinfer.supports_shape(256, 16, 128) and vecinfer.supports_shape(n_centroids=256, n_sub=32, head_dim=256)
+    assert not vecinfer.supports_shape(256, 16, 100) and not vecinfer.supports_shape(256, 16, 512)
+    assert not vecinfer.supports_shape(4096, 32, 128) and not vecinfer.supports_shape(0, 16, 128)
+    with pytest.raises(ValueError, match="one constant per candidate"):
+        k.rabitq_hamming_score(torch.zeros(2, dtype=torch.uint8), torch.zeros(5, 2, dtype=torch.uint8), 0.25, torch.zeros(5))

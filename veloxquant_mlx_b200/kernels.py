@@ -674,9 +674,31 @@ def turboquant_bit_unpack(packed: torch.Tensor, N: int, b: int) -> torch.Tensor:
     return out
 
 
+# The reference gathers every kernel wrapper in one module (``metal/kernels.py:19-146``), so that
+# ``from ...kernels import rvq_quant_pack`` works whatever file defines it. The wrappers of the other
+# code families live in their own modules here (which import this one), and are resolved on first use.
+_DEFINED_ELSEWHERE = {
+    "rabitq_encode": "rabitq", "rabitq_fused_attend": "rabitq", "rabitq_hamming_score": "rabitq",
+    "rabitq_pack_values": "rabitq", "rabitq_prefill_attend": "rabitq",
+    "rvq_quant_pack": "rvq", "rvq_unpack_decode": "rvq",
+    "vecinfer_quantize_metal": "vecinfer", "vecinfer_dequant_metal": "vecinfer",
+    "vecinfer_encode_decode_metal": "vecinfer", "vecinfer_encode_decode_simple_metal": "vecinfer",
+    "metal_fused_sdpa": "vecinfer",
+}
+
+
+def __getattr__(name: str):
+    module = _DEFINED_ELSEWHERE.get(name)
+    if module is None:
+        raise AttributeError(f"module {__name__!r} has no attribute {name!r}")
+    import importlib
+
+    return getattr(importlib.import_module("." + module, __package__), name)
+
+
 __all__ = [
     "kivi_available", "tune", "attend_status", "quantize_status", "storage_bits", "kivi_group_quant_dequant", "kivi_quantize", "kivi_quantize_into",
     "scalar_decode_once", "kivi_decode_attend", "scalar_fused_decode_attend", "scalar_predecoded_attend",
     "scalar_fused_decode_attend_batched", "lse_merge",
-    "turboquant_bit_pack", "turboquant_bit_unpack",
+    "turboquant_bit_pack", "turboquant_bit_unpack", *_DEFINED_ELSEWHERE,
 ]

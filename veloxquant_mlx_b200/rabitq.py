@@ -87,19 +87,28 @@ def rabitq_pack_values(v_idx: torch.Tensor) -> torch.Tensor:
     return out
 
 
-def rabitq_hamming_score(qbits: torch.Tensor, bits: torch.Tensor, scale: float, cx: torch.Tensor) -> torch.Tensor:
-    """``score[i] = popcount(q ^ bits[i]) * scale + cx[i]`` (``metal/_rabitq.py:63-103``)."""
+def rabitq_hamming_score(qbits: torch.Tensor, bits: torch.Tensor, Cx: torch.Tensor, scale) -> torch.Tensor:
+    """``score[i] = popcount(qbits ^ bits[i]) * scale + Cx[i]`` (``metal/_rabitq.py:63-103``, same argument
+    order): ``qbits [D//8]`` and ``bits [N, D//8]`` uint8, ``Cx [N]``, ``scale`` a number or a one-element
+    tensor. Returns float32 ``[N]``."""
     if qbits.ndim != 1:
         raise ValueError(f"rabitq_hamming_score: qbits must be 1D, got {tuple(qbits.shape)}")
     if bits.ndim != 2:
         raise ValueError(f"rabitq_hamming_score: bits must be 2D [N, D//8], got {tuple(bits.shape)}")
     N, n_bytes = bits.shape
     if qbits.shape[0] != n_bytes:
-        raise ValueError(f"rabitq_hamming_score: qbits has {qbits.shape[0]} bytes, bits rows have {n_bytes}")
+        raise ValueError(f"rabitq_hamming_score: qbits length {qbits.shape[0]} != bits cols {n_bytes}")
+    if not isinstance(Cx, torch.Tensor) or Cx.numel() != N:
+        raise ValueError(f"rabitq_hamming_score: Cx must hold one constant per candidate ({N}), got "
+                         f"{tuple(Cx.shape) if isinstance(Cx, torch.Tensor) else type(Cx).__name__}")
+    if isinstance(scale, torch.Tensor):
+        if scale.numel() != 1:
+            raise ValueError(f"rabitq_hamming_score: scale must be a single value, got {tuple(scale.shape)}")
+        scale = scale.reshape(()).item()
     require_cuda(bits, "rabitq_hamming_score: bits")
     qb = qbits.to(device=bits.device, dtype=torch.uint8).contiguous()
     bb = bits.to(torch.uint8).contiguous()
-    cxf = cx.to(device=bits.device, dtype=torch.float32).contiguous()
+    cxf = Cx.reshape(N).to(device=bits.device, dtype=torch.float32).contiguous()
     out = torch.empty((N,), dtype=torch.float32, device=bits.device)
     with _lib.on_device(bits.device):
         check(lib().vq_rabitq_hamming_score(qb.data_ptr(), bb.data_ptr(), N, n_bytes, float(scale), cxf.data_ptr(),

@@ -343,6 +343,16 @@ def fused_sdpa_vq(q_tilde: torch.Tensor, k_indices: torch.Tensor, k_codebook: to
     return out
 
 
+def supports_shape(n_centroids: int, n_sub: int, head_dim: int) -> bool:
+    """Whether the lookup-table attention of this package takes a configuration (the reference's
+    check of its own kernel's caps, ``metal/fused_sdpa.py:141-147``: 256 centroids, 16 sub-spaces,
+    head_dim 256). Here: head_dim a multiple of 32 up to 256, and one query head's table
+    (``n_sub * n_centroids`` float32) within 200 KiB of shared memory; the query heads of one KV head
+    share a thread block, up to eight of them, and their tables must fit together."""
+    return (n_centroids >= 1 and n_sub >= 1 and 1 <= head_dim <= 256 and head_dim % 32 == 0
+            and n_sub * n_centroids * 4 <= 200 * 1024)
+
+
 def metal_fused_sdpa(q_tilde, k_indices, k_codebook, v_indices, v_codebook, scale, *, causal=True,
                      sliding_window=0, out_dtype=None):
     """The reference's name for :func:`fused_sdpa_vq` (``metal/fused_sdpa.py:200``)."""
@@ -353,4 +363,4 @@ def metal_fused_sdpa(q_tilde, k_indices, k_codebook, v_indices, v_codebook, scal
 __all__ = ["walsh_hadamard_matrix", "apply_dual_transform_keys", "apply_dual_transform_queries", "quantize_vq",
            "vecinfer_quantize", "dequantize_vq", "compute_query_lut", "fused_sdpa_vq", "metal_fused_sdpa",
            "vecinfer_quantize_metal", "vecinfer_dequant_metal", "vecinfer_encode_decode_metal",
-           "vecinfer_encode_decode_simple_metal", "vecinfer_encode_keys"]
+           "vecinfer_encode_decode_simple_metal", "vecinfer_encode_keys", "supports_shape"]
