@@ -63,7 +63,8 @@ What is executed from the reference, unmodified:
 
 * The parameter lists of the kernel wrappers (``metal/_*.py``, ``metal/fused_sdpa.py``) and of the
   VecInfer functions are read from the parsed source, without executing them, into
-  ``wrapper_signatures.json``.
+  ``wrapper_signatures.json``; the public properties, setters and method parameter lists of the
+  cache classes the same way into ``class_surfaces.json``.
 
 Nothing here imports the oracle: the fixtures are the reference's outputs and
 the oracle is checked against them by ``tests/test_oracle_golden.py``.
@@ -549,6 +550,7 @@ def main():
     _kivi_quantizer_section(pkg)
     _vq_transform_section(pkg)
     _wrapper_signatures_section(pkg)
+    _class_surfaces_section(pkg)
     print("golden fixtures written to", HERE)
 
 
@@ -803,6 +805,45 @@ def _wrapper_signatures_section(pkg: str) -> None:
             out[name] = {"file": rel, "positional": [x.arg for x in a.posonlyargs + a.args], "keyword_only": [x.arg for x in a.kwonlyargs],
                          "n_defaults": len(a.defaults)}
     with open(os.path.join(HERE, "wrapper_signatures.json"), "w") as fh:
+        json.dump(out, fh, indent=1, sort_keys=True)
+
+
+CACHE_CLASS_FILES = {
+    "cache/kivi_cache.py": "KIVIKVCache", "cache/sink_cache.py": "SinkProtectedKVCache", "cache/vecinfer_cache.py": "VecInferKVCache",
+    "cache/turboquant_rvq_cache.py": "TurboQuantRVQKVCache", "cache/skvq_cache.py": "SKVQKVCache",
+    "cache/kitty_cache.py": "KittyKVCache", "cache/age_tiered_cache.py": "AgeTieredKVCache",
+}
+
+
+def _class_surfaces_section(pkg: str) -> None:
+    """The public surface the reference's cache classes define themselves (what they inherit from their
+    serving framework's container is not in the checkout), read from the parsed source: per class its
+    public properties, which of them have a setter, and its public methods with their parameter lists.
+    Writes ``class_surfaces.json``."""
+    import json
+
+    out = {}
+    for rel, cls_name in CACHE_CLASS_FILES.items():
+        with open(os.path.join(pkg, *rel.split("/")), "r", encoding="utf-8") as fh:
+            tree = ast.parse(fh.read())
+        node = next(n for n in tree.body if isinstance(n, ast.ClassDef) and n.name == cls_name)
+        rec = {"file": rel, "properties": [], "setters": [], "methods": {}}
+        for n in node.body:
+            if isinstance(n, ast.Assign) and isinstance(n.value, ast.Call) and getattr(n.value.func, "id", "") == "property":
+                rec["properties"] += [t.id for t in n.targets if isinstance(t, ast.Name) and not t.id.startswith("_")]
+            if not isinstance(n, ast.FunctionDef) or n.name.startswith("_"):
+                continue
+            decorators = [ast.unparse(d) for d in n.decorator_list]
+            if "property" in decorators:
+                rec["properties"].append(n.name)
+            elif any(d.endswith(".setter") for d in decorators):
+                rec["setters"].append(n.name)
+            else:
+                a = n.args
+                rec["methods"][n.name] = {"positional": [x.arg for x in a.posonlyargs + a.args][0 if "staticmethod" in decorators else 1:],
+                                          "keyword_only": [x.arg for x in a.kwonlyargs], "var_positional": a.vararg is not None}
+        out[cls_name] = rec
+    with open(os.path.join(HERE, "class_surfaces.json"), "w") as fh:
         json.dump(out, fh, indent=1, sort_keys=True)
 
 

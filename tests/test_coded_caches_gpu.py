@@ -90,8 +90,9 @@ def test_vecinfer_standard_mode_state_trim_growth_and_cap():
     q = torch.randn(2, 4, 1, D, device=DEV, dtype=torch.float16)
     assert d.offset == 340 and torch.equal(c.fused_sdpa(q, 0.125), d.fused_sdpa(q, 0.125))
     assert c.trim(100) == 100 and c.offset == 240
-    with pytest.raises(NotImplementedError):
-        c.merge()
+    with pytest.raises(AttributeError, match="does not support merge"):
+        c.merge
+    assert not hasattr(c, "merge")
     capped = _make("vecinfer", fused_sdpa=True, fused_sdpa_memory_bound=True, fused_sdpa_max_ctx=32, **kw)
     with pytest.raises(RuntimeError, match="fused_sdpa_max_ctx"):
         capped.update_and_fetch(k, v)

@@ -120,3 +120,80 @@ def test_standalone_calls_equal_the_batched_protocol(method):
     assert len(one) == 1
     if method != "vecinfer":        # one token: the output is that token's value (kept exact by these two caches)
         assert float((one.attend(q).float() - v[0].float()).abs().max()) < 1e-2
+
+
+def test_vecinfer_byte_counters_follow_the_reference_class_trace():
+    """The counters behind ``compressed_key_bytes`` / ``compressed_value_bytes`` / ``fp16_key_bytes`` /
+    ``fp16_value_bytes`` over the recorded call script (appends and a trim) against what the reference's
+    ``VecInferKVCache`` held after each call when it was executed over the NumPy stand-ins
+    (``tests/golden/cache_traces.npz``); the accounting is host arithmetic and needs no device."""
+    import os
+
+    import numpy as np
+
+    import veloxquant_mlx_b200.cache  # noqa: F401  (the package's import order: the registry first)
+    from veloxquant_mlx_b200.cache_coded import VecInferKVCache, _VQByteAccounting
+
+    assert issubclass(VecInferKVCache, _VQByteAccounting)
+    for name in ("compressed_key_bytes", "fp16_key_bytes", "compressed_value_bytes", "fp16_value_bytes", "codebook_bytes"):
+        assert isinstance(getattr(VecInferKVCache, name), property)
+
+    class Counters(_VQByteAccounting):
+        _key_sub_dim, _value_sub_dim, _key_bits, _value_bits = 4, 8, 8, 8      # the trace's configuration
+
+    z = np.load(os.path.join(os.path.dirname(__file__), "golden", "cache_traces.npz"))
+    B, H, _, D = z["k"].shape
+    c, offset, checked = Counters(), 0, 0
+    c._reset_bytes()
+    for i, (op, a, b) in enumerate(z["script"].tolist()):
+        if op == 1:
+            c._scale_bytes((offset - a) / offset)          # what trim(a) does after lowering the offset
+            offset -= a
+            continue
+        c._account_bytes(B, H, b - a, D)
+        offset += b - a
+        if f"vecinfer_c_{i}" in z:
+            want = z[f"vecinfer_c_{i}"].tolist()            # offset, key bytes, value bytes, fp16 key bytes, tokens seen
+            assert [offset, c.compressed_key_bytes, c.compressed_value_bytes, c.fp16_key_bytes, c._tokens_seen] == want, i
+            assert c.fp16_value_bytes == c.fp16_key_bytes
+            checked += 1
+    assert checked >= 10 and c.codebook_bytes == 256 * 4 * 2 + 256 * 8 * 2
+
+
+def test_cache_classes_define_the_public_surface_of_the_reference_classes():
+    """``tests/golden/class_surfaces.json``: the public properties, setters and method parameter lists the
+    reference's cache classes define themselves, read from its source. Each class here has every
+    property as a property (with a setter where the reference has one) and every method with the same
+    parameters in the same order. ``merge`` is a property that raises ``AttributeError`` wherever the
+    reference makes it one, so that ``hasattr(cache, "merge")`` is false. One name is left out:
+    ``TurboQuantRVQKVCache.make_mask``, which forwards to the mask builder of the reference's serving
+    framework; here the model library builds the masks."""
+    import inspect
+    import json
+    import os
+
+    from veloxquant_mlx_b200 import cache as c
+
+    with open(os.path.join(os.path.dirname(__file__), "golden", "class_surfaces.json")) as fh:
+        ref = json.load(fh)
+    left_out = {("TurboQuantRVQKVCache", "make_mask")}
+    assert len(ref) == 7
+    for cls_name, spec in ref.items():
+        cls = getattr(c, cls_name)
+        for name in spec["properties"]:
+            assert isinstance(inspect.getattr_static(cls, name), property), (cls_name, name)
+        for name in spec["setters"]:
+            assert inspect.getattr_static(cls, name).fset is not None, (cls_name, name)
+        for name, sig in spec["methods"].items():
+            if (cls_name, name) in left_out:
+                continue
+            fn = inspect.getattr_static(cls, name)
+            fn = fn.__func__ if isinstance(fn, (classmethod, staticmethod)) else fn
+            params = list(inspect.signature(fn).parameters.values())[1:]          # without self / cls
+            names = [p.name for p in params if p.kind in (p.POSITIONAL_ONLY, p.POSITIONAL_OR_KEYWORD)]
+            if not sig["var_positional"]:
+                assert names[:len(sig["positional"])] == sig["positional"], (cls_name, name, names)
+            assert set(sig["keyword_only"]) <= {p.name for p in params}, (cls_name, name)
+        if "merge" in spec["properties"]:
+            obj = object.__new__(cls)
+            assert not hasattr(obj, "merge"), cls_name

@@ -26,7 +26,53 @@ def _grow(old, shape, dtype, device):
     return t
 
 
-class VecInferKVCache(StandaloneProtocol):
+class _VQByteAccounting:
+    """Byte and token counters of the reference's VecInfer cache: estimated packed bytes of the index
+    streams and their float16 equivalents, added per append (``cache/vecinfer_cache.py:653-664``),
+    scaled with the token count on ``trim`` (``:627-637``), read through the reference's properties
+    (``:736-761``). Needs ``_key_sub_dim``, ``_value_sub_dim``, ``_key_bits``, ``_value_bits``."""
+
+    def _reset_bytes(self) -> None:
+        self._key_bytes_compressed = self._value_bytes_compressed = 0
+        self._key_bytes_fp16 = self._value_bytes_fp16 = 0
+        self._tokens_seen = 0
+
+    def _account_bytes(self, B: int, H: int, S: int, D: int) -> None:
+        k_bits_per_tok = (D // self._key_sub_dim) * self._key_bits
+        v_bits_per_tok = (D // self._value_sub_dim) * self._value_bits
+        self._key_bytes_compressed += math.ceil(k_bits_per_tok / 8) * H * B * S
+        self._value_bytes_compressed += math.ceil(v_bits_per_tok / 8) * H * B * S
+        self._key_bytes_fp16 += H * B * S * D * 2
+        self._value_bytes_fp16 += H * B * S * D * 2
+        self._tokens_seen += S
+
+    def _scale_bytes(self, keep: float) -> None:
+        for name in ("_key_bytes_compressed", "_value_bytes_compressed", "_key_bytes_fp16", "_value_bytes_fp16", "_tokens_seen"):
+            setattr(self, name, int(getattr(self, name) * keep))
+
+    @property
+    def compressed_key_bytes(self) -> int:
+        return self._key_bytes_compressed
+
+    @property
+    def fp16_key_bytes(self) -> int:
+        return self._key_bytes_fp16
+
+    @property
+    def compressed_value_bytes(self) -> int:
+        return self._value_bytes_compressed
+
+    @property
+    def fp16_value_bytes(self) -> int:
+        return self._value_bytes_fp16
+
+    @property
+    def codebook_bytes(self) -> int:
+        """Both codebooks at two bytes an entry."""
+        return (2 ** self._key_bits) * self._key_sub_dim * 2 + (2 ** self._value_bits) * self._value_sub_dim * 2
+
+
+class VecInferKVCache(_VQByteAccounting, StandaloneProtocol):
     """Keys dual-transformed (smooth + Hadamard) and product-VQ coded on append; values
     product-VQ coded. Only codebook indices are stored (one byte each for <= 256 centroids);
     :meth:`fused_sdpa` attends over them through a per-query lookup table.
@@ -86,7 +132,7 @@ class VecInferKVCache(StandaloneProtocol):
         self._H = None
         self.offset = 0
         self._dtype = None
-        self._key_bytes_fp16 = self._value_bytes_fp16 = 0
+        self._reset_bytes()
 
     # ------------------------------------------------------------------ helpers
     def _index_dtype(self, n_c: int):
@@ -151,8 +197,7 @@ class VecInferKVCache(StandaloneProtocol):
         self._k_idx[:, :, lo:hi] = vi.quantize_vq(k_tilde, self._key_codebook, self._key_sub_dim, index_dtype=self._k_idx.dtype)
         self._v_idx[:, :, lo:hi] = vi.quantize_vq(values, self._value_codebook, self._value_sub_dim, index_dtype=self._v_idx.dtype)
         self.offset = hi
-        self._key_bytes_fp16 += B * H * S * D * 2
-        self._value_bytes_fp16 += B * H * S * D * 2
+        self._account_bytes(B, H, S, D)
         if self._memory_bound:
             z = keys.new_zeros((B, H, 0, D))
             return z, z
@@ -177,13 +222,16 @@ class VecInferKVCache(StandaloneProtocol):
                                 causal=causal, sliding_window=sliding_window, out_dtype=q.dtype, s_kv=self.offset)
 
     def trim(self, n: int) -> int:
-        n = int(min(max(n, 0), self.offset))
+        old = self.offset
+        n = int(min(max(n, 0), old))
         self.offset -= n
+        if n:
+            self._scale_bytes(self.offset / old)
         return n
 
     def _reset_tokens(self) -> None:
         self.offset = 0
-        self._key_bytes_fp16 = self._value_bytes_fp16 = 0
+        self._reset_bytes()
 
     def check_status(self) -> None:
         """Raise if a bounded device-side wait of an earlier quantize or attention call ran out."""
@@ -236,8 +284,12 @@ class VecInferKVCache(StandaloneProtocol):
         if off == 0:
             self._reset_tokens()
 
-    def merge(self, *a, **k):
-        raise NotImplementedError("VecInferKVCache.merge: batched-cache merging is not supported")
+    @property
+    def merge(self):
+        """Not a method but a property that raises ``AttributeError``, as in the reference
+        (``cache/vecinfer_cache.py:785-789``): a serving loop that asks ``hasattr(cache, "merge")`` before
+        batching caches must be told no, instead of merging them into an uncompressed batch cache."""
+        raise AttributeError("VecInferKVCache does not support merge()")
 
     @property
     def nbytes(self) -> int:
