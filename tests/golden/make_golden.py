@@ -65,6 +65,11 @@ What is executed from the reference, unmodified:
   VecInfer functions are read from the parsed source, without executing them, into
   ``wrapper_signatures.json``; the public properties, setters and method parameter lists of the
   cache classes the same way into ``class_surfaces.json``.
+* The kernel-wrapper modules themselves (``metal/_kivi_quant.py``, ``_scalar_attend.py``,
+  ``_rabitq*.py``, ``_rvq_*.py``, ``_vecinfer.py``, ``fused_sdpa.py``, with ``_kernel_utils.py``) are
+  loaded whole over the stand-in, whose kernel launcher only raises, and called with the arguments of
+  ``wrapper_scenarios.py`` that they must refuse before any launch; ``wrapper_refusals.json`` records
+  the exception types and messages.
 
 Nothing here imports the oracle: the fixtures are the reference's outputs and
 the oracle is checked against them by ``tests/test_oracle_golden.py``.
@@ -551,6 +556,7 @@ def main():
     _vq_transform_section(pkg)
     _wrapper_signatures_section(pkg)
     _class_surfaces_section(pkg)
+    _wrapper_refusals_section(pkg)
     print("golden fixtures written to", HERE)
 
 
@@ -845,6 +851,52 @@ def _class_surfaces_section(pkg: str) -> None:
         out[cls_name] = rec
     with open(os.path.join(HERE, "class_surfaces.json"), "w") as fh:
         json.dump(out, fh, indent=1, sort_keys=True)
+
+
+def _wrapper_refusals_section(pkg: str) -> None:
+    """The reference's kernel wrappers (``metal/_*.py``, ``metal/fused_sdpa.py``), loaded whole over the
+    NumPy stand-in with a kernel launcher that is never reached, on the calls of
+    ``wrapper_scenarios.py`` that they must refuse: exception types and messages go to
+    ``wrapper_refusals.json``."""
+    import json
+    import sys
+    import types
+
+    import wrapper_scenarios
+
+    mx = _mx_numpy_module()
+
+    def metal_kernel(**kw):
+        def launch(**k):
+            raise RuntimeError("kernel launcher reached")
+        return launch
+
+    mx.fast = types.SimpleNamespace(metal_kernel=metal_kernel)
+    mlx_pkg = types.ModuleType("mlx")
+    mlx_pkg.core = mx
+    modules = {rel: "veloxquant_mlx." + rel[:-3].replace("/", ".") for rel in WRAPPER_FILES if rel.startswith("metal/")}
+    names = ["mlx", "mlx.core", "veloxquant_mlx", "veloxquant_mlx.metal", "veloxquant_mlx.metal._kernel_utils"] + list(modules.values())
+    saved = {k: sys.modules.get(k) for k in names}
+    try:
+        sys.modules["mlx"], sys.modules["mlx.core"] = mlx_pkg, mx
+        for name in ("veloxquant_mlx", "veloxquant_mlx.metal"):
+            sys.modules[name] = types.ModuleType(name)
+        load_module(os.path.join(pkg, "metal", "_kernel_utils.py"), "veloxquant_mlx.metal._kernel_utils")
+        ns = types.SimpleNamespace()
+        for rel, mod_name in modules.items():
+            mod = load_module(os.path.join(pkg, *rel.split("/")), mod_name)
+            for fn_name in WRAPPER_FILES[rel]:
+                setattr(ns, fn_name, getattr(mod, fn_name))
+        records = wrapper_scenarios.refusal_scenarios(ns, lambda a: a)
+        assert all(r[0] != "accepted" and "launcher" not in r[1] for r in records.values()), records
+        with open(os.path.join(HERE, "wrapper_refusals.json"), "w") as fh:
+            json.dump(records, fh, indent=1, sort_keys=True)
+    finally:
+        for key, val in saved.items():
+            if val is None:
+                sys.modules.pop(key, None)
+            else:
+                sys.modules[key] = val
 
 
 class _GrowingKV:

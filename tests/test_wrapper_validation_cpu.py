@@ -164,3 +164,25 @@ def test_every_wrapper_takes_the_reference_wrappers_arguments_in_their_order():
     assert not vecinfer.supports_shape(4096, 32, 128) and not vecinfer.supports_shape(0, 16, 128)
     with pytest.raises(ValueError, match="one constant per candidate"):
         k.rabitq_hamming_score(torch.zeros(2, dtype=torch.uint8), torch.zeros(5, 2, dtype=torch.uint8), 0.25, torch.zeros(5))
+
+
+def test_wrappers_refuse_what_the_reference_wrappers_refuse_with_the_same_words():
+    """31 calls the reference's wrappers refuse before any launch (wrong ranks, head counts that do not
+    group, widths a sub-vector does not divide, table sizes that do not fit the bit width, ...), recorded
+    by make_golden.py from the reference's own wrapper modules executed over a NumPy stand-in
+    (``tests/golden/wrapper_refusals.json``): the wrappers here raise the same exception type with the
+    same message on CPU tensors, i.e. before the device is looked at."""
+    import importlib.util
+    import json
+    import os
+
+    here = os.path.join(os.path.dirname(__file__), "golden")
+    spec = importlib.util.spec_from_file_location("wrapper_scenarios", os.path.join(here, "wrapper_scenarios.py"))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    with open(os.path.join(here, "wrapper_refusals.json")) as fh:
+        ref = json.load(fh)
+    mine = mod.refusal_scenarios(k, torch.from_numpy)
+    assert set(mine) == set(ref) and len(ref) == 31
+    for name, record in ref.items():
+        assert mine[name] == record, (name, mine[name], record)

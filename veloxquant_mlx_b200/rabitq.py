@@ -46,11 +46,11 @@ def _encode(keys: torch.Tensor, diag, rotate: int, who: str):
         raise ValueError(f"{who}: D={D} exceeds the 1024 limit")
     if keys.dtype not in _FLOAT_DTYPES:
         raise ValueError(f"{who}: unsupported dtype {keys.dtype}")
+    if rotate and tuple(diag.shape) != (D,):
+        raise ValueError(f"{who}: diag must be [{D}], got {tuple(diag.shape)}")
     require_cuda(keys, f"{who}: keys")
     dptr = None
     if rotate:
-        if tuple(diag.shape) != (D,):
-            raise ValueError(f"{who}: diag must be [{D}], got {tuple(diag.shape)}")
         diag = diag.to(device=keys.device, dtype=torch.float32).contiguous()
         dptr = diag.data_ptr()
     keys = keys.contiguous()
@@ -77,7 +77,7 @@ def rabitq_encode_rotated(y: torch.Tensor):
 def rabitq_pack_values(v_idx: torch.Tensor) -> torch.Tensor:
     """Two 4-bit indices per byte, low nibble = even element (``metal/_rabitq_values.py:64-95``)."""
     if v_idx.shape[-1] % 2 != 0:
-        raise ValueError(f"rabitq_pack_values: last dim must be even, got {v_idx.shape[-1]}")
+        raise ValueError(f"rabitq_pack_values: last dimension must be even, got {v_idx.shape[-1]}")
     require_cuda(v_idx, "rabitq_pack_values: v_idx")
     v = v_idx.to(torch.uint8).contiguous()
     out = torch.empty((*v.shape[:-1], v.shape[-1] // 2), dtype=torch.uint8, device=v.device)

@@ -187,6 +187,10 @@ def unpack_indices(packed: torch.Tensor, bits: int, d: int) -> torch.Tensor:
     return codes.reshape(*packed.shape[:-1], -1)[..., :d].to(torch.uint8)
 
 
+def _count(t) -> int:
+    return int(t.numel()) if isinstance(t, torch.Tensor) else int(np.asarray(t).size)
+
+
 def _host_f32(t, n: int, name: str, who: str):
     a = t.detach().float().cpu().numpy() if isinstance(t, torch.Tensor) else np.asarray(t, dtype=np.float32)
     a = np.ascontiguousarray(a.reshape(-1), dtype=np.float32)
@@ -230,7 +234,7 @@ def rvq_quant_pack(rotated: torch.Tensor, centroids1, boundaries1, boundaries2, 
     the 64 KiB code table (default: for inputs of at least 65 536 words)."""
     who = "rvq_quant_pack"
     if rotated.ndim != 2:
-        raise ValueError(f"{who}: rotated must be 2D [N, D], got shape {tuple(rotated.shape)}")
+        raise ValueError(f"{who}: rotated must be 2D [N, D], got {tuple(rotated.shape)}")
     if not 1 <= bits <= 4:
         raise ValueError(f"{who}: bits must be 1-4, got {bits}")
     N, D = rotated.shape
@@ -238,9 +242,15 @@ def rvq_quant_pack(rotated: torch.Tensor, centroids1, boundaries1, boundaries2, 
         raise ValueError(f"{who}: D={D} exceeds the 1024 limit")
     if rotated.dtype != torch.float16:
         raise ValueError(f"{who}: rotated must be float16, got {rotated.dtype}")
-    c1 = _host_f32(centroids1, 1 << bits, "stage-1 centroids", who)
-    b1 = _host_f32(boundaries1, (1 << bits) - 1, "stage-1 boundaries", who)
-    b2 = _host_f32(boundaries2, (1 << bits) - 1, "stage-2 boundaries", who)
+    n_levels = 1 << bits
+    if _count(centroids1) != n_levels:
+        raise ValueError(f"{who}: expected {n_levels} stage-1 centroids for bits={bits}, got {_count(centroids1)}")
+    if _count(boundaries1) != n_levels - 1 or _count(boundaries2) != n_levels - 1:
+        raise ValueError(f"{who}: expected {n_levels - 1} boundaries per stage for bits={bits}, "
+                         f"got {_count(boundaries1)} (stage 1), {_count(boundaries2)} (stage 2)")
+    c1 = _host_f32(centroids1, n_levels, "stage-1 centroids", who)
+    b1 = _host_f32(boundaries1, n_levels - 1, "stage-1 boundaries", who)
+    b2 = _host_f32(boundaries2, n_levels - 1, "stage-2 boundaries", who)
     require_cuda(rotated, f"{who}: rotated")
     y = rotated.contiguous()
     nw = n_words_for(D, bits)

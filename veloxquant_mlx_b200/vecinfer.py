@@ -187,6 +187,11 @@ def dequantize_vq(indices: torch.Tensor, codebook: torch.Tensor, *, out_dtype=No
 def vecinfer_quantize_metal(x: torch.Tensor, codebook: torch.Tensor, sub_dim: int) -> torch.Tensor:
     """``x [..., D] -> int32 [..., D // sub_dim]`` under the reference's kernel-wrapper name
     (``metal/_vecinfer.py:181-222``)."""
+    D = x.shape[-1]
+    if D % sub_dim != 0:
+        raise ValueError(f"vecinfer_quantize_metal: D={D} not divisible by sub_dim={sub_dim}")
+    if codebook.ndim != 2 or codebook.shape[1] != sub_dim:
+        raise ValueError(f"vecinfer_quantize_metal: codebook must be [n_centroids, {sub_dim}], got {tuple(codebook.shape)}")
     return quantize_vq(x, codebook, sub_dim)
 
 
@@ -292,15 +297,15 @@ def fused_sdpa_vq(q_tilde: torch.Tensor, k_indices: torch.Tensor, k_codebook: to
     """
     if q_tilde.ndim != 4 or k_indices.ndim != 4:
         raise ValueError("fused_sdpa: q_tilde and k_indices must be 4D")
-    require_cuda(q_tilde, "fused_sdpa: q_tilde")
     B, H_q, S_q, D = q_tilde.shape
     _, H_kv, cap, n_sub = k_indices.shape
     S_kv = cap if s_kv is None else int(s_kv)
-    kcb, k_stacked, n_c, sub_dim = _codebook_f32(k_codebook.to(q_tilde.device), "fused_sdpa")
-    if n_sub * sub_dim != D:
-        raise ValueError(f"fused_sdpa: D={D} must equal n_sub*sub_dim={n_sub * sub_dim}.")
+    if k_codebook.ndim in (2, 3) and n_sub * k_codebook.shape[-1] != D:
+        raise ValueError(f"fused_sdpa: D={D} must equal n_sub*sub_dim={n_sub * k_codebook.shape[-1]}.")
     if H_q % H_kv != 0:
         raise ValueError(f"fused_sdpa: H_q={H_q} must be a multiple of H_kv={H_kv}.")
+    require_cuda(q_tilde, "fused_sdpa: q_tilde")
+    kcb, k_stacked, n_c, sub_dim = _codebook_f32(k_codebook.to(q_tilde.device), "fused_sdpa")
     if k_indices.dtype not in _INDEX_DTYPES:
         k_indices = k_indices.to(torch.int32)
     k_indices = k_indices.contiguous()
