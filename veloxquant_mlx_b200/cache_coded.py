@@ -168,7 +168,8 @@ class VecInferKVCache(_VQByteAccounting, StandaloneProtocol):
 
     def _ensure_index_capacity(self, B, H, n_tokens, device) -> None:
         if self._max_ctx is not None and n_tokens > self._max_ctx:
-            raise RuntimeError(f"VecInferKVCache: context of {n_tokens} tokens exceeds fused_sdpa_max_ctx={self._max_ctx}")
+            raise RuntimeError(f"VecInferKVCache: context length {n_tokens} exceeded fused_sdpa_max_ctx={self._max_ctx}.  "
+                               "Raise or unset KVCacheConfig.fused_sdpa_max_ctx.")
         cap = 0 if self._k_idx is None else self._k_idx.shape[2]
         if n_tokens <= cap:
             return
