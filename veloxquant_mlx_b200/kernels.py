@@ -27,6 +27,12 @@ def kivi_available() -> bool:
     return os.path.exists(_lib.LIB_PATH) and torch.cuda.is_available()
 
 
+def metal_available() -> bool:
+    """The reference's name for the backend probe (``metal/__init__.py:26-31``): here, whether the
+    native kernels can run."""
+    return kivi_available()
+
+
 _KNOBS = {"attend_stages": _lib.VQ_KNOB_ATTEND_STAGES, "attend_waves": _lib.VQ_KNOB_ATTEND_WAVES,
           "vq_search": _lib.VQ_KNOB_VQ_SEARCH, "attend_wait_test": _lib.VQ_KNOB_ATTEND_WAIT_TEST,
           "vq_wait_test": _lib.VQ_KNOB_VQ_WAIT_TEST}
@@ -697,7 +703,7 @@ def __getattr__(name: str):
 
 
 __all__ = [
-    "kivi_available", "tune", "attend_status", "quantize_status", "storage_bits", "kivi_group_quant_dequant", "kivi_quantize", "kivi_quantize_into",
+    "kivi_available", "metal_available", "tune", "attend_status", "quantize_status", "storage_bits", "kivi_group_quant_dequant", "kivi_quantize", "kivi_quantize_into",
     "scalar_decode_once", "kivi_decode_attend", "scalar_fused_decode_attend", "scalar_predecoded_attend",
     "scalar_fused_decode_attend_batched", "lse_merge",
     "turboquant_bit_pack", "turboquant_bit_unpack", *_DEFINED_ELSEWHERE,
