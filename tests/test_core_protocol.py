@@ -197,3 +197,49 @@ def test_cache_classes_define_the_public_surface_of_the_reference_classes():
         if "merge" in spec["properties"]:
             obj = object.__new__(cls)
             assert not hasattr(obj, "merge"), cls_name
+
+
+def test_kivi_byte_counters_follow_the_reference_class_trace():
+    """``KIVIKVCache``'s own accounting methods (host arithmetic) driven through the recorded call script
+    with the reference's flush policy: the frontier, compressed key / value bytes, fp16 bytes, residual
+    bytes and token count equal what the reference's ``KIVIKVCache`` held after each recorded call, the
+    trim's roll-back included (``tests/golden/cache_traces.npz``; group 8, residual 16, 2 bits)."""
+    import os
+
+    import numpy as np
+
+    from oracle import kivi as o_kivi
+    from veloxquant_mlx_b200.cache import KIVIKVCache
+
+    z = np.load(os.path.join(os.path.dirname(__file__), "golden", "cache_traces.npz"))
+    B, H, _, D = z["k"].shape
+    g, R = 8, 16
+    c = object.__new__(KIVIKVCache)                      # the accounting needs no device
+    c._group_size, c._b, c._shape_bhd = g, 2, (B, H, D)
+    c.offset = c._n_quantized = 0
+    c._key_bytes_compressed = c._value_bytes_compressed = 0
+    c._key_bytes_fp16 = c._value_bytes_fp16 = c._residual_fp16_bytes = c._tokens_seen = 0
+    checked = 0
+    for i, (op, a, b) in enumerate(z["script"].tolist()):
+        if op == 1:                                      # trim(a): the frontier snaps down to a group multiple
+            new_offset = c.offset - a
+            n_rolled = 0
+            if new_offset < c._n_quantized:
+                new_nq = (new_offset // g) * g
+                n_rolled, c._n_quantized = c._n_quantized - new_nq, new_nq
+            c.offset = new_offset
+            c._rollback_bytes(a, n_rolled)
+            continue
+        S = b - a
+        c.offset += S
+        boundary = o_kivi.quantization_boundary(c.offset, R, g)
+        n_flush = max(boundary - c._n_quantized, 0)
+        c._n_quantized += n_flush
+        c._account_bytes(B, H, S, D, n_flush)
+        if f"kivi_c_{i}" in z:
+            want = z[f"kivi_c_{i}"].tolist()   # offset, frontier, key bytes, value bytes, fp16 key bytes, residual bytes, tokens
+            got = [c.offset, c._n_quantized, c.compressed_key_bytes, c.compressed_value_bytes, c.fp16_key_bytes,
+                   c.residual_fp16_bytes, c._tokens_seen]
+            assert got == want, (i, got, want)
+            checked += 1
+    assert checked >= 10
